@@ -1,0 +1,224 @@
+"""glm_moe_dsa: MLA latent attention + DSA sparse-attention indexer + sigmoid MoE + MTP head.
+
+One model definition runs on the fp32 reference op set (CPU, gloo ranks) and on the
+sm_100a kernel op set (GPU, NCCL + in-kernel NVLink collectives); the op set and the
+communicator are injected.  Layer math follows `src/glm51_model.ts:577-942` (layer),
+`:979-1003` (stack), `:1009-1065` (MTP layer); tensor-parallel sharding follows `:178-232`.
+
+Collective placement (explicit, two per layer as in the reference):
+  o_proj partial  --all-reduce + residual add + RMSNorm-->  MLP input
+  MLP partial     --all-reduce + residual add + RMSNorm-->  next layer's attention input
+Under context parallelism (`cp`) each rank keeps every `W`-th token's KV row, attends
+with all heads over its shard and the partial (o, lse) are merged by log-sum-exp into a
+head-sharded output; the indexer's per-rank top-k lists are merged into the global top-k.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import List, Optional
+
+import torch
+
+from ..config import GlmMoeDsaConfig, PAGE_SIZE
+from ..parallel.dist import Comm, ParallelContext
+from .weights import LayerWeights, ModelWeights
+
+
+@dataclass
+class LayerCache:
+    kv: torch.Tensor                      # u8 [num_slots, kv_row_bytes]
+    idx: Optional[torch.Tensor] = None    # u8 [num_slots, index_head_dim + 4] (full-indexer layers)
+
+
+@dataclass
+class KVCacheTensors:
+    """Per-layer paged caches.  Slot = page_id * PAGE_SIZE + offset; with CP each rank
+    stores the rows of the tokens it owns, so a page id covers PAGE_SIZE * W tokens."""
+
+    layers: List[LayerCache]
+    num_pages: int
+    page_size: int = PAGE_SIZE
+
+    @classmethod
+    def allocate(cls, cfg: GlmMoeDsaConfig, num_pages: int, device, num_layers: Optional[int] = None) -> "KVCacheTensors":
+        n = cfg.num_hidden_layers + cfg.num_nextn_predict_layers if num_layers is None else num_layers
+        layers = []
+        for i in range(n):
+            kv = torch.zeros(num_pages * PAGE_SIZE, cfg.kv_row_bytes, dtype=torch.uint8, device=device)
+            idx = None
+            if cfg.indexer_is_full(i):
+                idx = torch.zeros(num_pages * PAGE_SIZE, cfg.index_row_bytes, dtype=torch.uint8, device=device)
+            layers.append(LayerCache(kv, idx))
+        return cls(layers, num_pages)
+
+    def nbytes(self) -> int:
+        return sum(l.kv.numel() + (l.idx.numel() if l.idx is not None else 0) for l in self.layers)
+
+
+@dataclass
+class StepState:
+    """Device-side metadata of one forward step (the reference's `ExecutionState`,
+    `src/execution-workspace.ts:71-390`)."""
+
+    input_ids: torch.Tensor               # [T]
+    positions: torch.Tensor               # [T] int32, global position of each token
+    batch_idx: torch.Tensor               # [T] int32, sequence (row of page_table) of each token
+    page_table: torch.Tensor              # [B, P] int32 page ids
+    logits_idx: Optional[torch.Tensor] = None   # token indices whose logits are wanted (None = all)
+    page_size: int = PAGE_SIZE
+    cp_world: int = 1
+    cp_rank: int = 0
+    # carried between layers: slots chosen by the last full-indexer layer
+    slots: Optional[torch.Tensor] = None
+    lengths: Optional[torch.Tensor] = None
+    max_kv_len: int = 0                   # host-side bound on positions + 1 (kernel planning)
+    extra: dict = field(default_factory=dict)
+
+    @property
+    def num_tokens(self) -> int:
+        return self.input_ids.shape[0]
+
+
+class GlmMoeDsaModel:
+    def __init__(self, cfg: GlmMoeDsaConfig, weights: ModelWeights, ctx: Optional[ParallelContext] = None,
+                 ops=None, comm: Optional[Comm] = None):
+        from ..ops import get_ops
+        self.cfg = cfg
+        self.w = weights
+        self.ctx = ctx or ParallelContext(device=weights.embed.device)
+        self.ops = ops or get_ops(cfg, weights.embed.device, self.ctx)
+        self.comm = comm or Comm(self.ctx)
+
+    # -- attention -------------------------------------------------------------------------
+    def attention(self, layer: int, lw: LayerWeights, x: torch.Tensor, st: StepState, cache: KVCacheTensors):
+        ops, comm, ctx = self.ops, self.comm, self.ctx
+        lc = cache.layers[layer]
+        qkv = ops.linear(x, lw.w_qkv_a)
+        cq, idx_w = ops.attn_pre(qkv, lw, st, lc)
+        qb = ops.linear(cq, lw.w_q_b)
+        q_abs, q_pe, q8, w_eff = ops.q_post(qb, lw, st, idx_w)
+        if lw.has_indexer:
+            pos, score = ops.indexer_topk(q8, w_eff, lc, st)
+            if ctx.cp and ctx.world > 1:
+                pos = comm.cp_merge_topk(ops, pos, score, self.cfg.index_topk)
+            st.slots, st.lengths = ops.topk_to_slots(pos, st, local_only=ctx.cp)
+        elif st.slots is None:
+            raise RuntimeError(f"layer {layer} shares indexer slots but no full-indexer layer ran before it")
+        if ctx.cp and ctx.world > 1:
+            q_abs = comm.all_gather(q_abs, dim=1)
+            q_pe = comm.all_gather(q_pe, dim=1)
+            o, lse = ops.sparse_mla(q_abs, q_pe, lc, st.slots, st.lengths)
+            o = comm.cp_merge_heads(ops, o, lse)
+        else:
+            o, _ = ops.sparse_mla(q_abs, q_pe, lc, st.slots, st.lengths)
+        return ops.linear(ops.v_expand(o, lw.w_v), lw.o_proj)
+
+    # -- MLP ----------------------------------------------------------------------------------
+    def mlp(self, lw: LayerWeights, y: torch.Tensor):
+        ops, ctx = self.ops, self.ctx
+        if lw.experts is None:
+            return ops.dense_mlp(y, lw)
+        if not (ctx.ep and ctx.world > 1):
+            return ops.moe_tp(y, lw)
+        return self._moe_ep(lw, y)
+
+    def _moe_ep(self, lw: LayerWeights, y: torch.Tensor):
+        """Expert parallelism: tokens are split across ranks, each token's hidden row is
+        dispatched to the ranks owning its experts, expert outputs come back weighted and
+        are summed at the token's home rank.  The result is written into this rank's
+        token slice of the partial sum, so the following all-reduce also acts as the
+        token all-gather."""
+        ops, comm, ctx = self.ops, self.comm, self.ctx
+        W, r = ctx.world, ctx.rank
+        T = y.shape[0]
+        per = -(-T // W)
+        lo, hi = min(T, r * per), min(T, (r + 1) * per)
+        x_loc = y[lo:hi]
+        ids, wts = ops.route(x_loc, lw)
+        E_per = self.cfg.n_routed_experts // W
+        owner = torch.div(ids.to(torch.int64), E_per, rounding_mode="floor")      # [t, k]
+        send_x, send_ids, send_w, send_tok = [], [], [], []
+        for peer in range(W):
+            hit = owner == peer
+            tok = hit.any(1).nonzero(as_tuple=True)[0]
+            send_tok.append(tok)
+            send_x.append(x_loc[tok])
+            send_ids.append(torch.where(hit[tok], ids[tok], torch.full_like(ids[tok], -1)))
+            send_w.append(torch.where(hit[tok], wts[tok], torch.zeros_like(wts[tok])))
+        rx = comm.all_to_all(send_x)
+        rid = comm.all_to_all(send_ids)
+        rw = comm.all_to_all(send_w)
+        outs = []
+        for peer in range(W):
+            if rx[peer].shape[0] == 0:
+                outs.append(torch.zeros(0, y.shape[1], dtype=y.dtype, device=y.device))
+                continue
+            outs.append(ops.moe_local_experts(rx[peer], lw.experts, rid[peer], rw[peer]).to(y.dtype))
+        back = comm.all_to_all(outs)
+        out = ops.shared_expert(y, lw).to(y.dtype) if lw.shared is not None else torch.zeros_like(y)
+        for peer in range(W):
+            if back[peer].shape[0]:
+                out[lo:hi].index_add_(0, send_tok[peer], back[peer].to(out.dtype))
+        return out
+
+    # -- stack -----------------------------------------------------------------------------------
+    def _layer(self, layer: int, lw: LayerWeights, partial, residual, st, cache, first: bool):
+        ops, comm = self.ops, self.comm
+        if first:
+            x, residual = ops.add_rmsnorm(partial, residual, lw.input_norm)
+        else:
+            x, residual = comm.allreduce_add_rmsnorm(ops, partial, residual, lw.input_norm, self.cfg.rms_norm_eps)
+        attn = self.attention(layer, lw, x, st, cache)
+        y, residual = comm.allreduce_add_rmsnorm(ops, attn, residual, lw.post_attn_norm, self.cfg.rms_norm_eps)
+        return self.mlp(lw, y), residual
+
+    def forward_hidden(self, st: StepState, cache: KVCacheTensors) -> torch.Tensor:
+        """Token ids -> final-normed hidden states [T, H] (replicated on every rank)."""
+        ops = self.ops
+        partial, residual = ops.embed(st.input_ids, self.w.embed), None
+        st.slots = st.lengths = None
+        for i in range(self.cfg.num_hidden_layers):
+            partial, residual = self._layer(i, self.w.layers[i], partial, residual, st, cache, first=(i == 0))
+        hidden, _ = self.comm.allreduce_add_rmsnorm(ops, partial, residual, self.w.final_norm, self.cfg.rms_norm_eps)
+        return hidden
+
+    def forward_mtp(self, st: StepState, cache: KVCacheTensors, prev_hidden: torch.Tensor, depth: int = 0) -> torch.Tensor:
+        """MTP layer: combines the embedding of the *next* token (st.input_ids) with the
+        previous hidden state, runs one decoder layer, returns the head-normed hidden.
+
+        When the MTP layer shares indexer slots, `st.slots` must still hold the slots of
+        the main model's last full-indexer layer for the same tokens.
+        """
+        cfg, ops = self.cfg, self.ops
+        li = cfg.num_hidden_layers + min(depth, cfg.num_nextn_predict_layers - 1)
+        lw = self.w.layers[li]
+        e = ops.rmsnorm(ops.embed(st.input_ids, self.w.embed), lw.enorm)
+        g = ops.rmsnorm(prev_hidden, lw.hnorm)
+        z = ops.linear(torch.cat([e, g], dim=-1), lw.eh_proj)
+        partial, residual = self._layer(li, lw, z, None, st, cache, first=True)
+        hidden, _ = self.comm.allreduce_add_rmsnorm(ops, partial, residual, lw.shared_head_norm, cfg.rms_norm_eps)
+        return hidden
+
+    def compute_logits(self, hidden: torch.Tensor, logits_idx: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Full-vocabulary logits (column-sharded lm_head, then all-gather)."""
+        if logits_idx is not None:
+            hidden = hidden[logits_idx.to(torch.int64)]
+        return self.comm.all_gather(self.ops.logits(hidden, self.w.lm_head), dim=-1)
+
+    def forward(self, st: StepState, cache: KVCacheTensors) -> torch.Tensor:
+        return self.compute_logits(self.forward_hidden(st, cache), st.logits_idx)
+
+
+def make_step(input_ids, positions, batch_idx, page_table, ctx: Optional[ParallelContext] = None,
+              logits_idx=None) -> StepState:
+    """Build a StepState from host lists / tensors on the model's device."""
+    ctx = ctx or ParallelContext()
+    dev = ctx.device
+    t = lambda v, dt: torch.as_tensor(v, dtype=dt, device=dev)
+    pos = t(positions, torch.int32)
+    return StepState(
+        input_ids=t(input_ids, torch.int64), positions=pos, batch_idx=t(batch_idx, torch.int32),
+        page_table=t(page_table, torch.int32), logits_idx=None if logits_idx is None else t(logits_idx, torch.int64),
+        cp_world=ctx.cp_world, cp_rank=ctx.cp_rank,
+        max_kv_len=int(max(positions)) + 1 if len(positions) else 0,
+    )

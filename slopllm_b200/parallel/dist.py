@@ -1,0 +1,164 @@
+"""Process-group plumbing: one process per GPU under `torch.distributed`.
+
+The reference drives N GPUs from one process and infers collectives from tensor tags
+(`src/parallel_ops.ts:2362-2470`).  Here every rank is a process (NCCL on GPU, gloo on
+CPU); the model calls the collectives it needs explicitly through :class:`Comm`.
+"""
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass
+from datetime import timedelta
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+
+@dataclass
+class ParallelContext:
+    rank: int = 0
+    world: int = 1
+    device: torch.device = torch.device("cpu")
+    cp: bool = False           # context parallelism: KV rows interleaved across ranks
+    ep: bool = False           # expert parallelism for routed experts
+    group: Optional[object] = None
+
+    @property
+    def is_distributed(self) -> bool:
+        return self.world > 1
+
+    @property
+    def cp_world(self) -> int:
+        return self.world if self.cp else 1
+
+    @property
+    def cp_rank(self) -> int:
+        return self.rank if self.cp else 0
+
+
+def init_from_env(backend: Optional[str] = None, cp: bool = False, ep: bool = False,
+                  timeout_s: float = 600.0) -> ParallelContext:
+    """Initialise from torchrun's RANK / LOCAL_RANK / WORLD_SIZE / MASTER_* variables."""
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", str(rank)))
+    use_cuda = torch.cuda.is_available() and backend != "gloo"
+    device = torch.device("cuda", local) if use_cuda else torch.device("cpu")
+    if use_cuda:
+        torch.cuda.set_device(device)
+    if world > 1 and not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29511")
+        kw = {"device_id": device} if use_cuda else {}
+        dist.init_process_group(backend or ("nccl" if use_cuda else "gloo"), rank=rank, world_size=world,
+                                timeout=timedelta(seconds=timeout_s), **kw)
+    return ParallelContext(rank, world, device, cp, ep, dist.group.WORLD if world > 1 else None)
+
+
+def shutdown() -> None:
+    if dist.is_initialized():
+        dist.destroy_process_group()
+
+
+class Comm:
+    """Collectives the model needs, in their unfused (library) form.
+
+    This is the always-correct baseline (NCCL on GPU, gloo on CPU); the fused NVLink
+    kernels in :mod:`slopllm_b200.parallel.fused` subclass it and override the hot ones.
+    Reference call sites: `src/parallel_ops.ts:219-239` (all-reduce), `:328-420`
+    (all-gather), `:2870-3111` (CP merge), `:4233-4330` (top-k owner merge).
+    """
+
+    def __init__(self, ctx: ParallelContext):
+        self.ctx = ctx
+
+    # -- basic ---------------------------------------------------------------------------
+    def all_reduce(self, x: torch.Tensor) -> torch.Tensor:
+        if self.ctx.world == 1:
+            return x
+        y = x.contiguous().clone()
+        dist.all_reduce(y, group=self.ctx.group)
+        return y
+
+    def all_gather(self, x: torch.Tensor, dim: int = -1) -> torch.Tensor:
+        if self.ctx.world == 1:
+            return x
+        parts = [torch.empty_like(x) for _ in range(self.ctx.world)]
+        dist.all_gather(parts, x.contiguous(), group=self.ctx.group)
+        return torch.cat(parts, dim=dim)
+
+    def all_gather_list(self, x: torch.Tensor) -> List[torch.Tensor]:
+        if self.ctx.world == 1:
+            return [x]
+        parts = [torch.empty_like(x) for _ in range(self.ctx.world)]
+        dist.all_gather(parts, x.contiguous(), group=self.ctx.group)
+        return parts
+
+    def all_to_all(self, send: List[torch.Tensor]) -> List[torch.Tensor]:
+        """send[i] goes to rank i; shapes may differ per pair but must be known to both
+        sides (callers exchange counts first)."""
+        W = self.ctx.world
+        if W == 1:
+            return send
+        if self.ctx.device.type == "cuda":
+            raise RuntimeError("variable all_to_all goes through all_to_all_counts on CUDA")
+        recv: List[Optional[torch.Tensor]] = [None] * W
+        # gloo has no all_to_all: W broadcast-free rounds of paired send/recv
+        counts = self.all_gather_list(torch.tensor([s.shape[0] for s in send], dtype=torch.int64))
+        reqs = []
+        for peer in range(W):
+            n = int(counts[peer][self.ctx.rank])
+            recv[peer] = torch.empty((n,) + tuple(send[peer].shape[1:]), dtype=send[peer].dtype)
+            if peer == self.ctx.rank:
+                recv[peer].copy_(send[peer])
+                continue
+            reqs.append(dist.isend(send[peer].contiguous(), peer, group=self.ctx.group))
+            reqs.append(dist.irecv(recv[peer], peer, group=self.ctx.group))
+        for r in reqs:
+            r.wait()
+        return recv  # type: ignore[return-value]
+
+    def barrier(self) -> None:
+        if self.ctx.world > 1:
+            dist.barrier(group=self.ctx.group)
+
+    # -- fused-op shaped interface (overridden by the NVLink kernels) -------------------------
+    def allreduce_add_rmsnorm(self, ops, partial, residual, weight, eps):
+        """sum over ranks of `partial`, add to `residual`, RMSNorm.  Returns (normed, residual')."""
+        return ops.add_rmsnorm(self.all_reduce(partial), residual, weight, eps)
+
+    def cp_merge_heads(self, ops, o: torch.Tensor, lse: torch.Tensor):
+        """Merge per-rank attention partials over all heads and return this rank's head
+        slice `[T, h/W, R]` (log-sum-exp combine; `csrc/glm_context_parallel.cu:277-540`)."""
+        W, r = self.ctx.world, self.ctx.rank
+        if W == 1:
+            return o
+        os_ = torch.stack(self.all_gather_list(o.to(torch.float32)))
+        ls_ = torch.stack(self.all_gather_list(lse.to(torch.float32)))
+        merged, _ = ops.merge_attention_partials(os_, ls_)
+        hl = o.shape[1] // W
+        return merged[:, r * hl:(r + 1) * hl].contiguous()
+
+    def cp_merge_topk(self, ops, pos: torch.Tensor, score: torch.Tensor, top_k: int) -> torch.Tensor:
+        """Merge per-rank local top-k candidate lists (global positions + scores, -1 padded)
+        into the global top-k, ascending by position (`src/parallel_ops.ts:4233-4330`)."""
+        if self.ctx.world == 1:
+            return pos
+        allp = torch.cat(self.all_gather_list(pos), dim=1).to(torch.int64)
+        alls = torch.cat(self.all_gather_list(score.to(torch.float32)), dim=1)
+        valid = allp >= 0
+        n_valid = valid.sum(1)
+        T = pos.shape[0]
+        out = torch.full((T, top_k), -1, dtype=torch.int32, device=pos.device)
+        for t in range(T):
+            p, s = allp[t][valid[t]], alls[t][valid[t]]
+            if int(n_valid[t]) > top_k:
+                # highest score first, ties to the lower position
+                order = torch.sort(p).indices
+                p, s = p[order], s[order]
+                keep = torch.sort(s, descending=True, stable=True).indices[:top_k]
+                p = p[keep]
+            p = torch.sort(p).values
+            out[t, : p.numel()] = p.to(torch.int32)
+        return out

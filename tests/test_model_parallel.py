@@ -1,0 +1,54 @@
+"""Plumbing model (tiny glm_moe_dsa, fp32 dequantised NVFP4) on CPU ranks over gloo:
+TP=2, CP=2 and EP=2 must reproduce the single-rank greedy tokens.
+Mirrors the reference's TP=1 vs TP=2 / CP on-off model tests (`tests/test_glm51.ts`)."""
+import torch
+
+from slopllm_b200.config import GlmMoeDsaConfig
+from slopllm_b200.models.glm_moe_dsa import GlmMoeDsaModel, KVCacheTensors, make_step
+from slopllm_b200.models.weights import random_model
+from slopllm_b200.parallel.dist import ParallelContext, init_from_env
+
+from mp_util import run_ranks
+
+PROMPT, NEW = 128, 32
+
+
+def _greedy(rank, world, cp, ep, prompt_len, new):
+    ctx = init_from_env("gloo", cp=cp, ep=ep) if world > 1 else ParallelContext()
+    cfg = GlmMoeDsaConfig.tiny()
+    w = random_model(cfg, 0, tp_rank=ctx.rank, tp_world=ctx.world, ep=ep)
+    m = GlmMoeDsaModel(cfg, w, ctx)
+    cache = KVCacheTensors.allocate(cfg, 8, "cpu")
+    g = torch.Generator().manual_seed(0)
+    prompt = torch.randint(0, cfg.vocab_size, (prompt_len,), generator=g).tolist()
+    pt = [[0, 1, 2, 3, 4, 5, 6, 7]]
+    st = make_step(prompt, list(range(prompt_len)), [0] * prompt_len, pt, ctx, logits_idx=[prompt_len - 1])
+    toks = [int(m.forward(st, cache).argmax(-1))]
+    for i in range(new - 1):
+        st = make_step([toks[-1]], [prompt_len + i], [0], pt, ctx)
+        toks.append(int(m.forward(st, cache).argmax(-1)))
+    return toks
+
+
+def test_single_rank_deterministic():
+    a = _greedy(0, 1, False, False, PROMPT, 8)
+    b = _greedy(0, 1, False, False, PROMPT, 8)
+    assert a == b and len(set(a)) > 1
+
+
+def test_tp2_matches_tp1():
+    ref = _greedy(0, 1, False, False, PROMPT, NEW)
+    out = run_ranks(_greedy, 2, False, False, PROMPT, NEW)
+    assert out[0] == out[1] == ref
+
+
+def test_cp2_matches_single():
+    ref = _greedy(0, 1, False, False, PROMPT, 12)
+    out = run_ranks(_greedy, 2, True, False, PROMPT, 12)
+    assert out[0] == out[1] == ref
+
+
+def test_ep2_matches_single():
+    ref = _greedy(0, 1, False, False, 40, 6)
+    out = run_ranks(_greedy, 2, False, True, 40, 6)
+    assert out[0] == out[1] == ref
