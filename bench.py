@@ -1,0 +1,277 @@
+#!/usr/bin/env python
+"""Headline benchmark: GLM-5-class NVFP4 decode throughput (tokens/s), tensor parallel over N GPUs.
+
+`python bench.py --gpus N --steps K --warmup W`  (N > 1: launched under torch.distributed.run,
+one rank per GPU).  Synthetic token ids, random-init NVFP4 weights of the GLM-5 architecture
+(78 layers when they fit in N x 180 GB; otherwise the largest layer count that fits, named in
+`config.layers`).  Prints ONE JSON line on rank 0.
+
+value      : aggregate decode tokens/s at batch 8, MTP off, timed on the device with CUDA events
+             around K CUDA-graph replays (max over ranks).
+e2e.value  : the same K steps through the public `Engine.decode_step` API, each step copying
+             its inputs host->device from pinned memory and reading the sampled tokens back.
+details    : batch 1 decode, MTP=3 verification-step rates, prefill throughput.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+BASELINE_BS8_TOK_S = 418.9        # reference, 8x RTX PRO 6000, concurrency 8, MTP 3 (VLLM-bench.md:18)
+BASELINE_BS1_TOK_S = 161.9        # reference, concurrency 1, MTP 3
+BASELINE_BS1_STEPS_S = 60.8       # reference verification steps/s at concurrency 1
+BASELINE_BS8_STEPS_S = 163.5
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=32)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--layers", type=int, default=0, help="override the layer count (0 = as many as fit, up to 78)")
+    ap.add_argument("--prompt-len", type=int, default=4096)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--mtp", type=int, default=3)
+    ap.add_argument("--no-fused", action="store_true", help="use the NCCL collectives instead of the NVLink kernels")
+    ap.add_argument("--skip-details", action="store_true")
+    ap.add_argument("--tiny", action="store_true", help="small model (smoke runs)")
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """Samples `nvidia-smi` clocks / throttle reasons of one GPU during the timed region."""
+
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.path = f"/tmp/slopllm_clocks_{os.getpid()}.csv"
+
+    def start(self):
+        try:
+            self.f = open(self.path, "w")
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=self.f,
+                                         stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.f.close()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in open(self.path):
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        os.unlink(self.path)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def layer_bytes(cfg, world: int) -> int:
+    """Per-rank bytes of one MoE layer under tensor parallelism (NVFP4 experts, bf16 attention)."""
+    H, I, E = cfg.hidden_size, cfg.moe_intermediate_size, cfg.n_routed_experts
+    nv = lambda n: n * 9 // 16
+    experts = nv((E + 1) * 3 * I * H) // world
+    attn = 2 * (cfg.q_lora_rank * H + (cfg.kv_lora_rank + cfg.qk_rope_head_dim + cfg.index_head_dim + cfg.index_n_heads) * H
+                + cfg.index_n_heads * cfg.index_head_dim * cfg.q_lora_rank
+                + (cfg.num_attention_heads * (cfg.qk_head_dim) * cfg.q_lora_rank
+                   + cfg.num_attention_heads * (cfg.qk_nope_head_dim + cfg.v_head_dim) * cfg.kv_lora_rank) // world)
+    o = nv(cfg.num_attention_heads * cfg.v_head_dim * H) // world
+    return experts + attn + o + 2 * E * H
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable": "reference is a Node.js/N-API addon compiled only for sm_120a "
+                          "with an empty vendor/flashinfer submodule; `pip install /root/reference` fails: no setup.py/pyproject.toml"}))
+        return 0
+
+    import torch
+    import torch.distributed as dist
+    from slopllm_b200.config import GlmMoeDsaConfig
+    from slopllm_b200.models.glm_moe_dsa import GlmMoeDsaModel
+    from slopllm_b200.models.weights import random_model
+    from slopllm_b200.parallel.dist import init_from_env
+    from slopllm_b200.parallel.fused import make_comm
+    from slopllm_b200.runtime.engine import Engine
+    from slopllm_b200.ops import native as N
+
+    ctx = init_from_env()
+    W, rank, dev = ctx.world, ctx.rank, ctx.device
+    assert dev.type == "cuda", "bench.py needs a GPU"
+    torch.manual_seed(0)
+
+    if args.tiny:
+        cfg = GlmMoeDsaConfig.glm5(num_layers=args.layers or 4)
+    else:
+        probe = GlmMoeDsaConfig.glm5(78)
+        per_layer = layer_bytes(probe, W)
+        free, total = torch.cuda.mem_get_info()
+        fixed = 2 * probe.vocab_size * probe.hidden_size * (1 + 1 / W) + 14e9      # embed + lm_head shard + KV/workspace
+        fit = int((free - fixed) // per_layer) - 1                                  # one more for the MTP layer
+        L = args.layers or max(4, min(78, fit))
+        cfg = GlmMoeDsaConfig.glm5(num_layers=L)
+    L = cfg.num_hidden_layers
+    t0 = time.time()
+    weights = random_model(cfg, 0, dev, torch.bfloat16, rank, W, exact=False, with_mtp=args.mtp > 0)
+    torch.cuda.synchronize()
+    t_init = time.time() - t0
+    comm = make_comm(ctx, cfg, fused=not args.no_fused)
+    model = GlmMoeDsaModel(cfg, weights, ctx, comm=comm)
+    B, P, K, Wu = args.batch, args.prompt_len, args.steps, args.warmup
+    total_steps = 4 * (K + Wu) + 64
+    max_len = P + total_steps * (args.mtp + 1) + 64
+    pages = (B + 1) * (-(-max_len // 64) + 1)
+    eng = Engine(cfg, model, pages, max_batch=B, max_seq_len=max_len, mtp=args.mtp)
+
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(0, cfg.vocab_size, (P,), generator=g).tolist() for _ in range(B)]
+
+    def sync_barrier():
+        torch.cuda.synchronize()
+        if W > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms: float) -> float:
+        if W == 1:
+            return ms
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- prefill (outside the timed decode region; reported in details) ----
+    seqs = [eng.kv.new_sequence() for _ in range(B)]
+    sync_barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    last, hid = eng.prefill(seqs, prompts, chunk_size=min(P, 4096), want_hidden=True)
+    e1.record()
+    sync_barrier()
+    prefill_ms = max_over_ranks(e0.elapsed_time(e1))
+
+    def timed_decode(seq_group, last_tokens, label):
+        """K timed `decode_step` calls through the public API (e2e), then K device-timed
+        graph replays of the same step."""
+        cur = list(last_tokens)
+        for _ in range(Wu):
+            cur = eng.decode_step(seq_group, cur)
+        n0, h0, d0 = N.launch_count(), eng.h2d_bytes, eng.d2h_bytes
+        sync_barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(K):
+            cur = eng.decode_step(seq_group, cur)
+        b.record()
+        sync_barrier()
+        e2e_ms = max_over_ranks(a.elapsed_time(b)) / K
+        h2d, d2h = (eng.h2d_bytes - h0) // K, (eng.d2h_bytes - d0) // K
+        # device-only: replay the captured graph K times (inputs stay as last uploaded)
+        key = next(k for k in eng.graphs.entries if k[0] == "decode" and k[1] == len(seq_group)
+                   and eng.graphs.entries[k].graph is not None)
+        gr = eng.graphs.entries[key]
+        for _ in range(Wu):
+            gr.graph.replay()
+        sync_barrier()
+        a.record()
+        for _ in range(K):
+            gr.graph.replay()
+        b.record()
+        sync_barrier()
+        dev_ms = max_over_ranks(a.elapsed_time(b)) / K
+        return {"label": label, "ms_per_step": dev_ms, "e2e_ms_per_step": e2e_ms, "h2d": h2d, "d2h": d2h,
+                "launches_per_step": gr.launches, "last": cur}
+
+    sampler = ClockSampler(dev.index or 0)
+    if rank == 0:
+        sampler.start()
+    r8 = timed_decode(seqs, last, f"bs{B}")
+    clocks = sampler.stop() if rank == 0 else {}
+
+    details = {"prefill_tok_s": B * P / (prefill_ms / 1e3), "prefill_ms": prefill_ms, "weights_init_s": t_init,
+               "weights_gb_per_rank": weights.nbytes() / 1e9}
+    if not args.skip_details:
+        r1 = timed_decode(seqs[:1], r8["last"][:1], "bs1")
+        details["bs1"] = {"tok_s": 1e3 / r1["ms_per_step"], "ms_per_step": r1["ms_per_step"],
+                          "e2e_tok_s": 1e3 / r1["e2e_ms_per_step"], "launches_per_step": r1["launches_per_step"],
+                          "vs_ref_mtp3_tok_s": (1e3 / r1["ms_per_step"]) / BASELINE_BS1_TOK_S if L == 78 else None}
+        if args.mtp > 0:
+            for grp, name, ref in ((seqs[:1], "bs1", BASELINE_BS1_STEPS_S), (seqs, f"bs{B}", BASELINE_BS8_STEPS_S)):
+                lt = r1["last"] if name == "bs1" else r8["last"]
+                hs = [torch.zeros(1, cfg.hidden_size, dtype=torch.bfloat16, device=dev) for _ in grp]
+                seed = eng.mtp_seed(grp, lt, hs)
+                acc_tokens = 0
+                for _ in range(Wu):
+                    _, lt, seed = eng.mtp_decode_step(grp, lt, seed)
+                sync_barrier()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                for _ in range(K):
+                    acc, lt, seed = eng.mtp_decode_step(grp, lt, seed)
+                    acc_tokens += sum(len(x) for x in acc)
+                b.record()
+                sync_barrier()
+                ms = max_over_ranks(a.elapsed_time(b)) / K
+                details[f"mtp{args.mtp}_{name}"] = {
+                    "steps_s": 1e3 / ms, "ms_per_step": ms, "tok_s": acc_tokens / (ms * K / 1e3),
+                    "accept_len": acc_tokens / (K * len(grp)),
+                    "vs_ref_steps_s": (1e3 / ms) / ref if L == 78 else None,
+                    "note": "random-init weights: drafts are almost never accepted, so tok/s ~= steps/s * batch"}
+    from slopllm_b200.ops import tcgen05
+    tcgen05.check_errors(dev)
+    comm.check_status()
+
+    tok_s = B * 1e3 / r8["ms_per_step"]
+    out = {
+        "metric": f"decode_tok_s_bs{B}", "value": tok_s, "unit": "tokens/s", "n_gpus": W, "steps": K, "warmup": Wu,
+        "ms_per_step": r8["ms_per_step"], "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": tok_s / BASELINE_BS8_TOK_S if L == 78 else None, "dtype": "bf16 activations, NVFP4/bf16 weights",
+        "data": "synthetic token ids, random-init NVFP4 weights",
+        "config": {"model": "GLM-5-class glm_moe_dsa NVFP4", "layers": L, "layers_full_model": 78,
+                   "global_batch": B, "seq_len": P, "parallelism": f"tp{W}", "mtp": 0,
+                   "l2": "inputs larger than L2: every step streams the active weights (GBs per rank) from HBM",
+                   "baseline_note": "vs_baseline = value / 418.9 (reference bs8 MTP3 on 8x RTX PRO 6000); null when fewer than 78 layers fit"},
+        "clocks": clocks,
+        "e2e": {"value": B * 1e3 / r8["e2e_ms_per_step"], "unit": "tokens/s", "h2d_bytes_per_step": r8["h2d"],
+                "d2h_bytes_per_step": r8["d2h"]},
+        "gpu_launches": r8["launches_per_step"] * K,
+        "details": details,
+    }
+    if rank == 0:
+        print(json.dumps(out))
+    if W > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -199,7 +199,7 @@ class GlmMoeDsaConfig:
         types = ["full" if (i < 3 or (i - 3) % 4 == 0) else "shared" for i in range(num_layers)]
         return cls(
             num_hidden_layers=num_layers, n_group=8, topk_group=4,
-            indexer_types=types, index_share_for_mtp_iteration=True,
+            indexer_types=types, index_share_for_mtp_iteration=False,
             first_k_dense_replace=min(3, num_layers),
             quant_o_proj=quant_all, quant_dense_mlp=quant_all,
             eos_token_ids=[154820, 154827, 154829],

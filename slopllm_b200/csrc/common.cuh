@@ -1,0 +1,150 @@
+// Shared device helpers for the sm_100a kernels: vector loads, warp/block reductions,
+// E2M1 / E4M3 decode, bounded flag waits.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <cfloat>
+#include <cstdint>
+
+#define SL_API extern "C" __attribute__((visibility("default")))
+
+typedef __nv_bfloat16 bf16;
+typedef __nv_bfloat162 bf162;
+
+#define SL_LAUNCH_CHECK() (int)cudaGetLastError()
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Block-wide sum; `scratch` holds >= 33 floats.  All threads get the result.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < nw ? scratch[lane] : 0.f;
+        t = warp_sum(t);
+        if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < nw ? scratch[lane] : -FLT_MAX;
+        t = warp_max(t);
+        if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}
+
+__device__ __forceinline__ uint4 ldg_nc_16(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint2 ldg_nc_8(const void* p) {
+    uint2 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ float2 bf162_to_f2(uint32_t u) {
+    return make_float2(__uint_as_float(u << 16), __uint_as_float(u & 0xffff0000u));
+}
+__device__ __forceinline__ uint32_t f2_to_bf162(float a, float b) {
+    bf162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// Four packed bytes (8 E2M1 codes, low nibble = even element) -> 8 halves as 4 half2.
+__device__ __forceinline__ void e2m1x8_to_half2x4(uint32_t packed, __half2 out[4]) {
+    uint32_t r0, r1, r2, r3;
+    asm volatile(
+        "{\n"
+        ".reg .b8 b0, b1, b2, b3;\n"
+        "mov.b32 {b0, b1, b2, b3}, %4;\n"
+        "cvt.rn.f16x2.e2m1x2 %0, b0;\n"
+        "cvt.rn.f16x2.e2m1x2 %1, b1;\n"
+        "cvt.rn.f16x2.e2m1x2 %2, b2;\n"
+        "cvt.rn.f16x2.e2m1x2 %3, b3;\n"
+        "}\n"
+        : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(packed));
+    out[0] = *reinterpret_cast<__half2*>(&r0);
+    out[1] = *reinterpret_cast<__half2*>(&r1);
+    out[2] = *reinterpret_cast<__half2*>(&r2);
+    out[3] = *reinterpret_cast<__half2*>(&r3);
+}
+
+__device__ __forceinline__ float e4m3_to_float(uint8_t b) {
+    __half_raw h = __nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)b, __NV_E4M3);
+    return __half2float(*reinterpret_cast<__half*>(&h));
+}
+__device__ __forceinline__ float2 e4m3x2_to_float2(uint16_t b) {
+    __half2_raw h = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)b, __NV_E4M3);
+    return __half22float2(*reinterpret_cast<__half2*>(&h));
+}
+__device__ __forceinline__ uint8_t float_to_e4m3(float v) {
+    return (uint8_t)__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3);
+}
+
+// Power-of-two scale >= max(amax, 1e-4) / 448 (indexer K / Q rows).
+__device__ __forceinline__ float pow2_scale_ceil(float amax) {
+    float raw = fmaxf(amax, 1e-4f) / 448.f;
+    uint32_t bits = __float_as_uint(raw);
+    if (bits & 0x007fffffu) bits = (bits + 0x00800000u) & 0x7f800000u;
+    return __uint_as_float(bits);
+}
+
+// ---- bounded waits on flags written by other GPUs ---------------------------------------------
+// Every wait gives up after `max_spins` polls, records where it stopped in `status`
+// (status[0] = code, [1] = site, [2] = expected, [3] = observed) and lets the kernel
+// finish normally; the host reads the status word after the step.
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_relaxed_sys_u32(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ bool wait_flag_geq(const uint32_t* flag, uint32_t target, uint32_t max_spins,
+                                              int* status, int site) {
+    uint32_t seen = 0;
+    for (uint32_t i = 0; i < max_spins; ++i) {
+        seen = ld_acquire_sys_u32(flag);
+        if ((int32_t)(seen - target) >= 0) return true;
+        if (i > 64) __nanosleep(i > 4096 ? 256 : 32);
+    }
+    if (status != nullptr && atomicCAS(status, 0, 1) == 0) {
+        status[1] = site;
+        status[2] = (int)target;
+        status[3] = (int)seen;
+    }
+    return false;
+}

@@ -1,0 +1,516 @@
+// Normalisation, rotary, cache-row packing, routing top-k and small glue kernels (sm_100a).
+//
+// Covers what the reference spreads over `csrc/glm_ops.cu` (rmsnorm :210, fused add+rmsnorm
+// :358, rotary :1820-1876, layernorm :1029, route_top8 :2343, silu_and_mul :994,
+// rotate_input_ids :3308), `csrc/glm_flash.cu:1081-1230` (packed ckv row) and
+// `csrc/glm_indexer.cu:303-376,1338` (topk_to_slots, indexer Q quantise), fused along the
+// data flow of one decoder layer.
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------------------------
+// embedding lookup: out[t, :] = table[ids[t], :]
+__global__ void embed_kernel(bf16* __restrict__ out, const int64_t* __restrict__ ids, const bf16* __restrict__ table,
+                             int H) {
+    const int t = blockIdx.x;
+    const uint4* src = reinterpret_cast<const uint4*>(table + (size_t)ids[t] * H);
+    uint4* dst = reinterpret_cast<uint4*>(out + (size_t)t * H);
+    for (int i = threadIdx.x; i < H / 8; i += blockDim.x) dst[i] = src[i];
+}
+
+SL_API int sl_embed(void* out, const void* ids, const void* table, int T, int H, cudaStream_t s) {
+    if (T == 0) return 0;
+    embed_kernel<<<T, 256, 0, s>>>((bf16*)out, (const int64_t*)ids, (const bf16*)table, H);
+    return SL_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------------------------------------
+// residual' = residual + x (fp32) ; out = rmsnorm(residual') * w (bf16).
+// x is bf16 or fp32 (`x_f32`); residual_in may be null (first layer).  H <= 16384.
+template <bool XF32>
+__global__ void add_rmsnorm_kernel(bf16* __restrict__ out, float* __restrict__ res_out, const void* __restrict__ xin,
+                                   const float* __restrict__ res_in, const bf16* __restrict__ w, int H, float eps) {
+    extern __shared__ float row[];
+    __shared__ float scratch[33];
+    const int t = blockIdx.x;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = XF32 ? ((const float*)xin)[(size_t)t * H + i] : __bfloat162float(((const bf16*)xin)[(size_t)t * H + i]);
+        if (res_in != nullptr) v += res_in[(size_t)t * H + i];
+        row[i] = v;
+        ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = rsqrtf(ss / (float)H + eps);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float v = row[i];
+        if (res_out != nullptr) res_out[(size_t)t * H + i] = v;
+        out[(size_t)t * H + i] = __float2bfloat16(v * inv * __bfloat162float(w[i]));
+    }
+}
+
+SL_API int sl_add_rmsnorm(void* out, void* res_out, const void* x, const void* res_in, const void* w, int T, int H,
+                          float eps, int x_f32, cudaStream_t s) {
+    if (T == 0) return 0;
+    const size_t smem = (size_t)H * sizeof(float);
+    if (x_f32)
+        add_rmsnorm_kernel<true><<<T, 512, smem, s>>>((bf16*)out, (float*)res_out, x, (const float*)res_in, (const bf16*)w, H, eps);
+    else
+        add_rmsnorm_kernel<false><<<T, 512, smem, s>>>((bf16*)out, (float*)res_out, x, (const float*)res_in, (const bf16*)w, H, eps);
+    return SL_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------------------------------------
+// Rotary helper: rotate pair index i (0 <= i < rope_dim/2) of a vector held in shared memory.
+__device__ __forceinline__ void rope_pair(float* v, int i, int rope_dim, int pos, float theta, bool interleave) {
+    const float inv_freq = 1.0f / powf(theta, (float)(2 * i) / (float)rope_dim);
+    const float ang = (float)pos * inv_freq;
+    float sn, cs;
+    sincosf(ang, &sn, &cs);
+    const int ia = interleave ? 2 * i : i;
+    const int ib = interleave ? 2 * i + 1 : i + rope_dim / 2;
+    const float a = v[ia], b = v[ib];
+    v[ia] = a * cs - b * sn;
+    v[ib] = a * sn + b * cs;
+}
+
+struct AttnPreParams {
+    const bf16* qkv;          // [T, ld]
+    int ld;
+    int q_lora, kv_lora, rope_dim, idx_dim, idx_heads;   // idx_dim == 0: no indexer in this layer
+    const bf16 *q_norm_w, *kv_norm_w, *idx_ln_w, *idx_ln_b;
+    float eps, theta;
+    int rope_interleave, idx_rope_interleave;
+    const int* positions;     // [T]
+    const int* batch_idx;     // [T]
+    const int* page_table;    // [B, pt_stride]
+    int pt_stride, page_size, cp_world, cp_rank;
+    int kv_group;             // values per fp8 scale
+    uint8_t* kv_cache;        // [slots, kv_row_bytes]
+    uint8_t* idx_cache;       // [slots, idx_dim + 4]
+    bf16* cq_out;             // [T, q_lora]
+    float* idx_w_out;         // [T, idx_heads]
+};
+
+// One block per token: q_a RMSNorm; ckv RMSNorm -> fp8 groups; k_pe RoPE; packed row write;
+// indexer key LayerNorm -> RoPE -> fp8 (power-of-two scale) row write; indexer head weights.
+__global__ void attn_pre_kernel(AttnPreParams p) {
+    extern __shared__ float sm[];
+    __shared__ float scratch[33];
+    const int t = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
+    const bf16* row = p.qkv + (size_t)t * p.ld;
+    const int pos = p.positions[t];
+
+    // --- c_q = rmsnorm(q_a) ---
+    float ss = 0.f;
+    for (int i = tid; i < p.q_lora; i += nt) {
+        const float v = __bfloat162float(row[i]);
+        sm[i] = v;
+        ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    float inv = rsqrtf(ss / (float)p.q_lora + p.eps);
+    for (int i = tid; i < p.q_lora; i += nt)
+        p.cq_out[(size_t)t * p.q_lora + i] = __float2bfloat16(sm[i] * inv * __bfloat162float(p.q_norm_w[i]));
+    __syncthreads();
+
+    // --- where does this token's row live on this rank? ---
+    bool owned = true;
+    int local = pos;
+    if (p.cp_world > 1) {
+        owned = (pos % p.cp_world) == p.cp_rank;
+        local = pos / p.cp_world;
+    }
+    const int page = p.page_table[(size_t)p.batch_idx[t] * p.pt_stride + local / p.page_size];
+    const size_t slot = (size_t)page * p.page_size + (local % p.page_size);
+
+    // --- ckv = rmsnorm(kv_a[:R]) rounded to bf16, k_pe = rope(kv_a[R:R+Dr]) ---
+    const bf16* kv = row + p.q_lora;
+    float* ckv = sm;                         // [kv_lora]
+    float* kpe = sm + p.kv_lora;             // [rope_dim]
+    ss = 0.f;
+    for (int i = tid; i < p.kv_lora; i += nt) {
+        const float v = __bfloat162float(kv[i]);
+        ckv[i] = v;
+        ss += v * v;
+    }
+    for (int i = tid; i < p.rope_dim; i += nt) kpe[i] = __bfloat162float(kv[p.kv_lora + i]);
+    ss = block_sum(ss, scratch);
+    inv = rsqrtf(ss / (float)p.kv_lora + p.eps);
+    for (int i = tid; i < p.kv_lora; i += nt)
+        ckv[i] = __bfloat162float(__float2bfloat16(ckv[i] * inv * __bfloat162float(p.kv_norm_w[i])));
+    if (tid < p.rope_dim / 2) rope_pair(kpe, tid, p.rope_dim, pos, p.theta, p.rope_interleave != 0);
+    __syncthreads();
+
+    if (owned) {
+        const int ngroups = p.kv_lora / p.kv_group;
+        const int row_bytes = p.kv_lora + 4 * ngroups + 2 * p.rope_dim;
+        uint8_t* dst = p.kv_cache + slot * row_bytes;
+        // one warp per quantisation group
+        const int warp = tid >> 5, lane = tid & 31, nw = nt >> 5;
+        for (int g = warp; g < ngroups; g += nw) {
+            float amax = 0.f;
+            for (int i = lane; i < p.kv_group; i += 32) amax = fmaxf(amax, fabsf(ckv[g * p.kv_group + i]));
+            amax = warp_max(amax);
+            const float scale = fmaxf(amax / 448.f, FLT_MIN);
+            if (lane == 0) reinterpret_cast<float*>(dst + p.kv_lora)[g] = scale;
+            for (int i = lane; i < p.kv_group; i += 32)
+                dst[g * p.kv_group + i] = float_to_e4m3(ckv[g * p.kv_group + i] / scale);
+        }
+        bf16* dpe = reinterpret_cast<bf16*>(dst + p.kv_lora + 4 * ngroups);
+        for (int i = tid; i < p.rope_dim; i += nt) dpe[i] = __float2bfloat16(kpe[i]);
+    }
+    __syncthreads();
+
+    // --- indexer key and head weights ---
+    if (p.idx_dim > 0) {
+        const bf16* ik = kv + p.kv_lora + p.rope_dim;
+        float* kbuf = sm;
+        float s1 = 0.f;
+        for (int i = tid; i < p.idx_dim; i += nt) {
+            const float v = __bfloat162float(ik[i]);
+            kbuf[i] = v;
+            s1 += v;
+        }
+        const float mean = block_sum(s1, scratch) / (float)p.idx_dim;
+        float s2 = 0.f;
+        for (int i = tid; i < p.idx_dim; i += nt) {
+            const float d = kbuf[i] - mean;
+            s2 += d * d;
+        }
+        const float var = block_sum(s2, scratch) / (float)p.idx_dim;
+        const float rstd = rsqrtf(var + 1e-6f);
+        for (int i = tid; i < p.idx_dim; i += nt)
+            kbuf[i] = (kbuf[i] - mean) * rstd * __bfloat162float(p.idx_ln_w[i]) + __bfloat162float(p.idx_ln_b[i]);
+        __syncthreads();
+        if (tid < p.rope_dim / 2) rope_pair(kbuf, tid, p.rope_dim, pos, p.theta, p.idx_rope_interleave != 0);
+        __syncthreads();
+        float amax = 0.f;
+        for (int i = tid; i < p.idx_dim; i += nt) {
+            kbuf[i] = __bfloat162float(__float2bfloat16(kbuf[i]));
+            amax = fmaxf(amax, fabsf(kbuf[i]));
+        }
+        amax = block_max(amax, scratch);
+        const float scale = pow2_scale_ceil(amax);
+        if (owned) {
+            uint8_t* dst = p.idx_cache + slot * (size_t)(p.idx_dim + 4);
+            for (int i = tid; i < p.idx_dim; i += nt) dst[i] = float_to_e4m3(kbuf[i] / scale);
+            if (tid == 0) {
+                // the row is idx_dim + 4 bytes: 4-byte aligned because idx_dim % 4 == 0
+                *reinterpret_cast<float*>(dst + p.idx_dim) = scale;
+            }
+        }
+        const bf16* iw = ik + p.idx_dim;
+        const float hs = rsqrtf((float)p.idx_heads);
+        for (int i = tid; i < p.idx_heads; i += nt) p.idx_w_out[(size_t)t * p.idx_heads + i] = __bfloat162float(iw[i]) * hs;
+    }
+}
+
+SL_API int sl_attn_pre(const AttnPreParams* p, int T, cudaStream_t s) {
+    if (T == 0) return 0;
+    int n = p->q_lora > p->kv_lora + p->rope_dim ? p->q_lora : p->kv_lora + p->rope_dim;
+    if (p->idx_dim > n) n = p->idx_dim;
+    attn_pre_kernel<<<T, 256, (size_t)n * sizeof(float), s>>>(*p);
+    return SL_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------------------------------------
+// After the q_b | indexer wq_b projection.  grid (T, heads_local + idx_heads).
+//  MLA head h:    q_pe[t,h,:] = rope(qb[t, h*dqk + Dn : h*dqk + Dn + Dr])
+//  indexer head j: rope(first rope_dim of qi[t,j,:]) -> bf16 -> fp8 with power-of-two scale;
+//                  w_eff[t,j] = idx_w[t,j] * scale * Di^-0.5
+struct QPostParams {
+    const bf16* qb;
+    int ld, heads, d_nope, rope_dim, idx_heads, idx_dim;
+    float theta;
+    int rope_interleave, idx_rope_interleave;
+    const int* positions;
+    const float* idx_w;       // [T, idx_heads]
+    bf16* q_pe_out;           // [T, heads, rope_dim]
+    uint8_t* q8_out;          // [T, idx_heads, idx_dim]
+    float* w_eff_out;         // [T, idx_heads]
+};
+
+__global__ void q_post_kernel(QPostParams p) {
+    __shared__ float v[512];
+    __shared__ float scratch[33];
+    const int t = blockIdx.x, hh = blockIdx.y, tid = threadIdx.x;
+    const int pos = p.positions[t];
+    const int dqk = p.d_nope + p.rope_dim;
+    if (hh < p.heads) {
+        const bf16* src = p.qb + (size_t)t * p.ld + (size_t)hh * dqk + p.d_nope;
+        for (int i = tid; i < p.rope_dim; i += blockDim.x) v[i] = __bfloat162float(src[i]);
+        __syncthreads();
+        if (tid < p.rope_dim / 2) rope_pair(v, tid, p.rope_dim, pos, p.theta, p.rope_interleave != 0);
+        __syncthreads();
+        bf16* dst = p.q_pe_out + ((size_t)t * p.heads + hh) * p.rope_dim;
+        for (int i = tid; i < p.rope_dim; i += blockDim.x) dst[i] = __float2bfloat16(v[i]);
+    } else {
+        const int j = hh - p.heads;
+        const bf16* src = p.qb + (size_t)t * p.ld + (size_t)p.heads * dqk + (size_t)j * p.idx_dim;
+        for (int i = tid; i < p.idx_dim; i += blockDim.x) v[i] = __bfloat162float(src[i]);
+        __syncthreads();
+        if (tid < p.rope_dim / 2) rope_pair(v, tid, p.rope_dim, pos, p.theta, p.idx_rope_interleave != 0);
+        __syncthreads();
+        float amax = 0.f;
+        for (int i = tid; i < p.idx_dim; i += blockDim.x) {
+            v[i] = __bfloat162float(__float2bfloat16(v[i]));
+            amax = fmaxf(amax, fabsf(v[i]));
+        }
+        amax = block_max(amax, scratch);
+        const float scale = pow2_scale_ceil(amax);
+        uint8_t* dst = p.q8_out + ((size_t)t * p.idx_heads + j) * p.idx_dim;
+        for (int i = tid; i < p.idx_dim; i += blockDim.x) dst[i] = float_to_e4m3(v[i] / scale);
+        if (tid == 0)
+            p.w_eff_out[(size_t)t * p.idx_heads + j] = p.idx_w[(size_t)t * p.idx_heads + j] * scale * rsqrtf((float)p.idx_dim);
+    }
+}
+
+SL_API int sl_q_post(const QPostParams* p, int T, cudaStream_t s) {
+    if (T == 0) return 0;
+    dim3 grid(T, p->heads + p->idx_heads);
+    q_post_kernel<<<grid, 64, 0, s>>>(*p);
+    return SL_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------------------------------------
+// Batched vector x matrix: y[t,h,n] = sum_k x[t,h,k] * M[h,k,n]   (absorb: K=Dn,N=R; v_expand: K=R,N=Dv)
+// x element (t,h,k) at x[t*xs_t + h*xs_h + k]; y bf16 [T, Hh, N] contiguous.
+// grid (Hh, N/256, ceil(T/TT)); block 256: 128 column pairs x 2 halves of K.
+template <int TT>
+__global__ void bmv_kernel(bf16* __restrict__ y, const bf16* __restrict__ x, const bf16* __restrict__ M, int T, int Hh,
+                           int K, int N, int xs_t, int xs_h) {
+    extern __shared__ float xs[];            // [TT][K]
+    __shared__ float red[TT][128][2];
+    const int h = blockIdx.x, n0 = blockIdx.y * 256, t0 = blockIdx.z * TT;
+    const int tid = threadIdx.x, col = tid & 127, half = tid >> 7;
+    for (int i = tid; i < TT * K; i += blockDim.x) {
+        const int tt = i / K, k = i % K;
+        xs[i] = (t0 + tt < T) ? __bfloat162float(x[(size_t)(t0 + tt) * xs_t + (size_t)h * xs_h + k]) : 0.f;
+    }
+    __syncthreads();
+    float acc[TT][2];
+#pragma unroll
+    for (int tt = 0; tt < TT; ++tt) acc[tt][0] = acc[tt][1] = 0.f;
+    const int n = n0 + col * 2;
+    if (n < N) {
+        const int k_lo = half * (K / 2), k_hi = k_lo + K / 2;
+        const bf16* Mp = M + (size_t)h * K * N + n;
+#pragma unroll 4
+        for (int k = k_lo; k < k_hi; ++k) {
+            const float2 w = bf162_to_f2(*reinterpret_cast<const uint32_t*>(Mp + (size_t)k * N));
+#pragma unroll
+            for (int tt = 0; tt < TT; ++tt) {
+                acc[tt][0] += xs[tt * K + k] * w.x;
+                acc[tt][1] += xs[tt * K + k] * w.y;
+            }
+        }
+    }
+    if (half == 1) {
+#pragma unroll
+        for (int tt = 0; tt < TT; ++tt) { red[tt][col][0] = acc[tt][0]; red[tt][col][1] = acc[tt][1]; }
+    }
+    __syncthreads();
+    if (half == 0 && n < N) {
+#pragma unroll
+        for (int tt = 0; tt < TT; ++tt) {
+            if (t0 + tt < T) {
+                const uint32_t o = f2_to_bf162(acc[tt][0] + red[tt][col][0], acc[tt][1] + red[tt][col][1]);
+                *reinterpret_cast<uint32_t*>(y + ((size_t)(t0 + tt) * Hh + h) * N + n) = o;
+            }
+        }
+    }
+}
+
+SL_API int sl_bmv(void* y, const void* x, const void* M, int T, int Hh, int K, int N, int xs_t, int xs_h, cudaStream_t s) {
+    if (T == 0) return 0;
+    if ((K & 1) || (N & 1)) return -1;
+    constexpr int TT = 4;
+    dim3 grid(Hh, (N + 255) / 256, (T + TT - 1) / TT);
+    bmv_kernel<TT><<<grid, 256, (size_t)TT * K * sizeof(float), s>>>((bf16*)y, (const bf16*)x, (const bf16*)M, T, Hh, K, N, xs_t, xs_h);
+    return SL_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------------------------------------
+// act[t, i] = silu(gu[t, i]) * gu[t, I + i]
+__global__ void silu_mul_kernel(bf16* __restrict__ out, const bf16* __restrict__ gu, size_t total, int I) {
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = idx / I, i = idx % I;
+        const float g = __bfloat162float(gu[t * 2 * I + i]), u = __bfloat162float(gu[t * 2 * I + I + i]);
+        out[idx] = __float2bfloat16(g / (1.f + __expf(-g)) * u);
+    }
+}
+
+SL_API int sl_silu_mul(void* out, const void* gu, int T, int I, cudaStream_t s) {
+    const size_t total = (size_t)T * I;
+    if (total == 0) return 0;
+    int blocks = (int)((total + 255) / 256);
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    silu_mul_kernel<<<blocks, 256, 0, s>>>((bf16*)out, (const bf16*)gu, total, I);
+    return SL_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------------------------------------
+// MoE routing: one warp per token.  scores = sigmoid(logits); choose by scores + bias inside
+// the `topk_group` best groups (group rank = sum of its two best biased scores); weights =
+// unbiased scores of the chosen, normalised, scaled.  Ties prefer the lower expert id.
+// E <= 512, n_group <= 32, top_k <= 32.
+__global__ void route_topk_kernel(int* __restrict__ ids, float* __restrict__ wts, const float* __restrict__ logits,
+                                  const float* __restrict__ bias, int T, int E, int top_k, int n_group, int topk_group,
+                                  int norm, float scale) {
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (warp >= T) return;
+    constexpr int MAXPL = 16;                 // experts per lane
+    float sc[MAXPL], ch[MAXPL];
+    const int per = (E + 31) / 32;
+    for (int i = 0; i < MAXPL; ++i) {
+        const int e = lane + i * 32;           // strided so that lane order == id order within a step
+        if (i < per && e < E) {
+            const float s = 1.f / (1.f + expf(-logits[(size_t)warp * E + e]));
+            sc[i] = s;
+            ch[i] = s + (bias ? bias[e] : 0.f);
+        } else {
+            sc[i] = 0.f;
+            ch[i] = -INFINITY;
+        }
+    }
+    if (n_group > 1) {
+        const int gsz = E / n_group;
+        // group score = top-2 sum; lane g (< n_group) ends up holding group g's score
+        float gscore = -INFINITY;
+        for (int g = 0; g < n_group; ++g) {
+            float m1 = -INFINITY, m2 = -INFINITY;
+            for (int i = 0; i < per; ++i) {
+                const int e = lane + i * 32;
+                if (e < E && e / gsz == g) {
+                    const float v = ch[i];
+                    if (v > m1) { m2 = m1; m1 = v; } else if (v > m2) m2 = v;
+                }
+            }
+            // merge (m1, m2) pairs across lanes
+            for (int o = 16; o > 0; o >>= 1) {
+                const float o1 = __shfl_xor_sync(0xffffffffu, m1, o), o2 = __shfl_xor_sync(0xffffffffu, m2, o);
+                const float hi = fmaxf(m1, o1), lo = fmaxf(fminf(m1, o1), fmaxf(m2, o2));
+                m1 = hi; m2 = lo;
+            }
+            const float gs = gsz >= 2 ? m1 + m2 : m1;
+            if (lane == g) gscore = gs;
+        }
+        // select topk_group groups: repeated arg-max over lanes, ties to the lower group id
+        unsigned keep = 0;
+        float cur = gscore;
+        for (int r = 0; r < topk_group; ++r) {
+            float best = cur; int bi = lane;
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+            }
+            keep |= 1u << bi;
+            if (lane == bi) cur = -INFINITY;
+        }
+        for (int i = 0; i < per; ++i) {
+            const int e = lane + i * 32;
+            if (e < E && !((keep >> (e / gsz)) & 1u)) ch[i] = -INFINITY;
+        }
+    }
+    float wsum = 0.f, myw = 0.f;
+    int myid = 0;
+    for (int r = 0; r < top_k; ++r) {
+        float best = -INFINITY; int be = E, bslot = 0;
+        for (int i = 0; i < per; ++i) {
+            const int e = lane + i * 32;
+            if (e < E && (ch[i] > best)) { best = ch[i]; be = e; bslot = i; }
+        }
+        float gb = best; int ge = be;
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, gb, o);
+            const int oe = __shfl_xor_sync(0xffffffffu, ge, o);
+            if (ob > gb || (ob == gb && oe < ge)) { gb = ob; ge = oe; }
+        }
+        float s = 0.f;
+        if (ge == be && be < E) { s = sc[bslot]; ch[bslot] = -INFINITY; }
+        s = warp_sum(s);                       // only the owner lane contributed
+        wsum += s;
+        if (lane == r) { myw = s; myid = ge; }
+    }
+    if (lane < top_k) {
+        float w = myw;
+        if (norm) w = w / fmaxf(wsum, 1e-20f);
+        ids[(size_t)warp * top_k + lane] = myid;
+        wts[(size_t)warp * top_k + lane] = w * scale;
+    }
+}
+
+SL_API int sl_route_topk(void* ids, void* wts, const void* logits, const void* bias, int T, int E, int top_k, int n_group,
+                         int topk_group, int norm, float scale, cudaStream_t s) {
+    if (T == 0) return 0;
+    if (E > 512 || top_k > 32 || n_group > 32) return -1;
+    const int wpb = 4;
+    route_topk_kernel<<<(T + wpb - 1) / wpb, wpb * 32, 0, s>>>((int*)ids, (float*)wts, (const float*)logits, (const float*)bias,
+                                                              T, E, top_k, n_group, topk_group, norm, scale);
+    return SL_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------------------------------------
+// Global key positions -> this rank's physical slots, with ordered compaction of dropped
+// entries (-1, or owned by another CP rank when local_only).  One block per token, k <= 4096.
+__global__ void topk_to_slots_kernel(int* __restrict__ slots, int* __restrict__ lengths, const int* __restrict__ pos,
+                                     const int* __restrict__ page_table, const int* __restrict__ batch_idx, int k,
+                                     int pt_stride, int page_size, int cp_world, int cp_rank, int local_only) {
+    __shared__ int wsum[32];
+    __shared__ int base;
+    const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = blockDim.x >> 5;
+    const int* pt = page_table + (size_t)batch_idx[t] * pt_stride;
+    if (tid == 0) base = 0;
+    __syncthreads();
+    for (int c0 = 0; c0 < k; c0 += blockDim.x) {
+        const int i = c0 + tid;
+        int p = (i < k) ? pos[(size_t)t * k + i] : -1;
+        bool valid = p >= 0;
+        if (valid && local_only && cp_world > 1 && (p % cp_world) != cp_rank) valid = false;
+        const unsigned m = __ballot_sync(0xffffffffu, valid);
+        const int inw = __popc(m & ((1u << lane) - 1));
+        if (lane == 0) wsum[warp] = __popc(m);
+        __syncthreads();
+        int off = base;
+        for (int w = 0; w < warp; ++w) off += wsum[w];
+        if (valid) {
+            const int local = p / cp_world;
+            slots[(size_t)t * k + off + inw] = pt[local / page_size] * page_size + local % page_size;
+        }
+        __syncthreads();
+        if (tid == 0) {
+            int tot = 0;
+            for (int w = 0; w < nw; ++w) tot += wsum[w];
+            base += tot;
+        }
+        __syncthreads();
+    }
+    for (int i = base + tid; i < k; i += blockDim.x) slots[(size_t)t * k + i] = -1;
+    if (tid == 0) lengths[t] = base;
+}
+
+SL_API int sl_topk_to_slots(void* slots, void* lengths, const void* pos, const void* page_table, const void* batch_idx, int T,
+                            int k, int pt_stride, int page_size, int cp_world, int cp_rank, int local_only, cudaStream_t s) {
+    if (T == 0) return 0;
+    topk_to_slots_kernel<<<T, 256, 0, s>>>((int*)slots, (int*)lengths, (const int*)pos, (const int*)page_table,
+                                           (const int*)batch_idx, k, pt_stride, page_size, cp_world, cp_rank, local_only);
+    return SL_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------------------------------------
+// MTP input shift: within each sequence ids[t] <- ids[t+1]; the last slot takes the new token.
+// (reference `csrc/glm_ops.cu:3308`)
+__global__ void rotate_input_ids_kernel(int64_t* __restrict__ out, const int64_t* __restrict__ ids,
+                                        const int64_t* __restrict__ new_tokens, const int* __restrict__ qo_indptr, int B) {
+    const int b = blockIdx.x;
+    if (b >= B) return;
+    const int lo = qo_indptr[b], hi = qo_indptr[b + 1];
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) out[i] = (i + 1 < hi) ? ids[i + 1] : new_tokens[b];
+}
+
+SL_API int sl_rotate_input_ids(void* out, const void* ids, const void* new_tokens, const void* qo_indptr, int B, cudaStream_t s) {
+    if (B == 0) return 0;
+    rotate_input_ids_kernel<<<B, 128, 0, s>>>((int64_t*)out, (const int64_t*)ids, (const int64_t*)new_tokens, (const int*)qo_indptr, B);
+    return SL_LAUNCH_CHECK();
+}

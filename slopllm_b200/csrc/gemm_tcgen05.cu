@@ -1,0 +1,175 @@
+// Dense GEMM on the 5th-generation tensor cores: C[M,N] = A[M,K] * B[N,K]^T, bf16 inputs,
+// fp32 accumulation in TMEM, bf16 or fp32 output.
+//
+// Warp-specialised CTA of 192 threads per 128 x BN output tile:
+//   warp 0   TMA producer: 128-byte-swizzled K-major tiles of A and B into a multi-stage ring
+//   warp 1   allocates TMEM, one elected lane issues tcgen05.mma (M=128, N=BN, K=16 per
+//            instruction, 4 per 64-wide K block), commits release the ring slots
+//   warps 2-5 epilogue: tcgen05.ld the accumulator (one TMEM lane == one output row per thread)
+//            and store
+// No cluster multicast is used anywhere.  All mbarrier waits are bounded; on expiry the kernel
+// records an error code, still frees its TMEM and returns.
+//
+// This replaces the reference's cuBLASLt path for batch >= 3 (`csrc/glm_gemv.cu:1642-1770`) and
+// its `mma.sync` grouped kernels (`csrc/glm_mma_moe.cu:110`).
+#include "tcgen05.cuh"
+
+namespace {
+
+constexpr int BM = 128, BK = 64;
+
+template <int BN>
+struct GemmCfg {
+    static constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
+    static constexpr int STAGES = (BN >= 256) ? 4 : 6;
+    static constexpr int SMEM = STAGES * (A_BYTES + B_BYTES) + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA,
+                                                        const __grid_constant__ CUtensorMap tmB, void* __restrict__ C,
+                                                        int M, int N, int K, int ldc, int out_f32, int* __restrict__ err) {
+    using Cfg = GemmCfg<BN>;
+    constexpr int STAGES = Cfg::STAGES;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* sA = smem;
+    uint8_t* sB = smem + STAGES * Cfg::A_BYTES;
+    uint64_t* full = reinterpret_cast<uint64_t*>(sB + STAGES * Cfg::B_BYTES);
+    uint64_t* empty = full + STAGES;
+    uint64_t* tmem_full = empty + STAGES;
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tmem_full + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const int num_kb = (K + BK - 1) / BK;
+
+    if (warp == 0 && lane == 0) {
+        tc::tma_prefetch_desc(&tmA);
+        tc::tma_prefetch_desc(&tmB);
+        for (int s = 0; s < STAGES; ++s) { tc::mbar_init(&full[s], 1); tc::mbar_init(&empty[s], 1); }
+        tc::mbar_init(tmem_full, 1);
+        tc::mbar_fence_init();
+    }
+    if (warp == 1) {
+        tc::tmem_alloc(tmem_holder, BN);
+        tc::tmem_relinquish();
+    }
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+    const uint32_t tmem_base = *tmem_holder;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int kb = 0; kb < num_kb; ++kb) {
+                const int s = kb % STAGES;
+                const uint32_t ph = (kb / STAGES) & 1;
+                if (!tc::mbar_wait(&empty[s], ph ^ 1)) { atomicExch(err, 1); break; }
+                tc::mbar_expect_tx(&full[s], Cfg::A_BYTES + Cfg::B_BYTES);
+                tc::tma_load_2d(sA + s * Cfg::A_BYTES, &tmA, &full[s], kb * BK, m0);
+                tc::tma_load_2d(sB + s * Cfg::B_BYTES, &tmB, &full[s], kb * BK, n0);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = tc::idesc_f16(BM, BN, 1);
+            bool ok = true;
+            for (int kb = 0; kb < num_kb && ok; ++kb) {
+                const int s = kb % STAGES;
+                const uint32_t ph = (kb / STAGES) & 1;
+                if (!tc::mbar_wait(&full[s], ph)) { atomicExch(err, 2); ok = false; break; }
+                tc::fence_after_sync();
+                const uint32_t a_addr = tc::smem_u32(sA + s * Cfg::A_BYTES), b_addr = tc::smem_u32(sB + s * Cfg::B_BYTES);
+#pragma unroll
+                for (int k = 0; k < BK / 16; ++k) {
+                    const uint64_t ad = tc::smem_desc_sw128(a_addr + k * 32), bd = tc::smem_desc_sw128(b_addr + k * 32);
+                    tc::mma_f16_ss(tmem_base, ad, bd, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                }
+                tc::mma_commit(&empty[s]);
+            }
+            tc::mma_commit(tmem_full);       // arrives when every MMA above has finished
+        }
+    } else {
+        const int q = warp & 3;               // TMEM lane quarter this warp may access
+        const bool ok = tc::mbar_wait(tmem_full, 0);
+        if (!ok && lane == 0) atomicExch(err, 3);
+        tc::fence_after_sync();
+        const int row = m0 + q * 32 + lane;
+        if (ok) {
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t r[32];
+                tc::tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + c * 32, r);
+                tc::tmem_ld_wait();
+                const int col = n0 + c * 32;
+                if (row < M && col < N) {
+                    if (out_f32) {
+                        float* dst = (float*)C + (size_t)row * ldc + col;
+                        if (col + 32 <= N) {
+#pragma unroll
+                            for (int i = 0; i < 8; ++i)
+                                reinterpret_cast<uint4*>(dst)[i] = make_uint4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
+                        } else {
+                            for (int i = 0; i < 32 && col + i < N; ++i) dst[i] = __uint_as_float(r[i]);
+                        }
+                    } else {
+                        bf16* dst = (bf16*)C + (size_t)row * ldc + col;
+                        if (col + 32 <= N) {
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                uint4 v;
+                                v.x = f2_to_bf162(__uint_as_float(r[8 * i + 0]), __uint_as_float(r[8 * i + 1]));
+                                v.y = f2_to_bf162(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3]));
+                                v.z = f2_to_bf162(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5]));
+                                v.w = f2_to_bf162(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]));
+                                reinterpret_cast<uint4*>(dst)[i] = v;
+                            }
+                        } else {
+                            for (int i = 0; i < 32 && col + i < N; ++i) dst[i] = __float2bfloat16(__uint_as_float(r[i]));
+                        }
+                    }
+                }
+            }
+        }
+    }
+    tc::fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc::fence_after_sync();
+        tc::tmem_dealloc(tmem_base, BN);
+    }
+}
+
+template <int BN>
+int launch(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc, int out_f32, int* err,
+           cudaStream_t s) {
+    CUtensorMap tmA, tmB;
+    int rc = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)M, (uint64_t)K, (uint64_t)lda * 2, BM, BK);
+    if (rc) return rc;
+    rc = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)N, (uint64_t)K, (uint64_t)ldb * 2, BN, BK);
+    if (rc) return rc;
+    auto kern = gemm_bf16_kernel<BN>;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmCfg<BN>::SMEM);
+        attr_set = true;
+    }
+    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+    kern<<<grid, 192, GemmCfg<BN>::SMEM, s>>>(tmA, tmB, C, M, N, K, ldc, out_f32, err);
+    return (int)cudaGetLastError();
+}
+
+}  // namespace
+
+// A [M, K] bf16 (row stride lda), B [N, K] bf16 (row stride ldb), C [M, N] (row stride ldc; bf16 or fp32).
+// `err` is a device int the kernel sets to non-zero if one of its bounded waits expired.
+SL_API int sl_gemm_bf16_tcgen05(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
+                                int out_f32, void* err, int bn, cudaStream_t s) {
+    if (M <= 0 || N <= 0 || K <= 0) return 0;
+    if (K % 8 != 0 || lda % 8 != 0 || ldb % 8 != 0) return -1;
+    if ((out_f32 ? ldc % 4 : ldc % 8) != 0) return -1;
+    if (bn == 64) return launch<64>(A, B, C, M, N, K, lda, ldb, ldc, out_f32, (int*)err, s);
+    if (bn == 256) return launch<256>(A, B, C, M, N, K, lda, ldb, ldc, out_f32, (int*)err, s);
+    return launch<128>(A, B, C, M, N, K, lda, ldb, ldc, out_f32, (int*)err, s);
+}

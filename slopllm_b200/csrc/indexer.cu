@@ -1,0 +1,262 @@
+// DSA lightning indexer: FP8 scoring of a query token's 32x128 index heads against this
+// rank's paged FP8 key rows, and exact top-k selection with ascending-index output.
+//
+// score[j] = kscale[j] * sum_h w_eff[h] * relu(q8[h] . k8[j])
+//
+// Reference: `csrc/glm_indexer.cu:1375-1510` (fp8 mma scoring), `:490-870` (radix top-k,
+// stable gather, sort by index).  Here scoring runs on the FP8 tensor path with fp32
+// scores, the select is a 4x8-bit radix descent over order-preserving keys, and the gather
+// emits ascending positions directly (no separate sort).
+#include "common.cuh"
+
+__device__ __forceinline__ void mma_e4m3_m16n8k32(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+struct IndexerScoreParams {
+    const uint8_t* q8;        // [T, Hi, D] e4m3
+    const float* w_eff;       // [T, Hi]
+    const uint8_t* idx_cache; // [slots, D + 4]
+    const int* page_table; int pt_stride;
+    const int* batch_idx; const int* positions;
+    int Hi, D, page_size, cp_world, cp_rank, top_k;
+    float* scores; int ld_scores;     // [T, ld_scores]
+};
+
+// Visible local keys of a query at global position p: local key j is global j*W + r.
+__device__ __forceinline__ int local_visible(int p, int W, int r) { return p >= r ? (p - r) / W + 1 : 0; }
+
+// grid (key tiles of 8 warps x 8 keys x ITER, T); Hi == 32, D == 128.
+// The 128-byte key row is consumed with a fixed permutation of the reduction index that is
+// applied to Q as well, so every lane issues two 16-byte loads per key row quarter.
+template <int HI, int D>
+__global__ void __launch_bounds__(256) indexer_score_kernel(IndexerScoreParams p, int keys_per_block) {
+    static_assert(HI % 16 == 0 && D % 32 == 0, "index heads / dim");
+    constexpr int MT = HI / 16;          // m tiles (16 heads each)
+    constexpr int KS = D / 32;           // k steps of 32
+    const int t = blockIdx.y;
+    const int pos = p.positions[t];
+    if (pos + 1 <= p.top_k) return;      // everything visible is selected: no scores needed
+    const int n_local = local_visible(pos, p.cp_world, p.cp_rank);
+    const int k_begin = blockIdx.x * keys_per_block;
+    if (k_begin >= n_local) return;
+    const int k_end = min(n_local, k_begin + keys_per_block);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, c = lane & 3;
+    constexpr int RB = D + 4;
+
+    // A fragments: logical k (s, half, c, i) <-> dim c*(D/4) + s*8 + half*4 + i
+    uint32_t a[MT][KS][4];
+    float w[MT][2];
+    const uint8_t* q = p.q8 + (size_t)t * HI * D;
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+#pragma unroll
+        for (int s = 0; s < KS; ++s) {
+            const int d0 = c * (D / 4) + s * 8;
+            a[m][s][0] = *reinterpret_cast<const uint32_t*>(q + (size_t)(m * 16 + g) * D + d0);
+            a[m][s][1] = *reinterpret_cast<const uint32_t*>(q + (size_t)(m * 16 + g + 8) * D + d0);
+            a[m][s][2] = *reinterpret_cast<const uint32_t*>(q + (size_t)(m * 16 + g) * D + d0 + 4);
+            a[m][s][3] = *reinterpret_cast<const uint32_t*>(q + (size_t)(m * 16 + g + 8) * D + d0 + 4);
+        }
+        w[m][0] = p.w_eff[(size_t)t * HI + m * 16 + g];
+        w[m][1] = p.w_eff[(size_t)t * HI + m * 16 + g + 8];
+    }
+    const int* pt = p.page_table + (size_t)p.batch_idx[t] * p.pt_stride;
+    for (int j0 = k_begin + warp * 8; j0 < k_end; j0 += 64) {
+        // lane's key for the B fragment: j0 + g ; 8 consecutive keys never straddle a page
+        const int j = j0 + g;
+        const bool ok = j < k_end;
+        const size_t slot = (size_t)pt[j0 / p.page_size] * p.page_size + (j0 % p.page_size) + g;
+        const uint8_t* row = p.idx_cache + slot * RB;
+        uint32_t b[KS][2];
+        // row stride D+4 keeps 4-byte alignment only: read the lane's 32 bytes as 8 words
+#pragma unroll
+        for (int s = 0; s < KS; ++s) {
+            b[s][0] = ok ? *reinterpret_cast<const uint32_t*>(row + c * (D / 4) + s * 8) : 0u;
+            b[s][1] = ok ? *reinterpret_cast<const uint32_t*>(row + c * (D / 4) + s * 8 + 4) : 0u;
+        }
+        float part[2] = {0.f, 0.f};       // keys 2c, 2c+1 of this group of 8
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+            float d[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int s = 0; s < KS; ++s) mma_e4m3_m16n8k32(d, a[m][s], b[s]);
+            part[0] += w[m][0] * fmaxf(d[0], 0.f) + w[m][1] * fmaxf(d[2], 0.f);
+            part[1] += w[m][0] * fmaxf(d[1], 0.f) + w[m][1] * fmaxf(d[3], 0.f);
+        }
+        // reduce over the 8 row groups g (lanes with equal c)
+#pragma unroll
+        for (int o = 4; o < 32; o <<= 1) {
+            part[0] += __shfl_xor_sync(0xffffffffu, part[0], o);
+            part[1] += __shfl_xor_sync(0xffffffffu, part[1], o);
+        }
+        if (g == 0) {
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int jj = j0 + 2 * c + i;
+                if (jj < k_end) {
+                    const size_t sl = (size_t)pt[j0 / p.page_size] * p.page_size + (j0 % p.page_size) + 2 * c + i;
+                    const float ks = *reinterpret_cast<const float*>(p.idx_cache + sl * RB + D);
+                    p.scores[(size_t)t * p.ld_scores + jj] = part[i] * ks;
+                }
+            }
+        }
+    }
+}
+
+// Generic CUDA-core scorer for other head counts / dims (small test models).
+__global__ void indexer_score_generic_kernel(IndexerScoreParams p, int keys_per_block) {
+    extern __shared__ float qs[];          // [Hi*D] + [Hi]
+    const int t = blockIdx.y;
+    const int pos = p.positions[t];
+    if (pos + 1 <= p.top_k) return;
+    const int n_local = local_visible(pos, p.cp_world, p.cp_rank);
+    const int k_begin = blockIdx.x * keys_per_block;
+    if (k_begin >= n_local) return;
+    const int k_end = min(n_local, k_begin + keys_per_block);
+    float* ws = qs + p.Hi * p.D;
+    for (int i = threadIdx.x; i < p.Hi * p.D; i += blockDim.x) qs[i] = e4m3_to_float(p.q8[(size_t)t * p.Hi * p.D + i]);
+    for (int i = threadIdx.x; i < p.Hi; i += blockDim.x) ws[i] = p.w_eff[(size_t)t * p.Hi + i];
+    __syncthreads();
+    const int* pt = p.page_table + (size_t)p.batch_idx[t] * p.pt_stride;
+    const int RB = p.D + 4;
+    for (int j = k_begin + threadIdx.x; j < k_end; j += blockDim.x) {
+        const size_t slot = (size_t)pt[j / p.page_size] * p.page_size + (j % p.page_size);
+        const uint8_t* row = p.idx_cache + slot * RB;
+        float tot = 0.f;
+        for (int h = 0; h < p.Hi; ++h) {
+            float dot = 0.f;
+            for (int d = 0; d < p.D; ++d) dot += qs[h * p.D + d] * e4m3_to_float(row[d]);
+            tot += ws[h] * fmaxf(dot, 0.f);
+        }
+        p.scores[(size_t)t * p.ld_scores + j] = tot * *reinterpret_cast<const float*>(row + p.D);
+    }
+}
+
+SL_API int sl_indexer_scores(const IndexerScoreParams* p, int T, int max_local, cudaStream_t s) {
+    if (T == 0 || max_local <= 0) return 0;
+    // tile the keys so that the grid has a few waves of blocks
+    int kpb = 512;
+    while (kpb > 64 && (long)((max_local + kpb - 1) / kpb) * T < 296) kpb >>= 1;
+    dim3 grid((max_local + kpb - 1) / kpb, T);
+    if (p->Hi == 32 && p->D == 128) {
+        indexer_score_kernel<32, 128><<<grid, 256, 0, s>>>(*p, kpb);
+    } else {
+        const size_t smem = (size_t)(p->Hi * p->D + p->Hi) * sizeof(float);
+        if (smem > 48 * 1024) return -1;
+        indexer_score_generic_kernel<<<grid, 256, smem, s>>>(*p, kpb);
+    }
+    return SL_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t order_key(float f) {
+    const uint32_t u = __float_as_uint(f);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+struct TopkSelectParams {
+    const float* scores; int ld_scores;
+    const int* positions;
+    int top_k, cp_world, cp_rank;
+    int* out_pos;             // [T, top_k] global positions ascending, -1 padded
+    float* out_score;         // [T, top_k] (0 where unused)
+};
+
+// One block per query token.  If the query sees at most top_k keys in total, all local
+// keys are emitted.  Otherwise: radix descent for the k'-th largest key (k' = min(top_k,
+// n_local)), then an in-order gather of keys above the threshold plus the first ties.
+__global__ void __launch_bounds__(1024) topk_select_kernel(TopkSelectParams p) {
+    __shared__ uint32_t hist[256];
+    __shared__ uint32_t s_prefix, s_remaining;
+    __shared__ int wsum[32];
+    __shared__ int s_base, s_eq_used;
+    const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = blockDim.x >> 5;
+    const int pos = p.positions[t];
+    const int n = local_visible(pos, p.cp_world, p.cp_rank);
+    int* opos = p.out_pos + (size_t)t * p.top_k;
+    float* osc = p.out_score + (size_t)t * p.top_k;
+    if (pos + 1 <= p.top_k) {
+        for (int i = tid; i < p.top_k; i += blockDim.x) {
+            opos[i] = i < n ? i * p.cp_world + p.cp_rank : -1;
+            osc[i] = 0.f;
+        }
+        return;
+    }
+    const float* sc = p.scores + (size_t)t * p.ld_scores;
+    const int kk = min(p.top_k, n);
+    uint32_t prefix = 0, mask = 0;
+    if (tid == 0) { s_prefix = 0; s_remaining = (uint32_t)kk; }
+    for (int shift = 24; shift >= 0; shift -= 8) {
+        for (int i = tid; i < 256; i += blockDim.x) hist[i] = 0;
+        __syncthreads();
+        prefix = s_prefix;
+        for (int i = tid; i < n; i += blockDim.x) {
+            const uint32_t key = order_key(sc[i]);
+            if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1u);
+        }
+        __syncthreads();
+        if (tid == 0) {
+            uint32_t rem = s_remaining, cum = 0;
+            int b = 255;
+            for (; b > 0; --b) {
+                if (cum + hist[b] >= rem) break;
+                cum += hist[b];
+            }
+            s_remaining = rem - cum;
+            s_prefix = prefix | ((uint32_t)b << shift);
+        }
+        __syncthreads();
+        mask |= 0xffu << shift;
+    }
+    const uint32_t thr = s_prefix;
+    const int need_eq = (int)s_remaining;      // how many keys equal to thr are taken (lowest index first)
+    if (tid == 0) { s_base = 0; s_eq_used = 0; }
+    __syncthreads();
+    for (int c0 = 0; c0 < n; c0 += blockDim.x) {
+        const int i = c0 + tid;
+        uint32_t key = 0;
+        float v = 0.f;
+        if (i < n) { v = sc[i]; key = order_key(v); }
+        const bool gt = (i < n) && key > thr, eq = (i < n) && key == thr;
+        // rank of this tie among ties, in index order
+        const unsigned meq = __ballot_sync(0xffffffffu, eq);
+        const unsigned mgt = __ballot_sync(0xffffffffu, gt);
+        if (lane == 0) wsum[warp] = __popc(meq);
+        __syncthreads();
+        int eq_before = s_eq_used;
+        for (int w = 0; w < warp; ++w) eq_before += wsum[w];
+        eq_before += __popc(meq & ((1u << lane) - 1));
+        const bool take = gt || (eq && eq_before < need_eq);
+        int eq_total = 0;
+        for (int w = 0; w < nw; ++w) eq_total += wsum[w];
+        __syncthreads();
+        const unsigned mt = __ballot_sync(0xffffffffu, take);
+        if (lane == 0) wsum[warp] = __popc(mt);
+        __syncthreads();
+        int off = s_base;
+        for (int w = 0; w < warp; ++w) off += wsum[w];
+        off += __popc(mt & ((1u << lane) - 1));
+        if (take && off < p.top_k) {
+            opos[off] = i * p.cp_world + p.cp_rank;
+            osc[off] = v;
+        }
+        int tk_total = 0;
+        for (int w = 0; w < nw; ++w) tk_total += wsum[w];
+        __syncthreads();
+        if (tid == 0) { s_base += tk_total; s_eq_used += eq_total; }
+        __syncthreads();
+        (void)mgt;
+    }
+    for (int i = s_base + tid; i < p.top_k; i += blockDim.x) { opos[i] = -1; osc[i] = 0.f; }
+}
+
+SL_API int sl_topk_select(const TopkSelectParams* p, int T, cudaStream_t s) {
+    if (T == 0) return 0;
+    topk_select_kernel<<<T, 1024, 0, s>>>(*p);
+    return SL_LAUNCH_CHECK();
+}

@@ -111,7 +111,7 @@ class GlmMoeDsaModel:
             o = comm.cp_merge_heads(ops, o, lse)
         else:
             o, _ = ops.sparse_mla(q_abs, q_pe, lc, st.slots, st.lengths)
-        return ops.linear(ops.v_expand(o, lw.w_v), lw.o_proj)
+        return ops.linear(ops.v_expand(o, lw.w_v), lw.o_proj, out_f32=True)
 
     # -- MLP ----------------------------------------------------------------------------------
     def mlp(self, lw: LayerWeights, y: torch.Tensor):

@@ -1,0 +1,300 @@
+"""sm_100a op set: the staged model ops implemented with the in-tree CUDA kernels.
+
+Activations are bf16, the residual stream and partial sums are fp32, caches are packed
+bytes.  Every method launches hand-written kernels from `libslopllm_kernels.so` on the
+current stream (so the whole step can be captured in a CUDA graph); nothing here falls
+back to PyTorch math on the hot path.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+
+from . import native as N
+from . import reference as R
+
+DECODE_MAX_T = 32          # token rows handled by the weight-streaming (GEMV) kernels
+
+
+class CudaOps:
+    name = "cuda"
+    act_dtype = torch.bfloat16
+
+    def __init__(self, cfg, ctx=None):
+        self.cfg = cfg
+        self.ctx = ctx
+        N.kernels()            # fail loudly when the native library is missing
+
+    # -- helpers ----------------------------------------------------------------------------
+    @staticmethod
+    def _bf16(x):
+        return x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16)
+
+    # -- elementwise / linear ---------------------------------------------------------------
+    def embed(self, ids, table):
+        T, H = ids.shape[0], table.shape[1]
+        out = torch.empty(T, H, dtype=torch.bfloat16, device=table.device)
+        ids = ids.to(torch.int64).contiguous()
+        N.call("sl_embed", out.data_ptr(), ids.data_ptr(), table.data_ptr(), T, H, N.stream())
+        return out
+
+    def add_rmsnorm(self, x, residual, w, eps=None):
+        eps = self.cfg.rms_norm_eps if eps is None else eps
+        x = x.contiguous()
+        if x.dtype not in (torch.bfloat16, torch.float32):
+            x = x.to(torch.float32)
+        T, H = x.shape
+        out = torch.empty(T, H, dtype=torch.bfloat16, device=x.device)
+        res = torch.empty(T, H, dtype=torch.float32, device=x.device)
+        N.call("sl_add_rmsnorm", out.data_ptr(), res.data_ptr(), x.data_ptr(), N.ptr(residual), w.data_ptr(), T, H,
+               float(eps), int(x.dtype == torch.float32), N.stream())
+        return out, res
+
+    def rmsnorm(self, x, w, eps=None):
+        eps = self.cfg.rms_norm_eps if eps is None else eps
+        x = x.contiguous()
+        T, H = x.shape
+        out = torch.empty(T, H, dtype=torch.bfloat16, device=x.device)
+        N.call("sl_add_rmsnorm", out.data_ptr(), 0, x.data_ptr(), 0, w.data_ptr(), T, H, float(eps),
+               int(x.dtype == torch.float32), N.stream())
+        return out
+
+    def linear(self, x, w, out_f32: bool = False):
+        x = self._bf16(x)
+        if x.stride(-1) != 1:
+            x = x.contiguous()
+        T, K = x.shape
+        Nn = w.out_features
+        if T > DECODE_MAX_T:
+            from .gemm import gemm_large
+            return gemm_large(x, w, out_f32)
+        y = torch.empty(T, Nn, dtype=torch.float32 if out_f32 else torch.bfloat16, device=x.device)
+        if w.is_nvfp4:
+            N.call("sl_gemv_nvfp4", y.data_ptr(), x.data_ptr(), w.weight.data_ptr(), w.scale.data_ptr(),
+                   w.scale2.data_ptr(), T, Nn, K, x.stride(0), int(out_f32), N.stream())
+        else:
+            N.call("sl_gemv_bf16", y.data_ptr(), x.data_ptr(), w.weight.data_ptr(), T, Nn, K, x.stride(0), int(out_f32),
+                   N.stream())
+        return y
+
+    def merge_attention_partials(self, o, lse):
+        return R.merge_attention_partials(o, lse)
+
+    # -- attention stages ---------------------------------------------------------------------
+    def attn_pre(self, qkv, lw, st, layer_cache):
+        c = self.cfg
+        T = qkv.shape[0]
+        dev = qkv.device
+        cq = torch.empty(T, c.q_lora_rank, dtype=torch.bfloat16, device=dev)
+        idx_w = torch.empty(T, c.index_n_heads, dtype=torch.float32, device=dev) if lw.has_indexer else None
+        p = N.AttnPreParams(
+            qkv=qkv.data_ptr(), ld=qkv.stride(0), q_lora=c.q_lora_rank, kv_lora=c.kv_lora_rank, rope_dim=c.qk_rope_head_dim,
+            idx_dim=c.index_head_dim if lw.has_indexer else 0, idx_heads=c.index_n_heads,
+            q_norm_w=lw.q_a_norm.data_ptr(), kv_norm_w=lw.kv_a_norm.data_ptr(), idx_ln_w=N.ptr(lw.idx_k_norm_w),
+            idx_ln_b=N.ptr(lw.idx_k_norm_b), eps=c.rms_norm_eps, theta=c.rope_theta,
+            rope_interleave=int(c.rope_interleave), idx_rope_interleave=int(c.indexer_rope_interleave),
+            positions=st.positions.data_ptr(), batch_idx=st.batch_idx.data_ptr(), page_table=st.page_table.data_ptr(),
+            pt_stride=st.page_table.stride(0), page_size=st.page_size, cp_world=st.cp_world, cp_rank=st.cp_rank,
+            kv_group=c.kv_quant_group, kv_cache=layer_cache.kv.data_ptr(), idx_cache=N.ptr(layer_cache.idx),
+            cq_out=cq.data_ptr(), idx_w_out=N.ptr(idx_w))
+        N.call("sl_attn_pre", C.byref(p), T, N.stream())
+        return cq, idx_w
+
+    def q_post(self, qb, lw, st, idx_w):
+        c = self.cfg
+        T = qb.shape[0]
+        dev = qb.device
+        hl = lw.w_kn.shape[0]
+        q_pe = torch.empty(T, hl, c.qk_rope_head_dim, dtype=torch.bfloat16, device=dev)
+        q8 = w_eff = None
+        if lw.has_indexer:
+            q8 = torch.empty(T, c.index_n_heads, c.index_head_dim, dtype=torch.uint8, device=dev)
+            w_eff = torch.empty(T, c.index_n_heads, dtype=torch.float32, device=dev)
+        p = N.QPostParams(
+            qb=qb.data_ptr(), ld=qb.stride(0), heads=hl, d_nope=c.qk_nope_head_dim, rope_dim=c.qk_rope_head_dim,
+            idx_heads=c.index_n_heads if lw.has_indexer else 0, idx_dim=c.index_head_dim, theta=c.rope_theta,
+            rope_interleave=int(c.rope_interleave), idx_rope_interleave=int(c.indexer_rope_interleave),
+            positions=st.positions.data_ptr(), idx_w=N.ptr(idx_w), q_pe_out=q_pe.data_ptr(), q8_out=N.ptr(q8),
+            w_eff_out=N.ptr(w_eff))
+        N.call("sl_q_post", C.byref(p), T, N.stream())
+        q_abs = torch.empty(T, hl, c.kv_lora_rank, dtype=torch.bfloat16, device=dev)
+        N.call("sl_bmv", q_abs.data_ptr(), qb.data_ptr(), lw.w_kn.data_ptr(), T, hl, c.qk_nope_head_dim, c.kv_lora_rank,
+               qb.stride(0), c.qk_head_dim, N.stream())
+        return q_abs, q_pe, q8, w_eff
+
+    def indexer_topk(self, q8, w_eff, layer_cache, st):
+        c = self.cfg
+        T = q8.shape[0]
+        dev = q8.device
+        W, r = st.cp_world, st.cp_rank
+        max_local = max(0, -(-st.max_kv_len // W))
+        pos = torch.empty(T, c.index_topk, dtype=torch.int32, device=dev)
+        score = torch.empty(T, c.index_topk, dtype=torch.float32, device=dev)
+        ld = max(8, (max_local + 7) // 8 * 8)
+        scores = st.extra.get("idx_scores")
+        if scores is None or scores.shape[0] < T or scores.shape[1] < ld:
+            scores = torch.empty(T, ld, dtype=torch.float32, device=dev)
+            st.extra["idx_scores"] = scores
+        if st.max_kv_len > c.index_topk:
+            sp = N.IndexerScoreParams(
+                q8=q8.data_ptr(), w_eff=w_eff.data_ptr(), idx_cache=layer_cache.idx.data_ptr(),
+                page_table=st.page_table.data_ptr(), pt_stride=st.page_table.stride(0), batch_idx=st.batch_idx.data_ptr(),
+                positions=st.positions.data_ptr(), Hi=c.index_n_heads, D=c.index_head_dim, page_size=st.page_size,
+                cp_world=W, cp_rank=r, top_k=c.index_topk, scores=scores.data_ptr(), ld_scores=scores.stride(0))
+            N.call("sl_indexer_scores", C.byref(sp), T, max_local, N.stream())
+        tp = N.TopkSelectParams(scores=scores.data_ptr(), ld_scores=scores.stride(0), positions=st.positions.data_ptr(),
+                                top_k=c.index_topk, cp_world=W, cp_rank=r, out_pos=pos.data_ptr(), out_score=score.data_ptr())
+        N.call("sl_topk_select", C.byref(tp), T, N.stream())
+        return pos, score
+
+    def topk_to_slots(self, topk_pos, st, local_only: bool = False):
+        T, k = topk_pos.shape
+        dev = topk_pos.device
+        slots = torch.empty(T, k, dtype=torch.int32, device=dev)
+        lengths = torch.empty(T, dtype=torch.int32, device=dev)
+        topk_pos = topk_pos.contiguous()
+        N.call("sl_topk_to_slots", slots.data_ptr(), lengths.data_ptr(), topk_pos.data_ptr(), st.page_table.data_ptr(),
+               st.batch_idx.data_ptr(), T, k, st.page_table.stride(0), st.page_size, st.cp_world, st.cp_rank,
+               int(local_only), N.stream())
+        return slots, lengths
+
+    def _mla_splits(self, T: int, h: int) -> int:
+        """Split the selected keys so that the grid fills the 148 SMs a few times over
+        (the reference's `sparseMlaChunksPerBlock`, `src/sparse-mla-planner.ts:1-21`)."""
+        topk = self.cfg.index_topk
+        groups = (h + 7) // 8
+        want = max(1, (148 * 2) // max(1, T * groups))
+        return int(max(1, min(want, topk // 32, 64)))
+
+    def sparse_mla_partials(self, q_abs, q_pe, layer_cache, slots, lengths):
+        c = self.cfg
+        T, h, Rr = q_abs.shape
+        dev = q_abs.device
+        splits = self._mla_splits(T, h)
+        o_part = torch.empty(T, h, splits, Rr, dtype=torch.float32, device=dev)
+        lse_part = torch.empty(T, h, splits, dtype=torch.float32, device=dev)
+        p = N.SparseMlaParams(q_abs=q_abs.data_ptr(), q_pe=q_pe.data_ptr(), kv_cache=layer_cache.kv.data_ptr(),
+                              slots=slots.data_ptr(), lengths=lengths.data_ptr(), h=h, R=Rr, Dr=c.qk_rope_head_dim,
+                              group=c.kv_quant_group, topk=slots.shape[1], splits=splits, sm_scale=c.softmax_scale,
+                              o_part=o_part.data_ptr(), lse_part=lse_part.data_ptr())
+        N.call("sl_sparse_mla_split", C.byref(p), T, N.stream())
+        return o_part, lse_part
+
+    def combine(self, o_parts, lse_parts, head_begin=0, head_count=None, want_lse=True):
+        """o_parts: list of [T, h, S, R] fp32 buffers (one per rank under CP)."""
+        T, h, S, Rr = o_parts[0].shape
+        head_count = h if head_count is None else head_count
+        dev = o_parts[0].device
+        o = torch.empty(T, head_count, Rr, dtype=torch.bfloat16, device=dev)
+        lse = torch.empty(T, head_count, dtype=torch.float32, device=dev) if want_lse else None
+        p = N.CombineParams(n_buf=len(o_parts), parts_per_buf=S, h=h, R=Rr, head_begin=head_begin, head_count=head_count,
+                            o_out=o.data_ptr(), lse_out=N.ptr(lse))
+        for i, (a, b) in enumerate(zip(o_parts, lse_parts)):
+            p.o_ptrs[i] = a.data_ptr()
+            p.lse_ptrs[i] = b.data_ptr()
+        N.call("sl_mla_combine", C.byref(p), T, N.stream())
+        return o, lse
+
+    def sparse_mla(self, q_abs, q_pe, layer_cache, slots, lengths):
+        o_part, lse_part = self.sparse_mla_partials(q_abs, q_pe, layer_cache, slots, lengths)
+        return self.combine([o_part], [lse_part])
+
+    def v_expand(self, o, w_v):
+        T, hl, Rr = o.shape
+        Dv = w_v.shape[2]
+        o = self._bf16(o).contiguous()
+        out = torch.empty(T, hl * Dv, dtype=torch.bfloat16, device=o.device)
+        N.call("sl_bmv", out.data_ptr(), o.data_ptr(), w_v.data_ptr(), T, hl, Rr, Dv, hl * Rr, Rr, N.stream())
+        return out
+
+    # -- MLP --------------------------------------------------------------------------------------
+    def dense_mlp(self, x, lw):
+        gu = self.linear(x, lw.mlp_w13)
+        T, I2 = gu.shape
+        act = torch.empty(T, I2 // 2, dtype=torch.bfloat16, device=x.device)
+        N.call("sl_silu_mul", act.data_ptr(), gu.data_ptr(), T, I2 // 2, N.stream())
+        return self.linear(act, lw.mlp_w2, out_f32=True)
+
+    def route(self, x, lw):
+        c = self.cfg
+        T = x.shape[0]
+        E = lw.router_w.shape[0]
+        logits = self._router_logits(x, lw)
+        ids = torch.empty(T, c.num_experts_per_tok, dtype=torch.int32, device=x.device)
+        wts = torch.empty(T, c.num_experts_per_tok, dtype=torch.float32, device=x.device)
+        N.call("sl_route_topk", ids.data_ptr(), wts.data_ptr(), logits.data_ptr(), N.ptr(lw.router_bias), T, E,
+               c.num_experts_per_tok, c.n_group, c.topk_group, int(c.norm_topk_prob), float(c.routed_scaling_factor),
+               N.stream())
+        return ids, wts
+
+    def _router_logits(self, x, lw):
+        from ..models.weights import LinearWeight
+        return self.linear(x, LinearWeight(lw.router_w), out_f32=True)
+
+    def _moe_small(self, x, experts, shared, ids, wts):
+        """Weight-streaming MoE for a few token rows: gate/up + SiLU·mul per route, then
+        down-projection fused with the routing-weighted sum (and the shared expert)."""
+        x = self._bf16(x)
+        T, H = x.shape
+        k = ids.shape[1]
+        I = experts.inter
+        routes = T * k + (T if shared is not None else 0)
+        act = torch.empty(routes, I, dtype=torch.bfloat16, device=x.device)
+        gp = N.MoeGateUpParams(x=x.data_ptr(), ldx=x.stride(0), ids=ids.data_ptr(), T=T, top_k=k, H=H, I=I,
+                               expert_offset=experts.expert_offset, num_local=experts.num_experts,
+                               w13=experts.w13.data_ptr(), s13=experts.s13.data_ptr(), g13=experts.g13.data_ptr(),
+                               sw13=N.ptr(shared.w13) if shared else 0, ss13=N.ptr(shared.s13) if shared else 0,
+                               sg13=N.ptr(shared.g13) if shared else 0, act=act.data_ptr())
+        N.call("sl_moe_gate_up", C.byref(gp), N.stream())
+        out = torch.empty(T, H, dtype=torch.float32, device=x.device)
+        dp = N.MoeDownParams(act=act.data_ptr(), ids=ids.data_ptr(), wts=wts.data_ptr(), T=T, top_k=k, H=H, I=I,
+                             expert_offset=experts.expert_offset, num_local=experts.num_experts,
+                             w2=experts.w2.data_ptr(), s2=experts.s2.data_ptr(), g2=experts.g2.data_ptr(),
+                             sw2=N.ptr(shared.w2) if shared else 0, ss2=N.ptr(shared.s2) if shared else 0,
+                             sg2=N.ptr(shared.g2) if shared else 0, out=out.data_ptr(), out_f32=1, accumulate=0)
+        N.call("sl_moe_down", C.byref(dp), N.stream())
+        return out
+
+    def moe_tp(self, x, lw):
+        ids, wts = self.route(x, lw)
+        if x.shape[0] <= DECODE_MAX_T and lw.experts.is_nvfp4:
+            if lw.shared is not None and lw.shared.inter != lw.experts.inter:
+                out = self._moe_small(x, lw.experts, None, ids, wts)
+                return out + self.shared_expert(x, lw)
+            return self._moe_small(x, lw.experts, lw.shared, ids, wts)
+        from .gemm import moe_large
+        return moe_large(self, x, lw.experts, lw.shared, ids, wts)
+
+    def moe_local_experts(self, x, experts, ids, w):
+        ids = ids.to(torch.int32).contiguous()
+        w = w.to(torch.float32).contiguous()
+        if x.shape[0] <= DECODE_MAX_T and experts.is_nvfp4:
+            return self._moe_small(x, experts, None, ids, w)
+        from .gemm import moe_large
+        return moe_large(self, x, experts, None, ids, w)
+
+    def shared_expert(self, x, lw):
+        T = x.shape[0]
+        ids = torch.zeros(T, 1, dtype=torch.int32, device=x.device)
+        w = torch.ones(T, 1, dtype=torch.float32, device=x.device)
+        if T <= DECODE_MAX_T and lw.shared.is_nvfp4:
+            return self._moe_small(x, lw.shared, None, ids, w)
+        from .gemm import moe_large
+        return moe_large(self, x, lw.shared, None, ids, w)
+
+    # -- head ----------------------------------------------------------------------------------------
+    def logits(self, x, lm_head):
+        return self.linear(x, lm_head, out_f32=True)
+
+    def argmax(self, logits, id_offset: int = 0, want_val: bool = False):
+        B, V = logits.shape
+        out = torch.empty(B, dtype=torch.int64, device=logits.device)
+        val = torch.empty(B, dtype=torch.float32, device=logits.device) if want_val else None
+        N.call("sl_argmax", out.data_ptr(), logits.data_ptr(), B, V, logits.stride(0), int(logits.dtype == torch.float32),
+               id_offset, N.ptr(val), N.stream())
+        return (out, val) if want_val else out
+
+
+_ = Optional

@@ -1,0 +1,170 @@
+"""ctypes binding of the in-tree native libraries.
+
+`kernels()` returns the CUDA kernel library (`_lib/libslopllm_kernels.so`, built by
+`slopllm_b200.build_native` for sm_100a) and raises if it is missing: on a GPU box there is
+no silent PyTorch fallback.  The reference binds its `libglm_ops.so` the same way in its
+kernel tests (`tests/python/helpers.py`).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from functools import lru_cache
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_DIR = os.path.join(os.path.dirname(_HERE), "_lib")
+KERNELS_SO = os.path.join(LIB_DIR, "libslopllm_kernels.so")
+RUNTIME_SO = os.path.join(LIB_DIR, "libslopllm_runtime.so")
+
+vp, i32, f32, u32, i64 = C.c_void_p, C.c_int, C.c_float, C.c_uint32, C.c_longlong
+
+
+class NativeError(RuntimeError):
+    pass
+
+
+@lru_cache(maxsize=None)
+def kernels() -> C.CDLL:
+    if not os.path.exists(KERNELS_SO):
+        raise NativeError(f"{KERNELS_SO} is missing: run `python -m slopllm_b200.build_native` "
+                          "(the CUDA path has no PyTorch fallback)")
+    return C.CDLL(KERNELS_SO)
+
+
+@lru_cache(maxsize=None)
+def runtime() -> C.CDLL:
+    if not os.path.exists(RUNTIME_SO):
+        from .. import build_native
+        build_native.build_runtime()
+    return C.CDLL(RUNTIME_SO)
+
+
+def ptr(t) -> int:
+    return 0 if t is None else t.data_ptr()
+
+
+def stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        msg = f"{what} failed with code {rc}"
+        if rc > 0:
+            msg += f" (cudaError {rc})"
+        raise NativeError(msg)
+
+
+# ---- parameter structs (field order mirrors csrc/*.cu) --------------------------------------------
+
+
+class AttnPreParams(C.Structure):
+    _fields_ = [("qkv", vp), ("ld", i32), ("q_lora", i32), ("kv_lora", i32), ("rope_dim", i32), ("idx_dim", i32),
+                ("idx_heads", i32), ("q_norm_w", vp), ("kv_norm_w", vp), ("idx_ln_w", vp), ("idx_ln_b", vp),
+                ("eps", f32), ("theta", f32), ("rope_interleave", i32), ("idx_rope_interleave", i32),
+                ("positions", vp), ("batch_idx", vp), ("page_table", vp), ("pt_stride", i32), ("page_size", i32),
+                ("cp_world", i32), ("cp_rank", i32), ("kv_group", i32), ("kv_cache", vp), ("idx_cache", vp),
+                ("cq_out", vp), ("idx_w_out", vp)]
+
+
+class QPostParams(C.Structure):
+    _fields_ = [("qb", vp), ("ld", i32), ("heads", i32), ("d_nope", i32), ("rope_dim", i32), ("idx_heads", i32),
+                ("idx_dim", i32), ("theta", f32), ("rope_interleave", i32), ("idx_rope_interleave", i32),
+                ("positions", vp), ("idx_w", vp), ("q_pe_out", vp), ("q8_out", vp), ("w_eff_out", vp)]
+
+
+class IndexerScoreParams(C.Structure):
+    _fields_ = [("q8", vp), ("w_eff", vp), ("idx_cache", vp), ("page_table", vp), ("pt_stride", i32),
+                ("batch_idx", vp), ("positions", vp), ("Hi", i32), ("D", i32), ("page_size", i32), ("cp_world", i32),
+                ("cp_rank", i32), ("top_k", i32), ("scores", vp), ("ld_scores", i32)]
+
+
+class TopkSelectParams(C.Structure):
+    _fields_ = [("scores", vp), ("ld_scores", i32), ("positions", vp), ("top_k", i32), ("cp_world", i32),
+                ("cp_rank", i32), ("out_pos", vp), ("out_score", vp)]
+
+
+class SparseMlaParams(C.Structure):
+    _fields_ = [("q_abs", vp), ("q_pe", vp), ("kv_cache", vp), ("slots", vp), ("lengths", vp), ("h", i32), ("R", i32),
+                ("Dr", i32), ("group", i32), ("topk", i32), ("splits", i32), ("sm_scale", f32), ("o_part", vp),
+                ("lse_part", vp)]
+
+
+class CombineParams(C.Structure):
+    _fields_ = [("o_ptrs", vp * 8), ("lse_ptrs", vp * 8), ("n_buf", i32), ("parts_per_buf", i32), ("h", i32), ("R", i32),
+                ("head_begin", i32), ("head_count", i32), ("o_out", vp), ("lse_out", vp)]
+
+
+class MoeGateUpParams(C.Structure):
+    _fields_ = [("x", vp), ("ldx", i32), ("ids", vp), ("T", i32), ("top_k", i32), ("H", i32), ("I", i32),
+                ("expert_offset", i32), ("num_local", i32), ("w13", vp), ("s13", vp), ("g13", vp), ("sw13", vp),
+                ("ss13", vp), ("sg13", vp), ("act", vp)]
+
+
+class MoeDownParams(C.Structure):
+    _fields_ = [("act", vp), ("ids", vp), ("wts", vp), ("T", i32), ("top_k", i32), ("H", i32), ("I", i32),
+                ("expert_offset", i32), ("num_local", i32), ("w2", vp), ("s2", vp), ("g2", vp), ("sw2", vp), ("ss2", vp),
+                ("sg2", vp), ("out", vp), ("out_f32", i32), ("accumulate", i32)]
+
+
+class SampleParams(C.Structure):
+    _fields_ = [("logits", vp), ("V", i32), ("ld", i32), ("temperature", vp), ("top_p", vp), ("rep_penalty", vp),
+                ("presence_penalty", vp), ("top_k", vp), ("history", vp), ("hist_len", vp), ("window", i32),
+                ("max_k", i32), ("counter", u32), ("stream", u32), ("row_ids", vp), ("out_token", vp), ("cand_ids", vp),
+                ("cand_probs", vp)]
+
+
+class SpecRejectParams(C.Structure):
+    _fields_ = [("draft_tokens", vp), ("draft_ids", vp), ("draft_probs", vp), ("target_ids", vp), ("target_probs", vp),
+                ("D", i32), ("C", i32), ("counter", u32), ("out_tokens", vp), ("num_accepted", vp)]
+
+
+# ---- function signatures ----------------------------------------------------------------------------------
+
+_SIGS = {
+    "sl_embed": [vp, vp, vp, i32, i32, vp],
+    "sl_add_rmsnorm": [vp, vp, vp, vp, vp, i32, i32, f32, i32, vp],
+    "sl_attn_pre": [C.POINTER(AttnPreParams), i32, vp],
+    "sl_q_post": [C.POINTER(QPostParams), i32, vp],
+    "sl_bmv": [vp, vp, vp, i32, i32, i32, i32, i32, i32, vp],
+    "sl_silu_mul": [vp, vp, i32, i32, vp],
+    "sl_route_topk": [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, f32, vp],
+    "sl_topk_to_slots": [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp],
+    "sl_rotate_input_ids": [vp, vp, vp, vp, i32, vp],
+    "sl_gemv_bf16": [vp, vp, vp, i32, i32, i32, i32, i32, vp],
+    "sl_gemv_nvfp4": [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp],
+    "sl_moe_gate_up": [C.POINTER(MoeGateUpParams), vp],
+    "sl_moe_down": [C.POINTER(MoeDownParams), vp],
+    "sl_indexer_scores": [C.POINTER(IndexerScoreParams), i32, i32, vp],
+    "sl_topk_select": [C.POINTER(TopkSelectParams), i32, vp],
+    "sl_sparse_mla_split": [C.POINTER(SparseMlaParams), i32, vp],
+    "sl_mla_combine": [C.POINTER(CombineParams), i32, vp],
+    "sl_argmax": [vp, vp, i32, i32, i32, i32, i64, vp, vp],
+    "sl_sample": [C.POINTER(SampleParams), i32, vp],
+    "sl_spec_reject": [C.POINTER(SpecRejectParams), i32, vp],
+    "sl_gemm_bf16_tcgen05": [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp, i32, vp],
+}
+
+
+@lru_cache(maxsize=None)
+def fn(name: str):
+    f = getattr(kernels(), name)
+    f.argtypes = _SIGS[name]
+    f.restype = i32
+    return f
+
+
+_launches = 0
+
+
+def launch_count() -> int:
+    """Number of native kernel-launching calls made so far by this process."""
+    return _launches
+
+
+def call(name: str, *args) -> None:
+    global _launches
+    _launches += 1
+    check(fn(name)(*args), name)

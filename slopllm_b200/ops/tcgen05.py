@@ -1,0 +1,40 @@
+"""Python entry points of the tcgen05 (TMEM / TMA) GEMM kernels."""
+from __future__ import annotations
+
+import torch
+
+from . import native as N
+
+_err = {}
+
+
+def error_flag(device) -> torch.Tensor:
+    """Per-device int32 word that kernels set when one of their bounded waits expires."""
+    key = torch.device(device).index or 0
+    if key not in _err:
+        _err[key] = torch.zeros(4, dtype=torch.int32, device=device)
+    return _err[key]
+
+
+def check_errors(device) -> None:
+    code = int(error_flag(device)[0].item())
+    if code:
+        error_flag(device).zero_()
+        raise N.NativeError(f"tcgen05 kernel reported an expired wait (site {code})")
+
+
+def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out_f32: bool = False, bn: int = 128) -> torch.Tensor:
+    """y[M, N] = x[M, K] @ w[N, K]^T on tcgen05 tensor cores (bf16 in, fp32 accumulate)."""
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+    if x.stride(-1) != 1:
+        x = x.contiguous()
+    if w.stride(-1) != 1:
+        w = w.contiguous()
+    M, K = x.shape
+    Nn = w.shape[0]
+    pad = 4 if out_f32 else 8                        # 16-byte aligned rows for the vector stores
+    ld = (Nn + pad - 1) // pad * pad
+    y = torch.empty(M, ld, dtype=torch.float32 if out_f32 else torch.bfloat16, device=x.device)[:, :Nn]
+    N.call("sl_gemm_bf16_tcgen05", x.data_ptr(), w.data_ptr(), y.data_ptr(), M, Nn, K, x.stride(0), w.stride(0),
+           y.stride(0), int(out_f32), error_flag(x.device).data_ptr(), bn, N.stream())
+    return y

@@ -123,6 +123,9 @@ class Comm:
         if self.ctx.world > 1:
             dist.barrier(group=self.ctx.group)
 
+    def check_status(self) -> None:
+        """Raise if a device-side bounded wait expired (library collectives have none)."""
+
     # -- fused-op shaped interface (overridden by the NVLink kernels) -------------------------
     def allreduce_add_rmsnorm(self, ops, partial, residual, weight, eps):
         """sum over ranks of `partial`, add to `residual`, RMSNorm.  Returns (normed, residual')."""

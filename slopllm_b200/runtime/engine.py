@@ -1,0 +1,288 @@
+"""Execution engine: paged KV + step planning + CUDA-graph decode + MTP speculative decode.
+
+This is the layer the scheduler, the benchmarks and the server call.  It corresponds to the
+reference's `ExecutionWorkspace.planDecode/planPrefill` (`src/execution-workspace.ts:553-783`),
+`ChatModel.executePrefill/generateDecode` (`src/chat_model.ts:346-449`) and
+`Glm51Model.generateMtpDecode` (`src/glm51_model.ts:1195-1469`).
+
+Per decode step the host writes the step's token ids, positions and page table into one
+pinned staging buffer, issues a single async H2D copy into the static device buffers the
+captured graph reads, replays the graph, and reads the sampled tokens back with one D2H copy.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional, Sequence as Seq
+
+import torch
+
+from ..config import PAGE_SIZE, GlmMoeDsaConfig
+from ..kv.paged import PagedKVCache, Sequence
+from ..models.glm_moe_dsa import GlmMoeDsaModel, KVCacheTensors, StepState
+from ..ops import reference as R
+from ..parallel.dist import ParallelContext
+from .graphs import CaptureManager
+
+
+@dataclass
+class StepBuffers:
+    """Static device buffers (+ pinned host mirror) for one (batch, tokens-per-row) shape."""
+
+    B: int
+    tpr: int                       # tokens per row in the step (1 decode, D+1 verification)
+    width: int                     # page-table width
+    host: torch.Tensor             # pinned int32 [n]
+    dev: torch.Tensor              # device int32 [n]
+
+    @classmethod
+    def create(cls, B: int, tpr: int, width: int, device) -> "StepBuffers":
+        n = 3 * B * tpr + B * width
+        pin = device.type == "cuda"
+        host = torch.zeros(n, dtype=torch.int32, pin_memory=pin)
+        return cls(B, tpr, width, host, torch.zeros(n, dtype=torch.int32, device=device))
+
+    def views(self, t: torch.Tensor):
+        T = self.B * self.tpr
+        return t[:T], t[T:2 * T], t[2 * T:3 * T], t[3 * T:].view(self.B, self.width)
+
+    def nbytes(self) -> int:
+        return self.host.numel() * 4
+
+
+class Engine:
+    def __init__(self, cfg: GlmMoeDsaConfig, model: GlmMoeDsaModel, num_pages: int, max_batch: int = 8,
+                 max_seq_len: int = 16384, cuda_graph: bool = True, mtp: int = 0):
+        self.cfg = cfg
+        self.model = model
+        self.ctx: ParallelContext = model.ctx
+        self.device = self.ctx.device
+        self.kv = PagedKVCache(num_pages, self.ctx.cp_world, copy_page=self._copy_page)
+        self.cache = KVCacheTensors.allocate(cfg, num_pages, self.device, len(model.w.layers))
+        self.max_batch = max_batch
+        self.pt_width = -(-max_seq_len // (PAGE_SIZE * self.ctx.cp_world)) + 1
+        self.graphs = CaptureManager(enabled=cuda_graph and self.device.type == "cuda")
+        self.mtp = mtp
+        self._bufs = {}
+        self._out_host = {}
+        self.h2d_bytes = 0
+        self.d2h_bytes = 0
+
+    # ---- pages ---------------------------------------------------------------------------------------
+    def _copy_page(self, src: int, dst: int) -> None:
+        a, b = slice(src * PAGE_SIZE, (src + 1) * PAGE_SIZE), slice(dst * PAGE_SIZE, (dst + 1) * PAGE_SIZE)
+        for lc in self.cache.layers:
+            lc.kv[b] = lc.kv[a]
+            if lc.idx is not None:
+                lc.idx[b] = lc.idx[a]
+
+    def _buffers(self, B: int, tpr: int) -> StepBuffers:
+        key = (B, tpr)
+        if key not in self._bufs:
+            self._bufs[key] = StepBuffers.create(B, tpr, self.pt_width, self.device)
+        return self._bufs[key]
+
+    def _upload(self, buf: StepBuffers, ids, positions, batch_idx, seqs: Seq[Sequence]) -> None:
+        h_ids, h_pos, h_bi, h_pt = buf.views(buf.host)
+        h_ids[: len(ids)] = torch.as_tensor(ids, dtype=torch.int32)
+        h_pos[: len(ids)] = torch.as_tensor(positions, dtype=torch.int32)
+        h_bi[: len(ids)] = torch.as_tensor(batch_idx, dtype=torch.int32)
+        h_pt.zero_()
+        for b, s in enumerate(seqs):
+            n = min(len(s.pages), buf.width)
+            h_pt[b, :n] = torch.as_tensor(s.pages[:n], dtype=torch.int32)
+        buf.dev.copy_(buf.host, non_blocking=True)
+        self.h2d_bytes += buf.nbytes()
+
+    def _state(self, buf: StepBuffers, max_kv_len: int, logits_idx=None) -> StepState:
+        ids, pos, bi, pt = buf.views(buf.dev)
+        return StepState(input_ids=ids, positions=pos, batch_idx=bi, page_table=pt, logits_idx=logits_idx,
+                         cp_world=self.ctx.cp_world, cp_rank=self.ctx.cp_rank, max_kv_len=max_kv_len)
+
+    # ---- prefill -------------------------------------------------------------------------------------------
+    def prefill(self, seqs: Seq[Sequence], prompts: Seq[Seq[int]], chunk_size: int = 8192,
+                want_hidden: bool = False):
+        """Chunked prefill of each prompt's uncached tail.  Returns (next token per sequence
+        (greedy), last hidden per sequence or None).  Sequences are processed one after the
+        other in chunks of at most `chunk_size` tokens (page-aligned boundaries)."""
+        tokens, hiddens = [], []
+        for s, prompt in zip(seqs, prompts):
+            start = s.length
+            last_hidden = None
+            while start < len(prompt):
+                n = min(chunk_size, len(prompt) - start)
+                ids = list(prompt[start:start + n])
+                self.kv.append_tokens(s, ids)
+                positions = list(range(start, start + n))
+                st = self._eager_state(ids, positions, [0] * n, [s], max_kv_len=start + n)
+                hidden = self.model.forward_hidden(st, self.cache)
+                if self.mtp and self.cfg.num_nextn_predict_layers:
+                    self._prefill_mtp(st, hidden, prompt, start, n)
+                self.kv.report_tokens(s)
+                last_hidden = hidden[-1:]
+                start += n
+            logits = self.model.compute_logits(last_hidden)
+            tokens.append(int(logits.argmax(-1)))
+            hiddens.append(last_hidden)
+        return tokens, (hiddens if want_hidden else None)
+
+    def _prefill_mtp(self, st: StepState, hidden, prompt, start: int, n: int) -> None:
+        """Fill the MTP layer's KV over the chunk: position i pairs (h_i, token_{i+1})."""
+        nxt = list(prompt[start + 1:start + n + 1])
+        if len(nxt) < n:
+            nxt.append(0)            # the pair at the last prompt position is redone at decode time
+        st2 = StepState(input_ids=torch.as_tensor(nxt, dtype=torch.int64, device=self.device), positions=st.positions,
+                        batch_idx=st.batch_idx, page_table=st.page_table, cp_world=st.cp_world, cp_rank=st.cp_rank,
+                        max_kv_len=st.max_kv_len)
+        self.model.forward_mtp(st2, self.cache, hidden)
+
+    def _eager_state(self, ids, positions, batch_idx, seqs, max_kv_len, logits_idx=None) -> StepState:
+        dev = self.device
+        width = max(self.pt_width, max(len(s.pages) for s in seqs))
+        pt = torch.tensor(self.kv.page_table_rows(seqs, width), dtype=torch.int32, device=dev)
+        return StepState(input_ids=torch.as_tensor(ids, dtype=torch.int64, device=dev),
+                         positions=torch.as_tensor(positions, dtype=torch.int32, device=dev),
+                         batch_idx=torch.as_tensor(batch_idx, dtype=torch.int32, device=dev), page_table=pt,
+                         logits_idx=logits_idx, cp_world=self.ctx.cp_world, cp_rank=self.ctx.cp_rank,
+                         max_kv_len=max_kv_len)
+
+    # ---- plain decode -----------------------------------------------------------------------------------------
+    def decode_step(self, seqs: Seq[Sequence], last_tokens: Seq[int]) -> List[int]:
+        """One token per sequence: append `last_tokens`, run the model, return the next
+        (greedy) tokens.  Graph-captured per (batch, KV bucket)."""
+        B = len(seqs)
+        positions = []
+        for s, t in zip(seqs, last_tokens):
+            positions.append(s.length)
+            self.kv.append_tokens(s, [t])
+        buf = self._buffers(B, 1)
+        self._upload(buf, list(last_tokens), positions, list(range(B)), seqs)
+        bucket = R.padded_kv_len(max(positions) + 1)
+        st = self._state(buf, bucket)
+
+        def run():
+            hidden = self.model.forward_hidden(st, self.cache)
+            return self._greedy(hidden)
+
+        out = self.graphs.execute(("decode", B, bucket), run)
+        host = self._readback(("decode", B), out)
+        for s in seqs:
+            self.kv.report_tokens(s)
+        return host.tolist()
+
+    def _greedy(self, hidden: torch.Tensor) -> torch.Tensor:
+        """Next-token ids from hidden states (vocabulary-sharded lm_head: local argmax, then
+        the winner across ranks)."""
+        m = self.model
+        local = m.ops.logits(hidden, m.w.lm_head)
+        if self.ctx.world == 1:
+            return m.ops.argmax(local)
+        if hasattr(m.ops, "argmax") and self.device.type == "cuda":
+            ids, vals = m.ops.argmax(local, id_offset=m.w.vocab_offset, want_val=True)
+        else:
+            vals, ids = local.max(-1)
+            ids = ids + m.w.vocab_offset
+        all_v = torch.stack(m.comm.all_gather_list(vals.to(torch.float32)))
+        all_i = torch.stack(m.comm.all_gather_list(ids))
+        best = all_v.argmax(0, keepdim=True)
+        return all_i.gather(0, best).squeeze(0)
+
+    def _readback(self, key, dev_t: torch.Tensor) -> torch.Tensor:
+        host = self._out_host.get(key)
+        if host is None or host.shape != dev_t.shape or host.dtype != dev_t.dtype:
+            host = torch.empty(dev_t.shape, dtype=dev_t.dtype, pin_memory=self.device.type == "cuda")
+            self._out_host[key] = host
+        host.copy_(dev_t, non_blocking=True)
+        if self.device.type == "cuda":
+            torch.cuda.current_stream().synchronize()
+        self.d2h_bytes += host.numel() * host.element_size()
+        return host
+
+    # ---- MTP speculative decode -----------------------------------------------------------------------------------
+    def mtp_seed(self, seqs: Seq[Sequence], last_tokens: Seq[int], last_hiddens: Seq[torch.Tensor]) -> torch.Tensor:
+        """After prefill: run the MTP layer at each sequence's last prompt position with the
+        pair (h_last, first sampled token).  Returns the seed hidden [B, H] that predicts
+        the token after `last_tokens`."""
+        B = len(seqs)
+        positions = [s.length - 1 for s in seqs]
+        st = self._eager_state(list(last_tokens), positions, list(range(B)), seqs, max_kv_len=max(positions) + 1)
+        return self.model.forward_mtp(st, self.cache, torch.cat(list(last_hiddens), 0))
+
+    def mtp_decode_step(self, seqs: Seq[Sequence], last_tokens: Seq[int], seed: torch.Tensor):
+        """One speculative step with D = self.mtp drafts per sequence (greedy verification).
+
+        Returns (accepted tokens per sequence (1..D+1 each), new last tokens, new seed)."""
+        D, B = self.mtp, len(seqs)
+        tpr = D + 1
+        p0 = [s.length for s in seqs]
+        for s, t in zip(seqs, last_tokens):
+            self.kv.append_tokens(s, [t] + [0] * D)          # over-allocate D+1, truncated below
+        buf = self._buffers(B, tpr)
+        ids = []
+        positions = []
+        bidx = []
+        for b in range(B):
+            ids += [last_tokens[b]] + [0] * D
+            positions += list(range(p0[b], p0[b] + tpr))
+            bidx += [b] * tpr
+        self._upload(buf, ids, positions, bidx, seqs)
+        bucket = R.padded_kv_len(max(positions) + 1)
+        st = self._state(buf, bucket)
+        seed_buf = self._static("mtp_seed", (B, self.cfg.hidden_size), seed.dtype)
+        seed_buf.copy_(seed)
+
+        def run():
+            return self._mtp_graph_body(st, seed_buf, B, D)
+
+        out_tokens, n_acc, new_seed = self.graphs.execute(("mtp", B, D, bucket), run)
+        packed = self._readback(("mtp", B), torch.cat([out_tokens, n_acc.unsqueeze(1)], 1))
+        accepted, new_last = [], []
+        for b, s in enumerate(seqs):
+            a = int(packed[b, tpr])
+            toks = [int(x) for x in packed[b, :a + 1]]
+            # KV now holds last_token + a accepted drafts; the bonus token is the new last token
+            self.kv.truncate(s, p0[b] + a + 1)
+            s.token_ids[p0[b] + 1:p0[b] + a + 1] = toks[:a]
+            self.kv.report_tokens(s)
+            accepted.append(toks)
+            new_last.append(toks[-1])
+        return accepted, new_last, new_seed
+
+    def _static(self, name: str, shape, dtype) -> torch.Tensor:
+        key = (name, tuple(shape), dtype)
+        t = self._bufs.get(key)
+        if t is None:
+            t = torch.zeros(shape, dtype=dtype, device=self.device)
+            self._bufs[key] = t
+        return t
+
+    def _mtp_graph_body(self, st: StepState, seed: torch.Tensor, B: int, D: int):
+        m, dev = self.model, self.device
+        tpr = D + 1
+        ids2d = st.input_ids.view(B, tpr)
+        pos2d = st.positions.view(B, tpr)
+        rows = torch.arange(B, dtype=torch.int32, device=dev)
+        # --- draft chain: d1 from the seed, then D-1 single-token MTP passes ---
+        hidden = seed
+        for depth in range(D):
+            d = self._greedy(hidden)
+            ids2d[:, depth + 1] = d.to(ids2d.dtype)
+            if depth + 1 < D:
+                stp = StepState(input_ids=d, positions=pos2d[:, depth].contiguous(), batch_idx=rows,
+                                page_table=st.page_table, cp_world=st.cp_world, cp_rank=st.cp_rank,
+                                max_kv_len=st.max_kv_len)
+                hidden = m.forward_mtp(stp, self.cache, hidden)
+        # --- verification: main model over [last, d1..dD] ---
+        h = m.forward_hidden(st, self.cache)
+        target = self._greedy(h).view(B, tpr)
+        drafts = ids2d[:, 1:].to(target.dtype)
+        ok = (drafts == target[:, :D]).to(torch.int32)
+        n_acc = torch.cumprod(ok, dim=1).sum(1)                                   # [B]
+        j = torch.arange(tpr, device=dev).unsqueeze(0)
+        bonus = target.gather(1, n_acc.unsqueeze(1).to(torch.int64))               # [B, 1]
+        out_tokens = torch.where(j < n_acc.unsqueeze(1), torch.cat([drafts, drafts[:, :1]], 1), bonus.expand(B, tpr))
+        # --- reseed: MTP layer over the verification positions with (h_j, next token_j) ---
+        st2 = StepState(input_ids=out_tokens.reshape(-1), positions=st.positions, batch_idx=st.batch_idx,
+                        page_table=st.page_table, cp_world=st.cp_world, cp_rank=st.cp_rank, max_kv_len=st.max_kv_len)
+        hm = m.forward_mtp(st2, self.cache, h).view(B, tpr, -1)
+        new_seed = hm.gather(1, n_acc.view(B, 1, 1).to(torch.int64).expand(B, 1, hm.shape[-1])).squeeze(1)
+        return out_tokens, n_acc.to(out_tokens.dtype), new_seed

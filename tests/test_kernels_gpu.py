@@ -1,0 +1,270 @@
+"""Each sm_100a kernel against the plain PyTorch fp32 reference of the same op.
+
+Tolerances follow the reference's kernel tests (ATOL = RTOL = 1e-2 on bf16 data,
+`tests/python/helpers.py`), relative to the magnitude of the expected output.
+"""
+import math
+
+import pytest
+import torch
+
+from slopllm_b200.config import GlmMoeDsaConfig
+from slopllm_b200.models.glm_moe_dsa import KVCacheTensors, StepState
+from slopllm_b200.models.weights import LinearWeight, random_layer
+from slopllm_b200.ops import RefOps, quant, reference as R
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def close(a, b, tol=1e-2, what=""):
+    a, b = a.to(torch.float32), b.to(torch.float32)
+    assert a.shape == b.shape, (what, a.shape, b.shape)
+    scale = b.abs().max().clamp(min=1e-6)
+    err = ((a - b).abs().max() / scale).item()
+    assert err <= tol, f"{what}: max rel-to-peak error {err:.4g} > {tol}"
+
+
+def cuda_ops(cfg):
+    from slopllm_b200.ops.cuda_ops import CudaOps
+    return CudaOps(cfg)
+
+
+def mini_cfg(**kw):
+    """GLM-5 head geometry with a small hidden size and few experts."""
+    base = dict(hidden_size=1024, intermediate_size=1024, moe_intermediate_size=256, num_hidden_layers=2,
+                num_nextn_predict_layers=1, vocab_size=4096, num_attention_heads=8, q_lora_rank=512, kv_lora_rank=512,
+                qk_nope_head_dim=192, qk_rope_head_dim=64, v_head_dim=256, n_routed_experts=16, n_shared_experts=1,
+                num_experts_per_tok=4, n_group=4, topk_group=2, index_topk=256, index_head_dim=128, index_n_heads=32,
+                first_k_dense_replace=1, quant_o_proj=True, quant_dense_mlp=True)
+    base.update(kw)
+    return GlmMoeDsaConfig(**base)
+
+
+@pytest.mark.parametrize("T", [1, 2, 3, 8, 19])
+@pytest.mark.parametrize("N,K", [(256, 512), (2784, 6144), (1000, 2048)])
+def test_gemv_bf16(T, N, K):
+    g = torch.Generator(device=DEV).manual_seed(T * 7 + N)
+    x = torch.randn(T, K, device=DEV, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, device=DEV, generator=g) * 0.05).to(torch.bfloat16)
+    ops = cuda_ops(GlmMoeDsaConfig.tiny())
+    for f32 in (False, True):
+        y = ops.linear(x, LinearWeight(w), out_f32=f32)
+        close(y, x.float() @ w.float().t(), what=f"gemv_bf16 T={T} f32={f32}")
+
+
+@pytest.mark.parametrize("T", [1, 2, 4, 7, 16])
+@pytest.mark.parametrize("N,K", [(512, 256), (6144, 2048), (4096, 6144)])
+def test_gemv_nvfp4(T, N, K):
+    g = torch.Generator(device=DEV).manual_seed(T + K)
+    x = torch.randn(T, K, device=DEV, generator=g).to(torch.bfloat16)
+    w = LinearWeight(*quant.random_nvfp4((N, K), g, DEV))
+    w.scale2.fill_(0.37)
+    ops = cuda_ops(GlmMoeDsaConfig.tiny())
+    y = ops.linear(x, w, out_f32=True)
+    close(y, R.linear(x, w), what=f"gemv_nvfp4 T={T}")
+
+
+def test_nvfp4_roundtrip_quantize():
+    g = torch.Generator(device=DEV).manual_seed(3)
+    w = torch.randn(64, 256, device=DEV, generator=g)
+    p, s, gs = quant.nvfp4_quantize(w)
+    wd = quant.nvfp4_dequantize(p, s, gs)
+    assert ((wd - w).abs().mean() / w.abs().mean()).item() < 0.12
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (256, 384, 512), (300, 200, 1024), (1000, 2784, 6144), (4096, 6144, 2048)])
+@pytest.mark.parametrize("bn", [64, 128, 256])
+def test_gemm_tcgen05(M, N, K, bn):
+    from slopllm_b200.ops import tcgen05
+    g = torch.Generator(device=DEV).manual_seed(M + N)
+    a = torch.randn(M, K, device=DEV, generator=g).to(torch.bfloat16)
+    b = (torch.randn(N, K, device=DEV, generator=g) * 0.05).to(torch.bfloat16)
+    for f32 in (True, False):
+        y = tcgen05.gemm_bf16(a, b, f32, bn=bn)
+        torch.cuda.synchronize()
+        tcgen05.check_errors(DEV)
+        close(y, a.float() @ b.float().t(), tol=1e-2, what=f"tcgen05 gemm {M}x{N}x{K} bn={bn} f32={f32}")
+
+
+def test_add_rmsnorm_and_embed():
+    cfg = GlmMoeDsaConfig.tiny()
+    ops, ref = cuda_ops(cfg), RefOps(cfg)
+    g = torch.Generator(device=DEV).manual_seed(0)
+    H = 6144
+    table = torch.randn(100, H, device=DEV, generator=g).to(torch.bfloat16)
+    ids = torch.tensor([3, 99, 0, 7], device=DEV)
+    assert torch.equal(ops.embed(ids, table), table[ids])
+    x = torch.randn(5, H, device=DEV, generator=g)
+    res = torch.randn(5, H, device=DEV, generator=g)
+    w = torch.rand(H, device=DEV, generator=g).to(torch.bfloat16)
+    for xin in (x, x.to(torch.bfloat16)):
+        o, r = ops.add_rmsnorm(xin, res, w)
+        eo, er = ref.add_rmsnorm(xin, res, w)
+        close(o, eo, what="add_rmsnorm out")
+        close(r, er, tol=1e-5, what="residual")
+    o, r = ops.add_rmsnorm(x, None, w)
+    close(o, ref.add_rmsnorm(x, None, w)[0], what="rmsnorm first")
+
+
+def _state(cfg, positions, batch_idx, n_pages_per_seq, B, cp_world=1, cp_rank=0):
+    pt = torch.arange(B * n_pages_per_seq, dtype=torch.int32, device=DEV).reshape(B, n_pages_per_seq)
+    # shuffle physical pages so that logical != physical
+    perm = torch.randperm(B * n_pages_per_seq, device=DEV, generator=torch.Generator(device=DEV).manual_seed(5))
+    pt = perm[pt.to(torch.int64)].to(torch.int32)
+    pos = torch.tensor(positions, dtype=torch.int32, device=DEV)
+    return StepState(input_ids=torch.zeros(len(positions), dtype=torch.int64, device=DEV), positions=pos,
+                     batch_idx=torch.tensor(batch_idx, dtype=torch.int32, device=DEV), page_table=pt,
+                     cp_world=cp_world, cp_rank=cp_rank, max_kv_len=max(positions) + 1)
+
+
+@pytest.mark.parametrize("which", ["tiny", "mini"])
+@pytest.mark.parametrize("cp", [(1, 0), (2, 1)])
+def test_attn_pre_and_q_post(which, cp):
+    cfg = GlmMoeDsaConfig.tiny() if which == "tiny" else mini_cfg()
+    ops, ref = cuda_ops(cfg), RefOps(cfg)
+    lw = random_layer(cfg, 1 if which == "tiny" else 0, 0, DEV, torch.bfloat16)
+    T = 6
+    st = _state(cfg, [0, 1, 130, 131, 5, 64], [0, 0, 0, 0, 1, 1], 4, 2, *cp)
+    g = torch.Generator(device=DEV).manual_seed(1)
+    x = torch.randn(T, cfg.hidden_size, device=DEV, generator=g).to(torch.bfloat16)
+    qkv = ref.linear(x, lw.w_qkv_a).to(torch.bfloat16)
+    c1 = KVCacheTensors.allocate(cfg, 8, DEV, 1).layers[0]
+    c2 = KVCacheTensors.allocate(cfg, 8, DEV, 1).layers[0]
+    if c1.idx is None:
+        c1.idx = torch.zeros(8 * 64, cfg.index_row_bytes, dtype=torch.uint8, device=DEV)
+        c2.idx = torch.zeros_like(c1.idx)
+    cq, iw = ops.attn_pre(qkv, lw, st, c1)
+    ecq, eiw = ref.attn_pre(qkv, lw, st, c2)
+    close(cq, ecq, what="c_q")
+    close(iw, eiw, what="idx_w")
+    a, b = quant.unpack_kv_rows(c1.kv, cfg.kv_lora_rank, cfg.qk_rope_head_dim, cfg.kv_quant_group)
+    ea, eb = quant.unpack_kv_rows(c2.kv, cfg.kv_lora_rank, cfg.qk_rope_head_dim, cfg.kv_quant_group)
+    close(a, ea, tol=7e-2, what="ckv rows")      # one e4m3 step at most
+    close(b, eb, what="kpe rows")
+    close(quant.unpack_index_rows(c1.idx, cfg.index_head_dim), quant.unpack_index_rows(c2.idx, cfg.index_head_dim),
+          tol=7e-2, what="index rows")
+    qb = ref.linear(ecq, lw.w_q_b).to(torch.bfloat16)
+    qa, qp, q8, we = ops.q_post(qb, lw, st, iw)
+    eqa, eqp, eq8, ewe = ref.q_post(qb, lw, st, eiw)
+    close(qa, eqa, what="q_abs")
+    close(qp, eqp, what="q_pe")
+    got = q8.view(torch.float8_e4m3fn).float() * (we / (iw * cfg.index_head_dim ** -0.5)).unsqueeze(-1)
+    exp = eq8 * (ewe / (eiw * cfg.index_head_dim ** -0.5)).unsqueeze(-1)
+    close(got, exp, tol=7e-2, what="indexer q")
+
+
+@pytest.mark.parametrize("E,k,ng,tg", [(256, 8, 8, 4), (256, 8, 1, 1), (8, 2, 1, 1), (16, 4, 4, 2)])
+def test_route_topk(E, k, ng, tg):
+    cfg = mini_cfg(n_routed_experts=E, num_experts_per_tok=k, n_group=ng, topk_group=tg, hidden_size=512)
+    ops, ref = cuda_ops(cfg), RefOps(cfg)
+    g = torch.Generator(device=DEV).manual_seed(E)
+    lw = type("L", (), {})()
+    lw.router_w = torch.randn(E, 512, device=DEV, generator=g).to(torch.bfloat16)
+    lw.router_bias = torch.randn(E, device=DEV, generator=g) * 0.1
+    x = torch.randn(9, 512, device=DEV, generator=g).to(torch.bfloat16)
+    logits = ops._router_logits(x, lw)
+    ids, w = ops.route(x, lw)
+    eids, ew = R.moe_route(logits, lw.router_bias, k, ng, tg, True, cfg.routed_scaling_factor)
+    assert torch.equal(ids.sort(1).values, eids.sort(1).values)
+    close(w.gather(1, ids.argsort(1)), ew.gather(1, eids.argsort(1)), tol=1e-4, what="route weights")
+
+
+def test_topk_to_slots():
+    cfg = mini_cfg()
+    ops, ref = cuda_ops(cfg), RefOps(cfg)
+    st = _state(cfg, [300, 301, 17], [0, 0, 1], 8, 2, 2, 1)
+    pos = torch.full((3, 256), -1, dtype=torch.int32, device=DEV)
+    pos[0, :200] = torch.arange(0, 200, dtype=torch.int32, device=DEV) + 50
+    pos[1, :256] = torch.arange(0, 256, dtype=torch.int32, device=DEV) + 40
+    pos[2, :18] = torch.arange(18, dtype=torch.int32, device=DEV)
+    for local_only in (False, True):
+        s, l = ops.topk_to_slots(pos, st, local_only)
+        es, el = ref.topk_to_slots(pos, st, local_only)
+        assert torch.equal(l, el)
+        assert torch.equal(s, es)
+
+
+@pytest.mark.parametrize("which,ctx", [("tiny", 300), ("mini", 700), ("mini", 3000)])
+@pytest.mark.parametrize("cp", [(1, 0), (4, 3)])
+def test_indexer_topk(which, ctx, cp):
+    cfg = GlmMoeDsaConfig.tiny() if which == "tiny" else mini_cfg()
+    ops, ref = cuda_ops(cfg), RefOps(cfg)
+    W, r = cp
+    n_pages = -(-ctx // (64 * W)) + 1
+    positions = [ctx - 1, ctx - 2, cfg.index_topk - 1, 10]
+    st = _state(cfg, positions, [0, 0, 1, 1], n_pages, 2, W, r)
+    g = torch.Generator(device=DEV).manual_seed(ctx)
+    Di, Hi = cfg.index_head_dim, cfg.index_n_heads
+    cache = type("C", (), {})()
+    keys = torch.randn(2 * n_pages * 64, Di, device=DEV, generator=g)
+    cache.idx = quant.pack_index_rows(keys)
+    q = torch.randn(4, Hi, Di, device=DEV, generator=g)
+    hw = torch.rand(4, Hi, device=DEV, generator=g)
+    q8f, weff = R.indexer_quantize_q(q, hw, Di ** -0.5)
+    q8 = q8f.to(torch.float8_e4m3fn).view(torch.uint8)
+    pos, sc = ops.indexer_topk(q8, weff, cache, st)
+    epos, esc = ref.indexer_topk(q8f, weff, cache, st)
+    for t in range(4):
+        a, b = set(pos[t][pos[t] >= 0].tolist()), set(epos[t][epos[t] >= 0].tolist())
+        assert len(a) == len(b), (t, len(a), len(b))
+        assert len(a ^ b) <= max(2, len(b) // 100), (t, len(a ^ b))      # ties at the threshold only
+        valid = pos[t][pos[t] >= 0]
+        assert torch.all(valid[1:] > valid[:-1])
+
+
+@pytest.mark.parametrize("which", ["tiny", "mini"])
+def test_sparse_mla_and_v_expand(which):
+    cfg = GlmMoeDsaConfig.tiny() if which == "tiny" else mini_cfg()
+    ops, ref = cuda_ops(cfg), RefOps(cfg)
+    g = torch.Generator(device=DEV).manual_seed(11)
+    Rr, Dr, h, k = cfg.kv_lora_rank, cfg.qk_rope_head_dim, cfg.num_attention_heads, cfg.index_topk
+    nslots = 1024
+    cache = type("C", (), {})()
+    cache.kv = quant.pack_kv_rows(torch.randn(nslots, Rr, device=DEV, generator=g),
+                                  torch.randn(nslots, Dr, device=DEV, generator=g), cfg.kv_quant_group)
+    T = 3
+    q_abs = (torch.randn(T, h, Rr, device=DEV, generator=g) * 0.3).to(torch.bfloat16)
+    q_pe = (torch.randn(T, h, Dr, device=DEV, generator=g) * 0.3).to(torch.bfloat16)
+    slots = torch.full((T, k), -1, dtype=torch.int32, device=DEV)
+    lengths = torch.tensor([k, 37, 0], dtype=torch.int32, device=DEV)
+    for t in range(T):
+        n = int(lengths[t])
+        slots[t, :n] = torch.randperm(nslots, device=DEV, generator=g)[:n].to(torch.int32)
+    o, lse = ops.sparse_mla(q_abs, q_pe, cache, slots, lengths)
+    eo, elo = ref.sparse_mla(q_abs, q_pe, cache, slots, lengths)
+    close(o, eo, what="sparse mla o")
+    close(lse[:2], elo[:2], tol=1e-3, what="lse")
+    assert torch.isinf(lse[2]).all()
+    w_v = (torch.randn(h, Rr, cfg.v_head_dim, device=DEV, generator=g) * 0.05).to(torch.bfloat16)
+    close(ops.v_expand(o, w_v), ref.v_expand(o, w_v), what="v_expand")
+
+
+@pytest.mark.parametrize("T", [1, 4, 9])
+def test_moe_small_and_dense(T):
+    cfg = mini_cfg(hidden_size=2048, moe_intermediate_size=512)
+    ops, ref = cuda_ops(cfg), RefOps(cfg)
+    lw = random_layer(cfg, 1, 0, DEV, torch.bfloat16)
+    g = torch.Generator(device=DEV).manual_seed(T)
+    x = torch.randn(T, cfg.hidden_size, device=DEV, generator=g).to(torch.bfloat16)
+    close(ops.moe_tp(x, lw), ref.moe_tp(x, lw), tol=2e-2, what="moe_tp")
+    lw0 = random_layer(cfg, 0, 0, DEV, torch.bfloat16)
+    close(ops.dense_mlp(x, lw0), ref.dense_mlp(x, lw0), tol=2e-2, what="dense mlp")
+
+
+def test_moe_large_matches_reference():
+    cfg = mini_cfg(hidden_size=1024, moe_intermediate_size=256)
+    ops, ref = cuda_ops(cfg), RefOps(cfg)
+    lw = random_layer(cfg, 1, 0, DEV, torch.bfloat16)
+    x = torch.randn(200, cfg.hidden_size, device=DEV, generator=torch.Generator(device=DEV).manual_seed(2)).to(torch.bfloat16)
+    close(ops.moe_tp(x, lw), ref.moe_tp(x, lw), tol=2e-2, what="moe large")
+
+
+def test_argmax():
+    ops = cuda_ops(GlmMoeDsaConfig.tiny())
+    x = torch.randn(5, 154880, device=DEV)
+    assert torch.equal(ops.argmax(x), x.argmax(-1))
+    assert torch.equal(ops.argmax(x.to(torch.bfloat16), id_offset=10), x.to(torch.bfloat16).float().argmax(-1) + 10)
+
+
+_ = math
