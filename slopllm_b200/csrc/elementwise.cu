@@ -10,16 +10,18 @@
 // ---------------------------------------------------------------------------------------------
 // embedding lookup: out[t, :] = table[ids[t], :]
 __global__ void embed_kernel(bf16* __restrict__ out, const int64_t* __restrict__ ids, const bf16* __restrict__ table,
-                             int H) {
+                             int H, int V) {
     const int t = blockIdx.x;
-    const uint4* src = reinterpret_cast<const uint4*>(table + (size_t)ids[t] * H);
+    int64_t id = ids[t];
+    id = id < 0 ? 0 : (id >= V ? V - 1 : id);      // never read outside the table
+    const uint4* src = reinterpret_cast<const uint4*>(table + (size_t)id * H);
     uint4* dst = reinterpret_cast<uint4*>(out + (size_t)t * H);
     for (int i = threadIdx.x; i < H / 8; i += blockDim.x) dst[i] = src[i];
 }
 
-SL_API int sl_embed(void* out, const void* ids, const void* table, int T, int H, cudaStream_t s) {
+SL_API int sl_embed(void* out, const void* ids, const void* table, int T, int H, int V, cudaStream_t s) {
     if (T == 0) return 0;
-    embed_kernel<<<T, 256, 0, s>>>((bf16*)out, (const int64_t*)ids, (const bf16*)table, H);
+    embed_kernel<<<T, 256, 0, s>>>((bf16*)out, (const int64_t*)ids, (const bf16*)table, H, V);
     return SL_LAUNCH_CHECK();
 }
 
@@ -275,59 +277,68 @@ SL_API int sl_q_post(const QPostParams* p, int T, cudaStream_t s) {
 // ---------------------------------------------------------------------------------------------
 // Batched vector x matrix: y[t,h,n] = sum_k x[t,h,k] * M[h,k,n]   (absorb: K=Dn,N=R; v_expand: K=R,N=Dv)
 // x element (t,h,k) at x[t*xs_t + h*xs_h + k]; y bf16 [T, Hh, N] contiguous.
-// grid (Hh, N/256, ceil(T/TT)); block 256: 128 column pairs x 2 halves of K.
+// grid (Hh, N/128, ceil(T/TT)); block 256 = 8 warps.  A warp owns every 8th k row and reads
+// 256 contiguous bytes of it (4 columns per lane); the 8 partial sums meet in shared memory.
 template <int TT>
-__global__ void bmv_kernel(bf16* __restrict__ y, const bf16* __restrict__ x, const bf16* __restrict__ M, int T, int Hh,
-                           int K, int N, int xs_t, int xs_h) {
+__global__ void __launch_bounds__(256) bmv_kernel(bf16* __restrict__ y, const bf16* __restrict__ x, const bf16* __restrict__ M,
+                                                  int T, int Hh, int K, int N, int xs_t, int xs_h) {
     extern __shared__ float xs[];            // [TT][K]
-    __shared__ float red[TT][128][2];
-    const int h = blockIdx.x, n0 = blockIdx.y * 256, t0 = blockIdx.z * TT;
-    const int tid = threadIdx.x, col = tid & 127, half = tid >> 7;
+    __shared__ float red[8][TT][128];
+    const int h = blockIdx.x, n0 = blockIdx.y * 128, t0 = blockIdx.z * TT;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     for (int i = tid; i < TT * K; i += blockDim.x) {
         const int tt = i / K, k = i % K;
         xs[i] = (t0 + tt < T) ? __bfloat162float(x[(size_t)(t0 + tt) * xs_t + (size_t)h * xs_h + k]) : 0.f;
     }
     __syncthreads();
-    float acc[TT][2];
+    float acc[TT][4];
 #pragma unroll
-    for (int tt = 0; tt < TT; ++tt) acc[tt][0] = acc[tt][1] = 0.f;
-    const int n = n0 + col * 2;
+    for (int tt = 0; tt < TT; ++tt)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) acc[tt][c] = 0.f;
+    const int n = n0 + lane * 4;
     if (n < N) {
-        const int k_lo = half * (K / 2), k_hi = k_lo + K / 2;
         const bf16* Mp = M + (size_t)h * K * N + n;
 #pragma unroll 4
-        for (int k = k_lo; k < k_hi; ++k) {
-            const float2 w = bf162_to_f2(*reinterpret_cast<const uint32_t*>(Mp + (size_t)k * N));
+        for (int k = warp; k < K; k += 8) {
+            const uint2 u = ldg_nc_8(Mp + (size_t)k * N);
+            const float2 w0 = bf162_to_f2(u.x), w1 = bf162_to_f2(u.y);
 #pragma unroll
             for (int tt = 0; tt < TT; ++tt) {
-                acc[tt][0] += xs[tt * K + k] * w.x;
-                acc[tt][1] += xs[tt * K + k] * w.y;
+                const float xv = xs[tt * K + k];
+                acc[tt][0] += xv * w0.x; acc[tt][1] += xv * w0.y; acc[tt][2] += xv * w1.x; acc[tt][3] += xv * w1.y;
             }
         }
     }
-    if (half == 1) {
 #pragma unroll
-        for (int tt = 0; tt < TT; ++tt) { red[tt][col][0] = acc[tt][0]; red[tt][col][1] = acc[tt][1]; }
-    }
+    for (int tt = 0; tt < TT; ++tt)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) red[warp][tt][lane * 4 + c] = acc[tt][c];
     __syncthreads();
-    if (half == 0 && n < N) {
+    for (int i = tid; i < TT * 128; i += blockDim.x) {
+        const int tt = i / 128, c = i % 128;
+        if (t0 + tt < T && n0 + c < N) {
+            float v = 0.f;
 #pragma unroll
-        for (int tt = 0; tt < TT; ++tt) {
-            if (t0 + tt < T) {
-                const uint32_t o = f2_to_bf162(acc[tt][0] + red[tt][col][0], acc[tt][1] + red[tt][col][1]);
-                *reinterpret_cast<uint32_t*>(y + ((size_t)(t0 + tt) * Hh + h) * N + n) = o;
-            }
+            for (int w = 0; w < 8; ++w) v += red[w][tt][c];
+            y[((size_t)(t0 + tt) * Hh + h) * N + n0 + c] = __float2bfloat16(v);
         }
     }
 }
 
-SL_API int sl_bmv(void* y, const void* x, const void* M, int T, int Hh, int K, int N, int xs_t, int xs_h, cudaStream_t s) {
-    if (T == 0) return 0;
-    if ((K & 1) || (N & 1)) return -1;
-    constexpr int TT = 4;
-    dim3 grid(Hh, (N + 255) / 256, (T + TT - 1) / TT);
+template <int TT>
+static int launch_bmv(void* y, const void* x, const void* M, int T, int Hh, int K, int N, int xs_t, int xs_h, cudaStream_t s) {
+    dim3 grid(Hh, (N + 127) / 128, (T + TT - 1) / TT);
     bmv_kernel<TT><<<grid, 256, (size_t)TT * K * sizeof(float), s>>>((bf16*)y, (const bf16*)x, (const bf16*)M, T, Hh, K, N, xs_t, xs_h);
     return SL_LAUNCH_CHECK();
+}
+
+SL_API int sl_bmv(void* y, const void* x, const void* M, int T, int Hh, int K, int N, int xs_t, int xs_h, cudaStream_t s) {
+    if (T == 0) return 0;
+    if (N % 4 != 0) return -1;
+    if (T == 1) return launch_bmv<1>(y, x, M, T, Hh, K, N, xs_t, xs_h, s);
+    if (T == 2) return launch_bmv<2>(y, x, M, T, Hh, K, N, xs_t, xs_h, s);
+    return launch_bmv<4>(y, x, M, T, Hh, K, N, xs_t, xs_h, s);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -21,14 +21,15 @@ constexpr int BM = 128, BK = 64;
 template <int BN>
 struct GemmCfg {
     static constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
-    static constexpr int STAGES = (BN >= 256) ? 4 : 6;
+    static constexpr int STAGES = (BN >= 256) ? 4 : (BN <= 32 ? 10 : 6);
     static constexpr int SMEM = STAGES * (A_BYTES + B_BYTES) + 1024 /*align*/ + 256 /*barriers*/;
 };
 
 template <int BN>
 __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA,
                                                         const __grid_constant__ CUtensorMap tmB, void* __restrict__ C,
-                                                        int M, int N, int K, int ldc, int out_f32, int* __restrict__ err) {
+                                                        int M, int N, int K, int ldc, int out_f32, int transpose_out,
+                                                        int* __restrict__ err) {
     using Cfg = GemmCfg<BN>;
     constexpr int STAGES = Cfg::STAGES;
     extern __shared__ uint8_t smem_raw[];
@@ -103,7 +104,16 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
                 tc::tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + c * 32, r);
                 tc::tmem_ld_wait();
                 const int col = n0 + c * 32;
-                if (row < M && col < N) {
+                if (transpose_out) {
+                    // swap-AB use: tile rows are output features, tile columns are token rows;
+                    // C is [N, M] row-major (row stride ldc), a warp writes 32 consecutive features
+                    if (row < M) {
+                        for (int i = 0; i < 32 && col + i < N; ++i) {
+                            if (out_f32) ((float*)C)[(size_t)(col + i) * ldc + row] = __uint_as_float(r[i]);
+                            else ((bf16*)C)[(size_t)(col + i) * ldc + row] = __float2bfloat16(__uint_as_float(r[i]));
+                        }
+                    }
+                } else if (row < M && col < N) {
                     if (out_f32) {
                         float* dst = (float*)C + (size_t)row * ldc + col;
                         if (col + 32 <= N) {
@@ -142,8 +152,8 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
 }
 
 template <int BN>
-int launch(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc, int out_f32, int* err,
-           cudaStream_t s) {
+int launch(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc, int out_f32,
+           int transpose_out, int* err, cudaStream_t s) {
     CUtensorMap tmA, tmB;
     int rc = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)M, (uint64_t)K, (uint64_t)lda * 2, BM, BK);
     if (rc) return rc;
@@ -156,7 +166,7 @@ int launch(const void* A, const void* B, void* C, int M, int N, int K, int lda, 
         attr_set = true;
     }
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-    kern<<<grid, 192, GemmCfg<BN>::SMEM, s>>>(tmA, tmB, C, M, N, K, ldc, out_f32, err);
+    kern<<<grid, 192, GemmCfg<BN>::SMEM, s>>>(tmA, tmB, C, M, N, K, ldc, out_f32, transpose_out, err);
     return (int)cudaGetLastError();
 }
 
@@ -169,7 +179,17 @@ SL_API int sl_gemm_bf16_tcgen05(const void* A, const void* B, void* C, int M, in
     if (M <= 0 || N <= 0 || K <= 0) return 0;
     if (K % 8 != 0 || lda % 8 != 0 || ldb % 8 != 0) return -1;
     if ((out_f32 ? ldc % 4 : ldc % 8) != 0) return -1;
-    if (bn == 64) return launch<64>(A, B, C, M, N, K, lda, ldb, ldc, out_f32, (int*)err, s);
-    if (bn == 256) return launch<256>(A, B, C, M, N, K, lda, ldb, ldc, out_f32, (int*)err, s);
-    return launch<128>(A, B, C, M, N, K, lda, ldb, ldc, out_f32, (int*)err, s);
+    if (bn == 64) return launch<64>(A, B, C, M, N, K, lda, ldb, ldc, out_f32, 0, (int*)err, s);
+    if (bn == 256) return launch<256>(A, B, C, M, N, K, lda, ldb, ldc, out_f32, 0, (int*)err, s);
+    return launch<128>(A, B, C, M, N, K, lda, ldb, ldc, out_f32, 0, (int*)err, s);
+}
+
+// Weight-streaming form for a few token rows (T <= 32): y[T, N] = x[T, K] * W[N, K]^T computed as
+// (W tile of 128 features) x (all tokens): the weights are the 128-row MMA operand fed by a deep TMA
+// ring, the tokens are the narrow N = 32 operand, the epilogue writes the transposed tile.
+SL_API int sl_linear_smallT_bf16_tcgen05(const void* x, const void* W, void* y, int T, int N, int K, int ldx, int ldw, int ldy,
+                                         int out_f32, void* err, cudaStream_t s) {
+    if (T <= 0 || N <= 0 || K <= 0) return 0;
+    if (T > 32 || K % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0) return -1;
+    return launch<32>(W, x, y, N, T, K, ldw, ldx, ldy, out_f32, 1, (int*)err, s);
 }

@@ -63,19 +63,64 @@ __global__ void __launch_bounds__(256) gemv_bf16_kernel(void* __restrict__ y, co
     }
 }
 
+// Small N (router, narrow projections): one block per output row, the 256 threads split K.
 template <int TT>
-static int launch_gemv_bf16(void* y, const void* x, const void* W, int T, int N, int K, int ldx, int out_f32, cudaStream_t s) {
+__global__ void __launch_bounds__(256) gemv_bf16_rowblock_kernel(void* __restrict__ y, const bf16* __restrict__ x,
+                                                                 const bf16* __restrict__ W, int T, int N, int K, int ldx,
+                                                                 int out_f32) {
+    __shared__ float scratch[33];
+    const int n = blockIdx.x, t0 = blockIdx.y * TT;
+    float acc[TT];
+#pragma unroll
+    for (int tt = 0; tt < TT; ++tt) acc[tt] = 0.f;
+    for (int k = threadIdx.x * 8; k < K; k += 256 * 8) {
+        const uint4 w = ldg_nc_16(W + (size_t)n * K + k);
+        const float2 w0 = bf162_to_f2(w.x), w1 = bf162_to_f2(w.y), w2 = bf162_to_f2(w.z), w3 = bf162_to_f2(w.w);
+#pragma unroll
+        for (int tt = 0; tt < TT; ++tt) {
+            if (t0 + tt < T) {
+                const uint4 xv = *reinterpret_cast<const uint4*>(x + (size_t)(t0 + tt) * ldx + k);
+                const float2 x0 = bf162_to_f2(xv.x), x1 = bf162_to_f2(xv.y), x2 = bf162_to_f2(xv.z), x3 = bf162_to_f2(xv.w);
+                acc[tt] += x0.x * w0.x + x0.y * w0.y + x1.x * w1.x + x1.y * w1.y + x2.x * w2.x + x2.y * w2.y + x3.x * w3.x +
+                           x3.y * w3.y;
+            }
+        }
+    }
+#pragma unroll
+    for (int tt = 0; tt < TT; ++tt) {
+        const float v = block_sum(acc[tt], scratch);
+        if (threadIdx.x == 0 && t0 + tt < T) {
+            if (out_f32) ((float*)y)[(size_t)(t0 + tt) * N + n] = v;
+            else ((bf16*)y)[(size_t)(t0 + tt) * N + n] = __float2bfloat16(v);
+        }
+    }
+}
+
+template <int TT, int R>
+static int launch_gemv_bf16_r(void* y, const void* x, const void* W, int T, int N, int K, int ldx, int out_f32, cudaStream_t s) {
     const size_t smem = (size_t)TT * K * sizeof(bf16);
     const int tiles = (T + TT - 1) / TT;
-    constexpr int R = (TT >= 4) ? 2 : 4;
     auto kern = gemv_bf16_kernel<TT, R>;
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     int blocks = (N + 8 * R - 1) / (8 * R);
-    const int cap = 148 * 4;
+    const int cap = 148 * 8;
     if (blocks > cap) blocks = cap;
     if (blocks < 1) blocks = 1;
     kern<<<dim3(blocks, tiles), 256, smem, s>>>(y, (const bf16*)x, (const bf16*)W, T, N, K, ldx, out_f32, nullptr);
     return SL_LAUNCH_CHECK();
+}
+
+// Rows per warp: enough warps to cover the SMs a few times over, otherwise fewer rows each.
+template <int TT>
+static int launch_gemv_bf16(void* y, const void* x, const void* W, int T, int N, int K, int ldx, int out_f32, cudaStream_t s) {
+    if (N <= 1024 && K >= 2048) {
+        gemv_bf16_rowblock_kernel<TT><<<dim3(N, (T + TT - 1) / TT), 256, 0, s>>>(y, (const bf16*)x, (const bf16*)W, T, N, K, ldx, out_f32);
+        return SL_LAUNCH_CHECK();
+    }
+    constexpr int RMAX = (TT >= 4) ? 2 : 4;
+    if (RMAX >= 4 && N >= 148 * 8 * 4 * 2) return launch_gemv_bf16_r<TT, RMAX>(y, x, W, T, N, K, ldx, out_f32, s);
+    if (N >= 148 * 8 * 2 * 2) return launch_gemv_bf16_r<TT, 2>(y, x, W, T, N, K, ldx, out_f32, s);
+    return launch_gemv_bf16_r<TT, 1>(y, x, W, T, N, K, ldx, out_f32, s);
 }
 
 SL_API int sl_gemv_bf16(void* y, const void* x, const void* W, int T, int N, int K, int ldx, int out_f32, cudaStream_t s) {
@@ -189,18 +234,26 @@ __global__ void __launch_bounds__(256) gemv_nvfp4_kernel(void* __restrict__ y, c
     }
 }
 
-template <int TT>
-static int launch_gemv_nvfp4(void* y, const void* x, const void* Wp, const void* S, const void* g, int T, int N, int K,
-                             int ldx, int out_f32, cudaStream_t s) {
+template <int TT, int R>
+static int launch_gemv_nvfp4_r(void* y, const void* x, const void* Wp, const void* S, const void* g, int T, int N, int K,
+                               int ldx, int out_f32, cudaStream_t s) {
     const size_t smem = (size_t)TT * K * sizeof(__half);
-    constexpr int R = (TT >= 4) ? 2 : 4;
     auto kern = gemv_nvfp4_kernel<TT, R>;
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     int blocks = (N + 8 * R - 1) / (8 * R);
-    if (blocks > 148 * 4) blocks = 148 * 4;
+    if (blocks > 148 * 8) blocks = 148 * 8;
     kern<<<dim3(blocks, (T + TT - 1) / TT), 256, smem, s>>>(y, (const bf16*)x, (const uint8_t*)Wp, (const uint8_t*)S,
                                                             (const float*)g, T, N, K, ldx, out_f32);
     return SL_LAUNCH_CHECK();
+}
+
+template <int TT>
+static int launch_gemv_nvfp4(void* y, const void* x, const void* Wp, const void* S, const void* g, int T, int N, int K,
+                             int ldx, int out_f32, cudaStream_t s) {
+    constexpr int RMAX = (TT >= 4) ? 2 : 4;
+    if (RMAX >= 4 && N >= 148 * 8 * 4 * 2) return launch_gemv_nvfp4_r<TT, RMAX>(y, x, Wp, S, g, T, N, K, ldx, out_f32, s);
+    if (N >= 148 * 8 * 2 * 2) return launch_gemv_nvfp4_r<TT, 2>(y, x, Wp, S, g, T, N, K, ldx, out_f32, s);
+    return launch_gemv_nvfp4_r<TT, 1>(y, x, Wp, S, g, T, N, K, ldx, out_f32, s);
 }
 
 SL_API int sl_gemv_nvfp4(void* y, const void* x, const void* Wp, const void* S, const void* g, int T, int N, int K, int ldx,

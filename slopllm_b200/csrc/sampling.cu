@@ -24,14 +24,19 @@ __device__ __forceinline__ uint32_t order_key_f(float f) {
 }
 
 // ---------------------------------------------------------------------------------------------
+// Arg-max over the vocabulary in two stages: grid (chunks, B) partial winners, then one warp per
+// row.  Ties go to the lower index; a row of NaN / -inf still yields a valid id (0).
+#define SL_ARGMAX_CHUNKS 64
 template <typename TL>
-__global__ void __launch_bounds__(1024) argmax_kernel(int64_t* __restrict__ out, const TL* __restrict__ logits, int V,
-                                                      int ld, int64_t id_offset, float* __restrict__ out_val) {
-    __shared__ float sv[32];
-    __shared__ int si[32];
-    const int b = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+__global__ void __launch_bounds__(256) argmax_partial_kernel(float* __restrict__ pv, int* __restrict__ pi,
+                                                             const TL* __restrict__ logits, int V, int ld) {
+    __shared__ float sv[8];
+    __shared__ int si[8];
+    const int b = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int per = (V + gridDim.x - 1) / gridDim.x;
+    const int lo = blockIdx.x * per, hi = min(V, lo + per);
     float best = -INFINITY; int bi = 0x7fffffff;
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
         const float v = (float)logits[(size_t)b * ld + i];
         if (v > best) { best = v; bi = i; }
     }
@@ -42,26 +47,43 @@ __global__ void __launch_bounds__(1024) argmax_kernel(int64_t* __restrict__ out,
     }
     if (lane == 0) { sv[warp] = best; si[warp] = bi; }
     __syncthreads();
-    if (warp == 0) {
-        best = lane < (blockDim.x >> 5) ? sv[lane] : -INFINITY;
-        bi = lane < (blockDim.x >> 5) ? si[lane] : 0x7fffffff;
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
-        }
-        if (lane == 0) {
-            out[b] = (int64_t)bi + id_offset;
-            if (out_val) out_val[b] = best;
-        }
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 8; ++w)
+            if (sv[w] > best || (sv[w] == best && si[w] < bi)) { best = sv[w]; bi = si[w]; }
+        pv[(size_t)b * gridDim.x + blockIdx.x] = best;
+        pi[(size_t)b * gridDim.x + blockIdx.x] = bi;
     }
 }
 
+__global__ void argmax_final_kernel(int64_t* __restrict__ out, float* __restrict__ out_val, const float* __restrict__ pv,
+                                    const int* __restrict__ pi, int chunks, int64_t id_offset) {
+    const int b = blockIdx.x, lane = threadIdx.x;
+    float best = -INFINITY; int bi = 0x7fffffff;
+    for (int i = lane; i < chunks; i += 32) {
+        const float v = pv[(size_t)b * chunks + i]; const int id = pi[(size_t)b * chunks + i];
+        if (v > best || (v == best && id < bi)) { best = v; bi = id; }
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    if (lane == 0) {
+        if (bi == 0x7fffffff) bi = 0;
+        out[b] = (int64_t)bi + id_offset;
+        if (out_val) out_val[b] = best;
+    }
+}
+
+// scratch_val / scratch_idx: [B, 64] floats / ints owned by the caller.
 SL_API int sl_argmax(void* out, const void* logits, int B, int V, int ld, int is_f32, long long id_offset, void* out_val,
-                     cudaStream_t s) {
+                     void* scratch_val, void* scratch_idx, cudaStream_t s) {
     if (B == 0) return 0;
-    if (is_f32) argmax_kernel<float><<<B, 1024, 0, s>>>((int64_t*)out, (const float*)logits, V, ld, id_offset, (float*)out_val);
-    else argmax_kernel<bf16><<<B, 1024, 0, s>>>((int64_t*)out, (const bf16*)logits, V, ld, id_offset, (float*)out_val);
+    dim3 grid(SL_ARGMAX_CHUNKS, B);
+    if (is_f32) argmax_partial_kernel<float><<<grid, 256, 0, s>>>((float*)scratch_val, (int*)scratch_idx, (const float*)logits, V, ld);
+    else argmax_partial_kernel<bf16><<<grid, 256, 0, s>>>((float*)scratch_val, (int*)scratch_idx, (const bf16*)logits, V, ld);
+    argmax_final_kernel<<<B, 32, 0, s>>>((int64_t*)out, (float*)out_val, (const float*)scratch_val, (const int*)scratch_idx,
+                                         SL_ARGMAX_CHUNKS, id_offset);
     return SL_LAUNCH_CHECK();
 }
 

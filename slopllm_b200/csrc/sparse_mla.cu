@@ -179,41 +179,46 @@ struct CombineParams {
     float* lse_out;                      // [T, head_count] or null
 };
 
-__global__ void mla_combine_kernel(CombineParams p) {
+__global__ void __launch_bounds__(128) mla_combine_kernel(CombineParams p) {
     const int t = blockIdx.y, hh = blockIdx.x, head = p.head_begin + hh;
     __shared__ float wsh[8 * 64];
-    __shared__ float s_lse;
+    __shared__ float scratch[33];
     const int np = p.n_buf * p.parts_per_buf;
-    if (threadIdx.x == 0) {
-        float mx = -INFINITY;
-        for (int i = 0; i < np; ++i) {
-            const int b = i / p.parts_per_buf, q = i % p.parts_per_buf;
-            mx = fmaxf(mx, p.lse_ptrs[b][((size_t)t * p.h + head) * p.parts_per_buf + q]);
-        }
-        float den = 0.f;
-        for (int i = 0; i < np; ++i) {
-            const int b = i / p.parts_per_buf, q = i % p.parts_per_buf;
-            const float l = p.lse_ptrs[b][((size_t)t * p.h + head) * p.parts_per_buf + q];
-            const float w = (l == -INFINITY) ? 0.f : __expf(l - mx);
-            wsh[i] = w;
-            den += w;
-        }
-        for (int i = 0; i < np; ++i) wsh[i] = den > 0.f ? wsh[i] / den : 0.f;
-        s_lse = den > 0.f ? mx + logf(den) : -INFINITY;
+    const size_t th = (size_t)t * p.h + head;
+    // weights: one partial per thread (np <= 512 -> up to 4 per thread)
+    float mx = -INFINITY;
+    for (int i = threadIdx.x; i < np; i += blockDim.x) {
+        const int b = i / p.parts_per_buf, q = i % p.parts_per_buf;
+        const float l = p.lse_ptrs[b][th * p.parts_per_buf + q];
+        wsh[i] = l;
+        mx = fmaxf(mx, l);
     }
-    __syncthreads();
-    for (int d = threadIdx.x; d < p.R; d += blockDim.x) {
-        float acc = 0.f;
+    mx = block_max(mx, scratch);
+    float den = 0.f;
+    for (int i = threadIdx.x; i < np; i += blockDim.x) {
+        const float l = wsh[i];
+        const float w = (l == -INFINITY) ? 0.f : __expf(l - mx);
+        wsh[i] = w;
+        den += w;
+    }
+    den = block_sum(den, scratch);
+    const float inv = den > 0.f ? 1.f / den : 0.f;
+    for (int d = threadIdx.x * 4; d < p.R; d += blockDim.x * 4) {
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
         for (int i = 0; i < np; ++i) {
             const float w = wsh[i];
             if (w != 0.f) {
                 const int b = i / p.parts_per_buf, q = i % p.parts_per_buf;
-                acc += w * p.o_ptrs[b][(((size_t)t * p.h + head) * p.parts_per_buf + q) * p.R + d];
+                const float4 v = *reinterpret_cast<const float4*>(p.o_ptrs[b] + (th * p.parts_per_buf + q) * p.R + d);
+                acc.x += w * v.x; acc.y += w * v.y; acc.z += w * v.z; acc.w += w * v.w;
             }
         }
-        p.o_out[((size_t)t * p.head_count + hh) * p.R + d] = __float2bfloat16(acc);
+        uint2 o;
+        o.x = f2_to_bf162(acc.x * inv, acc.y * inv);
+        o.y = f2_to_bf162(acc.z * inv, acc.w * inv);
+        *reinterpret_cast<uint2*>(p.o_out + ((size_t)t * p.head_count + hh) * p.R + d) = o;
     }
-    if (threadIdx.x == 0 && p.lse_out) p.lse_out[(size_t)t * p.head_count + hh] = s_lse;
+    if (threadIdx.x == 0 && p.lse_out) p.lse_out[(size_t)t * p.head_count + hh] = den > 0.f ? mx + logf(den) : -INFINITY;
 }
 
 SL_API int sl_mla_combine(const CombineParams* p, int T, cudaStream_t s) {

@@ -16,6 +16,7 @@ from . import native as N
 from . import reference as R
 
 DECODE_MAX_T = 32          # token rows handled by the weight-streaming (GEMV) kernels
+TENSOR_MIN_T = 5           # from this many rows on the streaming kernels use the tensor cores
 
 
 class CudaOps:
@@ -37,7 +38,7 @@ class CudaOps:
         T, H = ids.shape[0], table.shape[1]
         out = torch.empty(T, H, dtype=torch.bfloat16, device=table.device)
         ids = ids.to(torch.int64).contiguous()
-        N.call("sl_embed", out.data_ptr(), ids.data_ptr(), table.data_ptr(), T, H, N.stream())
+        N.call("sl_embed", out.data_ptr(), ids.data_ptr(), table.data_ptr(), T, H, table.shape[0], N.stream())
         return out
 
     def add_rmsnorm(self, x, residual, w, eps=None):
@@ -71,6 +72,19 @@ class CudaOps:
             from .gemm import gemm_large
             return gemm_large(x, w, out_f32)
         y = torch.empty(T, Nn, dtype=torch.float32 if out_f32 else torch.bfloat16, device=x.device)
+        if T >= TENSOR_MIN_T:
+            # tensor-core weight streaming: tcgen05 swap-AB (bf16) / mma.sync with in-register FP4 expansion
+            if w.is_nvfp4 and K % 128 == 0 and x.stride(0) % 8 == 0:
+                xp = torch.empty(((T + 7) // 8) * 8 * K, dtype=torch.float16, device=x.device)
+                N.call("sl_linear_nvfp4_mma", y.data_ptr(), x.data_ptr(), xp.data_ptr(), w.weight.data_ptr(),
+                       w.scale.data_ptr(), w.scale2.data_ptr(), T, Nn, K, x.stride(0), int(out_f32), N.stream())
+                return y
+            if not w.is_nvfp4 and x.stride(0) % 8 == 0 and K % 8 == 0:
+                from . import tcgen05
+                N.call("sl_linear_smallT_bf16_tcgen05", x.data_ptr(), w.weight.data_ptr(), y.data_ptr(), T, Nn, K,
+                       x.stride(0), w.weight.stride(0), y.stride(0), int(out_f32),
+                       tcgen05.error_flag(x.device).data_ptr(), N.stream())
+                return y
         if w.is_nvfp4:
             N.call("sl_gemv_nvfp4", y.data_ptr(), x.data_ptr(), w.weight.data_ptr(), w.scale.data_ptr(),
                    w.scale2.data_ptr(), T, Nn, K, x.stride(0), int(out_f32), N.stream())
@@ -292,8 +306,10 @@ class CudaOps:
         B, V = logits.shape
         out = torch.empty(B, dtype=torch.int64, device=logits.device)
         val = torch.empty(B, dtype=torch.float32, device=logits.device) if want_val else None
+        sv = torch.empty(B, 64, dtype=torch.float32, device=logits.device)
+        si = torch.empty(B, 64, dtype=torch.int32, device=logits.device)
         N.call("sl_argmax", out.data_ptr(), logits.data_ptr(), B, V, logits.stride(0), int(logits.dtype == torch.float32),
-               id_offset, N.ptr(val), N.stream())
+               id_offset, N.ptr(val), sv.data_ptr(), si.data_ptr(), N.stream())
         return (out, val) if want_val else out
 
 

@@ -124,7 +124,7 @@ class SpecRejectParams(C.Structure):
 # ---- function signatures ----------------------------------------------------------------------------------
 
 _SIGS = {
-    "sl_embed": [vp, vp, vp, i32, i32, vp],
+    "sl_embed": [vp, vp, vp, i32, i32, i32, vp],
     "sl_add_rmsnorm": [vp, vp, vp, vp, vp, i32, i32, f32, i32, vp],
     "sl_attn_pre": [C.POINTER(AttnPreParams), i32, vp],
     "sl_q_post": [C.POINTER(QPostParams), i32, vp],
@@ -141,9 +141,11 @@ _SIGS = {
     "sl_topk_select": [C.POINTER(TopkSelectParams), i32, vp],
     "sl_sparse_mla_split": [C.POINTER(SparseMlaParams), i32, vp],
     "sl_mla_combine": [C.POINTER(CombineParams), i32, vp],
-    "sl_argmax": [vp, vp, i32, i32, i32, i32, i64, vp, vp],
+    "sl_argmax": [vp, vp, i32, i32, i32, i32, i64, vp, vp, vp, vp],
     "sl_sample": [C.POINTER(SampleParams), i32, vp],
     "sl_spec_reject": [C.POINTER(SpecRejectParams), i32, vp],
+    "sl_linear_nvfp4_mma": [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp],
+    "sl_linear_smallT_bf16_tcgen05": [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp, vp],
     "sl_gemm_bf16_tcgen05": [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp, i32, vp],
 }
 

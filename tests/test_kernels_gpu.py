@@ -41,8 +41,8 @@ def mini_cfg(**kw):
     return GlmMoeDsaConfig(**base)
 
 
-@pytest.mark.parametrize("T", [1, 2, 3, 8, 19])
-@pytest.mark.parametrize("N,K", [(256, 512), (2784, 6144), (1000, 2048)])
+@pytest.mark.parametrize("T", [1, 2, 3, 5, 8, 19, 32])
+@pytest.mark.parametrize("N,K", [(256, 512), (2784, 6144), (1000, 2048), (256, 6144)])
 def test_gemv_bf16(T, N, K):
     g = torch.Generator(device=DEV).manual_seed(T * 7 + N)
     x = torch.randn(T, K, device=DEV, generator=g).to(torch.bfloat16)
@@ -53,8 +53,8 @@ def test_gemv_bf16(T, N, K):
         close(y, x.float() @ w.float().t(), what=f"gemv_bf16 T={T} f32={f32}")
 
 
-@pytest.mark.parametrize("T", [1, 2, 4, 7, 16])
-@pytest.mark.parametrize("N,K", [(512, 256), (6144, 2048), (4096, 6144)])
+@pytest.mark.parametrize("T", [1, 2, 4, 7, 16, 23, 32])
+@pytest.mark.parametrize("N,K", [(512, 256), (6144, 2048), (4096, 6144), (1000, 128)])
 def test_gemv_nvfp4(T, N, K):
     g = torch.Generator(device=DEV).manual_seed(T + K)
     x = torch.randn(T, K, device=DEV, generator=g).to(torch.bfloat16)
@@ -63,6 +63,10 @@ def test_gemv_nvfp4(T, N, K):
     ops = cuda_ops(GlmMoeDsaConfig.tiny())
     y = ops.linear(x, w, out_f32=True)
     close(y, R.linear(x, w), what=f"gemv_nvfp4 T={T}")
+    close(ops.linear(x, w), R.linear(x, w), what=f"gemv_nvfp4 bf16 out T={T}")
+    from slopllm_b200.ops import tcgen05
+    torch.cuda.synchronize()
+    tcgen05.check_errors(DEV)
 
 
 def test_nvfp4_roundtrip_quantize():
