@@ -27,37 +27,65 @@ SL_API int sl_embed(void* out, const void* ids, const void* table, int T, int H,
 
 // ---------------------------------------------------------------------------------------------
 // residual' = residual + x (fp32) ; out = rmsnorm(residual') * w (bf16).
-// x is bf16 or fp32 (`x_f32`); residual_in may be null (first layer).  H <= 16384.
+// x is bf16 or fp32 (`x_f32`); residual_in may be null (first layer).  H % 4 == 0, H <= 16384.
+// One block per token; a thread keeps its (up to 4) float4 chunks in registers between the
+// sum-of-squares pass and the scaling pass.
 template <bool XF32>
-__global__ void add_rmsnorm_kernel(bf16* __restrict__ out, float* __restrict__ res_out, const void* __restrict__ xin,
-                                   const float* __restrict__ res_in, const bf16* __restrict__ w, int H, float eps) {
-    extern __shared__ float row[];
+__global__ void __launch_bounds__(1024) add_rmsnorm_kernel(bf16* __restrict__ out, float* __restrict__ res_out,
+                                                           const void* __restrict__ xin, const float* __restrict__ res_in,
+                                                           const bf16* __restrict__ w, int H, float eps) {
     __shared__ float scratch[33];
-    const int t = blockIdx.x;
+    const int t = blockIdx.x, nt = blockDim.x, n4 = H / 4;
+    float4 v[4];
     float ss = 0.f;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        float v = XF32 ? ((const float*)xin)[(size_t)t * H + i] : __bfloat162float(((const bf16*)xin)[(size_t)t * H + i]);
-        if (res_in != nullptr) v += res_in[(size_t)t * H + i];
-        row[i] = v;
-        ss += v * v;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        const int i = threadIdx.x + q * nt;
+        if (i < n4) {
+            float4 a;
+            if (XF32) {
+                a = reinterpret_cast<const float4*>((const float*)xin + (size_t)t * H)[i];
+            } else {
+                const uint2 u = reinterpret_cast<const uint2*>((const bf16*)xin + (size_t)t * H)[i];
+                const float2 lo = bf162_to_f2(u.x), hi = bf162_to_f2(u.y);
+                a = make_float4(lo.x, lo.y, hi.x, hi.y);
+            }
+            if (res_in != nullptr) {
+                const float4 r = reinterpret_cast<const float4*>(res_in + (size_t)t * H)[i];
+                a.x += r.x; a.y += r.y; a.z += r.z; a.w += r.w;
+            }
+            v[q] = a;
+            ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+        }
     }
     ss = block_sum(ss, scratch);
     const float inv = rsqrtf(ss / (float)H + eps);
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        const float v = row[i];
-        if (res_out != nullptr) res_out[(size_t)t * H + i] = v;
-        out[(size_t)t * H + i] = __float2bfloat16(v * inv * __bfloat162float(w[i]));
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        const int i = threadIdx.x + q * nt;
+        if (i < n4) {
+            if (res_out != nullptr) reinterpret_cast<float4*>(res_out + (size_t)t * H)[i] = v[q];
+            const uint2 wu = reinterpret_cast<const uint2*>(w)[i];
+            const float2 w0 = bf162_to_f2(wu.x), w1 = bf162_to_f2(wu.y);
+            uint2 o;
+            o.x = f2_to_bf162(v[q].x * inv * w0.x, v[q].y * inv * w0.y);
+            o.y = f2_to_bf162(v[q].z * inv * w1.x, v[q].w * inv * w1.y);
+            reinterpret_cast<uint2*>(out + (size_t)t * H)[i] = o;
+        }
     }
 }
 
 SL_API int sl_add_rmsnorm(void* out, void* res_out, const void* x, const void* res_in, const void* w, int T, int H,
                           float eps, int x_f32, cudaStream_t s) {
     if (T == 0) return 0;
-    const size_t smem = (size_t)H * sizeof(float);
+    if (H % 4 != 0 || H > 16384) return -1;
+    int threads = ((H / 4 + 3) / 4 + 31) / 32 * 32;      // 4 chunks per thread when possible
+    if (threads < 128) threads = 128;
+    if (threads > 1024) threads = 1024;
     if (x_f32)
-        add_rmsnorm_kernel<true><<<T, 512, smem, s>>>((bf16*)out, (float*)res_out, x, (const float*)res_in, (const bf16*)w, H, eps);
+        add_rmsnorm_kernel<true><<<T, threads, 0, s>>>((bf16*)out, (float*)res_out, x, (const float*)res_in, (const bf16*)w, H, eps);
     else
-        add_rmsnorm_kernel<false><<<T, 512, smem, s>>>((bf16*)out, (float*)res_out, x, (const float*)res_in, (const bf16*)w, H, eps);
+        add_rmsnorm_kernel<false><<<T, threads, 0, s>>>((bf16*)out, (float*)res_out, x, (const float*)res_in, (const bf16*)w, H, eps);
     return SL_LAUNCH_CHECK();
 }
 
@@ -277,50 +305,58 @@ SL_API int sl_q_post(const QPostParams* p, int T, cudaStream_t s) {
 // ---------------------------------------------------------------------------------------------
 // Batched vector x matrix: y[t,h,n] = sum_k x[t,h,k] * M[h,k,n]   (absorb: K=Dn,N=R; v_expand: K=R,N=Dv)
 // x element (t,h,k) at x[t*xs_t + h*xs_h + k]; y bf16 [T, Hh, N] contiguous.
-// grid (Hh, N/128, ceil(T/TT)); block 256 = 8 warps.  A warp owns every 8th k row and reads
-// 256 contiguous bytes of it (4 columns per lane); the 8 partial sums meet in shared memory.
+// grid (Hh, N/256, ceil(T/TT)); block 256 = 8 warps.  A warp owns every 8th k row and reads
+// 512 contiguous bytes of it (8 columns per lane, 16-byte loads, four rows in flight); the 8
+// partial sums meet in shared memory.
 template <int TT>
 __global__ void __launch_bounds__(256) bmv_kernel(bf16* __restrict__ y, const bf16* __restrict__ x, const bf16* __restrict__ M,
                                                   int T, int Hh, int K, int N, int xs_t, int xs_h) {
-    extern __shared__ float xs[];            // [TT][K]
-    __shared__ float red[8][TT][128];
-    const int h = blockIdx.x, n0 = blockIdx.y * 128, t0 = blockIdx.z * TT;
+    extern __shared__ float xs[];            // [TT][K], then red[8][TT][256]
+    float* red = xs + TT * K;
+    const int h = blockIdx.x, n0 = blockIdx.y * 256, t0 = blockIdx.z * TT;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     for (int i = tid; i < TT * K; i += blockDim.x) {
         const int tt = i / K, k = i % K;
         xs[i] = (t0 + tt < T) ? __bfloat162float(x[(size_t)(t0 + tt) * xs_t + (size_t)h * xs_h + k]) : 0.f;
     }
     __syncthreads();
-    float acc[TT][4];
+    float acc[TT][8];
 #pragma unroll
     for (int tt = 0; tt < TT; ++tt)
 #pragma unroll
-        for (int c = 0; c < 4; ++c) acc[tt][c] = 0.f;
-    const int n = n0 + lane * 4;
+        for (int c = 0; c < 8; ++c) acc[tt][c] = 0.f;
+    const int n = n0 + lane * 8;
     if (n < N) {
         const bf16* Mp = M + (size_t)h * K * N + n;
-#pragma unroll 4
-        for (int k = warp; k < K; k += 8) {
-            const uint2 u = ldg_nc_8(Mp + (size_t)k * N);
-            const float2 w0 = bf162_to_f2(u.x), w1 = bf162_to_f2(u.y);
+        for (int k = warp; k < K; k += 32) {
+            uint4 u[4];
 #pragma unroll
-            for (int tt = 0; tt < TT; ++tt) {
-                const float xv = xs[tt * K + k];
-                acc[tt][0] += xv * w0.x; acc[tt][1] += xv * w0.y; acc[tt][2] += xv * w1.x; acc[tt][3] += xv * w1.y;
+            for (int q = 0; q < 4; ++q) u[q] = (k + q * 8 < K) ? ldg_nc_16(Mp + (size_t)(k + q * 8) * N) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                if (k + q * 8 < K) {
+                    const float2 w0 = bf162_to_f2(u[q].x), w1 = bf162_to_f2(u[q].y), w2 = bf162_to_f2(u[q].z), w3 = bf162_to_f2(u[q].w);
+#pragma unroll
+                    for (int tt = 0; tt < TT; ++tt) {
+                        const float xv = xs[tt * K + k + q * 8];
+                        acc[tt][0] += xv * w0.x; acc[tt][1] += xv * w0.y; acc[tt][2] += xv * w1.x; acc[tt][3] += xv * w1.y;
+                        acc[tt][4] += xv * w2.x; acc[tt][5] += xv * w2.y; acc[tt][6] += xv * w3.x; acc[tt][7] += xv * w3.y;
+                    }
+                }
             }
         }
     }
 #pragma unroll
     for (int tt = 0; tt < TT; ++tt)
 #pragma unroll
-        for (int c = 0; c < 4; ++c) red[warp][tt][lane * 4 + c] = acc[tt][c];
+        for (int c = 0; c < 8; ++c) red[(warp * TT + tt) * 256 + lane * 8 + c] = acc[tt][c];
     __syncthreads();
-    for (int i = tid; i < TT * 128; i += blockDim.x) {
-        const int tt = i / 128, c = i % 128;
+    for (int i = tid; i < TT * 256; i += blockDim.x) {
+        const int tt = i / 256, c = i % 256;
         if (t0 + tt < T && n0 + c < N) {
             float v = 0.f;
 #pragma unroll
-            for (int w = 0; w < 8; ++w) v += red[w][tt][c];
+            for (int w = 0; w < 8; ++w) v += red[(w * TT + tt) * 256 + c];
             y[((size_t)(t0 + tt) * Hh + h) * N + n0 + c] = __float2bfloat16(v);
         }
     }
@@ -328,14 +364,17 @@ __global__ void __launch_bounds__(256) bmv_kernel(bf16* __restrict__ y, const bf
 
 template <int TT>
 static int launch_bmv(void* y, const void* x, const void* M, int T, int Hh, int K, int N, int xs_t, int xs_h, cudaStream_t s) {
-    dim3 grid(Hh, (N + 127) / 128, (T + TT - 1) / TT);
-    bmv_kernel<TT><<<grid, 256, (size_t)TT * K * sizeof(float), s>>>((bf16*)y, (const bf16*)x, (const bf16*)M, T, Hh, K, N, xs_t, xs_h);
+    dim3 grid(Hh, (N + 255) / 256, (T + TT - 1) / TT);
+    const size_t smem = (size_t)(TT * K + 8 * TT * 256) * sizeof(float);
+    auto kern = bmv_kernel<TT>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    kern<<<grid, 256, smem, s>>>((bf16*)y, (const bf16*)x, (const bf16*)M, T, Hh, K, N, xs_t, xs_h);
     return SL_LAUNCH_CHECK();
 }
 
 SL_API int sl_bmv(void* y, const void* x, const void* M, int T, int Hh, int K, int N, int xs_t, int xs_h, cudaStream_t s) {
     if (T == 0) return 0;
-    if (N % 4 != 0) return -1;
+    if (N % 8 != 0) return -1;
     if (T == 1) return launch_bmv<1>(y, x, M, T, Hh, K, N, xs_t, xs_h, s);
     if (T == 2) return launch_bmv<2>(y, x, M, T, Hh, K, N, xs_t, xs_h, s);
     return launch_bmv<4>(y, x, M, T, Hh, K, N, xs_t, xs_h, s);
@@ -364,18 +403,19 @@ SL_API int sl_silu_mul(void* out, const void* gu, int T, int I, cudaStream_t s) 
 // MoE routing: one warp per token.  scores = sigmoid(logits); choose by scores + bias inside
 // the `topk_group` best groups (group rank = sum of its two best biased scores); weights =
 // unbiased scores of the chosen, normalised, scaled.  Ties prefer the lower expert id.
-// E <= 512, n_group <= 32, top_k <= 32.
+// Lane l holds experts l*PER .. l*PER+PER-1 (contiguous, so a group of E/n_group experts is a
+// run of whole lanes when E/n_group >= PER).  E = 32*PER <= 512, n_group <= 32, top_k <= 32.
+template <int PER>
 __global__ void route_topk_kernel(int* __restrict__ ids, float* __restrict__ wts, const float* __restrict__ logits,
                                   const float* __restrict__ bias, int T, int E, int top_k, int n_group, int topk_group,
                                   int norm, float scale) {
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (warp >= T) return;
-    constexpr int MAXPL = 16;                 // experts per lane
-    float sc[MAXPL], ch[MAXPL];
-    const int per = (E + 31) / 32;
-    for (int i = 0; i < MAXPL; ++i) {
-        const int e = lane + i * 32;           // strided so that lane order == id order within a step
-        if (i < per && e < E) {
+    float sc[PER], ch[PER];
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+        const int e = lane * PER + i;
+        if (e < E) {
             const float s = 1.f / (1.f + expf(-logits[(size_t)warp * E + e]));
             sc[i] = s;
             ch[i] = s + (bias ? bias[e] : 0.f);
@@ -386,63 +426,57 @@ __global__ void route_topk_kernel(int* __restrict__ ids, float* __restrict__ wts
     }
     if (n_group > 1) {
         const int gsz = E / n_group;
-        // group score = top-2 sum; lane g (< n_group) ends up holding group g's score
-        float gscore = -INFINITY;
-        for (int g = 0; g < n_group; ++g) {
-            float m1 = -INFINITY, m2 = -INFINITY;
-            for (int i = 0; i < per; ++i) {
-                const int e = lane + i * 32;
-                if (e < E && e / gsz == g) {
-                    const float v = ch[i];
-                    if (v > m1) { m2 = m1; m1 = v; } else if (v > m2) m2 = v;
-                }
-            }
-            // merge (m1, m2) pairs across lanes
-            for (int o = 16; o > 0; o >>= 1) {
-                const float o1 = __shfl_xor_sync(0xffffffffu, m1, o), o2 = __shfl_xor_sync(0xffffffffu, m2, o);
-                const float hi = fmaxf(m1, o1), lo = fmaxf(fminf(m1, o1), fmaxf(m2, o2));
-                m1 = hi; m2 = lo;
-            }
-            const float gs = gsz >= 2 ? m1 + m2 : m1;
-            if (lane == g) gscore = gs;
+        // top-2 of this lane's experts, merged across the lanes of its group
+        float m1 = -INFINITY, m2 = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+            const float v = ch[i];
+            if (v > m1) { m2 = m1; m1 = v; } else if (v > m2) m2 = v;
         }
-        // select topk_group groups: repeated arg-max over lanes, ties to the lower group id
-        unsigned keep = 0;
-        float cur = gscore;
-        for (int r = 0; r < topk_group; ++r) {
-            float best = cur; int bi = lane;
-            for (int o = 16; o > 0; o >>= 1) {
-                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-                const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-                if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
-            }
-            keep |= 1u << bi;
-            if (lane == bi) cur = -INFINITY;
+        const int lanes_per_group = gsz / PER;            // >= 1 (checked by the launcher)
+        for (int o = 1; o < lanes_per_group; o <<= 1) {
+            const float o1 = __shfl_xor_sync(0xffffffffu, m1, o), o2 = __shfl_xor_sync(0xffffffffu, m2, o);
+            const float hi = fmaxf(m1, o1), lo = fmaxf(fminf(m1, o1), fmaxf(m2, o2));
+            m1 = hi; m2 = lo;
         }
-        for (int i = 0; i < per; ++i) {
-            const int e = lane + i * 32;
-            if (e < E && !((keep >> (e / gsz)) & 1u)) ch[i] = -INFINITY;
+        const int my_group = (lane * PER) / gsz;
+        const float gs = gsz >= 2 ? m1 + m2 : m1;
+        // rank of my group: number of groups that beat it (higher score, or equal score and lower id)
+        int beaten_by = 0;
+        for (int g2 = 0; g2 < n_group; ++g2) {
+            const float og = __shfl_sync(0xffffffffu, gs, g2 * lanes_per_group);
+            beaten_by += (og > gs) || (og == gs && g2 < my_group);
+        }
+        if (beaten_by >= topk_group || lane * PER >= E) {
+#pragma unroll
+            for (int i = 0; i < PER; ++i) ch[i] = -INFINITY;
         }
     }
     float wsum = 0.f, myw = 0.f;
     int myid = 0;
     for (int r = 0; r < top_k; ++r) {
-        float best = -INFINITY; int be = E, bslot = 0;
-        for (int i = 0; i < per; ++i) {
-            const int e = lane + i * 32;
-            if (e < E && (ch[i] > best)) { best = ch[i]; be = e; bslot = i; }
-        }
+        float best = -INFINITY; int bslot = 0;
+#pragma unroll
+        for (int i = 0; i < PER; ++i)
+            if (ch[i] > best) { best = ch[i]; bslot = i; }
+        const int be = best > -INFINITY ? lane * PER + bslot : E;
         float gb = best; int ge = be;
+#pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
             const float ob = __shfl_xor_sync(0xffffffffu, gb, o);
             const int oe = __shfl_xor_sync(0xffffffffu, ge, o);
             if (ob > gb || (ob == gb && oe < ge)) { gb = ob; ge = oe; }
         }
         float s = 0.f;
-        if (ge == be && be < E) { s = sc[bslot]; ch[bslot] = -INFINITY; }
-        s = warp_sum(s);                       // only the owner lane contributed
+        if (ge == be && be < E) {
+#pragma unroll
+            for (int i = 0; i < PER; ++i)
+                if (i == bslot) { s = sc[i]; ch[i] = -INFINITY; }
+        }
+        // hand the winner's unbiased score to every lane
+        s = __shfl_sync(0xffffffffu, s, ge < E ? ge / PER : 0);
         wsum += s;
-        if (lane == r) { myw = s; myid = ge; }
+        if (lane == r) { myw = s; myid = ge < E ? ge : 0; }
     }
     if (lane < top_k) {
         float w = myw;
@@ -455,10 +489,28 @@ __global__ void route_topk_kernel(int* __restrict__ ids, float* __restrict__ wts
 SL_API int sl_route_topk(void* ids, void* wts, const void* logits, const void* bias, int T, int E, int top_k, int n_group,
                          int topk_group, int norm, float scale, cudaStream_t s) {
     if (T == 0) return 0;
-    if (E > 512 || top_k > 32 || n_group > 32) return -1;
+    if (E > 512 || top_k > 32 || n_group > 32 || n_group < 1 || E % n_group != 0) return -1;
+    const int per = (E + 31) / 32;
+    int PER = 1;
+    while (PER < per) PER <<= 1;
+    if (n_group > 1) {
+        const int gsz = E / n_group;
+        if (gsz % PER != 0) return -1;                       // a group must be a run of whole lanes
+        const int lpg = gsz / PER;
+        if (lpg & (lpg - 1)) return -1;
+    }
     const int wpb = 4;
-    route_topk_kernel<<<(T + wpb - 1) / wpb, wpb * 32, 0, s>>>((int*)ids, (float*)wts, (const float*)logits, (const float*)bias,
-                                                              T, E, top_k, n_group, topk_group, norm, scale);
+    dim3 grid((T + wpb - 1) / wpb), block(wpb * 32);
+#define SL_ROUTE(P) route_topk_kernel<P><<<grid, block, 0, s>>>((int*)ids, (float*)wts, (const float*)logits, (const float*)bias, \
+                                                                T, E, top_k, n_group, topk_group, norm, scale)
+    switch (PER) {
+        case 1: SL_ROUTE(1); break;
+        case 2: SL_ROUTE(2); break;
+        case 4: SL_ROUTE(4); break;
+        case 8: SL_ROUTE(8); break;
+        default: SL_ROUTE(16); break;
+    }
+#undef SL_ROUTE
     return SL_LAUNCH_CHECK();
 }
 

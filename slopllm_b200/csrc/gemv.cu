@@ -32,11 +32,16 @@ __global__ void __launch_bounds__(256) gemv_bf16_kernel(void* __restrict__ y, co
         for (int r = 0; r < R; ++r)
 #pragma unroll
             for (int tt = 0; tt < TT; ++tt) acc[r][tt] = 0.f;
-        for (int k = lane * 8; k < K; k += 256) {
-            uint4 w[R];
+        uint4 w[R], wn[R];
+        int k = lane * 8;
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+            w[r] = (k < K && n0 + r < N) ? ldg_nc_16(W + (size_t)(n0 + r) * K + k) : make_uint4(0, 0, 0, 0);
+        for (; k < K; k += 256) {
+            const int kn = k + 256;
 #pragma unroll
             for (int r = 0; r < R; ++r)
-                w[r] = (n0 + r < N) ? ldg_nc_16(W + (size_t)(n0 + r) * K + k) : make_uint4(0, 0, 0, 0);
+                wn[r] = (kn < K && n0 + r < N) ? ldg_nc_16(W + (size_t)(n0 + r) * K + kn) : make_uint4(0, 0, 0, 0);
 #pragma unroll
             for (int tt = 0; tt < TT; ++tt) {
                 const uint4 xv = *reinterpret_cast<const uint4*>(xs + tt * K + k);
@@ -48,6 +53,8 @@ __global__ void __launch_bounds__(256) gemv_bf16_kernel(void* __restrict__ y, co
                                   x3.x * w3.x + x3.y * w3.y;
                 }
             }
+#pragma unroll
+            for (int r = 0; r < R; ++r) w[r] = wn[r];
         }
 #pragma unroll
         for (int r = 0; r < R; ++r)
@@ -140,17 +147,26 @@ template <int TT, int R>
 __device__ __forceinline__ void nvfp4_rows_dot(float (&acc)[R][TT], const uint8_t* __restrict__ Wp, const uint8_t* __restrict__ S,
                                                size_t w_stride, size_t s_stride, int rows_valid, int K,
                                                const __half* __restrict__ xs, int lane) {
-    for (int k = lane * 32; k < K; k += 1024) {
-        uint4 w[R];
-        uint16_t sc[R];
+    // software pipeline: the loads of step i+1 are in flight while step i is expanded and multiplied
+    uint4 w[R], wn[R];
+    uint16_t sc[R], scn[R];
+    int k = lane * 32;
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        w[r] = make_uint4(0, 0, 0, 0); sc[r] = 0;
+        if (k < K && r < rows_valid) {
+            w[r] = ldg_nc_16(Wp + (size_t)r * w_stride + (k >> 1));
+            sc[r] = *reinterpret_cast<const uint16_t*>(S + (size_t)r * s_stride + (k >> 4));
+        }
+    }
+    for (; k < K; k += 1024) {
+        const int kn = k + 1024;
 #pragma unroll
         for (int r = 0; r < R; ++r) {
-            if (r < rows_valid) {
-                w[r] = ldg_nc_16(Wp + (size_t)r * w_stride + (k >> 1));
-                sc[r] = *reinterpret_cast<const uint16_t*>(S + (size_t)r * s_stride + (k >> 4));
-            } else {
-                w[r] = make_uint4(0, 0, 0, 0);
-                sc[r] = 0;
+            wn[r] = make_uint4(0, 0, 0, 0); scn[r] = 0;
+            if (kn < K && r < rows_valid) {
+                wn[r] = ldg_nc_16(Wp + (size_t)r * w_stride + (kn >> 1));
+                scn[r] = *reinterpret_cast<const uint16_t*>(S + (size_t)r * s_stride + (kn >> 4));
             }
         }
 #pragma unroll
@@ -169,22 +185,26 @@ __device__ __forceinline__ void nvfp4_rows_dot(float (&acc)[R][TT], const uint8_
             for (int r = 0; r < R; ++r) {
                 const uint32_t words[4] = {w[r].x, w[r].y, w[r].z, w[r].w};
                 const float2 s2 = e4m3x2_to_float2(sc[r]);
-                // 16 values per scale block: words 0,1 -> scale .x ; words 2,3 -> scale .y
-                float part[2] = {0.f, 0.f};
+                // 16 values per scale block (words 0,1 -> scale .x ; words 2,3 -> scale .y): the 8
+                // products of a block are summed as half2 pairs, then once in fp32 with the scale
+                __half2 hb[2];
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
                     __half2 wv[4];
                     e2m1x8_to_half2x4(words[q], wv);
-                    __half2 a = __hmul2(wv[0], xv[q * 4 + 0]);
+                    __half2 a = (q & 1) ? hb[q >> 1] : __hmul2(wv[0], xv[q * 4 + 0]);
+                    if (q & 1) a = __hfma2(wv[0], xv[q * 4 + 0], a);
                     a = __hfma2(wv[1], xv[q * 4 + 1], a);
-                    __half2 b = __hmul2(wv[2], xv[q * 4 + 2]);
-                    b = __hfma2(wv[3], xv[q * 4 + 3], b);
-                    const float2 fa = __half22float2(a), fb = __half22float2(b);
-                    part[q >> 1] += fa.x + fa.y + fb.x + fb.y;
+                    a = __hfma2(wv[2], xv[q * 4 + 2], a);
+                    a = __hfma2(wv[3], xv[q * 4 + 3], a);
+                    hb[q >> 1] = a;
                 }
-                acc[r][tt] += part[0] * s2.x + part[1] * s2.y;
+                const float2 f0 = __half22float2(hb[0]), f1 = __half22float2(hb[1]);
+                acc[r][tt] += (f0.x + f0.y) * s2.x + (f1.x + f1.y) * s2.y;
             }
         }
+#pragma unroll
+        for (int r = 0; r < R; ++r) { w[r] = wn[r]; sc[r] = scn[r]; }
     }
 }
 
@@ -348,8 +368,11 @@ struct MoeDownParams {
 };
 
 __global__ void __launch_bounds__(256) moe_down_kernel(MoeDownParams p) {
+    // grid (H / 32, T).  The block owns 32 output rows of one token; warp w streams the rows of
+    // routes w, w+8, ... (independent weight streams), the partial sums meet in shared memory.
     extern __shared__ __align__(16) unsigned char smraw[];
     __half* xs = reinterpret_cast<__half*>(smraw);                 // [routes_of_t][I]
+    __shared__ float red[8][32];
     const int t = blockIdx.y;
     const int nr = p.top_k + (p.sw2 ? 1 : 0);
     for (int i = threadIdx.x; i < nr * (p.I / 2); i += blockDim.x) {
@@ -359,42 +382,50 @@ __global__ void __launch_bounds__(256) moe_down_kernel(MoeDownParams p) {
         reinterpret_cast<__half2*>(xs)[i] = __floats2half2_rn(f.x, f.y);
     }
     __syncthreads();
-    const int lane = threadIdx.x & 31;
-    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = (gridDim.x * blockDim.x) >> 5;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int n0 = blockIdx.x * 32;
     constexpr int R = 4;
-    for (int n0 = warp * R; n0 < p.H; n0 += nwarps * R) {
-        float tot[R];
+    float tot[8];                                   // rows n0 + pass*4 + r live in lane (pass*4 + r)
 #pragma unroll
-        for (int r = 0; r < R; ++r) tot[r] = 0.f;
-        const int rv = min(R, p.H - n0);
-        for (int j = 0; j < nr; ++j) {
-            const uint8_t *W, *S; float wj;
-            if (j < p.top_k) {
-                const int e = p.ids[(size_t)t * p.top_k + j] - p.expert_offset;
-                if (e < 0 || e >= p.num_local) continue;
-                W = p.w2 + (size_t)e * p.H * (p.I / 2);
-                S = p.s2 + (size_t)e * p.H * (p.I / 16);
-                wj = p.wts[(size_t)t * p.top_k + j] * p.g2[e];
-            } else {
-                W = p.sw2; S = p.ss2; wj = p.sg2[0];
-            }
+    for (int i = 0; i < 8; ++i) tot[i] = 0.f;
+    float mine = 0.f;                               // lane l keeps the total of row n0 + l
+    for (int j = warp; j < nr; j += 8) {
+        const uint8_t *W, *S; float wj;
+        if (j < p.top_k) {
+            const int e = p.ids[(size_t)t * p.top_k + j] - p.expert_offset;
+            if (e < 0 || e >= p.num_local) continue;
+            W = p.w2 + (size_t)e * p.H * (p.I / 2);
+            S = p.s2 + (size_t)e * p.H * (p.I / 16);
+            wj = p.wts[(size_t)t * p.top_k + j] * p.g2[e];
+        } else {
+            W = p.sw2; S = p.ss2; wj = p.sg2[0];
+        }
+#pragma unroll
+        for (int pass = 0; pass < 8; ++pass) {
+            const int r0 = n0 + pass * R;
+            if (r0 >= p.H) break;
             float acc[R][1];
 #pragma unroll
             for (int r = 0; r < R; ++r) acc[r][0] = 0.f;
-            nvfp4_rows_dot<1, R>(acc, W + (size_t)n0 * (p.I / 2), S + (size_t)n0 * (p.I / 16), p.I / 2, p.I / 16, rv, p.I,
-                                 xs + (size_t)j * p.I, lane);
+            nvfp4_rows_dot<1, R>(acc, W + (size_t)r0 * (p.I / 2), S + (size_t)r0 * (p.I / 16), p.I / 2, p.I / 16,
+                                 min(R, p.H - r0), p.I, xs + (size_t)j * p.I, lane);
 #pragma unroll
-            for (int r = 0; r < R; ++r) tot[r] += acc[r][0] * wj;
-        }
-#pragma unroll
-        for (int r = 0; r < R; ++r) {
-            const float v = warp_sum(tot[r]);
-            if (lane == 0 && r < rv) {
-                const size_t o = (size_t)t * p.H + n0 + r;
-                if (p.out_f32) ((float*)p.out)[o] = p.accumulate ? ((float*)p.out)[o] + v : v;
-                else ((bf16*)p.out)[o] = __float2bfloat16(v);
+            for (int r = 0; r < R; ++r) {
+                const float v = warp_sum(acc[r][0]) * wj;
+                if (lane == pass * R + r) mine += v;
             }
         }
+    }
+    (void)tot;
+    red[warp][lane] = mine;
+    __syncthreads();
+    if (warp == 0 && n0 + lane < p.H) {
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) v += red[w][lane];
+        const size_t o = (size_t)t * p.H + n0 + lane;
+        if (p.out_f32) ((float*)p.out)[o] = p.accumulate ? ((float*)p.out)[o] + v : v;
+        else ((bf16*)p.out)[o] = __float2bfloat16(v);
     }
 }
 
@@ -405,8 +436,7 @@ SL_API int sl_moe_down(const MoeDownParams* p, cudaStream_t s) {
     const size_t smem = (size_t)nr * p->I * sizeof(__half);
     if (smem > 200 * 1024) return -2;
     if (smem > 48 * 1024) cudaFuncSetAttribute(moe_down_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    int bx = (p->H + 31) / 32;                // 8 warps x 4 rows
-    if (bx > 148 * 2) bx = 148 * 2;
+    const int bx = (p->H + 31) / 32;          // 32 rows per block
     moe_down_kernel<<<dim3(bx, p->T), 256, smem, s>>>(*p);
     return SL_LAUNCH_CHECK();
 }

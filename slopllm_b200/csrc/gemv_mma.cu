@@ -1,13 +1,14 @@
-// NVFP4 weights x a few activation rows (5..32 tokens: batched decode, MTP verification):
+// NVFP4 weights x a few activation rows (2..32 tokens: batched decode, MTP verification):
 // the packed weights are streamed from HBM once, expanded E2M1 -> f16 (x UE4M3 block scale) in
 // registers and fed to the tensor cores as the 16-row operand of `mma.sync.m16n8k16`; the
-// tokens are the 8-wide operand, read from shared memory.  W4A16: activations stay f16.
+// tokens are the 8-wide operand.  W4A16: activations stay f16.
 //
-// Work split: a block owns 16 output features; its 8 warps take every 8th group of 128
-// reduction indices, so that one 16-byte load per lane covers a row's 32 consecutive codes,
-// and meet in shared memory at the end.  The reduction index is consumed in a permuted order
-// (a lane's 32 codes feed 8 MMAs, 4 codes each); the same permutation is applied to the
-// activations when they are staged, so every shared-memory read is a conflict-free 16-byte load.
+// Work split: a warp owns 16 (or 32) output features and every ksplit-th group of 128 reduction
+// indices, so that one 16-byte load per lane covers a row's 32 consecutive codes; the warps of
+// a block that share rows meet in shared memory at the end.  The reduction index is consumed
+// in a permuted order (a lane's 32 codes feed 8 MMAs, 4 codes each); a small kernel first
+// writes the activations as f16 in exactly that order, so that each lane's operand is one
+// 16-byte L1-cached load.
 //
 // Reference counterpart: `nvfp4_dequantize_gemm_smem_kernel` (`csrc/glm_gemv.cu:653`, batch 3-16
 // on CUDA cores) and the MoE small-batch kernels (`:738-990`).
@@ -78,24 +79,33 @@ __device__ __forceinline__ void warp_rows_times_tokens(float (&acc)[MT][NT][4], 
     const int lane = threadIdx.x & 31;
     const int g = lane >> 2, c = lane & 3;
     const int G = K / 128;
-    for (int group = kpart; group < G; group += ksplit) {
+    // software pipeline: raw rows of the next group are in flight while this group is expanded
+    uint4 w0[MT], w1[MT], w0n[MT], w1n[MT];
+    uint16_t s0[MT], s1[MT], s0n[MT], s1n[MT];
+    auto load_group = [&](int group, uint4 (&a0)[MT], uint4 (&a1)[MT], uint16_t (&b0)[MT], uint16_t (&b1)[MT]) {
         const int kk = group * 128 + c * 32;
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+            a0[mt] = make_uint4(0, 0, 0, 0); a1[mt] = a0[mt]; b0[mt] = 0; b1[mt] = 0;
+            const int ra = mt * 16 + g, rb = ra + 8;
+            if (group < G && ra < rows_valid) {
+                a0[mt] = ldg_nc_16(Wp + (size_t)ra * w_stride + (kk >> 1));
+                b0[mt] = *reinterpret_cast<const uint16_t*>(S + (size_t)ra * s_stride + (kk >> 4));
+            }
+            if (group < G && rb < rows_valid) {
+                a1[mt] = ldg_nc_16(Wp + (size_t)rb * w_stride + (kk >> 1));
+                b1[mt] = *reinterpret_cast<const uint16_t*>(S + (size_t)rb * s_stride + (kk >> 4));
+            }
+        }
+    };
+    load_group(kpart, w0, w1, s0, s1);
+    for (int group = kpart; group < G; group += ksplit) {
+        load_group(group + ksplit, w0n, w1n, s0n, s1n);
         __half2 a_lo[MT][16], a_hi[MT][16];
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
-            uint4 w0 = make_uint4(0, 0, 0, 0), w1 = w0;
-            uint16_t s0 = 0, s1 = 0;
-            const int ra = mt * 16 + g, rb = ra + 8;
-            if (ra < rows_valid) {
-                w0 = ldg_nc_16(Wp + (size_t)ra * w_stride + (kk >> 1));
-                s0 = *reinterpret_cast<const uint16_t*>(S + (size_t)ra * s_stride + (kk >> 4));
-            }
-            if (rb < rows_valid) {
-                w1 = ldg_nc_16(Wp + (size_t)rb * w_stride + (kk >> 1));
-                s1 = *reinterpret_cast<const uint16_t*>(S + (size_t)rb * s_stride + (kk >> 4));
-            }
-            expand_row(w0, s0, a_lo[mt]);
-            expand_row(w1, s1, a_hi[mt]);
+            expand_row(w0[mt], s0[mt], a_lo[mt]);
+            expand_row(w1[mt], s1[mt], a_hi[mt]);
         }
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
@@ -120,6 +130,8 @@ __device__ __forceinline__ void warp_rows_times_tokens(float (&acc)[MT][NT][4], 
                 }
             }
         }
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) { w0[mt] = w0n[mt]; w1[mt] = w1n[mt]; s0[mt] = s0n[mt]; s1[mt] = s1n[mt]; }
     }
 }
 

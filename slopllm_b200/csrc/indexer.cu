@@ -167,14 +167,49 @@ struct TopkSelectParams {
     float* out_score;         // [T, top_k] (0 where unused)
 };
 
+// Radix-descent helper: given hist[256] of the current digit among the candidates, find the bin
+// that contains the `rem`-th largest and update (prefix, remaining).  Threads 0..255 take part;
+// bins are scanned from the top with warp shuffles.  Must be called by the whole block.
+__device__ __forceinline__ void radix_pick_bin(const uint32_t* hist, uint32_t* wtot, uint32_t* s_prefix, uint32_t* s_remaining,
+                                               uint32_t prefix, int shift) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t rem = *s_remaining;             // read before anyone may update it (barrier below)
+    uint32_t v = 0, incl = 0;
+    if (tid < 256) {
+        v = hist[255 - tid];                       // reversed: prefix sums run from the top bin down
+        incl = v;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t n = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += n;
+        }
+        if (lane == 31) wtot[warp] = incl;
+    }
+    __syncthreads();
+    if (tid < 256) {
+        uint32_t base = 0;
+        for (int w = 0; w < warp; ++w) base += wtot[w];
+        incl += base;
+        const uint32_t above = incl - v;
+        if (above < rem && incl >= rem) {          // exactly one bin satisfies this
+            *s_prefix = prefix | ((uint32_t)(255 - tid) << shift);
+            *s_remaining = rem - above;
+        }
+    }
+    __syncthreads();
+}
+
 // One block per query token.  If the query sees at most top_k keys in total, all local
 // keys are emitted.  Otherwise: radix descent for the k'-th largest key (k' = min(top_k,
 // n_local)), then an in-order gather of keys above the threshold plus the first ties.
+// Scores of up to 8192 keys stay in registers between the passes.
 __global__ void __launch_bounds__(1024) topk_select_kernel(TopkSelectParams p) {
     __shared__ uint32_t hist[256];
+    __shared__ uint32_t wtot[8];
     __shared__ uint32_t s_prefix, s_remaining;
-    __shared__ int wsum[32];
+    __shared__ int wsum[32], wsum2[32];
     __shared__ int s_base, s_eq_used;
+    constexpr int ITEMS = 8;
     const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = blockDim.x >> 5;
     const int pos = p.positions[t];
     const int n = local_visible(pos, p.cp_world, p.cp_rank);
@@ -188,69 +223,81 @@ __global__ void __launch_bounds__(1024) topk_select_kernel(TopkSelectParams p) {
         return;
     }
     const float* sc = p.scores + (size_t)t * p.ld_scores;
+    const bool cached = n <= ITEMS * (int)blockDim.x;
+    uint32_t keys[ITEMS];
+    if (cached) {
+#pragma unroll
+        for (int q = 0; q < ITEMS; ++q) {
+            const int i = tid + q * blockDim.x;
+            keys[q] = i < n ? order_key(sc[i]) : 0u;
+        }
+    }
     const int kk = min(p.top_k, n);
-    uint32_t prefix = 0, mask = 0;
+    uint32_t mask = 0;
     if (tid == 0) { s_prefix = 0; s_remaining = (uint32_t)kk; }
     for (int shift = 24; shift >= 0; shift -= 8) {
         for (int i = tid; i < 256; i += blockDim.x) hist[i] = 0;
         __syncthreads();
-        prefix = s_prefix;
-        for (int i = tid; i < n; i += blockDim.x) {
-            const uint32_t key = order_key(sc[i]);
-            if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1u);
-        }
-        __syncthreads();
-        if (tid == 0) {
-            uint32_t rem = s_remaining, cum = 0;
-            int b = 255;
-            for (; b > 0; --b) {
-                if (cum + hist[b] >= rem) break;
-                cum += hist[b];
+        const uint32_t prefix = s_prefix;
+        if (cached) {
+#pragma unroll
+            for (int q = 0; q < ITEMS; ++q) {
+                const int i = tid + q * blockDim.x;
+                if (i < n && (keys[q] & mask) == prefix) atomicAdd(&hist[(keys[q] >> shift) & 255u], 1u);
             }
-            s_remaining = rem - cum;
-            s_prefix = prefix | ((uint32_t)b << shift);
+        } else {
+            for (int i = tid; i < n; i += blockDim.x) {
+                const uint32_t key = order_key(sc[i]);
+                if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1u);
+            }
         }
         __syncthreads();
+        radix_pick_bin(hist, wtot, &s_prefix, &s_remaining, prefix, shift);
         mask |= 0xffu << shift;
     }
     const uint32_t thr = s_prefix;
     const int need_eq = (int)s_remaining;      // how many keys equal to thr are taken (lowest index first)
     if (tid == 0) { s_base = 0; s_eq_used = 0; }
     __syncthreads();
-    for (int c0 = 0; c0 < n; c0 += blockDim.x) {
+    for (int c0 = 0, q = 0; c0 < n; c0 += blockDim.x, ++q) {
         const int i = c0 + tid;
         uint32_t key = 0;
-        float v = 0.f;
-        if (i < n) { v = sc[i]; key = order_key(v); }
+        if (i < n) {
+            if (cached) {
+                // q is uniform; select the register without dynamic indexing
+#pragma unroll
+                for (int r = 0; r < ITEMS; ++r) if (r == q) key = keys[r];
+            } else {
+                key = order_key(sc[i]);
+            }
+        }
         const bool gt = (i < n) && key > thr, eq = (i < n) && key == thr;
-        // rank of this tie among ties, in index order
         const unsigned meq = __ballot_sync(0xffffffffu, eq);
-        const unsigned mgt = __ballot_sync(0xffffffffu, gt);
         if (lane == 0) wsum[warp] = __popc(meq);
         __syncthreads();
-        int eq_before = s_eq_used;
-        for (int w = 0; w < warp; ++w) eq_before += wsum[w];
+        int eq_before = s_eq_used, eq_total = 0;
+        for (int w = 0; w < nw; ++w) {
+            if (w < warp) eq_before += wsum[w];
+            eq_total += wsum[w];
+        }
         eq_before += __popc(meq & ((1u << lane) - 1));
         const bool take = gt || (eq && eq_before < need_eq);
-        int eq_total = 0;
-        for (int w = 0; w < nw; ++w) eq_total += wsum[w];
-        __syncthreads();
         const unsigned mt = __ballot_sync(0xffffffffu, take);
-        if (lane == 0) wsum[warp] = __popc(mt);
+        if (lane == 0) wsum2[warp] = __popc(mt);
         __syncthreads();
-        int off = s_base;
-        for (int w = 0; w < warp; ++w) off += wsum[w];
+        int off = s_base, tk_total = 0;
+        for (int w = 0; w < nw; ++w) {
+            if (w < warp) off += wsum2[w];
+            tk_total += wsum2[w];
+        }
         off += __popc(mt & ((1u << lane) - 1));
         if (take && off < p.top_k) {
             opos[off] = i * p.cp_world + p.cp_rank;
-            osc[off] = v;
+            osc[off] = sc[i];
         }
-        int tk_total = 0;
-        for (int w = 0; w < nw; ++w) tk_total += wsum[w];
         __syncthreads();
         if (tid == 0) { s_base += tk_total; s_eq_used += eq_total; }
         __syncthreads();
-        (void)mgt;
     }
     for (int i = s_base + tid; i < p.top_k; i += blockDim.x) { opos[i] = -1; osc[i] = 0.f; }
 }

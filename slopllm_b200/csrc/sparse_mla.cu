@@ -205,12 +205,20 @@ __global__ void __launch_bounds__(128) mla_combine_kernel(CombineParams p) {
     const float inv = den > 0.f ? 1.f / den : 0.f;
     for (int d = threadIdx.x * 4; d < p.R; d += blockDim.x * 4) {
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int i = 0; i < np; ++i) {
-            const float w = wsh[i];
-            if (w != 0.f) {
+        // four independent loads in flight per step; zero-weight partials are finite (written by the split kernel)
+        for (int i0 = 0; i0 < np; i0 += 4) {
+            float4 v[4];
+            float w[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = min(i0 + u, np - 1);
                 const int b = i / p.parts_per_buf, q = i % p.parts_per_buf;
-                const float4 v = *reinterpret_cast<const float4*>(p.o_ptrs[b] + (th * p.parts_per_buf + q) * p.R + d);
-                acc.x += w * v.x; acc.y += w * v.y; acc.z += w * v.z; acc.w += w * v.w;
+                w[u] = (i0 + u < np) ? wsh[i] : 0.f;
+                v[u] = *reinterpret_cast<const float4*>(p.o_ptrs[b] + (th * p.parts_per_buf + q) * p.R + d);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                acc.x += w[u] * v[u].x; acc.y += w[u] * v[u].y; acc.z += w[u] * v[u].z; acc.w += w[u] * v[u].w;
             }
         }
         uint2 o;

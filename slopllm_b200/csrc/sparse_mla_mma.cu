@@ -1,0 +1,282 @@
+// Sparse MLA flash attention on the tensor cores (decode and prefill): per (key split, group of
+// 16 heads, query token) one CTA gathers its selected packed rows (fp8 latent x per-group scale,
+// bf16 rope), expands them to f16 in shared memory, computes S = Q K^T and O += P V with
+// `mma.sync.m16n8k16` (fp32 accumulation, online softmax) and emits a partial (o, lse) that the
+// combine kernel (or the cross-rank merge under context parallelism) finishes.
+//
+// Covers what the reference gets from the vendored `sparse_mla_sm120` decode / prefill kernels
+// (`csrc/glm_sparse_mla.cu:34-126`): split-K over the top-k rows, mid_out / mid_lse + combine.
+#include "common.cuh"
+
+namespace {
+
+struct Params {
+    const bf16* q_abs;        // [T, h, R]
+    const bf16* q_pe;         // [T, h, Dr]
+    const uint8_t* kv_cache;  // [slots, row_bytes]
+    const int* slots;         // [T, topk]
+    const int* lengths;       // [T]
+    int h, R, Dr, group, topk, splits;
+    float sm_scale;
+    float* o_part;            // [T, h, splits, R]
+    float* lse_part;          // [T, h, splits]
+};
+
+constexpr int HB = 16;        // heads per CTA (one MMA row tile)
+constexpr int KC = 64;        // keys per chunk (8 warps x 8 keys)
+
+__device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldmatrix_x2_trans(uint32_t& r0, uint32_t& r1, const void* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(a));
+}
+
+// grid (splits, ceil(h / 16), T); block 256.
+// Shared: Q [16][DP] f16, K [64][DP] f16 (DP = R + Dr + 8 halves: rows 16-byte aligned, bank-skewed),
+// P [16][72] f16, row statistics.
+__global__ void __launch_bounds__(256) sparse_mla_mma_kernel(Params p) {
+    extern __shared__ __align__(16) unsigned char smraw[];
+    const int D = p.R + p.Dr, DP = D + 8;
+    __half* qs = reinterpret_cast<__half*>(smraw);            // HB * DP
+    __half* ks = qs + HB * DP;                                // KC * DP
+    __half* ps = ks + KC * DP;                                // HB * 72
+    float* wmax = reinterpret_cast<float*>(ps + HB * 72);     // [8 warps][16 rows]
+    float* wsum = wmax + 8 * HB;                              // [8 warps][16 rows]
+    float* row_m = wsum + 8 * HB;                             // [16] running max
+    float* row_l = row_m + HB;                                // [16] running sum
+    float* row_a = row_l + HB;                                // [16] rescale of this chunk
+    int* s_slots = reinterpret_cast<int*>(row_a + HB);        // [64] slots of the current chunk
+
+    const int split = blockIdx.x, hg = blockIdx.y, t = blockIdx.z;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, c = lane & 3;
+    const int L = p.lengths[t];
+    const int per = (L + p.splits - 1) / p.splits;
+    const int j_begin = min(L, split * per), j_end = min(L, j_begin + per);
+    const int h0 = hg * HB, nh = min(HB, p.h - h0);
+    const int ngroups = p.R / p.group;
+    const int row_bytes = p.R + 4 * ngroups + 2 * p.Dr;
+    const int words = row_bytes / 4;
+    // 16-byte gather path: every field boundary of the row falls on a 16-byte boundary
+    const bool vec16 = row_bytes % 16 == 0 && p.R % 16 == 0 && (4 * ngroups) % 16 == 0 && p.group % 16 == 0 &&
+                       KC * (row_bytes / 16) <= 12 * 256;
+    const int* slots = p.slots + (size_t)t * p.topk;
+
+    // Q (pre-multiplied by the softmax scale) as f16; rows >= nh are zero
+    for (int i = tid; i < HB * (D / 2); i += blockDim.x) {
+        const int hh = i / (D / 2), d = (i % (D / 2)) * 2;
+        float2 v = make_float2(0.f, 0.f);
+        if (hh < nh) {
+            const uint32_t u = d < p.R ? *reinterpret_cast<const uint32_t*>(p.q_abs + ((size_t)t * p.h + h0 + hh) * p.R + d)
+                                       : *reinterpret_cast<const uint32_t*>(p.q_pe + ((size_t)t * p.h + h0 + hh) * p.Dr + (d - p.R));
+            v = bf162_to_f2(u);
+        }
+        *reinterpret_cast<__half2*>(qs + hh * DP + d) = __floats2half2_rn(v.x * p.sm_scale, v.y * p.sm_scale);
+    }
+    if (tid < HB) { row_m[tid] = -INFINITY; row_l[tid] = 0.f; }
+
+    // output accumulators: warp w owns dims [w*R/8, (w+1)*R/8), up to 8 n-tiles of 8 dims
+    const int dims_per_warp = p.R / 8, ntiles = dims_per_warp / 8;
+    float oacc[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.f;
+
+    for (int c0 = j_begin; c0 < j_end; c0 += KC) {
+        const int kc = min(KC, j_end - c0);
+        __syncthreads();
+        // ---- gather + expand kc rows ----
+        if (tid < KC) s_slots[tid] = tid < kc ? slots[c0 + tid] : 0;
+        __syncthreads();
+        if (vec16) {
+            // 16-byte chunks, all of a thread's loads issued before the first use
+            const int chunks = row_bytes / 16, total = kc * chunks;
+            constexpr int MAXLD = 12;
+            uint4 buf[MAXLD];
+            float scl[MAXLD];
+#pragma unroll
+            for (int n = 0; n < MAXLD; ++n) {
+                const int i = tid + n * 256;
+                if (i < total) {
+                    const int j = i / chunks, byte = (i % chunks) * 16;
+                    const uint8_t* row = p.kv_cache + (size_t)s_slots[j] * row_bytes;
+                    buf[n] = ldg_nc_16(row + byte);
+                    scl[n] = byte < p.R ? *reinterpret_cast<const float*>(row + p.R + 4 * (byte / p.group)) : 0.f;
+                }
+            }
+#pragma unroll
+            for (int n = 0; n < MAXLD; ++n) {
+                const int i = tid + n * 256;
+                if (i < total) {
+                    const int j = i / chunks, byte = (i % chunks) * 16;
+                    const uint32_t w4[4] = {buf[n].x, buf[n].y, buf[n].z, buf[n].w};
+                    if (byte < p.R) {
+                        uint32_t o[8];
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const float2 a = e4m3x2_to_float2((uint16_t)(w4[q] & 0xffffu)), b = e4m3x2_to_float2((uint16_t)(w4[q] >> 16));
+                            __half2 lo = __floats2half2_rn(a.x * scl[n], a.y * scl[n]), hi = __floats2half2_rn(b.x * scl[n], b.y * scl[n]);
+                            o[2 * q] = *reinterpret_cast<uint32_t*>(&lo);
+                            o[2 * q + 1] = *reinterpret_cast<uint32_t*>(&hi);
+                        }
+                        uint4* dst = reinterpret_cast<uint4*>(ks + j * DP + byte);
+                        dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+                        dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+                    } else if (byte >= p.R + 4 * ngroups) {
+                        const int d = p.R + (byte - p.R - 4 * ngroups) / 2;
+                        uint32_t o[4];
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const float2 f = bf162_to_f2(w4[q]);
+                            __half2 hv = __floats2half2_rn(f.x, f.y);
+                            o[q] = *reinterpret_cast<uint32_t*>(&hv);
+                        }
+                        *reinterpret_cast<uint4*>(ks + j * DP + d) = make_uint4(o[0], o[1], o[2], o[3]);
+                    }
+                }
+            }
+        } else
+        for (int i = tid; i < KC * words; i += blockDim.x) {
+            const int j = i / words, wd = i % words, byte = wd * 4;
+            if (j < kc) {
+                const uint8_t* row = p.kv_cache + (size_t)s_slots[j] * row_bytes;
+                const uint32_t u = *reinterpret_cast<const uint32_t*>(row + byte);
+                if (byte < p.R) {
+                    const float sc = *reinterpret_cast<const float*>(row + p.R + 4 * (byte / p.group));
+                    const float2 a = e4m3x2_to_float2((uint16_t)(u & 0xffffu)), b = e4m3x2_to_float2((uint16_t)(u >> 16));
+                    __half2 lo = __floats2half2_rn(a.x * sc, a.y * sc), hi = __floats2half2_rn(b.x * sc, b.y * sc);
+                    uint2 o;
+                    o.x = *reinterpret_cast<uint32_t*>(&lo);
+                    o.y = *reinterpret_cast<uint32_t*>(&hi);
+                    *reinterpret_cast<uint2*>(ks + j * DP + byte) = o;
+                } else if (byte >= p.R + 4 * ngroups) {
+                    const int d = p.R + (byte - p.R - 4 * ngroups) / 2;
+                    const float2 f = bf162_to_f2(u);
+                    *reinterpret_cast<__half2*>(ks + j * DP + d) = __floats2half2_rn(f.x, f.y);
+                }
+            }
+        }
+        // rows beyond kc contribute p = 0; keep them finite so that 0 * v stays 0
+        for (int i = tid; i < (KC - kc) * (D / 2); i += blockDim.x) {
+            const int j = kc + i / (D / 2), d2 = i % (D / 2);
+            reinterpret_cast<uint32_t*>(ks + j * DP)[d2] = 0u;
+        }
+        __syncthreads();
+        // ---- S = Q K^T : warp w -> keys 8w .. 8w+7 ----
+        float s[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int k0 = 0; k0 < D; k0 += 16) {
+            uint32_t a[4];
+            // A tile rows 0..15, cols k0..k0+15: lanes 0-15 -> rows, lanes 16-31 -> rows with col + 8
+            ldmatrix_x4(a, qs + (lane & 15) * DP + k0 + (lane >> 4) * 8);
+            const __half* kr = ks + (warp * 8 + g) * DP + k0 + 2 * c;
+            const uint32_t b0 = *reinterpret_cast<const uint32_t*>(kr), b1 = *reinterpret_cast<const uint32_t*>(kr + 8);
+            mma16816(s, a, b0, b1);
+        }
+        // s[0]:(head g, key 2c) s[1]:(g, 2c+1) s[2]:(g+8, 2c) s[3]:(g+8, 2c+1)
+        const int key0 = warp * 8 + 2 * c;
+        if (key0 >= kc) { s[0] = -INFINITY; s[2] = -INFINITY; }
+        if (key0 + 1 >= kc) { s[1] = -INFINITY; s[3] = -INFINITY; }
+        float m0 = fmaxf(s[0], s[1]), m1 = fmaxf(s[2], s[3]);
+        m0 = fmaxf(m0, __shfl_xor_sync(0xffffffffu, m0, 1)); m0 = fmaxf(m0, __shfl_xor_sync(0xffffffffu, m0, 2));
+        m1 = fmaxf(m1, __shfl_xor_sync(0xffffffffu, m1, 1)); m1 = fmaxf(m1, __shfl_xor_sync(0xffffffffu, m1, 2));
+        if (c == 0) { wmax[warp * HB + g] = m0; wmax[warp * HB + g + 8] = m1; }
+        __syncthreads();
+        if (tid < HB) {
+            float mx = row_m[tid];
+            const float old = mx;
+#pragma unroll
+            for (int w = 0; w < 8; ++w) mx = fmaxf(mx, wmax[w * HB + tid]);
+            row_a[tid] = (old == -INFINITY) ? 0.f : __expf(old - mx);
+            row_m[tid] = mx;
+        }
+        __syncthreads();
+        const float mn0 = row_m[g], mn1 = row_m[g + 8];
+        float e[4];
+        e[0] = (s[0] == -INFINITY) ? 0.f : __expf(s[0] - mn0);
+        e[1] = (s[1] == -INFINITY) ? 0.f : __expf(s[1] - mn0);
+        e[2] = (s[2] == -INFINITY) ? 0.f : __expf(s[2] - mn1);
+        e[3] = (s[3] == -INFINITY) ? 0.f : __expf(s[3] - mn1);
+        *reinterpret_cast<__half2*>(ps + g * 72 + key0) = __floats2half2_rn(e[0], e[1]);
+        *reinterpret_cast<__half2*>(ps + (g + 8) * 72 + key0) = __floats2half2_rn(e[2], e[3]);
+        float l0 = e[0] + e[1], l1 = e[2] + e[3];
+        l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+        l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+        if (c == 0) { wsum[warp * HB + g] = l0; wsum[warp * HB + g + 8] = l1; }
+        __syncthreads();
+        if (tid < HB) {
+            float sum = 0.f;
+#pragma unroll
+            for (int w = 0; w < 8; ++w) sum += wsum[w * HB + tid];
+            row_l[tid] = row_l[tid] * row_a[tid] + sum;
+        }
+        // ---- O = O * alpha + P V : warp w -> dims [w*dims_per_warp, ...) ----
+        const float a0 = row_a[g], a1 = row_a[g + 8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { oacc[i][0] *= a0; oacc[i][1] *= a0; oacc[i][2] *= a1; oacc[i][3] *= a1; }
+#pragma unroll
+        for (int k0 = 0; k0 < KC; k0 += 16) {
+            uint32_t a[4];
+            ldmatrix_x4(a, ps + (lane & 15) * 72 + k0 + (lane >> 4) * 8);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                if (i < ntiles) {
+                    uint32_t b0, b1;
+                    // V[k = key k0 + (lane & 15)][n = dim0 .. dim0 + 7], transposed on load
+                    ldmatrix_x2_trans(b0, b1, ks + (k0 + (lane & 15)) * DP + warp * dims_per_warp + i * 8);
+                    mma16816(oacc[i], a, b0, b1);
+                }
+            }
+        }
+    }
+    __syncthreads();
+    // ---- write the normalised partial ----
+    const float l0 = row_l[g], l1 = row_l[g + 8];
+    const float i0 = l0 > 0.f ? 1.f / l0 : 0.f, i1 = l1 > 0.f ? 1.f / l1 : 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        if (i < ntiles) {
+            const int d = warp * dims_per_warp + i * 8 + 2 * c;
+            if (g < nh) {
+                float* o = p.o_part + (((size_t)t * p.h + h0 + g) * p.splits + split) * p.R + d;
+                *reinterpret_cast<float2*>(o) = make_float2(oacc[i][0] * i0, oacc[i][1] * i0);
+            }
+            if (g + 8 < nh) {
+                float* o = p.o_part + (((size_t)t * p.h + h0 + g + 8) * p.splits + split) * p.R + d;
+                *reinterpret_cast<float2*>(o) = make_float2(oacc[i][2] * i1, oacc[i][3] * i1);
+            }
+        }
+    }
+    if (tid < nh) {
+        const float l = row_l[tid];
+        p.lse_part[((size_t)t * p.h + h0 + tid) * p.splits + split] = l > 0.f ? row_m[tid] + logf(l) : -INFINITY;
+    }
+}
+
+}  // namespace
+
+// Same contract as sl_sparse_mla_split (csrc/sparse_mla.cu).  Needs R % 64 == 0, (R + Dr) % 16 == 0,
+// R <= 512, Dr % 2 == 0, group % 4 == 0.  Returns -1 when the shape is not supported.
+SL_API int sl_sparse_mla_split_mma(const void* params, int T, cudaStream_t s) {
+    const Params* p = static_cast<const Params*>(params);
+    if (T == 0) return 0;
+    if (p->R % 64 != 0 || p->R > 512 || (p->R + p->Dr) % 16 != 0 || p->Dr % 2 != 0 || p->group % 4 != 0) return -1;
+    const int DP = p->R + p->Dr + 8;
+    const size_t smem = (size_t)(HB * DP + KC * DP + HB * 72) * sizeof(__half) + (size_t)(8 * HB * 2 + 3 * HB + KC) * sizeof(float);
+    static bool attr = false;
+    if (!attr) {
+        cudaFuncSetAttribute(sparse_mla_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+        attr = true;
+    }
+    if (smem > 160 * 1024) return -1;
+    dim3 grid(p->splits, (p->h + HB - 1) / HB, T);
+    sparse_mla_mma_kernel<<<grid, 256, smem, s>>>(*p);
+    return (int)cudaGetLastError();
+}

@@ -16,7 +16,7 @@ from . import native as N
 from . import reference as R
 
 DECODE_MAX_T = 32          # token rows handled by the weight-streaming (GEMV) kernels
-TENSOR_MIN_T = 5           # from this many rows on the streaming kernels use the tensor cores
+TENSOR_MIN_T = 2           # from this many rows on the streaming kernels use the tensor cores
 
 
 class CudaOps:
@@ -178,9 +178,9 @@ class CudaOps:
         """Split the selected keys so that the grid fills the 148 SMs a few times over
         (the reference's `sparseMlaChunksPerBlock`, `src/sparse-mla-planner.ts:1-21`)."""
         topk = self.cfg.index_topk
-        groups = (h + 7) // 8
+        groups = (h + 15) // 16
         want = max(1, (148 * 2) // max(1, T * groups))
-        return int(max(1, min(want, topk // 32, 64)))
+        return int(max(1, min(want, max(1, topk // 64), 64)))
 
     def sparse_mla_partials(self, q_abs, q_pe, layer_cache, slots, lengths):
         c = self.cfg
@@ -193,7 +193,8 @@ class CudaOps:
                               slots=slots.data_ptr(), lengths=lengths.data_ptr(), h=h, R=Rr, Dr=c.qk_rope_head_dim,
                               group=c.kv_quant_group, topk=slots.shape[1], splits=splits, sm_scale=c.softmax_scale,
                               o_part=o_part.data_ptr(), lse_part=lse_part.data_ptr())
-        N.call("sl_sparse_mla_split", C.byref(p), T, N.stream())
+        c_ok = Rr % 64 == 0 and Rr <= 512 and (Rr + c.qk_rope_head_dim) % 16 == 0
+        N.call("sl_sparse_mla_split_mma" if c_ok else "sl_sparse_mla_split", C.byref(p), T, N.stream())
         return o_part, lse_part
 
     def combine(self, o_parts, lse_parts, head_begin=0, head_count=None, want_lse=True):

@@ -140,6 +140,7 @@ _SIGS = {
     "sl_indexer_scores": [C.POINTER(IndexerScoreParams), i32, i32, vp],
     "sl_topk_select": [C.POINTER(TopkSelectParams), i32, vp],
     "sl_sparse_mla_split": [C.POINTER(SparseMlaParams), i32, vp],
+    "sl_sparse_mla_split_mma": [C.POINTER(SparseMlaParams), i32, vp],
     "sl_mla_combine": [C.POINTER(CombineParams), i32, vp],
     "sl_argmax": [vp, vp, i32, i32, i32, i32, i64, vp, vp, vp, vp],
     "sl_sample": [C.POINTER(SampleParams), i32, vp],
