@@ -13,6 +13,7 @@
 // This replaces the reference's cuBLASLt path for batch >= 3 (`csrc/glm_gemv.cu:1642-1770`) and
 // its `mma.sync` grouped kernels (`csrc/glm_mma_moe.cu:110`).
 #include "tcgen05.cuh"
+#include "push.cuh"
 
 namespace {
 
@@ -29,7 +30,7 @@ template <int BN>
 __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA,
                                                         const __grid_constant__ CUtensorMap tmB, void* __restrict__ C,
                                                         int M, int N, int K, int ldc, int out_f32, int transpose_out,
-                                                        int* __restrict__ err) {
+                                                        int* __restrict__ err, int use_push, PushCtx push) {
     using Cfg = GemmCfg<BN>;
     constexpr int STAGES = Cfg::STAGES;
     extern __shared__ uint8_t smem_raw[];
@@ -109,7 +110,9 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
                     // C is [N, M] row-major (row stride ldc), a warp writes 32 consecutive features
                     if (row < M) {
                         for (int i = 0; i < 32 && col + i < N; ++i) {
-                            if (out_f32) ((float*)C)[(size_t)(col + i) * ldc + row] = __uint_as_float(r[i]);
+                            if (use_push) {
+                                for (int pr = 0; pr < push.world; ++pr) *push_dst(push, pr, col + i, row) = __uint_as_float(r[i]);
+                            } else if (out_f32) ((float*)C)[(size_t)(col + i) * ldc + row] = __uint_as_float(r[i]);
                             else ((bf16*)C)[(size_t)(col + i) * ldc + row] = __float2bfloat16(__uint_as_float(r[i]));
                         }
                     }
@@ -149,11 +152,12 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
         tc::fence_after_sync();
         tc::tmem_dealloc(tmem_base, BN);
     }
+    if (use_push) push_finish(push, gridDim.x * gridDim.y);
 }
 
 template <int BN>
 int launch(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc, int out_f32,
-           int transpose_out, int* err, cudaStream_t s) {
+           int transpose_out, int* err, cudaStream_t s, const PushCtx* push = nullptr) {
     CUtensorMap tmA, tmB;
     int rc = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)M, (uint64_t)K, (uint64_t)lda * 2, BM, BK);
     if (rc) return rc;
@@ -166,7 +170,8 @@ int launch(const void* A, const void* B, void* C, int M, int N, int K, int lda, 
         attr_set = true;
     }
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-    kern<<<grid, 192, GemmCfg<BN>::SMEM, s>>>(tmA, tmB, C, M, N, K, ldc, out_f32, transpose_out, err);
+    kern<<<grid, 192, GemmCfg<BN>::SMEM, s>>>(tmA, tmB, C, M, N, K, ldc, out_f32, transpose_out, err, push ? 1 : 0,
+                                              push ? *push : PushCtx{});
     return (int)cudaGetLastError();
 }
 
@@ -192,4 +197,12 @@ SL_API int sl_linear_smallT_bf16_tcgen05(const void* x, const void* W, void* y, 
     if (T <= 0 || N <= 0 || K <= 0) return 0;
     if (T > 32 || K % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0) return -1;
     return launch<32>(W, x, y, N, T, K, ldw, ldx, ldy, out_f32, 1, (int*)err, s);
+}
+
+// Weight-streaming linear whose fp32 result rows go to every rank's receive slot (fused all-reduce producer).
+SL_API int sl_linear_smallT_bf16_tcgen05_push(const void* x, const void* W, int T, int N, int K, int ldx, int ldw, void* err,
+                                              const PushCtx* push, cudaStream_t s) {
+    if (T <= 0 || N <= 0 || K <= 0) return 0;
+    if (push == nullptr || T > 32 || K % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0 || T > push->slot_rows || N > push->row_len) return -1;
+    return launch<32>(W, x, nullptr, N, T, K, ldw, ldx, 0, 1, 1, (int*)err, s, push);
 }

@@ -6,7 +6,7 @@
 // `:738-990` (nvfp4_mul_mat_id), `:1291-1375` (fused down-proj + weighted top-k reduce).
 // The kernels here are memory-roofline designs for HBM3e: 16-byte non-allocating loads,
 // several rows in flight per warp, fp32 accumulation.
-#include "common.cuh"
+#include "push.cuh"
 
 // ---------------------------------------------------------------------------------------------
 // bf16: y[t, n] = sum_k x[t, k] W[n, k].   Warp handles R rows at a time for TT tokens.
@@ -367,7 +367,7 @@ struct MoeDownParams {
     int accumulate;            // add into out (fp32 only)
 };
 
-__global__ void __launch_bounds__(256) moe_down_kernel(MoeDownParams p) {
+__global__ void __launch_bounds__(256) moe_down_kernel(MoeDownParams p, int use_push, PushCtx push) {
     // grid (H / 32, T).  The block owns 32 output rows of one token; warp w streams the rows of
     // routes w, w+8, ... (independent weight streams), the partial sums meet in shared memory.
     extern __shared__ __align__(16) unsigned char smraw[];
@@ -424,9 +424,12 @@ __global__ void __launch_bounds__(256) moe_down_kernel(MoeDownParams p) {
 #pragma unroll
         for (int w = 0; w < 8; ++w) v += red[w][lane];
         const size_t o = (size_t)t * p.H + n0 + lane;
-        if (p.out_f32) ((float*)p.out)[o] = p.accumulate ? ((float*)p.out)[o] + v : v;
+        if (use_push) {
+            for (int pr = 0; pr < push.world; ++pr) *push_dst(push, pr, t, n0 + lane) = v;
+        } else if (p.out_f32) ((float*)p.out)[o] = p.accumulate ? ((float*)p.out)[o] + v : v;
         else ((bf16*)p.out)[o] = __float2bfloat16(v);
     }
+    if (use_push) push_finish(push, gridDim.x * gridDim.y);
 }
 
 SL_API int sl_moe_down(const MoeDownParams* p, cudaStream_t s) {
@@ -437,6 +440,19 @@ SL_API int sl_moe_down(const MoeDownParams* p, cudaStream_t s) {
     if (smem > 200 * 1024) return -2;
     if (smem > 48 * 1024) cudaFuncSetAttribute(moe_down_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     const int bx = (p->H + 31) / 32;          // 32 rows per block
-    moe_down_kernel<<<dim3(bx, p->T), 256, smem, s>>>(*p);
+    moe_down_kernel<<<dim3(bx, p->T), 256, smem, s>>>(*p, 0, PushCtx{});
+    return SL_LAUNCH_CHECK();
+}
+
+// Down projection whose result rows go to every rank's receive slot (fused all-reduce producer).
+SL_API int sl_moe_down_push(const MoeDownParams* p, const PushCtx* push, cudaStream_t s) {
+    if (p->T == 0) return 0;
+    if (p->I % 32 != 0 || push == nullptr || p->T > push->slot_rows || p->H > push->row_len) return -1;
+    const int nr = p->top_k + (p->sw2 ? 1 : 0);
+    const size_t smem = (size_t)nr * p->I * sizeof(__half);
+    if (smem > 200 * 1024) return -2;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(moe_down_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    const int bx = (p->H + 31) / 32;
+    moe_down_kernel<<<dim3(bx, p->T), 256, smem, s>>>(*p, 1, *push);
     return SL_LAUNCH_CHECK();
 }

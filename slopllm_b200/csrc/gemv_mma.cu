@@ -12,7 +12,7 @@
 //
 // Reference counterpart: `nvfp4_dequantize_gemm_smem_kernel` (`csrc/glm_gemv.cu:653`, batch 3-16
 // on CUDA cores) and the MoE small-batch kernels (`:738-990`).
-#include "common.cuh"
+#include "push.cuh"
 
 namespace {
 
@@ -141,7 +141,7 @@ template <int MT, int NT>
 __global__ void __launch_bounds__(256) linear_nvfp4_mma_kernel(void* __restrict__ y, const uint4* __restrict__ xp,
                                                                const uint8_t* __restrict__ Wp, const uint8_t* __restrict__ S,
                                                                const float* __restrict__ gscale, int T, int N, int K,
-                                                               int ksplit, int out_f32) {
+                                                               int ksplit, int out_f32, int use_push, PushCtx push) {
     extern __shared__ float red[];
     constexpr int ROWS = MT * 16, TOK = NT * 8;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -177,15 +177,19 @@ __global__ void __launch_bounds__(256) linear_nvfp4_mma_kernel(void* __restrict_
             float v = 0.f;
             for (int kp = 0; kp < ksplit; ++kp) v += red[(size_t)(tl * ksplit + kp) * (TOK * ROWS) + rem];
             v *= gs;
-            if (out_f32) ((float*)y)[(size_t)tok * N + n] = v;
+            if (use_push) {
+                // fused all-reduce, producer side: the partial goes to every rank's receive slot
+                for (int pr = 0; pr < push.world; ++pr) *push_dst(push, pr, tok, n) = v;
+            } else if (out_f32) ((float*)y)[(size_t)tok * N + n] = v;
             else ((bf16*)y)[(size_t)tok * N + n] = __float2bfloat16(v);
         }
     }
+    if (use_push) push_finish(push, gridDim.x);
 }
 
 template <int MT, int NT>
 int launch_linear(void* y, const void* x, void* xp, const void* Wp, const void* S, const void* g, int T, int N, int K, int ldx,
-                  int out_f32, cudaStream_t s) {
+                  int out_f32, const PushCtx* push, cudaStream_t s) {
     constexpr int ROWS = MT * 16, TOK = NT * 8;
     const int units = TOK * (K / 8);
     permute_x_kernel<<<(units + 255) / 256, 256, 0, s>>>((uint4*)xp, (const bf16*)x, T, TOK, K, ldx);
@@ -199,20 +203,33 @@ int launch_linear(void* y, const void* x, void* xp, const void* Wp, const void* 
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     kern<<<(tiles + tiles_per_block - 1) / tiles_per_block, 256, smem, s>>>(y, (const uint4*)xp, (const uint8_t*)Wp,
                                                                            (const uint8_t*)S, (const float*)g, T, N, K, ksplit,
-                                                                           out_f32);
+                                                                           out_f32, push ? 1 : 0, push ? *push : PushCtx{});
     return (int)cudaGetLastError();
 }
 
 }  // namespace
 
+static int dispatch_linear(void* y, const void* x, void* xp, const void* Wp, const void* S, const void* g, int T, int N, int K,
+                           int ldx, int out_f32, const PushCtx* push, cudaStream_t s) {
+    if (T == 0 || N == 0) return 0;
+    if (T > 32 || K % 128 != 0 || ldx % 8 != 0) return -1;
+    if (T <= 8) return launch_linear<1, 1>(y, x, xp, Wp, S, g, T, N, K, ldx, out_f32, push, s);
+    if (T <= 16) return launch_linear<1, 2>(y, x, xp, Wp, S, g, T, N, K, ldx, out_f32, push, s);
+    if (T <= 24) return launch_linear<2, 3>(y, x, xp, Wp, S, g, T, N, K, ldx, out_f32, push, s);
+    return launch_linear<2, 4>(y, x, xp, Wp, S, g, T, N, K, ldx, out_f32, push, s);
+}
+
 // y[T, N] = g * x[T, K] . dequant(Wp, S)^T for 1 <= T <= 32.  K % 128 == 0, ldx % 8 == 0.
 // `xp` is caller-owned scratch of ceil(T/8)*8 * K f16 values (the permuted copy of x).
 SL_API int sl_linear_nvfp4_mma(void* y, const void* x, void* xp, const void* Wp, const void* S, const void* g, int T, int N,
                                int K, int ldx, int out_f32, cudaStream_t s) {
-    if (T == 0 || N == 0) return 0;
-    if (T > 32 || K % 128 != 0 || ldx % 8 != 0) return -1;
-    if (T <= 8) return launch_linear<1, 1>(y, x, xp, Wp, S, g, T, N, K, ldx, out_f32, s);
-    if (T <= 16) return launch_linear<1, 2>(y, x, xp, Wp, S, g, T, N, K, ldx, out_f32, s);
-    if (T <= 24) return launch_linear<2, 3>(y, x, xp, Wp, S, g, T, N, K, ldx, out_f32, s);
-    return launch_linear<2, 4>(y, x, xp, Wp, S, g, T, N, K, ldx, out_f32, s);
+    return dispatch_linear(y, x, xp, Wp, S, g, T, N, K, ldx, out_f32, nullptr, s);
+}
+
+// Same product, but the fp32 result rows are stored into every rank's receive slot and the epoch
+// flags are published (producer half of the fused all-reduce; consumer: sl_ar_add_rmsnorm).
+SL_API int sl_linear_nvfp4_mma_push(const void* x, void* xp, const void* Wp, const void* S, const void* g, int T, int N, int K,
+                                    int ldx, const PushCtx* push, cudaStream_t s) {
+    if (push == nullptr || T > push->slot_rows || N > push->row_len) return -1;
+    return dispatch_linear(nullptr, x, xp, Wp, S, g, T, N, K, ldx, 1, push, s);
 }

@@ -175,8 +175,9 @@ struct CombineParams {
     const float* lse_ptrs[8];
     int n_buf, parts_per_buf, h, R;
     int head_begin, head_count;          // heads written (CP: this rank's slice)
-    bf16* o_out;                         // [T, head_count, R]
+    void* o_out;                         // [T, head_count, R] bf16 (or fp32 when out_f32)
     float* lse_out;                      // [T, head_count] or null
+    int out_f32;
 };
 
 __global__ void __launch_bounds__(128) mla_combine_kernel(CombineParams p) {
@@ -221,10 +222,15 @@ __global__ void __launch_bounds__(128) mla_combine_kernel(CombineParams p) {
                 acc.x += w[u] * v[u].x; acc.y += w[u] * v[u].y; acc.z += w[u] * v[u].z; acc.w += w[u] * v[u].w;
             }
         }
-        uint2 o;
-        o.x = f2_to_bf162(acc.x * inv, acc.y * inv);
-        o.y = f2_to_bf162(acc.z * inv, acc.w * inv);
-        *reinterpret_cast<uint2*>(p.o_out + ((size_t)t * p.head_count + hh) * p.R + d) = o;
+        const size_t oi = ((size_t)t * p.head_count + hh) * p.R + d;
+        if (p.out_f32) {
+            *reinterpret_cast<float4*>((float*)p.o_out + oi) = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+        } else {
+            uint2 o;
+            o.x = f2_to_bf162(acc.x * inv, acc.y * inv);
+            o.y = f2_to_bf162(acc.z * inv, acc.w * inv);
+            *reinterpret_cast<uint2*>((bf16*)p.o_out + oi) = o;
+        }
     }
     if (threadIdx.x == 0 && p.lse_out) p.lse_out[(size_t)t * p.head_count + hh] = den > 0.f ? mx + logf(den) : -INFINITY;
 }

@@ -107,20 +107,24 @@ class GlmMoeDsaModel:
         if ctx.cp and ctx.world > 1:
             q_abs = comm.all_gather(q_abs, dim=1)
             q_pe = comm.all_gather(q_pe, dim=1)
-            o, lse = ops.sparse_mla(q_abs, q_pe, lc, st.slots, st.lengths)
-            o = comm.cp_merge_heads(ops, o, lse)
+            if hasattr(ops, "sparse_mla_partials"):
+                o = comm.cp_merge_partials(ops, *ops.sparse_mla_partials(q_abs, q_pe, lc, st.slots, st.lengths))
+            else:
+                o, lse = ops.sparse_mla(q_abs, q_pe, lc, st.slots, st.lengths)
+                o = comm.cp_merge_heads(ops, o, lse)
         else:
             o, _ = ops.sparse_mla(q_abs, q_pe, lc, st.slots, st.lengths)
-        return ops.linear(ops.v_expand(o, lw.w_v), lw.o_proj, out_f32=True)
+        return ops.linear(ops.v_expand(o, lw.w_v), lw.o_proj, out_f32=True, sink=comm.partial_sink(x.shape[0]))
 
     # -- MLP ----------------------------------------------------------------------------------
-    def mlp(self, lw: LayerWeights, y: torch.Tensor):
+    def mlp(self, lw: LayerWeights, y: torch.Tensor, final: bool = False):
         ops, ctx = self.ops, self.ctx
+        if lw.experts is not None and ctx.ep and ctx.world > 1:
+            return self._moe_ep(lw, y)
+        sink = self.comm.partial_sink(y.shape[0], final=final)
         if lw.experts is None:
-            return ops.dense_mlp(y, lw)
-        if not (ctx.ep and ctx.world > 1):
-            return ops.moe_tp(y, lw)
-        return self._moe_ep(lw, y)
+            return ops.dense_mlp(y, lw, sink=sink)
+        return ops.moe_tp(y, lw, sink=sink)
 
     def _moe_ep(self, lw: LayerWeights, y: torch.Tensor):
         """Expert parallelism: tokens are split across ranks, each token's hidden row is
@@ -162,7 +166,7 @@ class GlmMoeDsaModel:
         return out
 
     # -- stack -----------------------------------------------------------------------------------
-    def _layer(self, layer: int, lw: LayerWeights, partial, residual, st, cache, first: bool):
+    def _layer(self, layer: int, lw: LayerWeights, partial, residual, st, cache, first: bool, last: bool = False):
         ops, comm = self.ops, self.comm
         if first:
             x, residual = ops.add_rmsnorm(partial, residual, lw.input_norm)
@@ -170,15 +174,17 @@ class GlmMoeDsaModel:
             x, residual = comm.allreduce_add_rmsnorm(ops, partial, residual, lw.input_norm, self.cfg.rms_norm_eps)
         attn = self.attention(layer, lw, x, st, cache)
         y, residual = comm.allreduce_add_rmsnorm(ops, attn, residual, lw.post_attn_norm, self.cfg.rms_norm_eps)
-        return self.mlp(lw, y), residual
+        return self.mlp(lw, y, final=last), residual
 
     def forward_hidden(self, st: StepState, cache: KVCacheTensors) -> torch.Tensor:
         """Token ids -> final-normed hidden states [T, H] (replicated on every rank)."""
         ops = self.ops
         partial, residual = ops.embed(st.input_ids, self.w.embed), None
         st.slots = st.lengths = None
-        for i in range(self.cfg.num_hidden_layers):
-            partial, residual = self._layer(i, self.w.layers[i], partial, residual, st, cache, first=(i == 0))
+        self.comm.begin_forward()
+        n = self.cfg.num_hidden_layers
+        for i in range(n):
+            partial, residual = self._layer(i, self.w.layers[i], partial, residual, st, cache, first=(i == 0), last=(i == n - 1))
         hidden, _ = self.comm.allreduce_add_rmsnorm(ops, partial, residual, self.w.final_norm, self.cfg.rms_norm_eps)
         return hidden
 
@@ -195,7 +201,8 @@ class GlmMoeDsaModel:
         e = ops.rmsnorm(ops.embed(st.input_ids, self.w.embed), lw.enorm)
         g = ops.rmsnorm(prev_hidden, lw.hnorm)
         z = ops.linear(torch.cat([e, g], dim=-1), lw.eh_proj)
-        partial, residual = self._layer(li, lw, z, None, st, cache, first=True)
+        self.comm.begin_forward()
+        partial, residual = self._layer(li, lw, z, None, st, cache, first=True, last=True)
         hidden, _ = self.comm.allreduce_add_rmsnorm(ops, partial, residual, lw.shared_head_norm, cfg.rms_norm_eps)
         return hidden
 

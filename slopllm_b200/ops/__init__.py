@@ -39,7 +39,7 @@ class RefOps:
     def add_rmsnorm(self, x, residual, w, eps=None):
         return R.add_rmsnorm(x, residual, w, self.cfg.rms_norm_eps if eps is None else eps)
 
-    def linear(self, x, w, out_f32: bool = False):
+    def linear(self, x, w, out_f32: bool = False, sink=None):
         return R.linear(x, w)
 
     def merge_attention_partials(self, o, lse):
@@ -108,7 +108,7 @@ class RefOps:
         return R.v_expand(o, w_v)
 
     # -- MLP ------------------------------------------------------------------------------------
-    def dense_mlp(self, x, lw):
+    def dense_mlp(self, x, lw, sink=None):
         return R.linear(R.silu_mul(R.linear(x, lw.mlp_w13)), lw.mlp_w2)
 
     def route(self, x, lw):
@@ -117,7 +117,7 @@ class RefOps:
         return R.moe_route(logits, lw.router_bias, c.num_experts_per_tok, c.n_group, c.topk_group,
                            c.norm_topk_prob, c.routed_scaling_factor)
 
-    def moe_tp(self, x, lw):
+    def moe_tp(self, x, lw, sink=None):
         """TP-sliced experts: every rank holds all experts' I/W slice; returns the partial sum
         (routed + shared) that the next all-reduce completes."""
         ids, w = self.route(x, lw)

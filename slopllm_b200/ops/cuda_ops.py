@@ -62,12 +62,27 @@ class CudaOps:
                int(x.dtype == torch.float32), N.stream())
         return out
 
-    def linear(self, x, w, out_f32: bool = False):
+    def linear(self, x, w, out_f32: bool = False, sink=None):
+        """y = x @ W^T.  With `sink` (a receive buffer on every rank) the fp32 result rows are
+        stored straight into the peers' memory by the producing kernel and the sink is returned."""
         x = self._bf16(x)
         if x.stride(-1) != 1:
             x = x.contiguous()
         T, K = x.shape
         Nn = w.out_features
+        if sink is not None:
+            sink.pushed_rows = T
+            if w.is_nvfp4 and K % 128 == 0 and x.stride(0) % 8 == 0:
+                xp = torch.empty(((T + 7) // 8) * 8 * K, dtype=torch.float16, device=x.device)
+                N.call("sl_linear_nvfp4_mma_push", x.data_ptr(), xp.data_ptr(), w.weight.data_ptr(), w.scale.data_ptr(),
+                       w.scale2.data_ptr(), T, Nn, K, x.stride(0), C.byref(sink.push), N.stream())
+                return sink
+            if not w.is_nvfp4 and x.stride(0) % 8 == 0 and K % 8 == 0:
+                from . import tcgen05
+                N.call("sl_linear_smallT_bf16_tcgen05_push", x.data_ptr(), w.weight.data_ptr(), T, Nn, K, x.stride(0),
+                       w.weight.stride(0), tcgen05.error_flag(x.device).data_ptr(), C.byref(sink.push), N.stream())
+                return sink
+            return sink.push_tensor(self.linear(x, w, out_f32=True))
         if T > DECODE_MAX_T:
             from .gemm import gemm_large
             return gemm_large(x, w, out_f32)
@@ -197,15 +212,20 @@ class CudaOps:
         N.call("sl_sparse_mla_split_mma" if c_ok else "sl_sparse_mla_split", C.byref(p), T, N.stream())
         return o_part, lse_part
 
-    def combine(self, o_parts, lse_parts, head_begin=0, head_count=None, want_lse=True):
-        """o_parts: list of [T, h, S, R] fp32 buffers (one per rank under CP)."""
+    def combine_f32(self, o_parts, lse_parts):
+        return self.combine(o_parts, lse_parts, out_f32=True)
+
+    def combine(self, o_parts, lse_parts, head_begin=0, head_count=None, want_lse=True, rows=None, out_f32=False):
+        """o_parts: list of [T, h, S, R] fp32 buffers (one per rank under CP); `rows` limits the
+        token rows processed when the buffers are staging areas with spare capacity."""
         T, h, S, Rr = o_parts[0].shape
+        T = T if rows is None else rows
         head_count = h if head_count is None else head_count
         dev = o_parts[0].device
-        o = torch.empty(T, head_count, Rr, dtype=torch.bfloat16, device=dev)
+        o = torch.empty(T, head_count, Rr, dtype=torch.float32 if out_f32 else torch.bfloat16, device=dev)
         lse = torch.empty(T, head_count, dtype=torch.float32, device=dev) if want_lse else None
         p = N.CombineParams(n_buf=len(o_parts), parts_per_buf=S, h=h, R=Rr, head_begin=head_begin, head_count=head_count,
-                            o_out=o.data_ptr(), lse_out=N.ptr(lse))
+                            o_out=o.data_ptr(), lse_out=N.ptr(lse), out_f32=int(out_f32))
         for i, (a, b) in enumerate(zip(o_parts, lse_parts)):
             p.o_ptrs[i] = a.data_ptr()
             p.lse_ptrs[i] = b.data_ptr()
@@ -225,12 +245,14 @@ class CudaOps:
         return out
 
     # -- MLP --------------------------------------------------------------------------------------
-    def dense_mlp(self, x, lw):
+    def dense_mlp(self, x, lw, sink=None):
         gu = self.linear(x, lw.mlp_w13)
+        if gu.stride(0) != gu.shape[1]:
+            gu = gu.contiguous()
         T, I2 = gu.shape
         act = torch.empty(T, I2 // 2, dtype=torch.bfloat16, device=x.device)
         N.call("sl_silu_mul", act.data_ptr(), gu.data_ptr(), T, I2 // 2, N.stream())
-        return self.linear(act, lw.mlp_w2, out_f32=True)
+        return self.linear(act, lw.mlp_w2, out_f32=True, sink=sink)
 
     def route(self, x, lw):
         c = self.cfg
@@ -248,7 +270,7 @@ class CudaOps:
         from ..models.weights import LinearWeight
         return self.linear(x, LinearWeight(lw.router_w), out_f32=True)
 
-    def _moe_small(self, x, experts, shared, ids, wts):
+    def _moe_small(self, x, experts, shared, ids, wts, sink=None):
         """Weight-streaming MoE for a few token rows: gate/up + SiLU·mul per route, then
         down-projection fused with the routing-weighted sum (and the shared expert)."""
         x = self._bf16(x)
@@ -269,18 +291,23 @@ class CudaOps:
                              w2=experts.w2.data_ptr(), s2=experts.s2.data_ptr(), g2=experts.g2.data_ptr(),
                              sw2=N.ptr(shared.w2) if shared else 0, ss2=N.ptr(shared.s2) if shared else 0,
                              sg2=N.ptr(shared.g2) if shared else 0, out=out.data_ptr(), out_f32=1, accumulate=0)
+        if sink is not None:
+            sink.pushed_rows = T
+            N.call("sl_moe_down_push", C.byref(dp), C.byref(sink.push), N.stream())
+            return sink
         N.call("sl_moe_down", C.byref(dp), N.stream())
         return out
 
-    def moe_tp(self, x, lw):
+    def moe_tp(self, x, lw, sink=None):
         ids, wts = self.route(x, lw)
         if x.shape[0] <= DECODE_MAX_T and lw.experts.is_nvfp4:
             if lw.shared is not None and lw.shared.inter != lw.experts.inter:
-                out = self._moe_small(x, lw.experts, None, ids, wts)
-                return out + self.shared_expert(x, lw)
-            return self._moe_small(x, lw.experts, lw.shared, ids, wts)
+                out = self._moe_small(x, lw.experts, None, ids, wts) + self.shared_expert(x, lw)
+                return out if sink is None else sink.push_tensor(out)
+            return self._moe_small(x, lw.experts, lw.shared, ids, wts, sink)
         from .gemm import moe_large
-        return moe_large(self, x, lw.experts, lw.shared, ids, wts)
+        out = moe_large(self, x, lw.experts, lw.shared, ids, wts)
+        return out if sink is None else sink.push_tensor(out)
 
     def moe_local_experts(self, x, experts, ids, w):
         ids = ids.to(torch.int32).contiguous()

@@ -94,7 +94,7 @@ class SparseMlaParams(C.Structure):
 
 class CombineParams(C.Structure):
     _fields_ = [("o_ptrs", vp * 8), ("lse_ptrs", vp * 8), ("n_buf", i32), ("parts_per_buf", i32), ("h", i32), ("R", i32),
-                ("head_begin", i32), ("head_count", i32), ("o_out", vp), ("lse_out", vp)]
+                ("head_begin", i32), ("head_count", i32), ("o_out", vp), ("lse_out", vp), ("out_f32", i32)]
 
 
 class MoeGateUpParams(C.Structure):

@@ -126,6 +126,18 @@ class Comm:
     def check_status(self) -> None:
         """Raise if a device-side bounded wait expired (library collectives have none)."""
 
+    def begin_forward(self) -> None:
+        """Called at the start of every forward pass (fused communicators rotate buffers)."""
+
+    def partial_sink(self, rows: int, final: bool = False):
+        """Where a partial-sum producer should put its result: None = return a tensor."""
+        return None
+
+    def cp_merge_partials(self, ops, o_part, lse_part):
+        """Merge this rank's split partials across ranks; returns this rank's head slice."""
+        o, lse = ops.combine([o_part], [lse_part])
+        return self.cp_merge_heads(ops, o, lse)
+
     # -- fused-op shaped interface (overridden by the NVLink kernels) -------------------------
     def allreduce_add_rmsnorm(self, ops, partial, residual, weight, eps):
         """sum over ranks of `partial`, add to `residual`, RMSNorm.  Returns (normed, residual')."""

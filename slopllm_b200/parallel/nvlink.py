@@ -1,0 +1,278 @@
+"""In-kernel NVLink / NVSwitch collectives over symmetric peer memory.
+
+Every rank allocates the same symmetric buffer (`torch.distributed._symmetric_memory`: CUDA VMM
+allocations whose handles are exchanged over the process group, every peer mapped into every
+rank's address space).  Kernels then move data themselves:
+
+* fused all-reduce + residual add + RMSNorm: the *producing* kernel (NVFP4 / bf16 linear, MoE
+  down-projection) stores its fp32 partial rows directly into each rank's receive slot and
+  publishes an epoch flag; the *consuming* kernel waits for the flags (bounded), sums the
+  slots in rank order, adds the residual and normalises.  No NCCL call, no separate copy.
+* context-parallel attention merge and all-gathers by peer stores (`sl_cp_merge_push`,
+  `sl_gather_push`).
+
+Three receive buffers rotate A, B, A, B, ..., C within one forward pass (C = the final norm),
+so a rank can never overwrite a slot that a slower peer is still reading: between two uses of
+the same buffer every rank has passed a wait that needs all peers' later flags.
+
+Plain peer loads/stores only (no multimem, no TMA multicast).  `Comm` (NCCL) stays available as
+the fallback and A/B baseline (`fused=False`).  Reference: `csrc/glm_p2p.cu`,
+`src/parallel_ops.ts:246-324, 2912-2975`.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..ops import native as N
+from .dist import Comm, ParallelContext
+
+MAX_RANKS = 8
+vp, i32, u32 = C.c_void_p, C.c_int, C.c_uint32
+
+
+class PushCtx(C.Structure):
+    _fields_ = [("bufs", vp * MAX_RANKS), ("flags", vp * MAX_RANKS), ("epoch", vp), ("block_counter", vp),
+                ("rank", i32), ("world", i32), ("slot_rows", i32), ("row_len", i32)]
+
+
+class RecvCtx(C.Structure):
+    _fields_ = [("buf", vp), ("flags", vp), ("epoch", vp), ("done_counter", vp), ("status", vp), ("world", i32),
+                ("slot_rows", i32), ("row_len", i32), ("max_spins", u32)]
+
+
+class CpPushCtx(C.Structure):
+    _fields_ = [("o_stage", vp * MAX_RANKS), ("lse_stage", vp * MAX_RANKS), ("flags", vp * MAX_RANKS), ("epoch", vp),
+                ("block_counter", vp), ("rank", i32), ("world", i32), ("Tmax", i32), ("h", i32), ("hl", i32), ("R", i32)]
+
+
+class GatherPushCtx(C.Structure):
+    _fields_ = [("bufs", vp * MAX_RANKS), ("flags", vp * MAX_RANKS), ("epoch", vp), ("block_counter", vp), ("rank", i32),
+                ("world", i32), ("slot_bytes", C.c_size_t)]
+
+
+N._SIGS.update({
+    "sl_ar_add_rmsnorm": [C.POINTER(RecvCtx), vp, vp, vp, vp, i32, i32, C.c_float, vp],
+    "sl_push_rows": [C.POINTER(PushCtx), vp, i32, i32, vp],
+    "sl_flag_barrier": [C.POINTER(vp), vp, i32, i32, u32, u32, vp, vp],
+    "sl_wait_flag": [vp, u32, u32, vp, vp],
+    "sl_cp_merge_push": [C.POINTER(CpPushCtx), vp, vp, i32, vp],
+    "sl_epoch_wait": [vp, vp, i32, u32, vp, i32, vp],
+    "sl_gather_push": [C.POINTER(GatherPushCtx), vp, C.c_size_t, vp],
+    "sl_linear_nvfp4_mma_push": [vp, vp, vp, vp, vp, i32, i32, i32, i32, C.POINTER(PushCtx), vp],
+    "sl_moe_down_push": [C.POINTER(N.MoeDownParams), C.POINTER(PushCtx), vp],
+    "sl_linear_smallT_bf16_tcgen05_push": [vp, vp, i32, i32, i32, i32, i32, vp, C.POINTER(PushCtx), vp],
+})
+
+
+class CollectiveTimeout(RuntimeError):
+    """A device-side bounded wait expired (a peer did not publish its flag in time)."""
+
+
+class PushSink:
+    """Destination of one partial-sum producer: a rotating receive buffer on every rank."""
+
+    def __init__(self, owner: "SymmetricRegion", index: int):
+        self.owner = owner
+        self.index = index
+        self.push = owner.push_ctx[index]
+        self.pushed_rows = 0
+
+    def push_tensor(self, x: torch.Tensor) -> "PushSink":
+        """Fallback for producers without a fused epilogue: push an fp32 [T, N] tensor."""
+        x = x.to(torch.float32).contiguous()
+        N.call("sl_push_rows", C.byref(self.push), x.data_ptr(), x.shape[0], x.shape[1], N.stream())
+        self.pushed_rows = x.shape[0]
+        return self
+
+
+class SymmetricRegion:
+    """Symmetric receive buffers + flags, and this rank's local epoch / counter words.
+
+    `peer_ptrs[r]` is the address at which rank r's copy of the region is mapped here.  In tests
+    that emulate W ranks on one GPU, W regions are plain allocations on the same device and
+    every "rank" gets the same pointer table.
+    """
+
+    NUM_BUFS = 3
+
+    def __init__(self, rank: int, world: int, slot_rows: int, row_len: int, local: torch.Tensor, peer_ptrs: List[int],
+                 gather_bytes: int = 0, cp_shape=None, wait_spins: int = 4_000_000):
+        assert world <= MAX_RANKS
+        self.rank, self.world, self.slot_rows, self.row_len = rank, world, slot_rows, row_len
+        self.local = local
+        self.peer_ptrs = peer_ptrs
+        dev = local.device
+        self.state = torch.zeros(64, dtype=torch.int32, device=dev)      # epochs, counters, status
+        self.wait_spins = wait_spins
+        lay = self.layout(world, slot_rows, row_len, gather_bytes, cp_shape)
+        self.lay = lay
+        st = self.state.data_ptr()
+        self.status_ptr = st + 4 * 48
+        self.push_ctx, self.recv_ctx = [], []
+        for b in range(self.NUM_BUFS):
+            pc = PushCtx(epoch=st + 4 * b, block_counter=st + 4 * (8 + b), rank=rank, world=world, slot_rows=slot_rows,
+                         row_len=row_len)
+            for r in range(world):
+                pc.bufs[r] = peer_ptrs[r] + lay["data"][b]
+                pc.flags[r] = peer_ptrs[r] + lay["flags"][b]
+            self.push_ctx.append(pc)
+            self.recv_ctx.append(RecvCtx(buf=peer_ptrs[rank] + lay["data"][b], flags=peer_ptrs[rank] + lay["flags"][b],
+                                         epoch=st + 4 * b, done_counter=st + 4 * (16 + b), status=self.status_ptr, world=world,
+                                         slot_rows=slot_rows, row_len=row_len, max_spins=wait_spins))
+        # generic gather (slot 3) and CP merge (slot 4) use their own flags / epochs
+        self.gather_ctx = None
+        if gather_bytes:
+            g = GatherPushCtx(epoch=st + 4 * 3, block_counter=st + 4 * (8 + 3), rank=rank, world=world,
+                              slot_bytes=gather_bytes)
+            for r in range(world):
+                g.bufs[r] = peer_ptrs[r] + lay["gather"]
+                g.flags[r] = peer_ptrs[r] + lay["flags"][3]
+            self.gather_ctx = g
+        self.cp_ctx = None
+        if cp_shape is not None:
+            Tmax, h, R = cp_shape
+            hl = h // world
+            cpc = CpPushCtx(epoch=st + 4 * 4, block_counter=st + 4 * (8 + 4), rank=rank, world=world, Tmax=Tmax, h=h, hl=hl, R=R)
+            for r in range(world):
+                cpc.o_stage[r] = peer_ptrs[r] + lay["cp_o"]
+                cpc.lse_stage[r] = peer_ptrs[r] + lay["cp_lse"]
+                cpc.flags[r] = peer_ptrs[r] + lay["flags"][4]
+            self.cp_ctx = cpc
+        self.cp_shape = cp_shape
+        self.gather_bytes = gather_bytes
+
+    @classmethod
+    def layout(cls, world, slot_rows, row_len, gather_bytes=0, cp_shape=None) -> dict:
+        off = 0
+
+        def take(n):
+            nonlocal off
+            o = off
+            off += (n + 255) // 256 * 256
+            return o
+        lay = {"flags": [take(4 * MAX_RANKS * 2) for _ in range(8)], "data": []}
+        for _ in range(cls.NUM_BUFS):
+            lay["data"].append(take(world * slot_rows * row_len * 4))
+        lay["gather"] = take(world * gather_bytes) if gather_bytes else 0
+        if cp_shape is not None:
+            Tmax, h, R = cp_shape
+            hl = h // world
+            lay["cp_o"] = take(world * Tmax * hl * R * 4)
+            lay["cp_lse"] = take(world * Tmax * hl * 4)
+        lay["total"] = off
+        return lay
+
+    def local_view(self, offset: int, nbytes: int) -> torch.Tensor:
+        return self.local[offset:offset + nbytes]
+
+    def check_status(self) -> None:
+        st = self.state[48:52].tolist()
+        if st[0]:
+            self.state[48:52].zero_()
+            raise CollectiveTimeout(f"rank {self.rank}: device wait expired at site {st[1]} (expected flag {st[2]}, saw {st[3]})")
+
+
+class NvlinkComm(Comm):
+    """Communicator whose hot collectives run inside our kernels over peer memory."""
+
+    MAX_ROWS = 32          # token rows served by the fused decode path; larger steps use NCCL
+
+    def __init__(self, ctx: ParallelContext, cfg=None, region: Optional[SymmetricRegion] = None):
+        super().__init__(ctx)
+        self.cfg = cfg
+        self._toggle = 0
+        self.region = region or self._make_region(ctx, cfg)
+
+    @staticmethod
+    def _make_region(ctx: ParallelContext, cfg) -> SymmetricRegion:
+        import torch.distributed._symmetric_memory as symm
+        H = cfg.hidden_size
+        cp_shape = (NvlinkComm.MAX_ROWS, cfg.num_attention_heads, cfg.kv_lora_rank) if ctx.cp else None
+        gather_bytes = 1 << 20
+        lay = SymmetricRegion.layout(ctx.world, NvlinkComm.MAX_ROWS, H, gather_bytes, cp_shape)
+        buf = symm.empty(lay["total"], dtype=torch.uint8, device=ctx.device)
+        buf.zero_()
+        hdl = symm.rendezvous(buf, group=dist.group.WORLD)
+        ptrs = [int(p) for p in hdl.buffer_ptrs]
+        torch.cuda.synchronize()
+        dist.barrier()
+        region = SymmetricRegion(ctx.rank, ctx.world, NvlinkComm.MAX_ROWS, H, buf, ptrs, gather_bytes, cp_shape)
+        region._handle = hdl
+        return region
+
+    # -- rotation -----------------------------------------------------------------------------
+    def begin_forward(self) -> None:
+        self._toggle = 0
+
+    def partial_sink(self, rows: int, final: bool = False) -> Optional[PushSink]:
+        if rows > self.MAX_ROWS:
+            return None
+        if final:
+            return PushSink(self.region, 2)
+        s = PushSink(self.region, self._toggle)
+        self._toggle ^= 1
+        return s
+
+    # -- fused all-reduce consumer ----------------------------------------------------------------
+    def allreduce_add_rmsnorm(self, ops, partial, residual, weight, eps):
+        if not isinstance(partial, PushSink):
+            return super().allreduce_add_rmsnorm(ops, partial, residual, weight, eps)
+        T, H = partial.pushed_rows, self.region.row_len
+        dev = self.ctx.device
+        out = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+        res = torch.empty(T, H, dtype=torch.float32, device=dev)
+        rc = self.region.recv_ctx[partial.index]
+        N.call("sl_ar_add_rmsnorm", C.byref(rc), out.data_ptr(), res.data_ptr(), N.ptr(residual), weight.data_ptr(), T, H,
+               float(eps), N.stream())
+        return out, res
+
+    # -- all-gather by peer stores -------------------------------------------------------------------
+    def all_gather_list(self, x: torch.Tensor) -> List[torch.Tensor]:
+        g = self.region.gather_ctx
+        nbytes = x.numel() * x.element_size()
+        if g is None or nbytes % 16 != 0 or nbytes > self.region.gather_bytes or self.ctx.world == 1:
+            return super().all_gather_list(x)
+        x = x.contiguous()
+        N.call("sl_gather_push", C.byref(g), x.data_ptr(), nbytes, N.stream())
+        W = self.ctx.world
+        rg = self.region
+        N.call("sl_epoch_wait", rg.peer_ptrs[rg.rank] + rg.lay["flags"][3], rg.state.data_ptr() + 4 * 3, W, rg.wait_spins,
+               rg.status_ptr, 4, N.stream())
+        parts = []
+        for r in range(W):
+            raw = rg.local_view(rg.lay["gather"] + r * rg.gather_bytes, nbytes)
+            parts.append(raw.view(x.dtype).view(x.shape).clone())
+        return parts
+
+    def all_gather(self, x: torch.Tensor, dim: int = -1) -> torch.Tensor:
+        if self.ctx.world == 1:
+            return x
+        return torch.cat(self.all_gather_list(x), dim=dim)
+
+    # -- context-parallel merge -----------------------------------------------------------------------
+    def cp_merge_partials(self, ops, o_part: torch.Tensor, lse_part: torch.Tensor):
+        """o_part [T, h, S, R] / lse_part [T, h, S]: this rank's split partials over its KV shard.
+        Returns the merged output for this rank's heads, bf16 [T, h/W, R]."""
+        rg = self.region
+        T, h, S, R = o_part.shape
+        W, r = self.ctx.world, self.ctx.rank
+        if rg.cp_ctx is None or T > rg.cp_shape[0]:
+            o, lse = ops.combine([o_part], [lse_part])
+            return super().cp_merge_heads(ops, o, lse)
+        # local combine over the splits (fp32 out is needed for the exchange): reuse combine with fp32 via torch
+        o, lse = ops.combine_f32([o_part], [lse_part])
+        N.call("sl_cp_merge_push", C.byref(rg.cp_ctx), o.data_ptr(), lse.data_ptr(), T, N.stream())
+        N.call("sl_epoch_wait", rg.peer_ptrs[r] + rg.lay["flags"][4], rg.state.data_ptr() + 4 * 4, W, rg.wait_spins,
+               rg.status_ptr, 5, N.stream())
+        Tmax, hl = rg.cp_shape[0], h // W
+        stage_o = rg.local_view(rg.lay["cp_o"], W * Tmax * hl * R * 4).view(torch.float32).view(W, Tmax, hl, 1, R)
+        stage_l = rg.local_view(rg.lay["cp_lse"], W * Tmax * hl * 4).view(torch.float32).view(W, Tmax, hl, 1)
+        merged, _ = ops.combine([stage_o[i] for i in range(W)], [stage_l[i] for i in range(W)], rows=T, want_lse=False)
+        return merged
+
+    def check_status(self) -> None:
+        self.region.check_status()
