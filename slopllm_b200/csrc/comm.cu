@@ -17,6 +17,7 @@
 // Every wait is bounded: on expiry the kernel records {code, site, expected, observed} in a
 // status word block and finishes normally.
 #include "push.cuh"
+#include <cstring>
 
 struct RecvCtx {
     const float* buf;          // this rank's receive buffer [world][slot_rows][row_len]
@@ -243,4 +244,43 @@ SL_API int sl_gather_push(const GatherPushCtx* c, const void* src, size_t bytes,
     if (blocks > 148) blocks = 148;
     gather_push_kernel<<<blocks, 256, 0, s>>>(*c, (const uint4*)src, n16);
     return SL_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------------------------------------
+// Peer mapping of the symmetric region through CUDA IPC (one process per GPU on one node).
+// Every rank exports the allocation that holds its region, the 64-byte handles travel over the
+// process group, every rank opens the others' handles (peer access is enabled lazily by the
+// open).  Reference: `glm_cuda_ipc_get/open/close_mem_handle` (`csrc/glm_device.cpp`),
+// `glm_p2p_enable_peer_access` (`csrc/glm_p2p.cu:723-744`).
+#include <cuda.h>
+
+typedef CUresult (*PFN_getAddressRange)(CUdeviceptr*, size_t*, CUdeviceptr);
+
+SL_API int sl_ipc_export(const void* ptr, void* handle_out, unsigned long long* offset_out) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &fn, cudaEnableDefault, &q) != cudaSuccess || fn == nullptr) return -100;
+    CUdeviceptr base = 0;
+    size_t size = 0;
+    if (((PFN_getAddressRange)fn)(&base, &size, (CUdeviceptr)ptr) != CUDA_SUCCESS) return -101;
+    cudaIpcMemHandle_t h;
+    const cudaError_t e = cudaIpcGetMemHandle(&h, (void*)base);
+    if (e != cudaSuccess) return (int)e;
+    memcpy(handle_out, &h, sizeof(h));
+    *offset_out = (unsigned long long)((CUdeviceptr)ptr - base);
+    return 0;
+}
+
+SL_API int sl_ipc_open(const void* handle, unsigned long long offset, void** ptr_out) {
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, sizeof(h));
+    void* base = nullptr;
+    const cudaError_t e = cudaIpcOpenMemHandle(&base, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) return (int)e;
+    *ptr_out = (char*)base + offset;
+    return 0;
+}
+
+SL_API int sl_ipc_close(void* ptr, unsigned long long offset) {
+    return (int)cudaIpcCloseMemHandle((char*)ptr - offset);
 }

@@ -94,7 +94,8 @@ struct SampleParams {
     const int* top_k;                    // [B] (<= 0: max_k)
     const int64_t* history; const int* hist_len; int window;             // [B, window]
     int max_k;                           // candidate capacity (<= 64)
-    uint32_t counter, stream;
+    const uint32_t* counter;             // device word: RNG counter (advanced by sl_advance_counter)
+    uint32_t stream;
     const int* row_ids;                  // RNG row id per batch row (null = row index)
     int64_t* out_token;                  // [B]
     int64_t* cand_ids; float* cand_probs;                                 // [B, max_k] or null
@@ -208,7 +209,7 @@ __global__ void __launch_bounds__(1024) sample_kernel(SampleParams p) {
         }
         for (int j = 0; j < nk; ++j) probs[j] /= kept;
         const uint32_t row = p.row_ids ? (uint32_t)p.row_ids[b] : (uint32_t)b;
-        const double u = uniform_from_counter(p.counter, row, p.stream);
+        const double u = uniform_from_counter(*p.counter, row, p.stream);
         double c = 0.0; int pick = nk - 1;
         for (int j = 0; j < nk; ++j) { c += (double)probs[j]; if (u < c) { pick = j; break; } }
         p.out_token[b] = sidx[pick];
@@ -235,7 +236,7 @@ struct SpecRejectParams {
     const int64_t* draft_ids; const float* draft_probs;              // [B, D, C]
     const int64_t* target_ids; const float* target_probs;            // [B, D+1, C]
     int D, C;
-    uint32_t counter;
+    const uint32_t* counter;
     int64_t* out_tokens;                                             // [B, D+1] (-1 padded)
     int* num_accepted;                                               // [B]
 };
@@ -265,7 +266,7 @@ __global__ void spec_reject_kernel(SpecRejectParams p, int B) {
         const float* dp = p.draft_probs + ((size_t)b * D + i) * C;
         float pt = 0.f, pd = 0.f;
         for (int c = 0; c < C; ++c) { if (tid_[c] == x) pt += tp[c]; if (did[c] == x) pd += dp[c]; }
-        const double ua = uniform_from_counter(p.counter, (uint32_t)b, 2u * i + 1u);
+        const double ua = uniform_from_counter(*p.counter, (uint32_t)b, 2u * i + 1u);
         if (pd > 0.f && ua < (double)fminf(1.f, pt / pd)) {
             p.out_tokens[(size_t)b * (D + 1) + i] = x;
             continue;
@@ -280,14 +281,14 @@ __global__ void spec_reject_kernel(SpecRejectParams p, int B) {
         }
         if (rs <= 0.f) for (int c = 0; c < C; ++c) res[c] = tp[c];
         int64_t tok;
-        pick_from(tid_, res, C, uniform_from_counter(p.counter, (uint32_t)b, 2u * i + 2u), &tok);
+        pick_from(tid_, res, C, uniform_from_counter(*p.counter, (uint32_t)b, 2u * i + 2u), &tok);
         p.out_tokens[(size_t)b * (D + 1) + i] = tok;
         break;
     }
     if (i == D) {
         int64_t tok;
         pick_from(p.target_ids + ((size_t)b * (D + 1) + D) * C, p.target_probs + ((size_t)b * (D + 1) + D) * C, C,
-                  uniform_from_counter(p.counter, (uint32_t)b, 2u * D + 2u), &tok);
+                  uniform_from_counter(*p.counter, (uint32_t)b, 2u * D + 2u), &tok);
         p.out_tokens[(size_t)b * (D + 1) + D] = tok;
     }
     p.num_accepted[b] = i;
@@ -297,5 +298,12 @@ SL_API int sl_spec_reject(const SpecRejectParams* p, int B, cudaStream_t s) {
     if (B == 0) return 0;
     if (p->C > SL_MAX_CAND) return -1;
     spec_reject_kernel<<<(B + 63) / 64, 64, 0, s>>>(*p, B);
+    return SL_LAUNCH_CHECK();
+}
+
+// RNG counter += inc (one thread; keeps graph replays from repeating random numbers).
+__global__ void advance_counter_kernel(uint32_t* counter, uint32_t inc) { *counter += inc; }
+SL_API int sl_advance_counter(void* counter, unsigned inc, cudaStream_t s) {
+    advance_counter_kernel<<<1, 1, 0, s>>>((uint32_t*)counter, inc);
     return SL_LAUNCH_CHECK();
 }

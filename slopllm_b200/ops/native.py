@@ -112,13 +112,13 @@ class MoeDownParams(C.Structure):
 class SampleParams(C.Structure):
     _fields_ = [("logits", vp), ("V", i32), ("ld", i32), ("temperature", vp), ("top_p", vp), ("rep_penalty", vp),
                 ("presence_penalty", vp), ("top_k", vp), ("history", vp), ("hist_len", vp), ("window", i32),
-                ("max_k", i32), ("counter", u32), ("stream", u32), ("row_ids", vp), ("out_token", vp), ("cand_ids", vp),
+                ("max_k", i32), ("counter", vp), ("stream", u32), ("row_ids", vp), ("out_token", vp), ("cand_ids", vp),
                 ("cand_probs", vp)]
 
 
 class SpecRejectParams(C.Structure):
     _fields_ = [("draft_tokens", vp), ("draft_ids", vp), ("draft_probs", vp), ("target_ids", vp), ("target_probs", vp),
-                ("D", i32), ("C", i32), ("counter", u32), ("out_tokens", vp), ("num_accepted", vp)]
+                ("D", i32), ("C", i32), ("counter", vp), ("out_tokens", vp), ("num_accepted", vp)]
 
 
 # ---- function signatures ----------------------------------------------------------------------------------
@@ -145,6 +145,7 @@ _SIGS = {
     "sl_argmax": [vp, vp, i32, i32, i32, i32, i64, vp, vp, vp, vp],
     "sl_sample": [C.POINTER(SampleParams), i32, vp],
     "sl_spec_reject": [C.POINTER(SpecRejectParams), i32, vp],
+    "sl_advance_counter": [vp, u32, vp],
     "sl_linear_nvfp4_mma": [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp],
     "sl_linear_smallT_bf16_tcgen05": [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp, vp],
     "sl_gemm_bf16_tcgen05": [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp, i32, vp],

@@ -189,19 +189,47 @@ class NvlinkComm(Comm):
 
     @staticmethod
     def _make_region(ctx: ParallelContext, cfg) -> SymmetricRegion:
-        import torch.distributed._symmetric_memory as symm
+        """Allocate this rank's region, exchange CUDA IPC handles over the process group and map
+        every peer's region (`SLOPLLM_B200_SYMM=torch` uses torch's symmetric-memory rendezvous
+        instead)."""
+        from ..config import env_str
         H = cfg.hidden_size
         cp_shape = (NvlinkComm.MAX_ROWS, cfg.num_attention_heads, cfg.kv_lora_rank) if ctx.cp else None
         gather_bytes = 1 << 20
         lay = SymmetricRegion.layout(ctx.world, NvlinkComm.MAX_ROWS, H, gather_bytes, cp_shape)
-        buf = symm.empty(lay["total"], dtype=torch.uint8, device=ctx.device)
-        buf.zero_()
-        hdl = symm.rendezvous(buf, group=dist.group.WORLD)
-        ptrs = [int(p) for p in hdl.buffer_ptrs]
+        if env_str("SYMM") == "torch":
+            import torch.distributed._symmetric_memory as symm
+            buf = symm.empty(lay["total"], dtype=torch.uint8, device=ctx.device)
+            buf.zero_()
+            hdl = symm.rendezvous(buf, group=dist.group.WORLD)
+            ptrs = [int(p) for p in hdl.buffer_ptrs]
+            keep = hdl
+        else:
+            buf = torch.zeros(lay["total"], dtype=torch.uint8, device=ctx.device)
+            torch.cuda.synchronize()
+            handle = (C.c_ubyte * 64)()
+            offset = C.c_ulonglong(0)
+            lib = N.kernels()
+            lib.sl_ipc_export.argtypes = [vp, vp, C.POINTER(C.c_ulonglong)]
+            lib.sl_ipc_open.argtypes = [vp, C.c_ulonglong, C.POINTER(vp)]
+            N.check(lib.sl_ipc_export(buf.data_ptr(), handle, C.byref(offset)), "sl_ipc_export")
+            mine = (bytes(handle), int(offset.value))
+            everyone = [None] * ctx.world
+            dist.all_gather_object(everyone, mine)
+            ptrs = []
+            for r, (hb, off) in enumerate(everyone):
+                if r == ctx.rank:
+                    ptrs.append(buf.data_ptr())
+                    continue
+                out = vp()
+                hbuf = (C.c_ubyte * 64).from_buffer_copy(hb)
+                N.check(lib.sl_ipc_open(hbuf, off, C.byref(out)), f"sl_ipc_open(rank {r})")
+                ptrs.append(int(out.value))
+            keep = everyone
         torch.cuda.synchronize()
         dist.barrier()
         region = SymmetricRegion(ctx.rank, ctx.world, NvlinkComm.MAX_ROWS, H, buf, ptrs, gather_bytes, cp_shape)
-        region._handle = hdl
+        region._keep = keep
         return region
 
     # -- rotation -----------------------------------------------------------------------------

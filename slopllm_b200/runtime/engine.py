@@ -51,7 +51,7 @@ class StepBuffers:
 
 class Engine:
     def __init__(self, cfg: GlmMoeDsaConfig, model: GlmMoeDsaModel, num_pages: int, max_batch: int = 8,
-                 max_seq_len: int = 16384, cuda_graph: bool = True, mtp: int = 0):
+                 max_seq_len: int = 16384, cuda_graph: bool = True, mtp: int = 0, sampler=None):
         self.cfg = cfg
         self.model = model
         self.ctx: ParallelContext = model.ctx
@@ -62,6 +62,7 @@ class Engine:
         self.pt_width = -(-max_seq_len // (PAGE_SIZE * self.ctx.cp_world)) + 1
         self.graphs = CaptureManager(enabled=cuda_graph and self.device.type == "cuda")
         self.mtp = mtp
+        self.sampler = sampler               # SamplingWorkspace (row b of a step <-> workspace row rows[b])
         self._bufs = {}
         self._out_host = {}
         self.h2d_bytes = 0
@@ -100,16 +101,19 @@ class Engine:
 
     # ---- prefill -------------------------------------------------------------------------------------------
     def prefill(self, seqs: Seq[Sequence], prompts: Seq[Seq[int]], chunk_size: int = 8192,
-                want_hidden: bool = False):
-        """Chunked prefill of each prompt's uncached tail.  Returns (next token per sequence
-        (greedy), last hidden per sequence or None).  Sequences are processed one after the
-        other in chunks of at most `chunk_size` tokens (page-aligned boundaries)."""
+                want_hidden: bool = False, rows: Optional[Seq[int]] = None, limits: Optional[Seq[int]] = None):
+        """Chunked prefill of each prompt's uncached tail (up to `limits[b]` tokens when given:
+        the scheduler spreads a long prompt over several steps).  Returns (next token per
+        sequence, last hidden per sequence or None); the token is meaningful only for
+        sequences whose whole prompt is now cached.  Sequences are processed one after the
+        other in chunks of at most `chunk_size` tokens."""
         tokens, hiddens = [], []
-        for s, prompt in zip(seqs, prompts):
+        for b, (s, prompt) in enumerate(zip(seqs, prompts)):
             start = s.length
             last_hidden = None
-            while start < len(prompt):
-                n = min(chunk_size, len(prompt) - start)
+            upto = len(prompt) if limits is None else min(len(prompt), limits[b])
+            while start < upto:
+                n = min(chunk_size, upto - start)
                 ids = list(prompt[start:start + n])
                 self.kv.append_tokens(s, ids)
                 positions = list(range(start, start + n))
@@ -120,8 +124,15 @@ class Engine:
                 self.kv.report_tokens(s)
                 last_hidden = hidden[-1:]
                 start += n
-            logits = self.model.compute_logits(last_hidden)
-            tokens.append(int(logits.argmax(-1)))
+            if upto < len(prompt) or last_hidden is None:
+                tokens.append(-1)
+                hiddens.append(last_hidden)
+                continue
+            row = None if rows is None else rows[b]
+            if row is not None and self.sampler is not None and not self.sampler.all_greedy([row]):
+                tokens.append(int(self._select(last_hidden, [row])[0]))
+            else:
+                tokens.append(int(self._greedy(last_hidden)[0]))
             hiddens.append(last_hidden)
         return tokens, (hiddens if want_hidden else None)
 
@@ -146,10 +157,13 @@ class Engine:
                          max_kv_len=max_kv_len)
 
     # ---- plain decode -----------------------------------------------------------------------------------------
-    def decode_step(self, seqs: Seq[Sequence], last_tokens: Seq[int]) -> List[int]:
-        """One token per sequence: append `last_tokens`, run the model, return the next
-        (greedy) tokens.  Graph-captured per (batch, KV bucket)."""
+    def decode_step(self, seqs: Seq[Sequence], last_tokens: Seq[int], rows: Optional[Seq[int]] = None) -> List[int]:
+        """One token per sequence: append `last_tokens`, run the model, return the next tokens
+        (greedy, or drawn by the sampling workspace for its `rows`).  Graph-captured per
+        (batch, KV bucket, sampling mode)."""
         B = len(seqs)
+        rows = list(range(B)) if rows is None else list(rows)
+        sampled = self.sampler is not None and not self.sampler.all_greedy(rows)
         positions = []
         for s, t in zip(seqs, last_tokens):
             positions.append(s.length)
@@ -161,13 +175,24 @@ class Engine:
 
         def run():
             hidden = self.model.forward_hidden(st, self.cache)
-            return self._greedy(hidden)
+            return self._select(hidden, rows if sampled else None)
 
-        out = self.graphs.execute(("decode", B, bucket), run)
+        out = self.graphs.execute(("decode", B, bucket, tuple(rows) if sampled else None), run)
         host = self._readback(("decode", B), out)
         for s in seqs:
             self.kv.report_tokens(s)
-        return host.tolist()
+        toks = host.tolist()
+        if sampled and self.sampler.uses_penalties(rows):
+            self.sampler.record(rows, toks)
+        return toks
+
+    def _select(self, hidden: torch.Tensor, rows: Optional[Seq[int]], stream: int = 0) -> torch.Tensor:
+        """Next tokens from hidden states: greedy arg-max, or the sampling kernel over the
+        full-vocabulary logits for the given workspace rows."""
+        if rows is None:
+            return self._greedy(hidden)
+        logits = self.model.compute_logits(hidden).to(torch.float32)
+        return self.sampler.sample(logits, rows, stream=stream)
 
     def _greedy(self, hidden: torch.Tensor) -> torch.Tensor:
         """Next-token ids from hidden states (vocabulary-sharded lm_head: local argmax, then
@@ -207,11 +232,16 @@ class Engine:
         st = self._eager_state(list(last_tokens), positions, list(range(B)), seqs, max_kv_len=max(positions) + 1)
         return self.model.forward_mtp(st, self.cache, torch.cat(list(last_hiddens), 0))
 
-    def mtp_decode_step(self, seqs: Seq[Sequence], last_tokens: Seq[int], seed: torch.Tensor):
-        """One speculative step with D = self.mtp drafts per sequence (greedy verification).
+    def mtp_decode_step(self, seqs: Seq[Sequence], last_tokens: Seq[int], seed: torch.Tensor,
+                        rows: Optional[Seq[int]] = None):
+        """One speculative step with D = self.mtp drafts per sequence.  Greedy rows compare
+        arg-max tokens; sampled rows draw drafts from the MTP distribution and verify them by
+        linear-chain rejection sampling on the device (distribution-preserving).
 
         Returns (accepted tokens per sequence (1..D+1 each), new last tokens, new seed)."""
         D, B = self.mtp, len(seqs)
+        rows = list(range(B)) if rows is None else list(rows)
+        sampled = self.sampler is not None and not self.sampler.all_greedy(rows)
         tpr = D + 1
         p0 = [s.length for s in seqs]
         for s, t in zip(seqs, last_tokens):
@@ -231,9 +261,9 @@ class Engine:
         seed_buf.copy_(seed)
 
         def run():
-            return self._mtp_graph_body(st, seed_buf, B, D)
+            return self._mtp_graph_body(st, seed_buf, B, D, rows if sampled else None)
 
-        out_tokens, n_acc, new_seed = self.graphs.execute(("mtp", B, D, bucket), run)
+        out_tokens, n_acc, new_seed = self.graphs.execute(("mtp", B, D, bucket, tuple(rows) if sampled else None), run)
         packed = self._readback(("mtp", B), torch.cat([out_tokens, n_acc.unsqueeze(1)], 1))
         accepted, new_last = [], []
         for b, s in enumerate(seqs):
@@ -255,7 +285,9 @@ class Engine:
             self._bufs[key] = t
         return t
 
-    def _mtp_graph_body(self, st: StepState, seed: torch.Tensor, B: int, D: int):
+    def _mtp_graph_body(self, st: StepState, seed: torch.Tensor, B: int, D: int, rows=None):
+        if rows is not None:
+            return self._mtp_graph_body_sampled(st, seed, B, D, rows)
         m, dev = self.model, self.device
         tpr = D + 1
         ids2d = st.input_ids.view(B, tpr)
@@ -282,6 +314,39 @@ class Engine:
         out_tokens = torch.where(j < n_acc.unsqueeze(1), torch.cat([drafts, drafts[:, :1]], 1), bonus.expand(B, tpr))
         # --- reseed: MTP layer over the verification positions with (h_j, next token_j) ---
         st2 = StepState(input_ids=out_tokens.reshape(-1), positions=st.positions, batch_idx=st.batch_idx,
+                        page_table=st.page_table, cp_world=st.cp_world, cp_rank=st.cp_rank, max_kv_len=st.max_kv_len)
+        hm = m.forward_mtp(st2, self.cache, h).view(B, tpr, -1)
+        new_seed = hm.gather(1, n_acc.view(B, 1, 1).to(torch.int64).expand(B, 1, hm.shape[-1])).squeeze(1)
+        return out_tokens, n_acc.to(out_tokens.dtype), new_seed
+
+    def _mtp_graph_body_sampled(self, st: StepState, seed: torch.Tensor, B: int, D: int, rows):
+        """Speculative step with sampling: drafts are drawn from the MTP head's candidate
+        distribution, the main model's candidate distributions at the D+1 positions verify them."""
+        m, dev, sw = self.model, self.device, self.sampler
+        tpr = D + 1
+        ids2d = st.input_ids.view(B, tpr)
+        pos2d = st.positions.view(B, tpr)
+        brow = torch.arange(B, dtype=torch.int32, device=dev)
+        hidden = seed
+        d_tok, d_ids, d_probs = [], [], []
+        for depth in range(D):
+            logits = m.compute_logits(hidden).to(torch.float32)
+            tok, cid, cpr = sw.sample(logits, rows, stream=16 + depth, want_candidates=True, advance=False)
+            d_tok.append(tok); d_ids.append(cid); d_probs.append(cpr)
+            ids2d[:, depth + 1] = tok.to(ids2d.dtype)
+            if depth + 1 < D:
+                stp = StepState(input_ids=tok, positions=pos2d[:, depth].contiguous(), batch_idx=brow,
+                                page_table=st.page_table, cp_world=st.cp_world, cp_rank=st.cp_rank,
+                                max_kv_len=st.max_kv_len)
+                hidden = m.forward_mtp(stp, self.cache, hidden)
+        h = m.forward_hidden(st, self.cache)
+        logits = m.compute_logits(h).to(torch.float32)                               # [B * tpr, V]
+        rep_rows = [r for r in rows for _ in range(tpr)]
+        _, t_ids, t_probs = sw.sample(logits, rep_rows, stream=48, want_candidates=True, advance=False)
+        Cc = t_ids.shape[-1]
+        out_tokens, n_acc = sw.verify(torch.stack(d_tok, 1), torch.stack(d_ids, 1), torch.stack(d_probs, 1),
+                                      t_ids.view(B, tpr, Cc), t_probs.view(B, tpr, Cc))
+        st2 = StepState(input_ids=out_tokens.clamp(min=0).reshape(-1), positions=st.positions, batch_idx=st.batch_idx,
                         page_table=st.page_table, cp_world=st.cp_world, cp_rank=st.cp_rank, max_kv_len=st.max_kv_len)
         hm = m.forward_mtp(st2, self.cache, h).view(B, tpr, -1)
         new_seed = hm.gather(1, n_acc.view(B, 1, 1).to(torch.int64).expand(B, 1, hm.shape[-1])).squeeze(1)

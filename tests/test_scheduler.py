@@ -1,0 +1,173 @@
+"""Scheduler, prefix cache and host tier on a fake engine (no model, no GPU).
+Mirrors the reference's `tests/test_generation_scheduler.ts`, `test_prefix_cache.ts`,
+`test_prefix_resume.ts`."""
+import pytest
+
+from slopllm_b200.config import SamplingParams
+from slopllm_b200.kv.paged import PageAllocationError, PagedKVCache
+from slopllm_b200.scheduler.scheduler import GenerationRequest, GenerationScheduler, HostTier
+
+
+class FakeEngine:
+    """Allocates pages like the real engine and 'generates' token = (last + 1) % 1000."""
+
+    def __init__(self, pages=32, mtp=0, fail_on=None):
+        self.kv = PagedKVCache(pages)
+        self.mtp = mtp
+        self.prefill_calls = []
+        self.decode_batches = []
+        self.fail_on = fail_on
+
+    def prefill(self, seqs, prompts, chunk_size=8192, want_hidden=False, rows=None, limits=None):
+        toks = []
+        for b, (s, p) in enumerate(zip(seqs, prompts)):
+            upto = len(p) if limits is None else limits[b]
+            self.prefill_calls.append((s.seq_id, s.length, upto))
+            self.kv.append_tokens(s, p[s.length:upto])
+            self.kv.report_tokens(s)
+            toks.append((p[-1] + 1) % 1000 if upto == len(p) else -1)
+        return toks, ([None] * len(seqs) if want_hidden else None)
+
+    def decode_step(self, seqs, last, rows=None):
+        if self.fail_on is not None and len(self.decode_batches) == self.fail_on:
+            self.decode_batches.append(None)
+            raise RuntimeError("boom")
+        self.decode_batches.append(len(seqs))
+        for s, t in zip(seqs, last):
+            self.kv.append_tokens(s, [t])
+            self.kv.report_tokens(s)
+        return [(t + 1) % 1000 for t in last]
+
+
+def _req(i, prompt, n=4, **kw):
+    got = []
+    r = GenerationRequest(id=str(i), input_ids=list(prompt), max_tokens=n, sampling=SamplingParams(temperature=0),
+                          on_token=got.append, **kw)
+    r.got = got
+    return r
+
+
+def _drain(s, limit=200):
+    for _ in range(limit):
+        if s.idle():
+            s.step()       # retire
+            return
+        s.step()
+    raise AssertionError("scheduler did not finish")
+
+
+def test_continuous_batching_and_finish_reasons():
+    eng = FakeEngine()
+    s = GenerationScheduler(eng, max_batch=2, chunk_size=64, eos_token_ids=[7])
+    reqs = [_req(0, range(10, 20), 5), _req(1, [3, 4], 10), _req(2, range(100, 130), 3)]
+    for r in reqs:
+        s.submit(r)
+    _drain(s)
+    assert reqs[0].generated == [20, 21, 22, 23, 24] and reqs[0].finish_reason == "length"
+    assert reqs[1].generated == [5, 6, 7] and reqs[1].finish_reason == "stop"          # hit eos
+    assert reqs[2].generated == [130, 131, 132]
+    assert max(b for b in eng.decode_batches if b) == 2                                   # two rows decoded together
+    assert s.metrics.request_success_total == 3 and s.metrics.generation_tokens_total == 11
+    assert reqs[0].got == reqs[0].generated
+
+
+def test_chunked_prefill_budget():
+    eng = FakeEngine(pages=64)
+    s = GenerationScheduler(eng, max_batch=2, chunk_size=100)
+    r = _req(0, range(250), 2)
+    s.submit(r)
+    _drain(s)
+    spans = [(a, b) for (_, a, b) in eng.prefill_calls]
+    assert spans == [(0, 100), (100, 200), (200, 250)]
+    assert r.generated == [250, 251]
+
+
+def test_prefix_sharing_resume_and_cow():
+    kv = PagedKVCache(16)
+    a, cached = kv.start_request(list(range(200)))
+    assert cached == 0
+    kv.append_tokens(a, list(range(200)))
+    kv.report_tokens(a)
+    kv.stage(a)
+    # shares whole pages only, and never the whole prompt
+    b, cached = kv.start_request(list(range(128)) + [999] * 10)
+    assert cached == 128 and b.pages == a.pages[:2] and kv.pool.refcount(a.pages[0]) == 2
+    c, cached = kv.start_request(list(range(128)))
+    assert cached == 64                      # (len - 1) // 64 pages
+    # resume: exact proper prefix ending mid-page, donor adopted in place
+    d, cached = kv.start_request(list(range(200)) + [5, 6])
+    assert d is a and cached == 200
+    # appending to the resumed sequence writes into its private last page; shared pages untouched
+    kv.append_tokens(d, [5, 6])
+    assert d.pages[:2] == b.pages[:2]
+    # copy-on-write: b appends into a fresh private page after its 2 shared ones
+    kv.append_tokens(b, [999] * 10)
+    assert len(b.pages) == 3 and b.pages[2] not in a.pages
+
+
+def test_truncate_returns_pages_and_allocation_error():
+    kv = PagedKVCache(4)
+    s = kv.new_sequence()
+    kv.append_tokens(s, [1] * 130)
+    assert len(s.pages) == 3
+    kv.truncate(s, 64)
+    assert len(s.pages) == 1 and kv.free_pages == 3
+    with pytest.raises(PageAllocationError):
+        kv.append_tokens(s, [1] * 400)
+    kv.free_sequence(s)
+    kv.assert_clear()
+
+
+def test_eviction_to_host_tier_and_restore():
+    eng = FakeEngine(pages=8)
+    store = {}
+    host = HostTier(16, 64, read_page=lambda p: ("blob", p), write_page=lambda p, blob: store.__setitem__(p, blob))
+    s = GenerationScheduler(eng, max_batch=1, chunk_size=512, host_tier=host)
+    r1 = _req(0, range(300), 2)
+    s.submit(r1)
+    _drain(s)
+    assert eng.kv.staged                      # finished sequence staged on the GPU tier
+    r2 = _req(1, range(1000, 1400), 2)        # needs 7 pages: evicts the staged one, offloading it to the host
+    s.submit(r2)
+    _drain(s)
+    assert host.used_pages == 4
+    ev = s.flush_gpu_cache()
+    s.step()
+    assert ev.done.is_set() and not eng.kv.staged
+    r3 = _req(2, list(range(300)) + [1, 2, 3], 2)
+    s.submit(r3)
+    _drain(s)
+    assert r3.cached_tokens == 256 and len(store) == 4      # restored from pinned host pages
+    ev = s.flush_host_cache()
+    s.step()
+    assert ev.result["host_pages_freed"] >= 4
+
+
+def test_error_rolls_back_the_batch_and_scheduler_survives():
+    eng = FakeEngine(fail_on=1)
+    s = GenerationScheduler(eng, max_batch=2, chunk_size=64)
+    a, b = _req(0, [1, 2, 3], 8), _req(1, [4, 5], 8)
+    s.submit(a)
+    s.submit(b)
+    _drain(s)
+    assert a.finish_reason == "error" and "boom" in a.error and b.finish_reason == "error"
+    eng.kv.assert_clear()
+    c = _req(2, [9], 3)
+    s.submit(c)
+    _drain(s)
+    assert c.generated == [10, 11, 12]
+
+
+def test_cancel_and_too_long_prompt():
+    eng = FakeEngine(pages=2)
+    s = GenerationScheduler(eng, max_batch=1, chunk_size=64)
+    big = _req(0, range(500), 2)
+    s.submit(big)
+    s.step()
+    assert big.finish_reason == "error" and "fit" in big.error
+    r = _req(1, [1], 100)
+    s.submit(r)
+    s.step()
+    r.cancel()
+    _drain(s)
+    assert r.finish_reason == "cancelled" and len(r.generated) < 100
