@@ -266,11 +266,13 @@ def main():
         "details": details,
     }
     if rank == 0:
-        print(json.dumps(out))
+        print(json.dumps(out), flush=True)
     if W > 1:
         dist.barrier()
-        dist.destroy_process_group()
-    return 0
+    torch.cuda.synchronize()
+    sys.stdout.flush()
+    # captured graphs still reference the communicators: skip the library teardown
+    os._exit(0)
 
 
 if __name__ == "__main__":

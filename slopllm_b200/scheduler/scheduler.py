@@ -409,11 +409,12 @@ class GenerationScheduler:
                 break
             req.generated.append(int(t))
             self.metrics.generation_tokens_total += 1
+            if int(t) in self.eos or int(t) in req.stop_token_ids:
+                req.finish_reason = "stop"            # the end-of-sequence token itself is not streamed
+                break
             if req.on_token and not req.cancelled:
                 req.on_token(int(t))
-            if int(t) in self.eos or int(t) in req.stop_token_ids:
-                req.finish_reason = "stop"
-            elif len(req.generated) >= req.max_tokens:
+            if len(req.generated) >= req.max_tokens:
                 req.finish_reason = "length"
 
     def _fail_all(self, err: BaseException) -> None:

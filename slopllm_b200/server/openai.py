@@ -1,0 +1,379 @@
+"""OpenAI-compatible HTTP server (asyncio, no third-party web framework).
+
+Endpoints and behaviour follow `src/openai-server.ts:963-1030`:
+  POST /v1/chat/completions   (stream / non-stream, stream_options.include_usage, tools,
+                               reasoning_content, stop strings, max_tokens | max_completion_tokens,
+                               temperature / top_p / top_k / repetition_penalty (alias
+                               frequency_penalty) / presence_penalty, chat_template_kwargs)
+  POST /tokenize
+  POST /admin/flush_gpu_cache, POST /admin/flush_host_cache   (admin key)
+  GET  /metrics  (Prometheus text, vLLM-compatible metric names), /v1/models, /version, /health
+Bearer authentication (`--api-key`, `--admin-api-key`), CORS preflight.
+
+The scheduler runs in its own thread; tokens cross into the event loop with
+`loop.call_soon_threadsafe`.
+"""
+from __future__ import annotations
+
+import asyncio
+import json
+import time
+import uuid
+from typing import Dict, List, Optional, Tuple
+
+from .. import __version__
+from ..config import EngineConfig, SamplingParams
+from ..scheduler.scheduler import GenerationRequest, GenerationScheduler
+from .parsers import ChatModelParser, GlmParser, check_stop_sequences, resolve_control_tokens, starts_in_reasoning
+
+CORS = {"Access-Control-Allow-Origin": "*", "Access-Control-Allow-Headers": "authorization, content-type",
+        "Access-Control-Allow-Methods": "GET, POST, OPTIONS"}
+
+
+class HttpError(Exception):
+    def __init__(self, status: int, message: str, etype: str = "invalid_request_error", param: Optional[str] = None):
+        super().__init__(message)
+        self.status, self.message, self.etype, self.param = status, message, etype, param
+
+    def body(self) -> dict:
+        err = {"message": self.message, "type": self.etype}
+        if self.param:
+            err["param"] = self.param
+        return {"error": err}
+
+
+def render_metrics(m, pending: int, kv, batch_size: int, chunk_size: int, max_model_len: int, cp_world: int = 1) -> str:
+    """Prometheus exposition text; metric names match `src/openai-server.ts:335-407`."""
+    waiting = max(0, pending - max(0, batch_size - m.running_requests))
+    used = (kv.num_pages - kv.free_pages) / kv.num_pages if kv.num_pages else 0.0
+    lines = [
+        "# TYPE vllm:num_requests_running gauge", f"vllm:num_requests_running {m.running_requests}",
+        "# TYPE vllm:num_requests_waiting gauge", f"vllm:num_requests_waiting {waiting}",
+        "# TYPE vllm:generation_tokens_total counter", f"vllm:generation_tokens_total {m.generation_tokens_total}",
+        "# TYPE vllm:prompt_tokens_total counter", f"vllm:prompt_tokens_total {m.prompt_tokens_total}",
+        "# TYPE vllm:prefix_cache_hits_total counter", f"vllm:prefix_cache_hits_total {m.cached_prompt_tokens_total}",
+        "# TYPE vllm:spec_decode_num_drafts_total counter", f"vllm:spec_decode_num_drafts_total {m.spec_decode_num_drafts_total}",
+        "# TYPE vllm:spec_decode_num_draft_tokens_total counter",
+        f"vllm:spec_decode_num_draft_tokens_total {m.spec_decode_num_draft_tokens_total}",
+        "# TYPE vllm:spec_decode_num_accepted_tokens_total counter",
+        f"vllm:spec_decode_num_accepted_tokens_total {m.spec_decode_num_accepted_tokens_total}",
+        "# TYPE vllm:request_success_total counter", f"vllm:request_success_total {m.request_success_total}",
+        "# TYPE vllm:kv_cache_usage_perc gauge", f"vllm:kv_cache_usage_perc {used}",
+        "# TYPE vllm:cache_config_info gauge",
+        f'vllm:cache_config_info{{block_size="{kv.tokens_per_page}",num_gpu_blocks="{kv.num_pages}",'
+        f'max_total_num_tokens="{kv.num_pages * kv.tokens_per_page}",cp_world_size="{cp_world}"}} 1',
+        "# TYPE vllm:scheduler_config_info gauge",
+        f'vllm:scheduler_config_info{{max_num_seqs="{batch_size}",max_num_batched_tokens="{chunk_size}",'
+        f'max_model_len="{max_model_len}"}} 1',
+        "# TYPE vllm:request_prefill_time_seconds histogram",
+        f'vllm:request_prefill_time_seconds_bucket{{le="+Inf"}} {m.prefill_time_seconds_count}',
+        f"vllm:request_prefill_time_seconds_sum {m.prefill_time_seconds_sum}",
+        f"vllm:request_prefill_time_seconds_count {m.prefill_time_seconds_count}",
+        "# TYPE glm:phase_seconds_total counter", "# TYPE glm:phase_count_total counter",
+        "# TYPE glm:collective_timeouts_total counter", f"glm:collective_timeouts_total {m.collective_timeouts_total}",
+    ]
+    for key, sec in m.phase_seconds.items():
+        phase, b = key.split("/b")
+        lab = f'{{phase="{phase}",batch_size="{b}"}}'
+        lines += [f"glm:phase_seconds_total{lab} {sec}", f"glm:phase_count_total{lab} {m.phase_count.get(key, 0)}"]
+    return "\n".join(lines) + "\n"
+
+
+class OpenAIServer:
+    def __init__(self, scheduler: GenerationScheduler, tokenizer, cfg: EngineConfig, model_name: str = "glm",
+                 max_model_len: int = 65536, healthy=lambda: True):
+        self.sched = scheduler
+        self.tok = tokenizer
+        self.cfg = cfg
+        self.model_name = model_name
+        self.max_model_len = max_model_len
+        self.healthy = healthy
+        self.control = resolve_control_tokens(tokenizer)
+        self.pending = 0
+        self._server: Optional[asyncio.AbstractServer] = None
+
+    # ---- plumbing ---------------------------------------------------------------------------------------
+    async def start(self) -> None:
+        self._server = await asyncio.start_server(self._client, self.cfg.host, self.cfg.port)
+
+    @property
+    def port(self) -> int:
+        return self._server.sockets[0].getsockname()[1]
+
+    async def close(self) -> None:
+        if self._server:
+            self._server.close()
+            await self._server.wait_closed()
+
+    async def _client(self, reader: asyncio.StreamReader, writer: asyncio.StreamWriter) -> None:
+        try:
+            head = await reader.readuntil(b"\r\n\r\n")
+            lines = head.decode("latin1").split("\r\n")
+            method, path, _ = lines[0].split(" ", 2)
+            headers = {}
+            for ln in lines[1:]:
+                if ":" in ln:
+                    k, v = ln.split(":", 1)
+                    headers[k.strip().lower()] = v.strip()
+            n = int(headers.get("content-length", "0") or 0)
+            body = await reader.readexactly(n) if n else b""
+            await self._route(method, path.split("?")[0], headers, body, writer)
+        except (asyncio.IncompleteReadError, ConnectionError, ValueError):
+            pass
+        finally:
+            try:
+                writer.close()
+            except Exception:  # noqa: BLE001
+                pass
+
+    @staticmethod
+    def _send(writer, status: int, body, ctype="application/json", extra: Optional[Dict[str, str]] = None) -> None:
+        data = body if isinstance(body, (bytes, bytearray)) else (json.dumps(body) if not isinstance(body, str) else body).encode()
+        reason = {200: "OK", 204: "No Content", 400: "Bad Request", 401: "Unauthorized", 403: "Forbidden", 404: "Not Found",
+                  405: "Method Not Allowed", 500: "Internal Server Error", 503: "Service Unavailable"}.get(status, "OK")
+        hdr = {"Content-Type": ctype, "Content-Length": str(len(data)), "Connection": "close", **CORS, **(extra or {})}
+        writer.write((f"HTTP/1.1 {status} {reason}\r\n" + "".join(f"{k}: {v}\r\n" for k, v in hdr.items()) + "\r\n").encode() + data)
+
+    def _auth(self, headers, admin: bool = False) -> None:
+        key = self.cfg.admin_api_key if admin else self.cfg.api_key
+        if admin and not key:
+            raise HttpError(403, "admin endpoints need --admin-api-key", "permission_error")
+        if key and headers.get("authorization", "") != f"Bearer {key}":
+            raise HttpError(401, "invalid API key", "authentication_error")
+
+    async def _route(self, method, path, headers, body, writer) -> None:
+        try:
+            if method == "OPTIONS":
+                return self._send(writer, 204, b"")
+            if method == "GET" and path == "/health":
+                ok = self.healthy()
+                return self._send(writer, 200 if ok else 503, {"status": "ok" if ok else "unhealthy"})
+            if method == "GET" and path == "/version":
+                return self._send(writer, 200, {"version": __version__})
+            if method == "GET" and path == "/metrics":
+                txt = render_metrics(self.sched.metrics, self.pending, self.sched.engine.kv, self.cfg.batch_size,
+                                     self.cfg.chunk_size, self.max_model_len)
+                return self._send(writer, 200, txt, "text/plain; version=0.0.4; charset=utf-8")
+            if method == "GET" and path == "/v1/models":
+                self._auth(headers)
+                return self._send(writer, 200, {"object": "list", "data": [{"id": self.model_name, "object": "model",
+                                                                              "owned_by": "slopllm_b200",
+                                                                              "max_model_len": self.max_model_len}]})
+            if method == "POST" and path == "/tokenize":
+                self._auth(headers)
+                params = json.loads(body or b"{}")
+                ids = self._tokenize(params)
+                return self._send(writer, 200, {"tokens": ids, "count": len(ids), "max_model_len": self.max_model_len})
+            if method == "POST" and path in ("/admin/flush_gpu_cache", "/admin/flush_host_cache"):
+                self._auth(headers, admin=True)
+                ev = self.sched.flush_gpu_cache() if path.endswith("gpu_cache") else self.sched.flush_host_cache()
+                await asyncio.get_running_loop().run_in_executor(None, ev.done.wait, 60)
+                return self._send(writer, 200, ev.result)
+            if method == "POST" and path == "/v1/chat/completions":
+                self._auth(headers)
+                return await self._chat(json.loads(body or b"{}"), writer)
+            raise HttpError(404, f"no route {method} {path}", "not_found")
+        except HttpError as e:
+            self._send(writer, e.status, e.body())
+        except json.JSONDecodeError:
+            self._send(writer, 400, HttpError(400, "request body is not valid JSON").body())
+        except Exception as e:  # noqa: BLE001
+            self._send(writer, 500, HttpError(500, f"{type(e).__name__}: {e}", "server_error").body())
+        finally:
+            try:
+                await writer.drain()
+            except ConnectionError:
+                pass
+
+    # ---- request preparation ----------------------------------------------------------------------------------
+    def _tokenize(self, params: dict, kwargs: Optional[dict] = None) -> List[int]:
+        if "messages" in params:
+            kw = dict(params.get("chat_template_kwargs") or {})
+            kw.update(kwargs or {})
+            cont = bool(kw.pop("continue_final_message", False))
+            ids = self.tok.apply_chat_template(params["messages"], tokenize=True, add_generation_prompt=not cont,
+                                               continue_final_message=cont, tools=params.get("tools"), **kw)
+            return list(ids["input_ids"] if isinstance(ids, dict) else ids)
+        return list(self.tok.encode(params.get("prompt", ""), add_special_tokens=False))
+
+    def _sampling(self, p: dict) -> SamplingParams:
+        d = self.cfg.sampling
+
+        def num(name, default, alias=None):
+            v = p.get(name, p.get(alias) if alias else None)
+            v = default if v is None else v
+            if not isinstance(v, (int, float)) or v != v or v in (float("inf"), float("-inf")):
+                raise HttpError(400, f"{name} must be a finite number", param=name)
+            return v
+        sp = SamplingParams(temperature=max(0.0, float(num("temperature", d.temperature))), top_p=float(num("top_p", d.top_p)),
+                            top_k=int(num("top_k", d.top_k)),
+                            repetition_penalty=float(num("repetition_penalty", d.repetition_penalty, "frequency_penalty")),
+                            presence_penalty=float(num("presence_penalty", d.presence_penalty)),
+                            repetition_penalty_window=d.repetition_penalty_window)
+        if self.cfg.mtp > 0:
+            if sp.top_k > 256:
+                raise HttpError(400, "Linear MTP supports top_k <= 256", param="top_k")
+            if sp.repetition_penalty != 1 or sp.presence_penalty != 0:
+                raise HttpError(400, "MTP decoding currently requires repetition_penalty=1 and presence_penalty=0")
+        return sp
+
+    def _parser(self, kwargs: dict) -> ChatModelParser:
+        if self.control is None:
+            return ChatModelParser(lambda ids: self.tok.decode(list(ids)))
+        think = not kwargs.get("continue_final_message") and starts_in_reasoning(
+            lambda: self.tok.apply_chat_template([{"role": "user", "content": "Hello"}], tokenize=False,
+                                                 add_generation_prompt=True,
+                                                 **{k: v for k, v in kwargs.items() if k != "continue_final_message"}))
+        return GlmParser(lambda ids: self.tok.decode(list(ids)), self.control, think)
+
+    # ---- chat completions ------------------------------------------------------------------------------------------
+    async def _chat(self, params: dict, writer) -> None:
+        messages = params.get("messages")
+        if not isinstance(messages, list) or not messages:
+            raise HttpError(400, "messages must be a non-empty array", param="messages")
+        kwargs = dict(params.get("chat_template_kwargs") or {})
+        if params.get("reasoning_effort") is not None:
+            kwargs["reasoning_effort"] = params["reasoning_effort"]
+        sp = self._sampling(params)
+        stops = params.get("stop") or []
+        stops = [stops] if isinstance(stops, str) else [s for s in stops if isinstance(s, str)]
+        try:
+            ids = self._tokenize(params, kwargs)
+            parser = self._parser(kwargs)
+            if kwargs.get("continue_final_message"):
+                parser.continue_from(self.tok.encode(messages[-1].get("content") or "", add_special_tokens=False))
+        except HttpError:
+            raise
+        except Exception as e:  # noqa: BLE001
+            raise HttpError(400, f"unable to prepare chat prompt: {e}")
+        if len(ids) >= self.max_model_len:
+            raise HttpError(400, f"prompt has {len(ids)} tokens, the model context is {self.max_model_len}")
+        max_tokens = params.get("max_tokens") or params.get("max_completion_tokens") or self.cfg.max_tokens
+        max_tokens = max(1, min(int(max_tokens), self.max_model_len - len(ids)))
+        stream = params.get("stream") is True
+        include_usage = bool((params.get("stream_options") or {}).get("include_usage"))
+
+        loop = asyncio.get_running_loop()
+        q: asyncio.Queue = asyncio.Queue()
+        req = GenerationRequest(id="chatcmpl-" + uuid.uuid4().hex[:24], input_ids=ids, max_tokens=max_tokens, sampling=sp,
+                                on_token=lambda t: loop.call_soon_threadsafe(q.put_nowait, ("tok", t)),
+                                on_finish=lambda r: loop.call_soon_threadsafe(q.put_nowait, ("end", r)))
+        created = int(time.time())
+        self.pending += 1
+        self.sched.submit(req)
+        state = {"content": "", "sent": 0, "reasoning": "", "tools": [], "stopped": False}
+
+        def held_back(text: str) -> int:
+            """Length of the longest tail of `text` that could still grow into a stop string."""
+            best = 0
+            for s_ in stops:
+                for k in range(min(len(s_) - 1, len(text)), 0, -1):
+                    if text.endswith(s_[:k]):
+                        best = max(best, k)
+                        break
+            return best
+
+        def chunk(delta: dict, finish=None, usage=None) -> bytes:
+            obj = {"id": req.id, "object": "chat.completion.chunk", "created": created, "model": self.model_name,
+                   "choices": [{"index": 0, "delta": delta, "finish_reason": finish}]}
+            if usage is not None:
+                obj["usage"] = usage
+            return b"data: " + json.dumps(obj).encode() + b"\n\n"
+
+        def usage_obj() -> dict:
+            return {"prompt_tokens": req.prompt_tokens, "completion_tokens": len(req.generated),
+                    "total_tokens": req.prompt_tokens + len(req.generated),
+                    "prompt_tokens_details": {"cached_tokens": req.cached_tokens}}
+
+        def apply(events) -> List[dict]:
+            deltas = []
+            for ev in events:
+                if ev.type == "content_delta":
+                    text, hit = check_stop_sequences(state["content"] + ev.text, stops)
+                    state["content"] = text
+                    upto = len(text) if hit else len(text) - held_back(text)
+                    if upto > state["sent"]:
+                        deltas.append({"content": text[state["sent"]:upto]})
+                        state["sent"] = upto
+                    if hit:
+                        state["stopped"] = True
+                        break
+                elif ev.type == "reasoning_delta":
+                    state["reasoning"] += ev.text
+                    deltas.append({"reasoning_content": ev.text})
+                elif ev.type == "tool_call":
+                    call = {"index": ev.index, "id": "call_" + uuid.uuid4().hex[:24], "type": "function",
+                            "function": {"name": ev.name, "arguments": ev.arguments}}
+                    state["tools"].append(call)
+                    deltas.append({"tool_calls": [call]})
+                elif ev.type == "parse_error":
+                    state["content"] += ev.raw
+                    deltas.append({"content": state["content"][state["sent"]:]})
+                    state["sent"] = len(state["content"])
+            return deltas
+
+        try:
+            if stream:
+                hdr = {"Content-Type": "text/event-stream", "Cache-Control": "no-cache", "Connection": "close", **CORS}
+                writer.write(("HTTP/1.1 200 OK\r\n" + "".join(f"{k}: {v}\r\n" for k, v in hdr.items()) + "\r\n").encode())
+                writer.write(chunk({"role": "assistant"}))
+            final: Optional[GenerationRequest] = None
+            while final is None:
+                kind, val = await q.get()
+                if kind == "end":
+                    final = val
+                    events = parser.finish() if not state["stopped"] else []
+                else:
+                    events = parser.on_token(val) if not state["stopped"] else []
+                deltas = apply(events)
+                if kind == "end" and not state["stopped"] and state["sent"] < len(state["content"]):
+                    deltas.append({"content": state["content"][state["sent"]:]})      # text held for a stop string that never came
+                    state["sent"] = len(state["content"])
+                if state["stopped"] and not req.finish_reason:
+                    req.finish_reason = "stop"            # stop string hit: the row retires at the next step
+                    req.cancel()
+                if stream:
+                    for d in deltas:
+                        writer.write(chunk(d))
+                    try:
+                        await writer.drain()
+                    except ConnectionError:
+                        req.cancel()                      # client went away
+                        return
+            if final.error and not state["stopped"]:
+                raise HttpError(500, final.error, "server_error")
+            finish = "tool_calls" if parser.produced_tool_calls else ("stop" if state["stopped"] else final.finish_reason or "stop")
+            if finish == "cancelled":
+                finish = "stop"
+            if stream:
+                writer.write(chunk({}, finish))
+                if include_usage:
+                    obj = {"id": req.id, "object": "chat.completion.chunk", "created": created, "model": self.model_name,
+                           "choices": [], "usage": usage_obj()}
+                    writer.write(b"data: " + json.dumps(obj).encode() + b"\n\n")
+                writer.write(b"data: [DONE]\n\n")
+            else:
+                msg = {"role": "assistant", "content": state["content"] or None}
+                if state["reasoning"]:
+                    msg["reasoning_content"] = state["reasoning"]
+                if state["tools"]:
+                    msg["tool_calls"] = [{k: v for k, v in c.items() if k != "index"} for c in state["tools"]]
+                self._send(writer, 200, {"id": req.id, "object": "chat.completion", "created": created, "model": self.model_name,
+                                         "choices": [{"index": 0, "message": msg, "finish_reason": finish}],
+                                         "usage": usage_obj()})
+        except HttpError as e:
+            if stream:
+                writer.write(b"data: " + json.dumps(e.body()).encode() + b"\n\ndata: [DONE]\n\n")
+            else:
+                raise
+        finally:
+            self.pending -= 1
+
+
+async def serve(server: OpenAIServer) -> None:
+    await server.start()
+    await asyncio.Event().wait()
+
+
+def _unused() -> Tuple:
+    return ()

@@ -1,0 +1,140 @@
+"""OpenAI server over a fake engine: SSE streaming, usage, reasoning / tool-call parsing, stop
+strings, auth, /metrics, /tokenize, admin flush.  Parser behaviours mirror the reference's
+`tests/test_glm_parser.ts` and `tests/test_incremental_decoder.ts`."""
+import asyncio
+import json
+
+from slopllm_b200.config import EngineConfig
+from slopllm_b200.kv.paged import PagedKVCache
+from slopllm_b200.scheduler.scheduler import GenerationScheduler
+from slopllm_b200.server.openai import OpenAIServer
+from slopllm_b200.server.parsers import GlmParser, IncrementalDecoder, check_stop_sequences, resolve_control_tokens
+from slopllm_b200.server.tokenizer import ByteTokenizer
+
+
+class ScriptEngine:
+    """Emits a fixed token script regardless of the prompt."""
+
+    def __init__(self, script):
+        self.kv = PagedKVCache(64)
+        self.mtp = 0
+        self.script = list(script)
+        self.pos = {}
+
+    def prefill(self, seqs, prompts, chunk_size=8192, want_hidden=False, rows=None, limits=None):
+        out = []
+        for s, p in zip(seqs, prompts):
+            self.kv.append_tokens(s, p[s.length:])
+            self.kv.report_tokens(s)
+            self.pos[s.seq_id] = 1
+            out.append(self.script[0])
+        return out, None
+
+    def decode_step(self, seqs, last, rows=None):
+        out = []
+        for s, t in zip(seqs, last):
+            self.kv.append_tokens(s, [t])
+            self.kv.report_tokens(s)
+            i = self.pos[s.seq_id]
+            self.pos[s.seq_id] = i + 1
+            out.append(self.script[min(i, len(self.script) - 1)])
+        return out
+
+
+def test_incremental_decoder_holds_partial_utf8():
+    tok = ByteTokenizer()
+    dec = IncrementalDecoder(lambda ids: tok.decode(list(ids)))
+    ids = tok.encode("héllo ✓")
+    out = [dec.push(t) for t in ids]
+    assert "".join(out) + dec.flush() == "héllo ✓"
+    assert all("�" not in o for o in out)
+
+
+def test_glm_parser_reasoning_tool_call_and_errors():
+    tok = ByteTokenizer()
+    ctl = resolve_control_tokens(tok)
+    p = GlmParser(lambda ids: tok.decode(list(ids)), ctl, starts_in_reasoning=True)
+    text = ("let me think</think>Hello!<tool_call>get_weather\n<arg_key>city</arg_key>\n<arg_value>\"Paris\"</arg_value>\n"
+            "<arg_key>days</arg_key><arg_value>3</arg_value></tool_call><tool_call><arg_key>x</arg_key></tool_call>")
+    events = []
+    for t in tok.encode(text):
+        events += p.on_token(t)
+    events += p.finish()
+    reasoning = "".join(e.text for e in events if e.type == "reasoning_delta")
+    content = "".join(e.text for e in events if e.type == "content_delta")
+    calls = [e for e in events if e.type == "tool_call"]
+    errs = [e for e in events if e.type == "parse_error"]
+    assert reasoning == "let me think" and content == "Hello!"
+    assert len(calls) == 1 and calls[0].name == "get_weather"
+    assert json.loads(calls[0].arguments) == {"city": "Paris", "days": 3}
+    assert len(errs) == 1 and "no function name" in errs[0].message
+    assert check_stop_sequences("abc STOP def", ["STOP", "def"]) == ("abc ", True)
+
+
+async def _http(port, method, path, body=None, headers=None):
+    r, w = await asyncio.open_connection("127.0.0.1", port)
+    data = json.dumps(body).encode() if body is not None else b""
+    h = {"Host": "x", "Content-Length": str(len(data)), **(headers or {})}
+    w.write((f"{method} {path} HTTP/1.1\r\n" + "".join(f"{k}: {v}\r\n" for k, v in h.items()) + "\r\n").encode() + data)
+    await w.drain()
+    raw = await r.read()
+    w.close()
+    head, _, payload = raw.partition(b"\r\n\r\n")
+    return int(head.split()[1]), payload
+
+
+def test_server_endpoints():
+    tok = ByteTokenizer()
+    script = tok.encode("hm</think>Hi there STOP never<tool_call>f<arg_key>a</arg_key><arg_value>1</arg_value></tool_call>") + [tok.eos_token_id]
+    eng = ScriptEngine(script)
+    cfg = EngineConfig(host="127.0.0.1", port=0, api_key="k", admin_api_key="adm", batch_size=2, chunk_size=256)
+    sched = GenerationScheduler(eng, max_batch=2, chunk_size=256, eos_token_ids=[tok.eos_token_id])
+    sched.start()
+
+    async def run():
+        srv = OpenAIServer(sched, tok, cfg, model_name="test-model", max_model_len=4096)
+        await srv.start()
+        port = srv.port
+        auth = {"Authorization": "Bearer k"}
+        st, body = await _http(port, "GET", "/health")
+        assert st == 200
+        st, body = await _http(port, "GET", "/v1/models")
+        assert st == 401
+        st, body = await _http(port, "GET", "/v1/models", headers=auth)
+        assert json.loads(body)["data"][0]["id"] == "test-model"
+        st, body = await _http(port, "POST", "/tokenize", {"prompt": "abc"}, auth)
+        assert json.loads(body)["tokens"] == [97, 98, 99]
+        # non-streaming: reasoning + content + tool call
+        st, body = await _http(port, "POST", "/v1/chat/completions",
+                               {"messages": [{"role": "user", "content": "hi"}], "max_tokens": 200, "temperature": 0}, auth)
+        out = json.loads(body)
+        msg = out["choices"][0]["message"]
+        assert st == 200 and msg["reasoning_content"] == "hm" and msg["content"] == "Hi there STOP never"
+        assert msg["tool_calls"][0]["function"] == {"name": "f", "arguments": '{"a": 1}'}
+        assert out["choices"][0]["finish_reason"] == "tool_calls" and out["usage"]["completion_tokens"] == len(script)
+        # streaming with a stop string and usage
+        st, body = await _http(port, "POST", "/v1/chat/completions",
+                               {"messages": [{"role": "user", "content": "hi"}], "stream": True, "stop": ["STOP"],
+                                "stream_options": {"include_usage": True}}, auth)
+        chunks = [json.loads(l[6:]) for l in body.decode().split("\n\n") if l.startswith("data: {")]
+        text = "".join(c["choices"][0]["delta"].get("content", "") for c in chunks if c["choices"])
+        assert text == "Hi there " and body.decode().rstrip().endswith("data: [DONE]")
+        assert [c for c in chunks if c["choices"] and c["choices"][0]["finish_reason"]][0]["choices"][0]["finish_reason"] == "stop"
+        assert any("usage" in c and not c["choices"] for c in chunks)
+        # second identical prompt is served from the prefix cache? (prompt shorter than a page: no) - metrics still count
+        st, body = await _http(port, "GET", "/metrics")
+        m = body.decode()
+        assert "vllm:generation_tokens_total" in m and "vllm:request_success_total 1" in m or "vllm:request_success_total 2" in m
+        assert 'vllm:cache_config_info{block_size="64"' in m
+        st, body = await _http(port, "POST", "/admin/flush_gpu_cache", {}, auth)
+        assert st == 401
+        st, body = await _http(port, "POST", "/admin/flush_gpu_cache", {}, {"Authorization": "Bearer adm"})
+        assert st == 200 and "gpu_pages_freed" in json.loads(body)
+        st, body = await _http(port, "POST", "/v1/chat/completions", {"messages": []}, auth)
+        assert st == 400
+        st, body = await _http(port, "POST", "/v1/chat/completions", {"messages": [{"role": "user", "content": "x"}], "top_p": "a"}, auth)
+        assert st == 400
+        await srv.close()
+
+    asyncio.run(run())
+    sched.stop()
