@@ -72,10 +72,13 @@ __device__ __forceinline__ uint4 ldg_ca_16(const void* p) {
 }
 
 // One warp: MT tiles of 16 rows x NT*8 tokens over the groups kpart, kpart+ksplit, ... of the row's K.
+// Tile mt covers rows tile_row0[mt] .. +15 (relative to Wp / S); rows >= rows_valid[mt] read as zero.
+// `tok[nt]` is the activation row (in the permuted copy) that this lane supplies for column g of n-tile nt.
 template <int MT, int NT>
 __device__ __forceinline__ void warp_rows_times_tokens(float (&acc)[MT][NT][4], const uint8_t* __restrict__ Wp,
                                                        const uint8_t* __restrict__ S, size_t w_stride, size_t s_stride,
-                                                       int rows_valid, int K, const uint4* __restrict__ xp, int kpart, int ksplit) {
+                                                       const int (&tile_row0)[MT], const int (&rows_valid)[MT], int K,
+                                                       const uint4* __restrict__ xp, const int (&tok)[NT], int kpart, int ksplit) {
     const int lane = threadIdx.x & 31;
     const int g = lane >> 2, c = lane & 3;
     const int G = K / 128;
@@ -87,12 +90,12 @@ __device__ __forceinline__ void warp_rows_times_tokens(float (&acc)[MT][NT][4], 
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
             a0[mt] = make_uint4(0, 0, 0, 0); a1[mt] = a0[mt]; b0[mt] = 0; b1[mt] = 0;
-            const int ra = mt * 16 + g, rb = ra + 8;
-            if (group < G && ra < rows_valid) {
+            const int ra = tile_row0[mt] + g, rb = ra + 8;
+            if (group < G && g < rows_valid[mt]) {
                 a0[mt] = ldg_nc_16(Wp + (size_t)ra * w_stride + (kk >> 1));
                 b0[mt] = *reinterpret_cast<const uint16_t*>(S + (size_t)ra * s_stride + (kk >> 4));
             }
-            if (group < G && rb < rows_valid) {
+            if (group < G && g + 8 < rows_valid[mt]) {
                 a1[mt] = ldg_nc_16(Wp + (size_t)rb * w_stride + (kk >> 1));
                 b1[mt] = *reinterpret_cast<const uint16_t*>(S + (size_t)rb * s_stride + (kk >> 4));
             }
@@ -109,7 +112,7 @@ __device__ __forceinline__ void warp_rows_times_tokens(float (&acc)[MT][NT][4], 
         }
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
-            const uint4* xr = xp + ((size_t)(nt * 8 + g) * G + group) * 16 + c;
+            const uint4* xr = xp + ((size_t)tok[nt] * G + group) * 16 + c;
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const uint4 xv = ldg_ca_16(xr + j * 4);          // x[token][kk + j*8 .. +7]
@@ -154,9 +157,15 @@ __global__ void __launch_bounds__(256) linear_nvfp4_mma_kernel(void* __restrict_
     for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) acc[mt][nt][0] = acc[mt][nt][1] = acc[mt][nt][2] = acc[mt][nt][3] = 0.f;
-    if (n0 < N)
-        warp_rows_times_tokens<MT, NT>(acc, Wp + (size_t)n0 * (K / 2), S + (size_t)n0 * (K / 16), K / 2, K / 16, min(ROWS, N - n0), K,
-                                       xp, kpart, ksplit);
+    if (n0 < N) {
+        int row0[MT], valid[MT], tok[NT];
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) { row0[mt] = mt * 16; valid[mt] = min(16, N - n0 - mt * 16); }
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) tok[nt] = nt * 8 + g;
+        warp_rows_times_tokens<MT, NT>(acc, Wp + (size_t)n0 * (K / 2), S + (size_t)n0 * (K / 16), K / 2, K / 16, row0, valid, K,
+                                       xp, tok, kpart, ksplit);
+    }
     float* mine = red + (size_t)warp * (TOK * ROWS);
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt)
@@ -232,4 +241,276 @@ SL_API int sl_linear_nvfp4_mma_push(const void* x, void* xp, const void* Wp, con
                                     int ldx, const PushCtx* push, cudaStream_t s) {
     if (push == nullptr || T > push->slot_rows || N > push->row_len) return -1;
     return dispatch_linear(nullptr, x, xp, Wp, S, g, T, N, K, ldx, 1, push, s);
+}
+
+// ======================================================================================================
+// Decode-time MoE on the same weight-streaming scheme.  Routes (token, choice) that share an expert are
+// grouped into work items of up to 8 activation rows, so an expert's weights are read once per step no
+// matter how many tokens chose it.  Reference: `nvfp4_mul_mat_id_kernel` / `nvfp4_down_reduce_kernel`
+// (`csrc/glm_gemv.cu:738-990, 1291-1375`) and the hybrid plan of `csrc/glm_mma_moe_coop.cu:43`.
+//   plan      : routes -> items {expert, up to 8 routes}
+//   gate/up   : act[route, :] = silu(g13[e,0] W1_e x_t) * (g13[e,1] W3_e x_t), written as f16 in operand order
+//   down      : y_route[route, :] = g2[e] W2_e act[route, :]
+//   reduce    : out[t, :] = sum_j wt[t,j] y_route[t*k+j, :] + y_route[shared(t), :]  (fp32, or pushed to peers)
+namespace {
+
+constexpr int kItemRoutes = 8;
+
+struct MoePlanView {
+    int* item_expert;      // [max_items]   local expert index, or -1 for the shared expert
+    int* item_routes;      // [max_items][8] route ids (-1 padded)
+    int* num_items;        // [1]
+};
+
+// One block.  Routed routes r = t*top_k + j (expert ids[r]); shared routes r = T*top_k + t.
+__global__ void __launch_bounds__(512) moe_plan_kernel(MoePlanView pv, const int* __restrict__ ids, int T, int top_k,
+                                                       int expert_offset, int num_local, int has_shared, int max_items) {
+    extern __shared__ int sh[];
+    int* ex = sh;                                  // expert of each routed route (-1 if not local)
+    const int n = T * top_k;
+    __shared__ int s_items;
+    for (int r = threadIdx.x; r < n; r += blockDim.x) {
+        const int e = ids[r] - expert_offset;
+        ex[r] = (e >= 0 && e < num_local) ? e : -1;
+    }
+    if (threadIdx.x == 0) s_items = 0;
+    for (int i = threadIdx.x; i < max_items * kItemRoutes; i += blockDim.x) pv.item_routes[i] = -1;
+    __syncthreads();
+    // leaders (first route of each chunk of 8 routes of an expert) claim item slots in route order
+    for (int base = 0; base < n; base += blockDim.x) {
+        const int r = base + threadIdx.x;
+        int before = -1;
+        if (r < n && ex[r] >= 0) {
+            before = 0;
+            for (int q = 0; q < r; ++q) before += (ex[q] == ex[r]);
+        }
+        const bool leader = before >= 0 && (before % kItemRoutes) == 0;
+        // deterministic slot: number of leaders with a smaller route id
+        __shared__ int flags[512];
+        flags[threadIdx.x] = leader ? 1 : 0;
+        __syncthreads();
+        if (leader) {
+            int slot = s_items;
+            for (int q = 0; q < (int)threadIdx.x; ++q) slot += flags[q];
+            if (slot < max_items) { pv.item_expert[slot] = ex[r]; pv.item_routes[slot * kItemRoutes] = r; }
+            ex[n + r] = slot;                      // remember my item for the members
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) { int c = 0; for (int q = 0; q < (int)blockDim.x; ++q) c += flags[q]; s_items += c; }
+        __syncthreads();
+    }
+    // members find their leader: same expert, chunk start
+    for (int r = threadIdx.x; r < n; r += blockDim.x) {
+        if (ex[r] < 0) continue;
+        int before = 0, lead = -1, seen = 0;
+        for (int q = 0; q < r; ++q) before += (ex[q] == ex[r]);
+        if (before % kItemRoutes == 0) continue;   // is a leader
+        const int want = before - before % kItemRoutes;
+        for (int q = 0; q < r; ++q) {
+            if (ex[q] == ex[r]) { if (seen == want) { lead = q; break; } ++seen; }
+        }
+        const int slot = ex[n + lead];
+        if (slot < max_items) pv.item_routes[slot * kItemRoutes + before % kItemRoutes] = r;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int items = s_items;
+        if (has_shared) {
+            for (int t0 = 0; t0 < T; t0 += kItemRoutes) {
+                if (items < max_items) {
+                    pv.item_expert[items] = -1;
+                    for (int q = 0; q < kItemRoutes && t0 + q < T; ++q) pv.item_routes[items * kItemRoutes + q] = n + t0 + q;
+                }
+                ++items;
+            }
+        }
+        *pv.num_items = items < max_items ? items : max_items;
+    }
+}
+
+struct MoeGroupedParams {
+    const int* item_expert; const int* item_routes; const int* num_items;
+    int T, top_k, H, I;
+    const uint8_t *w13, *s13; const float* g13;        // [E, 2I, H/2], [E, 2I, H/16], [E, 2]
+    const uint8_t *sw13, *ss13; const float* sg13;     // shared stack or null
+    const uint8_t *w2, *s2; const float* g2;           // [E, H, I/2], [E, H, I/16], [E]
+    const uint8_t *sw2, *ss2; const float* sg2;
+    const uint4* xp;                                   // permuted x, [Tpad rows][H]
+    uint4* act_perm;                                   // permuted act, [routes_pad][I] f16
+    float* y_route;                                    // [routes, H]
+};
+
+// grid (ceil(I/16 / tiles_per_block), max_items).  Warp = (tile, kpart): gate rows i0..i0+15 and up rows I+i0.. .
+__global__ void __launch_bounds__(256) moe_gate_up_mma_kernel(MoeGroupedParams p, int ksplit) {
+    extern __shared__ float red[];                 // [8 warps][2 tiles][8 tok][16 rows]
+    const int item = blockIdx.y;
+    if (item >= *p.num_items) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
+    const int tiles_per_block = 8 / ksplit, tile = warp / ksplit, kpart = warp % ksplit;
+    const int i0 = (blockIdx.x * tiles_per_block + tile) * 16;
+    const int e = p.item_expert[item];
+    const uint8_t* W = e < 0 ? p.sw13 : p.w13 + (size_t)e * 2 * p.I * (p.H / 2);
+    const uint8_t* S = e < 0 ? p.ss13 : p.s13 + (size_t)e * 2 * p.I * (p.H / 16);
+    const float* G = e < 0 ? p.sg13 : p.g13 + (size_t)e * 2;
+    const int n_routed = p.T * p.top_k;
+    const int route_g = p.item_routes[item * kItemRoutes + g];
+    int tok[1];
+    tok[0] = route_g < 0 ? 0 : (route_g < n_routed ? route_g / p.top_k : route_g - n_routed);
+    float acc[2][1][4];
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt) acc[mt][0][0] = acc[mt][0][1] = acc[mt][0][2] = acc[mt][0][3] = 0.f;
+    if (i0 < p.I) {
+        const int row0[2] = {i0, p.I + i0};
+        const int v = min(16, p.I - i0);
+        const int valid[2] = {v, v};
+        warp_rows_times_tokens<2, 1>(acc, W, S, p.H / 2, p.H / 16, row0, valid, p.H, p.xp, tok, kpart, ksplit);
+    }
+    float* mine = red + (size_t)warp * (2 * 8 * 16);
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt) {
+        mine[(mt * 8 + 2 * c) * 16 + g] = acc[mt][0][0];
+        mine[(mt * 8 + 2 * c + 1) * 16 + g] = acc[mt][0][1];
+        mine[(mt * 8 + 2 * c) * 16 + g + 8] = acc[mt][0][2];
+        mine[(mt * 8 + 2 * c + 1) * 16 + g + 8] = acc[mt][0][3];
+    }
+    __syncthreads();
+    const float gg = G[0], gu = G[1];
+    const int Gd = p.I / 128;
+    __half* act = reinterpret_cast<__half*>(p.act_perm);
+    for (int idx = threadIdx.x; idx < tiles_per_block * 8 * 16; idx += blockDim.x) {
+        const int tl = idx / 128, rem = idx % 128, slot = rem / 16, r = rem % 16;
+        const int i = (blockIdx.x * tiles_per_block + tl) * 16 + r;
+        const int route = p.item_routes[item * kItemRoutes + slot];
+        if (route < 0 || i >= p.I) continue;
+        float gs = 0.f, us = 0.f;
+        for (int kp = 0; kp < ksplit; ++kp) {
+            const float* w = red + (size_t)(tl * ksplit + kp) * (2 * 8 * 16);
+            gs += w[(0 * 8 + slot) * 16 + r];
+            us += w[(1 * 8 + slot) * 16 + r];
+        }
+        gs *= gg; us *= gu;
+        const float a = gs / (1.f + __expf(-gs)) * us;
+        const int w128 = i % 128, cc = w128 / 32, jj = (w128 % 32) / 8, ee = w128 % 8;
+        act[((((size_t)route * Gd + i / 128) * 16 + jj * 4 + cc) * 8) + ee] = __float2half(a);
+    }
+}
+
+// grid (ceil(H/16 / tiles_per_block), max_items).  B operand rows = the item's routes (their act rows).
+__global__ void __launch_bounds__(256) moe_down_mma_kernel(MoeGroupedParams p, int ksplit) {
+    extern __shared__ float red[];                 // [8 warps][8 tok][16 rows]
+    const int item = blockIdx.y;
+    if (item >= *p.num_items) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
+    const int tiles_per_block = 8 / ksplit, tile = warp / ksplit, kpart = warp % ksplit;
+    const int n0 = (blockIdx.x * tiles_per_block + tile) * 16;
+    const int e = p.item_expert[item];
+    const uint8_t* W = e < 0 ? p.sw2 : p.w2 + (size_t)e * p.H * (p.I / 2);
+    const uint8_t* S = e < 0 ? p.ss2 : p.s2 + (size_t)e * p.H * (p.I / 16);
+    const float gs = e < 0 ? p.sg2[0] : p.g2[e];
+    const int route_g = p.item_routes[item * kItemRoutes + g];
+    int tok[1];
+    tok[0] = route_g < 0 ? 0 : route_g;
+    float acc[1][1][4] = {{{0.f, 0.f, 0.f, 0.f}}};
+    if (n0 < p.H) {
+        const int row0[1] = {n0};
+        const int valid[1] = {min(16, p.H - n0)};
+        warp_rows_times_tokens<1, 1>(acc, W, S, p.I / 2, p.I / 16, row0, valid, p.I, p.act_perm, tok, kpart, ksplit);
+    }
+    float* mine = red + (size_t)warp * (8 * 16);
+    mine[(2 * c) * 16 + g] = acc[0][0][0];
+    mine[(2 * c + 1) * 16 + g] = acc[0][0][1];
+    mine[(2 * c) * 16 + g + 8] = acc[0][0][2];
+    mine[(2 * c + 1) * 16 + g + 8] = acc[0][0][3];
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < tiles_per_block * 8 * 16; idx += blockDim.x) {
+        const int tl = idx / 128, rem = idx % 128, slot = rem / 16, r = rem % 16;
+        const int n = (blockIdx.x * tiles_per_block + tl) * 16 + r;
+        const int route = p.item_routes[item * kItemRoutes + slot];
+        if (route < 0 || n >= p.H) continue;
+        float v = 0.f;
+        for (int kp = 0; kp < ksplit; ++kp) v += red[(size_t)(tl * ksplit + kp) * (8 * 16) + rem];
+        p.y_route[(size_t)route * p.H + n] = v * gs;
+    }
+}
+
+// out[t, n] = sum_j wt[t,j] * y_route[t*k+j, n] (local experts only) + y_route[T*k + t, n]
+__global__ void moe_route_reduce_kernel(const float* __restrict__ y_route, const int* __restrict__ ids, const float* __restrict__ wts,
+                                        int T, int top_k, int H, int expert_offset, int num_local, int has_shared,
+                                        float* __restrict__ out, int use_push, PushCtx push) {
+    const int t = blockIdx.y;
+    for (int n = blockIdx.x * blockDim.x + threadIdx.x; n < H; n += gridDim.x * blockDim.x) {
+        float v = 0.f;
+        for (int j = 0; j < top_k; ++j) {
+            const int e = ids[t * top_k + j] - expert_offset;
+            if (e >= 0 && e < num_local) v += wts[t * top_k + j] * y_route[(size_t)(t * top_k + j) * H + n];
+        }
+        if (has_shared) v += y_route[(size_t)(T * top_k + t) * H + n];
+        if (use_push) {
+            for (int pr = 0; pr < push.world; ++pr) *push_dst(push, pr, t, n) = v;
+        } else {
+            out[(size_t)t * H + n] = v;
+        }
+    }
+    if (use_push) push_finish(push, gridDim.x * gridDim.y);
+}
+
+int pick_ksplit(int K, int min_groups_per_warp) {
+    int ks = 8;
+    while (ks > 1 && (K / 128) / ks < min_groups_per_warp) ks >>= 1;
+    return ks;
+}
+
+}  // namespace
+
+struct MoeGroupedArgs {
+    const void* x; int ldx;
+    const void* ids; const void* wts;
+    int T, top_k, H, I, expert_offset, num_local;
+    const void *w13, *s13, *g13, *sw13, *ss13, *sg13;
+    const void *w2, *s2, *g2, *sw2, *ss2, *sg2;
+    // caller-owned scratch
+    void* xp;            // f16 [ceil(T/8)*8, H]
+    void* act_perm;      // f16 [routes + 8, I]
+    void* y_route;       // f32 [routes, H]
+    void* plan;          // int32 [max_items * 9 + 1]
+    int max_items;
+    void* out;           // f32 [T, H] (ignored when pushing)
+};
+
+// Decode-time MoE layer for T <= 32 tokens: plan, gate/up, down, weighted reduce (optionally pushed to
+// every rank's receive slot as the producer half of the fused all-reduce).  H % 128 == 0, I % 128 == 0.
+SL_API int sl_moe_grouped_mma(const MoeGroupedArgs* a, const PushCtx* push, cudaStream_t s) {
+    if (a->T == 0) return 0;
+    if (a->T > 32 || a->H % 128 != 0 || a->I % 128 != 0 || a->ldx % 8 != 0 || a->T * a->top_k > 480) return -1;
+    if (push != nullptr && (a->T > push->slot_rows || a->H > push->row_len)) return -1;
+    const int has_shared = a->sw13 != nullptr;
+    const int n_routed = a->T * a->top_k;
+    int* plan = (int*)a->plan;
+    MoePlanView pv{plan, plan + a->max_items, plan + a->max_items * (1 + kItemRoutes)};
+    moe_plan_kernel<<<1, 512, (size_t)2 * (n_routed + 8) * sizeof(int), s>>>(pv, (const int*)a->ids, a->T, a->top_k, a->expert_offset,
+                                                                           a->num_local, has_shared, a->max_items);
+    const int tpad = (a->T + 7) / 8 * 8;
+    const int units = tpad * (a->H / 8);
+    permute_x_kernel<<<(units + 255) / 256, 256, 0, s>>>((uint4*)a->xp, (const bf16*)a->x, a->T, tpad, a->H, a->ldx);
+    MoeGroupedParams p{pv.item_expert, pv.item_routes, pv.num_items, a->T, a->top_k, a->H, a->I,
+                       (const uint8_t*)a->w13, (const uint8_t*)a->s13, (const float*)a->g13,
+                       (const uint8_t*)a->sw13, (const uint8_t*)a->ss13, (const float*)a->sg13,
+                       (const uint8_t*)a->w2, (const uint8_t*)a->s2, (const float*)a->g2,
+                       (const uint8_t*)a->sw2, (const uint8_t*)a->ss2, (const float*)a->sg2,
+                       (const uint4*)a->xp, (uint4*)a->act_perm, (float*)a->y_route};
+    {
+        const int ks = pick_ksplit(a->H, 4), tpb = 8 / ks, tiles = (a->I + 15) / 16;
+        const size_t smem = (size_t)8 * 2 * 8 * 16 * sizeof(float);
+        moe_gate_up_mma_kernel<<<dim3((tiles + tpb - 1) / tpb, a->max_items), 256, smem, s>>>(p, ks);
+    }
+    {
+        const int ks = pick_ksplit(a->I, 4), tpb = 8 / ks, tiles = (a->H + 15) / 16;
+        const size_t smem = (size_t)8 * 8 * 16 * sizeof(float);
+        moe_down_mma_kernel<<<dim3((tiles + tpb - 1) / tpb, a->max_items), 256, smem, s>>>(p, ks);
+    }
+    int bx = (a->H + 255) / 256;
+    moe_route_reduce_kernel<<<dim3(bx, a->T), 256, 0, s>>>((const float*)a->y_route, (const int*)a->ids, (const float*)a->wts, a->T,
+                                                          a->top_k, a->H, a->expert_offset, a->num_local, has_shared,
+                                                          (float*)a->out, push ? 1 : 0, push ? *push : PushCtx{});
+    return (int)cudaGetLastError();
 }

@@ -278,6 +278,8 @@ class CudaOps:
         k = ids.shape[1]
         I = experts.inter
         routes = T * k + (T if shared is not None else 0)
+        if H % 128 == 0 and I % 128 == 0 and x.stride(0) % 8 == 0 and T * k <= 480:
+            return self._moe_grouped(x, experts, shared, ids, wts, sink)
         act = torch.empty(routes, I, dtype=torch.bfloat16, device=x.device)
         gp = N.MoeGateUpParams(x=x.data_ptr(), ldx=x.stride(0), ids=ids.data_ptr(), T=T, top_k=k, H=H, I=I,
                                expert_offset=experts.expert_offset, num_local=experts.num_experts,
@@ -296,6 +298,37 @@ class CudaOps:
             N.call("sl_moe_down_push", C.byref(dp), C.byref(sink.push), N.stream())
             return sink
         N.call("sl_moe_down", C.byref(dp), N.stream())
+        return out
+
+    def _moe_grouped(self, x, experts, shared, ids, wts, sink=None):
+        """Tensor-core weight streaming: routes that share an expert form one work item, so each
+        chosen expert's weights are read once per step."""
+        T, H = x.shape
+        k = ids.shape[1]
+        I = experts.inter
+        dev = x.device
+        routes = T * k + (T if shared is not None else 0)
+        max_items = T * k + (T + 7) // 8
+        xp = torch.empty(((T + 7) // 8) * 8 * H, dtype=torch.float16, device=dev)
+        act = torch.empty((routes + 8) * I, dtype=torch.float16, device=dev)
+        y_route = torch.empty(routes, H, dtype=torch.float32, device=dev)
+        plan = torch.empty(max_items * 9 + 1, dtype=torch.int32, device=dev)
+        out = None if sink is not None else torch.empty(T, H, dtype=torch.float32, device=dev)
+        a = N.MoeGroupedArgs(x=x.data_ptr(), ldx=x.stride(0), ids=ids.data_ptr(), wts=wts.data_ptr(), T=T, top_k=k, H=H, I=I,
+                             expert_offset=experts.expert_offset, num_local=experts.num_experts,
+                             w13=experts.w13.data_ptr(), s13=experts.s13.data_ptr(), g13=experts.g13.data_ptr(),
+                             sw13=N.ptr(shared.w13) if shared else 0, ss13=N.ptr(shared.s13) if shared else 0,
+                             sg13=N.ptr(shared.g13) if shared else 0,
+                             w2=experts.w2.data_ptr(), s2=experts.s2.data_ptr(), g2=experts.g2.data_ptr(),
+                             sw2=N.ptr(shared.w2) if shared else 0, ss2=N.ptr(shared.s2) if shared else 0,
+                             sg2=N.ptr(shared.g2) if shared else 0,
+                             xp=xp.data_ptr(), act_perm=act.data_ptr(), y_route=y_route.data_ptr(), plan=plan.data_ptr(),
+                             max_items=max_items, out=N.ptr(out))
+        if sink is not None:
+            sink.pushed_rows = T
+            N.call("sl_moe_grouped_mma", C.byref(a), C.cast(C.byref(sink.push), C.c_void_p), N.stream())
+            return sink
+        N.call("sl_moe_grouped_mma", C.byref(a), None, N.stream())
         return out
 
     def moe_tp(self, x, lw, sink=None):

@@ -109,6 +109,13 @@ class MoeDownParams(C.Structure):
                 ("sg2", vp), ("out", vp), ("out_f32", i32), ("accumulate", i32)]
 
 
+class MoeGroupedArgs(C.Structure):
+    _fields_ = [("x", vp), ("ldx", i32), ("ids", vp), ("wts", vp), ("T", i32), ("top_k", i32), ("H", i32), ("I", i32),
+                ("expert_offset", i32), ("num_local", i32), ("w13", vp), ("s13", vp), ("g13", vp), ("sw13", vp), ("ss13", vp),
+                ("sg13", vp), ("w2", vp), ("s2", vp), ("g2", vp), ("sw2", vp), ("ss2", vp), ("sg2", vp), ("xp", vp),
+                ("act_perm", vp), ("y_route", vp), ("plan", vp), ("max_items", i32), ("out", vp)]
+
+
 class SampleParams(C.Structure):
     _fields_ = [("logits", vp), ("V", i32), ("ld", i32), ("temperature", vp), ("top_p", vp), ("rep_penalty", vp),
                 ("presence_penalty", vp), ("top_k", vp), ("history", vp), ("hist_len", vp), ("window", i32),
@@ -146,6 +153,7 @@ _SIGS = {
     "sl_sample": [C.POINTER(SampleParams), i32, vp],
     "sl_spec_reject": [C.POINTER(SpecRejectParams), i32, vp],
     "sl_advance_counter": [vp, u32, vp],
+    "sl_moe_grouped_mma": [C.POINTER(MoeGroupedArgs), vp, vp],
     "sl_linear_nvfp4_mma": [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp],
     "sl_linear_smallT_bf16_tcgen05": [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp, vp],
     "sl_gemm_bf16_tcgen05": [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp, i32, vp],
