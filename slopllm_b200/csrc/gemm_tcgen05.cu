@@ -30,7 +30,8 @@ template <int BN>
 __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA,
                                                         const __grid_constant__ CUtensorMap tmB, void* __restrict__ C,
                                                         int M, int N, int K, int ldc, int out_f32, int transpose_out,
-                                                        int* __restrict__ err, int use_push, PushCtx push) {
+                                                        int* __restrict__ err, int use_push, PushCtx push,
+                                                        const int4* __restrict__ tiles, const int* __restrict__ num_tiles) {
     using Cfg = GemmCfg<BN>;
     constexpr int STAGES = Cfg::STAGES;
     extern __shared__ uint8_t smem_raw[];
@@ -43,7 +44,15 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
     uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tmem_full + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    // Plain GEMM: tile (blockIdx.y, blockIdx.x).  Grouped GEMM: blockIdx.x indexes a tile table whose
+    // entries are {first A row, end of the group's A rows, first B row of the group, output column};
+    // rows at or beyond the group's end belong to the next group and are not stored.
+    int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN, b_row0 = n0, m_end = M;
+    if (tiles != nullptr) {
+        if ((int)blockIdx.x >= *num_tiles) return;
+        const int4 t = tiles[blockIdx.x];
+        m0 = t.x; m_end = t.y; b_row0 = t.z + t.w; n0 = t.w;
+    }
     const int num_kb = (K + BK - 1) / BK;
 
     if (warp == 0 && lane == 0) {
@@ -70,7 +79,7 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
                 if (!tc::mbar_wait(&empty[s], ph ^ 1)) { atomicExch(err, 1); break; }
                 tc::mbar_expect_tx(&full[s], Cfg::A_BYTES + Cfg::B_BYTES);
                 tc::tma_load_2d(sA + s * Cfg::A_BYTES, &tmA, &full[s], kb * BK, m0);
-                tc::tma_load_2d(sB + s * Cfg::B_BYTES, &tmB, &full[s], kb * BK, n0);
+                tc::tma_load_2d(sB + s * Cfg::B_BYTES, &tmB, &full[s], kb * BK, b_row0);
             }
         }
     } else if (warp == 1) {
@@ -116,7 +125,7 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
                             else ((bf16*)C)[(size_t)(col + i) * ldc + row] = __float2bfloat16(__uint_as_float(r[i]));
                         }
                     }
-                } else if (row < M && col < N) {
+                } else if (row < m_end && col < N) {
                     if (out_f32) {
                         float* dst = (float*)C + (size_t)row * ldc + col;
                         if (col + 32 <= N) {
@@ -157,11 +166,12 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
 
 template <int BN>
 int launch(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc, int out_f32,
-           int transpose_out, int* err, cudaStream_t s, const PushCtx* push = nullptr) {
+           int transpose_out, int* err, cudaStream_t s, const PushCtx* push = nullptr, const int4* tiles = nullptr,
+           const int* num_tiles = nullptr, int max_tiles = 0, int b_rows = 0) {
     CUtensorMap tmA, tmB;
     int rc = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)M, (uint64_t)K, (uint64_t)lda * 2, BM, BK);
     if (rc) return rc;
-    rc = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)N, (uint64_t)K, (uint64_t)ldb * 2, BN, BK);
+    rc = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)(b_rows ? b_rows : N), (uint64_t)K, (uint64_t)ldb * 2, BN, BK);
     if (rc) return rc;
     auto kern = gemm_bf16_kernel<BN>;
     static bool attr_set = false;
@@ -170,8 +180,9 @@ int launch(const void* A, const void* B, void* C, int M, int N, int K, int lda, 
         attr_set = true;
     }
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+    if (tiles != nullptr) grid = dim3(max_tiles, 1);
     kern<<<grid, 192, GemmCfg<BN>::SMEM, s>>>(tmA, tmB, C, M, N, K, ldc, out_f32, transpose_out, err, push ? 1 : 0,
-                                              push ? *push : PushCtx{});
+                                              push ? *push : PushCtx{}, tiles, num_tiles);
     return (int)cudaGetLastError();
 }
 
@@ -205,4 +216,47 @@ SL_API int sl_linear_smallT_bf16_tcgen05_push(const void* x, const void* W, int 
     if (T <= 0 || N <= 0 || K <= 0) return 0;
     if (push == nullptr || T > 32 || K % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0 || T > push->slot_rows || N > push->row_len) return -1;
     return launch<32>(W, x, nullptr, N, T, K, ldw, ldx, 0, 1, 1, (int*)err, s, push);
+}
+
+// Grouped GEMM over row groups of A (tokens sorted by expert): group g owns A rows [off[g], off[g+1]) and B rows
+// [g*N, (g+1)*N) of the stacked weight matrix B [groups*N, K].  `tiles` is a device table of at most `max_tiles`
+// entries {m0, group row end, g*N, n0} built by sl_build_group_tiles, `num_tiles` its length on the device.
+// C [M, N] row-major.  Replaces the reference's sort + `grouped_mma_kernel` (`csrc/glm_mma_moe.cu:110-460`).
+SL_API int sl_grouped_gemm_bf16_tcgen05(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
+                                        int out_f32, int groups, const void* tiles, const void* num_tiles, int max_tiles,
+                                        void* err, cudaStream_t s) {
+    if (M <= 0 || N <= 0 || K <= 0 || max_tiles <= 0) return 0;
+    if (K % 8 != 0 || lda % 8 != 0 || ldb % 8 != 0 || (out_f32 ? ldc % 4 : ldc % 8) != 0) return -1;
+    return launch<128>(A, B, C, M, N, K, lda, ldb, ldc, out_f32, 0, (int*)err, s, nullptr, (const int4*)tiles,
+                       (const int*)num_tiles, max_tiles, groups * N);
+}
+
+// offsets [groups + 1] (device, int32) -> tile table.  One thread per group enumerates its (row tile, column tile) pairs
+// at a position given by a prefix sum over the groups' tile counts.
+__global__ void build_group_tiles_kernel(int4* __restrict__ tiles, int* __restrict__ num_tiles, const int* __restrict__ offsets,
+                                         int groups, int N, int max_tiles) {
+    __shared__ int base[1025];
+    const int g = threadIdx.x;
+    const int ncol = (N + 127) / 128;
+    int mine = 0;
+    if (g < groups) mine = ((offsets[g + 1] - offsets[g] + 127) / 128) * ncol;
+    base[g + 1] = mine;
+    if (g == 0) base[0] = 0;
+    __syncthreads();
+    if (g == 0) for (int i = 1; i <= groups; ++i) base[i] += base[i - 1];
+    __syncthreads();
+    if (g < groups) {
+        int at = base[g];
+        const int r0 = offsets[g], r1 = offsets[g + 1];
+        for (int m = r0; m < r1; m += 128)
+            for (int c = 0; c < ncol; ++c, ++at)
+                if (at < max_tiles) tiles[at] = make_int4(m, r1, g * N, c * 128);
+    }
+    if (g == 0) *num_tiles = min(base[groups], max_tiles);
+}
+
+SL_API int sl_build_group_tiles(void* tiles, void* num_tiles, const void* offsets, int groups, int N, int max_tiles, cudaStream_t s) {
+    if (groups <= 0 || groups > 1024) return -1;
+    build_group_tiles_kernel<<<1, 1024, 0, s>>>((int4*)tiles, (int*)num_tiles, (const int*)offsets, groups, N, max_tiles);
+    return (int)cudaGetLastError();
 }

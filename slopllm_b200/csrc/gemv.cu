@@ -456,3 +456,71 @@ SL_API int sl_moe_down_push(const MoeDownParams* p, const PushCtx* push, cudaStr
     moe_down_kernel<<<dim3(bx, p->T), 256, smem, s>>>(*p, 1, *push);
     return SL_LAUNCH_CHECK();
 }
+
+// ---------------------------------------------------------------------------------------------
+// NVFP4 -> bf16 expansion of stacked matrices: out[m, n, k] = e2m1 * e4m3 block scale * global scale, where the
+// global scale of row n of matrix m is g[m * g_per + (n >= split ? 1 : 0)] (gate / up halves of a fused W13).
+// Feeds the tcgen05 grouped GEMMs of the prefill path.  grid-stride over 32-value groups.
+__global__ void nvfp4_dequant_bf16_kernel(bf16* __restrict__ out, const uint8_t* __restrict__ Wp, const uint8_t* __restrict__ S,
+                                          const float* __restrict__ g, int mats, int N, int K, int g_per, int split) {
+    const size_t groups = (size_t)mats * N * (K / 32);
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < groups; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t row = i / (K / 32);
+        const int kg = (int)(i % (K / 32));
+        const int m = (int)(row / N), n = (int)(row % N);
+        const float gs = g ? g[(size_t)m * g_per + ((g_per > 1 && n >= split) ? 1 : 0)] : 1.f;
+        const uint4 w = ldg_nc_16(Wp + row * (K / 2) + kg * 16);
+        const float2 sc = e4m3x2_to_float2(*reinterpret_cast<const uint16_t*>(S + row * (K / 16) + kg * 2));
+        const uint32_t words[4] = {w.x, w.y, w.z, w.w};
+        uint32_t o[16];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            __half2 h[4];
+            e2m1x8_to_half2x4(words[q], h);
+            const float s = (q < 2 ? sc.x : sc.y) * gs;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 f = __half22float2(h[j]);
+                o[q * 4 + j] = f2_to_bf162(f.x * s, f.y * s);
+            }
+        }
+        uint4* dst = reinterpret_cast<uint4*>(out + row * K + kg * 32);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) dst[q] = make_uint4(o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
+    }
+}
+
+SL_API int sl_nvfp4_dequant_bf16(void* out, const void* Wp, const void* S, const void* g, int mats, int N, int K, int g_per,
+                                 int split, cudaStream_t s) {
+    if (mats == 0 || N == 0) return 0;
+    if (K % 32 != 0) return -1;
+    const size_t groups = (size_t)mats * N * (K / 32);
+    int blocks = (int)((groups + 255) / 256);
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    nvfp4_dequant_bf16_kernel<<<blocks, 256, 0, s>>>((bf16*)out, (const uint8_t*)Wp, (const uint8_t*)S, (const float*)g, mats, N, K,
+                                                     g_per, split);
+    return SL_LAUNCH_CHECK();
+}
+
+// out[tok[r], :] += w[r] * y[r, :]   (weighted scatter of expert-sorted rows back to token order; fp32 atomics-free
+// because each block owns one output token: rows of a token are found through `token_rows` [T, k] indices)
+__global__ void moe_unsort_reduce_kernel(float* __restrict__ out, const float* __restrict__ y, const int* __restrict__ rows_of,
+                                         const float* __restrict__ wts, int k, int H, int accumulate) {
+    const int t = blockIdx.y;
+    for (int n = blockIdx.x * blockDim.x + threadIdx.x; n < H; n += gridDim.x * blockDim.x) {
+        float v = accumulate ? out[(size_t)t * H + n] : 0.f;
+        for (int j = 0; j < k; ++j) {
+            const int r = rows_of[t * k + j];
+            if (r >= 0) v += wts[t * k + j] * y[(size_t)r * H + n];
+        }
+        out[(size_t)t * H + n] = v;
+    }
+}
+
+SL_API int sl_moe_unsort_reduce(void* out, const void* y, const void* rows_of, const void* wts, int T, int k, int H, int accumulate,
+                                cudaStream_t s) {
+    if (T == 0) return 0;
+    moe_unsort_reduce_kernel<<<dim3((H + 255) / 256, T), 256, 0, s>>>((float*)out, (const float*)y, (const int*)rows_of,
+                                                                     (const float*)wts, k, H, accumulate);
+    return SL_LAUNCH_CHECK();
+}

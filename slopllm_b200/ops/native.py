@@ -156,6 +156,10 @@ _SIGS = {
     "sl_moe_grouped_mma": [C.POINTER(MoeGroupedArgs), vp, vp],
     "sl_linear_nvfp4_mma": [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp],
     "sl_linear_smallT_bf16_tcgen05": [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp, vp],
+    "sl_grouped_gemm_bf16_tcgen05": [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, vp, vp, i32, vp, vp],
+    "sl_build_group_tiles": [vp, vp, vp, i32, i32, i32, vp],
+    "sl_nvfp4_dequant_bf16": [vp, vp, vp, vp, i32, i32, i32, i32, i32, vp],
+    "sl_moe_unsort_reduce": [vp, vp, vp, vp, i32, i32, i32, i32, vp],
     "sl_gemm_bf16_tcgen05": [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp, i32, vp],
 }
 
