@@ -33,6 +33,7 @@ struct RecvCtx {
 __global__ void __launch_bounds__(1024) ar_add_rmsnorm_kernel(RecvCtx c, bf16* __restrict__ out, float* __restrict__ res_out,
                                                               const float* __restrict__ res_in, const bf16* __restrict__ w,
                                                               int H, float eps) {
+    pdl_grid_sync();
     __shared__ float scratch[33];
     const int t = blockIdx.x, nt = blockDim.x, n4 = H / 4;
     const uint32_t target = *c.epoch + 1u;
@@ -93,13 +94,14 @@ SL_API int sl_ar_add_rmsnorm(const RecvCtx* c, void* out, void* res_out, const v
     int threads = ((H / 4 + 3) / 4 + 31) / 32 * 32;
     if (threads < 128) threads = 128;
     if (threads > 1024) threads = 1024;
-    ar_add_rmsnorm_kernel<<<T, threads, 0, s>>>(*c, (bf16*)out, (float*)res_out, (const float*)res_in, (const bf16*)w, H, eps);
+    sl_launch(ar_add_rmsnorm_kernel, T, threads, 0, s, *c, (bf16*)out, (float*)res_out, (const float*)res_in, (const bf16*)w, H, eps);
     return SL_LAUNCH_CHECK();
 }
 
 // ---------------------------------------------------------------------------------------------
 // Plain push of an existing fp32 [T, row_len] tensor (producers that are not fused yet, and tests).
 __global__ void push_rows_kernel(PushCtx c, const float* __restrict__ x, int T, int N) {
+    pdl_grid_sync();
     const size_t total = (size_t)T * N;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const int row = (int)(i / N), col = (int)(i % N);
@@ -114,7 +116,7 @@ SL_API int sl_push_rows(const PushCtx* c, const void* x, int T, int N, cudaStrea
     if (T > c->slot_rows || N > c->row_len) return -1;
     int blocks = (int)(((size_t)T * N + 255) / 256);
     if (blocks > 148) blocks = 148;
-    push_rows_kernel<<<blocks, 256, 0, s>>>(*c, (const float*)x, T, N);
+    sl_launch(push_rows_kernel, blocks, 256, 0, s, *c, (const float*)x, T, N);
     return SL_LAUNCH_CHECK();
 }
 
@@ -124,6 +126,7 @@ SL_API int sl_push_rows(const PushCtx* c, const void* x, int T, int N, cudaStrea
 struct PtrTable { uint32_t* p[SL_MAX_RANKS]; };
 __global__ void flag_barrier_kernel_v(PtrTable peers, uint32_t* local_flags, int rank, int world, uint32_t value,
                                       uint32_t max_spins, int* status) {
+    pdl_grid_sync();
     const int p = threadIdx.x;
     if (p < world) {
         __threadfence_system();
@@ -144,6 +147,7 @@ SL_API int sl_flag_barrier(void* const* peer_flags, void* local_flags, int rank,
 // A wait that nothing satisfies, used by the tests of the timeout path: returns after max_spins
 // polls with the status record filled in.
 __global__ void wait_only_kernel(const uint32_t* flag, uint32_t target, uint32_t max_spins, int* status) {
+    pdl_grid_sync();
     if (threadIdx.x == 0) wait_flag_geq(flag, target, max_spins, status, 3);
 }
 SL_API int sl_wait_flag(const void* flag, unsigned target, unsigned max_spins, void* status, cudaStream_t s) {
@@ -165,6 +169,7 @@ struct CpPushCtx {
 };
 
 __global__ void cp_merge_push_kernel(CpPushCtx c, const float* __restrict__ o, const float* __restrict__ lse, int T) {
+    pdl_grid_sync();
     // grid (h, T): one block per (head, token)
     const int head = blockIdx.x, t = blockIdx.y;
     const int owner = head / c.hl, hh = head % c.hl;
@@ -188,13 +193,14 @@ __global__ void cp_merge_push_kernel(CpPushCtx c, const float* __restrict__ o, c
 SL_API int sl_cp_merge_push(const CpPushCtx* c, const void* o, const void* lse, int T, cudaStream_t s) {
     if (T == 0) return 0;
     if (T > c->Tmax || c->R % 4 != 0) return -1;
-    cp_merge_push_kernel<<<dim3(c->h, T), 128, 0, s>>>(*c, (const float*)o, (const float*)lse, T);
+    sl_launch(cp_merge_push_kernel, dim3(c->h, T), 128, 0, s, *c, (const float*)o, (const float*)lse, T);
     return SL_LAUNCH_CHECK();
 }
 
 // Owner side: wait for all ranks, then the combine kernel (csrc/sparse_mla.cu) merges the world
 // staged partials per local head.  This kernel only waits and closes the epoch.
 __global__ void epoch_wait_kernel(const uint32_t* flags, uint32_t* epoch, int world, uint32_t max_spins, int* status, int site) {
+    pdl_grid_sync();
     const uint32_t target = *epoch + 1u;
     if (threadIdx.x < world) wait_flag_geq(flags + threadIdx.x, target, max_spins, status, site);
     __syncthreads();
@@ -219,6 +225,7 @@ struct GatherPushCtx {
 };
 
 __global__ void gather_push_kernel(GatherPushCtx c, const uint4* __restrict__ src, size_t n16) {
+    pdl_grid_sync();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += (size_t)gridDim.x * blockDim.x) {
         const uint4 v = src[i];
         for (int p = 0; p < c.world; ++p) reinterpret_cast<uint4*>(c.bufs[p] + (size_t)c.rank * c.slot_bytes)[i] = v;
@@ -242,7 +249,7 @@ SL_API int sl_gather_push(const GatherPushCtx* c, const void* src, size_t bytes,
     const size_t n16 = bytes / 16;
     int blocks = (int)((n16 + 255) / 256);
     if (blocks > 148) blocks = 148;
-    gather_push_kernel<<<blocks, 256, 0, s>>>(*c, (const uint4*)src, n16);
+    sl_launch(gather_push_kernel, blocks, 256, 0, s, *c, (const uint4*)src, n16);
     return SL_LAUNCH_CHECK();
 }
 

@@ -16,6 +16,40 @@ typedef __nv_bfloat162 bf162;
 
 #define SL_LAUNCH_CHECK() (int)cudaGetLastError()
 
+// ---- programmatic dependent launch ------------------------------------------------------------
+// Every kernel starts with pdl_grid_sync(): it first lets the next kernel in the stream be
+// scheduled (its blocks become resident and park in their own pdl_grid_sync), then waits until
+// the kernels it depends on have finished and their writes are visible.  Nothing that reads or
+// writes activation memory may precede it.  On a launch without the programmatic attribute both
+// instructions do nothing.
+#ifndef SL_PDL_EARLY_TRIGGER
+#define SL_PDL_EARLY_TRIGGER 0
+#endif
+__device__ __forceinline__ void pdl_grid_sync() {
+#if SL_PDL_EARLY_TRIGGER
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+#endif
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+// Process-wide switch (sl_set_pdl); on by default.
+extern int g_sl_pdl_enabled;
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t sl_launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_sl_pdl_enabled ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

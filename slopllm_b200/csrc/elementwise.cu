@@ -6,11 +6,17 @@
 // `csrc/glm_indexer.cu:303-376,1338` (topk_to_slots, indexer Q quantise), fused along the
 // data flow of one decoder layer.
 #include "common.cuh"
+#include "route.cuh"
+
+int g_sl_pdl_enabled = 1;
+// Turns programmatic dependent launch of the library's kernels on or off (process-wide).
+SL_API void sl_set_pdl(int enabled) { g_sl_pdl_enabled = enabled ? 1 : 0; }
 
 // ---------------------------------------------------------------------------------------------
 // embedding lookup: out[t, :] = table[ids[t], :]
 __global__ void embed_kernel(bf16* __restrict__ out, const int64_t* __restrict__ ids, const bf16* __restrict__ table,
                              int H, int V) {
+    pdl_grid_sync();
     const int t = blockIdx.x;
     int64_t id = ids[t];
     id = id < 0 ? 0 : (id >= V ? V - 1 : id);      // never read outside the table
@@ -21,7 +27,7 @@ __global__ void embed_kernel(bf16* __restrict__ out, const int64_t* __restrict__
 
 SL_API int sl_embed(void* out, const void* ids, const void* table, int T, int H, int V, cudaStream_t s) {
     if (T == 0) return 0;
-    embed_kernel<<<T, 256, 0, s>>>((bf16*)out, (const int64_t*)ids, (const bf16*)table, H, V);
+    sl_launch(embed_kernel, T, 256, 0, s, (bf16*)out, (const int64_t*)ids, (const bf16*)table, H, V);
     return SL_LAUNCH_CHECK();
 }
 
@@ -34,6 +40,7 @@ template <bool XF32>
 __global__ void __launch_bounds__(1024) add_rmsnorm_kernel(bf16* __restrict__ out, float* __restrict__ res_out,
                                                            const void* __restrict__ xin, const float* __restrict__ res_in,
                                                            const bf16* __restrict__ w, int H, float eps) {
+    pdl_grid_sync();
     __shared__ float scratch[33];
     const int t = blockIdx.x, nt = blockDim.x, n4 = H / 4;
     float4 v[4];
@@ -83,9 +90,9 @@ SL_API int sl_add_rmsnorm(void* out, void* res_out, const void* x, const void* r
     if (threads < 128) threads = 128;
     if (threads > 1024) threads = 1024;
     if (x_f32)
-        add_rmsnorm_kernel<true><<<T, threads, 0, s>>>((bf16*)out, (float*)res_out, x, (const float*)res_in, (const bf16*)w, H, eps);
+        sl_launch(add_rmsnorm_kernel<true>, T, threads, 0, s, (bf16*)out, (float*)res_out, x, (const float*)res_in, (const bf16*)w, H, eps);
     else
-        add_rmsnorm_kernel<false><<<T, threads, 0, s>>>((bf16*)out, (float*)res_out, x, (const float*)res_in, (const bf16*)w, H, eps);
+        sl_launch(add_rmsnorm_kernel<false>, T, threads, 0, s, (bf16*)out, (float*)res_out, x, (const float*)res_in, (const bf16*)w, H, eps);
     return SL_LAUNCH_CHECK();
 }
 
@@ -103,8 +110,17 @@ __device__ __forceinline__ void rope_pair(float* v, int i, int rope_dim, int pos
     v[ib] = a * sn + b * cs;
 }
 
+// Activation that is either bf16 [T, ld] (n_slabs == 0) or a sum of n_slabs fp32 slabs [T, ld] left by a split-K
+// GEMM; the sum is rounded to bf16 so both forms give the same value.
+__device__ __forceinline__ float load_act(const void* base, int n_slabs, long long slab_stride, size_t idx) {
+    if (n_slabs == 0) return __bfloat162float(reinterpret_cast<const bf16*>(base)[idx]);
+    float v = 0.f;
+    for (int s = 0; s < n_slabs; ++s) v += reinterpret_cast<const float*>(base)[(size_t)s * slab_stride + idx];
+    return __bfloat162float(__float2bfloat16(v));
+}
+
 struct AttnPreParams {
-    const bf16* qkv;          // [T, ld]
+    const void* qkv;          // [T, ld] bf16, or fp32 slabs (see load_act)
     int ld;
     int q_lora, kv_lora, rope_dim, idx_dim, idx_heads;   // idx_dim == 0: no indexer in this layer
     const bf16 *q_norm_w, *kv_norm_w, *idx_ln_w, *idx_ln_b;
@@ -119,29 +135,35 @@ struct AttnPreParams {
     uint8_t* idx_cache;       // [slots, idx_dim + 4]
     bf16* cq_out;             // [T, q_lora]
     float* idx_w_out;         // [T, idx_heads]
+    int n_slabs; long long slab_stride;
 };
 
-// One block per token: q_a RMSNorm; ckv RMSNorm -> fp8 groups; k_pe RoPE; packed row write;
-// indexer key LayerNorm -> RoPE -> fp8 (power-of-two scale) row write; indexer head weights.
+// grid (T, 3): three independent pieces of work per token run as separate blocks.
+//   role 0  c_q = rmsnorm(q_a)
+//   role 1  ckv RMSNorm -> fp8 groups; k_pe RoPE; packed cache row write
+//   role 2  indexer key LayerNorm -> RoPE -> fp8 (power-of-two scale) row write; indexer head weights
 __global__ void attn_pre_kernel(AttnPreParams p) {
+    pdl_grid_sync();
     extern __shared__ float sm[];
     __shared__ float scratch[33];
-    const int t = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
-    const bf16* row = p.qkv + (size_t)t * p.ld;
+    const int t = blockIdx.x, role = blockIdx.y, tid = threadIdx.x, nt = blockDim.x;
+    const size_t row = (size_t)t * p.ld;
     const int pos = p.positions[t];
 
-    // --- c_q = rmsnorm(q_a) ---
-    float ss = 0.f;
-    for (int i = tid; i < p.q_lora; i += nt) {
-        const float v = __bfloat162float(row[i]);
-        sm[i] = v;
-        ss += v * v;
+    if (role == 0) {
+        float ss = 0.f;
+        for (int i = tid; i < p.q_lora; i += nt) {
+            const float v = load_act(p.qkv, p.n_slabs, p.slab_stride, row + i);
+            sm[i] = v;
+            ss += v * v;
+        }
+        ss = block_sum(ss, scratch);
+        const float inv = rsqrtf(ss / (float)p.q_lora + p.eps);
+        for (int i = tid; i < p.q_lora; i += nt)
+            p.cq_out[(size_t)t * p.q_lora + i] = __float2bfloat16(sm[i] * inv * __bfloat162float(p.q_norm_w[i]));
+        return;
     }
-    ss = block_sum(ss, scratch);
-    float inv = rsqrtf(ss / (float)p.q_lora + p.eps);
-    for (int i = tid; i < p.q_lora; i += nt)
-        p.cq_out[(size_t)t * p.q_lora + i] = __float2bfloat16(sm[i] * inv * __bfloat162float(p.q_norm_w[i]));
-    __syncthreads();
+    if (role == 2 && p.idx_dim == 0) return;
 
     // --- where does this token's row live on this rank? ---
     bool owned = true;
@@ -152,26 +174,26 @@ __global__ void attn_pre_kernel(AttnPreParams p) {
     }
     const int page = p.page_table[(size_t)p.batch_idx[t] * p.pt_stride + local / p.page_size];
     const size_t slot = (size_t)page * p.page_size + (local % p.page_size);
+    const size_t kv = row + p.q_lora;
 
-    // --- ckv = rmsnorm(kv_a[:R]) rounded to bf16, k_pe = rope(kv_a[R:R+Dr]) ---
-    const bf16* kv = row + p.q_lora;
-    float* ckv = sm;                         // [kv_lora]
-    float* kpe = sm + p.kv_lora;             // [rope_dim]
-    ss = 0.f;
-    for (int i = tid; i < p.kv_lora; i += nt) {
-        const float v = __bfloat162float(kv[i]);
-        ckv[i] = v;
-        ss += v * v;
-    }
-    for (int i = tid; i < p.rope_dim; i += nt) kpe[i] = __bfloat162float(kv[p.kv_lora + i]);
-    ss = block_sum(ss, scratch);
-    inv = rsqrtf(ss / (float)p.kv_lora + p.eps);
-    for (int i = tid; i < p.kv_lora; i += nt)
-        ckv[i] = __bfloat162float(__float2bfloat16(ckv[i] * inv * __bfloat162float(p.kv_norm_w[i])));
-    if (tid < p.rope_dim / 2) rope_pair(kpe, tid, p.rope_dim, pos, p.theta, p.rope_interleave != 0);
-    __syncthreads();
-
-    if (owned) {
+    if (role == 1) {
+        // --- ckv = rmsnorm(kv_a[:R]) rounded to bf16, k_pe = rope(kv_a[R:R+Dr]) ---
+        float* ckv = sm;                         // [kv_lora]
+        float* kpe = sm + p.kv_lora;             // [rope_dim]
+        float ss = 0.f;
+        for (int i = tid; i < p.kv_lora; i += nt) {
+            const float v = load_act(p.qkv, p.n_slabs, p.slab_stride, kv + i);
+            ckv[i] = v;
+            ss += v * v;
+        }
+        for (int i = tid; i < p.rope_dim; i += nt) kpe[i] = load_act(p.qkv, p.n_slabs, p.slab_stride, kv + p.kv_lora + i);
+        ss = block_sum(ss, scratch);
+        const float inv = rsqrtf(ss / (float)p.kv_lora + p.eps);
+        for (int i = tid; i < p.kv_lora; i += nt)
+            ckv[i] = __bfloat162float(__float2bfloat16(ckv[i] * inv * __bfloat162float(p.kv_norm_w[i])));
+        if (tid < p.rope_dim / 2) rope_pair(kpe, tid, p.rope_dim, pos, p.theta, p.rope_interleave != 0);
+        __syncthreads();
+        if (!owned) return;
         const int ngroups = p.kv_lora / p.kv_group;
         const int row_bytes = p.kv_lora + 4 * ngroups + 2 * p.rope_dim;
         uint8_t* dst = p.kv_cache + slot * row_bytes;
@@ -188,58 +210,56 @@ __global__ void attn_pre_kernel(AttnPreParams p) {
         }
         bf16* dpe = reinterpret_cast<bf16*>(dst + p.kv_lora + 4 * ngroups);
         for (int i = tid; i < p.rope_dim; i += nt) dpe[i] = __float2bfloat16(kpe[i]);
+        return;
     }
-    __syncthreads();
 
-    // --- indexer key and head weights ---
-    if (p.idx_dim > 0) {
-        const bf16* ik = kv + p.kv_lora + p.rope_dim;
-        float* kbuf = sm;
-        float s1 = 0.f;
-        for (int i = tid; i < p.idx_dim; i += nt) {
-            const float v = __bfloat162float(ik[i]);
-            kbuf[i] = v;
-            s1 += v;
-        }
-        const float mean = block_sum(s1, scratch) / (float)p.idx_dim;
-        float s2 = 0.f;
-        for (int i = tid; i < p.idx_dim; i += nt) {
-            const float d = kbuf[i] - mean;
-            s2 += d * d;
-        }
-        const float var = block_sum(s2, scratch) / (float)p.idx_dim;
-        const float rstd = rsqrtf(var + 1e-6f);
-        for (int i = tid; i < p.idx_dim; i += nt)
-            kbuf[i] = (kbuf[i] - mean) * rstd * __bfloat162float(p.idx_ln_w[i]) + __bfloat162float(p.idx_ln_b[i]);
-        __syncthreads();
-        if (tid < p.rope_dim / 2) rope_pair(kbuf, tid, p.rope_dim, pos, p.theta, p.idx_rope_interleave != 0);
-        __syncthreads();
-        float amax = 0.f;
-        for (int i = tid; i < p.idx_dim; i += nt) {
-            kbuf[i] = __bfloat162float(__float2bfloat16(kbuf[i]));
-            amax = fmaxf(amax, fabsf(kbuf[i]));
-        }
-        amax = block_max(amax, scratch);
-        const float scale = pow2_scale_ceil(amax);
-        if (owned) {
-            uint8_t* dst = p.idx_cache + slot * (size_t)(p.idx_dim + 4);
-            for (int i = tid; i < p.idx_dim; i += nt) dst[i] = float_to_e4m3(kbuf[i] / scale);
-            if (tid == 0) {
-                // the row is idx_dim + 4 bytes: 4-byte aligned because idx_dim % 4 == 0
-                *reinterpret_cast<float*>(dst + p.idx_dim) = scale;
-            }
-        }
-        const bf16* iw = ik + p.idx_dim;
-        const float hs = rsqrtf((float)p.idx_heads);
-        for (int i = tid; i < p.idx_heads; i += nt) p.idx_w_out[(size_t)t * p.idx_heads + i] = __bfloat162float(iw[i]) * hs;
+    // --- role 2: indexer key and head weights ---
+    const size_t ik = kv + p.kv_lora + p.rope_dim;
+    float* kbuf = sm;
+    float s1 = 0.f;
+    for (int i = tid; i < p.idx_dim; i += nt) {
+        const float v = load_act(p.qkv, p.n_slabs, p.slab_stride, ik + i);
+        kbuf[i] = v;
+        s1 += v;
     }
+    const float mean = block_sum(s1, scratch) / (float)p.idx_dim;
+    float s2 = 0.f;
+    for (int i = tid; i < p.idx_dim; i += nt) {
+        const float d = kbuf[i] - mean;
+        s2 += d * d;
+    }
+    const float var = block_sum(s2, scratch) / (float)p.idx_dim;
+    const float rstd = rsqrtf(var + 1e-6f);
+    for (int i = tid; i < p.idx_dim; i += nt)
+        kbuf[i] = (kbuf[i] - mean) * rstd * __bfloat162float(p.idx_ln_w[i]) + __bfloat162float(p.idx_ln_b[i]);
+    __syncthreads();
+    if (tid < p.rope_dim / 2) rope_pair(kbuf, tid, p.rope_dim, pos, p.theta, p.idx_rope_interleave != 0);
+    __syncthreads();
+    float amax = 0.f;
+    for (int i = tid; i < p.idx_dim; i += nt) {
+        kbuf[i] = __bfloat162float(__float2bfloat16(kbuf[i]));
+        amax = fmaxf(amax, fabsf(kbuf[i]));
+    }
+    amax = block_max(amax, scratch);
+    const float scale = pow2_scale_ceil(amax);
+    if (owned) {
+        uint8_t* dst = p.idx_cache + slot * (size_t)(p.idx_dim + 4);
+        for (int i = tid; i < p.idx_dim; i += nt) dst[i] = float_to_e4m3(kbuf[i] / scale);
+        if (tid == 0) {
+            // the row is idx_dim + 4 bytes: 4-byte aligned because idx_dim % 4 == 0
+            *reinterpret_cast<float*>(dst + p.idx_dim) = scale;
+        }
+    }
+    const float hs = rsqrtf((float)p.idx_heads);
+    for (int i = tid; i < p.idx_heads; i += nt)
+        p.idx_w_out[(size_t)t * p.idx_heads + i] = load_act(p.qkv, p.n_slabs, p.slab_stride, ik + p.idx_dim + i) * hs;
 }
 
 SL_API int sl_attn_pre(const AttnPreParams* p, int T, cudaStream_t s) {
     if (T == 0) return 0;
     int n = p->q_lora > p->kv_lora + p->rope_dim ? p->q_lora : p->kv_lora + p->rope_dim;
     if (p->idx_dim > n) n = p->idx_dim;
-    attn_pre_kernel<<<T, 256, (size_t)n * sizeof(float), s>>>(*p);
+    sl_launch(attn_pre_kernel, dim3(T, 3), 256, (size_t)n * sizeof(float), s, *p);
     return SL_LAUNCH_CHECK();
 }
 
@@ -249,7 +269,7 @@ SL_API int sl_attn_pre(const AttnPreParams* p, int T, cudaStream_t s) {
 //  indexer head j: rope(first rope_dim of qi[t,j,:]) -> bf16 -> fp8 with power-of-two scale;
 //                  w_eff[t,j] = idx_w[t,j] * scale * Di^-0.5
 struct QPostParams {
-    const bf16* qb;
+    const void* qb;           // [T, ld] bf16, or fp32 slabs (see load_act)
     int ld, heads, d_nope, rope_dim, idx_heads, idx_dim;
     float theta;
     int rope_interleave, idx_rope_interleave;
@@ -258,17 +278,19 @@ struct QPostParams {
     bf16* q_pe_out;           // [T, heads, rope_dim]
     uint8_t* q8_out;          // [T, idx_heads, idx_dim]
     float* w_eff_out;         // [T, idx_heads]
+    int n_slabs; long long slab_stride;
 };
 
 __global__ void q_post_kernel(QPostParams p) {
+    pdl_grid_sync();
     __shared__ float v[512];
     __shared__ float scratch[33];
     const int t = blockIdx.x, hh = blockIdx.y, tid = threadIdx.x;
     const int pos = p.positions[t];
     const int dqk = p.d_nope + p.rope_dim;
     if (hh < p.heads) {
-        const bf16* src = p.qb + (size_t)t * p.ld + (size_t)hh * dqk + p.d_nope;
-        for (int i = tid; i < p.rope_dim; i += blockDim.x) v[i] = __bfloat162float(src[i]);
+        const size_t src = (size_t)t * p.ld + (size_t)hh * dqk + p.d_nope;
+        for (int i = tid; i < p.rope_dim; i += blockDim.x) v[i] = load_act(p.qb, p.n_slabs, p.slab_stride, src + i);
         __syncthreads();
         if (tid < p.rope_dim / 2) rope_pair(v, tid, p.rope_dim, pos, p.theta, p.rope_interleave != 0);
         __syncthreads();
@@ -276,8 +298,8 @@ __global__ void q_post_kernel(QPostParams p) {
         for (int i = tid; i < p.rope_dim; i += blockDim.x) dst[i] = __float2bfloat16(v[i]);
     } else {
         const int j = hh - p.heads;
-        const bf16* src = p.qb + (size_t)t * p.ld + (size_t)p.heads * dqk + (size_t)j * p.idx_dim;
-        for (int i = tid; i < p.idx_dim; i += blockDim.x) v[i] = __bfloat162float(src[i]);
+        const size_t src = (size_t)t * p.ld + (size_t)p.heads * dqk + (size_t)j * p.idx_dim;
+        for (int i = tid; i < p.idx_dim; i += blockDim.x) v[i] = load_act(p.qb, p.n_slabs, p.slab_stride, src + i);
         __syncthreads();
         if (tid < p.rope_dim / 2) rope_pair(v, tid, p.rope_dim, pos, p.theta, p.idx_rope_interleave != 0);
         __syncthreads();
@@ -298,26 +320,28 @@ __global__ void q_post_kernel(QPostParams p) {
 SL_API int sl_q_post(const QPostParams* p, int T, cudaStream_t s) {
     if (T == 0) return 0;
     dim3 grid(T, p->heads + p->idx_heads);
-    q_post_kernel<<<grid, 64, 0, s>>>(*p);
+    sl_launch(q_post_kernel, grid, 64, 0, s, *p);
     return SL_LAUNCH_CHECK();
 }
 
 // ---------------------------------------------------------------------------------------------
 // Batched vector x matrix: y[t,h,n] = sum_k x[t,h,k] * M[h,k,n]   (absorb: K=Dn,N=R; v_expand: K=R,N=Dv)
 // x element (t,h,k) at x[t*xs_t + h*xs_h + k]; y bf16 [T, Hh, N] contiguous.
-// grid (Hh, N/256, ceil(T/TT)); block 256 = 8 warps.  A warp owns every 8th k row and reads
-// 512 contiguous bytes of it (8 columns per lane, 16-byte loads, four rows in flight); the 8
-// partial sums meet in shared memory.
+// grid (Hh, N/64, ceil(T/TT)); block 256 = 8 warps.  A warp reads 4 matrix rows x 64 columns
+// per load instruction (8 columns per lane, 16 bytes), four loads in flight; the partial sums
+// of a lane's row group meet by shuffle, those of the 8 warps in shared memory.
 template <int TT>
-__global__ void __launch_bounds__(256) bmv_kernel(bf16* __restrict__ y, const bf16* __restrict__ x, const bf16* __restrict__ M,
-                                                  int T, int Hh, int K, int N, int xs_t, int xs_h) {
-    extern __shared__ float xs[];            // [TT][K], then red[8][TT][256]
+__global__ void __launch_bounds__(256) bmv_kernel(bf16* __restrict__ y, const void* __restrict__ x, const bf16* __restrict__ M,
+                                                  int T, int Hh, int K, int N, int xs_t, int xs_h, int n_slabs,
+                                                  long long slab_stride) {
+    pdl_grid_sync();
+    extern __shared__ float xs[];            // [TT][K], then red[8][TT][64]
     float* red = xs + TT * K;
-    const int h = blockIdx.x, n0 = blockIdx.y * 256, t0 = blockIdx.z * TT;
+    const int h = blockIdx.x, n0 = blockIdx.y * 64, t0 = blockIdx.z * TT;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     for (int i = tid; i < TT * K; i += blockDim.x) {
         const int tt = i / K, k = i % K;
-        xs[i] = (t0 + tt < T) ? __bfloat162float(x[(size_t)(t0 + tt) * xs_t + (size_t)h * xs_h + k]) : 0.f;
+        xs[i] = (t0 + tt < T) ? load_act(x, n_slabs, slab_stride, (size_t)(t0 + tt) * xs_t + (size_t)h * xs_h + k) : 0.f;
     }
     __syncthreads();
     float acc[TT][8];
@@ -325,20 +349,22 @@ __global__ void __launch_bounds__(256) bmv_kernel(bf16* __restrict__ y, const bf
     for (int tt = 0; tt < TT; ++tt)
 #pragma unroll
         for (int c = 0; c < 8; ++c) acc[tt][c] = 0.f;
-    const int n = n0 + lane * 8;
+    // a warp covers 4 matrix rows x 64 columns per load; 8 warps x 4 loads in flight = 128 rows a step
+    const int cg = lane & 7, kr = lane >> 3;
+    const int n = n0 + cg * 8;
     if (n < N) {
         const bf16* Mp = M + (size_t)h * K * N + n;
-        for (int k = warp; k < K; k += 32) {
+        for (int k = warp * 4 + kr; k < K; k += 128) {
             uint4 u[4];
 #pragma unroll
-            for (int q = 0; q < 4; ++q) u[q] = (k + q * 8 < K) ? ldg_nc_16(Mp + (size_t)(k + q * 8) * N) : make_uint4(0, 0, 0, 0);
+            for (int q = 0; q < 4; ++q) u[q] = (k + q * 32 < K) ? ldg_nc_16(Mp + (size_t)(k + q * 32) * N) : make_uint4(0, 0, 0, 0);
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
-                if (k + q * 8 < K) {
+                if (k + q * 32 < K) {
                     const float2 w0 = bf162_to_f2(u[q].x), w1 = bf162_to_f2(u[q].y), w2 = bf162_to_f2(u[q].z), w3 = bf162_to_f2(u[q].w);
 #pragma unroll
                     for (int tt = 0; tt < TT; ++tt) {
-                        const float xv = xs[tt * K + k + q * 8];
+                        const float xv = xs[tt * K + k + q * 32];
                         acc[tt][0] += xv * w0.x; acc[tt][1] += xv * w0.y; acc[tt][2] += xv * w1.x; acc[tt][3] += xv * w1.y;
                         acc[tt][4] += xv * w2.x; acc[tt][5] += xv * w2.y; acc[tt][6] += xv * w3.x; acc[tt][7] += xv * w3.y;
                     }
@@ -349,40 +375,50 @@ __global__ void __launch_bounds__(256) bmv_kernel(bf16* __restrict__ y, const bf
 #pragma unroll
     for (int tt = 0; tt < TT; ++tt)
 #pragma unroll
-        for (int c = 0; c < 8; ++c) red[(warp * TT + tt) * 256 + lane * 8 + c] = acc[tt][c];
+        for (int c = 0; c < 8; ++c) {
+            float v = acc[tt][c];
+            v += __shfl_xor_sync(0xffffffffu, v, 8);
+            v += __shfl_xor_sync(0xffffffffu, v, 16);
+            if (kr == 0) red[(warp * TT + tt) * 64 + cg * 8 + c] = v;
+        }
     __syncthreads();
-    for (int i = tid; i < TT * 256; i += blockDim.x) {
-        const int tt = i / 256, c = i % 256;
+    for (int i = tid; i < TT * 64; i += blockDim.x) {
+        const int tt = i / 64, c = i % 64;
         if (t0 + tt < T && n0 + c < N) {
             float v = 0.f;
 #pragma unroll
-            for (int w = 0; w < 8; ++w) v += red[(w * TT + tt) * 256 + c];
+            for (int w = 0; w < 8; ++w) v += red[(w * TT + tt) * 64 + c];
             y[((size_t)(t0 + tt) * Hh + h) * N + n0 + c] = __float2bfloat16(v);
         }
     }
 }
 
 template <int TT>
-static int launch_bmv(void* y, const void* x, const void* M, int T, int Hh, int K, int N, int xs_t, int xs_h, cudaStream_t s) {
-    dim3 grid(Hh, (N + 255) / 256, (T + TT - 1) / TT);
-    const size_t smem = (size_t)(TT * K + 8 * TT * 256) * sizeof(float);
+static int launch_bmv(void* y, const void* x, const void* M, int T, int Hh, int K, int N, int xs_t, int xs_h, int n_slabs,
+                      long long slab_stride, cudaStream_t s) {
+    dim3 grid(Hh, (N + 63) / 64, (T + TT - 1) / TT);
+    const size_t smem = (size_t)(TT * K + 8 * TT * 64) * sizeof(float);
     auto kern = bmv_kernel<TT>;
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    kern<<<grid, 256, smem, s>>>((bf16*)y, (const bf16*)x, (const bf16*)M, T, Hh, K, N, xs_t, xs_h);
+    sl_launch(kern, grid, 256, smem, s, (bf16*)y, x, (const bf16*)M, T, Hh, K, N, xs_t, xs_h, n_slabs, slab_stride);
     return SL_LAUNCH_CHECK();
 }
 
-SL_API int sl_bmv(void* y, const void* x, const void* M, int T, int Hh, int K, int N, int xs_t, int xs_h, cudaStream_t s) {
+// x is bf16, or (n_slabs > 0) a sum of fp32 slabs with the same element indexing (see load_act).
+SL_API int sl_bmv(void* y, const void* x, const void* M, int T, int Hh, int K, int N, int xs_t, int xs_h, int n_slabs,
+                  long long slab_stride, cudaStream_t s) {
     if (T == 0) return 0;
     if (N % 8 != 0) return -1;
-    if (T == 1) return launch_bmv<1>(y, x, M, T, Hh, K, N, xs_t, xs_h, s);
-    if (T == 2) return launch_bmv<2>(y, x, M, T, Hh, K, N, xs_t, xs_h, s);
-    return launch_bmv<4>(y, x, M, T, Hh, K, N, xs_t, xs_h, s);
+    if (T == 1) return launch_bmv<1>(y, x, M, T, Hh, K, N, xs_t, xs_h, n_slabs, slab_stride, s);
+    if (T == 2) return launch_bmv<2>(y, x, M, T, Hh, K, N, xs_t, xs_h, n_slabs, slab_stride, s);
+    if (T <= 4) return launch_bmv<4>(y, x, M, T, Hh, K, N, xs_t, xs_h, n_slabs, slab_stride, s);
+    return launch_bmv<8>(y, x, M, T, Hh, K, N, xs_t, xs_h, n_slabs, slab_stride, s);
 }
 
 // ---------------------------------------------------------------------------------------------
 // act[t, i] = silu(gu[t, i]) * gu[t, I + i]
 __global__ void silu_mul_kernel(bf16* __restrict__ out, const bf16* __restrict__ gu, size_t total, int I) {
+    pdl_grid_sync();
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
         const size_t t = idx / I, i = idx % I;
         const float g = __bfloat162float(gu[t * 2 * I + i]), u = __bfloat162float(gu[t * 2 * I + I + i]);
@@ -395,94 +431,30 @@ SL_API int sl_silu_mul(void* out, const void* gu, int T, int I, cudaStream_t s) 
     if (total == 0) return 0;
     int blocks = (int)((total + 255) / 256);
     if (blocks > 148 * 16) blocks = 148 * 16;
-    silu_mul_kernel<<<blocks, 256, 0, s>>>((bf16*)out, (const bf16*)gu, total, I);
+    sl_launch(silu_mul_kernel, blocks, 256, 0, s, (bf16*)out, (const bf16*)gu, total, I);
     return SL_LAUNCH_CHECK();
 }
 
 // ---------------------------------------------------------------------------------------------
-// MoE routing: one warp per token.  scores = sigmoid(logits); choose by scores + bias inside
-// the `topk_group` best groups (group rank = sum of its two best biased scores); weights =
-// unbiased scores of the chosen, normalised, scaled.  Ties prefer the lower expert id.
-// Lane l holds experts l*PER .. l*PER+PER-1 (contiguous, so a group of E/n_group experts is a
-// run of whole lanes when E/n_group >= PER).  E = 32*PER <= 512, n_group <= 32, top_k <= 32.
+// MoE routing: one warp per token (see route.cuh).
 template <int PER>
 __global__ void route_topk_kernel(int* __restrict__ ids, float* __restrict__ wts, const float* __restrict__ logits,
                                   const float* __restrict__ bias, int T, int E, int top_k, int n_group, int topk_group,
                                   int norm, float scale) {
+    pdl_grid_sync();
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (warp >= T) return;
-    float sc[PER], ch[PER];
+    float lg[PER];
 #pragma unroll
     for (int i = 0; i < PER; ++i) {
         const int e = lane * PER + i;
-        if (e < E) {
-            const float s = 1.f / (1.f + expf(-logits[(size_t)warp * E + e]));
-            sc[i] = s;
-            ch[i] = s + (bias ? bias[e] : 0.f);
-        } else {
-            sc[i] = 0.f;
-            ch[i] = -INFINITY;
-        }
+        lg[i] = e < E ? logits[(size_t)warp * E + e] : 0.f;
     }
-    if (n_group > 1) {
-        const int gsz = E / n_group;
-        // top-2 of this lane's experts, merged across the lanes of its group
-        float m1 = -INFINITY, m2 = -INFINITY;
-#pragma unroll
-        for (int i = 0; i < PER; ++i) {
-            const float v = ch[i];
-            if (v > m1) { m2 = m1; m1 = v; } else if (v > m2) m2 = v;
-        }
-        const int lanes_per_group = gsz / PER;            // >= 1 (checked by the launcher)
-        for (int o = 1; o < lanes_per_group; o <<= 1) {
-            const float o1 = __shfl_xor_sync(0xffffffffu, m1, o), o2 = __shfl_xor_sync(0xffffffffu, m2, o);
-            const float hi = fmaxf(m1, o1), lo = fmaxf(fminf(m1, o1), fmaxf(m2, o2));
-            m1 = hi; m2 = lo;
-        }
-        const int my_group = (lane * PER) / gsz;
-        const float gs = gsz >= 2 ? m1 + m2 : m1;
-        // rank of my group: number of groups that beat it (higher score, or equal score and lower id)
-        int beaten_by = 0;
-        for (int g2 = 0; g2 < n_group; ++g2) {
-            const float og = __shfl_sync(0xffffffffu, gs, g2 * lanes_per_group);
-            beaten_by += (og > gs) || (og == gs && g2 < my_group);
-        }
-        if (beaten_by >= topk_group || lane * PER >= E) {
-#pragma unroll
-            for (int i = 0; i < PER; ++i) ch[i] = -INFINITY;
-        }
-    }
-    float wsum = 0.f, myw = 0.f;
-    int myid = 0;
-    for (int r = 0; r < top_k; ++r) {
-        float best = -INFINITY; int bslot = 0;
-#pragma unroll
-        for (int i = 0; i < PER; ++i)
-            if (ch[i] > best) { best = ch[i]; bslot = i; }
-        const int be = best > -INFINITY ? lane * PER + bslot : E;
-        float gb = best; int ge = be;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ob = __shfl_xor_sync(0xffffffffu, gb, o);
-            const int oe = __shfl_xor_sync(0xffffffffu, ge, o);
-            if (ob > gb || (ob == gb && oe < ge)) { gb = ob; ge = oe; }
-        }
-        float s = 0.f;
-        if (ge == be && be < E) {
-#pragma unroll
-            for (int i = 0; i < PER; ++i)
-                if (i == bslot) { s = sc[i]; ch[i] = -INFINITY; }
-        }
-        // hand the winner's unbiased score to every lane
-        s = __shfl_sync(0xffffffffu, s, ge < E ? ge / PER : 0);
-        wsum += s;
-        if (lane == r) { myw = s; myid = ge < E ? ge : 0; }
-    }
+    int id; float w;
+    route_warp<PER>(lg, bias, E, top_k, n_group, topk_group, norm, scale, id, w);
     if (lane < top_k) {
-        float w = myw;
-        if (norm) w = w / fmaxf(wsum, 1e-20f);
-        ids[(size_t)warp * top_k + lane] = myid;
-        wts[(size_t)warp * top_k + lane] = w * scale;
+        ids[(size_t)warp * top_k + lane] = id;
+        wts[(size_t)warp * top_k + lane] = w;
     }
 }
 
@@ -501,7 +473,7 @@ SL_API int sl_route_topk(void* ids, void* wts, const void* logits, const void* b
     }
     const int wpb = 4;
     dim3 grid((T + wpb - 1) / wpb), block(wpb * 32);
-#define SL_ROUTE(P) route_topk_kernel<P><<<grid, block, 0, s>>>((int*)ids, (float*)wts, (const float*)logits, (const float*)bias, \
+#define SL_ROUTE(P) sl_launch(route_topk_kernel<P>, grid, block, 0, s, (int*)ids, (float*)wts, (const float*)logits, (const float*)bias, \
                                                                 T, E, top_k, n_group, topk_group, norm, scale)
     switch (PER) {
         case 1: SL_ROUTE(1); break;
@@ -520,6 +492,7 @@ SL_API int sl_route_topk(void* ids, void* wts, const void* logits, const void* b
 __global__ void topk_to_slots_kernel(int* __restrict__ slots, int* __restrict__ lengths, const int* __restrict__ pos,
                                      const int* __restrict__ page_table, const int* __restrict__ batch_idx, int k,
                                      int pt_stride, int page_size, int cp_world, int cp_rank, int local_only) {
+    pdl_grid_sync();
     __shared__ int wsum[32];
     __shared__ int base;
     const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = blockDim.x >> 5;
@@ -556,7 +529,7 @@ __global__ void topk_to_slots_kernel(int* __restrict__ slots, int* __restrict__ 
 SL_API int sl_topk_to_slots(void* slots, void* lengths, const void* pos, const void* page_table, const void* batch_idx, int T,
                             int k, int pt_stride, int page_size, int cp_world, int cp_rank, int local_only, cudaStream_t s) {
     if (T == 0) return 0;
-    topk_to_slots_kernel<<<T, 256, 0, s>>>((int*)slots, (int*)lengths, (const int*)pos, (const int*)page_table,
+    sl_launch(topk_to_slots_kernel, T, 256, 0, s, (int*)slots, (int*)lengths, (const int*)pos, (const int*)page_table,
                                            (const int*)batch_idx, k, pt_stride, page_size, cp_world, cp_rank, local_only);
     return SL_LAUNCH_CHECK();
 }
@@ -566,6 +539,7 @@ SL_API int sl_topk_to_slots(void* slots, void* lengths, const void* pos, const v
 // (reference `csrc/glm_ops.cu:3308`)
 __global__ void rotate_input_ids_kernel(int64_t* __restrict__ out, const int64_t* __restrict__ ids,
                                         const int64_t* __restrict__ new_tokens, const int* __restrict__ qo_indptr, int B) {
+    pdl_grid_sync();
     const int b = blockIdx.x;
     if (b >= B) return;
     const int lo = qo_indptr[b], hi = qo_indptr[b + 1];
@@ -574,6 +548,6 @@ __global__ void rotate_input_ids_kernel(int64_t* __restrict__ out, const int64_t
 
 SL_API int sl_rotate_input_ids(void* out, const void* ids, const void* new_tokens, const void* qo_indptr, int B, cudaStream_t s) {
     if (B == 0) return 0;
-    rotate_input_ids_kernel<<<B, 128, 0, s>>>((int64_t*)out, (const int64_t*)ids, (const int64_t*)new_tokens, (const int*)qo_indptr, B);
+    sl_launch(rotate_input_ids_kernel, B, 128, 0, s, (int64_t*)out, (const int64_t*)ids, (const int64_t*)new_tokens, (const int*)qo_indptr, B);
     return SL_LAUNCH_CHECK();
 }

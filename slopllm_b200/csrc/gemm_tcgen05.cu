@@ -22,7 +22,7 @@ constexpr int BM = 128, BK = 64;
 template <int BN>
 struct GemmCfg {
     static constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
-    static constexpr int STAGES = (BN >= 256) ? 4 : (BN <= 32 ? 10 : 6);
+    static constexpr int STAGES = (BN >= 256) ? 4 : (BN <= 32 ? 5 : 6);   // BN=32: two CTAs per SM
     static constexpr int SMEM = STAGES * (A_BYTES + B_BYTES) + 1024 /*align*/ + 256 /*barriers*/;
 };
 
@@ -31,7 +31,8 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
                                                         const __grid_constant__ CUtensorMap tmB, void* __restrict__ C,
                                                         int M, int N, int K, int ldc, int out_f32, int transpose_out,
                                                         int* __restrict__ err, int use_push, PushCtx push,
-                                                        const int4* __restrict__ tiles, const int* __restrict__ num_tiles) {
+                                                        const int4* __restrict__ tiles, const int* __restrict__ num_tiles,
+                                                        int kb_per_split, long long split_stride) {
     using Cfg = GemmCfg<BN>;
     constexpr int STAGES = Cfg::STAGES;
     extern __shared__ uint8_t smem_raw[];
@@ -44,17 +45,7 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
     uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tmem_full + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // Plain GEMM: tile (blockIdx.y, blockIdx.x).  Grouped GEMM: blockIdx.x indexes a tile table whose
-    // entries are {first A row, end of the group's A rows, first B row of the group, output column};
-    // rows at or beyond the group's end belong to the next group and are not stored.
-    int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN, b_row0 = n0, m_end = M;
-    if (tiles != nullptr) {
-        if ((int)blockIdx.x >= *num_tiles) return;
-        const int4 t = tiles[blockIdx.x];
-        m0 = t.x; m_end = t.y; b_row0 = t.z + t.w; n0 = t.w;
-    }
-    const int num_kb = (K + BK - 1) / BK;
-
+    // Set-up touches no global memory, so it runs while the preceding kernel is still finishing.
     if (warp == 0 && lane == 0) {
         tc::tma_prefetch_desc(&tmA);
         tc::tma_prefetch_desc(&tmB);
@@ -70,16 +61,37 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
     __syncthreads();
     tc::fence_after_sync();
     const uint32_t tmem_base = *tmem_holder;
+    pdl_grid_sync();
 
-    if (warp == 0) {
+    // Plain GEMM: tile (blockIdx.y, blockIdx.x).  Grouped GEMM: blockIdx.x indexes a tile table whose
+    // entries are {first A row, end of the group's A rows, first B row of the group, output column};
+    // rows at or beyond the group's end belong to the next group and are not stored.
+    int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN, b_row0 = n0, m_end = M;
+    bool active = true;
+    if (tiles != nullptr) {
+        active = (int)blockIdx.x < *num_tiles;
+        if (active) {
+            const int4 t = tiles[blockIdx.x];
+            m0 = t.x; m_end = t.y; b_row0 = t.z + t.w; n0 = t.w;
+        }
+    }
+    // split-K: blockIdx.z owns K blocks [kb0, kb0 + num_kb) and its own fp32 output slab
+    const int total_kb = (K + BK - 1) / BK;
+    const int kb0 = kb_per_split > 0 ? (int)blockIdx.z * kb_per_split : 0;
+    const int num_kb = kb_per_split > 0 ? max(0, min(kb_per_split, total_kb - kb0)) : total_kb;
+    if (kb_per_split > 0) C = (void*)((float*)C + (size_t)blockIdx.z * split_stride);
+
+    if (!active) {
+        // nothing to compute: fall through to the common TMEM release
+    } else if (warp == 0) {
         if (lane == 0) {
             for (int kb = 0; kb < num_kb; ++kb) {
                 const int s = kb % STAGES;
                 const uint32_t ph = (kb / STAGES) & 1;
                 if (!tc::mbar_wait(&empty[s], ph ^ 1)) { atomicExch(err, 1); break; }
                 tc::mbar_expect_tx(&full[s], Cfg::A_BYTES + Cfg::B_BYTES);
-                tc::tma_load_2d(sA + s * Cfg::A_BYTES, &tmA, &full[s], kb * BK, m0);
-                tc::tma_load_2d(sB + s * Cfg::B_BYTES, &tmB, &full[s], kb * BK, b_row0);
+                tc::tma_load_2d(sA + s * Cfg::A_BYTES, &tmA, &full[s], (kb0 + kb) * BK, m0);
+                tc::tma_load_2d(sB + s * Cfg::B_BYTES, &tmB, &full[s], (kb0 + kb) * BK, b_row0);
             }
         }
     } else if (warp == 1) {
@@ -99,7 +111,7 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
                 }
                 tc::mma_commit(&empty[s]);
             }
-            tc::mma_commit(tmem_full);       // arrives when every MMA above has finished
+            tc::mma_commit(tmem_full);       // arrives when every MMA above has finished (at once if there were none)
         }
     } else {
         const int q = warp & 3;               // TMEM lane quarter this warp may access
@@ -167,7 +179,7 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
 template <int BN>
 int launch(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc, int out_f32,
            int transpose_out, int* err, cudaStream_t s, const PushCtx* push = nullptr, const int4* tiles = nullptr,
-           const int* num_tiles = nullptr, int max_tiles = 0, int b_rows = 0) {
+           const int* num_tiles = nullptr, int max_tiles = 0, int b_rows = 0, int splits = 1, long long split_stride = 0) {
     CUtensorMap tmA, tmB;
     int rc = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)M, (uint64_t)K, (uint64_t)lda * 2, BM, BK);
     if (rc) return rc;
@@ -181,8 +193,14 @@ int launch(const void* A, const void* B, void* C, int M, int N, int K, int lda, 
     }
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
     if (tiles != nullptr) grid = dim3(max_tiles, 1);
-    kern<<<grid, 192, GemmCfg<BN>::SMEM, s>>>(tmA, tmB, C, M, N, K, ldc, out_f32, transpose_out, err, push ? 1 : 0,
-                                              push ? *push : PushCtx{}, tiles, num_tiles);
+    int kb_per_split = 0;
+    if (splits > 1) {
+        const int total_kb = (K + BK - 1) / BK;
+        kb_per_split = (total_kb + splits - 1) / splits;
+        grid.z = (total_kb + kb_per_split - 1) / kb_per_split;
+    }
+    sl_launch(kern, grid, 192, GemmCfg<BN>::SMEM, s, tmA, tmB, C, M, N, K, ldc, out_f32, transpose_out, err, push ? 1 : 0,
+                                              push ? *push : PushCtx{}, tiles, num_tiles, kb_per_split, split_stride);
     return (int)cudaGetLastError();
 }
 
@@ -203,11 +221,53 @@ SL_API int sl_gemm_bf16_tcgen05(const void* A, const void* B, void* C, int M, in
 // Weight-streaming form for a few token rows (T <= 32): y[T, N] = x[T, K] * W[N, K]^T computed as
 // (W tile of 128 features) x (all tokens): the weights are the 128-row MMA operand fed by a deep TMA
 // ring, the tokens are the narrow N = 32 operand, the epilogue writes the transposed tile.
+// `partials` (caller-owned fp32 scratch of at least 8 * T * N floats, may be null) enables split-K when the feature
+// count alone gives too few CTAs to pull HBM bandwidth: each K split writes its own slab, a small kernel sums them.
+__global__ void splitk_reduce_kernel(void* __restrict__ y, const float* __restrict__ part, int splits, size_t slab, int T, int N,
+                                     int ldy, int out_f32) {
+    pdl_grid_sync();
+    const size_t total = (size_t)T * N;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        float v = 0.f;
+        for (int s = 0; s < splits; ++s) v += part[(size_t)s * slab + i];
+        const size_t t = i / N, n = i % N;
+        if (out_f32) ((float*)y)[t * ldy + n] = v;
+        else ((bf16*)y)[t * ldy + n] = __float2bfloat16(v);
+    }
+}
+
+// Number of K splits the small-T linear uses for this shape (1 = no split).
+SL_API int sl_smallT_splits(int T, int N, int K) {
+    const int ctas = (N + BM - 1) / BM, total_kb = (K + BK - 1) / BK;
+    int splits = 1;
+    if (T > 0 && ctas < 120 && total_kb >= 8) {
+        // two CTAs fit on each of the 148 SMs
+        splits = (200 + ctas - 1) / ctas;
+        if (splits > 8) splits = 8;
+        if (splits > total_kb / 4) splits = total_kb / 4;
+        // every split must own at least one K block
+        const int per = (total_kb + splits - 1) / splits;
+        splits = (total_kb + per - 1) / per;
+    }
+    return splits < 1 ? 1 : splits;
+}
+
+// `splits` must be 1 or the value of sl_smallT_splits for this shape.  With splits > 1 every K split writes an fp32
+// slab [T, N] into `partials` ([splits, T, N]); if `y` is not null a small kernel then sums the slabs into it,
+// otherwise the slabs are the result (the consumer adds them up).
 SL_API int sl_linear_smallT_bf16_tcgen05(const void* x, const void* W, void* y, int T, int N, int K, int ldx, int ldw, int ldy,
-                                         int out_f32, void* err, cudaStream_t s) {
+                                         int out_f32, void* err, void* partials, int splits, cudaStream_t s) {
     if (T <= 0 || N <= 0 || K <= 0) return 0;
     if (T > 32 || K % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0) return -1;
-    return launch<32>(W, x, y, N, T, K, ldw, ldx, ldy, out_f32, 1, (int*)err, s);
+    if (splits <= 1) return launch<32>(W, x, y, N, T, K, ldw, ldx, ldy, out_f32, 1, (int*)err, s);
+    if (partials == nullptr || splits != sl_smallT_splits(T, N, K)) return -1;
+    const long long slab = (long long)T * N;
+    int rc = launch<32>(W, x, partials, N, T, K, ldw, ldx, N, 1, 1, (int*)err, s, nullptr, nullptr, nullptr, 0, 0, splits, slab);
+    if (rc || y == nullptr) return rc;
+    int blocks = (int)(((size_t)T * N + 255) / 256);
+    if (blocks > 148 * 4) blocks = 148 * 4;
+    sl_launch(splitk_reduce_kernel, blocks, 256, 0, s, y, (const float*)partials, splits, (size_t)slab, T, N, ldy, out_f32);
+    return (int)cudaGetLastError();
 }
 
 // Weight-streaming linear whose fp32 result rows go to every rank's receive slot (fused all-reduce producer).
@@ -235,6 +295,7 @@ SL_API int sl_grouped_gemm_bf16_tcgen05(const void* A, const void* B, void* C, i
 // at a position given by a prefix sum over the groups' tile counts.
 __global__ void build_group_tiles_kernel(int4* __restrict__ tiles, int* __restrict__ num_tiles, const int* __restrict__ offsets,
                                          int groups, int N, int max_tiles) {
+    pdl_grid_sync();
     __shared__ int base[1025];
     const int g = threadIdx.x;
     const int ncol = (N + 127) / 128;
@@ -257,6 +318,6 @@ __global__ void build_group_tiles_kernel(int4* __restrict__ tiles, int* __restri
 
 SL_API int sl_build_group_tiles(void* tiles, void* num_tiles, const void* offsets, int groups, int N, int max_tiles, cudaStream_t s) {
     if (groups <= 0 || groups > 1024) return -1;
-    build_group_tiles_kernel<<<1, 1024, 0, s>>>((int4*)tiles, (int*)num_tiles, (const int*)offsets, groups, N, max_tiles);
+    sl_launch(build_group_tiles_kernel, 1, 1024, 0, s, (int4*)tiles, (int*)num_tiles, (const int*)offsets, groups, N, max_tiles);
     return (int)cudaGetLastError();
 }

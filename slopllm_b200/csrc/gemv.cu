@@ -14,6 +14,7 @@ template <int TT, int R>
 __global__ void __launch_bounds__(256) gemv_bf16_kernel(void* __restrict__ y, const bf16* __restrict__ x,
                                                         const bf16* __restrict__ W, int T, int N, int K, int ldx,
                                                         int out_f32, const float* __restrict__ bias) {
+    pdl_grid_sync();
     extern __shared__ __align__(16) unsigned char smraw[];
     bf16* xs = reinterpret_cast<bf16*>(smraw);           // [TT][K]
     const int t0 = blockIdx.y * TT;
@@ -32,29 +33,34 @@ __global__ void __launch_bounds__(256) gemv_bf16_kernel(void* __restrict__ y, co
         for (int r = 0; r < R; ++r)
 #pragma unroll
             for (int tt = 0; tt < TT; ++tt) acc[r][tt] = 0.f;
-        uint4 w[R], wn[R];
-        int k = lane * 8;
+        // U chunks of 256 reduction indices per step, every load of the step issued before the first use
+        constexpr int U = (R * TT <= 4) ? 4 : 2;
+        for (int k0 = lane * 8; k0 < K; k0 += 256 * U) {
+            uint4 w[U][R];
 #pragma unroll
-        for (int r = 0; r < R; ++r)
-            w[r] = (k < K && n0 + r < N) ? ldg_nc_16(W + (size_t)(n0 + r) * K + k) : make_uint4(0, 0, 0, 0);
-        for (; k < K; k += 256) {
-            const int kn = k + 256;
-#pragma unroll
-            for (int r = 0; r < R; ++r)
-                wn[r] = (kn < K && n0 + r < N) ? ldg_nc_16(W + (size_t)(n0 + r) * K + kn) : make_uint4(0, 0, 0, 0);
-#pragma unroll
-            for (int tt = 0; tt < TT; ++tt) {
-                const uint4 xv = *reinterpret_cast<const uint4*>(xs + tt * K + k);
-                const float2 x0 = bf162_to_f2(xv.x), x1 = bf162_to_f2(xv.y), x2 = bf162_to_f2(xv.z), x3 = bf162_to_f2(xv.w);
+            for (int u = 0; u < U; ++u)
 #pragma unroll
                 for (int r = 0; r < R; ++r) {
-                    const float2 w0 = bf162_to_f2(w[r].x), w1 = bf162_to_f2(w[r].y), w2 = bf162_to_f2(w[r].z), w3 = bf162_to_f2(w[r].w);
-                    acc[r][tt] += x0.x * w0.x + x0.y * w0.y + x1.x * w1.x + x1.y * w1.y + x2.x * w2.x + x2.y * w2.y +
-                                  x3.x * w3.x + x3.y * w3.y;
+                    const int k = k0 + u * 256;
+                    w[u][r] = (k < K && n0 + r < N) ? ldg_nc_16(W + (size_t)(n0 + r) * K + k) : make_uint4(0, 0, 0, 0);
+                }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int k = k0 + u * 256;
+                if (k >= K) break;
+#pragma unroll
+                for (int tt = 0; tt < TT; ++tt) {
+                    const uint4 xv = *reinterpret_cast<const uint4*>(xs + tt * K + k);
+                    const float2 x0 = bf162_to_f2(xv.x), x1 = bf162_to_f2(xv.y), x2 = bf162_to_f2(xv.z), x3 = bf162_to_f2(xv.w);
+#pragma unroll
+                    for (int r = 0; r < R; ++r) {
+                        const float2 w0 = bf162_to_f2(w[u][r].x), w1 = bf162_to_f2(w[u][r].y), w2 = bf162_to_f2(w[u][r].z),
+                                     w3 = bf162_to_f2(w[u][r].w);
+                        acc[r][tt] += x0.x * w0.x + x0.y * w0.y + x1.x * w1.x + x1.y * w1.y + x2.x * w2.x + x2.y * w2.y +
+                                      x3.x * w3.x + x3.y * w3.y;
+                    }
                 }
             }
-#pragma unroll
-            for (int r = 0; r < R; ++r) w[r] = wn[r];
         }
 #pragma unroll
         for (int r = 0; r < R; ++r)
@@ -75,6 +81,7 @@ template <int TT>
 __global__ void __launch_bounds__(256) gemv_bf16_rowblock_kernel(void* __restrict__ y, const bf16* __restrict__ x,
                                                                  const bf16* __restrict__ W, int T, int N, int K, int ldx,
                                                                  int out_f32) {
+    pdl_grid_sync();
     __shared__ float scratch[33];
     const int n = blockIdx.x, t0 = blockIdx.y * TT;
     float acc[TT];
@@ -113,7 +120,7 @@ static int launch_gemv_bf16_r(void* y, const void* x, const void* W, int T, int 
     const int cap = 148 * 8;
     if (blocks > cap) blocks = cap;
     if (blocks < 1) blocks = 1;
-    kern<<<dim3(blocks, tiles), 256, smem, s>>>(y, (const bf16*)x, (const bf16*)W, T, N, K, ldx, out_f32, nullptr);
+    sl_launch(kern, dim3(blocks, tiles), 256, smem, s, y, (const bf16*)x, (const bf16*)W, T, N, K, ldx, out_f32, nullptr);
     return SL_LAUNCH_CHECK();
 }
 
@@ -121,7 +128,11 @@ static int launch_gemv_bf16_r(void* y, const void* x, const void* W, int T, int 
 template <int TT>
 static int launch_gemv_bf16(void* y, const void* x, const void* W, int T, int N, int K, int ldx, int out_f32, cudaStream_t s) {
     if (N <= 1024 && K >= 2048) {
-        gemv_bf16_rowblock_kernel<TT><<<dim3(N, (T + TT - 1) / TT), 256, 0, s>>>(y, (const bf16*)x, (const bf16*)W, T, N, K, ldx, out_f32);
+        sl_launch(gemv_bf16_rowblock_kernel<TT>, dim3(N, (T + TT - 1) / TT), 256, 0, s, y, (const bf16*)x, (const bf16*)W, T, N, K, ldx, out_f32);
+        return SL_LAUNCH_CHECK();
+    }
+    if (N < 148 * 8 && K >= 1024) {          // few rows: one block per row keeps every SM busy
+        sl_launch(gemv_bf16_rowblock_kernel<TT>, dim3(N, (T + TT - 1) / TT), 256, 0, s, y, (const bf16*)x, (const bf16*)W, T, N, K, ldx, out_f32);
         return SL_LAUNCH_CHECK();
     }
     constexpr int RMAX = (TT >= 4) ? 2 : 4;
@@ -225,6 +236,7 @@ __global__ void __launch_bounds__(256) gemv_nvfp4_kernel(void* __restrict__ y, c
                                                          const uint8_t* __restrict__ Wp, const uint8_t* __restrict__ S,
                                                          const float* __restrict__ gscale, int T, int N, int K, int ldx,
                                                          int out_f32) {
+    pdl_grid_sync();
     extern __shared__ __align__(16) unsigned char smraw[];
     __half* xs = reinterpret_cast<__half*>(smraw);
     const int t0 = blockIdx.y * TT;
@@ -262,7 +274,7 @@ static int launch_gemv_nvfp4_r(void* y, const void* x, const void* Wp, const voi
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     int blocks = (N + 8 * R - 1) / (8 * R);
     if (blocks > 148 * 8) blocks = 148 * 8;
-    kern<<<dim3(blocks, (T + TT - 1) / TT), 256, smem, s>>>(y, (const bf16*)x, (const uint8_t*)Wp, (const uint8_t*)S,
+    sl_launch(kern, dim3(blocks, (T + TT - 1) / TT), 256, smem, s, y, (const bf16*)x, (const uint8_t*)Wp, (const uint8_t*)S,
                                                             (const float*)g, T, N, K, ldx, out_f32);
     return SL_LAUNCH_CHECK();
 }
@@ -301,6 +313,7 @@ struct MoeGateUpParams {
 };
 
 __global__ void __launch_bounds__(256) moe_gate_up_kernel(MoeGateUpParams p) {
+    pdl_grid_sync();
     extern __shared__ __align__(16) unsigned char smraw[];
     __half* xs = reinterpret_cast<__half*>(smraw);
     const int route = blockIdx.y;
@@ -351,7 +364,7 @@ SL_API int sl_moe_gate_up(const MoeGateUpParams* p, cudaStream_t s) {
     const size_t smem = (size_t)p->H * sizeof(__half);
     int bx = (p->I + 15) / 16;                // 8 warps x 2 rows per block pass
     if (bx > 64) bx = 64;
-    moe_gate_up_kernel<<<dim3(bx, routes), 256, smem, s>>>(*p);
+    sl_launch(moe_gate_up_kernel, dim3(bx, routes), 256, smem, s, *p);
     return SL_LAUNCH_CHECK();
 }
 
@@ -368,6 +381,7 @@ struct MoeDownParams {
 };
 
 __global__ void __launch_bounds__(256) moe_down_kernel(MoeDownParams p, int use_push, PushCtx push) {
+    pdl_grid_sync();
     // grid (H / 32, T).  The block owns 32 output rows of one token; warp w streams the rows of
     // routes w, w+8, ... (independent weight streams), the partial sums meet in shared memory.
     extern __shared__ __align__(16) unsigned char smraw[];
@@ -440,7 +454,7 @@ SL_API int sl_moe_down(const MoeDownParams* p, cudaStream_t s) {
     if (smem > 200 * 1024) return -2;
     if (smem > 48 * 1024) cudaFuncSetAttribute(moe_down_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     const int bx = (p->H + 31) / 32;          // 32 rows per block
-    moe_down_kernel<<<dim3(bx, p->T), 256, smem, s>>>(*p, 0, PushCtx{});
+    sl_launch(moe_down_kernel, dim3(bx, p->T), 256, smem, s, *p, 0, PushCtx{});
     return SL_LAUNCH_CHECK();
 }
 
@@ -453,7 +467,7 @@ SL_API int sl_moe_down_push(const MoeDownParams* p, const PushCtx* push, cudaStr
     if (smem > 200 * 1024) return -2;
     if (smem > 48 * 1024) cudaFuncSetAttribute(moe_down_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     const int bx = (p->H + 31) / 32;
-    moe_down_kernel<<<dim3(bx, p->T), 256, smem, s>>>(*p, 1, *push);
+    sl_launch(moe_down_kernel, dim3(bx, p->T), 256, smem, s, *p, 1, *push);
     return SL_LAUNCH_CHECK();
 }
 
@@ -463,6 +477,7 @@ SL_API int sl_moe_down_push(const MoeDownParams* p, const PushCtx* push, cudaStr
 // Feeds the tcgen05 grouped GEMMs of the prefill path.  grid-stride over 32-value groups.
 __global__ void nvfp4_dequant_bf16_kernel(bf16* __restrict__ out, const uint8_t* __restrict__ Wp, const uint8_t* __restrict__ S,
                                           const float* __restrict__ g, int mats, int N, int K, int g_per, int split) {
+    pdl_grid_sync();
     const size_t groups = (size_t)mats * N * (K / 32);
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < groups; i += (size_t)gridDim.x * blockDim.x) {
         const size_t row = i / (K / 32);
@@ -497,7 +512,7 @@ SL_API int sl_nvfp4_dequant_bf16(void* out, const void* Wp, const void* S, const
     const size_t groups = (size_t)mats * N * (K / 32);
     int blocks = (int)((groups + 255) / 256);
     if (blocks > 148 * 16) blocks = 148 * 16;
-    nvfp4_dequant_bf16_kernel<<<blocks, 256, 0, s>>>((bf16*)out, (const uint8_t*)Wp, (const uint8_t*)S, (const float*)g, mats, N, K,
+    sl_launch(nvfp4_dequant_bf16_kernel, blocks, 256, 0, s, (bf16*)out, (const uint8_t*)Wp, (const uint8_t*)S, (const float*)g, mats, N, K,
                                                      g_per, split);
     return SL_LAUNCH_CHECK();
 }
@@ -506,6 +521,7 @@ SL_API int sl_nvfp4_dequant_bf16(void* out, const void* Wp, const void* S, const
 // because each block owns one output token: rows of a token are found through `token_rows` [T, k] indices)
 __global__ void moe_unsort_reduce_kernel(float* __restrict__ out, const float* __restrict__ y, const int* __restrict__ rows_of,
                                          const float* __restrict__ wts, int k, int H, int accumulate) {
+    pdl_grid_sync();
     const int t = blockIdx.y;
     for (int n = blockIdx.x * blockDim.x + threadIdx.x; n < H; n += gridDim.x * blockDim.x) {
         float v = accumulate ? out[(size_t)t * H + n] : 0.f;
@@ -520,7 +536,7 @@ __global__ void moe_unsort_reduce_kernel(float* __restrict__ out, const float* _
 SL_API int sl_moe_unsort_reduce(void* out, const void* y, const void* rows_of, const void* wts, int T, int k, int H, int accumulate,
                                 cudaStream_t s) {
     if (T == 0) return 0;
-    moe_unsort_reduce_kernel<<<dim3((H + 255) / 256, T), 256, 0, s>>>((float*)out, (const float*)y, (const int*)rows_of,
+    sl_launch(moe_unsort_reduce_kernel, dim3((H + 255) / 256, T), 256, 0, s, (float*)out, (const float*)y, (const int*)rows_of,
                                                                      (const float*)wts, k, H, accumulate);
     return SL_LAUNCH_CHECK();
 }

@@ -13,6 +13,7 @@
 // Reference counterpart: `nvfp4_dequantize_gemm_smem_kernel` (`csrc/glm_gemv.cu:653`, batch 3-16
 // on CUDA cores) and the MoE small-batch kernels (`:738-990`).
 #include "push.cuh"
+#include "route.cuh"
 
 namespace {
 
@@ -33,6 +34,7 @@ __device__ __forceinline__ __half2 e4m3x2_to_half2(uint16_t v) {
 // x[token][group*128 + c*32 + j*8 .. +7] at unit index (token*G + group)*16 + j*4 + c, G = K/128.
 // Rows T..tpad-1 are zero.
 __global__ void permute_x_kernel(uint4* __restrict__ xp, const bf16* __restrict__ x, int T, int tpad, int K, int ldx) {
+    pdl_grid_sync();
     const int units = tpad * (K / 8);
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < units; i += gridDim.x * blockDim.x) {
         const int tok = i / (K / 8), u = i % (K / 8);
@@ -145,6 +147,7 @@ __global__ void __launch_bounds__(256) linear_nvfp4_mma_kernel(void* __restrict_
                                                                const uint8_t* __restrict__ Wp, const uint8_t* __restrict__ S,
                                                                const float* __restrict__ gscale, int T, int N, int K,
                                                                int ksplit, int out_f32, int use_push, PushCtx push) {
+    pdl_grid_sync();
     extern __shared__ float red[];
     constexpr int ROWS = MT * 16, TOK = NT * 8;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -201,7 +204,7 @@ int launch_linear(void* y, const void* x, void* xp, const void* Wp, const void* 
                   int out_f32, const PushCtx* push, cudaStream_t s) {
     constexpr int ROWS = MT * 16, TOK = NT * 8;
     const int units = TOK * (K / 8);
-    permute_x_kernel<<<(units + 255) / 256, 256, 0, s>>>((uint4*)xp, (const bf16*)x, T, TOK, K, ldx);
+    sl_launch(permute_x_kernel, (units + 255) / 256, 256, 0, s, (uint4*)xp, (const bf16*)x, T, TOK, K, ldx);
     int ksplit = 8;
     while (ksplit > 1 && K / 128 < ksplit) ksplit >>= 1;
     // few rows: keep the reduction split so that there are enough blocks to fill the machine
@@ -210,7 +213,7 @@ int launch_linear(void* y, const void* x, void* xp, const void* Wp, const void* 
     auto kern = linear_nvfp4_mma_kernel<MT, NT>;
     const size_t smem = (size_t)8 * TOK * ROWS * sizeof(float);
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    kern<<<(tiles + tiles_per_block - 1) / tiles_per_block, 256, smem, s>>>(y, (const uint4*)xp, (const uint8_t*)Wp,
+    sl_launch(kern, (tiles + tiles_per_block - 1) / tiles_per_block, 256, smem, s, y, (const uint4*)xp, (const uint8_t*)Wp,
                                                                            (const uint8_t*)S, (const float*)g, T, N, K, ksplit,
                                                                            out_f32, push ? 1 : 0, push ? *push : PushCtx{});
     return (int)cudaGetLastError();
@@ -263,57 +266,69 @@ struct MoePlanView {
 };
 
 // One block.  Routed routes r = t*top_k + j (expert ids[r]); shared routes r = T*top_k + t.
-__global__ void __launch_bounds__(512) moe_plan_kernel(MoePlanView pv, const int* __restrict__ ids, int T, int top_k,
-                                                       int expert_offset, int num_local, int has_shared, int max_items) {
-    extern __shared__ int sh[];
-    int* ex = sh;                                  // expert of each routed route (-1 if not local)
+// Called by every thread of one block (<= 512 threads, a multiple of 32); `sh` is 2 * (T * top_k + 8) ints of
+// shared memory and `ids` may point to global or shared memory.  Items are numbered in the order of their first
+// route, so the plan does not depend on thread timing.
+__device__ void moe_plan_body(MoePlanView pv, const int* ids, int T, int top_k, int expert_offset, int num_local,
+                              int has_shared, int max_items, int* sh) {
     const int n = T * top_k;
+    int* ex = sh;                                  // expert of each routed route (-1 if not local)
+    int* slot_of = sh + n + 8;                     // item of each chunk leader
     __shared__ int s_items;
-    for (int r = threadIdx.x; r < n; r += blockDim.x) {
+    __shared__ int wcnt[16];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = blockDim.x >> 5;
+    for (int r = tid; r < n; r += blockDim.x) {
         const int e = ids[r] - expert_offset;
         ex[r] = (e >= 0 && e < num_local) ? e : -1;
     }
-    if (threadIdx.x == 0) s_items = 0;
-    for (int i = threadIdx.x; i < max_items * kItemRoutes; i += blockDim.x) pv.item_routes[i] = -1;
+    if (tid == 0) s_items = 0;
+    for (int i = tid; i < max_items * kItemRoutes; i += blockDim.x) pv.item_routes[i] = -1;
     __syncthreads();
     // leaders (first route of each chunk of 8 routes of an expert) claim item slots in route order
     for (int base = 0; base < n; base += blockDim.x) {
-        const int r = base + threadIdx.x;
+        const int r = base + tid;
         int before = -1;
         if (r < n && ex[r] >= 0) {
             before = 0;
-            for (int q = 0; q < r; ++q) before += (ex[q] == ex[r]);
+            const int e = ex[r];
+            for (int q = 0; q < r; ++q) before += (ex[q] == e);
         }
         const bool leader = before >= 0 && (before % kItemRoutes) == 0;
-        // deterministic slot: number of leaders with a smaller route id
-        __shared__ int flags[512];
-        flags[threadIdx.x] = leader ? 1 : 0;
+        const unsigned m = __ballot_sync(0xffffffffu, leader);
+        if (lane == 0) wcnt[warp] = __popc(m);
         __syncthreads();
+        int slot = s_items, total = 0;
+        for (int w = 0; w < nw; ++w) {
+            if (w < warp) slot += wcnt[w];
+            total += wcnt[w];
+        }
+        slot += __popc(m & ((1u << lane) - 1));
         if (leader) {
-            int slot = s_items;
-            for (int q = 0; q < (int)threadIdx.x; ++q) slot += flags[q];
             if (slot < max_items) { pv.item_expert[slot] = ex[r]; pv.item_routes[slot * kItemRoutes] = r; }
-            ex[n + r] = slot;                      // remember my item for the members
+            slot_of[r] = slot;
         }
         __syncthreads();
-        if (threadIdx.x == 0) { int c = 0; for (int q = 0; q < (int)blockDim.x; ++q) c += flags[q]; s_items += c; }
+        if (tid == 0) s_items += total;
         __syncthreads();
     }
-    // members find their leader: same expert, chunk start
-    for (int r = threadIdx.x; r < n; r += blockDim.x) {
-        if (ex[r] < 0) continue;
-        int before = 0, lead = -1, seen = 0;
-        for (int q = 0; q < r; ++q) before += (ex[q] == ex[r]);
-        if (before % kItemRoutes == 0) continue;   // is a leader
-        const int want = before - before % kItemRoutes;
+    // members find their leader: same expert, start of their chunk
+    for (int r = tid; r < n; r += blockDim.x) {
+        const int e = ex[r];
+        if (e < 0) continue;
+        int before = 0;
+        for (int q = 0; q < r; ++q) before += (ex[q] == e);
+        const int within = before % kItemRoutes;
+        if (within == 0) continue;                 // is a leader
+        const int want = before - within;
+        int lead = -1, seen = 0;
         for (int q = 0; q < r; ++q) {
-            if (ex[q] == ex[r]) { if (seen == want) { lead = q; break; } ++seen; }
+            if (ex[q] == e) { if (seen == want) { lead = q; break; } ++seen; }
         }
-        const int slot = ex[n + lead];
-        if (slot < max_items) pv.item_routes[slot * kItemRoutes + before % kItemRoutes] = r;
+        const int slot = slot_of[lead];
+        if (slot < max_items) pv.item_routes[slot * kItemRoutes + within] = r;
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
+    if (tid == 0) {
         int items = s_items;
         if (has_shared) {
             for (int t0 = 0; t0 < T; t0 += kItemRoutes) {
@@ -326,6 +341,110 @@ __global__ void __launch_bounds__(512) moe_plan_kernel(MoePlanView pv, const int
         }
         *pv.num_items = items < max_items ? items : max_items;
     }
+}
+
+__global__ void __launch_bounds__(512) moe_plan_kernel(MoePlanView pv, const int* __restrict__ ids, int T, int top_k,
+                                                       int expert_offset, int num_local, int has_shared, int max_items) {
+    pdl_grid_sync();
+    extern __shared__ int sh[];
+    moe_plan_body(pv, ids, T, top_k, expert_offset, num_local, has_shared, max_items, sh);
+}
+
+// ---- router GEMV + routing + plan in one launch --------------------------------------------------------------
+// grid (E/32, H/256): block (nb, kc) multiplies 32 router rows by the 256-wide K chunk kc for every token and
+// stores the partial logits in slab kc.  The block that finishes last (ticket counter) adds the slabs up, routes
+// every token (one warp per token) and builds the work-item plan, so the MoE layer needs no further launch before
+// its expert GEMMs.  Replaces the reference's router GEMV + `route_top8` + host-side plan
+// (`csrc/glm_gemv.cu:1642`, `csrc/glm_ops.cu:2343`).
+struct RouterFusedParams {
+    const bf16* x; int ldx;                 // [T, H]
+    const bf16* router_w;                   // [E, H]
+    const float* bias;                      // [E] or null
+    int T, H, E, top_k, n_group, topk_group, norm;
+    float scale;
+    float* slabs;                           // [H/256][T][E]
+    unsigned int* counter;                  // zero before the first use; the kernel leaves it zero
+    int* ids; float* wts;                   // [T, top_k]
+    MoePlanView pv;
+    int expert_offset, num_local, has_shared, max_items;
+};
+
+template <int PER>
+__global__ void __launch_bounds__(256) router_route_plan_kernel(RouterFusedParams p) {
+    pdl_grid_sync();
+    extern __shared__ float dyn[];           // phase 1: x chunk [T][256] fp32; phase 2: plan scratch + ids
+    __shared__ int s_last;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int n0 = blockIdx.x * 32, kc = blockIdx.y, k0 = kc * 256;
+    for (int i = tid; i < p.T * 256; i += blockDim.x) {
+        const int t = i >> 8, k = i & 255;
+        dyn[i] = __bfloat162float(p.x[(size_t)t * p.ldx + k0 + k]);
+    }
+    // this warp's four weight rows, 8 K values per lane
+    uint4 wv[4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        const int n = n0 + warp * 4 + r;
+        wv[r] = n < p.E ? ldg_nc_16(p.router_w + (size_t)n * p.H + k0 + lane * 8) : make_uint4(0, 0, 0, 0);
+    }
+    __syncthreads();
+    float wf[4][8];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        const float2 a = bf162_to_f2(wv[r].x), b = bf162_to_f2(wv[r].y), c = bf162_to_f2(wv[r].z), d = bf162_to_f2(wv[r].w);
+        wf[r][0] = a.x; wf[r][1] = a.y; wf[r][2] = b.x; wf[r][3] = b.y; wf[r][4] = c.x; wf[r][5] = c.y; wf[r][6] = d.x; wf[r][7] = d.y;
+    }
+    for (int t = 0; t < p.T; ++t) {
+        const float4 x0 = *reinterpret_cast<const float4*>(dyn + t * 256 + lane * 8);
+        const float4 x1 = *reinterpret_cast<const float4*>(dyn + t * 256 + lane * 8 + 4);
+        float acc[4];
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            acc[r] = wf[r][0] * x0.x + wf[r][1] * x0.y + wf[r][2] * x0.z + wf[r][3] * x0.w + wf[r][4] * x1.x + wf[r][5] * x1.y +
+                     wf[r][6] * x1.z + wf[r][7] * x1.w;
+            acc[r] = warp_sum(acc[r]);
+        }
+        if (lane < 4) {
+            const int n = n0 + warp * 4 + lane;
+            const float v = lane == 0 ? acc[0] : lane == 1 ? acc[1] : lane == 2 ? acc[2] : acc[3];
+            if (n < p.E) p.slabs[((size_t)kc * p.T + t) * p.E + n] = v;
+        }
+    }
+    // ---- last block to finish takes over ----
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        const unsigned int total = gridDim.x * gridDim.y;
+        const unsigned int ticket = atomicAdd(p.counter, 1u);
+        s_last = ticket == total - 1;
+        if (s_last) *p.counter = 0u;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    int* plan_sh = reinterpret_cast<int*>(dyn);
+    int* s_ids = plan_sh + 2 * (p.T * p.top_k + 8);
+    const int ks = p.H / 256;
+    for (int t = warp; t < p.T; t += 8) {
+        float lg[PER];
+#pragma unroll
+        for (int i = 0; i < PER; ++i) lg[i] = 0.f;
+        for (int s = 0; s < ks; ++s) {
+            const float* src = p.slabs + ((size_t)s * p.T + t) * p.E + lane * PER;
+#pragma unroll
+            for (int i = 0; i < PER; ++i)
+                if (lane * PER + i < p.E) lg[i] += __ldcg(src + i);
+        }
+        int id; float w;
+        route_warp<PER>(lg, p.bias, p.E, p.top_k, p.n_group, p.topk_group, p.norm, p.scale, id, w);
+        if (lane < p.top_k) {
+            p.ids[(size_t)t * p.top_k + lane] = id;
+            p.wts[(size_t)t * p.top_k + lane] = w;
+            s_ids[t * p.top_k + lane] = id;
+        }
+    }
+    __syncthreads();
+    moe_plan_body(p.pv, s_ids, p.T, p.top_k, p.expert_offset, p.num_local, p.has_shared, p.max_items, plan_sh);
 }
 
 struct MoeGroupedParams {
@@ -342,6 +461,7 @@ struct MoeGroupedParams {
 
 // grid (ceil(I/16 / tiles_per_block), max_items).  Warp = (tile, kpart): gate rows i0..i0+15 and up rows I+i0.. .
 __global__ void __launch_bounds__(256) moe_gate_up_mma_kernel(MoeGroupedParams p, int ksplit) {
+    pdl_grid_sync();
     extern __shared__ float red[];                 // [8 warps][2 tiles][8 tok][16 rows]
     const int item = blockIdx.y;
     if (item >= *p.num_items) return;
@@ -397,6 +517,7 @@ __global__ void __launch_bounds__(256) moe_gate_up_mma_kernel(MoeGroupedParams p
 
 // grid (ceil(H/16 / tiles_per_block), max_items).  B operand rows = the item's routes (their act rows).
 __global__ void __launch_bounds__(256) moe_down_mma_kernel(MoeGroupedParams p, int ksplit) {
+    pdl_grid_sync();
     extern __shared__ float red[];                 // [8 warps][8 tok][16 rows]
     const int item = blockIdx.y;
     if (item >= *p.num_items) return;
@@ -437,6 +558,7 @@ __global__ void __launch_bounds__(256) moe_down_mma_kernel(MoeGroupedParams p, i
 __global__ void moe_route_reduce_kernel(const float* __restrict__ y_route, const int* __restrict__ ids, const float* __restrict__ wts,
                                         int T, int top_k, int H, int expert_offset, int num_local, int has_shared,
                                         float* __restrict__ out, int use_push, PushCtx push) {
+    pdl_grid_sync();
     const int t = blockIdx.y;
     for (int n = blockIdx.x * blockDim.x + threadIdx.x; n < H; n += gridDim.x * blockDim.x) {
         float v = 0.f;
@@ -477,9 +599,27 @@ struct MoeGroupedArgs {
     void* out;           // f32 [T, H] (ignored when pushing)
 };
 
-// Decode-time MoE layer for T <= 32 tokens: plan, gate/up, down, weighted reduce (optionally pushed to
-// every rank's receive slot as the producer half of the fused all-reduce).  H % 128 == 0, I % 128 == 0.
-SL_API int sl_moe_grouped_mma(const MoeGroupedArgs* a, const PushCtx* push, cudaStream_t s) {
+// Optional router stage: with it the layer starts from the normed hidden state alone and writes the chosen
+// experts and weights to a->ids / a->wts itself.
+struct MoeRouterArgs {
+    const void* router_w;    // bf16 [E, H]
+    const void* bias;        // f32 [E] or null
+    int E, n_group, topk_group, norm;
+    float scale;
+    void* slabs;             // f32 [H/256, T, E] scratch
+    void* counter;           // u32, zero before the first use (the kernel leaves it zero)
+};
+
+template <int PER>
+static void launch_router(const RouterFusedParams& rp, dim3 grid, size_t smem, cudaStream_t s) {
+    auto kern = router_route_plan_kernel<PER>;
+    sl_launch(kern, grid, 256, smem, s, rp);
+}
+
+// Decode-time MoE layer for T <= 32 tokens: (router, routing,) plan, gate/up, down, weighted reduce (optionally
+// pushed to every rank's receive slot as the producer half of the fused all-reduce).  H % 128 == 0, I % 128 == 0;
+// with a router stage also H % 256 == 0.
+SL_API int sl_moe_grouped_mma(const MoeGroupedArgs* a, const MoeRouterArgs* r, const PushCtx* push, cudaStream_t s) {
     if (a->T == 0) return 0;
     if (a->T > 32 || a->H % 128 != 0 || a->I % 128 != 0 || a->ldx % 8 != 0 || a->T * a->top_k > 480) return -1;
     if (push != nullptr && (a->T > push->slot_rows || a->H > push->row_len)) return -1;
@@ -487,11 +627,38 @@ SL_API int sl_moe_grouped_mma(const MoeGroupedArgs* a, const PushCtx* push, cuda
     const int n_routed = a->T * a->top_k;
     int* plan = (int*)a->plan;
     MoePlanView pv{plan, plan + a->max_items, plan + a->max_items * (1 + kItemRoutes)};
-    moe_plan_kernel<<<1, 512, (size_t)2 * (n_routed + 8) * sizeof(int), s>>>(pv, (const int*)a->ids, a->T, a->top_k, a->expert_offset,
-                                                                           a->num_local, has_shared, a->max_items);
+    if (r != nullptr) {
+        if (a->H % 256 != 0 || r->E > 512 || a->top_k > 32 || r->n_group > 32 || r->n_group < 1 || r->E % r->n_group != 0) return -1;
+        int PER = 1;
+        while (PER * 32 < r->E) PER <<= 1;
+        if (r->n_group > 1) {
+            const int gsz = r->E / r->n_group;
+            if (gsz % PER != 0) return -1;                   // a group must be a run of whole lanes
+            const int lpg = gsz / PER;
+            if (lpg & (lpg - 1)) return -1;
+        }
+        RouterFusedParams rp{(const bf16*)a->x, a->ldx, (const bf16*)r->router_w, (const float*)r->bias, a->T, a->H, r->E,
+                             a->top_k, r->n_group, r->topk_group, r->norm, r->scale, (float*)r->slabs,
+                             (unsigned int*)r->counter, (int*)a->ids, (float*)a->wts, pv, a->expert_offset, a->num_local,
+                             has_shared, a->max_items};
+        size_t smem = (size_t)a->T * 256 * sizeof(float);
+        const size_t smem2 = (size_t)(3 * n_routed + 16) * sizeof(int);
+        if (smem2 > smem) smem = smem2;
+        const dim3 grid((r->E + 31) / 32, a->H / 256);
+        switch (PER) {
+            case 1: launch_router<1>(rp, grid, smem, s); break;
+            case 2: launch_router<2>(rp, grid, smem, s); break;
+            case 4: launch_router<4>(rp, grid, smem, s); break;
+            case 8: launch_router<8>(rp, grid, smem, s); break;
+            default: launch_router<16>(rp, grid, smem, s); break;
+        }
+    } else {
+        sl_launch(moe_plan_kernel, 1, 512, (size_t)2 * (n_routed + 8) * sizeof(int), s, pv, (const int*)a->ids, a->T, a->top_k,
+                  a->expert_offset, a->num_local, has_shared, a->max_items);
+    }
     const int tpad = (a->T + 7) / 8 * 8;
     const int units = tpad * (a->H / 8);
-    permute_x_kernel<<<(units + 255) / 256, 256, 0, s>>>((uint4*)a->xp, (const bf16*)a->x, a->T, tpad, a->H, a->ldx);
+    sl_launch(permute_x_kernel, (units + 255) / 256, 256, 0, s, (uint4*)a->xp, (const bf16*)a->x, a->T, tpad, a->H, a->ldx);
     MoeGroupedParams p{pv.item_expert, pv.item_routes, pv.num_items, a->T, a->top_k, a->H, a->I,
                        (const uint8_t*)a->w13, (const uint8_t*)a->s13, (const float*)a->g13,
                        (const uint8_t*)a->sw13, (const uint8_t*)a->ss13, (const float*)a->sg13,
@@ -501,15 +668,15 @@ SL_API int sl_moe_grouped_mma(const MoeGroupedArgs* a, const PushCtx* push, cuda
     {
         const int ks = pick_ksplit(a->H, 4), tpb = 8 / ks, tiles = (a->I + 15) / 16;
         const size_t smem = (size_t)8 * 2 * 8 * 16 * sizeof(float);
-        moe_gate_up_mma_kernel<<<dim3((tiles + tpb - 1) / tpb, a->max_items), 256, smem, s>>>(p, ks);
+        sl_launch(moe_gate_up_mma_kernel, dim3((tiles + tpb - 1) / tpb, a->max_items), 256, smem, s, p, ks);
     }
     {
         const int ks = pick_ksplit(a->I, 4), tpb = 8 / ks, tiles = (a->H + 15) / 16;
         const size_t smem = (size_t)8 * 8 * 16 * sizeof(float);
-        moe_down_mma_kernel<<<dim3((tiles + tpb - 1) / tpb, a->max_items), 256, smem, s>>>(p, ks);
+        sl_launch(moe_down_mma_kernel, dim3((tiles + tpb - 1) / tpb, a->max_items), 256, smem, s, p, ks);
     }
     int bx = (a->H + 255) / 256;
-    moe_route_reduce_kernel<<<dim3(bx, a->T), 256, 0, s>>>((const float*)a->y_route, (const int*)a->ids, (const float*)a->wts, a->T,
+    sl_launch(moe_route_reduce_kernel, dim3(bx, a->T), 256, 0, s, (const float*)a->y_route, (const int*)a->ids, (const float*)a->wts, a->T,
                                                           a->top_k, a->H, a->expert_offset, a->num_local, has_shared,
                                                           (float*)a->out, push ? 1 : 0, push ? *push : PushCtx{});
     return (int)cudaGetLastError();

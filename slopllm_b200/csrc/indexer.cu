@@ -34,6 +34,7 @@ __device__ __forceinline__ int local_visible(int p, int W, int r) { return p >= 
 // applied to Q as well, so every lane issues two 16-byte loads per key row quarter.
 template <int HI, int D>
 __global__ void __launch_bounds__(256) indexer_score_kernel(IndexerScoreParams p, int keys_per_block) {
+    pdl_grid_sync();
     static_assert(HI % 16 == 0 && D % 32 == 0, "index heads / dim");
     constexpr int MT = HI / 16;          // m tiles (16 heads each)
     constexpr int KS = D / 32;           // k steps of 32
@@ -110,6 +111,7 @@ __global__ void __launch_bounds__(256) indexer_score_kernel(IndexerScoreParams p
 
 // Generic CUDA-core scorer for other head counts / dims (small test models).
 __global__ void indexer_score_generic_kernel(IndexerScoreParams p, int keys_per_block) {
+    pdl_grid_sync();
     extern __shared__ float qs[];          // [Hi*D] + [Hi]
     const int t = blockIdx.y;
     const int pos = p.positions[t];
@@ -144,11 +146,11 @@ SL_API int sl_indexer_scores(const IndexerScoreParams* p, int T, int max_local, 
     while (kpb > 64 && (long)((max_local + kpb - 1) / kpb) * T < 296) kpb >>= 1;
     dim3 grid((max_local + kpb - 1) / kpb, T);
     if (p->Hi == 32 && p->D == 128) {
-        indexer_score_kernel<32, 128><<<grid, 256, 0, s>>>(*p, kpb);
+        sl_launch(indexer_score_kernel<32, 128>, grid, 256, 0, s, *p, kpb);
     } else {
         const size_t smem = (size_t)(p->Hi * p->D + p->Hi) * sizeof(float);
         if (smem > 48 * 1024) return -1;
-        indexer_score_generic_kernel<<<grid, 256, smem, s>>>(*p, kpb);
+        sl_launch(indexer_score_generic_kernel, grid, 256, smem, s, *p, kpb);
     }
     return SL_LAUNCH_CHECK();
 }
@@ -165,6 +167,11 @@ struct TopkSelectParams {
     int top_k, cp_world, cp_rank;
     int* out_pos;             // [T, top_k] global positions ascending, -1 padded
     float* out_score;         // [T, top_k] (0 where unused)
+    // optional fused slot lookup (cp_world == 1 only; null to skip): physical cache slots of the
+    // selected keys in the same order, -1 padded, and the number selected per token
+    int* slots; int* lengths;
+    const int* page_table; const int* batch_idx;
+    int pt_stride, page_size;
 };
 
 // Radix-descent helper: given hist[256] of the current digit among the candidates, find the bin
@@ -204,6 +211,7 @@ __device__ __forceinline__ void radix_pick_bin(const uint32_t* hist, uint32_t* w
 // n_local)), then an in-order gather of keys above the threshold plus the first ties.
 // Scores of up to 8192 keys stay in registers between the passes.
 __global__ void __launch_bounds__(1024) topk_select_kernel(TopkSelectParams p) {
+    pdl_grid_sync();
     __shared__ uint32_t hist[256];
     __shared__ uint32_t wtot[8];
     __shared__ uint32_t s_prefix, s_remaining;
@@ -215,11 +223,15 @@ __global__ void __launch_bounds__(1024) topk_select_kernel(TopkSelectParams p) {
     const int n = local_visible(pos, p.cp_world, p.cp_rank);
     int* opos = p.out_pos + (size_t)t * p.top_k;
     float* osc = p.out_score + (size_t)t * p.top_k;
+    int* oslot = p.slots != nullptr ? p.slots + (size_t)t * p.top_k : nullptr;
+    const int* pt = p.slots != nullptr ? p.page_table + (size_t)p.batch_idx[t] * p.pt_stride : nullptr;
     if (pos + 1 <= p.top_k) {
         for (int i = tid; i < p.top_k; i += blockDim.x) {
             opos[i] = i < n ? i * p.cp_world + p.cp_rank : -1;
             osc[i] = 0.f;
+            if (oslot != nullptr) oslot[i] = i < n ? pt[i / p.page_size] * p.page_size + i % p.page_size : -1;
         }
+        if (oslot != nullptr && tid == 0) p.lengths[t] = n;
         return;
     }
     const float* sc = p.scores + (size_t)t * p.ld_scores;
@@ -294,16 +306,23 @@ __global__ void __launch_bounds__(1024) topk_select_kernel(TopkSelectParams p) {
         if (take && off < p.top_k) {
             opos[off] = i * p.cp_world + p.cp_rank;
             osc[off] = sc[i];
+            if (oslot != nullptr) oslot[off] = pt[i / p.page_size] * p.page_size + i % p.page_size;
         }
         __syncthreads();
         if (tid == 0) { s_base += tk_total; s_eq_used += eq_total; }
         __syncthreads();
     }
-    for (int i = s_base + tid; i < p.top_k; i += blockDim.x) { opos[i] = -1; osc[i] = 0.f; }
+    for (int i = s_base + tid; i < p.top_k; i += blockDim.x) {
+        opos[i] = -1;
+        osc[i] = 0.f;
+        if (oslot != nullptr) oslot[i] = -1;
+    }
+    if (oslot != nullptr && tid == 0) p.lengths[t] = min(s_base, p.top_k);
 }
 
 SL_API int sl_topk_select(const TopkSelectParams* p, int T, cudaStream_t s) {
     if (T == 0) return 0;
-    topk_select_kernel<<<T, 1024, 0, s>>>(*p);
+    if (p->slots != nullptr && p->cp_world != 1) return -1;
+    sl_launch(topk_select_kernel, T, 1024, 0, s, *p);
     return SL_LAUNCH_CHECK();
 }

@@ -30,6 +30,7 @@ __device__ __forceinline__ uint32_t order_key_f(float f) {
 template <typename TL>
 __global__ void __launch_bounds__(256) argmax_partial_kernel(float* __restrict__ pv, int* __restrict__ pi,
                                                              const TL* __restrict__ logits, int V, int ld) {
+    pdl_grid_sync();
     __shared__ float sv[8];
     __shared__ int si[8];
     const int b = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -57,6 +58,7 @@ __global__ void __launch_bounds__(256) argmax_partial_kernel(float* __restrict__
 
 __global__ void argmax_final_kernel(int64_t* __restrict__ out, float* __restrict__ out_val, const float* __restrict__ pv,
                                     const int* __restrict__ pi, int chunks, int64_t id_offset) {
+    pdl_grid_sync();
     const int b = blockIdx.x, lane = threadIdx.x;
     float best = -INFINITY; int bi = 0x7fffffff;
     for (int i = lane; i < chunks; i += 32) {
@@ -80,9 +82,9 @@ SL_API int sl_argmax(void* out, const void* logits, int B, int V, int ld, int is
                      void* scratch_val, void* scratch_idx, cudaStream_t s) {
     if (B == 0) return 0;
     dim3 grid(SL_ARGMAX_CHUNKS, B);
-    if (is_f32) argmax_partial_kernel<float><<<grid, 256, 0, s>>>((float*)scratch_val, (int*)scratch_idx, (const float*)logits, V, ld);
-    else argmax_partial_kernel<bf16><<<grid, 256, 0, s>>>((float*)scratch_val, (int*)scratch_idx, (const bf16*)logits, V, ld);
-    argmax_final_kernel<<<B, 32, 0, s>>>((int64_t*)out, (float*)out_val, (const float*)scratch_val, (const int*)scratch_idx,
+    if (is_f32) sl_launch(argmax_partial_kernel<float>, grid, 256, 0, s, (float*)scratch_val, (int*)scratch_idx, (const float*)logits, V, ld);
+    else sl_launch(argmax_partial_kernel<bf16>, grid, 256, 0, s, (float*)scratch_val, (int*)scratch_idx, (const bf16*)logits, V, ld);
+    sl_launch(argmax_final_kernel, B, 32, 0, s, (int64_t*)out, (float*)out_val, (const float*)scratch_val, (const int*)scratch_idx,
                                          SL_ARGMAX_CHUNKS, id_offset);
     return SL_LAUNCH_CHECK();
 }
@@ -102,6 +104,7 @@ struct SampleParams {
 };
 
 __global__ void __launch_bounds__(1024) sample_kernel(SampleParams p) {
+    pdl_grid_sync();
     __shared__ uint32_t hist[256];
     __shared__ uint32_t s_prefix, s_remaining;
     __shared__ float cv[SL_MAX_CAND];
@@ -225,7 +228,7 @@ __global__ void __launch_bounds__(1024) sample_kernel(SampleParams p) {
 SL_API int sl_sample(const SampleParams* p, int B, cudaStream_t s) {
     if (B == 0) return 0;
     if (p->max_k > SL_MAX_CAND || p->window > 1024) return -1;
-    sample_kernel<<<B, 1024, 0, s>>>(*p);
+    sl_launch(sample_kernel, B, 1024, 0, s, *p);
     return SL_LAUNCH_CHECK();
 }
 
@@ -253,6 +256,7 @@ __device__ int pick_from(const int64_t* ids, const float* w, int C, double u, in
 }
 
 __global__ void spec_reject_kernel(SpecRejectParams p, int B) {
+    pdl_grid_sync();
     const int b = blockIdx.x * blockDim.x + threadIdx.x;
     if (b >= B) return;
     const int D = p.D, C = p.C;
@@ -297,13 +301,14 @@ __global__ void spec_reject_kernel(SpecRejectParams p, int B) {
 SL_API int sl_spec_reject(const SpecRejectParams* p, int B, cudaStream_t s) {
     if (B == 0) return 0;
     if (p->C > SL_MAX_CAND) return -1;
-    spec_reject_kernel<<<(B + 63) / 64, 64, 0, s>>>(*p, B);
+    sl_launch(spec_reject_kernel, (B + 63) / 64, 64, 0, s, *p, B);
     return SL_LAUNCH_CHECK();
 }
 
 // RNG counter += inc (one thread; keeps graph replays from repeating random numbers).
-__global__ void advance_counter_kernel(uint32_t* counter, uint32_t inc) { *counter += inc; }
+__global__ void advance_counter_kernel(uint32_t* counter, uint32_t inc) {
+    pdl_grid_sync(); *counter += inc; }
 SL_API int sl_advance_counter(void* counter, unsigned inc, cudaStream_t s) {
-    advance_counter_kernel<<<1, 1, 0, s>>>((uint32_t*)counter, inc);
+    sl_launch(advance_counter_kernel, 1, 1, 0, s, (uint32_t*)counter, inc);
     return SL_LAUNCH_CHECK();
 }

@@ -22,6 +22,7 @@ struct SparseMlaParams {
 // Shared: q [HB][DP], k [KC][DP] (dequantised fp32, row pitch DP = R + Dr + 1), p [HB][KC].
 template <int HB, int KC>
 __global__ void __launch_bounds__(256) sparse_mla_split_kernel(SparseMlaParams p) {
+    pdl_grid_sync();
     extern __shared__ float sm[];
     const int D = p.R + p.Dr, DP = D + 1;
     float* qs = sm;                       // HB * DP
@@ -161,7 +162,7 @@ SL_API int sl_sparse_mla_split(const SparseMlaParams* p, int T, cudaStream_t s) 
     auto kern = sparse_mla_split_kernel<HB, KC>;
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     dim3 grid(p->splits, (p->h + HB - 1) / HB, T);
-    kern<<<grid, 256, smem, s>>>(*p);
+    sl_launch(kern, grid, 256, smem, s, *p);
     return SL_LAUNCH_CHECK();
 }
 
@@ -181,6 +182,7 @@ struct CombineParams {
 };
 
 __global__ void __launch_bounds__(128) mla_combine_kernel(CombineParams p) {
+    pdl_grid_sync();
     const int t = blockIdx.y, hh = blockIdx.x, head = p.head_begin + hh;
     __shared__ float wsh[8 * 64];
     __shared__ float scratch[33];
@@ -238,6 +240,6 @@ __global__ void __launch_bounds__(128) mla_combine_kernel(CombineParams p) {
 SL_API int sl_mla_combine(const CombineParams* p, int T, cudaStream_t s) {
     if (T == 0 || p->head_count == 0) return 0;
     if (p->n_buf * p->parts_per_buf > 8 * 64) return -1;
-    mla_combine_kernel<<<dim3(p->head_count, T), 128, 0, s>>>(*p);
+    sl_launch(mla_combine_kernel, dim3(p->head_count, T), 128, 0, s, *p);
     return SL_LAUNCH_CHECK();
 }

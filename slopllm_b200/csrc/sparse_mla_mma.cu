@@ -44,6 +44,7 @@ __device__ __forceinline__ void ldmatrix_x2_trans(uint32_t& r0, uint32_t& r1, co
 // Shared: Q [16][DP] f16, K [64][DP] f16 (DP = R + Dr + 8 halves: rows 16-byte aligned, bank-skewed),
 // P [16][72] f16, row statistics.
 __global__ void __launch_bounds__(256) sparse_mla_mma_kernel(Params p) {
+    pdl_grid_sync();
     extern __shared__ __align__(16) unsigned char smraw[];
     const int D = p.R + p.Dr, DP = D + 8;
     __half* qs = reinterpret_cast<__half*>(smraw);            // HB * DP
@@ -277,6 +278,6 @@ SL_API int sl_sparse_mla_split_mma(const void* params, int T, cudaStream_t s) {
     }
     if (smem > 160 * 1024) return -1;
     dim3 grid(p->splits, (p->h + HB - 1) / HB, T);
-    sparse_mla_mma_kernel<<<grid, 256, smem, s>>>(*p);
+    sl_launch(sparse_mla_mma_kernel, grid, 256, smem, s, *p);
     return (int)cudaGetLastError();
 }

@@ -93,9 +93,9 @@ class GlmMoeDsaModel:
     def attention(self, layer: int, lw: LayerWeights, x: torch.Tensor, st: StepState, cache: KVCacheTensors):
         ops, comm, ctx = self.ops, self.comm, self.ctx
         lc = cache.layers[layer]
-        qkv = ops.linear(x, lw.w_qkv_a)
+        qkv = ops.linear(x, lw.w_qkv_a, defer_reduce=True)
         cq, idx_w = ops.attn_pre(qkv, lw, st, lc)
-        qb = ops.linear(cq, lw.w_q_b)
+        qb = ops.linear(cq, lw.w_q_b, defer_reduce=True)
         q_abs, q_pe, q8, w_eff = ops.q_post(qb, lw, st, idx_w)
         if lw.has_indexer:
             pos, score = ops.indexer_topk(q8, w_eff, lc, st)

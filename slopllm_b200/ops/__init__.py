@@ -39,7 +39,7 @@ class RefOps:
     def add_rmsnorm(self, x, residual, w, eps=None):
         return R.add_rmsnorm(x, residual, w, self.cfg.rms_norm_eps if eps is None else eps)
 
-    def linear(self, x, w, out_f32: bool = False, sink=None):
+    def linear(self, x, w, out_f32: bool = False, sink=None, defer_reduce: bool = False):
         return R.linear(x, w)
 
     def merge_attention_partials(self, o, lse):

@@ -19,6 +19,31 @@ DECODE_MAX_T = 32          # token rows handled by the weight-streaming (GEMV) k
 TENSOR_MIN_T = 2           # from this many rows on the streaming kernels use the tensor cores
 
 
+class SplitKSlabs:
+    """fp32 partial sums [splits, T, N] of a split-K product; their sum rounded to bf16 is the value."""
+
+    def __init__(self, slabs: torch.Tensor):
+        self.slabs = slabs
+
+    @property
+    def shape(self):
+        return self.slabs.shape[1:]
+
+    @property
+    def device(self):
+        return self.slabs.device
+
+    def reduce(self) -> torch.Tensor:
+        return self.slabs.sum(0).to(torch.bfloat16)
+
+
+def _act_source(a):
+    """(row-0 view, n_slabs, slab_stride) of an activation in either form."""
+    if isinstance(a, SplitKSlabs):
+        return a.slabs[0], a.slabs.shape[0], a.slabs.stride(0)
+    return a, 0, 0
+
+
 class CudaOps:
     name = "cuda"
     act_dtype = torch.bfloat16
@@ -27,6 +52,7 @@ class CudaOps:
         self.cfg = cfg
         self.ctx = ctx
         N.kernels()            # fail loudly when the native library is missing
+        self._counters = {}
 
     # -- helpers ----------------------------------------------------------------------------
     @staticmethod
@@ -62,9 +88,11 @@ class CudaOps:
                int(x.dtype == torch.float32), N.stream())
         return out
 
-    def linear(self, x, w, out_f32: bool = False, sink=None):
+    def linear(self, x, w, out_f32: bool = False, sink=None, defer_reduce: bool = False):
         """y = x @ W^T.  With `sink` (a receive buffer on every rank) the fp32 result rows are
-        stored straight into the peers' memory by the producing kernel and the sink is returned."""
+        stored straight into the peers' memory by the producing kernel and the sink is returned.
+        With `defer_reduce` a split-K product may come back as `SplitKSlabs` (fp32 partial sums the
+        consumer adds up while it loads them); only `attn_pre` and `q_post` accept that form."""
         x = self._bf16(x)
         if x.stride(-1) != 1:
             x = x.contiguous()
@@ -94,12 +122,15 @@ class CudaOps:
                 N.call("sl_linear_nvfp4_mma", y.data_ptr(), x.data_ptr(), xp.data_ptr(), w.weight.data_ptr(),
                        w.scale.data_ptr(), w.scale2.data_ptr(), T, Nn, K, x.stride(0), int(out_f32), N.stream())
                 return y
-            if not w.is_nvfp4 and x.stride(0) % 8 == 0 and K % 8 == 0:
+            if not w.is_nvfp4 and x.stride(0) % 8 == 0 and K % 8 == 0 and Nn > 1024:
                 from . import tcgen05
-                N.call("sl_linear_smallT_bf16_tcgen05", x.data_ptr(), w.weight.data_ptr(), y.data_ptr(), T, Nn, K,
-                       x.stride(0), w.weight.stride(0), y.stride(0), int(out_f32),
-                       tcgen05.error_flag(x.device).data_ptr(), N.stream())
-                return y
+                splits = N.kernels().sl_smallT_splits(T, Nn, K)
+                part = torch.empty(splits, T, Nn, dtype=torch.float32, device=x.device) if splits > 1 else None
+                deferred = defer_reduce and splits > 1
+                N.call("sl_linear_smallT_bf16_tcgen05", x.data_ptr(), w.weight.data_ptr(), 0 if deferred else y.data_ptr(),
+                       T, Nn, K, x.stride(0), w.weight.stride(0), y.stride(0), int(out_f32),
+                       tcgen05.error_flag(x.device).data_ptr(), N.ptr(part), splits, N.stream())
+                return SplitKSlabs(part) if deferred else y
         if w.is_nvfp4:
             N.call("sl_gemv_nvfp4", y.data_ptr(), x.data_ptr(), w.weight.data_ptr(), w.scale.data_ptr(),
                    w.scale2.data_ptr(), T, Nn, K, x.stride(0), int(out_f32), N.stream())
@@ -118,8 +149,9 @@ class CudaOps:
         dev = qkv.device
         cq = torch.empty(T, c.q_lora_rank, dtype=torch.bfloat16, device=dev)
         idx_w = torch.empty(T, c.index_n_heads, dtype=torch.float32, device=dev) if lw.has_indexer else None
+        qkv, n_slabs, slab_stride = _act_source(qkv)
         p = N.AttnPreParams(
-            qkv=qkv.data_ptr(), ld=qkv.stride(0), q_lora=c.q_lora_rank, kv_lora=c.kv_lora_rank, rope_dim=c.qk_rope_head_dim,
+            n_slabs=n_slabs, slab_stride=slab_stride, qkv=qkv.data_ptr(), ld=qkv.stride(0), q_lora=c.q_lora_rank, kv_lora=c.kv_lora_rank, rope_dim=c.qk_rope_head_dim,
             idx_dim=c.index_head_dim if lw.has_indexer else 0, idx_heads=c.index_n_heads,
             q_norm_w=lw.q_a_norm.data_ptr(), kv_norm_w=lw.kv_a_norm.data_ptr(), idx_ln_w=N.ptr(lw.idx_k_norm_w),
             idx_ln_b=N.ptr(lw.idx_k_norm_b), eps=c.rms_norm_eps, theta=c.rope_theta,
@@ -141,8 +173,9 @@ class CudaOps:
         if lw.has_indexer:
             q8 = torch.empty(T, c.index_n_heads, c.index_head_dim, dtype=torch.uint8, device=dev)
             w_eff = torch.empty(T, c.index_n_heads, dtype=torch.float32, device=dev)
+        qb, n_slabs, slab_stride = _act_source(qb)
         p = N.QPostParams(
-            qb=qb.data_ptr(), ld=qb.stride(0), heads=hl, d_nope=c.qk_nope_head_dim, rope_dim=c.qk_rope_head_dim,
+            n_slabs=n_slabs, slab_stride=slab_stride, qb=qb.data_ptr(), ld=qb.stride(0), heads=hl, d_nope=c.qk_nope_head_dim, rope_dim=c.qk_rope_head_dim,
             idx_heads=c.index_n_heads if lw.has_indexer else 0, idx_dim=c.index_head_dim, theta=c.rope_theta,
             rope_interleave=int(c.rope_interleave), idx_rope_interleave=int(c.indexer_rope_interleave),
             positions=st.positions.data_ptr(), idx_w=N.ptr(idx_w), q_pe_out=q_pe.data_ptr(), q8_out=N.ptr(q8),
@@ -150,7 +183,7 @@ class CudaOps:
         N.call("sl_q_post", C.byref(p), T, N.stream())
         q_abs = torch.empty(T, hl, c.kv_lora_rank, dtype=torch.bfloat16, device=dev)
         N.call("sl_bmv", q_abs.data_ptr(), qb.data_ptr(), lw.w_kn.data_ptr(), T, hl, c.qk_nope_head_dim, c.kv_lora_rank,
-               qb.stride(0), c.qk_head_dim, N.stream())
+               qb.stride(0), c.qk_head_dim, n_slabs, slab_stride, N.stream())
         return q_abs, q_pe, q8, w_eff
 
     def indexer_topk(self, q8, w_eff, layer_cache, st):
@@ -175,10 +208,21 @@ class CudaOps:
             N.call("sl_indexer_scores", C.byref(sp), T, max_local, N.stream())
         tp = N.TopkSelectParams(scores=scores.data_ptr(), ld_scores=scores.stride(0), positions=st.positions.data_ptr(),
                                 top_k=c.index_topk, cp_world=W, cp_rank=r, out_pos=pos.data_ptr(), out_score=score.data_ptr())
+        if W == 1:
+            # without context parallelism the selected positions are final: look the slots up in the same kernel
+            slots = torch.empty(T, c.index_topk, dtype=torch.int32, device=dev)
+            lengths = torch.empty(T, dtype=torch.int32, device=dev)
+            tp.slots, tp.lengths = slots.data_ptr(), lengths.data_ptr()
+            tp.page_table, tp.batch_idx = st.page_table.data_ptr(), st.batch_idx.data_ptr()
+            tp.pt_stride, tp.page_size = st.page_table.stride(0), st.page_size
+            st.extra["fused_slots"] = (pos, slots, lengths)
         N.call("sl_topk_select", C.byref(tp), T, N.stream())
         return pos, score
 
     def topk_to_slots(self, topk_pos, st, local_only: bool = False):
+        fused = st.extra.pop("fused_slots", None)
+        if fused is not None and fused[0] is topk_pos:
+            return fused[1], fused[2]
         T, k = topk_pos.shape
         dev = topk_pos.device
         slots = torch.empty(T, k, dtype=torch.int32, device=dev)
@@ -241,7 +285,7 @@ class CudaOps:
         Dv = w_v.shape[2]
         o = self._bf16(o).contiguous()
         out = torch.empty(T, hl * Dv, dtype=torch.bfloat16, device=o.device)
-        N.call("sl_bmv", out.data_ptr(), o.data_ptr(), w_v.data_ptr(), T, hl, Rr, Dv, hl * Rr, Rr, N.stream())
+        N.call("sl_bmv", out.data_ptr(), o.data_ptr(), w_v.data_ptr(), T, hl, Rr, Dv, hl * Rr, Rr, 0, 0, N.stream())
         return out
 
     # -- MLP --------------------------------------------------------------------------------------
@@ -300,13 +344,26 @@ class CudaOps:
         N.call("sl_moe_down", C.byref(dp), N.stream())
         return out
 
-    def _moe_grouped(self, x, experts, shared, ids, wts, sink=None):
+    def _moe_grouped(self, x, experts, shared, ids, wts, sink=None, router=None):
         """Tensor-core weight streaming: routes that share an expert form one work item, so each
-        chosen expert's weights are read once per step."""
+        chosen expert's weights are read once per step.  With `router` (a layer's weights) the
+        router product, the routing and the plan run in the first kernel and ids/wts are outputs."""
         T, H = x.shape
+        dev = x.device
+        c = self.cfg
+        rargs = None
+        if router is not None:
+            k = c.num_experts_per_tok
+            E = router.router_w.shape[0]
+            ids = torch.empty(T, k, dtype=torch.int32, device=dev)
+            wts = torch.empty(T, k, dtype=torch.float32, device=dev)
+            slabs = torch.empty(H // 256, T, E, dtype=torch.float32, device=dev)
+            counter = self._zero_counter(dev)
+            rargs = N.MoeRouterArgs(router_w=router.router_w.data_ptr(), bias=N.ptr(router.router_bias), E=E,
+                                    n_group=c.n_group, topk_group=c.topk_group, norm=int(c.norm_topk_prob),
+                                    scale=float(c.routed_scaling_factor), slabs=slabs.data_ptr(), counter=counter.data_ptr())
         k = ids.shape[1]
         I = experts.inter
-        dev = x.device
         routes = T * k + (T if shared is not None else 0)
         max_items = T * k + (T + 7) // 8
         xp = torch.empty(((T + 7) // 8) * 8 * H, dtype=torch.float16, device=dev)
@@ -326,12 +383,31 @@ class CudaOps:
                              max_items=max_items, out=N.ptr(out))
         if sink is not None:
             sink.pushed_rows = T
-            N.call("sl_moe_grouped_mma", C.byref(a), C.cast(C.byref(sink.push), C.c_void_p), N.stream())
+            N.call("sl_moe_grouped_mma", C.byref(a), C.cast(C.byref(rargs), C.c_void_p) if rargs is not None else None,
+                   C.cast(C.byref(sink.push), C.c_void_p), N.stream())
             return sink
-        N.call("sl_moe_grouped_mma", C.byref(a), None, N.stream())
+        N.call("sl_moe_grouped_mma", C.byref(a), C.cast(C.byref(rargs), C.c_void_p) if rargs is not None else None, None,
+               N.stream())
         return out
 
+    def _zero_counter(self, dev):
+        """A device word that the fused router kernel expects to be zero and leaves zero."""
+        key = (dev.type, dev.index)
+        t = self._counters.get(key)
+        if t is None:
+            t = torch.zeros(1, dtype=torch.int32, device=dev)
+            self._counters[key] = t
+        return t
+
     def moe_tp(self, x, lw, sink=None):
+        T, H = x.shape
+        fused_ok = (T <= DECODE_MAX_T and lw.experts.is_nvfp4 and H % 256 == 0 and lw.experts.inter % 128 == 0
+                    and T * self.cfg.num_experts_per_tok <= 480 and lw.router_w.dtype == torch.bfloat16
+                    and (lw.shared is None or lw.shared.inter == lw.experts.inter))
+        if fused_ok:
+            x = self._bf16(x)
+            if x.stride(-1) == 1 and x.stride(0) % 8 == 0:
+                return self._moe_grouped(x, lw.experts, lw.shared, None, None, sink, router=lw)
         ids, wts = self.route(x, lw)
         if x.shape[0] <= DECODE_MAX_T and lw.experts.is_nvfp4:
             if lw.shared is not None and lw.shared.inter != lw.experts.inter:

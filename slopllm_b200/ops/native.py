@@ -30,7 +30,12 @@ def kernels() -> C.CDLL:
     if not os.path.exists(KERNELS_SO):
         raise NativeError(f"{KERNELS_SO} is missing: run `python -m slopllm_b200.build_native` "
                           "(the CUDA path has no PyTorch fallback)")
-    return C.CDLL(KERNELS_SO)
+    lib = C.CDLL(os.environ.get("SLOPLLM_B200_KERNELS_SO", KERNELS_SO))
+    # programmatic dependent launch between the library's kernels; SLOPLLM_B200_PDL=0 turns it off
+    lib.sl_set_pdl.argtypes = [i32]
+    lib.sl_set_pdl.restype = None
+    lib.sl_set_pdl(0 if os.environ.get("SLOPLLM_B200_PDL", "1") == "0" else 1)
+    return lib
 
 
 @lru_cache(maxsize=None)
@@ -66,13 +71,14 @@ class AttnPreParams(C.Structure):
                 ("eps", f32), ("theta", f32), ("rope_interleave", i32), ("idx_rope_interleave", i32),
                 ("positions", vp), ("batch_idx", vp), ("page_table", vp), ("pt_stride", i32), ("page_size", i32),
                 ("cp_world", i32), ("cp_rank", i32), ("kv_group", i32), ("kv_cache", vp), ("idx_cache", vp),
-                ("cq_out", vp), ("idx_w_out", vp)]
+                ("cq_out", vp), ("idx_w_out", vp), ("n_slabs", i32), ("slab_stride", i64)]
 
 
 class QPostParams(C.Structure):
     _fields_ = [("qb", vp), ("ld", i32), ("heads", i32), ("d_nope", i32), ("rope_dim", i32), ("idx_heads", i32),
                 ("idx_dim", i32), ("theta", f32), ("rope_interleave", i32), ("idx_rope_interleave", i32),
-                ("positions", vp), ("idx_w", vp), ("q_pe_out", vp), ("q8_out", vp), ("w_eff_out", vp)]
+                ("positions", vp), ("idx_w", vp), ("q_pe_out", vp), ("q8_out", vp), ("w_eff_out", vp), ("n_slabs", i32),
+                ("slab_stride", i64)]
 
 
 class IndexerScoreParams(C.Structure):
@@ -83,7 +89,8 @@ class IndexerScoreParams(C.Structure):
 
 class TopkSelectParams(C.Structure):
     _fields_ = [("scores", vp), ("ld_scores", i32), ("positions", vp), ("top_k", i32), ("cp_world", i32),
-                ("cp_rank", i32), ("out_pos", vp), ("out_score", vp)]
+                ("cp_rank", i32), ("out_pos", vp), ("out_score", vp), ("slots", vp), ("lengths", vp),
+                ("page_table", vp), ("batch_idx", vp), ("pt_stride", i32), ("page_size", i32)]
 
 
 class SparseMlaParams(C.Structure):
@@ -116,6 +123,11 @@ class MoeGroupedArgs(C.Structure):
                 ("act_perm", vp), ("y_route", vp), ("plan", vp), ("max_items", i32), ("out", vp)]
 
 
+class MoeRouterArgs(C.Structure):
+    _fields_ = [("router_w", vp), ("bias", vp), ("E", i32), ("n_group", i32), ("topk_group", i32), ("norm", i32),
+                ("scale", f32), ("slabs", vp), ("counter", vp)]
+
+
 class SampleParams(C.Structure):
     _fields_ = [("logits", vp), ("V", i32), ("ld", i32), ("temperature", vp), ("top_p", vp), ("rep_penalty", vp),
                 ("presence_penalty", vp), ("top_k", vp), ("history", vp), ("hist_len", vp), ("window", i32),
@@ -135,7 +147,8 @@ _SIGS = {
     "sl_add_rmsnorm": [vp, vp, vp, vp, vp, i32, i32, f32, i32, vp],
     "sl_attn_pre": [C.POINTER(AttnPreParams), i32, vp],
     "sl_q_post": [C.POINTER(QPostParams), i32, vp],
-    "sl_bmv": [vp, vp, vp, i32, i32, i32, i32, i32, i32, vp],
+    "sl_bmv": [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i64, vp],
+    "sl_smallT_splits": [i32, i32, i32],
     "sl_silu_mul": [vp, vp, i32, i32, vp],
     "sl_route_topk": [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, f32, vp],
     "sl_topk_to_slots": [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp],
@@ -153,9 +166,9 @@ _SIGS = {
     "sl_sample": [C.POINTER(SampleParams), i32, vp],
     "sl_spec_reject": [C.POINTER(SpecRejectParams), i32, vp],
     "sl_advance_counter": [vp, u32, vp],
-    "sl_moe_grouped_mma": [C.POINTER(MoeGroupedArgs), vp, vp],
+    "sl_moe_grouped_mma": [C.POINTER(MoeGroupedArgs), vp, vp, vp],
     "sl_linear_nvfp4_mma": [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp],
-    "sl_linear_smallT_bf16_tcgen05": [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp, vp],
+    "sl_linear_smallT_bf16_tcgen05": [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp, vp, i32, vp],
     "sl_grouped_gemm_bf16_tcgen05": [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, vp, vp, i32, vp, vp],
     "sl_build_group_tiles": [vp, vp, vp, i32, i32, i32, vp],
     "sl_nvfp4_dequant_bf16": [vp, vp, vp, vp, i32, i32, i32, i32, i32, vp],

@@ -256,6 +256,25 @@ def test_moe_small_and_dense(T):
     close(ops.dense_mlp(x, lw0), ref.dense_mlp(x, lw0), tol=2e-2, what="dense mlp")
 
 
+@pytest.mark.parametrize("T", [1, 8, 32])
+def test_moe_fused_router_glm5_routing(T):
+    """Router product + grouped sigmoid top-8 + plan in the first kernel of the layer (256 experts,
+    8 groups) against the stand-alone route kernel followed by the same expert kernels."""
+    cfg = mini_cfg(hidden_size=1024, moe_intermediate_size=256, n_routed_experts=256, num_experts_per_tok=8, n_group=8,
+                   topk_group=4)
+    ops, ref = cuda_ops(cfg), RefOps(cfg)
+    lw = random_layer(cfg, 1, 0, DEV, torch.bfloat16)
+    x = torch.randn(T, cfg.hidden_size, device=DEV, generator=torch.Generator(device=DEV).manual_seed(T)).to(torch.bfloat16)
+    fused = ops.moe_tp(x, lw)
+    ids, wts = ops.route(x, lw)
+    unfused = ops._moe_small(x, lw.experts, lw.shared, ids, wts)
+    close(fused, unfused, tol=2e-3, what="fused vs unfused router")
+    close(fused, ref.moe_tp(x, lw), tol=2e-2, what="fused router vs reference")
+    # the kernel must leave its ticket counter at zero for the next call
+    assert int(ops._zero_counter(x.device).item()) == 0
+    close(ops.moe_tp(x, lw), fused, tol=1e-6, what="second call")
+
+
 def test_moe_large_matches_reference():
     cfg = mini_cfg(hidden_size=1024, moe_intermediate_size=256)
     ops, ref = cuda_ops(cfg), RefOps(cfg)
