@@ -281,11 +281,10 @@ struct QPostParams {
     int n_slabs; long long slab_stride;
 };
 
-__global__ void q_post_kernel(QPostParams p) {
-    pdl_grid_sync();
+__device__ __forceinline__ void q_post_body(const QPostParams& p, int t, int hh) {
     __shared__ float v[512];
     __shared__ float scratch[33];
-    const int t = blockIdx.x, hh = blockIdx.y, tid = threadIdx.x;
+    const int tid = threadIdx.x;
     const int pos = p.positions[t];
     const int dqk = p.d_nope + p.rope_dim;
     if (hh < p.heads) {
@@ -317,6 +316,11 @@ __global__ void q_post_kernel(QPostParams p) {
     }
 }
 
+__global__ void q_post_kernel(QPostParams p) {
+    pdl_grid_sync();
+    q_post_body(p, blockIdx.x, blockIdx.y);
+}
+
 SL_API int sl_q_post(const QPostParams* p, int T, cudaStream_t s) {
     if (T == 0) return 0;
     dim3 grid(T, p->heads + p->idx_heads);
@@ -327,21 +331,27 @@ SL_API int sl_q_post(const QPostParams* p, int T, cudaStream_t s) {
 // ---------------------------------------------------------------------------------------------
 // Batched vector x matrix: y[t,h,n] = sum_k x[t,h,k] * M[h,k,n]   (absorb: K=Dn,N=R; v_expand: K=R,N=Dv)
 // x element (t,h,k) at x[t*xs_t + h*xs_h + k]; y bf16 [T, Hh, N] contiguous.
-// grid (Hh, N/64, ceil(T/TT)); block 256 = 8 warps.  A warp reads 4 matrix rows x 64 columns
+// grid (Hh, N/32, ceil(T/TT)); block 256 = 8 warps.  A warp reads 8 matrix rows x 32 columns
 // per load instruction (8 columns per lane, 16 bytes), four loads in flight; the partial sums
 // of a lane's row group meet by shuffle, those of the 8 warps in shared memory.
 template <int TT>
-__global__ void __launch_bounds__(256) bmv_kernel(bf16* __restrict__ y, const void* __restrict__ x, const bf16* __restrict__ M,
-                                                  int T, int Hh, int K, int N, int xs_t, int xs_h, int n_slabs,
-                                                  long long slab_stride) {
-    pdl_grid_sync();
-    extern __shared__ float xs[];            // [TT][K], then red[8][TT][64]
+__device__ __forceinline__ void bmv_body(bf16* __restrict__ y, const void* __restrict__ x, const bf16* __restrict__ M, int T,
+                                         int Hh, int K, int N, int xs_t, int xs_h, int n_slabs, long long slab_stride, int h,
+                                         int n0, int t0) {
+    extern __shared__ float xs[];            // [TT][K], then red[8][TT][32]
     float* red = xs + TT * K;
-    const int h = blockIdx.x, n0 = blockIdx.y * 64, t0 = blockIdx.z * TT;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int cg = lane & 3, kr = lane >> 2;
+    const int n = n0 + cg * 8;
+    const bf16* Mp = M + (size_t)h * K * N + n;
+    // the first weight loads do not depend on x: issue them before staging x
+    uint4 u[4];
+    int k = warp * 8 + kr;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) u[q] = (n < N && k + q * 64 < K) ? ldg_nc_16(Mp + (size_t)(k + q * 64) * N) : make_uint4(0, 0, 0, 0);
     for (int i = tid; i < TT * K; i += blockDim.x) {
-        const int tt = i / K, k = i % K;
-        xs[i] = (t0 + tt < T) ? load_act(x, n_slabs, slab_stride, (size_t)(t0 + tt) * xs_t + (size_t)h * xs_h + k) : 0.f;
+        const int tt = i / K, kk = i % K;
+        xs[i] = (t0 + tt < T) ? load_act(x, n_slabs, slab_stride, (size_t)(t0 + tt) * xs_t + (size_t)h * xs_h + kk) : 0.f;
     }
     __syncthreads();
     float acc[TT][8];
@@ -349,26 +359,24 @@ __global__ void __launch_bounds__(256) bmv_kernel(bf16* __restrict__ y, const vo
     for (int tt = 0; tt < TT; ++tt)
 #pragma unroll
         for (int c = 0; c < 8; ++c) acc[tt][c] = 0.f;
-    // a warp covers 4 matrix rows x 64 columns per load; 8 warps x 4 loads in flight = 128 rows a step
-    const int cg = lane & 7, kr = lane >> 3;
-    const int n = n0 + cg * 8;
     if (n < N) {
-        const bf16* Mp = M + (size_t)h * K * N + n;
-        for (int k = warp * 4 + kr; k < K; k += 128) {
-            uint4 u[4];
-#pragma unroll
-            for (int q = 0; q < 4; ++q) u[q] = (k + q * 32 < K) ? ldg_nc_16(Mp + (size_t)(k + q * 32) * N) : make_uint4(0, 0, 0, 0);
+        for (; k < K; k += 256) {
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
-                if (k + q * 32 < K) {
+                if (k + q * 64 < K) {
                     const float2 w0 = bf162_to_f2(u[q].x), w1 = bf162_to_f2(u[q].y), w2 = bf162_to_f2(u[q].z), w3 = bf162_to_f2(u[q].w);
 #pragma unroll
                     for (int tt = 0; tt < TT; ++tt) {
-                        const float xv = xs[tt * K + k + q * 32];
+                        const float xv = xs[tt * K + k + q * 64];
                         acc[tt][0] += xv * w0.x; acc[tt][1] += xv * w0.y; acc[tt][2] += xv * w1.x; acc[tt][3] += xv * w1.y;
                         acc[tt][4] += xv * w2.x; acc[tt][5] += xv * w2.y; acc[tt][6] += xv * w3.x; acc[tt][7] += xv * w3.y;
                     }
                 }
+            }
+            const int kn = k + 256;
+            if (kn < K) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) u[q] = (kn + q * 64 < K) ? ldg_nc_16(Mp + (size_t)(kn + q * 64) * N) : make_uint4(0, 0, 0, 0);
             }
         }
     }
@@ -377,27 +385,73 @@ __global__ void __launch_bounds__(256) bmv_kernel(bf16* __restrict__ y, const vo
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
             float v = acc[tt][c];
+            v += __shfl_xor_sync(0xffffffffu, v, 4);
             v += __shfl_xor_sync(0xffffffffu, v, 8);
             v += __shfl_xor_sync(0xffffffffu, v, 16);
-            if (kr == 0) red[(warp * TT + tt) * 64 + cg * 8 + c] = v;
+            if (kr == 0) red[(warp * TT + tt) * 32 + cg * 8 + c] = v;
         }
     __syncthreads();
-    for (int i = tid; i < TT * 64; i += blockDim.x) {
-        const int tt = i / 64, c = i % 64;
+    for (int i = tid; i < TT * 32; i += blockDim.x) {
+        const int tt = i / 32, c = i % 32;
         if (t0 + tt < T && n0 + c < N) {
             float v = 0.f;
 #pragma unroll
-            for (int w = 0; w < 8; ++w) v += red[(w * TT + tt) * 64 + c];
+            for (int w = 0; w < 8; ++w) v += red[(w * TT + tt) * 32 + c];
             y[((size_t)(t0 + tt) * Hh + h) * N + n0 + c] = __float2bfloat16(v);
         }
     }
 }
 
 template <int TT>
+__global__ void __launch_bounds__(256) bmv_kernel(bf16* __restrict__ y, const void* __restrict__ x, const bf16* __restrict__ M,
+                                                  int T, int Hh, int K, int N, int xs_t, int xs_h, int n_slabs,
+                                                  long long slab_stride) {
+    pdl_grid_sync();
+    bmv_body<TT>(y, x, M, T, Hh, K, N, xs_t, xs_h, n_slabs, slab_stride, blockIdx.x, blockIdx.y * 32, blockIdx.z * TT);
+}
+
+// q_post and the absorb product (q_nope x W_kn) read the same projection and do not depend on each other: one
+// launch, the first `bmv_blocks` blocks do the product, the rest the per-head rotary / quantisation work.
+template <int TT>
+__global__ void __launch_bounds__(256) q_post_absorb_kernel(QPostParams p, bf16* __restrict__ q_abs, const bf16* __restrict__ w_kn,
+                                                            int T, int K, int N, int bmv_blocks, int col_chunks) {
+    pdl_grid_sync();
+    const int b = blockIdx.x;
+    if (b < bmv_blocks) {
+        const int h = b % p.heads, rest = b / p.heads, nc = rest % col_chunks, tz = rest / col_chunks;
+        bmv_body<TT>(q_abs, p.qb, w_kn, T, p.heads, K, N, p.ld, p.d_nope + p.rope_dim, p.n_slabs, p.slab_stride, h, nc * 32, tz * TT);
+    } else {
+        const int i = b - bmv_blocks, per_t = p.heads + p.idx_heads;
+        q_post_body(p, i / per_t, i % per_t);
+    }
+}
+
+template <int TT>
+static int launch_q_post_absorb(const QPostParams* p, void* q_abs, const void* w_kn, int T, int K, int N, cudaStream_t s) {
+    const int col_chunks = (N + 31) / 32, tz = (T + TT - 1) / TT;
+    const int bmv_blocks = p->heads * col_chunks * tz, post_blocks = T * (p->heads + p->idx_heads);
+    const size_t smem = (size_t)(TT * K + 8 * TT * 32) * sizeof(float);
+    auto kern = q_post_absorb_kernel<TT>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    sl_launch(kern, bmv_blocks + post_blocks, 256, smem, s, *p, (bf16*)q_abs, (const bf16*)w_kn, T, K, N, bmv_blocks, col_chunks);
+    return SL_LAUNCH_CHECK();
+}
+
+// q_post plus q_abs[t, h, :] = q_nope[t, h, :] x w_kn[h] (K = d_nope, N = kv_lora) in one launch.
+SL_API int sl_q_post_absorb(const QPostParams* p, void* q_abs, const void* w_kn, int T, int N, cudaStream_t s) {
+    if (T == 0) return 0;
+    if (N % 8 != 0 || p->idx_dim > 512 || p->rope_dim > 512) return -1;
+    const int K = p->d_nope;
+    if (T == 1) return launch_q_post_absorb<1>(p, q_abs, w_kn, T, K, N, s);
+    if (T == 2) return launch_q_post_absorb<2>(p, q_abs, w_kn, T, K, N, s);
+    return launch_q_post_absorb<4>(p, q_abs, w_kn, T, K, N, s);
+}
+
+template <int TT>
 static int launch_bmv(void* y, const void* x, const void* M, int T, int Hh, int K, int N, int xs_t, int xs_h, int n_slabs,
                       long long slab_stride, cudaStream_t s) {
-    dim3 grid(Hh, (N + 63) / 64, (T + TT - 1) / TT);
-    const size_t smem = (size_t)(TT * K + 8 * TT * 64) * sizeof(float);
+    dim3 grid(Hh, (N + 31) / 32, (T + TT - 1) / TT);
+    const size_t smem = (size_t)(TT * K + 8 * TT * 32) * sizeof(float);
     auto kern = bmv_kernel<TT>;
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     sl_launch(kern, grid, 256, smem, s, (bf16*)y, x, (const bf16*)M, T, Hh, K, N, xs_t, xs_h, n_slabs, slab_stride);
@@ -411,8 +465,7 @@ SL_API int sl_bmv(void* y, const void* x, const void* M, int T, int Hh, int K, i
     if (N % 8 != 0) return -1;
     if (T == 1) return launch_bmv<1>(y, x, M, T, Hh, K, N, xs_t, xs_h, n_slabs, slab_stride, s);
     if (T == 2) return launch_bmv<2>(y, x, M, T, Hh, K, N, xs_t, xs_h, n_slabs, slab_stride, s);
-    if (T <= 4) return launch_bmv<4>(y, x, M, T, Hh, K, N, xs_t, xs_h, n_slabs, slab_stride, s);
-    return launch_bmv<8>(y, x, M, T, Hh, K, N, xs_t, xs_h, n_slabs, slab_stride, s);
+    return launch_bmv<4>(y, x, M, T, Hh, K, N, xs_t, xs_h, n_slabs, slab_stride, s);
 }
 
 // ---------------------------------------------------------------------------------------------

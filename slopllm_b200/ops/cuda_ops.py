@@ -180,10 +180,8 @@ class CudaOps:
             rope_interleave=int(c.rope_interleave), idx_rope_interleave=int(c.indexer_rope_interleave),
             positions=st.positions.data_ptr(), idx_w=N.ptr(idx_w), q_pe_out=q_pe.data_ptr(), q8_out=N.ptr(q8),
             w_eff_out=N.ptr(w_eff))
-        N.call("sl_q_post", C.byref(p), T, N.stream())
         q_abs = torch.empty(T, hl, c.kv_lora_rank, dtype=torch.bfloat16, device=dev)
-        N.call("sl_bmv", q_abs.data_ptr(), qb.data_ptr(), lw.w_kn.data_ptr(), T, hl, c.qk_nope_head_dim, c.kv_lora_rank,
-               qb.stride(0), c.qk_head_dim, n_slabs, slab_stride, N.stream())
+        N.call("sl_q_post_absorb", C.byref(p), q_abs.data_ptr(), lw.w_kn.data_ptr(), T, c.kv_lora_rank, N.stream())
         return q_abs, q_pe, q8, w_eff
 
     def indexer_topk(self, q8, w_eff, layer_cache, st):

@@ -147,6 +147,7 @@ _SIGS = {
     "sl_add_rmsnorm": [vp, vp, vp, vp, vp, i32, i32, f32, i32, vp],
     "sl_attn_pre": [C.POINTER(AttnPreParams), i32, vp],
     "sl_q_post": [C.POINTER(QPostParams), i32, vp],
+    "sl_q_post_absorb": [C.POINTER(QPostParams), vp, vp, i32, i32, vp],
     "sl_bmv": [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i64, vp],
     "sl_smallT_splits": [i32, i32, i32],
     "sl_silu_mul": [vp, vp, i32, i32, vp],
