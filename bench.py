@@ -243,7 +243,9 @@ def main():
                 details[f"mtp{args.mtp}_{name}"] = {
                     "steps_s": 1e3 / ms, "ms_per_step": ms, "tok_s": acc_tokens / (ms * K / 1e3),
                     "accept_len": acc_tokens / (K * len(grp)),
-                    "vs_ref_steps_s": (1e3 / ms) / ref if L == 78 else None,
+                    # the reference's figure is tok/s divided by the accept length, i.e. sequence-steps per second
+                    "seq_steps_s": len(grp) * 1e3 / ms,
+                    "vs_ref_steps_s": (len(grp) * 1e3 / ms) / ref if L == 78 else None,
                     "note": "random-init weights: drafts are almost never accepted, so tok/s ~= steps/s * batch"}
     from slopllm_b200.ops import tcgen05
     tcgen05.check_errors(dev)

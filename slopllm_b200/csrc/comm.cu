@@ -185,7 +185,7 @@ __global__ void cp_merge_push_kernel(CpPushCtx c, const float* __restrict__ o, c
             *c.block_counter = 0;
             __threadfence_system();
             const uint32_t e = *c.epoch + 1u;
-            for (int p = 0; p < c.world; ++p) st_release_sys_u32(c.flags[p] + c.rank, e);
+            for (int p = 0; p < c.world; ++p) st_relaxed_sys_u32(c.flags[p] + c.rank, e);
         }
     }
 }
@@ -238,7 +238,7 @@ __global__ void gather_push_kernel(GatherPushCtx c, const uint4* __restrict__ sr
             *c.block_counter = 0;
             __threadfence_system();
             const uint32_t e = *c.epoch + 1u;
-            for (int p = 0; p < c.world; ++p) st_release_sys_u32(c.flags[p] + c.rank, e);
+            for (int p = 0; p < c.world; ++p) st_relaxed_sys_u32(c.flags[p] + c.rank, e);
         }
     }
 }

@@ -37,7 +37,7 @@ __device__ __forceinline__ void push_finish(const PushCtx& c, unsigned total_blo
             *c.block_counter = 0;
             __threadfence_system();
             const uint32_t e = *c.epoch + 1u;
-            for (int p = 0; p < c.world; ++p) st_release_sys_u32(c.flags[p] + c.rank, e);
+            for (int p = 0; p < c.world; ++p) st_relaxed_sys_u32(c.flags[p] + c.rank, e);
         }
     }
 }
