@@ -52,6 +52,7 @@ class PagedKVCache:
         self.copy_page = copy_page or (lambda src, dst: None)     # device copy of one page in every layer
         self.sequences: Dict[int, Sequence] = {}
         self.staged: Dict[int, Sequence] = {}                     # finished sequences kept for prefix reuse
+        self.prefix_sharing = True                                # off for models whose state is not in the pages
         self._next_id = 0
 
     # ---- pool ----------------------------------------------------------------------------------------
@@ -128,8 +129,11 @@ class PagedKVCache:
         keep = self.pages_for(s.reported)
         self._release(s.pages[keep:])
         del s.pages[keep:]
-        if s.pages:
+        if s.pages and self.prefix_sharing:
             self.staged[s.seq_id] = s
+        elif s.pages:
+            self._release(s.pages)
+            s.pages = []
 
     # ---- prefix sharing ----------------------------------------------------------------------------------------
     def match_prefix(self, prompt: Seq[int]) -> Tuple[Optional[Sequence], int, bool]:
@@ -157,7 +161,7 @@ class PagedKVCache:
     def start_request(self, prompt: Seq[int]) -> Tuple[Sequence, int]:
         """Create (or resume) the sequence for a prompt.  Returns (sequence, cached_tokens):
         KV of the first `cached_tokens` tokens is already present."""
-        donor, shared, resume = self.match_prefix(prompt)
+        donor, shared, resume = self.match_prefix(prompt) if self.prefix_sharing else (None, 0, False)
         if donor is not None and resume:
             self.staged.pop(donor.seq_id)
             self.sequences[donor.seq_id] = donor

@@ -150,6 +150,15 @@ _SIGS = {
     "sl_q_post_absorb": [C.POINTER(QPostParams), vp, vp, i32, i32, vp],
     "sl_bmv": [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i64, vp],
     "sl_smallT_splits": [i32, i32, i32],
+    "sl_qk_norm_rope_cache": [vp, i32, vp],
+    "sl_paged_attn_prefill": [vp, i32, i32, vp],
+    "sl_paged_attn_decode": [vp, i32, vp],
+    "sl_delta_scan": [vp, i32, vp],
+    "sl_causal_conv1d": [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp],
+    "sl_rmsnorm_gated": [vp, vp, vp, vp, i32, i32, f32, i32, vp],
+    "sl_mhc_pre": [vp, vp, vp, vp, vp, i32, i32, i32, i32, vp],
+    "sl_mhc_post": [vp, vp, vp, vp, i32, i32, i32, vp],
+    "sl_mhc_streams": [vp, vp, i32, i32, i32, vp],
     "sl_silu_mul": [vp, vp, i32, i32, vp],
     "sl_route_topk": [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, f32, vp],
     "sl_topk_to_slots": [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp],

@@ -57,7 +57,10 @@ class Engine:
         self.ctx: ParallelContext = model.ctx
         self.device = self.ctx.device
         self.kv = PagedKVCache(num_pages, self.ctx.cp_world, copy_page=self._copy_page)
-        self.cache = KVCacheTensors.allocate(cfg, num_pages, self.device, len(model.w.layers))
+        self.kv.prefix_sharing = getattr(model, "supports_prefix_sharing", True)
+        # model families bring their own cache layout (dense K/V, recurrent state); the flagship uses packed MLA rows
+        self.cache = (model.allocate_cache(num_pages) if hasattr(model, "allocate_cache")
+                      else KVCacheTensors.allocate(cfg, num_pages, self.device, len(model.w.layers)))
         self.max_batch = max_batch
         self.pt_width = -(-max_seq_len // (PAGE_SIZE * self.ctx.cp_world)) + 1
         self.graphs = CaptureManager(enabled=cuda_graph and self.device.type == "cuda")
@@ -70,6 +73,9 @@ class Engine:
 
     # ---- pages ---------------------------------------------------------------------------------------
     def _copy_page(self, src: int, dst: int) -> None:
+        if hasattr(self.cache, "copy_page"):
+            self.cache.copy_page(src, dst)
+            return
         a, b = slice(src * PAGE_SIZE, (src + 1) * PAGE_SIZE), slice(dst * PAGE_SIZE, (dst + 1) * PAGE_SIZE)
         for lc in self.cache.layers:
             lc.kv[b] = lc.kv[a]
@@ -118,8 +124,9 @@ class Engine:
                 self.kv.append_tokens(s, ids)
                 positions = list(range(start, start + n))
                 st = self._eager_state(ids, positions, [0] * n, [s], max_kv_len=start + n)
+                self._prepare(st, [s])
                 hidden = self.model.forward_hidden(st, self.cache)
-                if self.mtp and self.cfg.num_nextn_predict_layers:
+                if self.mtp and getattr(self.cfg, "num_nextn_predict_layers", 0):
                     self._prefill_mtp(st, hidden, prompt, start, n)
                 self.kv.report_tokens(s)
                 last_hidden = hidden[-1:]
@@ -145,6 +152,16 @@ class Engine:
                         batch_idx=st.batch_idx, page_table=st.page_table, cp_world=st.cp_world, cp_rank=st.cp_rank,
                         max_kv_len=st.max_kv_len)
         self.model.forward_mtp(st2, self.cache, hidden)
+
+    def _prepare(self, st: StepState, seqs) -> None:
+        """Per-step host work of the model that must stay outside a graph capture (recurrent-state slots)."""
+        if hasattr(self.model, "prepare_step"):
+            self.model.prepare_step(st, seqs)
+
+    def release(self, s: Sequence) -> None:
+        """Tell the model that a sequence is gone (frees per-sequence state outside the page pool)."""
+        if hasattr(self.model, "release_sequence"):
+            self.model.release_sequence(s.seq_id)
 
     def _eager_state(self, ids, positions, batch_idx, seqs, max_kv_len, logits_idx=None) -> StepState:
         dev = self.device
@@ -172,6 +189,7 @@ class Engine:
         self._upload(buf, list(last_tokens), positions, list(range(B)), seqs)
         bucket = R.padded_kv_len(max(positions) + 1)
         st = self._state(buf, bucket)
+        self._prepare(st, seqs)
 
         def run():
             hidden = self.model.forward_hidden(st, self.cache)

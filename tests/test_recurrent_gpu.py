@@ -1,0 +1,153 @@
+"""sm_100a kernels of the dense / hybrid families against their fp32 definitions: the same op
+wrapper is run on CUDA tensors (native kernel) and on CPU copies (plain PyTorch)."""
+import pytest
+import torch
+
+from slopllm_b200.ops import dense as D
+from slopllm_b200.ops import recurrent as RC
+
+pytestmark = pytest.mark.gpu
+
+
+def rel_err(a, b):
+    a, b = a.to(torch.float32).cpu(), b.to(torch.float32).cpu()
+    return ((a - b).abs().max() / b.abs().max().clamp(min=1e-6)).item()
+
+
+def gen(seed):
+    return torch.Generator().manual_seed(seed)
+
+
+@pytest.mark.parametrize("dk,dv,h", [(128, 128, 4), (64, 64, 2)])
+@pytest.mark.parametrize("lens", [[1, 1, 1], [37, 5, 64]])
+def test_gdn_scan(dk, dv, h, lens):
+    g = gen(1)
+    T, B = sum(lens), len(lens)
+    qkv = torch.randn(T, h * (2 * dk + dv), generator=g).to(torch.bfloat16)
+    a = torch.randn(T, h, generator=g).to(torch.bfloat16)
+    b = torch.randn(T, h, generator=g).to(torch.bfloat16)
+    A_log, dt_bias = torch.randn(h, generator=g) * 0.5, torch.randn(h, generator=g) * 0.1
+    state = torch.randn(B + 2, h, dk, dv, generator=g) * 0.1
+    ind = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32)
+    sidx = torch.tensor([2, 0, 3][:B], dtype=torch.int32)
+    s_cpu, s_gpu = state.clone(), state.clone().cuda()
+    want = RC.gdn_scan(qkv, a, b, A_log, dt_bias, s_cpu, ind, sidx, h, dk, dv)
+    got = RC.gdn_scan(qkv.cuda(), a.cuda(), b.cuda(), A_log.cuda(), dt_bias.cuda(), s_gpu, ind.cuda(), sidx.cuda(), h, dk, dv)
+    assert rel_err(got, want) < 2e-2
+    assert rel_err(s_gpu, s_cpu) < 1e-3
+
+
+def test_kda_scan():
+    g = gen(2)
+    h, dk, dv, lens = 2, 128, 128, [9, 20]
+    T = sum(lens)
+    qkv = (torch.randn(T, h * (2 * dk + dv), generator=g) * 0.3).to(torch.bfloat16)
+    gl = (-torch.rand(T, h, dk, generator=g)).to(torch.bfloat16)
+    b = torch.randn(T, h, generator=g).to(torch.bfloat16)
+    state = torch.zeros(2, h, dk, dv)
+    ind = torch.tensor([0, 9, 29], dtype=torch.int32)
+    sidx = torch.tensor([1, 0], dtype=torch.int32)
+    s_cpu, s_gpu = state.clone(), state.clone().cuda()
+    want = RC.kda_scan(qkv, gl, b, s_cpu, ind, sidx, h, dk, dv)
+    got = RC.kda_scan(qkv.cuda(), gl.cuda(), b.cuda(), s_gpu, ind.cuda(), sidx.cuda(), h, dk, dv)
+    assert rel_err(got, want) < 2e-2
+    assert rel_err(s_gpu, s_cpu) < 2e-3
+
+
+def test_causal_conv1d_prefill_then_update():
+    g = gen(3)
+    C_, Kw = 320, 4
+    w = (torch.randn(C_, Kw, generator=g) * 0.5).to(torch.bfloat16)
+    x1 = torch.randn(45, C_, generator=g).to(torch.bfloat16)
+    x2 = torch.randn(2, C_, generator=g).to(torch.bfloat16)
+    st_c, st_g = torch.zeros(3, C_, Kw - 1), torch.zeros(3, C_, Kw - 1).cuda()
+    ind1, sid = torch.tensor([0, 30, 45], dtype=torch.int32), torch.tensor([2, 1], dtype=torch.int32)
+    ind2 = torch.tensor([0, 1, 2], dtype=torch.int32)
+    for x, ind in ((x1, ind1), (x2, ind2)):
+        want = RC.causal_conv1d(x, w, None, st_c, ind, sid)
+        got = RC.causal_conv1d(x.cuda(), w.cuda(), None, st_g, ind.cuda(), sid.cuda())
+        assert rel_err(got, want) < 1e-2
+    assert rel_err(st_g, st_c) < 1e-6
+
+
+@pytest.mark.parametrize("sig", [False, True])
+def test_rmsnorm_gated(sig):
+    g = gen(4)
+    x = torch.randn(50, 128, generator=g).to(torch.bfloat16)
+    gate = torch.randn(50, 128, generator=g).to(torch.bfloat16)
+    w = (1 + 0.1 * torch.randn(128, generator=g)).to(torch.bfloat16)
+    assert rel_err(RC.rmsnorm_gated(x.cuda(), gate.cuda(), w.cuda(), 1e-6, sig), RC.rmsnorm_gated(x, gate, w, 1e-6, sig)) < 1e-2
+
+
+def test_mhc():
+    g = gen(5)
+    T, n, H = 6, 4, 512
+    streams = torch.randn(T, n, H, generator=g)
+    mix, cw, ew = torch.randn(T, n, n, generator=g), torch.randn(T, n, generator=g), torch.randn(T, n, generator=g)
+    mixed_c, x_c = RC.mhc_pre(streams, mix, cw)
+    mixed_g, x_g = RC.mhc_pre(streams.cuda(), mix.cuda(), cw.cuda())
+    assert rel_err(mixed_g, mixed_c) < 1e-4 and rel_err(x_g, x_c) < 1e-2
+    y = torch.randn(T, H, generator=g).to(torch.bfloat16)
+    assert rel_err(RC.mhc_post(mixed_c.cuda(), y.cuda(), ew.cuda()), RC.mhc_post(mixed_c, y, ew)) < 1e-5
+    assert rel_err(RC.mhc_streams_mean(streams.cuda()), RC.mhc_streams_mean(streams)) < 1e-2
+
+
+def _paged_setup(g, B, lens, n_kv, hd, page=64):
+    pages_per = [(-(-l // page)) for l in lens]
+    total = sum(pages_per) + 1
+    perm = torch.randperm(total - 1, generator=g) + 1
+    pt = torch.zeros(B, max(pages_per), dtype=torch.int32)
+    o = 0
+    for b, n in enumerate(pages_per):
+        pt[b, :n] = perm[o:o + n].to(torch.int32)
+        o += n
+    k_cache = torch.randn(total * page, n_kv, hd, generator=g).to(torch.bfloat16)
+    v_cache = torch.randn(total * page, n_kv, hd, generator=g).to(torch.bfloat16)
+    return pt, k_cache, v_cache
+
+
+@pytest.mark.parametrize("hd,heads,n_kv", [(128, 8, 2), (64, 4, 4), (128, 16, 1)])
+def test_paged_attention_decode_and_prefill(hd, heads, n_kv):
+    g = gen(6)
+    lens = [300, 77, 1025]
+    B = len(lens)
+    pt, kc, vc = _paged_setup(g, B, lens, n_kv, hd)
+    scale = hd ** -0.5
+    # decode: one query per sequence at its last position
+    q = torch.randn(B, heads, hd, generator=g).to(torch.bfloat16)
+    pos = torch.tensor([l - 1 for l in lens], dtype=torch.int32)
+    bi = torch.arange(B, dtype=torch.int32)
+    want = D.paged_attention(q, kc, vc, pos, bi, pt, 64, scale)
+    got = D.paged_attention(q.cuda(), kc.cuda(), vc.cuda(), pos.cuda(), bi.cuda(), pt.cuda(), 64, scale, max_kv_len=max(lens))
+    assert rel_err(got, want) < 2e-2
+    # prefill: the last 70 / 77 / 130 positions of each sequence as one batch of query ranges
+    qlens = [70, 77, 130]
+    T = sum(qlens)
+    q = torch.randn(T, heads, hd, generator=g).to(torch.bfloat16)
+    pos = torch.cat([torch.arange(l - n, l) for l, n in zip(lens, qlens)]).to(torch.int32)
+    bi = torch.cat([torch.full((n,), b) for b, n in enumerate(qlens)]).to(torch.int32)
+    ind = torch.tensor([0, 70, 147, 277], dtype=torch.int32)
+    want = D.paged_attention(q, kc, vc, pos, bi, pt, 64, scale)
+    got = D.paged_attention(q.cuda(), kc.cuda(), vc.cuda(), pos.cuda(), bi.cuda(), pt.cuda(), 64, scale, qo_indptr=ind.cuda(),
+                            max_q=max(qlens))
+    assert rel_err(got, want) < 2e-2
+
+
+def test_qk_norm_rope_cache_write():
+    g = gen(7)
+    T, heads, n_kv, hd, rope = 9, 4, 2, 128, 64
+    q = torch.randn(T, heads * hd * 2, generator=g).to(torch.bfloat16)        # gate packed after each head's q
+    k = torch.randn(T, n_kv * hd, generator=g).to(torch.bfloat16)
+    v = torch.randn(T, n_kv * hd, generator=g).to(torch.bfloat16)
+    qn = (1 + 0.1 * torch.randn(hd, generator=g)).to(torch.bfloat16)
+    kn = (1 + 0.1 * torch.randn(hd, generator=g)).to(torch.bfloat16)
+    pos = torch.arange(60, 60 + T, dtype=torch.int32)
+    bi = torch.zeros(T, dtype=torch.int32)
+    pt = torch.tensor([[3, 1]], dtype=torch.int32)
+    kc_c, vc_c = torch.zeros(4 * 64, n_kv, hd, dtype=torch.bfloat16), torch.zeros(4 * 64, n_kv, hd, dtype=torch.bfloat16)
+    kc_g, vc_g = kc_c.clone().cuda(), vc_c.clone().cuda()
+    want = D.qk_norm_rope_cache(q, k, v, qn, kn, pos, bi, pt, 64, kc_c, vc_c, heads, n_kv, hd, rope, 1e6, 1e-6, q_stride=2 * hd)
+    got = D.qk_norm_rope_cache(q.cuda(), k.cuda(), v.cuda(), qn.cuda(), kn.cuda(), pos.cuda(), bi.cuda(), pt.cuda(), 64, kc_g, vc_g,
+                               heads, n_kv, hd, rope, 1e6, 1e-6, q_stride=2 * hd)
+    assert rel_err(got, want) < 1e-2
+    assert rel_err(kc_g, kc_c) < 1e-2 and rel_err(vc_g, vc_c) < 1e-6
