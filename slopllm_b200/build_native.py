@@ -82,6 +82,11 @@ def build_all(force: bool = False, verbose: bool = False) -> None:
     build_kernels(force, verbose)
 
 
-if __name__ == "__main__":
+def main() -> int:
     build_all(force="--force" in sys.argv, verbose="-v" in sys.argv)
     print("built", KERNELS_SO, RUNTIME_SO)
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

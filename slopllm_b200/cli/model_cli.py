@@ -1,0 +1,135 @@
+"""Shared command-line handling of the entry points: which model, which GPUs, which
+parallelism; builds the engine, the sampler, the scheduler and the tokenizer.
+
+Flags follow the reference (`src/model_cli.ts:1-154`, `src/openai-server.ts:51-103`):
+`--model --gpus --arena --cp --mtp --batch-size --chunk-size --max-pages --max-host-pages ...`.
+One process drives one GPU: start N ranks with
+`python -m torch.distributed.run --nproc-per-node N --master-addr 127.0.0.1 -m slopllm_b200.cli.serve ...`;
+`--gpus` then only states the expected world size.
+"""
+from __future__ import annotations
+
+import argparse
+import os
+from dataclasses import dataclass
+from typing import List, Optional
+
+import torch
+
+from ..config import EngineConfig, GlmMoeDsaConfig, SamplingParams
+from ..parallel.dist import ParallelContext, init_from_env
+
+
+def add_model_args(ap: argparse.ArgumentParser) -> None:
+    ap.add_argument("--model", default="", help="checkpoint directory or Hugging Face hub id (local cache only)")
+    ap.add_argument("--random-init", default="", metavar="SPEC",
+                    help="no checkpoint: random weights of 'tiny', 'glm5[:layers]', 'qwen3-tiny' or 'qwen35-tiny'")
+    ap.add_argument("--gpus", default="", help="comma-separated device list; its length must equal the number of ranks")
+    ap.add_argument("--arena", type=float, default=92.0, help="GiB of device memory the weights + KV cache may take per GPU")
+    ap.add_argument("--cp", action="store_true", help="context parallelism (KV tokens interleaved across ranks)")
+    ap.add_argument("--ep", action="store_true", help="expert parallelism for the routed experts")
+    ap.add_argument("--mtp", type=int, nargs="?", const=3, default=0, help="speculative drafts per step (bare flag: 3)")
+    ap.add_argument("--batch-size", type=int, default=8)
+    ap.add_argument("--chunk-size", type=int, default=8192)
+    ap.add_argument("--max-pages", type=int, default=0, help="KV pages of 64 tokens (0: batch-size * ceil(chunk-size / 64))")
+    ap.add_argument("--max-host-pages", type=int, default=0, help="pinned-host prefix tier size in pages (0: off)")
+    ap.add_argument("--max-model-len", type=int, default=65536)
+    ap.add_argument("--no-cuda-graph", action="store_true")
+    ap.add_argument("--no-fused-collectives", action="store_true", help="NCCL collectives instead of the in-kernel NVLink ones")
+    ap.add_argument("--cpu", action="store_true", help="run on the CPU reference ops (plumbing / debugging)")
+    ap.add_argument("--seed", type=int, default=0)
+
+
+@dataclass
+class Runtime:
+    cfg: object
+    model: object
+    engine: object
+    scheduler: object
+    tokenizer: object
+    ctx: ParallelContext
+    engine_cfg: EngineConfig
+    model_type: str
+
+
+def _context(args) -> ParallelContext:
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    gpus: List[int] = [int(x) for x in args.gpus.split(",") if x != ""] if args.gpus else list(range(world))
+    if len(gpus) != world:
+        raise SystemExit(f"--gpus names {len(gpus)} devices but the job has {world} rank(s): start one rank per GPU with torchrun")
+    if world > 1:
+        return init_from_env("gloo" if args.cpu else None, cp=args.cp, ep=args.ep)
+    dev = torch.device("cpu") if args.cpu or not torch.cuda.is_available() else torch.device("cuda", gpus[0] if gpus else 0)
+    if dev.type == "cuda":
+        torch.cuda.set_device(dev)
+    return ParallelContext(device=dev, cp=args.cp, ep=args.ep)
+
+
+def _random_model(spec: str, ctx: ParallelContext, mtp: int):
+    from ..parallel.fused import make_comm
+    dtype = torch.bfloat16 if ctx.device.type == "cuda" else torch.float32
+    tp_world = 1 if ctx.cp else ctx.world
+    tp_rank = ctx.rank if tp_world > 1 else 0
+    if spec.startswith("qwen"):
+        from ..models.dense import DenseConfig, DenseModel, random_dense_model
+        cfg = DenseConfig.tiny(hybrid=spec.startswith("qwen35"))
+        w, _ = random_dense_model(cfg, 0, ctx.device, dtype, tp_rank, tp_world)
+        return cfg, DenseModel(cfg, w, ctx), cfg.model_type
+    from ..models.glm_moe_dsa import GlmMoeDsaModel
+    from ..models.weights import random_model
+    if spec.startswith("glm5"):
+        layers = int(spec.split(":")[1]) if ":" in spec else 78
+        cfg = GlmMoeDsaConfig.glm5(num_layers=layers)
+        exact = False
+    else:
+        cfg, exact = GlmMoeDsaConfig.tiny(), True
+    w = random_model(cfg, 0, ctx.device, dtype, tp_rank, tp_world, ep=ctx.ep, exact=exact, with_mtp=mtp > 0)
+    return cfg, GlmMoeDsaModel(cfg, w, ctx, comm=make_comm(ctx, cfg)), "glm_moe_dsa"
+
+
+def build_runtime(args, with_scheduler: bool = True) -> Runtime:
+    from ..models.registry import inspect_model
+    from ..runtime.engine import Engine
+    from ..sampling.workspace import SamplingWorkspace
+    from ..scheduler.replicated import make_channel
+    from ..scheduler.scheduler import GenerationScheduler, HostTier
+    from ..server.tokenizer import load_tokenizer
+    from ..utils.model_path import resolve_model_path
+
+    ctx = _context(args)
+    if args.no_fused_collectives:
+        os.environ["SLOPLLM_B200_FUSED"] = "0"
+    model_dir: Optional[str] = None
+    if args.random_init:
+        cfg, model, model_type = _random_model(args.random_init, ctx, args.mtp)
+    else:
+        if not args.model:
+            raise SystemExit("give --model DIR|HUB_ID or --random-init SPEC")
+        model_dir = resolve_model_path(args.model)
+        model_type, reg, _ = inspect_model(model_dir, cp=args.cp, mtp=args.mtp)
+        cfg, model = reg.load(model_dir, ctx, args.mtp)
+    ecfg = EngineConfig(model=args.model or args.random_init, gpus=list(range(ctx.world)), arena_gb=args.arena, cp=args.cp, ep=args.ep,
+                        mtp=args.mtp, batch_size=args.batch_size, chunk_size=args.chunk_size, max_pages=args.max_pages,
+                        max_host_pages=args.max_host_pages, cuda_graph=not args.no_cuda_graph,
+                        host=getattr(args, "host", "127.0.0.1"), port=getattr(args, "port", 8000),
+                        api_key=getattr(args, "api_key", None), admin_api_key=getattr(args, "admin_api_key", None),
+                        fused_collectives=not args.no_fused_collectives)
+    vocab = cfg.vocab_size
+    sampler = SamplingWorkspace(ctx.device, vocab, seed=args.seed)
+    engine = Engine(cfg, model, num_pages=ecfg.max_pages, max_batch=ecfg.batch_size, max_seq_len=args.max_model_len,
+                    cuda_graph=ecfg.cuda_graph, mtp=args.mtp, sampler=sampler)
+    sched = None
+    if with_scheduler:
+        eos = list(getattr(cfg, "eos_token_ids", None) or getattr(cfg, "eos_token_id", None) or [])
+        tier = None
+        if ecfg.max_host_pages > 0 and hasattr(engine, "read_page"):
+            tier = HostTier(ecfg.max_host_pages, engine.kv.tokens_per_page, engine.read_page, engine.write_page)
+        sched = GenerationScheduler(engine, max_batch=ecfg.batch_size, chunk_size=ecfg.chunk_size, eos_token_ids=eos, host_tier=tier,
+                                    decode_latency_ms=ecfg.decode_latency_ms, replica_channel=make_channel(ctx))
+    tok = load_tokenizer(model_dir, vocab)
+    return Runtime(cfg, model, engine, sched, tok, ctx, ecfg, model_type)
+
+
+def default_sampling(args) -> SamplingParams:
+    return SamplingParams(temperature=getattr(args, "temperature", 0.6), top_p=getattr(args, "top_p", 0.95),
+                          top_k=getattr(args, "top_k", 20))

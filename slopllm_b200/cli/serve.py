@@ -1,0 +1,69 @@
+"""OpenAI-compatible server entry point.
+
+    python -m slopllm_b200.cli.serve --model DIR --mtp --batch-size 8 --port 8000
+    python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 -m slopllm_b200.cli.serve --model DIR --gpus 0,1,2,3,4,5,6,7
+
+Rank 0 listens; the other ranks follow its scheduler step by step.  Reference:
+`src/openai-server.ts:51-103` (flags), `:476-539` (warm-up), `src/main.ts`.
+"""
+from __future__ import annotations
+
+import argparse
+import asyncio
+import sys
+import time
+
+from .model_cli import add_model_args, build_runtime
+
+
+def parse_args(argv=None):
+    ap = argparse.ArgumentParser(prog="slopllm_b200.cli.serve", description=__doc__.split("\n")[0])
+    add_model_args(ap)
+    ap.add_argument("--host", default="127.0.0.1")
+    ap.add_argument("--port", type=int, default=8000)
+    ap.add_argument("--api-key", default=None)
+    ap.add_argument("--admin-api-key", default=None)
+    ap.add_argument("--served-model-name", default="")
+    ap.add_argument("--no-warmup", action="store_true")
+    return ap.parse_args(argv)
+
+
+def warm_up(rt, tokens: int = 32) -> float:
+    """A short greedy request through the scheduler so that the first user request finds the decode graphs captured."""
+    import threading
+    from ..config import SamplingParams
+    from ..scheduler.scheduler import GenerationRequest
+    done = threading.Event()
+    req = GenerationRequest(id="warmup", input_ids=[1] * 16, max_tokens=tokens, sampling=SamplingParams(temperature=0.0),
+                            on_finish=lambda r: done.set())
+    t0 = time.time()
+    rt.scheduler.submit(req)
+    done.wait(timeout=600)
+    rt.scheduler.flush_gpu_cache().done.wait(timeout=60)
+    return time.time() - t0
+
+
+def main(argv=None) -> int:
+    args = parse_args(argv)
+    rt = build_runtime(args)
+    rt.scheduler.start()
+    if rt.ctx.rank != 0:
+        rt.scheduler._thread.join()              # followers mirror rank 0 until it broadcasts stop
+        return 0
+    from ..server.openai import OpenAIServer, serve
+    if not args.no_warmup:
+        print(f"warm-up took {warm_up(rt):.1f} s", file=sys.stderr)
+    name = args.served_model_name or (args.model.rstrip("/").split("/")[-1] if args.model else args.random_init)
+    server = OpenAIServer(rt.scheduler, rt.tokenizer, rt.engine_cfg, model_name=name, max_model_len=args.max_model_len)
+    print(f"listening on http://{args.host}:{args.port}  model={name}  ranks={rt.ctx.world}  mtp={args.mtp}", file=sys.stderr)
+    try:
+        asyncio.run(serve(server))
+    except KeyboardInterrupt:
+        pass
+    finally:
+        rt.scheduler.stop()
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -31,11 +31,13 @@ struct GdnParams {
     const bf16* b;             // [T, h]   beta input
     const float* A_log;        // [h]
     const float* dt_bias;      // [h]
-    const bf16* g;             // KDA: per-channel log decay [T, h, dk] (null for GDN)
+    const bf16* g;             // KDA: per-channel forget input [T, h, dk] (null for GDN); dt_bias is then [h, dk]
     const int* qo_indptr;      // [B + 1] token ranges of the sequences
     const int* state_idx;      // [B] state slot of each sequence
     int h, dk, dv;
-    int normalize_qk;          // GDN: L2-normalise q (then scale dk^-0.5) and k
+    int normalize_qk;          // L2-normalise q (then scale dk^-0.5) and k
+    float lower_bound;         // KDA: decay = exp(lower_bound * sigmoid(exp(A_log[h]) * (forget + dt_bias)))
+    float norm_eps;            // added to the squared norms (GDN 1e-8, KDA 1e-6)
 };
 
 // One block per (sequence, head); thread j owns state column S[:, j] (dv <= blockDim.x), kept in
@@ -64,14 +66,18 @@ __global__ void __launch_bounds__(128) delta_scan_kernel(GdnParams p) {
             const float q = __bfloat162float(row[qoff + i]), k = __bfloat162float(row[koff + i]);
             s_q[i] = q; s_k[i] = k;
             qq += q * q; kk += k * k;
-            if (p.g != nullptr) s_g[i] = __expf(__bfloat162float(p.g[((size_t)t * p.h + h) * DK + i]));
+            if (p.g != nullptr)
+                s_g[i] = __expf(p.lower_bound * sigmoid_f(__expf(p.A_log[h]) * (__bfloat162float(p.g[((size_t)t * p.h + h) * DK + i]) +
+                                                                              p.dt_bias[h * DK + i])));
         }
         if (p.normalize_qk) {
             qq = warp_sum(qq); kk = warp_sum(kk);
             if ((tid & 31) == 0) { s_red[(tid >> 5) * 2] = qq; s_red[(tid >> 5) * 2 + 1] = kk; }
         }
         if (tid == 0) {
-            s_scal[0] = sigmoid_f(__bfloat162float(p.b[(size_t)t * p.h + h]));
+            // KDA: the beta logits are bf16 and so is their sigmoid in the checkpoint's definition
+            const float bsig = sigmoid_f(__bfloat162float(p.b[(size_t)t * p.h + h]));
+            s_scal[0] = p.g != nullptr ? __bfloat162float(__float2bfloat16(bsig)) : bsig;
             s_scal[1] = p.g != nullptr ? 1.f
                                        : __expf(-__expf(p.A_log[h]) * softplus_f(__bfloat162float(p.a[(size_t)t * p.h + h]) + p.dt_bias[h]));
         }
@@ -80,8 +86,8 @@ __global__ void __launch_bounds__(128) delta_scan_kernel(GdnParams p) {
         if (p.normalize_qk) {
             float q2 = 0.f, k2 = 0.f;
             for (int w = 0; w < (int)(blockDim.x >> 5); ++w) { q2 += s_red[w * 2]; k2 += s_red[w * 2 + 1]; }
-            qs = rsqrtf(q2 + 1e-8f) * rsqrtf((float)DK);
-            ks = rsqrtf(k2 + 1e-8f);
+            qs = rsqrtf(q2 + p.norm_eps) * rsqrtf((float)DK);
+            ks = rsqrtf(k2 + p.norm_eps);
         }
         const float beta = s_scal[0], decay = s_scal[1];
         if (active) {
@@ -153,67 +159,101 @@ __global__ void rmsnorm_gated_kernel(bf16* __restrict__ out, const bf16* __restr
     }
 }
 
-// ---- manifold hyper-connections (n <= 8 residual streams) ----------------------------------------------
-// pre: M = sinkhorn(exp(mix_logits[t])), mixed = M x streams[t], x = softmax(collapse_w[t]) . mixed.
-// One block per token.
-__global__ void mhc_pre_kernel(float* __restrict__ mixed, bf16* __restrict__ x, const float* __restrict__ streams,
-                               const float* __restrict__ mix_logits, const float* __restrict__ collapse_w, int n, int H, int iters) {
+// ---- manifold hyper-connections: 4 residual streams per token -------------------------------------------
+// pre: 24 coefficient logits = (x / rms(x)) . fn[c] over the 4*H values of the token (fp32), then
+//   pre[i]  = sigmoid(l[i] * scale[0] + base[i]) + hc_eps                 (collapse weights)
+//   post[i] = 2 * sigmoid(l[4+i] * scale[1] + base[4+i])                  (expansion weights)
+//   comb    = Sinkhorn(softmax_rows(l[8..24] * scale[2] + base[8..24]) + hc_eps)
+//   collapsed[d] = sum_s pre[s] * x[s, d]
+// One block of 256 threads per token: each warp computes three of the 24 dot products.
+__global__ void __launch_bounds__(256) mhc_pre_kernel(bf16* __restrict__ collapsed, float* __restrict__ post, float* __restrict__ comb,
+                                                      const bf16* __restrict__ x, const bf16* __restrict__ fn,
+                                                      const float* __restrict__ base, const float* __restrict__ scale, int H,
+                                                      float norm_eps, float hc_eps, int iters) {
     pdl_grid_sync();
-    __shared__ float M[64], cw[8];
-    const int t = blockIdx.x, tid = threadIdx.x;
+    __shared__ float scratch[33];
+    __shared__ float logits[24], pre[4], mix[16];
+    const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, width = 4 * H;
+    const bf16* xr = x + (size_t)t * width;
+    float ss = 0.f;
+    for (int i = tid; i < width; i += blockDim.x) {
+        const float v = __bfloat162float(xr[i]);
+        ss += v * v;
+    }
+    const float inv = rsqrtf(block_sum(ss, scratch) / (float)width + norm_eps);
+    for (int c = warp * 3; c < warp * 3 + 3; ++c) {
+        float dot = 0.f;
+        for (int i = lane; i < width; i += 32) dot += (__bfloat162float(xr[i]) * inv) * __bfloat162float(fn[(size_t)c * width + i]);
+        dot = warp_sum(dot);
+        if (lane == 0) logits[c] = dot;
+    }
+    __syncthreads();
     if (tid == 0) {
-        float mx = -INFINITY;
-        for (int i = 0; i < n * n; ++i) mx = fmaxf(mx, mix_logits[(size_t)t * n * n + i]);
-        for (int i = 0; i < n * n; ++i) M[i] = __expf(mix_logits[(size_t)t * n * n + i] - mx);
-        for (int it = 0; it < iters; ++it) {
-            for (int r = 0; r < n; ++r) {
-                float s = 0.f;
-                for (int c = 0; c < n; ++c) s += M[r * n + c];
-                for (int c = 0; c < n; ++c) M[r * n + c] /= s;
+        for (int i = 0; i < 4; ++i) {
+            pre[i] = sigmoid_f(logits[i] * scale[0] + base[i]) + hc_eps;
+            post[t * 4 + i] = 2.f * sigmoid_f(logits[4 + i] * scale[1] + base[4 + i]);
+        }
+        for (int i = 0; i < 4; ++i) {
+            float mx = -INFINITY, den = 0.f;
+            for (int j = 0; j < 4; ++j) {
+                mix[i * 4 + j] = logits[8 + i * 4 + j] * scale[2] + base[8 + i * 4 + j];
+                mx = fmaxf(mx, mix[i * 4 + j]);
             }
-            for (int c = 0; c < n; ++c) {
-                float s = 0.f;
-                for (int r = 0; r < n; ++r) s += M[r * n + c];
-                for (int r = 0; r < n; ++r) M[r * n + c] /= s;
+            for (int j = 0; j < 4; ++j) { mix[i * 4 + j] = expf(mix[i * 4 + j] - mx); den += mix[i * 4 + j]; }
+            for (int j = 0; j < 4; ++j) mix[i * 4 + j] = mix[i * 4 + j] / den + hc_eps;
+        }
+        for (int it = 0; it < iters; ++it) {
+            if (it > 0) {
+                for (int i = 0; i < 4; ++i) {
+                    float den = hc_eps;
+                    for (int j = 0; j < 4; ++j) den += mix[i * 4 + j];
+                    for (int j = 0; j < 4; ++j) mix[i * 4 + j] /= den;
+                }
+            }
+            for (int j = 0; j < 4; ++j) {
+                float den = hc_eps;
+                for (int i = 0; i < 4; ++i) den += mix[i * 4 + j];
+                for (int i = 0; i < 4; ++i) mix[i * 4 + j] /= den;
             }
         }
-        float cm = -INFINITY, cs = 0.f;
-        for (int i = 0; i < n; ++i) cm = fmaxf(cm, collapse_w[(size_t)t * n + i]);
-        for (int i = 0; i < n; ++i) { cw[i] = __expf(collapse_w[(size_t)t * n + i] - cm); cs += cw[i]; }
-        for (int i = 0; i < n; ++i) cw[i] /= cs;
+        for (int i = 0; i < 16; ++i) comb[t * 16 + i] = mix[i];
     }
     __syncthreads();
     for (int d = tid; d < H; d += blockDim.x) {
-        float s[8], xo = 0.f;
-        for (int jn = 0; jn < n; ++jn) s[jn] = streams[((size_t)t * n + jn) * H + d];
-        for (int i = 0; i < n; ++i) {
-            float m = 0.f;
-            for (int jn = 0; jn < n; ++jn) m += M[i * n + jn] * s[jn];
-            mixed[((size_t)t * n + i) * H + d] = m;
-            xo += cw[i] * m;
+        float v = 0.f;
+        for (int sidx = 0; sidx < 4; ++sidx) v += pre[sidx] * __bfloat162float(xr[sidx * H + d]);
+        collapsed[(size_t)t * H + d] = __float2bfloat16(v);
+    }
+}
+
+// post: out[t, s, :] = post[t, s] * block[t, :] + sum_i comb[t, i, s] * residual[t, i, :]
+__global__ void mhc_post_kernel(bf16* __restrict__ out, const bf16* __restrict__ residual, const bf16* __restrict__ block,
+                                const float* __restrict__ post, const float* __restrict__ comb, int H) {
+    pdl_grid_sync();
+    const int t = blockIdx.x, sidx = blockIdx.y;
+    float cw[4];
+    for (int i = 0; i < 4; ++i) cw[i] = comb[t * 16 + i * 4 + sidx];
+    const float pw = post[t * 4 + sidx];
+    for (int d = threadIdx.x; d < H; d += blockDim.x) {
+        float v = pw * __bfloat162float(block[(size_t)t * H + d]);
+        for (int i = 0; i < 4; ++i) v += cw[i] * __bfloat162float(residual[((size_t)t * 4 + i) * H + d]);
+        out[((size_t)t * 4 + sidx) * H + d] = __float2bfloat16(v);
+    }
+}
+
+// expand: copy a [T, H] activation into 4 streams; collapse: mean of the 4 streams
+__global__ void mhc_streams_kernel(bf16* __restrict__ out, const bf16* __restrict__ x, int H, int expand) {
+    pdl_grid_sync();
+    const int t = blockIdx.x;
+    for (int d = threadIdx.x; d < H; d += blockDim.x) {
+        if (expand) {
+            const bf16 v = x[(size_t)t * H + d];
+            for (int sidx = 0; sidx < 4; ++sidx) out[((size_t)t * 4 + sidx) * H + d] = v;
+        } else {
+            float v = 0.f;
+            for (int sidx = 0; sidx < 4; ++sidx) v += __bfloat162float(x[((size_t)t * 4 + sidx) * H + d]);
+            out[(size_t)t * H + d] = __float2bfloat16(v * 0.25f);
         }
-        x[(size_t)t * H + d] = __float2bfloat16(xo);
-    }
-}
-
-// post: streams_out[t, i, :] = mixed[t, i, :] + expand_w[t, i] * y[t, :]
-__global__ void mhc_post_kernel(float* __restrict__ out, const float* __restrict__ mixed, const bf16* __restrict__ y,
-                                const float* __restrict__ expand_w, int n, int H, size_t total) {
-    pdl_grid_sync();
-    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
-        const size_t d = idx % H, ti = idx / H, t = ti / n;
-        out[idx] = mixed[idx] + expand_w[ti] * __bfloat162float(y[t * H + d]);
-    }
-}
-
-// final collapse: mean over the streams
-__global__ void mhc_streams_kernel(bf16* __restrict__ out, const float* __restrict__ streams, int n, int H, size_t total) {
-    pdl_grid_sync();
-    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
-        const size_t d = idx % H, t = idx / H;
-        float s = 0.f;
-        for (int i = 0; i < n; ++i) s += streams[(t * n + i) * H + d];
-        out[idx] = __float2bfloat16(s / (float)n);
     }
 }
 
@@ -247,29 +287,25 @@ SL_API int sl_rmsnorm_gated(void* out, const void* x, const void* gate, const vo
     return SL_LAUNCH_CHECK();
 }
 
-SL_API int sl_mhc_pre(void* mixed, void* x, const void* streams, const void* mix_logits, const void* collapse_w, int T, int n,
-                      int H, int iters, cudaStream_t s) {
+SL_API int sl_mhc_pre(void* collapsed, void* post, void* comb, const void* x, const void* fn, const void* base, const void* scale,
+                      int T, int H, float norm_eps, float hc_eps, int iters, cudaStream_t s) {
     if (T == 0) return 0;
-    if (n > 8 || n < 1) return -1;
-    sl_launch(mhc_pre_kernel, T, 256, 0, s, (float*)mixed, (bf16*)x, (const float*)streams, (const float*)mix_logits,
-              (const float*)collapse_w, n, H, iters);
+    if (iters < 1) return -1;
+    sl_launch(mhc_pre_kernel, T, 256, 0, s, (bf16*)collapsed, (float*)post, (float*)comb, (const bf16*)x, (const bf16*)fn,
+              (const float*)base, (const float*)scale, H, norm_eps, hc_eps, iters);
     return SL_LAUNCH_CHECK();
 }
 
-SL_API int sl_mhc_post(void* out, const void* mixed, const void* y, const void* expand_w, int T, int n, int H, cudaStream_t s) {
+SL_API int sl_mhc_post(void* out, const void* residual, const void* block, const void* post, const void* comb, int T, int H,
+                       cudaStream_t s) {
     if (T == 0) return 0;
-    const size_t total = (size_t)T * n * H;
-    int blocks = (int)((total + 255) / 256);
-    if (blocks > 148 * 8) blocks = 148 * 8;
-    sl_launch(mhc_post_kernel, blocks, 256, 0, s, (float*)out, (const float*)mixed, (const bf16*)y, (const float*)expand_w, n, H, total);
+    sl_launch(mhc_post_kernel, dim3(T, 4), 256, 0, s, (bf16*)out, (const bf16*)residual, (const bf16*)block, (const float*)post,
+              (const float*)comb, H);
     return SL_LAUNCH_CHECK();
 }
 
-SL_API int sl_mhc_streams(void* out, const void* streams, int T, int n, int H, cudaStream_t s) {
+SL_API int sl_mhc_streams(void* out, const void* x, int T, int H, int expand, cudaStream_t s) {
     if (T == 0) return 0;
-    const size_t total = (size_t)T * H;
-    int blocks = (int)((total + 255) / 256);
-    if (blocks > 148 * 8) blocks = 148 * 8;
-    sl_launch(mhc_streams_kernel, blocks, 256, 0, s, (bf16*)out, (const float*)streams, n, H, total);
+    sl_launch(mhc_streams_kernel, T, 256, 0, s, (bf16*)out, (const bf16*)x, H, expand);
     return SL_LAUNCH_CHECK();
 }

@@ -156,8 +156,8 @@ _SIGS = {
     "sl_delta_scan": [vp, i32, vp],
     "sl_causal_conv1d": [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp],
     "sl_rmsnorm_gated": [vp, vp, vp, vp, i32, i32, f32, i32, vp],
-    "sl_mhc_pre": [vp, vp, vp, vp, vp, i32, i32, i32, i32, vp],
-    "sl_mhc_post": [vp, vp, vp, vp, i32, i32, i32, vp],
+    "sl_mhc_pre": [vp, vp, vp, vp, vp, vp, vp, i32, i32, f32, f32, i32, vp],
+    "sl_mhc_post": [vp, vp, vp, vp, vp, i32, i32, vp],
     "sl_mhc_streams": [vp, vp, i32, i32, i32, vp],
     "sl_silu_mul": [vp, vp, i32, i32, vp],
     "sl_route_topk": [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, f32, vp],

@@ -15,7 +15,8 @@ from . import reference as R
 class GdnParams(C.Structure):
     _fields_ = [("out", C.c_void_p), ("state", C.c_void_p), ("qkv", C.c_void_p), ("ld_qkv", C.c_int), ("a", C.c_void_p),
                 ("b", C.c_void_p), ("A_log", C.c_void_p), ("dt_bias", C.c_void_p), ("g", C.c_void_p), ("qo_indptr", C.c_void_p),
-                ("state_idx", C.c_void_p), ("h", C.c_int), ("dk", C.c_int), ("dv", C.c_int), ("normalize_qk", C.c_int)]
+                ("state_idx", C.c_void_p), ("h", C.c_int), ("dk", C.c_int), ("dv", C.c_int), ("normalize_qk", C.c_int),
+                ("lower_bound", C.c_float), ("norm_eps", C.c_float)]
 
 
 def _native():
@@ -45,7 +46,7 @@ def gdn_scan(qkv, a, b, A_log, dt_bias, state, qo_indptr, state_idx, h: int, dk:
         out = torch.empty(T, h, dv, dtype=torch.bfloat16, device=qkv.device)
         p = GdnParams(out=out.data_ptr(), state=state.data_ptr(), qkv=qkv.data_ptr(), ld_qkv=qkv.stride(0), a=a.data_ptr(),
                       b=b.data_ptr(), A_log=A_log.data_ptr(), dt_bias=dt_bias.data_ptr(), g=0, qo_indptr=qo_indptr.data_ptr(),
-                      state_idx=state_idx.data_ptr(), h=h, dk=dk, dv=dv, normalize_qk=1)
+                      state_idx=state_idx.data_ptr(), h=h, dk=dk, dv=dv, normalize_qk=1, lower_bound=0.0, norm_eps=1e-8)
         N.call("sl_delta_scan", C.byref(p), qo_indptr.numel() - 1, N.stream())
         return out
     q, k, v = _split_qkv(qkv.to(torch.float32), h, dk, dv)
@@ -63,27 +64,32 @@ def gdn_scan(qkv, a, b, A_log, dt_bias, state, qo_indptr, state_idx, h: int, dk:
     return out.to(torch.bfloat16)
 
 
-def kda_scan(qkv, g, b, state, qo_indptr, state_idx, h: int, dk: int, dv: int):
-    """KDA: as :func:`gdn_scan` with a per-channel log decay g [T, h, dk] and no q/k normalisation."""
+def kda_scan(qkv, forget, b, A_log, dt_bias, state, qo_indptr, state_idx, h: int, dk: int, dv: int, lower_bound: float):
+    """KDA recurrence: as :func:`gdn_scan` but with a per-channel decay
+    exp(lower_bound * sigmoid(exp(A_log[h]) * (forget[t, h, :] + dt_bias[h, :]))), lower_bound < 0.
+    qkv [T, h*dk | h*dk | h*dv] (conv outputs), forget [T, h, dk] bf16, b [T, h], dt_bias [h, dk] fp32."""
+    if not lower_bound < 0:
+        raise ValueError("kda_scan: the gate lower bound must be negative and finite")
     T = qkv.shape[0]
     if qkv.is_cuda:
         N = _native()
         out = torch.empty(T, h, dv, dtype=torch.bfloat16, device=qkv.device)
-        g = g.to(torch.bfloat16).contiguous()
+        forget = forget.to(torch.bfloat16).contiguous()
         p = GdnParams(out=out.data_ptr(), state=state.data_ptr(), qkv=qkv.data_ptr(), ld_qkv=qkv.stride(0), a=0, b=b.data_ptr(),
-                      A_log=0, dt_bias=0, g=g.data_ptr(), qo_indptr=qo_indptr.data_ptr(), state_idx=state_idx.data_ptr(), h=h,
-                      dk=dk, dv=dv, normalize_qk=0)
+                      A_log=A_log.data_ptr(), dt_bias=dt_bias.contiguous().data_ptr(), g=forget.data_ptr(),
+                      qo_indptr=qo_indptr.data_ptr(), state_idx=state_idx.data_ptr(), h=h, dk=dk, dv=dv, normalize_qk=1,
+                      lower_bound=float(lower_bound), norm_eps=1e-6)
         N.call("sl_delta_scan", C.byref(p), qo_indptr.numel() - 1, N.stream())
         return out
     q, k, v = _split_qkv(qkv.to(torch.float32), h, dk, dv)
-    beta = torch.sigmoid(b.to(torch.float32))
     out = torch.empty(T, h, dv, dtype=torch.float32, device=qkv.device)
     ind = qo_indptr.tolist()
     for bi in range(len(ind) - 1):
         lo, hi = ind[bi], ind[bi + 1]
         if hi > lo:
             slot = int(state_idx[bi])
-            out[lo:hi], state[slot] = R.kda_scan(q[lo:hi], k[lo:hi], v[lo:hi], g[lo:hi].to(torch.float32), beta[lo:hi], state[slot])
+            out[lo:hi], state[slot] = R.kda_scan(q[lo:hi], k[lo:hi], v[lo:hi], forget[lo:hi].reshape(hi - lo, h, dk), b[lo:hi], A_log,
+                                                 dt_bias.reshape(h, dk), state[slot], lower_bound)
     return out.to(torch.bfloat16)
 
 
@@ -121,37 +127,49 @@ def rmsnorm_gated(x, gate, weight, eps: float, sigmoid_gate: bool = False):
     return f(x, gate, weight, eps).to(x.dtype)
 
 
-def mhc_pre(streams, mix_logits, collapse_w, iters: int = 20):
-    """streams [T, n, H] fp32 -> (mixed [T, n, H] fp32, x [T, H] bf16)."""
-    if streams.is_cuda:
+def mhc_pre(x, fn, base, scale, norm_eps: float, hc_eps: float, iters: int):
+    """x [T, 4, H] bf16 residual streams -> (collapsed [T, H] bf16, post [T, 4] f32, comb [T, 4, 4] f32)."""
+    if x.dim() != 3 or x.shape[1] != 4 or not norm_eps > 0 or not hc_eps > 0 or iters < 1:
+        raise ValueError("mhc_pre: expected [tokens, 4, hidden] and positive epsilons / iteration count")
+    T, _, H = x.shape
+    if tuple(fn.shape) != (24, 4 * H) or base.numel() != 24 or scale.numel() != 3:
+        raise ValueError("mhc_pre: expected fn [24, 4*hidden], base [24], scale [3]")
+    if x.is_cuda:
         N = _native()
-        T, n, H = streams.shape
-        mixed = torch.empty_like(streams)
-        x = torch.empty(T, H, dtype=torch.bfloat16, device=streams.device)
-        N.call("sl_mhc_pre", mixed.data_ptr(), x.data_ptr(), streams.contiguous().data_ptr(),
-               mix_logits.to(torch.float32).contiguous().data_ptr(), collapse_w.to(torch.float32).contiguous().data_ptr(), T, n, H,
-               iters, N.stream())
-        return mixed, x
-    mixed, x = R.mhc_pre(streams, mix_logits, collapse_w, iters)
-    return mixed, x.to(torch.bfloat16)
+        collapsed = torch.empty(T, H, dtype=torch.bfloat16, device=x.device)
+        post = torch.empty(T, 4, dtype=torch.float32, device=x.device)
+        comb = torch.empty(T, 4, 4, dtype=torch.float32, device=x.device)
+        N.call("sl_mhc_pre", collapsed.data_ptr(), post.data_ptr(), comb.data_ptr(), x.to(torch.bfloat16).contiguous().data_ptr(),
+               fn.to(torch.bfloat16).contiguous().data_ptr(), base.to(torch.float32).contiguous().data_ptr(),
+               scale.to(torch.float32).contiguous().data_ptr(), T, H, float(norm_eps), float(hc_eps), int(iters), N.stream())
+        return collapsed, post, comb
+    collapsed, post, comb = R.mhc_pre(x, fn, base, scale, norm_eps, hc_eps, iters)
+    return collapsed.to(torch.bfloat16), post, comb
 
 
-def mhc_post(mixed, y, expand_w):
-    if mixed.is_cuda:
+def mhc_post(residual, block, post, comb):
+    """residual [T, 4, H], block [T, H] -> new streams [T, 4, H] bf16."""
+    if residual.dim() != 3 or residual.shape[1] != 4:
+        raise ValueError("mhc_post: expected [tokens, 4, hidden]")
+    if residual.is_cuda:
         N = _native()
-        T, n, H = mixed.shape
-        out = torch.empty_like(mixed)
-        N.call("sl_mhc_post", out.data_ptr(), mixed.contiguous().data_ptr(), y.to(torch.bfloat16).contiguous().data_ptr(),
-               expand_w.to(torch.float32).contiguous().data_ptr(), T, n, H, N.stream())
+        T, _, H = residual.shape
+        out = torch.empty(T, 4, H, dtype=torch.bfloat16, device=residual.device)
+        N.call("sl_mhc_post", out.data_ptr(), residual.to(torch.bfloat16).contiguous().data_ptr(),
+               block.to(torch.bfloat16).contiguous().data_ptr(), post.contiguous().data_ptr(), comb.contiguous().data_ptr(), T, H,
+               N.stream())
         return out
-    return R.mhc_post(mixed, y, expand_w)
+    return R.mhc_post(residual, block, post, comb).to(torch.bfloat16)
 
 
-def mhc_streams_mean(streams):
-    if streams.is_cuda:
+def mhc_streams(x, expand: bool):
+    """expand: [T, H] -> [T, 4, H] (copies); collapse: [T, 4, H] -> [T, H] (mean)."""
+    if (x.dim() != 2) if expand else (x.dim() != 3 or x.shape[1] != 4):
+        raise ValueError("mhc_streams: expected [tokens, hidden] to expand or [tokens, 4, hidden] to collapse")
+    if x.is_cuda:
         N = _native()
-        T, n, H = streams.shape
-        out = torch.empty(T, H, dtype=torch.bfloat16, device=streams.device)
-        N.call("sl_mhc_streams", out.data_ptr(), streams.contiguous().data_ptr(), T, n, H, N.stream())
+        T, H = x.shape[0], x.shape[-1]
+        out = torch.empty((T, 4, H) if expand else (T, H), dtype=torch.bfloat16, device=x.device)
+        N.call("sl_mhc_streams", out.data_ptr(), x.to(torch.bfloat16).contiguous().data_ptr(), T, H, int(expand), N.stream())
         return out
-    return R.mhc_streams_mean(streams).to(torch.bfloat16)
+    return R.mhc_streams(x, expand).to(torch.bfloat16)

@@ -469,17 +469,24 @@ def gdn_recurrent(q, k, v, g, beta, state):
     return out, S
 
 
-def kda_scan(q, k, v, g, beta, state):
-    """Kimi-Delta-Attention style recurrence with a **per-channel** decay g [T, h, Dk]
-    (`csrc/glm_flash_hybrid.cu:31-72`).  Otherwise as :func:`gdn_recurrent`."""
+def kda_scan(q, k, v, forget, beta, A_log, dt_bias, state, lower_bound: float):
+    """KDA recurrence (`csrc/glm_flash_hybrid.cu:31-72`): q, k L2-normalised (eps 1e-6 inside the
+    root), q scaled by Dk^-0.5; per-channel decay exp(lower_bound * sigmoid(exp(A_log[h]) *
+    (forget + dt_bias[h, :]))) with lower_bound < 0; beta = bf16(sigmoid(beta logits)).
+    q, k, forget [T, h, Dk], v [T, h, Dv], beta [T, h], dt_bias [h, Dk], state [h, Dk, Dv]."""
     T, h, Dk = q.shape
     S = state.to(torch.float32).clone()
     out = torch.empty(T, h, v.shape[-1], dtype=torch.float32, device=q.device)
     qf, kf, vf = q.to(torch.float32), k.to(torch.float32), v.to(torch.float32)
+    qf = qf / torch.sqrt((qf * qf).sum(-1, keepdim=True) + 1e-6) * Dk ** -0.5
+    kf = kf / torch.sqrt((kf * kf).sum(-1, keepdim=True) + 1e-6)
+    decay = torch.exp(lower_bound * torch.sigmoid(torch.exp(A_log.to(torch.float32)).view(1, h, 1)
+                                                   * (forget.to(torch.float32) + dt_bias.to(torch.float32).view(1, h, Dk))))
+    bt = torch.sigmoid(beta.to(torch.float32)).to(torch.bfloat16).to(torch.float32)
     for t in range(T):
-        S = S * torch.exp(g[t].to(torch.float32)).unsqueeze(-1)
+        S = S * decay[t].unsqueeze(-1)
         kv = torch.einsum("hk,hkv->hv", kf[t], S)
-        delta = (vf[t] - kv) * beta[t].to(torch.float32).unsqueeze(-1)
+        delta = (vf[t] - kv) * bt[t].unsqueeze(-1)
         S = S + torch.einsum("hk,hv->hkv", kf[t], delta)
         out[t] = torch.einsum("hk,hkv->hv", qf[t], S)
     return out, S
@@ -490,36 +497,40 @@ def kda_norm(x, gate, weight, eps):
     return rmsnorm(x, weight, eps) * torch.sigmoid(gate.to(torch.float32))
 
 
-def sinkhorn(logits: torch.Tensor, iters: int = 20) -> torch.Tensor:
-    """Doubly-stochastic normalisation of exp(logits) [..., n, n]."""
-    m = torch.exp(logits.to(torch.float32) - logits.amax(dim=(-1, -2), keepdim=True))
-    for _ in range(iters):
-        m = m / m.sum(-1, keepdim=True)
-        m = m / m.sum(-2, keepdim=True)
-    return m
+def mhc_pre(x: torch.Tensor, fn: torch.Tensor, base: torch.Tensor, scale: torch.Tensor, norm_eps: float, hc_eps: float,
+            iters: int):
+    """Manifold hyper-connection, pre-sublayer (`csrc/glm_flash_hybrid.cu:84-142`).
+
+    x [T, 4, H] residual streams, fn [24, 4H] coefficient projection, base [24], scale [3].
+    Returns (collapsed [T, H], post [T, 4], comb [T, 4, 4]): the sublayer input, the weights
+    that add the sublayer output back to each stream and the stream-mixing matrix
+    (softmax rows + eps, then alternating column / row normalisation)."""
+    T, n, H = x.shape
+    xf = x.to(torch.float32).reshape(T, n * H)
+    inv = torch.rsqrt((xf * xf).mean(-1, keepdim=True) + norm_eps)
+    logits = (xf * inv) @ fn.to(torch.float32).t()                            # [T, 24]
+    base, scale = base.to(torch.float32), scale.to(torch.float32)
+    pre = torch.sigmoid(logits[:, :4] * scale[0] + base[:4]) + hc_eps
+    post = 2.0 * torch.sigmoid(logits[:, 4:8] * scale[1] + base[4:8])
+    mix = torch.softmax((logits[:, 8:24] * scale[2] + base[8:24]).view(T, 4, 4), -1) + hc_eps
+    for it in range(iters):
+        if it > 0:
+            mix = mix / (mix.sum(-1, keepdim=True) + hc_eps)
+        mix = mix / (mix.sum(-2, keepdim=True) + hc_eps)
+    collapsed = torch.einsum("ts,tsh->th", pre, x.to(torch.float32))
+    return collapsed, post, mix
 
 
-def mhc_pre(streams: torch.Tensor, mix_logits: torch.Tensor, collapse_w: torch.Tensor, iters: int = 20):
-    """Manifold hyper-connection, pre-sublayer: mix the n residual streams with a
-    Sinkhorn-normalised matrix and collapse them into the sublayer input.
-
-    streams [T, n, H], mix_logits [T, n, n], collapse_w [T, n] -> (mixed [T, n, H], x [T, H]).
-    Reference `csrc/glm_flash_hybrid.cu:84-142`.
-    """
-    M = sinkhorn(mix_logits, iters)
-    mixed = torch.einsum("tij,tjh->tih", M, streams.to(torch.float32))
-    x = torch.einsum("ti,tih->th", torch.softmax(collapse_w.to(torch.float32), -1), mixed)
-    return mixed, x
+def mhc_post(residual: torch.Tensor, block: torch.Tensor, post: torch.Tensor, comb: torch.Tensor) -> torch.Tensor:
+    """out[t, s] = post[t, s] * block[t] + sum_i comb[t, i, s] * residual[t, i]  (`:143-154`)."""
+    return post.unsqueeze(-1) * block.to(torch.float32).unsqueeze(1) + torch.einsum("tis,tih->tsh", comb, residual.to(torch.float32))
 
 
-def mhc_post(mixed: torch.Tensor, y: torch.Tensor, expand_w: torch.Tensor) -> torch.Tensor:
-    """Post-sublayer: add the sublayer output back into each stream with weights expand_w [T, n]."""
-    return mixed + expand_w.to(torch.float32).unsqueeze(-1) * y.to(torch.float32).unsqueeze(1)
-
-
-def mhc_streams_mean(streams: torch.Tensor) -> torch.Tensor:
-    """Final collapse: mean over the residual streams (`csrc/glm_flash_hybrid.cu:155`)."""
-    return streams.to(torch.float32).mean(1)
+def mhc_streams(x: torch.Tensor, expand: bool) -> torch.Tensor:
+    """expand: [T, H] -> 4 identical streams [T, 4, H]; collapse: mean of the streams (`:155-170`)."""
+    if expand:
+        return x.unsqueeze(1).expand(-1, 4, -1).contiguous()
+    return x.to(torch.float32).mean(1)
 
 
 def log_softmax_nll(logits: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:

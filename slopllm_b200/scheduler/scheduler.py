@@ -51,7 +51,8 @@ class GenerationRequest:
     cached_tokens: int = 0
     prefill_tokens: int = 0
     prefill_seconds: float = 0.0
-    cancelled: bool = False
+    cancelled: bool = False                  # set by the client side at any time
+    cancel_seen: bool = False                # what the scheduler acts on (copied at step boundaries, on every rank alike)
     submitted_at: float = field(default_factory=time.time)
     first_token_at: Optional[float] = None
 
@@ -163,8 +164,11 @@ class _Row:
 
 class GenerationScheduler:
     def __init__(self, engine: EngineLike, max_batch: int = 8, chunk_size: int = 8192, eos_token_ids: Seq[int] = (),
-                 host_tier: Optional[HostTier] = None, decode_latency_ms: float = 0.0):
+                 host_tier: Optional[HostTier] = None, decode_latency_ms: float = 0.0, replica_channel=None):
         self.engine = engine
+        # multi-process serving: rank 0 owns the request queue and broadcasts every step's events so that all
+        # ranks admit, cancel and flush in the same step (see scheduler/replicated.py)
+        self.replica = replica_channel
         self.max_batch = max_batch
         self.chunk_size = chunk_size
         self.eos = set(eos_token_ids)
@@ -178,17 +182,20 @@ class GenerationScheduler:
         self._thread: Optional[threading.Thread] = None
 
     # ---- public -------------------------------------------------------------------------------------
+    def _inbox(self) -> "queue.Queue":
+        return self.replica.inbox if self.replica is not None else self.events
+
     def submit(self, req: GenerationRequest) -> None:
-        self.events.put(req)
+        self._inbox().put(req)
 
     def flush_gpu_cache(self) -> CacheFlushEvent:
         ev = CacheFlushEvent("flush_gpu_cache")
-        self.events.put(ev)
+        self._inbox().put(ev)
         return ev
 
     def flush_host_cache(self) -> CacheFlushEvent:
         ev = CacheFlushEvent("flush_host_cache")
-        self.events.put(ev)
+        self._inbox().put(ev)
         return ev
 
     def start(self) -> None:
@@ -196,13 +203,22 @@ class GenerationScheduler:
         self._thread.start()
 
     def stop(self) -> None:
-        self._stop.set()
-        self.events.put(None)
+        if self.replica is not None:
+            self.replica.inbox.put(None)          # travels to every rank with the next exchange
+        else:
+            self._stop.set()
+            self.events.put(None)
         if self._thread:
             self._thread.join(timeout=30)
 
     def run(self) -> None:
         while not self._stop.is_set():
+            if self.replica is not None:
+                self.replica.exchange(self)
+                if self._stop.is_set():
+                    break
+                self.step()
+                continue
             if not self.rows and self.events.empty():
                 ev = self.events.get()
                 if ev is None:
@@ -213,6 +229,9 @@ class GenerationScheduler:
     # ---- one iteration ----------------------------------------------------------------------------------
     def step(self) -> None:
         try:
+            if self.replica is None:
+                for r in self.rows:
+                    r.req.cancel_seen = r.req.cancel_seen or r.req.cancelled
             self._retire()
             self._drain_events()
             self._prefill()
@@ -231,11 +250,11 @@ class GenerationScheduler:
         keep = []
         for r in self.rows:
             req = r.req
-            done = bool(req.finish_reason) or req.cancelled
+            done = bool(req.finish_reason) or req.cancel_seen
             if not done:
                 keep.append(r)
                 continue
-            if req.cancelled and not req.finish_reason:
+            if req.cancel_seen and not req.finish_reason:
                 req.finish_reason = "cancelled"
             self.engine.kv.stage(r.seq)           # keep the pages for prefix reuse
             self._free_rows.append(r.row)
@@ -364,7 +383,7 @@ class GenerationScheduler:
                 self._publish(r, [toks[0]])
 
     def _decode(self) -> None:
-        active = [r for r in self.rows if r.prompt_done and not r.req.finish_reason and not r.req.cancelled]
+        active = [r for r in self.rows if r.prompt_done and not r.req.finish_reason and not r.req.cancel_seen]
         if not active:
             return
         if self.decode_latency:

@@ -1,0 +1,89 @@
+"""Entry points on the CPU reference ops with random tiny models: argument handling, registry
+checks and the evaluation / benchmark tools end to end (reference: `src/model_cli.ts`,
+`src/run_*.ts`, `src/mtp_stats.ts`, `src/model_registry.ts`, `src/model_path.ts`)."""
+import io
+import json
+import os
+from contextlib import redirect_stdout
+
+import pytest
+
+from slopllm_b200.cli import mtp_bench, nll, prefill_bench, sweep
+from slopllm_b200.models import registry
+from slopllm_b200.utils.model_path import ModelNotFoundError, list_safetensors_shards, resolve_model_path
+from slopllm_b200.utils.mtp_stats import MtpStats
+
+
+def run_tool(mod, argv):
+    buf = io.StringIO()
+    with redirect_stdout(buf):
+        assert mod.main(argv) == 0
+    return [json.loads(l) for l in buf.getvalue().splitlines() if l.startswith("{")]
+
+
+BASE = ["--cpu", "--random-init", "tiny", "--no-cuda-graph", "--batch-size", "2", "--chunk-size", "64", "--max-pages", "32"]
+
+
+def test_prefill_bench_and_sweep():
+    out = run_tool(prefill_bench, BASE + ["--contexts", "100,200"])
+    assert [o["context"] for o in out] == [100, 200] and all(o["prefill_tok_s"] > 0 for o in out)
+    out = run_tool(sweep, BASE + ["--batches", "1,2", "--contexts", "70", "--steps", "3", "--warmup", "1"])
+    assert [(o["batch"], o["context"]) for o in out] == [(1, 70), (2, 70)]
+
+
+def test_nll_tool(tmp_path):
+    ids = [(7 * i + 3) % 500 for i in range(150)]
+    p = tmp_path / "ids.json"
+    p.write_text(json.dumps(ids))
+    out = run_tool(nll, BASE + ["--ids-file", str(p), "--window", "64"])[0]
+    assert out["tokens"] == 149 and out["ppl"] > 1.0
+
+
+def test_mtp_bench_and_stats():
+    out = run_tool(mtp_bench, BASE + ["--mtp", "2", "--context", "80", "--steps", "4", "--warmup", "1"])[0]
+    assert out["drafts"] == 2 and out["sequence_steps"] == 8 and 1.0 <= out["accept_length"] <= 3.0
+    s = MtpStats(3)
+    s.record([[1, 2, 3, 4], [5], [6, 7]])
+    assert s.accept_length == pytest.approx(7 / 3) and s.per_position_rates() == [pytest.approx(2 / 3), 0.5, 1.0]
+    assert s.summary()["histogram"] == {"1": 1, "2": 1, "4": 1}
+
+
+def test_dense_family_through_cli():
+    out = run_tool(prefill_bench, ["--cpu", "--random-init", "qwen35-tiny", "--no-cuda-graph", "--batch-size", "2", "--chunk-size", "64",
+                                   "--max-pages", "32", "--contexts", "90"])
+    assert out[0]["context"] == 90
+
+
+def test_registry_checks(tmp_path):
+    (tmp_path / "config.json").write_text(json.dumps({"model_type": "qwen3"}))
+    mt, reg, _ = registry.inspect_model(str(tmp_path))
+    assert mt == "qwen3" and not reg.mtp
+    with pytest.raises(ValueError, match="does not support --cp"):
+        registry.inspect_model(str(tmp_path), cp=True)
+    with pytest.raises(ValueError, match="does not support --mtp"):
+        registry.inspect_model(str(tmp_path), mtp=3)
+    (tmp_path / "config.json").write_text(json.dumps({"model_type": "llama"}))
+    with pytest.raises(ValueError, match="unsupported model_type"):
+        registry.inspect_model(str(tmp_path))
+
+
+def test_model_path_resolution(tmp_path, monkeypatch):
+    monkeypatch.setenv("HF_HOME", str(tmp_path))
+    with pytest.raises(ModelNotFoundError):
+        resolve_model_path("org/name")
+    base = tmp_path / "hub" / "models--org--name"
+    (base / "refs").mkdir(parents=True)
+    (base / "refs" / "main").write_text("abc123\n")
+    with pytest.raises(ModelNotFoundError, match="snapshot"):
+        resolve_model_path("org/name")
+    snap = base / "snapshots" / "abc123"
+    snap.mkdir(parents=True)
+    assert resolve_model_path("org/name") == str(snap)
+    assert resolve_model_path(str(snap)) == str(snap)
+    with pytest.raises(FileNotFoundError):
+        list_safetensors_shards(str(snap))
+    (snap / "b.safetensors").write_bytes(b"")
+    (snap / "a.safetensors").write_bytes(b"")
+    assert [os.path.basename(p) for p in list_safetensors_shards(str(snap))] == ["a.safetensors", "b.safetensors"]
+    (snap / "model.safetensors.index.json").write_text(json.dumps({"weight_map": {"x": "b.safetensors", "y": "b.safetensors", "z": "a.safetensors"}}))
+    assert [os.path.basename(p) for p in list_safetensors_shards(str(snap))] == ["b.safetensors", "a.safetensors"]

@@ -42,14 +42,15 @@ def test_kda_scan():
     h, dk, dv, lens = 2, 128, 128, [9, 20]
     T = sum(lens)
     qkv = (torch.randn(T, h * (2 * dk + dv), generator=g) * 0.3).to(torch.bfloat16)
-    gl = (-torch.rand(T, h, dk, generator=g)).to(torch.bfloat16)
+    forget = torch.randn(T, h, dk, generator=g).to(torch.bfloat16)
     b = torch.randn(T, h, generator=g).to(torch.bfloat16)
+    A_log, dt_bias = torch.randn(h, generator=g) * 0.3, torch.randn(h, dk, generator=g) * 0.2
     state = torch.zeros(2, h, dk, dv)
     ind = torch.tensor([0, 9, 29], dtype=torch.int32)
     sidx = torch.tensor([1, 0], dtype=torch.int32)
     s_cpu, s_gpu = state.clone(), state.clone().cuda()
-    want = RC.kda_scan(qkv, gl, b, s_cpu, ind, sidx, h, dk, dv)
-    got = RC.kda_scan(qkv.cuda(), gl.cuda(), b.cuda(), s_gpu, ind.cuda(), sidx.cuda(), h, dk, dv)
+    want = RC.kda_scan(qkv, forget, b, A_log, dt_bias, s_cpu, ind, sidx, h, dk, dv, -5.0)
+    got = RC.kda_scan(qkv.cuda(), forget.cuda(), b.cuda(), A_log.cuda(), dt_bias.cuda(), s_gpu, ind.cuda(), sidx.cuda(), h, dk, dv, -5.0)
     assert rel_err(got, want) < 2e-2
     assert rel_err(s_gpu, s_cpu) < 2e-3
 
@@ -81,15 +82,19 @@ def test_rmsnorm_gated(sig):
 
 def test_mhc():
     g = gen(5)
-    T, n, H = 6, 4, 512
-    streams = torch.randn(T, n, H, generator=g)
-    mix, cw, ew = torch.randn(T, n, n, generator=g), torch.randn(T, n, generator=g), torch.randn(T, n, generator=g)
-    mixed_c, x_c = RC.mhc_pre(streams, mix, cw)
-    mixed_g, x_g = RC.mhc_pre(streams.cuda(), mix.cuda(), cw.cuda())
-    assert rel_err(mixed_g, mixed_c) < 1e-4 and rel_err(x_g, x_c) < 1e-2
+    T, H = 6, 512
+    x = torch.randn(T, 4, H, generator=g).to(torch.bfloat16)
+    fn = (torch.randn(24, 4 * H, generator=g) * 0.05).to(torch.bfloat16)
+    base, scale = torch.randn(24, generator=g) * 0.5, torch.tensor([0.7, 1.3, 0.9])
+    c_c, p_c, m_c = RC.mhc_pre(x, fn, base, scale, 1e-6, 1e-6, 20)
+    c_g, p_g, m_g = RC.mhc_pre(x.cuda(), fn.cuda(), base.cuda(), scale.cuda(), 1e-6, 1e-6, 20)
+    assert rel_err(c_g, c_c) < 1e-2 and rel_err(p_g, p_c) < 1e-3 and rel_err(m_g, m_c) < 1e-3
+    # the mixing matrix is (close to) doubly stochastic
+    assert (m_c.sum(-2) - 1).abs().max() < 1e-3
     y = torch.randn(T, H, generator=g).to(torch.bfloat16)
-    assert rel_err(RC.mhc_post(mixed_c.cuda(), y.cuda(), ew.cuda()), RC.mhc_post(mixed_c, y, ew)) < 1e-5
-    assert rel_err(RC.mhc_streams_mean(streams.cuda()), RC.mhc_streams_mean(streams)) < 1e-2
+    assert rel_err(RC.mhc_post(x.cuda(), y.cuda(), p_c.cuda(), m_c.cuda()), RC.mhc_post(x, y, p_c, m_c)) < 1e-2
+    assert rel_err(RC.mhc_streams(x.cuda(), False), RC.mhc_streams(x, False)) < 1e-2
+    assert torch.equal(RC.mhc_streams(y.cuda(), True).cpu(), RC.mhc_streams(y, True))
 
 
 def _paged_setup(g, B, lens, n_kv, hd, page=64):
