@@ -68,7 +68,7 @@ def _context(args) -> ParallelContext:
 def _random_model(spec: str, ctx: ParallelContext, mtp: int):
     from ..parallel.fused import make_comm
     dtype = torch.bfloat16 if ctx.device.type == "cuda" else torch.float32
-    tp_world = 1 if ctx.cp else ctx.world
+    tp_world = ctx.world          # weights stay tensor-parallel under context parallelism too
     tp_rank = ctx.rank if tp_world > 1 else 0
     if spec.startswith("qwen"):
         from ..models.dense import DenseConfig, DenseModel, random_dense_model

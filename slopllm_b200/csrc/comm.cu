@@ -20,8 +20,8 @@
 #include <cstring>
 
 struct RecvCtx {
-    const float* buf;          // this rank's receive buffer [world][slot_rows][row_len]
-    const uint32_t* flags;     // this rank's flag array [world]
+    const uint2* buf;          // this rank's receive buffer [world][slot_rows][row_len] of {value bits, tag}
+    const uint32_t* flags;     // unused by the tagged protocol
     uint32_t* epoch;           // completed collectives on this buffer (incremented here)
     uint32_t* done_counter;    // consumer blocks that have finished
     int* status;               // [4] error record
@@ -29,7 +29,28 @@ struct RecvCtx {
     uint32_t max_spins;
 };
 
-// One block per token row.  H % 4 == 0, H <= 16384.
+// Two adjacent tagged words (16 bytes): poll until both carry `target`.  Gives up after max_spins polls and
+// records where (the values seen last are used, the host reads the status word after the step).
+__device__ __forceinline__ void ll_load2(const uint2* p, uint32_t target, uint32_t max_spins, int* status, float& a, float& b) {
+    uint4 v;
+    for (uint32_t i = 0;; ++i) {
+        asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+        if (v.y == target && v.w == target) break;
+        if (i >= max_spins) {
+            if (status != nullptr && atomicCAS(status, 0, 1) == 0) {
+                status[1] = 1;
+                status[2] = (int)target;
+                status[3] = (int)v.y;
+            }
+            break;
+        }
+        if (i > 256) __nanosleep(64);
+    }
+    a = __uint_as_float(v.x);
+    b = __uint_as_float(v.z);
+}
+
+// One block per token row.  H % 4 == 0, H <= 16384.  Sums the ranks' slots in rank order (deterministic).
 __global__ void __launch_bounds__(1024) ar_add_rmsnorm_kernel(RecvCtx c, bf16* __restrict__ out, float* __restrict__ res_out,
                                                               const float* __restrict__ res_in, const bf16* __restrict__ w,
                                                               int H, float eps) {
@@ -37,8 +58,6 @@ __global__ void __launch_bounds__(1024) ar_add_rmsnorm_kernel(RecvCtx c, bf16* _
     __shared__ float scratch[33];
     const int t = blockIdx.x, nt = blockDim.x, n4 = H / 4;
     const uint32_t target = *c.epoch + 1u;
-    if (threadIdx.x < c.world) wait_flag_geq(c.flags + threadIdx.x, target, c.max_spins, c.status, 1);
-    __syncthreads();
     float4 v[4];
     float ss = 0.f;
 #pragma unroll
@@ -47,9 +66,11 @@ __global__ void __launch_bounds__(1024) ar_add_rmsnorm_kernel(RecvCtx c, bf16* _
         if (i < n4) {
             float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
             for (int r = 0; r < c.world; ++r) {
-                // ld.volatile-equivalent: the data was written by other GPUs; the acquire on the flag orders it
-                const float4 p = __ldcg(reinterpret_cast<const float4*>(c.buf + ((size_t)r * c.slot_rows + t) * c.row_len) + i);
-                a.x += p.x; a.y += p.y; a.z += p.z; a.w += p.w;
+                const uint2* src = c.buf + ((size_t)r * c.slot_rows + t) * c.row_len + 4 * i;
+                float p0, p1, p2, p3;
+                ll_load2(src, target, c.max_spins, c.status, p0, p1);
+                ll_load2(src + 2, target, c.max_spins, c.status, p2, p3);
+                a.x += p0; a.y += p1; a.z += p2; a.w += p3;
             }
             if (res_in != nullptr) {
                 const float4 r = reinterpret_cast<const float4*>(res_in + (size_t)t * H)[i];
@@ -103,12 +124,12 @@ SL_API int sl_ar_add_rmsnorm(const RecvCtx* c, void* out, void* res_out, const v
 __global__ void push_rows_kernel(PushCtx c, const float* __restrict__ x, int T, int N) {
     pdl_grid_sync();
     const size_t total = (size_t)T * N;
+    const uint32_t tag = push_tag(c);
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const int row = (int)(i / N), col = (int)(i % N);
         const float v = x[i];
-        for (int p = 0; p < c.world; ++p) *push_dst(c, p, row, col) = v;
+        push_store_all(c, row, col, v, tag);
     }
-    push_finish(c, gridDim.x);
 }
 
 SL_API int sl_push_rows(const PushCtx* c, const void* x, int T, int N, cudaStream_t s) {
@@ -179,7 +200,9 @@ __global__ void cp_merge_push_kernel(CpPushCtx c, const float* __restrict__ o, c
     if (threadIdx.x == 0) c.lse_stage[owner][((size_t)c.rank * c.Tmax + t) * c.hl + hh] = lse[(size_t)t * c.h + head];
     __syncthreads();
     if (threadIdx.x == 0) {
-        __threadfence_system();
+        // device-scope fence here, system-scope fence once in the last block: the counter chains the blocks' stores
+        // before the flag stores (a system fence per block costs microseconds each)
+        __threadfence();
         const unsigned prev = atomicAdd(c.block_counter, 1u);
         if (prev == gridDim.x * gridDim.y - 1) {
             *c.block_counter = 0;
@@ -232,7 +255,9 @@ __global__ void gather_push_kernel(GatherPushCtx c, const uint4* __restrict__ sr
     }
     __syncthreads();
     if (threadIdx.x == 0) {
-        __threadfence_system();
+        // device-scope fence here, system-scope fence once in the last block: the counter chains the blocks' stores
+        // before the flag stores (a system fence per block costs microseconds each)
+        __threadfence();
         const unsigned prev = atomicAdd(c.block_counter, 1u);
         if (prev == gridDim.x - 1) {
             *c.block_counter = 0;

@@ -119,6 +119,7 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
         if (!ok && lane == 0) atomicExch(err, 3);
         tc::fence_after_sync();
         const int row = m0 + q * 32 + lane;
+        const uint32_t ptag = use_push ? push_tag(push) : 0u;
         if (ok) {
 #pragma unroll 1
             for (int c = 0; c < BN / 32; ++c) {
@@ -132,7 +133,7 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
                     if (row < M) {
                         for (int i = 0; i < 32 && col + i < N; ++i) {
                             if (use_push) {
-                                for (int pr = 0; pr < push.world; ++pr) *push_dst(push, pr, col + i, row) = __uint_as_float(r[i]);
+                                push_store_all(push, col + i, row, __uint_as_float(r[i]), ptag);
                             } else if (out_f32) ((float*)C)[(size_t)(col + i) * ldc + row] = __uint_as_float(r[i]);
                             else ((bf16*)C)[(size_t)(col + i) * ldc + row] = __float2bfloat16(__uint_as_float(r[i]));
                         }
@@ -173,7 +174,6 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
         tc::fence_after_sync();
         tc::tmem_dealloc(tmem_base, BN);
     }
-    if (use_push) push_finish(push, gridDim.x * gridDim.y);
 }
 
 template <int BN>

@@ -439,11 +439,10 @@ __global__ void __launch_bounds__(256) moe_down_kernel(MoeDownParams p, int use_
         for (int w = 0; w < 8; ++w) v += red[w][lane];
         const size_t o = (size_t)t * p.H + n0 + lane;
         if (use_push) {
-            for (int pr = 0; pr < push.world; ++pr) *push_dst(push, pr, t, n0 + lane) = v;
+            push_store_all(push, t, n0 + lane, v, push_tag(push));
         } else if (p.out_f32) ((float*)p.out)[o] = p.accumulate ? ((float*)p.out)[o] + v : v;
         else ((bf16*)p.out)[o] = __float2bfloat16(v);
     }
-    if (use_push) push_finish(push, gridDim.x * gridDim.y);
 }
 
 SL_API int sl_moe_down(const MoeDownParams* p, cudaStream_t s) {

@@ -182,6 +182,7 @@ __global__ void __launch_bounds__(256) linear_nvfp4_mma_kernel(void* __restrict_
         }
     __syncthreads();
     const float gs = gscale ? *gscale : 1.f;
+    const uint32_t ptag = use_push ? push_tag(push) : 0u;
     for (int i = threadIdx.x; i < tiles_per_block * TOK * ROWS; i += blockDim.x) {
         const int tl = i / (TOK * ROWS), rem = i % (TOK * ROWS), tok = rem / ROWS, r = rem % ROWS;
         const int n = (blockIdx.x * tiles_per_block + tl) * ROWS + r;
@@ -191,12 +192,11 @@ __global__ void __launch_bounds__(256) linear_nvfp4_mma_kernel(void* __restrict_
             v *= gs;
             if (use_push) {
                 // fused all-reduce, producer side: the partial goes to every rank's receive slot
-                for (int pr = 0; pr < push.world; ++pr) *push_dst(push, pr, tok, n) = v;
+                push_store_all(push, tok, n, v, ptag);
             } else if (out_f32) ((float*)y)[(size_t)tok * N + n] = v;
             else ((bf16*)y)[(size_t)tok * N + n] = __float2bfloat16(v);
         }
     }
-    if (use_push) push_finish(push, gridDim.x);
 }
 
 template <int MT, int NT>
@@ -560,6 +560,7 @@ __global__ void moe_route_reduce_kernel(const float* __restrict__ y_route, const
                                         float* __restrict__ out, int use_push, PushCtx push) {
     pdl_grid_sync();
     const int t = blockIdx.y;
+    const uint32_t ptag = use_push ? push_tag(push) : 0u;
     for (int n = blockIdx.x * blockDim.x + threadIdx.x; n < H; n += gridDim.x * blockDim.x) {
         float v = 0.f;
         for (int j = 0; j < top_k; ++j) {
@@ -568,12 +569,11 @@ __global__ void moe_route_reduce_kernel(const float* __restrict__ y_route, const
         }
         if (has_shared) v += y_route[(size_t)(T * top_k + t) * H + n];
         if (use_push) {
-            for (int pr = 0; pr < push.world; ++pr) *push_dst(push, pr, t, n) = v;
+            push_store_all(push, t, n, v, ptag);
         } else {
             out[(size_t)t * H + n] = v;
         }
     }
-    if (use_push) push_finish(push, gridDim.x * gridDim.y);
 }
 
 int pick_ksplit(int K, int min_groups_per_warp) {

@@ -25,7 +25,7 @@ def _load_glm_moe_dsa(model_dir: str, ctx: ParallelContext, mtp: int = 0):
     from ..parallel.fused import make_comm
     from .glm_moe_dsa import GlmMoeDsaModel
     dtype = torch.bfloat16 if ctx.device.type == "cuda" else torch.float32
-    tp_world = 1 if ctx.cp else ctx.world
+    tp_world = ctx.world          # weights stay tensor-parallel under context parallelism too
     cfg, w = load_model(model_dir, ctx.device, dtype, ctx.rank if tp_world > 1 else 0, tp_world, ep=ctx.ep, with_mtp=mtp > 0)
     return cfg, GlmMoeDsaModel(cfg, w, ctx, comm=make_comm(ctx, cfg))
 

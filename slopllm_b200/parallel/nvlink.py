@@ -156,7 +156,7 @@ class SymmetricRegion:
             return o
         lay = {"flags": [take(4 * MAX_RANKS * 2) for _ in range(8)], "data": []}
         for _ in range(cls.NUM_BUFS):
-            lay["data"].append(take(world * slot_rows * row_len * 4))
+            lay["data"].append(take(world * slot_rows * row_len * 8))      # {fp32 value, tag} per element
         lay["gather"] = take(world * gather_bytes) if gather_bytes else 0
         if cp_shape is not None:
             Tmax, h, R = cp_shape

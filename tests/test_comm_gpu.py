@@ -104,6 +104,25 @@ def test_wait_times_out_cleanly():
     assert float((torch.ones(4, device=DEV) * 2).sum()) == 8.0
 
 
+def test_tagged_consumer_times_out_cleanly():
+    """The all-reduce consumer polls tagged words; when no producer ever writes them it gives up after
+    its poll budget, records the timeout in the status block and finishes, leaving the context usable."""
+    import ctypes as C
+    from slopllm_b200.ops import native as N
+    from slopllm_b200.parallel.nvlink import CollectiveTimeout
+    H, T = 256, 2
+    region = _regions(2, 8, H, wait_spins=300)[0]
+    out = torch.empty(T, H, dtype=torch.bfloat16, device=DEV)
+    res = torch.empty(T, H, dtype=torch.float32, device=DEV)
+    w = torch.ones(H, dtype=torch.bfloat16, device=DEV)
+    N.call("sl_ar_add_rmsnorm", C.byref(region.recv_ctx[0]), out.data_ptr(), res.data_ptr(), 0, w.data_ptr(), T, H, 1e-5, N.stream())
+    torch.cuda.synchronize()
+    with pytest.raises(CollectiveTimeout):
+        region.check_status()
+    region.check_status()
+    assert float((torch.ones(4, device=DEV) * 2).sum()) == 8.0
+
+
 def test_cp_merge_push_emulated():
     from slopllm_b200.ops.cuda_ops import CudaOps
     from slopllm_b200.parallel.dist import ParallelContext
