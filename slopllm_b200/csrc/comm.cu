@@ -29,49 +29,75 @@ struct RecvCtx {
     uint32_t max_spins;
 };
 
-// Two adjacent tagged words (16 bytes): poll until both carry `target`.  Gives up after max_spins polls and
-// records where (the values seen last are used, the host reads the status word after the step).
-__device__ __forceinline__ void ll_load2(const uint2* p, uint32_t target, uint32_t max_spins, int* status, float& a, float& b) {
+__device__ __forceinline__ uint4 ld_volatile_16(const void* p) {
     uint4 v;
-    for (uint32_t i = 0;; ++i) {
-        asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
-        if (v.y == target && v.w == target) break;
-        if (i >= max_spins) {
-            if (status != nullptr && atomicCAS(status, 0, 1) == 0) {
-                status[1] = 1;
-                status[2] = (int)target;
-                status[3] = (int)v.y;
+    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+
+// Four consecutive tagged words of every rank's slot (element columns 4i .. 4i+3 of row t): all loads of a poll
+// round are issued before any tag is tested, so a round costs one memory latency, not one per rank.  Rounds repeat
+// until every tag equals `target`; after max_spins rounds the timeout is recorded in `status` and the last values
+// seen are used (the host reads the status word after the step).  The sum runs in rank order (deterministic).
+__device__ __forceinline__ float4 ll_gather_sum(const RecvCtx& c, int t, int i, uint32_t target) {
+    uint4 lo[SL_MAX_RANKS], hi[SL_MAX_RANKS];
+    for (uint32_t spin = 0;; ++spin) {
+#pragma unroll
+        for (int r = 0; r < SL_MAX_RANKS; ++r) {
+            if (r < c.world) {
+                const uint2* src = c.buf + ((size_t)r * c.slot_rows + t) * c.row_len + 4 * i;
+                lo[r] = ld_volatile_16(src);
+                hi[r] = ld_volatile_16(src + 2);
+            }
+        }
+        bool ok = true;
+        uint32_t seen = target;
+#pragma unroll
+        for (int r = 0; r < SL_MAX_RANKS; ++r) {
+            if (r < c.world) {
+                if (lo[r].y != target) { ok = false; seen = lo[r].y; }
+                if (lo[r].w != target) { ok = false; seen = lo[r].w; }
+                if (hi[r].y != target) { ok = false; seen = hi[r].y; }
+                if (hi[r].w != target) { ok = false; seen = hi[r].w; }
+            }
+        }
+        if (ok) break;
+        if (spin >= c.max_spins) {
+            if (c.status != nullptr && atomicCAS(c.status, 0, 1) == 0) {
+                c.status[1] = 1;
+                c.status[2] = (int)target;
+                c.status[3] = (int)seen;
             }
             break;
         }
-        if (i > 256) __nanosleep(64);
+        if (spin > 64) __nanosleep(64);
     }
-    a = __uint_as_float(v.x);
-    b = __uint_as_float(v.z);
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int r = 0; r < SL_MAX_RANKS; ++r) {
+        if (r < c.world) {
+            a.x += __uint_as_float(lo[r].x); a.y += __uint_as_float(lo[r].z);
+            a.z += __uint_as_float(hi[r].x); a.w += __uint_as_float(hi[r].z);
+        }
+    }
+    return a;
 }
 
 // One block per token row.  H % 4 == 0, H <= 16384.  Sums the ranks' slots in rank order (deterministic).
-__global__ void __launch_bounds__(1024) ar_add_rmsnorm_kernel(RecvCtx c, bf16* __restrict__ out, float* __restrict__ res_out,
+__global__ void __launch_bounds__(512) ar_add_rmsnorm_kernel(RecvCtx c, bf16* __restrict__ out, float* __restrict__ res_out,
                                                               const float* __restrict__ res_in, const bf16* __restrict__ w,
                                                               int H, float eps) {
     pdl_grid_sync();
     __shared__ float scratch[33];
     const int t = blockIdx.x, nt = blockDim.x, n4 = H / 4;
     const uint32_t target = *c.epoch + 1u;
-    float4 v[4];
+    float4 v[8];
     float ss = 0.f;
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
+    for (int q = 0; q < 8; ++q) {
         const int i = threadIdx.x + q * nt;
         if (i < n4) {
-            float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (int r = 0; r < c.world; ++r) {
-                const uint2* src = c.buf + ((size_t)r * c.slot_rows + t) * c.row_len + 4 * i;
-                float p0, p1, p2, p3;
-                ll_load2(src, target, c.max_spins, c.status, p0, p1);
-                ll_load2(src + 2, target, c.max_spins, c.status, p2, p3);
-                a.x += p0; a.y += p1; a.z += p2; a.w += p3;
-            }
+            float4 a = ll_gather_sum(c, t, i, target);
             if (res_in != nullptr) {
                 const float4 r = reinterpret_cast<const float4*>(res_in + (size_t)t * H)[i];
                 a.x += r.x; a.y += r.y; a.z += r.z; a.w += r.w;
@@ -83,7 +109,7 @@ __global__ void __launch_bounds__(1024) ar_add_rmsnorm_kernel(RecvCtx c, bf16* _
     ss = block_sum(ss, scratch);
     const float inv = rsqrtf(ss / (float)H + eps);
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
+    for (int q = 0; q < 8; ++q) {
         const int i = threadIdx.x + q * nt;
         if (i < n4) {
             if (res_out != nullptr) reinterpret_cast<float4*>(res_out + (size_t)t * H)[i] = v[q];
@@ -112,9 +138,9 @@ SL_API int sl_ar_add_rmsnorm(const RecvCtx* c, void* out, void* res_out, const v
                              float eps, cudaStream_t s) {
     if (T == 0) return 0;
     if (H % 4 != 0 || H > 16384 || c->world > SL_MAX_RANKS) return -1;
-    int threads = ((H / 4 + 3) / 4 + 31) / 32 * 32;
+    int threads = ((H / 4 + 3) / 4 + 31) / 32 * 32;           // four float4 per thread up to H = 8192, eight beyond
     if (threads < 128) threads = 128;
-    if (threads > 1024) threads = 1024;
+    if (threads > 512) threads = 512;
     sl_launch(ar_add_rmsnorm_kernel, T, threads, 0, s, *c, (bf16*)out, (float*)res_out, (const float*)res_in, (const bf16*)w, H, eps);
     return SL_LAUNCH_CHECK();
 }

@@ -284,9 +284,15 @@ SL_API int sl_linear_smallT_bf16_tcgen05_push(const void* x, const void* W, int 
 // C [M, N] row-major.  Replaces the reference's sort + `grouped_mma_kernel` (`csrc/glm_mma_moe.cu:110-460`).
 SL_API int sl_grouped_gemm_bf16_tcgen05(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
                                         int out_f32, int groups, const void* tiles, const void* num_tiles, int max_tiles,
-                                        void* err, cudaStream_t s) {
+                                        void* err, int bn, cudaStream_t s) {
     if (M <= 0 || N <= 0 || K <= 0 || max_tiles <= 0) return 0;
     if (K % 8 != 0 || lda % 8 != 0 || ldb % 8 != 0 || (out_f32 ? ldc % 4 : ldc % 8) != 0) return -1;
+    // `bn` (128 or 256) is the column width the tile table was built with; wide tiles halve the number of CTAs
+    // when the reduction is short and the per-tile set-up dominates
+    if (bn == 256)
+        return launch<256>(A, B, C, M, N, K, lda, ldb, ldc, out_f32, 0, (int*)err, s, nullptr, (const int4*)tiles,
+                           (const int*)num_tiles, max_tiles, groups * N);
+    if (bn != 128) return -1;
     return launch<128>(A, B, C, M, N, K, lda, ldb, ldc, out_f32, 0, (int*)err, s, nullptr, (const int4*)tiles,
                        (const int*)num_tiles, max_tiles, groups * N);
 }
@@ -294,11 +300,11 @@ SL_API int sl_grouped_gemm_bf16_tcgen05(const void* A, const void* B, void* C, i
 // offsets [groups + 1] (device, int32) -> tile table.  One thread per group enumerates its (row tile, column tile) pairs
 // at a position given by a prefix sum over the groups' tile counts.
 __global__ void build_group_tiles_kernel(int4* __restrict__ tiles, int* __restrict__ num_tiles, const int* __restrict__ offsets,
-                                         int groups, int N, int max_tiles) {
+                                         int groups, int N, int max_tiles, int bn) {
     pdl_grid_sync();
     __shared__ int base[1025];
     const int g = threadIdx.x;
-    const int ncol = (N + 127) / 128;
+    const int ncol = (N + bn - 1) / bn;
     int mine = 0;
     if (g < groups) mine = ((offsets[g + 1] - offsets[g] + 127) / 128) * ncol;
     base[g + 1] = mine;
@@ -311,13 +317,14 @@ __global__ void build_group_tiles_kernel(int4* __restrict__ tiles, int* __restri
         const int r0 = offsets[g], r1 = offsets[g + 1];
         for (int m = r0; m < r1; m += 128)
             for (int c = 0; c < ncol; ++c, ++at)
-                if (at < max_tiles) tiles[at] = make_int4(m, r1, g * N, c * 128);
+                if (at < max_tiles) tiles[at] = make_int4(m, r1, g * N, c * bn);
     }
     if (g == 0) *num_tiles = min(base[groups], max_tiles);
 }
 
-SL_API int sl_build_group_tiles(void* tiles, void* num_tiles, const void* offsets, int groups, int N, int max_tiles, cudaStream_t s) {
-    if (groups <= 0 || groups > 1024) return -1;
-    sl_launch(build_group_tiles_kernel, 1, 1024, 0, s, (int4*)tiles, (int*)num_tiles, (const int*)offsets, groups, N, max_tiles);
+SL_API int sl_build_group_tiles(void* tiles, void* num_tiles, const void* offsets, int groups, int N, int max_tiles, int bn,
+                                cudaStream_t s) {
+    if (groups <= 0 || groups > 1024 || (bn != 128 && bn != 256)) return -1;
+    sl_launch(build_group_tiles_kernel, 1, 1024, 0, s, (int4*)tiles, (int*)num_tiles, (const int*)offsets, groups, N, max_tiles, bn);
     return (int)cudaGetLastError();
 }

@@ -518,24 +518,25 @@ SL_API int sl_nvfp4_dequant_bf16(void* out, const void* Wp, const void* S, const
 
 // out[tok[r], :] += w[r] * y[r, :]   (weighted scatter of expert-sorted rows back to token order; fp32 atomics-free
 // because each block owns one output token: rows of a token are found through `token_rows` [T, k] indices)
-__global__ void moe_unsort_reduce_kernel(float* __restrict__ out, const float* __restrict__ y, const int* __restrict__ rows_of,
-                                         const float* __restrict__ wts, int k, int H, int accumulate) {
+__global__ void moe_unsort_reduce_kernel(float* __restrict__ out, const void* __restrict__ y, const int* __restrict__ rows_of,
+                                         const float* __restrict__ wts, int k, int H, int accumulate, int y_bf16) {
     pdl_grid_sync();
     const int t = blockIdx.y;
     for (int n = blockIdx.x * blockDim.x + threadIdx.x; n < H; n += gridDim.x * blockDim.x) {
         float v = accumulate ? out[(size_t)t * H + n] : 0.f;
         for (int j = 0; j < k; ++j) {
             const int r = rows_of[t * k + j];
-            if (r >= 0) v += wts[t * k + j] * y[(size_t)r * H + n];
+            if (r >= 0)
+                v += wts[t * k + j] * (y_bf16 ? __bfloat162float(((const bf16*)y)[(size_t)r * H + n]) : ((const float*)y)[(size_t)r * H + n]);
         }
         out[(size_t)t * H + n] = v;
     }
 }
 
 SL_API int sl_moe_unsort_reduce(void* out, const void* y, const void* rows_of, const void* wts, int T, int k, int H, int accumulate,
-                                cudaStream_t s) {
+                                int y_bf16, cudaStream_t s) {
     if (T == 0) return 0;
-    sl_launch(moe_unsort_reduce_kernel, dim3((H + 255) / 256, T), 256, 0, s, (float*)out, (const float*)y, (const int*)rows_of,
-                                                                     (const float*)wts, k, H, accumulate);
+    sl_launch(moe_unsort_reduce_kernel, dim3((H + 255) / 256, T), 256, 0, s, (float*)out, y, (const int*)rows_of,
+                                                                     (const float*)wts, k, H, accumulate, y_bf16);
     return SL_LAUNCH_CHECK();
 }

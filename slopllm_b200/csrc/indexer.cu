@@ -172,6 +172,9 @@ struct TopkSelectParams {
     int* slots; int* lengths;
     const int* page_table; const int* batch_idx;
     int pt_stride, page_size;
+    // plain mode (n_fixed > 0): every row has exactly n_fixed candidates and the output is the candidate index
+    // (used to merge the ranks' candidate lists under context parallelism); `positions` is not read
+    int n_fixed;
 };
 
 // Radix-descent helper: given hist[256] of the current digit among the candidates, find the bin
@@ -219,8 +222,8 @@ __global__ void __launch_bounds__(1024) topk_select_kernel(TopkSelectParams p) {
     __shared__ int s_base, s_eq_used;
     constexpr int ITEMS = 8;
     const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = blockDim.x >> 5;
-    const int pos = p.positions[t];
-    const int n = local_visible(pos, p.cp_world, p.cp_rank);
+    const int pos = p.n_fixed > 0 ? p.n_fixed - 1 : p.positions[t];
+    const int n = p.n_fixed > 0 ? p.n_fixed : local_visible(pos, p.cp_world, p.cp_rank);
     int* opos = p.out_pos + (size_t)t * p.top_k;
     float* osc = p.out_score + (size_t)t * p.top_k;
     int* oslot = p.slots != nullptr ? p.slots + (size_t)t * p.top_k : nullptr;

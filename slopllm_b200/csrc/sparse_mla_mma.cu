@@ -55,7 +55,7 @@ __global__ void __launch_bounds__(256) sparse_mla_mma_kernel(Params p) {
     float* row_m = wsum + 8 * HB;                             // [16] running max
     float* row_l = row_m + HB;                                // [16] running sum
     float* row_a = row_l + HB;                                // [16] rescale of this chunk
-    int* s_slots = reinterpret_cast<int*>(row_a + HB);        // [64] slots of the current chunk
+    int* s_slots = reinterpret_cast<int*>(row_a + HB);        // [2][64] slots of the current / next chunk
 
     const int split = blockIdx.x, hg = blockIdx.y, t = blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -91,28 +91,39 @@ __global__ void __launch_bounds__(256) sparse_mla_mma_kernel(Params p) {
 #pragma unroll
     for (int i = 0; i < 8; ++i) oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.f;
 
+    // 16-byte gather path: the rows of chunk c+1 are loaded into registers while chunk c is multiplied, so the
+    // gather latency overlaps the tensor-core phases (a thread's loads are all issued before their first use).
+    constexpr int MAXLD = 12;
+    uint4 buf[MAXLD];
+    float scl[MAXLD];
+    const int chunks = row_bytes / 16;
+    auto issue_loads = [&](int c0n, const int* sl) {
+        const int kcn = min(KC, j_end - c0n), total = kcn * chunks;
+#pragma unroll
+        for (int n = 0; n < MAXLD; ++n) {
+            const int i = tid + n * 256;
+            if (i < total) {
+                const int j = i / chunks, byte = (i % chunks) * 16;
+                const uint8_t* row = p.kv_cache + (size_t)sl[j] * row_bytes;
+                buf[n] = ldg_nc_16(row + byte);
+                scl[n] = byte < p.R ? *reinterpret_cast<const float*>(row + p.R + 4 * (byte / p.group)) : 0.f;
+            }
+        }
+    };
+    int* s_slots2 = s_slots + KC;                               // second slot buffer (pipelined path)
+    if (vec16 && j_begin < j_end) {
+        if (tid < KC) s_slots[tid] = tid < min(KC, j_end - j_begin) ? slots[j_begin + tid] : 0;
+        __syncthreads();
+        issue_loads(j_begin, s_slots);
+    }
+    int parity = 0;
+
     for (int c0 = j_begin; c0 < j_end; c0 += KC) {
         const int kc = min(KC, j_end - c0);
         __syncthreads();
         // ---- gather + expand kc rows ----
-        if (tid < KC) s_slots[tid] = tid < kc ? slots[c0 + tid] : 0;
-        __syncthreads();
         if (vec16) {
-            // 16-byte chunks, all of a thread's loads issued before the first use
-            const int chunks = row_bytes / 16, total = kc * chunks;
-            constexpr int MAXLD = 12;
-            uint4 buf[MAXLD];
-            float scl[MAXLD];
-#pragma unroll
-            for (int n = 0; n < MAXLD; ++n) {
-                const int i = tid + n * 256;
-                if (i < total) {
-                    const int j = i / chunks, byte = (i % chunks) * 16;
-                    const uint8_t* row = p.kv_cache + (size_t)s_slots[j] * row_bytes;
-                    buf[n] = ldg_nc_16(row + byte);
-                    scl[n] = byte < p.R ? *reinterpret_cast<const float*>(row + p.R + 4 * (byte / p.group)) : 0.f;
-                }
-            }
+            const int total = kc * chunks;
 #pragma unroll
             for (int n = 0; n < MAXLD; ++n) {
                 const int i = tid + n * 256;
@@ -144,7 +155,16 @@ __global__ void __launch_bounds__(256) sparse_mla_mma_kernel(Params p) {
                     }
                 }
             }
-        } else
+            // slots of the next chunk, then its loads (in flight during this chunk's MMAs)
+            const int c0n = c0 + KC;
+            int* sl_next = parity ? s_slots : s_slots2;
+            if (c0n < j_end && tid < KC) sl_next[tid] = tid < min(KC, j_end - c0n) ? slots[c0n + tid] : 0;
+            __syncthreads();
+            if (c0n < j_end) issue_loads(c0n, sl_next);
+            parity ^= 1;
+        } else {
+        if (tid < KC) s_slots[tid] = tid < kc ? slots[c0 + tid] : 0;
+        __syncthreads();
         for (int i = tid; i < KC * words; i += blockDim.x) {
             const int j = i / words, wd = i % words, byte = wd * 4;
             if (j < kc) {
@@ -164,6 +184,7 @@ __global__ void __launch_bounds__(256) sparse_mla_mma_kernel(Params p) {
                     *reinterpret_cast<__half2*>(ks + j * DP + d) = __floats2half2_rn(f.x, f.y);
                 }
             }
+        }
         }
         // rows beyond kc contribute p = 0; keep them finite so that 0 * v stays 0
         for (int i = tid; i < (KC - kc) * (D / 2); i += blockDim.x) {
@@ -270,7 +291,7 @@ SL_API int sl_sparse_mla_split_mma(const void* params, int T, cudaStream_t s) {
     if (T == 0) return 0;
     if (p->R % 64 != 0 || p->R > 512 || (p->R + p->Dr) % 16 != 0 || p->Dr % 2 != 0 || p->group % 4 != 0) return -1;
     const int DP = p->R + p->Dr + 8;
-    const size_t smem = (size_t)(HB * DP + KC * DP + HB * 72) * sizeof(__half) + (size_t)(8 * HB * 2 + 3 * HB + KC) * sizeof(float);
+    const size_t smem = (size_t)(HB * DP + KC * DP + HB * 72) * sizeof(__half) + (size_t)(8 * HB * 2 + 3 * HB + 2 * KC) * sizeof(float);
     static bool attr = false;
     if (!attr) {
         cudaFuncSetAttribute(sparse_mla_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);

@@ -180,6 +180,13 @@ class CudaOps:
             rope_interleave=int(c.rope_interleave), idx_rope_interleave=int(c.indexer_rope_interleave),
             positions=st.positions.data_ptr(), idx_w=N.ptr(idx_w), q_pe_out=q_pe.data_ptr(), q8_out=N.ptr(q8),
             w_eff_out=N.ptr(w_eff))
+        if T > DECODE_MAX_T and n_slabs == 0:
+            # prefill: the absorb product is a plain batched GEMM (one per head): library bmm, as in the reference
+            # (`glm_bmm`, `csrc/glm_ops.cu`); the rotary / quantisation part keeps its own kernel
+            N.call("sl_q_post", C.byref(p), T, N.stream())
+            q_nope = qb[:, :hl * c.qk_head_dim].view(T, hl, c.qk_head_dim)[..., :c.qk_nope_head_dim]
+            q_abs = torch.bmm(q_nope.transpose(0, 1), lw.w_kn).transpose(0, 1).contiguous()
+            return q_abs, q_pe, q8, w_eff
         q_abs = torch.empty(T, hl, c.kv_lora_rank, dtype=torch.bfloat16, device=dev)
         N.call("sl_q_post_absorb", C.byref(p), q_abs.data_ptr(), lw.w_kn.data_ptr(), T, c.kv_lora_rank, N.stream())
         return q_abs, q_pe, q8, w_eff
@@ -216,6 +223,17 @@ class CudaOps:
             st.extra["fused_slots"] = (pos, slots, lengths)
         N.call("sl_topk_select", C.byref(tp), T, N.stream())
         return pos, score
+
+    def topk_select_plain(self, scores: torch.Tensor, k: int) -> torch.Tensor:
+        """Indices of the k largest entries of each row (ascending index order, ties to the lower index, -1 padded
+        when a row has fewer than k entries).  scores fp32 [T, n], row stride a multiple of 4 bytes."""
+        T, n = scores.shape
+        out = torch.empty(T, k, dtype=torch.int32, device=scores.device)
+        sc = torch.empty(T, k, dtype=torch.float32, device=scores.device)
+        tp = N.TopkSelectParams(scores=scores.data_ptr(), ld_scores=scores.stride(0), positions=0, top_k=k, cp_world=1, cp_rank=0,
+                                out_pos=out.data_ptr(), out_score=sc.data_ptr(), n_fixed=n)
+        N.call("sl_topk_select", C.byref(tp), T, N.stream())
+        return out
 
     def topk_to_slots(self, topk_pos, st, local_only: bool = False):
         fused = st.extra.pop("fused_slots", None)
@@ -282,6 +300,9 @@ class CudaOps:
         T, hl, Rr = o.shape
         Dv = w_v.shape[2]
         o = self._bf16(o).contiguous()
+        if T > DECODE_MAX_T:
+            # prefill: plain batched GEMM over the heads (library bmm; the reference uses cuBLAS strided-batched here too)
+            return torch.bmm(o.transpose(0, 1), w_v).transpose(0, 1).reshape(T, hl * Dv)
         out = torch.empty(T, hl * Dv, dtype=torch.bfloat16, device=o.device)
         N.call("sl_bmv", out.data_ptr(), o.data_ptr(), w_v.data_ptr(), T, hl, Rr, Dv, hl * Rr, Rr, 0, 0, N.stream())
         return out

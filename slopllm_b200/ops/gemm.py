@@ -47,13 +47,15 @@ def grouped_gemm(a: torch.Tensor, b_stack: torch.Tensor, offsets: torch.Tensor, 
     M, K = a.shape
     G, Nn, _ = b_stack.shape
     c = torch.empty(M, Nn, dtype=torch.float32 if out_f32 else torch.bfloat16, device=a.device)
-    ncol = (Nn + 127) // 128
+    # short reductions are dominated by the per-tile set-up and the output store: use 128 x 256 tiles there
+    bn = 256 if (K <= 1024 and Nn >= 1024) else 128
+    ncol = (Nn + bn - 1) // bn
     max_tiles = ((M + 127) // 128 + G) * ncol
     tiles = torch.empty(max_tiles, 4, dtype=torch.int32, device=a.device)
     ntiles = torch.empty(1, dtype=torch.int32, device=a.device)
-    N.call("sl_build_group_tiles", tiles.data_ptr(), ntiles.data_ptr(), offsets.data_ptr(), G, Nn, max_tiles, N.stream())
+    N.call("sl_build_group_tiles", tiles.data_ptr(), ntiles.data_ptr(), offsets.data_ptr(), G, Nn, max_tiles, bn, N.stream())
     N.call("sl_grouped_gemm_bf16_tcgen05", a.data_ptr(), b_stack.data_ptr(), c.data_ptr(), M, Nn, K, a.stride(0), K, c.stride(0),
-           int(out_f32), G, tiles.data_ptr(), ntiles.data_ptr(), max_tiles, tcgen05.error_flag(a.device).data_ptr(), N.stream())
+           int(out_f32), G, tiles.data_ptr(), ntiles.data_ptr(), max_tiles, tcgen05.error_flag(a.device).data_ptr(), bn, N.stream())
     return c
 
 
@@ -80,7 +82,7 @@ def moe_large(ops, x, experts, shared, ids, wts) -> torch.Tensor:
     M = xs.shape[0]
     per_expert = 3 * I * H * 2
     group = max(1, min(E, DEQUANT_BUDGET_BYTES // max(1, per_expert)))
-    y = torch.empty(M, H, dtype=torch.float32, device=dev)
+    y = torch.empty(M, H, dtype=torch.bfloat16, device=dev)     # per-route outputs; the weighted un-sort accumulates in fp32
     act = torch.empty(M, I, dtype=torch.bfloat16, device=dev)
     for g0 in range(0, E, group):
         g1 = min(E, g0 + group)
@@ -92,7 +94,7 @@ def moe_large(ops, x, experts, shared, ids, wts) -> torch.Tensor:
             w13, w2 = experts.w13[g0:g1], experts.w2[g0:g1]
         h = grouped_gemm(xs, w13, off, False)                                      # rows of other groups are left untouched
         N.call("sl_silu_mul", act.data_ptr(), h.data_ptr(), M, I, N.stream())
-        yg = grouped_gemm(act, w2, off, True)
+        yg = grouped_gemm(act, w2, off, False)
         if group >= E:
             y = yg
         else:                                                                      # keep only this group's rows
@@ -100,7 +102,7 @@ def moe_large(ops, x, experts, shared, ids, wts) -> torch.Tensor:
             y[lo:hi] = yg[lo:hi]
     out = torch.empty(T, H, dtype=torch.float32, device=dev)
     wts = wts.to(torch.float32).contiguous()
-    N.call("sl_moe_unsort_reduce", out.data_ptr(), y.data_ptr(), rows_of.data_ptr(), wts.data_ptr(), T, k, H, 0, N.stream())
+    N.call("sl_moe_unsort_reduce", out.data_ptr(), y.data_ptr(), rows_of.data_ptr(), wts.data_ptr(), T, k, H, 0, 1, N.stream())
     if shared is not None:
         if shared.is_nvfp4:
             w13 = dequant_bf16(shared.w13[0], shared.s13[0], shared.g13[0], g_per=2, split=shared.inter)

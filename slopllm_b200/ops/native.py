@@ -90,7 +90,7 @@ class IndexerScoreParams(C.Structure):
 class TopkSelectParams(C.Structure):
     _fields_ = [("scores", vp), ("ld_scores", i32), ("positions", vp), ("top_k", i32), ("cp_world", i32),
                 ("cp_rank", i32), ("out_pos", vp), ("out_score", vp), ("slots", vp), ("lengths", vp),
-                ("page_table", vp), ("batch_idx", vp), ("pt_stride", i32), ("page_size", i32)]
+                ("page_table", vp), ("batch_idx", vp), ("pt_stride", i32), ("page_size", i32), ("n_fixed", i32)]
 
 
 class SparseMlaParams(C.Structure):
@@ -179,10 +179,10 @@ _SIGS = {
     "sl_moe_grouped_mma": [C.POINTER(MoeGroupedArgs), vp, vp, vp],
     "sl_linear_nvfp4_mma": [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp],
     "sl_linear_smallT_bf16_tcgen05": [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp, vp, i32, vp],
-    "sl_grouped_gemm_bf16_tcgen05": [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, vp, vp, i32, vp, vp],
-    "sl_build_group_tiles": [vp, vp, vp, i32, i32, i32, vp],
+    "sl_grouped_gemm_bf16_tcgen05": [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, vp, vp, i32, vp, i32, vp],
+    "sl_build_group_tiles": [vp, vp, vp, i32, i32, i32, i32, vp],
     "sl_nvfp4_dequant_bf16": [vp, vp, vp, vp, i32, i32, i32, i32, i32, vp],
-    "sl_moe_unsort_reduce": [vp, vp, vp, vp, i32, i32, i32, i32, vp],
+    "sl_moe_unsort_reduce": [vp, vp, vp, vp, i32, i32, i32, i32, i32, vp],
     "sl_gemm_bf16_tcgen05": [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp, i32, vp],
 }
 

@@ -135,7 +135,7 @@ class Comm:
 
     def cp_merge_partials(self, ops, o_part, lse_part):
         """Merge this rank's split partials across ranks; returns this rank's head slice."""
-        o, lse = ops.combine([o_part], [lse_part])
+        o, lse = (ops.combine_f32 if hasattr(ops, "combine_f32") else ops.combine)([o_part], [lse_part])
         return self.cp_merge_heads(ops, o, lse)
 
     # -- fused-op shaped interface (overridden by the NVLink kernels) -------------------------
@@ -149,6 +149,18 @@ class Comm:
         W, r = self.ctx.world, self.ctx.rank
         if W == 1:
             return o
+        if o.is_cuda and hasattr(ops, "combine"):
+            # every rank needs only its own heads: exchange head slices (all-to-all), then merge the W partials
+            T, h, R = o.shape
+            hl = h // W
+            send_o = o.to(torch.float32).view(T, W, hl, R).permute(1, 0, 2, 3).contiguous()
+            send_l = lse.to(torch.float32).view(T, W, hl).permute(1, 0, 2).contiguous()
+            recv_o, recv_l = torch.empty_like(send_o), torch.empty_like(send_l)
+            dist.all_to_all_single(recv_o, send_o, group=self.ctx.group)
+            dist.all_to_all_single(recv_l, send_l, group=self.ctx.group)
+            merged, _ = ops.combine([recv_o[i].unsqueeze(2) for i in range(W)], [recv_l[i].unsqueeze(2) for i in range(W)],
+                                    want_lse=False)
+            return merged
         os_ = torch.stack(self.all_gather_list(o.to(torch.float32)))
         ls_ = torch.stack(self.all_gather_list(lse.to(torch.float32)))
         merged, _ = ops.merge_attention_partials(os_, ls_)
@@ -156,24 +168,25 @@ class Comm:
         return merged[:, r * hl:(r + 1) * hl].contiguous()
 
     def cp_merge_topk(self, ops, pos: torch.Tensor, score: torch.Tensor, top_k: int) -> torch.Tensor:
-        """Merge per-rank local top-k candidate lists (global positions + scores, -1 padded)
-        into the global top-k, ascending by position (`src/parallel_ops.ts:4233-4330`)."""
-        if self.ctx.world == 1:
+        """Global top-k over the ranks' local candidate lists (global positions + scores, -1 padded).
+
+        Only the scores travel: every rank gathers all candidate scores [T, W*k], selects the k best of the
+        union (the same selection everywhere) and keeps the winners that are its own candidates.  Returns
+        [T, k] global positions of THIS rank's selected keys, -1 elsewhere; the caller turns them into local
+        cache slots.  Ties go to the lower (rank, candidate index).  Reference: the all-gather + re-select of
+        `src/parallel_ops.ts:4233-4330`, which also moves the positions."""
+        W, r = self.ctx.world, self.ctx.rank
+        if W == 1:
             return pos
-        allp = torch.cat(self.all_gather_list(pos), dim=1).to(torch.int64)
-        alls = torch.cat(self.all_gather_list(score.to(torch.float32)), dim=1)
-        valid = allp >= 0
-        n_valid = valid.sum(1)
-        T = pos.shape[0]
-        out = torch.full((T, top_k), -1, dtype=torch.int32, device=pos.device)
-        for t in range(T):
-            p, s = allp[t][valid[t]], alls[t][valid[t]]
-            if int(n_valid[t]) > top_k:
-                # highest score first, ties to the lower position
-                order = torch.sort(p).indices
-                p, s = p[order], s[order]
-                keep = torch.sort(s, descending=True, stable=True).indices[:top_k]
-                p = p[keep]
-            p = torch.sort(p).values
-            out[t, : p.numel()] = p.to(torch.int32)
-        return out
+        T, k = pos.shape
+        s = torch.where(pos >= 0, score.to(torch.float32), torch.full_like(score, float("-inf"), dtype=torch.float32))
+        alls = torch.cat(self.all_gather_list(s.contiguous()), dim=1)                   # [T, W*k]
+        if hasattr(ops, "topk_select_plain") and alls.is_cuda:
+            idx = ops.topk_select_plain(alls, top_k).to(torch.int64)                    # ascending candidate index
+        else:
+            order = torch.sort(alls, dim=1, descending=True, stable=True).indices[:, :top_k]
+            idx = torch.sort(order, dim=1).values
+        mine = (idx >= r * k) & (idx < (r + 1) * k)
+        local_j = torch.where(mine, idx - r * k, torch.zeros_like(idx))
+        out = torch.where(mine, pos.gather(1, local_j).to(torch.int32), torch.full((1,), -1, dtype=torch.int32, device=pos.device))
+        return out.contiguous()

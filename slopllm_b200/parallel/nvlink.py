@@ -289,7 +289,7 @@ class NvlinkComm(Comm):
         T, h, S, R = o_part.shape
         W, r = self.ctx.world, self.ctx.rank
         if rg.cp_ctx is None or T > rg.cp_shape[0]:
-            o, lse = ops.combine([o_part], [lse_part])
+            o, lse = ops.combine_f32([o_part], [lse_part])
             return super().cp_merge_heads(ops, o, lse)
         # local combine over the splits (fp32 out is needed for the exchange): reuse combine with fp32 via torch
         o, lse = ops.combine_f32([o_part], [lse_part])
