@@ -25,6 +25,18 @@ def parse_args(argv=None):
     ap.add_argument("--admin-api-key", default=None)
     ap.add_argument("--served-model-name", default="")
     ap.add_argument("--no-warmup", action="store_true")
+    # sampling defaults applied when a request does not set them (reference `src/openai-server.ts:51-103`)
+    ap.add_argument("--max-tokens", type=int, default=65536)
+    ap.add_argument("--temperature", type=float, default=0.6)
+    ap.add_argument("--top-p", type=float, default=0.95)
+    ap.add_argument("--top-k", type=int, default=20)
+    ap.add_argument("--repetition-penalty", type=float, default=1.0)
+    ap.add_argument("--presence-penalty", type=float, default=0.0)
+    ap.add_argument("--repetition-penalty-window", type=int, default=64)
+    ap.add_argument("--decode-latency", type=float, default=0.0, help="minimum milliseconds per decode step (rate limit)")
+    ap.add_argument("--phased-prefill", dest="phased_prefill", action="store_true", default=True)
+    ap.add_argument("--no-phased-prefill", dest="phased_prefill", action="store_false")
+    ap.add_argument("--no-mtp", action="store_true", help="ignore --mtp")
     return ap.parse_args(argv)
 
 
@@ -45,7 +57,17 @@ def warm_up(rt, tokens: int = 32) -> float:
 
 def main(argv=None) -> int:
     args = parse_args(argv)
+    if args.no_mtp:
+        args.mtp = 0
     rt = build_runtime(args)
+    from ..config import SamplingParams
+    rt.engine_cfg.max_tokens = args.max_tokens
+    rt.engine_cfg.phased_prefill = args.phased_prefill
+    rt.engine_cfg.decode_latency_ms = args.decode_latency
+    rt.scheduler.decode_latency = args.decode_latency / 1e3
+    rt.engine_cfg.sampling = SamplingParams(temperature=args.temperature, top_p=args.top_p, top_k=args.top_k,
+                                            repetition_penalty=args.repetition_penalty, presence_penalty=args.presence_penalty,
+                                            repetition_penalty_window=args.repetition_penalty_window)
     rt.scheduler.start()
     if rt.ctx.rank != 0:
         rt.scheduler._thread.join()              # followers mirror rank 0 until it broadcasts stop

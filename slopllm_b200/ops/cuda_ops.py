@@ -252,10 +252,8 @@ class CudaOps:
     def _mla_splits(self, T: int, h: int) -> int:
         """Split the selected keys so that the grid fills the 148 SMs a few times over
         (the reference's `sparseMlaChunksPerBlock`, `src/sparse-mla-planner.ts:1-21`)."""
-        topk = self.cfg.index_topk
-        groups = (h + 15) // 16
-        want = max(1, (148 * 2) // max(1, T * groups))
-        return int(max(1, min(want, max(1, topk // 64), 64)))
+        from ..runtime.planner import sparse_mla_splits
+        return sparse_mla_splits(T, h, self.cfg.index_topk)
 
     def sparse_mla_partials(self, q_abs, q_pe, layer_cache, slots, lengths):
         c = self.cfg

@@ -150,6 +150,11 @@ _SIGS = {
     "sl_q_post_absorb": [C.POINTER(QPostParams), vp, vp, i32, i32, vp],
     "sl_bmv": [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i64, vp],
     "sl_smallT_splits": [i32, i32, i32],
+    "sl_quantize_fp8": [vp, vp, vp, i32, i32, vp],
+    "sl_prefetch_l2": [vp, C.c_size_t, vp],
+    "sl_gather_mark": [vp, vp, vp, i32, i32, vp],
+    "sl_gather_rows": [vp, vp, vp, vp, i32, i32, i32, i32, vp],
+    "sl_gather_fanout": [vp, vp, vp, vp, i32, i32, vp],
     "sl_qk_norm_rope_cache": [vp, i32, vp],
     "sl_paged_attn_prefill": [vp, i32, i32, vp],
     "sl_paged_attn_decode": [vp, i32, vp],

@@ -87,3 +87,41 @@ def test_model_path_resolution(tmp_path, monkeypatch):
     assert [os.path.basename(p) for p in list_safetensors_shards(str(snap))] == ["a.safetensors", "b.safetensors"]
     (snap / "model.safetensors.index.json").write_text(json.dumps({"weight_map": {"x": "b.safetensors", "y": "b.safetensors", "z": "a.safetensors"}}))
     assert [os.path.basename(p) for p in list_safetensors_shards(str(snap))] == ["b.safetensors", "a.safetensors"]
+
+
+def test_serve_entry_point_end_to_end():
+    """`python -m slopllm_b200 serve` on the CPU ops with a random tiny model: health, model list, one completion."""
+    import subprocess
+    import sys
+    import time
+    import urllib.request
+    from mp_util import _free_port
+    port = _free_port()
+    proc = subprocess.Popen([sys.executable, "-m", "slopllm_b200", "serve", "--cpu", "--random-init", "tiny", "--no-cuda-graph",
+                             "--batch-size", "2", "--chunk-size", "64", "--max-pages", "32", "--port", str(port), "--no-warmup",
+                             "--temperature", "0"], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    try:
+        ok = False
+        for _ in range(120):
+            try:
+                with urllib.request.urlopen(f"http://127.0.0.1:{port}/health", timeout=2) as r:
+                    ok = r.status == 200
+                    break
+            except Exception:  # noqa: BLE001
+                if proc.poll() is not None:
+                    break
+                time.sleep(0.5)
+        assert ok, proc.stdout.read() if proc.poll() is not None else "server did not come up"
+        with urllib.request.urlopen(f"http://127.0.0.1:{port}/v1/models", timeout=10) as r:
+            assert json.loads(r.read())["data"][0]["id"] == "tiny"
+        body = json.dumps({"model": "tiny", "messages": [{"role": "user", "content": "hi"}], "max_tokens": 4}).encode()
+        req = urllib.request.Request(f"http://127.0.0.1:{port}/v1/chat/completions", data=body, headers={"Content-Type": "application/json"})
+        with urllib.request.urlopen(req, timeout=120) as r:
+            out = json.loads(r.read())
+        assert out["usage"]["completion_tokens"] >= 1 and out["choices"][0]["finish_reason"] in ("length", "stop")
+    finally:
+        proc.terminate()
+        try:
+            proc.wait(timeout=20)
+        except subprocess.TimeoutExpired:
+            proc.kill()

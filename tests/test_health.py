@@ -1,0 +1,129 @@
+"""Failure detection without touching a GPU: heartbeats over a TCP store between CPU processes, a rank
+that leaves between steps, a rank that stops beating, and host-side fault injection in the scheduler
+and the page allocator."""
+import time
+
+import pytest
+
+from slopllm_b200.utils.health import FaultInjector, HealthMonitor, RankFailure, make_store
+from slopllm_b200.utils.tracing import PhaseTimers, nvtx_range
+
+from mp_util import _free_port, run_ranks
+
+
+class DictStore:
+    def __init__(self):
+        self.d = {}
+
+    def set(self, k, v):
+        self.d[k] = v.encode()
+
+    def get(self, k):
+        return self.d[k]
+
+
+def test_monitor_detects_stale_peer_with_fake_clock():
+    store, now = DictStore(), [100.0]
+    events = []
+    a = HealthMonitor(store, 0, 2, timeout_s=2.0, on_failure=events.append, clock=lambda: now[0])
+    b = HealthMonitor(store, 1, 2, timeout_s=2.0, clock=lambda: now[0])
+    a.beat(); b.beat()
+    assert a.check_peers().healthy
+    now[0] += 1.5
+    b.beat()
+    assert a.check_peers().healthy
+    b.pause()                                    # injected fault: rank 1 stops beating
+    now[0] += 2.5
+    b.beat()
+    st = a.check_peers()
+    assert not st.healthy and st.failed_ranks == [1] and len(events) == 1
+    with pytest.raises(RankFailure):
+        a.raise_if_unhealthy()
+    a.reset()
+    assert a.is_healthy()
+
+
+def _rank(rank, world, port):
+    store = make_store(rank, world, port=port)
+    mon = HealthMonitor(store, rank, world, interval_s=0.05, timeout_s=0.6).start()
+    steps = 0
+    t0 = time.time()
+    while time.time() - t0 < 6.0:
+        if rank == 2 and steps == 5:
+            mon.stop()                           # rank 2 leaves between steps (no work in flight)
+            return {"left_after": steps}
+        if not mon.is_healthy():
+            mon.stop()
+            return {"detected": mon.state.failed_ranks, "steps": steps, "seconds": time.time() - t0}
+        steps += 1
+        time.sleep(0.05)
+    mon.stop()
+    return {"detected": [], "steps": steps}
+
+
+def test_ranks_notice_a_peer_that_left():
+    res = run_ranks(_rank, 3, _free_port(), timeout=60)
+    assert res[2] == {"left_after": 5}
+    for r in (0, 1):
+        assert res[r]["detected"] == [2] and res[r]["seconds"] < 4.0
+
+
+def test_fault_injector_counts_down():
+    fi = FaultInjector()
+    fi.arm("page_alloc", after=2)
+    assert [fi.hit("page_alloc") for _ in range(4)] == [False, False, True, False]
+    fi.arm("send")
+    with pytest.raises(ConnectionError):
+        fi.maybe_raise("send", ConnectionError("dropped"))
+    assert fi.fired == ["page_alloc", "send"]
+
+
+def test_scheduler_fails_requests_fast_when_unhealthy():
+    """An engine whose step raises RankFailure: the scheduler ends every admitted request with an error and
+    stays usable (per-batch rollback, `src/generation-scheduler.ts:669-689`)."""
+    import torch
+    from slopllm_b200.config import GlmMoeDsaConfig, SamplingParams
+    from slopllm_b200.models.glm_moe_dsa import GlmMoeDsaModel
+    from slopllm_b200.models.weights import random_model
+    from slopllm_b200.runtime.engine import Engine
+    from slopllm_b200.scheduler.scheduler import GenerationRequest, GenerationScheduler
+    cfg = GlmMoeDsaConfig.tiny()
+    eng = Engine(cfg, GlmMoeDsaModel(cfg, random_model(cfg, 0)), num_pages=16, max_batch=2, max_seq_len=256, cuda_graph=False)
+    fi = FaultInjector()
+    real = eng.decode_step
+
+    def decode_step(*a, **k):
+        fi.maybe_raise("peer_lost", RankFailure("no heartbeat from rank(s) [1]"))
+        return real(*a, **k)
+
+    eng.decode_step = decode_step
+    sched = GenerationScheduler(eng, max_batch=2, chunk_size=64)
+    fi.arm("peer_lost", after=1)
+    done = []
+    req = GenerationRequest(id="a", input_ids=list(range(3, 30)), max_tokens=8, sampling=SamplingParams(temperature=0.0),
+                            on_finish=done.append)
+    sched.submit(req)
+    for _ in range(20):
+        sched.step()
+        if done:
+            break
+    assert done and req.error and "heartbeat" in req.error and req.finish_reason == "error"
+    ok = GenerationRequest(id="b", input_ids=list(range(3, 20)), max_tokens=3, sampling=SamplingParams(temperature=0.0),
+                           on_finish=done.append)
+    sched.submit(ok)
+    for _ in range(20):
+        sched.step()
+        if len(done) == 2:
+            break
+    assert ok.finish_reason == "length" and len(ok.generated) == 3
+    assert torch.is_tensor(torch.zeros(1))
+
+
+def test_phase_timers_and_nvtx_noop():
+    t = PhaseTimers()
+    with t.phase("decode", 4):
+        with nvtx_range("layer0"):
+            pass
+    t.record("decode", 4, 0.5)
+    text = t.prometheus()
+    assert 'phase="decode",batch_size="4"' in text and "phase_seconds_count" in text and t.count[("decode", 4)] == 2

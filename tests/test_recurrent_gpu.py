@@ -156,3 +156,33 @@ def test_qk_norm_rope_cache_write():
                                heads, n_kv, hd, rope, 1e6, 1e-6, q_stride=2 * hd)
     assert rel_err(got, want) < 1e-2
     assert rel_err(kc_g, kc_c) < 1e-2 and rel_err(vc_g, vc_c) < 1e-6
+
+
+def test_quantize_fp8_and_prefetch():
+    from slopllm_b200.ops import misc
+    g = gen(8)
+    x = (torch.randn(37, 300, generator=g) * 3).to(torch.bfloat16)
+    q_c, s_c = misc.quantize_fp8(x)
+    q_g, s_g = misc.quantize_fp8(x.cuda())
+    assert torch.equal(s_g.cpu(), s_c)
+    deq = lambda q, s: q.view(torch.float8_e4m3fn).to(torch.float32) * s.repeat_interleave(128, 1)[:, :300]
+    assert rel_err(deq(q_g.cpu(), s_g.cpu()), deq(q_c, s_c)) < 1e-6
+    assert rel_err(deq(q_c, s_c), x) < 0.07
+    misc.prefetch_l2(x.cuda())                       # must simply run
+    torch.cuda.synchronize()
+
+
+def test_gather_topk_ckv():
+    from slopllm_b200.ops import misc, quant
+    g = gen(9)
+    R, Dr, group, n, T, k = 512, 64, 128, 300, 5, 64
+    cache = quant.pack_kv_rows(torch.randn(n, R, generator=g), torch.randn(n, Dr, generator=g), group)
+    slots = torch.randint(0, n, (T, k), generator=g).to(torch.int32)
+    lengths = torch.tensor([64, 10, 0, 33, 64], dtype=torch.int32)
+    d_c, w_c, u_c = misc.gather_topk_ckv(cache, slots, lengths, R, Dr, group)
+    d_g, w_g, u_g = misc.gather_topk_ckv(cache.cuda(), slots.cuda(), lengths.cuda(), R, Dr, group)
+    assert u_c == u_g and torch.equal(w_g.cpu(), w_c)
+    assert rel_err(d_g, d_c) < 1e-2
+    # fan-out consistency: row where[t, j] of the dense buffer is the row of slot slots[t, j]
+    ckv, kpe = quant.unpack_kv_rows(cache[slots[0, 3].long()].unsqueeze(0), R, Dr, group)
+    assert rel_err(d_g[w_g[0, 3].long()].cpu(), torch.cat([ckv, kpe], 1)[0]) < 1e-2

@@ -1,0 +1,93 @@
+"""Workspace arena, lifetime helpers, launch planner and the shape-only backend
+(reference: `src/workspace.ts`, `src/heap.ts`, `src/using-holder.ts`, `src/tensor-tree.ts`,
+`src/sparse-mla-planner.ts`, `src/meta_ops.ts`)."""
+import pytest
+import torch
+
+from slopllm_b200.config import GlmMoeDsaConfig
+from slopllm_b200.models.glm_moe_dsa import GlmMoeDsaModel, KVCacheTensors, make_step
+from slopllm_b200.models.weights import random_model
+from slopllm_b200.ops.meta_ops import MetaOps
+from slopllm_b200.runtime.planner import padded_kv_len, smallt_splits, sparse_mla_splits
+from slopllm_b200.runtime.workspace import UsingHolder, Workspace, walk_tensors
+
+
+def test_workspace_alloc_free_and_lineage():
+    ws = Workspace(1 << 16)
+    a = ws.alloc((100,), torch.float32, "a", stream=1)
+    b = ws.alloc((64, 4), torch.bfloat16, "b", stream=2)
+    assert a.data_ptr() % 256 == 0 and b.data_ptr() % 256 == 0 and a.numel() == 100
+    a.fill_(3.0)
+    used = ws.used
+    ws.free(a)
+    # a block freed on stream 1 is reused by stream 1 first, and not handed to another stream before promote()
+    c = ws.alloc((100,), torch.float32, "c", stream=2)
+    assert c.data_ptr() != a.data_ptr()
+    d = ws.alloc((50,), torch.float32, "d", stream=1)
+    assert d.data_ptr() == a.data_ptr()
+    ws.free(d)
+    ws.promote(1)
+    assert ws.used < used + 1024
+    with pytest.raises(ValueError):
+        ws.free(d)
+    assert [n for n, _, _ in ws.layout()] == ["b", "c"]
+
+
+def test_workspace_scope_freeze_reset_and_exhaustion():
+    ws = Workspace(4096)
+    w = ws.alloc((256,), torch.float32, "weight")
+    ws.freeze()
+    with ws.scope():
+        t1 = ws.alloc((128,), torch.float32, "tmp1")
+        t2 = ws.alloc((128,), torch.float32, "tmp2")
+        assert len(ws.live) == 3 and t1.data_ptr() != t2.data_ptr()
+    assert len(ws.live) == 1
+    with pytest.raises(MemoryError):
+        ws.alloc((4096,), torch.float32)
+    ws.reset()
+    assert len(ws.live) == 1 and ws.live[w.data_ptr()].name == "weight"
+    big = ws.alloc((700,), torch.float32)             # the lineage blocks were returned to the heap
+    assert big.numel() == 700
+
+
+def test_using_holder_and_tensor_tree():
+    log = []
+
+    class D:
+        def __init__(self, n):
+            self.n = n
+
+        def dispose(self):
+            log.append(self.n)
+
+    with UsingHolder(D(1)) as h:
+        h.replace(D(2))
+        kept = h.detach()
+        h.replace(D(3))
+    assert log == [1, 3] and kept.n == 2
+    seen = []
+    walk_tensors({"a": [torch.zeros(1), (torch.ones(2), 5)], "b": type("O", (), {})()}, lambda t: seen.append(t.numel()))
+    assert seen == [1, 2]
+
+
+def test_planner():
+    assert sparse_mla_splits(1, 8, 2048) == 32             # one token, one head group: split the 2048 keys 32 ways
+    assert sparse_mla_splits(8, 64, 2048) == 9
+    assert sparse_mla_splits(4096, 64, 2048) == 1
+    assert smallt_splits(8, 2784, 6144) == 8 and smallt_splits(8, 154880 // 8, 6144) == 1
+    assert padded_kv_len(5) == 1024 and padded_kv_len(1025) == 2048 and padded_kv_len(4096) == 4096
+
+
+def test_meta_ops_runs_the_model_without_memory():
+    cfg = GlmMoeDsaConfig.tiny()
+    w = random_model(cfg, 0)
+    ops = MetaOps(cfg)
+    m = GlmMoeDsaModel(cfg, w, ops=ops)
+    cache = KVCacheTensors.allocate(cfg, 4, "cpu")
+    T = 37
+    st = make_step(list(range(T)), list(range(T)), [0] * T, [[0, 1, 2, 3]])
+    hidden = m.forward_hidden(st, cache)
+    assert hidden.device.type == "meta" and tuple(hidden.shape) == (T, cfg.hidden_size)
+    s = ops.summary()
+    assert s["calls"]["linear"] >= 3 * cfg.num_hidden_layers and s["total_flops"] > 0 and s["total_weight_bytes"] > 0
+    assert s["calls"]["moe"] == cfg.num_hidden_layers - cfg.first_k_dense_replace
