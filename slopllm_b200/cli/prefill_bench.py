@@ -25,6 +25,7 @@ def main(argv=None) -> int:
             ms = timed_ms(rt.ctx, lambda: eng.prefill([s], [prompt], chunk_size=args.chunk_size))
             eng.kv.free_sequence(s)
             eng.release(s)
+            eng.check_device_errors()
             best = ms if best is None else min(best, ms)
         if rt.ctx.rank == 0:
             print(json.dumps({"context": n, "ttft_s": best / 1e3, "prefill_tok_s": n / (best / 1e3), "chunk_size": args.chunk_size,

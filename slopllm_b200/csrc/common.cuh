@@ -150,6 +150,21 @@ __device__ __forceinline__ float pow2_scale_ceil(float amax) {
     return __uint_as_float(bits);
 }
 
+// ---- index self-checks ----------------------------------------------------------------------------
+// Every index that a kernel reads from device metadata (cache slots, page-table entries) is checked
+// against its bound before it is used as an address.  A bad index is recorded once in `guard`
+// ({site, value, limit, block}) and the access is skipped, so a corrupt table shows up as a host-side
+// error after the step instead of a memory fault.  `guard` may be null (no record, access still skipped).
+__device__ __forceinline__ bool guard_ok(int* guard, int site, long long value, long long limit) {
+    if (value >= 0 && value < limit) return true;
+    if (guard != nullptr && atomicCAS(guard, 0, site) == 0) {
+        guard[1] = (int)value;
+        guard[2] = (int)limit;
+        guard[3] = (int)blockIdx.x;
+    }
+    return false;
+}
+
 // ---- bounded waits on flags written by other GPUs ---------------------------------------------
 // Every wait gives up after `max_spins` polls, records where it stopped in `status`
 // (status[0] = code, [1] = site, [2] = expected, [3] = observed) and lets the kernel

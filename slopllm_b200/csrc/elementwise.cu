@@ -136,6 +136,8 @@ struct AttnPreParams {
     bf16* cq_out;             // [T, q_lora]
     float* idx_w_out;         // [T, idx_heads]
     int n_slabs; long long slab_stride;
+    int num_slots;            // rows of the caches (0 = unknown: no check)
+    int* guard;               // index self-check record (see guard_ok), may be null
 };
 
 // grid (T, 3): three independent pieces of work per token run as separate blocks.
@@ -172,8 +174,10 @@ __global__ void attn_pre_kernel(AttnPreParams p) {
         owned = (pos % p.cp_world) == p.cp_rank;
         local = pos / p.cp_world;
     }
+    if (!guard_ok(p.guard, 41, local / p.page_size, p.pt_stride)) return;     // block-uniform
     const int page = p.page_table[(size_t)p.batch_idx[t] * p.pt_stride + local / p.page_size];
     const size_t slot = (size_t)page * p.page_size + (local % p.page_size);
+    if (p.num_slots != 0 && !guard_ok(p.guard, 42, (long long)slot, p.num_slots)) return;
     const size_t kv = row + p.q_lora;
 
     if (role == 1) {
@@ -544,7 +548,7 @@ SL_API int sl_route_topk(void* ids, void* wts, const void* logits, const void* b
 // entries (-1, or owned by another CP rank when local_only).  One block per token, k <= 4096.
 __global__ void topk_to_slots_kernel(int* __restrict__ slots, int* __restrict__ lengths, const int* __restrict__ pos,
                                      const int* __restrict__ page_table, const int* __restrict__ batch_idx, int k,
-                                     int pt_stride, int page_size, int cp_world, int cp_rank, int local_only) {
+                                     int pt_stride, int page_size, int cp_world, int cp_rank, int local_only, int* guard) {
     pdl_grid_sync();
     __shared__ int wsum[32];
     __shared__ int base;
@@ -565,7 +569,8 @@ __global__ void topk_to_slots_kernel(int* __restrict__ slots, int* __restrict__ 
         for (int w = 0; w < warp; ++w) off += wsum[w];
         if (valid) {
             const int local = p / cp_world;
-            slots[(size_t)t * k + off + inw] = pt[local / page_size] * page_size + local % page_size;
+            slots[(size_t)t * k + off + inw] =
+                guard_ok(guard, 31, local / page_size, pt_stride) ? pt[local / page_size] * page_size + local % page_size : 0;
         }
         __syncthreads();
         if (tid == 0) {
@@ -580,10 +585,11 @@ __global__ void topk_to_slots_kernel(int* __restrict__ slots, int* __restrict__ 
 }
 
 SL_API int sl_topk_to_slots(void* slots, void* lengths, const void* pos, const void* page_table, const void* batch_idx, int T,
-                            int k, int pt_stride, int page_size, int cp_world, int cp_rank, int local_only, cudaStream_t s) {
+                            int k, int pt_stride, int page_size, int cp_world, int cp_rank, int local_only, void* guard,
+                            cudaStream_t s) {
     if (T == 0) return 0;
     sl_launch(topk_to_slots_kernel, T, 256, 0, s, (int*)slots, (int*)lengths, (const int*)pos, (const int*)page_table,
-                                           (const int*)batch_idx, k, pt_stride, page_size, cp_world, cp_rank, local_only);
+                                           (const int*)batch_idx, k, pt_stride, page_size, cp_world, cp_rank, local_only, (int*)guard);
     return SL_LAUNCH_CHECK();
 }
 

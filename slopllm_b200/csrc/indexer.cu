@@ -24,6 +24,8 @@ struct IndexerScoreParams {
     const int* batch_idx; const int* positions;
     int Hi, D, page_size, cp_world, cp_rank, top_k;
     float* scores; int ld_scores;     // [T, ld_scores]
+    int num_slots;                    // rows of idx_cache (0 = unknown: no check)
+    int* guard;                       // index self-check record (see guard_ok), may be null
 };
 
 // Visible local keys of a query at global position p: local key j is global j*W + r.
@@ -70,8 +72,11 @@ __global__ void __launch_bounds__(256) indexer_score_kernel(IndexerScoreParams p
     for (int j0 = k_begin + warp * 8; j0 < k_end; j0 += 64) {
         // lane's key for the B fragment: j0 + g ; 8 consecutive keys never straddle a page
         const int j = j0 + g;
-        const bool ok = j < k_end;
-        const size_t slot = (size_t)pt[j0 / p.page_size] * p.page_size + (j0 % p.page_size) + g;
+        bool ok = j < k_end;
+        const int pidx = j0 / p.page_size;
+        if (!guard_ok(p.guard, 21, pidx, p.pt_stride)) continue;            // warp-uniform
+        const size_t slot = (size_t)pt[pidx] * p.page_size + (j0 % p.page_size) + g;
+        if (ok && p.num_slots != 0 && !guard_ok(p.guard, 22, (long long)slot, p.num_slots)) ok = false;
         const uint8_t* row = p.idx_cache + slot * RB;
         uint32_t b[KS][2];
         // row stride D+4 keeps 4-byte alignment only: read the lane's 32 bytes as 8 words
@@ -101,6 +106,7 @@ __global__ void __launch_bounds__(256) indexer_score_kernel(IndexerScoreParams p
                 const int jj = j0 + 2 * c + i;
                 if (jj < k_end) {
                     const size_t sl = (size_t)pt[j0 / p.page_size] * p.page_size + (j0 % p.page_size) + 2 * c + i;
+                    if (p.num_slots != 0 && !guard_ok(p.guard, 23, (long long)sl, p.num_slots)) continue;
                     const float ks = *reinterpret_cast<const float*>(p.idx_cache + sl * RB + D);
                     p.scores[(size_t)t * p.ld_scores + jj] = part[i] * ks;
                 }
@@ -127,7 +133,9 @@ __global__ void indexer_score_generic_kernel(IndexerScoreParams p, int keys_per_
     const int* pt = p.page_table + (size_t)p.batch_idx[t] * p.pt_stride;
     const int RB = p.D + 4;
     for (int j = k_begin + threadIdx.x; j < k_end; j += blockDim.x) {
+        if (!guard_ok(p.guard, 24, j / p.page_size, p.pt_stride)) continue;
         const size_t slot = (size_t)pt[j / p.page_size] * p.page_size + (j % p.page_size);
+        if (p.num_slots != 0 && !guard_ok(p.guard, 25, (long long)slot, p.num_slots)) continue;
         const uint8_t* row = p.idx_cache + slot * RB;
         float tot = 0.f;
         for (int h = 0; h < p.Hi; ++h) {

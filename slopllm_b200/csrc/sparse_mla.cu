@@ -16,6 +16,8 @@ struct SparseMlaParams {
     float sm_scale;
     float* o_part;            // [T, h, splits, R]
     float* lse_part;          // [T, h, splits]
+    int num_slots;            // rows of kv_cache (0 = unknown: no check)
+    int* guard;               // index self-check record (see guard_ok), may be null
 };
 
 // grid (splits, head groups of HB, T); block 256.
@@ -64,7 +66,9 @@ __global__ void __launch_bounds__(256) sparse_mla_split_kernel(SparseMlaParams p
         // dequantise kc rows into shared memory
         for (int i = tid; i < kc * (row_bytes / 4); i += blockDim.x) {
             const int j = i / (row_bytes / 4), wd = i % (row_bytes / 4);
-            const uint8_t* row = p.kv_cache + (size_t)slots[c0 + j] * row_bytes;
+            int slot_j = slots[c0 + j];
+            if (p.num_slots != 0 && !guard_ok(p.guard, 12, slot_j, p.num_slots)) slot_j = 0;
+            const uint8_t* row = p.kv_cache + (size_t)slot_j * row_bytes;
             const uint32_t u = *reinterpret_cast<const uint32_t*>(row + wd * 4);
             const int byte = wd * 4;
             if (byte < p.R) {

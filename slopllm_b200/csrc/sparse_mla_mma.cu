@@ -20,6 +20,8 @@ struct Params {
     float sm_scale;
     float* o_part;            // [T, h, splits, R]
     float* lse_part;          // [T, h, splits]
+    int num_slots;            // rows of kv_cache (0 = unknown: no check)
+    int* guard;               // index self-check record (see guard_ok), may be null
 };
 
 constexpr int HB = 16;        // heads per CTA (one MMA row tile)
@@ -91,6 +93,8 @@ __global__ void __launch_bounds__(256) sparse_mla_mma_kernel(Params p) {
 #pragma unroll
     for (int i = 0; i < 8; ++i) oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.f;
 
+    // a slot outside the cache is recorded and replaced by row 0 (its score is garbage, the step is reported as failed)
+    auto checked_slot = [&](int s) { return (p.num_slots == 0 || guard_ok(p.guard, 11, s, p.num_slots)) ? s : 0; };
     // 16-byte gather path: the rows of chunk c+1 are loaded into registers while chunk c is multiplied, so the
     // gather latency overlaps the tensor-core phases (a thread's loads are all issued before their first use).
     constexpr int MAXLD = 12;
@@ -112,7 +116,7 @@ __global__ void __launch_bounds__(256) sparse_mla_mma_kernel(Params p) {
     };
     int* s_slots2 = s_slots + KC;                               // second slot buffer (pipelined path)
     if (vec16 && j_begin < j_end) {
-        if (tid < KC) s_slots[tid] = tid < min(KC, j_end - j_begin) ? slots[j_begin + tid] : 0;
+        if (tid < KC) s_slots[tid] = tid < min(KC, j_end - j_begin) ? checked_slot(slots[j_begin + tid]) : 0;
         __syncthreads();
         issue_loads(j_begin, s_slots);
     }
@@ -158,12 +162,12 @@ __global__ void __launch_bounds__(256) sparse_mla_mma_kernel(Params p) {
             // slots of the next chunk, then its loads (in flight during this chunk's MMAs)
             const int c0n = c0 + KC;
             int* sl_next = parity ? s_slots : s_slots2;
-            if (c0n < j_end && tid < KC) sl_next[tid] = tid < min(KC, j_end - c0n) ? slots[c0n + tid] : 0;
+            if (c0n < j_end && tid < KC) sl_next[tid] = tid < min(KC, j_end - c0n) ? checked_slot(slots[c0n + tid]) : 0;
             __syncthreads();
             if (c0n < j_end) issue_loads(c0n, sl_next);
             parity ^= 1;
         } else {
-        if (tid < KC) s_slots[tid] = tid < kc ? slots[c0 + tid] : 0;
+        if (tid < KC) s_slots[tid] = tid < kc ? checked_slot(slots[c0 + tid]) : 0;
         __syncthreads();
         for (int i = tid; i < KC * words; i += blockDim.x) {
             const int j = i / words, wd = i % words, byte = wd * 4;

@@ -159,7 +159,7 @@ class CudaOps:
             positions=st.positions.data_ptr(), batch_idx=st.batch_idx.data_ptr(), page_table=st.page_table.data_ptr(),
             pt_stride=st.page_table.stride(0), page_size=st.page_size, cp_world=st.cp_world, cp_rank=st.cp_rank,
             kv_group=c.kv_quant_group, kv_cache=layer_cache.kv.data_ptr(), idx_cache=N.ptr(layer_cache.idx),
-            cq_out=cq.data_ptr(), idx_w_out=N.ptr(idx_w))
+            cq_out=cq.data_ptr(), idx_w_out=N.ptr(idx_w), num_slots=layer_cache.kv.shape[0], guard=self._guard(dev))
         N.call("sl_attn_pre", C.byref(p), T, N.stream())
         return cq, idx_w
 
@@ -209,7 +209,8 @@ class CudaOps:
                 q8=q8.data_ptr(), w_eff=w_eff.data_ptr(), idx_cache=layer_cache.idx.data_ptr(),
                 page_table=st.page_table.data_ptr(), pt_stride=st.page_table.stride(0), batch_idx=st.batch_idx.data_ptr(),
                 positions=st.positions.data_ptr(), Hi=c.index_n_heads, D=c.index_head_dim, page_size=st.page_size,
-                cp_world=W, cp_rank=r, top_k=c.index_topk, scores=scores.data_ptr(), ld_scores=scores.stride(0))
+                cp_world=W, cp_rank=r, top_k=c.index_topk, scores=scores.data_ptr(), ld_scores=scores.stride(0),
+                num_slots=layer_cache.idx.shape[0], guard=self._guard(dev))
             N.call("sl_indexer_scores", C.byref(sp), T, max_local, N.stream())
         tp = N.TopkSelectParams(scores=scores.data_ptr(), ld_scores=scores.stride(0), positions=st.positions.data_ptr(),
                                 top_k=c.index_topk, cp_world=W, cp_rank=r, out_pos=pos.data_ptr(), out_score=score.data_ptr())
@@ -246,7 +247,7 @@ class CudaOps:
         topk_pos = topk_pos.contiguous()
         N.call("sl_topk_to_slots", slots.data_ptr(), lengths.data_ptr(), topk_pos.data_ptr(), st.page_table.data_ptr(),
                st.batch_idx.data_ptr(), T, k, st.page_table.stride(0), st.page_size, st.cp_world, st.cp_rank,
-               int(local_only), N.stream())
+               int(local_only), self._guard(dev), N.stream())
         return slots, lengths
 
     def _mla_splits(self, T: int, h: int) -> int:
@@ -265,7 +266,8 @@ class CudaOps:
         p = N.SparseMlaParams(q_abs=q_abs.data_ptr(), q_pe=q_pe.data_ptr(), kv_cache=layer_cache.kv.data_ptr(),
                               slots=slots.data_ptr(), lengths=lengths.data_ptr(), h=h, R=Rr, Dr=c.qk_rope_head_dim,
                               group=c.kv_quant_group, topk=slots.shape[1], splits=splits, sm_scale=c.softmax_scale,
-                              o_part=o_part.data_ptr(), lse_part=lse_part.data_ptr())
+                              o_part=o_part.data_ptr(), lse_part=lse_part.data_ptr(), num_slots=layer_cache.kv.shape[0],
+                              guard=self._guard(dev))
         c_ok = Rr % 64 == 0 and Rr <= 512 and (Rr + c.qk_rope_head_dim) % 16 == 0
         N.call("sl_sparse_mla_split_mma" if c_ok else "sl_sparse_mla_split", C.byref(p), T, N.stream())
         return o_part, lse_part
@@ -406,6 +408,12 @@ class CudaOps:
         N.call("sl_moe_grouped_mma", C.byref(a), C.cast(C.byref(rargs), C.c_void_p) if rargs is not None else None, None,
                N.stream())
         return out
+
+    @staticmethod
+    def _guard(dev) -> int:
+        """Address of the per-device index self-check record (words 4..7 of the error block)."""
+        from . import tcgen05
+        return tcgen05.error_flag(dev).data_ptr() + 16
 
     def _zero_counter(self, dev):
         """A device word that the fused router kernel expects to be zero and leaves zero."""

@@ -71,7 +71,7 @@ class AttnPreParams(C.Structure):
                 ("eps", f32), ("theta", f32), ("rope_interleave", i32), ("idx_rope_interleave", i32),
                 ("positions", vp), ("batch_idx", vp), ("page_table", vp), ("pt_stride", i32), ("page_size", i32),
                 ("cp_world", i32), ("cp_rank", i32), ("kv_group", i32), ("kv_cache", vp), ("idx_cache", vp),
-                ("cq_out", vp), ("idx_w_out", vp), ("n_slabs", i32), ("slab_stride", i64)]
+                ("cq_out", vp), ("idx_w_out", vp), ("n_slabs", i32), ("slab_stride", i64), ("num_slots", i32), ("guard", vp)]
 
 
 class QPostParams(C.Structure):
@@ -84,7 +84,7 @@ class QPostParams(C.Structure):
 class IndexerScoreParams(C.Structure):
     _fields_ = [("q8", vp), ("w_eff", vp), ("idx_cache", vp), ("page_table", vp), ("pt_stride", i32),
                 ("batch_idx", vp), ("positions", vp), ("Hi", i32), ("D", i32), ("page_size", i32), ("cp_world", i32),
-                ("cp_rank", i32), ("top_k", i32), ("scores", vp), ("ld_scores", i32)]
+                ("cp_rank", i32), ("top_k", i32), ("scores", vp), ("ld_scores", i32), ("num_slots", i32), ("guard", vp)]
 
 
 class TopkSelectParams(C.Structure):
@@ -96,7 +96,7 @@ class TopkSelectParams(C.Structure):
 class SparseMlaParams(C.Structure):
     _fields_ = [("q_abs", vp), ("q_pe", vp), ("kv_cache", vp), ("slots", vp), ("lengths", vp), ("h", i32), ("R", i32),
                 ("Dr", i32), ("group", i32), ("topk", i32), ("splits", i32), ("sm_scale", f32), ("o_part", vp),
-                ("lse_part", vp)]
+                ("lse_part", vp), ("num_slots", i32), ("guard", vp)]
 
 
 class CombineParams(C.Structure):
@@ -166,7 +166,7 @@ _SIGS = {
     "sl_mhc_streams": [vp, vp, i32, i32, i32, vp],
     "sl_silu_mul": [vp, vp, i32, i32, vp],
     "sl_route_topk": [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, f32, vp],
-    "sl_topk_to_slots": [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp],
+    "sl_topk_to_slots": [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp, vp],
     "sl_rotate_input_ids": [vp, vp, vp, vp, i32, vp],
     "sl_gemv_bf16": [vp, vp, vp, i32, i32, i32, i32, i32, vp],
     "sl_gemv_nvfp4": [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp],

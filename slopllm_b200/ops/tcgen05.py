@@ -12,15 +12,18 @@ def error_flag(device) -> torch.Tensor:
     """Per-device int32 word that kernels set when one of their bounded waits expires."""
     key = torch.device(device).index or 0
     if key not in _err:
-        _err[key] = torch.zeros(4, dtype=torch.int32, device=device)
+        _err[key] = torch.zeros(8, dtype=torch.int32, device=device)     # [0] expired wait, [4..7] index self-check record
     return _err[key]
 
 
 def check_errors(device) -> None:
-    code = int(error_flag(device)[0].item())
-    if code:
+    words = error_flag(device).tolist()
+    if words[0]:
         error_flag(device).zero_()
-        raise N.NativeError(f"tcgen05 kernel reported an expired wait (site {code})")
+        raise N.NativeError(f"tcgen05 kernel reported an expired wait (site {words[0]})")
+    if words[4]:
+        error_flag(device).zero_()
+        raise N.NativeError(f"index self-check failed at site {words[4]}: value {words[5]} outside [0, {words[6]}) in block {words[7]}")
 
 
 def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out_f32: bool = False, bn: int = 128) -> torch.Tensor:

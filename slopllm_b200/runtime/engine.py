@@ -158,6 +158,17 @@ class Engine:
         if hasattr(self.model, "prepare_step"):
             self.model.prepare_step(st, seqs)
 
+    def check_device_errors(self) -> None:
+        """Raise if a kernel recorded an expired wait, a failed index self-check or a collective timeout
+        since the last call (reads a few status words back from the device)."""
+        if self.device.type != "cuda":
+            return
+        from ..ops import tcgen05
+        tcgen05.check_errors(self.device)
+        comm = getattr(self.model, "comm", None)
+        if comm is not None and hasattr(comm, "check_status"):
+            comm.check_status()
+
     def release(self, s: Sequence) -> None:
         """Tell the model that a sequence is gone (frees per-sequence state outside the page pool)."""
         if hasattr(self.model, "release_sequence"):
