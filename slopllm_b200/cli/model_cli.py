@@ -35,6 +35,9 @@ def add_model_args(ap: argparse.ArgumentParser) -> None:
     ap.add_argument("--max-host-pages", type=int, default=0, help="pinned-host prefix tier size in pages (0: off)")
     ap.add_argument("--max-model-len", type=int, default=65536)
     ap.add_argument("--no-cuda-graph", action="store_true")
+    ap.add_argument("--phased-prefill", dest="phased_prefill", action="store_true", default=True,
+                    help="run large prefill chunks as two halves on two streams (multi-rank jobs)")
+    ap.add_argument("--no-phased-prefill", dest="phased_prefill", action="store_false")
     ap.add_argument("--no-fused-collectives", action="store_true", help="NCCL collectives instead of the in-kernel NVLink ones")
     ap.add_argument("--cpu", action="store_true", help="run on the CPU reference ops (plumbing / debugging)")
     ap.add_argument("--seed", type=int, default=0)
@@ -117,7 +120,8 @@ def build_runtime(args, with_scheduler: bool = True) -> Runtime:
     vocab = cfg.vocab_size
     sampler = SamplingWorkspace(ctx.device, vocab, seed=args.seed)
     engine = Engine(cfg, model, num_pages=ecfg.max_pages, max_batch=ecfg.batch_size, max_seq_len=args.max_model_len,
-                    cuda_graph=ecfg.cuda_graph, mtp=args.mtp, sampler=sampler)
+                    cuda_graph=ecfg.cuda_graph, mtp=args.mtp, sampler=sampler,
+                    phased_prefill=getattr(args, "phased_prefill", False) and ctx.world > 1)
     sched = None
     if with_scheduler:
         eos = list(getattr(cfg, "eos_token_ids", None) or getattr(cfg, "eos_token_id", None) or [])

@@ -34,8 +34,6 @@ def parse_args(argv=None):
     ap.add_argument("--presence-penalty", type=float, default=0.0)
     ap.add_argument("--repetition-penalty-window", type=int, default=64)
     ap.add_argument("--decode-latency", type=float, default=0.0, help="minimum milliseconds per decode step (rate limit)")
-    ap.add_argument("--phased-prefill", dest="phased_prefill", action="store_true", default=True)
-    ap.add_argument("--no-phased-prefill", dest="phased_prefill", action="store_false")
     ap.add_argument("--no-mtp", action="store_true", help="ignore --mtp")
     return ap.parse_args(argv)
 

@@ -188,6 +188,50 @@ class GlmMoeDsaModel:
         hidden, _ = self.comm.allreduce_add_rmsnorm(ops, partial, residual, self.w.final_norm, self.cfg.rms_norm_eps)
         return hidden
 
+    def forward_hidden_phased(self, sts, cache: KVCacheTensors, streams=None):
+        """Phased prefill: the chunk is cut into consecutive parts (normally two halves) that walk the layers
+        in lock step, part p on `streams[p]`.  Part p+1 starts layer i once part p has finished it (its KV
+        rows of that layer are then in the cache), so one part's collectives run under the other part's
+        GEMMs.  With `streams=None` the parts simply alternate on the current stream (CPU, tests).
+        Returns the parts' hidden states.  Reference: `forwardPhased` generators driven by
+        `planPhasedPrefill` (`src/chat_model.ts:204-282`, `src/glm51_model.ts:979-1003`)."""
+        import contextlib
+        ops, n, P = self.ops, self.cfg.num_hidden_layers, len(sts)
+        use_streams = streams is not None and sts[0].input_ids.is_cuda
+        ctx = (lambda p: torch.cuda.stream(streams[p])) if use_streams else (lambda p: contextlib.nullcontext())
+        if use_streams:
+            start = torch.cuda.Event()
+            start.record()
+            for s in streams:
+                s.wait_event(start)
+        partial, residual = [None] * P, [None] * P
+        for p, st in enumerate(sts):
+            with ctx(p):
+                partial[p] = ops.embed(st.input_ids, self.w.embed)
+                st.slots = st.lengths = None
+        self.comm.begin_forward()
+        done = [None] * P
+        for i in range(n):
+            for p, st in enumerate(sts):
+                with ctx(p):
+                    if use_streams and p > 0:
+                        streams[p].wait_event(done[p - 1])
+                    partial[p], residual[p] = self._layer(i, self.w.layers[i], partial[p], residual[p], st, cache,
+                                                          first=(i == 0), last=(i == n - 1))
+                    if use_streams:
+                        done[p] = torch.cuda.Event()
+                        done[p].record(streams[p])
+        hidden = []
+        for p in range(P):
+            with ctx(p):
+                h, _ = self.comm.allreduce_add_rmsnorm(ops, partial[p], residual[p], self.w.final_norm, self.cfg.rms_norm_eps)
+                hidden.append(h)
+        if use_streams:
+            cur = torch.cuda.current_stream()
+            for s in streams:
+                cur.wait_stream(s)
+        return hidden
+
     def forward_mtp(self, st: StepState, cache: KVCacheTensors, prev_hidden: torch.Tensor, depth: int = 0) -> torch.Tensor:
         """MTP layer: combines the embedding of the *next* token (st.input_ids) with the
         previous hidden state, runs one decoder layer, returns the head-normed hidden.

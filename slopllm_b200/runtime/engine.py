@@ -51,7 +51,8 @@ class StepBuffers:
 
 class Engine:
     def __init__(self, cfg: GlmMoeDsaConfig, model: GlmMoeDsaModel, num_pages: int, max_batch: int = 8,
-                 max_seq_len: int = 16384, cuda_graph: bool = True, mtp: int = 0, sampler=None):
+                 max_seq_len: int = 16384, cuda_graph: bool = True, mtp: int = 0, sampler=None, phased_prefill: bool = False,
+                 phased_min_tokens: int = 2048):
         self.cfg = cfg
         self.model = model
         self.ctx: ParallelContext = model.ctx
@@ -66,6 +67,11 @@ class Engine:
         self.graphs = CaptureManager(enabled=cuda_graph and self.device.type == "cuda")
         self.mtp = mtp
         self.sampler = sampler               # SamplingWorkspace (row b of a step <-> workspace row rows[b])
+        # phased prefill: a chunk of at least `phased_min_tokens` is run as two halves on two streams so that one
+        # half's collectives overlap the other half's GEMMs (only useful with more than one rank)
+        self.phased_prefill = phased_prefill and hasattr(model, "forward_hidden_phased")
+        self.phased_min_tokens = phased_min_tokens
+        self._phase_streams = None
         self._bufs = {}
         self._out_host = {}
         self.h2d_bytes = 0
@@ -125,7 +131,10 @@ class Engine:
                 positions = list(range(start, start + n))
                 st = self._eager_state(ids, positions, [0] * n, [s], max_kv_len=start + n)
                 self._prepare(st, [s])
-                hidden = self.model.forward_hidden(st, self.cache)
+                if self.phased_prefill and n >= self.phased_min_tokens:
+                    hidden = self._forward_phased(ids, positions, s, start, n)
+                else:
+                    hidden = self.model.forward_hidden(st, self.cache)
                 if self.mtp and getattr(self.cfg, "num_nextn_predict_layers", 0):
                     self._prefill_mtp(st, hidden, prompt, start, n)
                 self.kv.report_tokens(s)
@@ -142,6 +151,17 @@ class Engine:
                 tokens.append(int(self._greedy(last_hidden)[0]))
             hiddens.append(last_hidden)
         return tokens, (hiddens if want_hidden else None)
+
+    def _forward_phased(self, ids, positions, s: Sequence, start: int, n: int) -> torch.Tensor:
+        half = (n // 2 + 63) // 64 * 64
+        parts = [(0, half), (half, n)]
+        sts = [self._eager_state(ids[a:b], positions[a:b], [0] * (b - a), [s], max_kv_len=start + b) for a, b in parts]
+        streams = None
+        if self.device.type == "cuda":
+            if self._phase_streams is None:
+                self._phase_streams = [torch.cuda.Stream(self.device), torch.cuda.Stream(self.device)]
+            streams = self._phase_streams
+        return torch.cat(self.model.forward_hidden_phased(sts, self.cache, streams), 0)
 
     def _prefill_mtp(self, st: StepState, hidden, prompt, start: int, n: int) -> None:
         """Fill the MTP layer's KV over the chunk: position i pairs (h_i, token_{i+1})."""
