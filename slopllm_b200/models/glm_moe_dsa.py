@@ -88,6 +88,40 @@ class GlmMoeDsaModel:
         self.ctx = ctx or ParallelContext(device=weights.embed.device)
         self.ops = ops or get_ops(cfg, weights.embed.device, self.ctx)
         self.comm = comm or Comm(self.ctx)
+        # context-parallel fallback: gather every layer's KV rows into a flat replicated buffer and attend like a
+        # TP rank (no top-k / partial merge); SLOPLLM_B200_CP_GATHER_KV=1
+        from ..config import env_str
+        self.cp_gather_kv = env_str("CP_GATHER_KV") == "1"
+
+    # -- context parallelism, gather-KV mode ------------------------------------------------
+    def _gathered_view(self, lc: LayerCache, st: StepState):
+        """Flat replicated copy of the step's sequences' rows of one layer, and a StepState that addresses it.
+
+        Every rank reads its local rows (local index i of sequence b = global position i*W + r) through the page
+        table, the ranks all-gather them and interleave so that row b*L + p of the flat buffer is global position
+        p.  The returned state has an identity page table and no CP, so the ordinary TP attention path runs on it.
+        Reference: `gatherPages` + all-gather + `deinterleave` (`src/parallel_ops.ts:4139-4203`), the reference's
+        gather-KV mode (`shouldGatherKv`, `src/glm51_model.ts:380-413`)."""
+        W = st.cp_world
+        ps = st.page_size
+        B = st.page_table.shape[0]
+        n_local = -(-max(1, st.max_kv_len) // W)
+        n_local = -(-n_local // ps) * ps                                   # whole pages
+        dev = lc.kv.device
+        i = torch.arange(n_local, device=dev)
+        slots = (st.page_table[:, : n_local // ps].long().repeat_interleave(ps, dim=1) * ps + (i % ps).unsqueeze(0)).reshape(-1)
+
+        def flat(cache_t):
+            rows = cache_t[slots].view(B, n_local, -1)                      # this rank's rows, local order
+            allr = torch.stack(self.comm.all_gather_list(rows.contiguous()), dim=2)     # [B, n_local, W, bytes]
+            return allr.reshape(B * n_local * W, -1)                        # position p = i*W + r -> row b*L + p
+
+        L = n_local * W
+        table = (torch.arange(B, device=dev).unsqueeze(1) * (L // ps) + torch.arange(L // ps, device=dev).unsqueeze(0)).to(torch.int32)
+        st2 = StepState(input_ids=st.input_ids, positions=st.positions, batch_idx=st.batch_idx, page_table=table.contiguous(),
+                        logits_idx=st.logits_idx, page_size=ps, cp_world=1, cp_rank=0, slots=st.slots, lengths=st.lengths,
+                        max_kv_len=st.max_kv_len, extra=st.extra)
+        return LayerCache(flat(lc.kv), flat(lc.idx) if lc.idx is not None else None), st2
 
     # -- attention -------------------------------------------------------------------------
     def attention(self, layer: int, lw: LayerWeights, x: torch.Tensor, st: StepState, cache: KVCacheTensors):
@@ -97,6 +131,16 @@ class GlmMoeDsaModel:
         cq, idx_w = ops.attn_pre(qkv, lw, st, lc)
         qb = ops.linear(cq, lw.w_q_b, defer_reduce=True)
         q_abs, q_pe, q8, w_eff = ops.q_post(qb, lw, st, idx_w)
+        if ctx.cp and ctx.world > 1 and self.cp_gather_kv:
+            flat_lc, fst = self._gathered_view(lc, st)
+            if lw.has_indexer:
+                pos, _ = ops.indexer_topk(q8, w_eff, flat_lc, fst)
+                fst.slots, fst.lengths = ops.topk_to_slots(pos, fst)
+                st.slots, st.lengths = fst.slots, fst.lengths           # flat-buffer slots are valid for the sharing layers too
+            elif st.slots is None:
+                raise RuntimeError(f"layer {layer} shares indexer slots but no full-indexer layer ran before it")
+            o, _ = ops.sparse_mla(q_abs, q_pe, flat_lc, st.slots, st.lengths)
+            return ops.linear(ops.v_expand(o, lw.w_v), lw.o_proj, out_f32=True, sink=comm.partial_sink(x.shape[0]))
         if lw.has_indexer:
             pos, score = ops.indexer_topk(q8, w_eff, lc, st)
             if ctx.cp and ctx.world > 1:

@@ -102,7 +102,17 @@ class Comm:
         if W == 1:
             return send
         if self.ctx.device.type == "cuda":
-            raise RuntimeError("variable all_to_all goes through all_to_all_counts on CUDA")
+            # NCCL: exchange the row counts, then one all_to_all_single with per-peer split sizes
+            dev = self.ctx.device
+            mine = torch.tensor([s.shape[0] for s in send], dtype=torch.int64, device=dev)
+            counts = torch.stack(self.all_gather_list(mine)).tolist()            # counts[src][dst]
+            in_splits = [int(c) for c in counts[self.ctx.rank]]
+            out_splits = [int(counts[peer][self.ctx.rank]) for peer in range(W)]
+            tail = tuple(send[0].shape[1:])
+            inp = torch.cat([s.contiguous() for s in send], 0) if sum(in_splits) else torch.empty((0,) + tail, dtype=send[0].dtype, device=dev)
+            out = torch.empty((sum(out_splits),) + tail, dtype=send[0].dtype, device=dev)
+            dist.all_to_all_single(out, inp, out_splits, in_splits, group=self.ctx.group)
+            return list(out.split(out_splits, 0))
         recv: List[Optional[torch.Tensor]] = [None] * W
         # gloo has no all_to_all: W broadcast-free rounds of paired send/recv
         counts = self.all_gather_list(torch.tensor([s.shape[0] for s in send], dtype=torch.int64))

@@ -48,6 +48,20 @@ def test_cp2_matches_single():
     assert out[0] == out[1] == ref
 
 
+def _greedy_gather(rank, world, prompt_len, new):
+    import os
+    os.environ["SLOPLLM_B200_CP_GATHER_KV"] = "1"
+    return _greedy(rank, world, True, False, prompt_len, new)
+
+
+def test_cp2_gather_kv_mode_matches_single():
+    """Fallback CP mode: KV stays sharded by token, every layer's rows are gathered into a flat replicated
+    buffer and each rank attends like a TP rank (no top-k or partial merge)."""
+    ref = _greedy(0, 1, False, False, PROMPT, 10)
+    out = run_ranks(_greedy_gather, 2, PROMPT, 10)
+    assert out[0] == out[1] == ref
+
+
 def test_ep2_matches_single():
     ref = _greedy(0, 1, False, False, 40, 6)
     out = run_ranks(_greedy, 2, False, True, 40, 6)
