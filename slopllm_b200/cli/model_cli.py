@@ -35,8 +35,9 @@ def add_model_args(ap: argparse.ArgumentParser) -> None:
     ap.add_argument("--max-host-pages", type=int, default=0, help="pinned-host prefix tier size in pages (0: off)")
     ap.add_argument("--max-model-len", type=int, default=65536)
     ap.add_argument("--no-cuda-graph", action="store_true")
-    ap.add_argument("--phased-prefill", dest="phased_prefill", action="store_true", default=True,
-                    help="run large prefill chunks as two halves on two streams (multi-rank jobs)")
+    ap.add_argument("--phased-prefill", dest="phased_prefill", action="store_true", default=False,
+                    help="run large prefill chunks as two halves on two streams (multi-rank jobs); off by default: over "
+                         "NVLink the all-reduce is short and two half-size GEMM streams measured slower than one")
     ap.add_argument("--no-phased-prefill", dest="phased_prefill", action="store_false")
     ap.add_argument("--no-fused-collectives", action="store_true", help="NCCL collectives instead of the in-kernel NVLink ones")
     ap.add_argument("--cpu", action="store_true", help="run on the CPU reference ops (plumbing / debugging)")

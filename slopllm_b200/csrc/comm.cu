@@ -220,10 +220,12 @@ __global__ void cp_merge_push_kernel(CpPushCtx c, const float* __restrict__ o, c
     // grid (h, T): one block per (head, token)
     const int head = blockIdx.x, t = blockIdx.y;
     const int owner = head / c.hl, hh = head % c.hl;
+    // staging is double-buffered by epoch parity (see gather_push_kernel)
+    const size_t par = *c.epoch & 1u;
     const float4* src = reinterpret_cast<const float4*>(o + ((size_t)t * c.h + head) * c.R);
-    float4* dst = reinterpret_cast<float4*>(c.o_stage[owner] + (((size_t)c.rank * c.Tmax + t) * c.hl + hh) * c.R);
+    float4* dst = reinterpret_cast<float4*>(c.o_stage[owner] + (((par * c.world + c.rank) * c.Tmax + t) * c.hl + hh) * c.R);
     for (int i = threadIdx.x; i < c.R / 4; i += blockDim.x) dst[i] = src[i];
-    if (threadIdx.x == 0) c.lse_stage[owner][((size_t)c.rank * c.Tmax + t) * c.hl + hh] = lse[(size_t)t * c.h + head];
+    if (threadIdx.x == 0) c.lse_stage[owner][((par * c.world + c.rank) * c.Tmax + t) * c.hl + hh] = lse[(size_t)t * c.h + head];
     __syncthreads();
     if (threadIdx.x == 0) {
         // device-scope fence here, system-scope fence once in the last block: the counter chains the blocks' stores
@@ -275,9 +277,12 @@ struct GatherPushCtx {
 
 __global__ void gather_push_kernel(GatherPushCtx c, const uint4* __restrict__ src, size_t n16) {
     pdl_grid_sync();
+    // two buffer halves, chosen by the parity of the epoch: a rank can be at most one collective ahead of the slowest
+    // one (it waits for every rank's flag each time), so it never overwrites a half that a peer is still reading
+    const size_t half = (size_t)(*c.epoch & 1u) * c.world * c.slot_bytes;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += (size_t)gridDim.x * blockDim.x) {
         const uint4 v = src[i];
-        for (int p = 0; p < c.world; ++p) reinterpret_cast<uint4*>(c.bufs[p] + (size_t)c.rank * c.slot_bytes)[i] = v;
+        for (int p = 0; p < c.world; ++p) reinterpret_cast<uint4*>(c.bufs[p] + half + (size_t)c.rank * c.slot_bytes)[i] = v;
     }
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -292,6 +297,31 @@ __global__ void gather_push_kernel(GatherPushCtx c, const uint4* __restrict__ sr
             for (int p = 0; p < c.world; ++p) st_relaxed_sys_u32(c.flags[p] + c.rank, e);
         }
     }
+}
+
+// Copy the `world` slots of the half that the just-completed gather used (the epoch was advanced by the wait kernel,
+// so that half is (epoch - 1) & 1) into a private tensor [world, bytes].  Reading the parity on the device keeps the
+// sequence valid inside a replayed CUDA graph.
+__global__ void gather_fetch_kernel(uint4* __restrict__ out, const uint8_t* __restrict__ local_buf, const uint32_t* __restrict__ epoch,
+                                    int world, size_t slot_bytes, size_t n16) {
+    pdl_grid_sync();
+    const size_t half = (size_t)((*epoch - 1u) & 1u) * world * slot_bytes;
+    const size_t total = (size_t)world * n16;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / n16, j = i % n16;
+        out[i] = reinterpret_cast<const uint4*>(local_buf + half + r * slot_bytes)[j];
+    }
+}
+
+SL_API int sl_gather_fetch(void* out, const void* local_buf, const void* epoch, int world, size_t slot_bytes, size_t bytes,
+                           cudaStream_t s) {
+    if (bytes == 0) return 0;
+    if (bytes % 16 != 0 || bytes > slot_bytes) return -1;
+    const size_t n16 = bytes / 16;
+    int blocks = (int)((world * n16 + 255) / 256);
+    if (blocks > 148) blocks = 148;
+    sl_launch(gather_fetch_kernel, blocks, 256, 0, s, (uint4*)out, (const uint8_t*)local_buf, (const uint32_t*)epoch, world, slot_bytes, n16);
+    return SL_LAUNCH_CHECK();
 }
 
 SL_API int sl_gather_push(const GatherPushCtx* c, const void* src, size_t bytes, cudaStream_t s) {

@@ -183,6 +183,10 @@ struct CombineParams {
     void* o_out;                         // [T, head_count, R] bf16 (or fp32 when out_f32)
     float* lse_out;                      // [T, head_count] or null
     int out_f32;
+    // double-buffered staging (context-parallel merge): when parity_epoch is set, every input pointer is advanced
+    // by ((*parity_epoch - 1) & 1) strides; reading the parity on the device keeps a replayed CUDA graph valid
+    const uint32_t* parity_epoch;
+    long long parity_o_stride, parity_lse_stride;     // in floats
 };
 
 __global__ void __launch_bounds__(128) mla_combine_kernel(CombineParams p) {
@@ -192,11 +196,13 @@ __global__ void __launch_bounds__(128) mla_combine_kernel(CombineParams p) {
     __shared__ float scratch[33];
     const int np = p.n_buf * p.parts_per_buf;
     const size_t th = (size_t)t * p.h + head;
+    const size_t par = p.parity_epoch != nullptr ? ((*p.parity_epoch - 1u) & 1u) : 0u;
+    const size_t po = par * (size_t)p.parity_o_stride, pl = par * (size_t)p.parity_lse_stride;
     // weights: one partial per thread (np <= 512 -> up to 4 per thread)
     float mx = -INFINITY;
     for (int i = threadIdx.x; i < np; i += blockDim.x) {
         const int b = i / p.parts_per_buf, q = i % p.parts_per_buf;
-        const float l = p.lse_ptrs[b][th * p.parts_per_buf + q];
+        const float l = p.lse_ptrs[b][pl + th * p.parts_per_buf + q];
         wsh[i] = l;
         mx = fmaxf(mx, l);
     }
@@ -221,7 +227,7 @@ __global__ void __launch_bounds__(128) mla_combine_kernel(CombineParams p) {
                 const int i = min(i0 + u, np - 1);
                 const int b = i / p.parts_per_buf, q = i % p.parts_per_buf;
                 w[u] = (i0 + u < np) ? wsh[i] : 0.f;
-                v[u] = *reinterpret_cast<const float4*>(p.o_ptrs[b] + (th * p.parts_per_buf + q) * p.R + d);
+                v[u] = *reinterpret_cast<const float4*>(p.o_ptrs[b] + po + (th * p.parts_per_buf + q) * p.R + d);
             }
 #pragma unroll
             for (int u = 0; u < 4; ++u) {

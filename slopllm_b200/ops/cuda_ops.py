@@ -275,7 +275,7 @@ class CudaOps:
     def combine_f32(self, o_parts, lse_parts):
         return self.combine(o_parts, lse_parts, out_f32=True)
 
-    def combine(self, o_parts, lse_parts, head_begin=0, head_count=None, want_lse=True, rows=None, out_f32=False):
+    def combine(self, o_parts, lse_parts, head_begin=0, head_count=None, want_lse=True, rows=None, out_f32=False, parity=None):
         """o_parts: list of [T, h, S, R] fp32 buffers (one per rank under CP); `rows` limits the
         token rows processed when the buffers are staging areas with spare capacity."""
         T, h, S, Rr = o_parts[0].shape
@@ -286,6 +286,8 @@ class CudaOps:
         lse = torch.empty(T, head_count, dtype=torch.float32, device=dev) if want_lse else None
         p = N.CombineParams(n_buf=len(o_parts), parts_per_buf=S, h=h, R=Rr, head_begin=head_begin, head_count=head_count,
                             o_out=o.data_ptr(), lse_out=N.ptr(lse), out_f32=int(out_f32))
+        if parity is not None:          # (epoch word address, o stride, lse stride): double-buffered staging, see csrc/sparse_mla.cu
+            p.parity_epoch, p.parity_o_stride, p.parity_lse_stride = parity
         for i, (a, b) in enumerate(zip(o_parts, lse_parts)):
             p.o_ptrs[i] = a.data_ptr()
             p.lse_ptrs[i] = b.data_ptr()

@@ -101,7 +101,8 @@ class SparseMlaParams(C.Structure):
 
 class CombineParams(C.Structure):
     _fields_ = [("o_ptrs", vp * 8), ("lse_ptrs", vp * 8), ("n_buf", i32), ("parts_per_buf", i32), ("h", i32), ("R", i32),
-                ("head_begin", i32), ("head_count", i32), ("o_out", vp), ("lse_out", vp), ("out_f32", i32)]
+                ("head_begin", i32), ("head_count", i32), ("o_out", vp), ("lse_out", vp), ("out_f32", i32), ("parity_epoch", vp),
+                ("parity_o_stride", i64), ("parity_lse_stride", i64)]
 
 
 class MoeGateUpParams(C.Structure):
@@ -150,6 +151,7 @@ _SIGS = {
     "sl_q_post_absorb": [C.POINTER(QPostParams), vp, vp, i32, i32, vp],
     "sl_bmv": [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i64, vp],
     "sl_smallT_splits": [i32, i32, i32],
+    "sl_gather_fetch": [vp, vp, vp, i32, C.c_size_t, C.c_size_t, vp],
     "sl_quantize_fp8": [vp, vp, vp, i32, i32, vp],
     "sl_prefetch_l2": [vp, C.c_size_t, vp],
     "sl_gather_mark": [vp, vp, vp, i32, i32, vp],

@@ -157,12 +157,12 @@ class SymmetricRegion:
         lay = {"flags": [take(4 * MAX_RANKS * 2) for _ in range(8)], "data": []}
         for _ in range(cls.NUM_BUFS):
             lay["data"].append(take(world * slot_rows * row_len * 8))      # {fp32 value, tag} per element
-        lay["gather"] = take(world * gather_bytes) if gather_bytes else 0
+        lay["gather"] = take(2 * world * gather_bytes) if gather_bytes else 0          # two halves (epoch parity)
         if cp_shape is not None:
             Tmax, h, R = cp_shape
             hl = h // world
-            lay["cp_o"] = take(world * Tmax * hl * R * 4)
-            lay["cp_lse"] = take(world * Tmax * hl * 4)
+            lay["cp_o"] = take(2 * world * Tmax * hl * R * 4)                          # two halves (epoch parity)
+            lay["cp_lse"] = take(2 * world * Tmax * hl * 4)
         lay["total"] = off
         return lay
 
@@ -265,16 +265,13 @@ class NvlinkComm(Comm):
         if g is None or nbytes % 16 != 0 or nbytes > self.region.gather_bytes or self.ctx.world == 1:
             return super().all_gather_list(x)
         x = x.contiguous()
+        W, rg = self.ctx.world, self.region
+        epoch = rg.state.data_ptr() + 4 * 3
         N.call("sl_gather_push", C.byref(g), x.data_ptr(), nbytes, N.stream())
-        W = self.ctx.world
-        rg = self.region
-        N.call("sl_epoch_wait", rg.peer_ptrs[rg.rank] + rg.lay["flags"][3], rg.state.data_ptr() + 4 * 3, W, rg.wait_spins,
-               rg.status_ptr, 4, N.stream())
-        parts = []
-        for r in range(W):
-            raw = rg.local_view(rg.lay["gather"] + r * rg.gather_bytes, nbytes)
-            parts.append(raw.view(x.dtype).view(x.shape).clone())
-        return parts
+        N.call("sl_epoch_wait", rg.peer_ptrs[rg.rank] + rg.lay["flags"][3], epoch, W, rg.wait_spins, rg.status_ptr, 4, N.stream())
+        out = torch.empty((W,) + tuple(x.shape), dtype=x.dtype, device=x.device)
+        N.call("sl_gather_fetch", out.data_ptr(), rg.peer_ptrs[rg.rank] + rg.lay["gather"], epoch, W, rg.gather_bytes, nbytes, N.stream())
+        return list(out.unbind(0))
 
     def all_gather(self, x: torch.Tensor, dim: int = -1) -> torch.Tensor:
         if self.ctx.world == 1:
@@ -299,7 +296,9 @@ class NvlinkComm(Comm):
         Tmax, hl = rg.cp_shape[0], h // W
         stage_o = rg.local_view(rg.lay["cp_o"], W * Tmax * hl * R * 4).view(torch.float32).view(W, Tmax, hl, 1, R)
         stage_l = rg.local_view(rg.lay["cp_lse"], W * Tmax * hl * 4).view(torch.float32).view(W, Tmax, hl, 1)
-        merged, _ = ops.combine([stage_o[i] for i in range(W)], [stage_l[i] for i in range(W)], rows=T, want_lse=False)
+        # the half of the staging area that this merge used is chosen on the device from the epoch word
+        merged, _ = ops.combine([stage_o[i] for i in range(W)], [stage_l[i] for i in range(W)], rows=T, want_lse=False,
+                                parity=(rg.state.data_ptr() + 4 * 4, W * Tmax * hl * R, W * Tmax * hl))
         return merged
 
     def check_status(self) -> None:

@@ -139,24 +139,26 @@ def test_cp_merge_push_emulated():
     # emulate: every rank pushes, then every rank merges
     from slopllm_b200.ops import native as N
     import ctypes as C
-    staged = []
-    for r in range(W):
-        o, lse = ops.combine_f32([o_parts[r]], [l_parts[r]])
-        staged.append((o, lse))
-        N.call("sl_cp_merge_push", C.byref(regions[r].cp_ctx), o.data_ptr(), lse.data_ptr(), T, N.stream())
-    allo = torch.stack([s[0] for s in staged])
-    alll = torch.stack([s[1] for s in staged])
-    expect, _ = R.merge_attention_partials(allo, alll)
     hl = h // W
-    for r in range(W):
-        rg = regions[r]
-        N.call("sl_epoch_wait", rg.peer_ptrs[r] + rg.lay["flags"][4], rg.state.data_ptr() + 16, W, rg.wait_spins,
-               rg.status_ptr, 5, N.stream())
-        so = rg.local_view(rg.lay["cp_o"], W * 32 * hl * Rr * 4).view(torch.float32).view(W, 32, hl, 1, Rr)
-        sl = rg.local_view(rg.lay["cp_lse"], W * 32 * hl * 4).view(torch.float32).view(W, 32, hl, 1)
-        merged, _ = ops.combine([so[i] for i in range(W)], [sl[i] for i in range(W)], rows=T, want_lse=False)
-        _close(merged, expect[:, r * hl:(r + 1) * hl])
-        rg.check_status()
+    for rnd in range(3):                     # three merges in a row: the staging halves alternate with the epoch parity
+        staged = []
+        for r in range(W):
+            o, lse = ops.combine_f32([o_parts[r] * (rnd + 1)], [l_parts[r]])
+            staged.append((o, lse))
+            N.call("sl_cp_merge_push", C.byref(regions[r].cp_ctx), o.data_ptr(), lse.data_ptr(), T, N.stream())
+        allo = torch.stack([s[0] for s in staged])
+        alll = torch.stack([s[1] for s in staged])
+        expect, _ = R.merge_attention_partials(allo, alll)
+        for r in range(W):
+            rg = regions[r]
+            N.call("sl_epoch_wait", rg.peer_ptrs[r] + rg.lay["flags"][4], rg.state.data_ptr() + 16, W, rg.wait_spins,
+                   rg.status_ptr, 5, N.stream())
+            so = rg.local_view(rg.lay["cp_o"], W * 32 * hl * Rr * 4).view(torch.float32).view(W, 32, hl, 1, Rr)
+            sl = rg.local_view(rg.lay["cp_lse"], W * 32 * hl * 4).view(torch.float32).view(W, 32, hl, 1)
+            merged, _ = ops.combine([so[i] for i in range(W)], [sl[i] for i in range(W)], rows=T, want_lse=False,
+                                    parity=(rg.state.data_ptr() + 16, W * 32 * hl * Rr, W * 32 * hl))
+            _close(merged, expect[:, r * hl:(r + 1) * hl])
+            rg.check_status()
 
 
 # ---- real multi-GPU -------------------------------------------------------------------------------
@@ -168,7 +170,8 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _mgpu_worker(rank, world, port, q):
+def _mgpu_worker(rank, world, port, q, cp=False):
+    import dataclasses
     import traceback
     os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
                       MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
@@ -180,6 +183,8 @@ def _mgpu_worker(rank, world, port, q):
         from slopllm_b200.parallel.fused import make_comm
         from slopllm_b200.runtime.engine import Engine
         ctx = init_from_env()
+        if cp:
+            ctx = dataclasses.replace(ctx, cp=True)      # KV tokens interleaved over the ranks, weights stay TP-sharded
         cfg = GlmMoeDsaConfig(hidden_size=1024, intermediate_size=2048, moe_intermediate_size=512, num_hidden_layers=3,
                               num_nextn_predict_layers=0, vocab_size=2048, num_attention_heads=8, q_lora_rank=256,
                               n_routed_experts=16, num_experts_per_tok=4, n_group=4, topk_group=2, index_topk=64,
@@ -211,13 +216,16 @@ def _mgpu_worker(rank, world, port, q):
 
 
 @pytest.mark.multigpu
-def test_tp2_fused_equals_nccl_on_two_gpus():
+@pytest.mark.parametrize("cp", [False, True])
+def test_tp2_fused_equals_nccl_on_two_gpus(cp):
+    """Prefill + graph-captured decode on two GPUs, in-kernel NVLink collectives against NCCL; with `cp` the KV is
+    sharded by token and the indexer top-k / attention partials are merged across the ranks."""
     import torch.multiprocessing as mp
     world = 2
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_mgpu_worker, args=(r, world, port, q), daemon=True) for r in range(world)]
+    procs = [ctx.Process(target=_mgpu_worker, args=(r, world, port, q, cp), daemon=True) for r in range(world)]
     for p in procs:
         p.start()
     res = {}
