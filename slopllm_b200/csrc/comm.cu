@@ -86,7 +86,7 @@ __device__ __forceinline__ float4 ll_gather_sum(const RecvCtx& c, int t, int i, 
 // One block per token row.  H % 4 == 0, H <= 16384.  Sums the ranks' slots in rank order (deterministic).
 __global__ void __launch_bounds__(512) ar_add_rmsnorm_kernel(RecvCtx c, bf16* __restrict__ out, float* __restrict__ res_out,
                                                               const float* __restrict__ res_in, const bf16* __restrict__ w,
-                                                              int H, float eps) {
+                                                              int H, float eps, uint4* __restrict__ xp) {
     pdl_grid_sync();
     __shared__ float scratch[33];
     const int t = blockIdx.x, nt = blockDim.x, n4 = H / 4;
@@ -119,6 +119,7 @@ __global__ void __launch_bounds__(512) ar_add_rmsnorm_kernel(RecvCtx c, bf16* __
             o.x = f2_to_bf162(v[q].x * inv * w0.x, v[q].y * inv * w0.y);
             o.y = f2_to_bf162(v[q].z * inv * w1.x, v[q].w * inv * w1.y);
             reinterpret_cast<uint2*>(out + (size_t)t * H)[i] = o;
+            if (xp != nullptr) store_perm4(xp, t, H, i, o.x, o.y);
         }
     }
     // the last block to finish closes the epoch (producers of the next use read it)
@@ -135,13 +136,14 @@ __global__ void __launch_bounds__(512) ar_add_rmsnorm_kernel(RecvCtx c, bf16* __
 }
 
 SL_API int sl_ar_add_rmsnorm(const RecvCtx* c, void* out, void* res_out, const void* res_in, const void* w, int T, int H,
-                             float eps, cudaStream_t s) {
+                             float eps, void* xp, cudaStream_t s) {
     if (T == 0) return 0;
-    if (H % 4 != 0 || H > 16384 || c->world > SL_MAX_RANKS) return -1;
+    if (H % 4 != 0 || H > 16384 || c->world > SL_MAX_RANKS || (xp != nullptr && H % 128 != 0)) return -1;
     int threads = ((H / 4 + 3) / 4 + 31) / 32 * 32;           // four float4 per thread up to H = 8192, eight beyond
     if (threads < 128) threads = 128;
     if (threads > 512) threads = 512;
-    sl_launch(ar_add_rmsnorm_kernel, T, threads, 0, s, *c, (bf16*)out, (float*)res_out, (const float*)res_in, (const bf16*)w, H, eps);
+    sl_launch(ar_add_rmsnorm_kernel, T, threads, 0, s, *c, (bf16*)out, (float*)res_out, (const float*)res_in, (const bf16*)w, H, eps,
+              (uint4*)xp);
     return SL_LAUNCH_CHECK();
 }
 

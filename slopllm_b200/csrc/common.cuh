@@ -22,15 +22,47 @@ typedef __nv_bfloat162 bf162;
 // the kernels it depends on have finished and their writes are visible.  Nothing that reads or
 // writes activation memory may precede it.  On a launch without the programmatic attribute both
 // instructions do nothing.
-#ifndef SL_PDL_EARLY_TRIGGER
-#define SL_PDL_EARLY_TRIGGER 0
+// SL_PDL_MODE selects where a kernel lets its successor start:
+//   0  at kernel exit (implicit trigger): only the launch latency overlaps
+//   1  after the main loop of the heavy kernels (pdl_trigger_late): the successor's blocks become resident and run
+//      their prologue under this kernel's epilogue
+//   2  at kernel entry, and the weight-streaming kernels prefetch their first weight rows into L2 before they wait
+//      for the predecessor (weights do not depend on it), so consecutive kernels' memory streams overlap
+#ifndef SL_PDL_MODE
+#define SL_PDL_MODE 0
 #endif
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_grid_sync() {
-#if SL_PDL_EARLY_TRIGGER
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+#if SL_PDL_MODE == 2
+    pdl_trigger();
 #endif
-    asm volatile("griddepcontrol.wait;" ::: "memory");
+    pdl_wait();
 }
+__device__ __forceinline__ void pdl_trigger_late() {
+#if SL_PDL_MODE == 1
+    pdl_trigger();
+#endif
+}
+__device__ __forceinline__ void prefetch_l2_line(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+// All threads of the block: prefetch `rows` rows of `row_bytes` bytes starting at `base` (row stride = row_bytes).
+__device__ __forceinline__ void prefetch_l2_rows(const void* base, int rows, size_t row_bytes, size_t max_bytes_per_row = 1 << 20) {
+    const size_t rb = row_bytes < max_bytes_per_row ? row_bytes : max_bytes_per_row;
+    const int lines = (int)((rb + 127) / 128);
+    for (int i = threadIdx.x; i < rows * lines; i += blockDim.x)
+        prefetch_l2_line(reinterpret_cast<const uint8_t*>(base) + (size_t)(i / lines) * row_bytes + (size_t)(i % lines) * 128);
+}
+// Kernel entry of a weight-streaming kernel: `PREFETCH` may only touch memory that no kernel of the step writes.
+#if SL_PDL_MODE == 2
+#define PDL_ENTRY_WITH_PREFETCH(PREFETCH) \
+    do {                                  \
+        pdl_trigger();                    \
+        PREFETCH;                         \
+        pdl_wait();                       \
+    } while (0)
+#else
+#define PDL_ENTRY_WITH_PREFETCH(PREFETCH) pdl_grid_sync()
+#endif
 
 // Process-wide switch (sl_set_pdl); on by default.
 extern int g_sl_pdl_enabled;
@@ -148,6 +180,21 @@ __device__ __forceinline__ float pow2_scale_ceil(float amax) {
     uint32_t bits = __float_as_uint(raw);
     if (bits & 0x007fffffu) bits = (bits + 0x00800000u) & 0x7f800000u;
     return __uint_as_float(bits);
+}
+
+// ---- permuted f16 activation copy for the NVFP4 tensor-core kernels --------------------------------
+// 16-byte unit (token, group, j, c) of the copy holds x[token][group*128 + c*32 + j*8 .. +7] at unit index
+// (token*G + group)*16 + j*4 + c, G = K/128 (see permute_x_kernel, csrc/gemv_mma.cu).  A producer that already
+// has four consecutive bf16-rounded values of a row (columns 4i .. 4i+3, packed as two bf16x2 words) stores its
+// half unit here, which saves the separate permute launch in front of the consumer.
+__device__ __forceinline__ void store_perm4(uint4* xp, int tok, int K, int i, uint32_t lo_bf162, uint32_t hi_bf162) {
+    const int u = i >> 1, group = u >> 4, within = u & 15, c = within >> 2, j = within & 3;
+    const float2 a = bf162_to_f2(lo_bf162), b = bf162_to_f2(hi_bf162);
+    const __half2 h0 = __floats2half2_rn(a.x, a.y), h1 = __floats2half2_rn(b.x, b.y);
+    uint2 v;
+    v.x = *reinterpret_cast<const uint32_t*>(&h0);
+    v.y = *reinterpret_cast<const uint32_t*>(&h1);
+    reinterpret_cast<uint2*>(xp + ((size_t)tok * (K / 128) + group) * 16 + j * 4 + c)[i & 1] = v;
 }
 
 // ---- index self-checks ----------------------------------------------------------------------------

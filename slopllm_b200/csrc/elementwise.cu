@@ -39,7 +39,7 @@ SL_API int sl_embed(void* out, const void* ids, const void* table, int T, int H,
 template <bool XF32>
 __global__ void __launch_bounds__(1024) add_rmsnorm_kernel(bf16* __restrict__ out, float* __restrict__ res_out,
                                                            const void* __restrict__ xin, const float* __restrict__ res_in,
-                                                           const bf16* __restrict__ w, int H, float eps) {
+                                                           const bf16* __restrict__ w, int H, float eps, uint4* __restrict__ xp) {
     pdl_grid_sync();
     __shared__ float scratch[33];
     const int t = blockIdx.x, nt = blockDim.x, n4 = H / 4;
@@ -78,21 +78,26 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_kernel(bf16* __restrict__ ou
             o.x = f2_to_bf162(v[q].x * inv * w0.x, v[q].y * inv * w0.y);
             o.y = f2_to_bf162(v[q].z * inv * w1.x, v[q].w * inv * w1.y);
             reinterpret_cast<uint2*>(out + (size_t)t * H)[i] = o;
+            if (xp != nullptr) store_perm4(xp, t, H, i, o.x, o.y);
         }
     }
 }
 
+// `xp` (optional): also write the normed row as the permuted f16 copy that the NVFP4 tensor-core kernels consume
+// (H % 128 == 0; rows of the copy beyond T are never read for valid outputs).
 SL_API int sl_add_rmsnorm(void* out, void* res_out, const void* x, const void* res_in, const void* w, int T, int H,
-                          float eps, int x_f32, cudaStream_t s) {
+                          float eps, int x_f32, void* xp, cudaStream_t s) {
     if (T == 0) return 0;
-    if (H % 4 != 0 || H > 16384) return -1;
+    if (H % 4 != 0 || H > 16384 || (xp != nullptr && H % 128 != 0)) return -1;
     int threads = ((H / 4 + 3) / 4 + 31) / 32 * 32;      // 4 chunks per thread when possible
     if (threads < 128) threads = 128;
     if (threads > 1024) threads = 1024;
     if (x_f32)
-        sl_launch(add_rmsnorm_kernel<true>, T, threads, 0, s, (bf16*)out, (float*)res_out, x, (const float*)res_in, (const bf16*)w, H, eps);
+        sl_launch(add_rmsnorm_kernel<true>, T, threads, 0, s, (bf16*)out, (float*)res_out, x, (const float*)res_in, (const bf16*)w, H, eps,
+                  (uint4*)xp);
     else
-        sl_launch(add_rmsnorm_kernel<false>, T, threads, 0, s, (bf16*)out, (float*)res_out, x, (const float*)res_in, (const bf16*)w, H, eps);
+        sl_launch(add_rmsnorm_kernel<false>, T, threads, 0, s, (bf16*)out, (float*)res_out, x, (const float*)res_in, (const bf16*)w, H, eps,
+                  (uint4*)xp);
     return SL_LAUNCH_CHECK();
 }
 

@@ -61,7 +61,25 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
     __syncthreads();
     tc::fence_after_sync();
     const uint32_t tmem_base = *tmem_holder;
+    // Swap-AB weight streaming: operand A is the weight matrix, which no kernel of the step writes, so (SL_PDL_MODE 2)
+    // the producer starts the first ring of weight tiles before waiting for the predecessor's activations.
+    int pre = 0;
+#if SL_PDL_MODE == 2
+    pdl_trigger();
+    if (transpose_out && tiles == nullptr && warp == 0 && lane == 0) {
+        const int tkb = (K + BK - 1) / BK;
+        const int k0 = kb_per_split > 0 ? (int)blockIdx.z * kb_per_split : 0;
+        const int nkb = kb_per_split > 0 ? max(0, min(kb_per_split, tkb - k0)) : tkb;
+        pre = min(STAGES, nkb);
+        for (int kb = 0; kb < pre; ++kb) {
+            tc::mbar_expect_tx(&full[kb], Cfg::A_BYTES + Cfg::B_BYTES);
+            tc::tma_load_2d(sA + kb * Cfg::A_BYTES, &tmA, &full[kb], (k0 + kb) * BK, (int)blockIdx.y * BM);
+        }
+    }
+    pdl_wait();
+#else
     pdl_grid_sync();
+#endif
 
     // Plain GEMM: tile (blockIdx.y, blockIdx.x).  Grouped GEMM: blockIdx.x indexes a tile table whose
     // entries are {first A row, end of the group's A rows, first B row of the group, output column};
@@ -88,6 +106,10 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
             for (int kb = 0; kb < num_kb; ++kb) {
                 const int s = kb % STAGES;
                 const uint32_t ph = (kb / STAGES) & 1;
+                if (kb < pre) {           // weight tile already in flight (issued before the dependency wait)
+                    tc::tma_load_2d(sB + s * Cfg::B_BYTES, &tmB, &full[s], (kb0 + kb) * BK, b_row0);
+                    continue;
+                }
                 if (!tc::mbar_wait(&empty[s], ph ^ 1)) { atomicExch(err, 1); break; }
                 tc::mbar_expect_tx(&full[s], Cfg::A_BYTES + Cfg::B_BYTES);
                 tc::tma_load_2d(sA + s * Cfg::A_BYTES, &tmA, &full[s], (kb0 + kb) * BK, m0);
@@ -112,6 +134,7 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
                 tc::mma_commit(&empty[s]);
             }
             tc::mma_commit(tmem_full);       // arrives when every MMA above has finished (at once if there were none)
+            pdl_trigger_late();
         }
     } else {
         const int q = warp & 3;               // TMEM lane quarter this warp may access

@@ -14,7 +14,11 @@ template <int TT, int R>
 __global__ void __launch_bounds__(256) gemv_bf16_kernel(void* __restrict__ y, const bf16* __restrict__ x,
                                                         const bf16* __restrict__ W, int T, int N, int K, int ldx,
                                                         int out_f32, const float* __restrict__ bias) {
-    pdl_grid_sync();
+    // first rows of every warp of this block: 8 warps x R rows, whole rows
+    PDL_ENTRY_WITH_PREFETCH({
+        const int first = blockIdx.x * 8 * R;
+        if (first < N) prefetch_l2_rows(W + (size_t)first * K, min(8 * R, N - first), (size_t)K * 2);
+    });
     extern __shared__ __align__(16) unsigned char smraw[];
     bf16* xs = reinterpret_cast<bf16*>(smraw);           // [TT][K]
     const int t0 = blockIdx.y * TT;
@@ -74,6 +78,7 @@ __global__ void __launch_bounds__(256) gemv_bf16_kernel(void* __restrict__ y, co
                 }
             }
     }
+    pdl_trigger_late();
 }
 
 // Small N (router, narrow projections): one block per output row, the 256 threads split K.
@@ -236,7 +241,13 @@ __global__ void __launch_bounds__(256) gemv_nvfp4_kernel(void* __restrict__ y, c
                                                          const uint8_t* __restrict__ Wp, const uint8_t* __restrict__ S,
                                                          const float* __restrict__ gscale, int T, int N, int K, int ldx,
                                                          int out_f32) {
-    pdl_grid_sync();
+    PDL_ENTRY_WITH_PREFETCH({
+        const int first = blockIdx.x * 8 * R;
+        if (first < N) {
+            prefetch_l2_rows(Wp + (size_t)first * (K / 2), min(8 * R, N - first), (size_t)K / 2);
+            prefetch_l2_rows(S + (size_t)first * (K / 16), min(8 * R, N - first), (size_t)K / 16);
+        }
+    });
     extern __shared__ __align__(16) unsigned char smraw[];
     __half* xs = reinterpret_cast<__half*>(smraw);
     const int t0 = blockIdx.y * TT;

@@ -147,7 +147,15 @@ __global__ void __launch_bounds__(256) linear_nvfp4_mma_kernel(void* __restrict_
                                                                const uint8_t* __restrict__ Wp, const uint8_t* __restrict__ S,
                                                                const float* __restrict__ gscale, int T, int N, int K,
                                                                int ksplit, int out_f32, int use_push, PushCtx push) {
-    pdl_grid_sync();
+    // this block's weight rows (8 / ksplit tiles of MT*16 features, all of K) and their block scales
+    PDL_ENTRY_WITH_PREFETCH({
+        const int first = blockIdx.x * (8 / ksplit) * MT * 16;
+        if (first < N) {
+            const int rows = min((8 / ksplit) * MT * 16, N - first);
+            prefetch_l2_rows(Wp + (size_t)first * (K / 2), rows, (size_t)K / 2);
+            prefetch_l2_rows(S + (size_t)first * (K / 16), rows, (size_t)K / 16);
+        }
+    });
     extern __shared__ float red[];
     constexpr int ROWS = MT * 16, TOK = NT * 8;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -169,6 +177,7 @@ __global__ void __launch_bounds__(256) linear_nvfp4_mma_kernel(void* __restrict_
         warp_rows_times_tokens<MT, NT>(acc, Wp + (size_t)n0 * (K / 2), S + (size_t)n0 * (K / 16), K / 2, K / 16, row0, valid, K,
                                        xp, tok, kpart, ksplit);
     }
+    pdl_trigger_late();
     float* mine = red + (size_t)warp * (TOK * ROWS);
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt)
@@ -204,7 +213,8 @@ int launch_linear(void* y, const void* x, void* xp, const void* Wp, const void* 
                   int out_f32, const PushCtx* push, cudaStream_t s) {
     constexpr int ROWS = MT * 16, TOK = NT * 8;
     const int units = TOK * (K / 8);
-    sl_launch(permute_x_kernel, (units + 255) / 256, 256, 0, s, (uint4*)xp, (const bf16*)x, T, TOK, K, ldx);
+    // x == nullptr: the producer of the activations already wrote the permuted copy into xp
+    if (x != nullptr) sl_launch(permute_x_kernel, (units + 255) / 256, 256, 0, s, (uint4*)xp, (const bf16*)x, T, TOK, K, ldx);
     int ksplit = 8;
     while (ksplit > 1 && K / 128 < ksplit) ksplit >>= 1;
     // few rows: keep the reduction split so that there are enough blocks to fill the machine
@@ -597,6 +607,7 @@ struct MoeGroupedArgs {
     void* plan;          // int32 [max_items * 9 + 1]
     int max_items;
     void* out;           // f32 [T, H] (ignored when pushing)
+    int xp_ready;        // the activations' producer already wrote the permuted copy into xp
 };
 
 // Optional router stage: with it the layer starts from the normed hidden state alone and writes the chosen
@@ -658,7 +669,8 @@ SL_API int sl_moe_grouped_mma(const MoeGroupedArgs* a, const MoeRouterArgs* r, c
     }
     const int tpad = (a->T + 7) / 8 * 8;
     const int units = tpad * (a->H / 8);
-    sl_launch(permute_x_kernel, (units + 255) / 256, 256, 0, s, (uint4*)a->xp, (const bf16*)a->x, a->T, tpad, a->H, a->ldx);
+    if (!a->xp_ready)
+        sl_launch(permute_x_kernel, (units + 255) / 256, 256, 0, s, (uint4*)a->xp, (const bf16*)a->x, a->T, tpad, a->H, a->ldx);
     MoeGroupedParams p{pv.item_expert, pv.item_routes, pv.num_items, a->T, a->top_k, a->H, a->I,
                        (const uint8_t*)a->w13, (const uint8_t*)a->s13, (const float*)a->g13,
                        (const uint8_t*)a->sw13, (const uint8_t*)a->ss13, (const float*)a->sg13,

@@ -217,7 +217,7 @@ class GlmMoeDsaModel:
         else:
             x, residual = comm.allreduce_add_rmsnorm(ops, partial, residual, lw.input_norm, self.cfg.rms_norm_eps)
         attn = self.attention(layer, lw, x, st, cache)
-        y, residual = comm.allreduce_add_rmsnorm(ops, attn, residual, lw.post_attn_norm, self.cfg.rms_norm_eps)
+        y, residual = comm.allreduce_add_rmsnorm(ops, attn, residual, lw.post_attn_norm, self.cfg.rms_norm_eps, want_perm=True)
         return self.mlp(lw, y, final=last), residual
 
     def forward_hidden(self, st: StepState, cache: KVCacheTensors) -> torch.Tensor:

@@ -36,7 +36,7 @@ class RefOps:
     def rmsnorm(self, x, w, eps=None):
         return R.rmsnorm(x, w, self.cfg.rms_norm_eps if eps is None else eps)
 
-    def add_rmsnorm(self, x, residual, w, eps=None):
+    def add_rmsnorm(self, x, residual, w, eps=None, want_perm: bool = False):
         return R.add_rmsnorm(x, residual, w, self.cfg.rms_norm_eps if eps is None else eps)
 
     def linear(self, x, w, out_f32: bool = False, sink=None, defer_reduce: bool = False):

@@ -67,7 +67,7 @@ class CudaOps:
         N.call("sl_embed", out.data_ptr(), ids.data_ptr(), table.data_ptr(), T, H, table.shape[0], N.stream())
         return out
 
-    def add_rmsnorm(self, x, residual, w, eps=None):
+    def add_rmsnorm(self, x, residual, w, eps=None, want_perm: bool = False):
         eps = self.cfg.rms_norm_eps if eps is None else eps
         x = x.contiguous()
         if x.dtype not in (torch.bfloat16, torch.float32):
@@ -75,9 +75,20 @@ class CudaOps:
         T, H = x.shape
         out = torch.empty(T, H, dtype=torch.bfloat16, device=x.device)
         res = torch.empty(T, H, dtype=torch.float32, device=x.device)
+        xp = None
+        if want_perm and T <= DECODE_MAX_T and H % 128 == 0:
+            # the consumer is an NVFP4 tensor-core kernel: write its permuted f16 operand in the same pass
+            xp = torch.empty(((T + 7) // 8) * 8 * H, dtype=torch.float16, device=x.device)
+            out._sl_perm = xp
         N.call("sl_add_rmsnorm", out.data_ptr(), res.data_ptr(), x.data_ptr(), N.ptr(residual), w.data_ptr(), T, H,
-               float(eps), int(x.dtype == torch.float32), N.stream())
+               float(eps), int(x.dtype == torch.float32), N.ptr(xp), N.stream())
         return out, res
+
+    @staticmethod
+    def _perm_of(x, T: int, K: int):
+        """The permuted f16 copy that x's producer left with it, if it has the shape this consumer needs."""
+        p = getattr(x, "_sl_perm", None)
+        return p if p is not None and p.numel() == ((T + 7) // 8) * 8 * K else None
 
     def rmsnorm(self, x, w, eps=None):
         eps = self.cfg.rms_norm_eps if eps is None else eps
@@ -85,7 +96,7 @@ class CudaOps:
         T, H = x.shape
         out = torch.empty(T, H, dtype=torch.bfloat16, device=x.device)
         N.call("sl_add_rmsnorm", out.data_ptr(), 0, x.data_ptr(), 0, w.data_ptr(), T, H, float(eps),
-               int(x.dtype == torch.float32), N.stream())
+               int(x.dtype == torch.float32), 0, N.stream())
         return out
 
     def linear(self, x, w, out_f32: bool = False, sink=None, defer_reduce: bool = False):
@@ -101,9 +112,12 @@ class CudaOps:
         if sink is not None:
             sink.pushed_rows = T
             if w.is_nvfp4 and K % 128 == 0 and x.stride(0) % 8 == 0:
-                xp = torch.empty(((T + 7) // 8) * 8 * K, dtype=torch.float16, device=x.device)
-                N.call("sl_linear_nvfp4_mma_push", x.data_ptr(), xp.data_ptr(), w.weight.data_ptr(), w.scale.data_ptr(),
-                       w.scale2.data_ptr(), T, Nn, K, x.stride(0), C.byref(sink.push), N.stream())
+                xp = self._perm_of(x, T, K)
+                ready = xp is not None
+                if not ready:
+                    xp = torch.empty(((T + 7) // 8) * 8 * K, dtype=torch.float16, device=x.device)
+                N.call("sl_linear_nvfp4_mma_push", 0 if ready else x.data_ptr(), xp.data_ptr(), w.weight.data_ptr(),
+                       w.scale.data_ptr(), w.scale2.data_ptr(), T, Nn, K, K if ready else x.stride(0), C.byref(sink.push), N.stream())
                 return sink
             if not w.is_nvfp4 and x.stride(0) % 8 == 0 and K % 8 == 0:
                 from . import tcgen05
@@ -118,9 +132,12 @@ class CudaOps:
         if T >= TENSOR_MIN_T:
             # tensor-core weight streaming: tcgen05 swap-AB (bf16) / mma.sync with in-register FP4 expansion
             if w.is_nvfp4 and K % 128 == 0 and x.stride(0) % 8 == 0:
-                xp = torch.empty(((T + 7) // 8) * 8 * K, dtype=torch.float16, device=x.device)
-                N.call("sl_linear_nvfp4_mma", y.data_ptr(), x.data_ptr(), xp.data_ptr(), w.weight.data_ptr(),
-                       w.scale.data_ptr(), w.scale2.data_ptr(), T, Nn, K, x.stride(0), int(out_f32), N.stream())
+                xp = self._perm_of(x, T, K)
+                ready = xp is not None
+                if not ready:
+                    xp = torch.empty(((T + 7) // 8) * 8 * K, dtype=torch.float16, device=x.device)
+                N.call("sl_linear_nvfp4_mma", y.data_ptr(), 0 if ready else x.data_ptr(), xp.data_ptr(), w.weight.data_ptr(),
+                       w.scale.data_ptr(), w.scale2.data_ptr(), T, Nn, K, K if ready else x.stride(0), int(out_f32), N.stream())
                 return y
             if not w.is_nvfp4 and x.stride(0) % 8 == 0 and K % 8 == 0 and Nn > 1024:
                 from . import tcgen05
@@ -387,7 +404,10 @@ class CudaOps:
         I = experts.inter
         routes = T * k + (T if shared is not None else 0)
         max_items = T * k + (T + 7) // 8
-        xp = torch.empty(((T + 7) // 8) * 8 * H, dtype=torch.float16, device=dev)
+        xp = self._perm_of(x, T, H)
+        xp_ready = xp is not None
+        if not xp_ready:
+            xp = torch.empty(((T + 7) // 8) * 8 * H, dtype=torch.float16, device=dev)
         act = torch.empty((routes + 8) * I, dtype=torch.float16, device=dev)
         y_route = torch.empty(routes, H, dtype=torch.float32, device=dev)
         plan = torch.empty(max_items * 9 + 1, dtype=torch.int32, device=dev)
@@ -401,7 +421,7 @@ class CudaOps:
                              sw2=N.ptr(shared.w2) if shared else 0, ss2=N.ptr(shared.s2) if shared else 0,
                              sg2=N.ptr(shared.g2) if shared else 0,
                              xp=xp.data_ptr(), act_perm=act.data_ptr(), y_route=y_route.data_ptr(), plan=plan.data_ptr(),
-                             max_items=max_items, out=N.ptr(out))
+                             max_items=max_items, out=N.ptr(out), xp_ready=int(xp_ready))
         if sink is not None:
             sink.pushed_rows = T
             N.call("sl_moe_grouped_mma", C.byref(a), C.cast(C.byref(rargs), C.c_void_p) if rargs is not None else None,

@@ -48,7 +48,7 @@ class MetaOps:
         self._note("rmsnorm")
         return _meta(*x.shape)
 
-    def add_rmsnorm(self, x, residual, w, eps=None):
+    def add_rmsnorm(self, x, residual, w, eps=None, want_perm: bool = False):
         self._note("add_rmsnorm")
         return _meta(*x.shape), _meta(*x.shape, dtype=torch.float32)
 

@@ -121,7 +121,7 @@ class MoeGroupedArgs(C.Structure):
     _fields_ = [("x", vp), ("ldx", i32), ("ids", vp), ("wts", vp), ("T", i32), ("top_k", i32), ("H", i32), ("I", i32),
                 ("expert_offset", i32), ("num_local", i32), ("w13", vp), ("s13", vp), ("g13", vp), ("sw13", vp), ("ss13", vp),
                 ("sg13", vp), ("w2", vp), ("s2", vp), ("g2", vp), ("sw2", vp), ("ss2", vp), ("sg2", vp), ("xp", vp),
-                ("act_perm", vp), ("y_route", vp), ("plan", vp), ("max_items", i32), ("out", vp)]
+                ("act_perm", vp), ("y_route", vp), ("plan", vp), ("max_items", i32), ("out", vp), ("xp_ready", i32)]
 
 
 class MoeRouterArgs(C.Structure):
@@ -145,7 +145,7 @@ class SpecRejectParams(C.Structure):
 
 _SIGS = {
     "sl_embed": [vp, vp, vp, i32, i32, i32, vp],
-    "sl_add_rmsnorm": [vp, vp, vp, vp, vp, i32, i32, f32, i32, vp],
+    "sl_add_rmsnorm": [vp, vp, vp, vp, vp, i32, i32, f32, i32, vp, vp],
     "sl_attn_pre": [C.POINTER(AttnPreParams), i32, vp],
     "sl_q_post": [C.POINTER(QPostParams), i32, vp],
     "sl_q_post_absorb": [C.POINTER(QPostParams), vp, vp, i32, i32, vp],

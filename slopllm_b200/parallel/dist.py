@@ -149,8 +149,11 @@ class Comm:
         return self.cp_merge_heads(ops, o, lse)
 
     # -- fused-op shaped interface (overridden by the NVLink kernels) -------------------------
-    def allreduce_add_rmsnorm(self, ops, partial, residual, weight, eps):
-        """sum over ranks of `partial`, add to `residual`, RMSNorm.  Returns (normed, residual')."""
+    def allreduce_add_rmsnorm(self, ops, partial, residual, weight, eps, want_perm: bool = False):
+        """sum over ranks of `partial`, add to `residual`, RMSNorm.  Returns (normed, residual').
+        `want_perm`: the consumer is an NVFP4 tensor-core kernel; a CUDA backend then also emits its permuted operand."""
+        if want_perm and getattr(ops, "name", "") == "cuda":
+            return ops.add_rmsnorm(self.all_reduce(partial), residual, weight, eps, want_perm=True)
         return ops.add_rmsnorm(self.all_reduce(partial), residual, weight, eps)
 
     def cp_merge_heads(self, ops, o: torch.Tensor, lse: torch.Tensor):

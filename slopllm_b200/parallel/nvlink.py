@@ -55,7 +55,7 @@ class GatherPushCtx(C.Structure):
 
 
 N._SIGS.update({
-    "sl_ar_add_rmsnorm": [C.POINTER(RecvCtx), vp, vp, vp, vp, i32, i32, C.c_float, vp],
+    "sl_ar_add_rmsnorm": [C.POINTER(RecvCtx), vp, vp, vp, vp, i32, i32, C.c_float, vp, vp],
     "sl_push_rows": [C.POINTER(PushCtx), vp, i32, i32, vp],
     "sl_flag_barrier": [C.POINTER(vp), vp, i32, i32, u32, u32, vp, vp],
     "sl_wait_flag": [vp, u32, u32, vp, vp],
@@ -246,16 +246,21 @@ class NvlinkComm(Comm):
         return s
 
     # -- fused all-reduce consumer ----------------------------------------------------------------
-    def allreduce_add_rmsnorm(self, ops, partial, residual, weight, eps):
+    def allreduce_add_rmsnorm(self, ops, partial, residual, weight, eps, want_perm: bool = False):
         if not isinstance(partial, PushSink):
-            return super().allreduce_add_rmsnorm(ops, partial, residual, weight, eps)
+            return super().allreduce_add_rmsnorm(ops, partial, residual, weight, eps, want_perm)
         T, H = partial.pushed_rows, self.region.row_len
         dev = self.ctx.device
         out = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
         res = torch.empty(T, H, dtype=torch.float32, device=dev)
         rc = self.region.recv_ctx[partial.index]
+        xp = None
+        if want_perm and H % 128 == 0:
+            # the consumer of `out` is an NVFP4 tensor-core kernel: write its permuted f16 operand here too
+            xp = torch.empty(((T + 7) // 8) * 8 * H, dtype=torch.float16, device=dev)
+            out._sl_perm = xp
         N.call("sl_ar_add_rmsnorm", C.byref(rc), out.data_ptr(), res.data_ptr(), N.ptr(residual), weight.data_ptr(), T, H,
-               float(eps), N.stream())
+               float(eps), N.ptr(xp), N.stream())
         return out, res
 
     # -- all-gather by peer stores -------------------------------------------------------------------

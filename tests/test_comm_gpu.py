@@ -115,7 +115,7 @@ def test_tagged_consumer_times_out_cleanly():
     out = torch.empty(T, H, dtype=torch.bfloat16, device=DEV)
     res = torch.empty(T, H, dtype=torch.float32, device=DEV)
     w = torch.ones(H, dtype=torch.bfloat16, device=DEV)
-    N.call("sl_ar_add_rmsnorm", C.byref(region.recv_ctx[0]), out.data_ptr(), res.data_ptr(), 0, w.data_ptr(), T, H, 1e-5, N.stream())
+    N.call("sl_ar_add_rmsnorm", C.byref(region.recv_ctx[0]), out.data_ptr(), res.data_ptr(), 0, w.data_ptr(), T, H, 1e-5, 0, N.stream())
     torch.cuda.synchronize()
     with pytest.raises(CollectiveTimeout):
         region.check_status()

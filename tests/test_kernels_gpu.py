@@ -275,6 +275,25 @@ def test_moe_fused_router_glm5_routing(T):
     close(ops.moe_tp(x, lw), fused, tol=1e-6, what="second call")
 
 
+@pytest.mark.parametrize("T", [1, 5, 8, 19])
+def test_norm_emits_permuted_operand(T):
+    """add+RMSNorm can write the permuted f16 operand of the NVFP4 tensor-core kernels itself: the linear and the
+    MoE layer fed from it must give the same result as with their own permute launch."""
+    cfg = mini_cfg(hidden_size=2048, moe_intermediate_size=512)
+    ops = cuda_ops(cfg)
+    lw = random_layer(cfg, 1, 0, DEV, torch.bfloat16)
+    g = torch.Generator(device=DEV).manual_seed(T)
+    x = torch.randn(T, cfg.hidden_size, device=DEV, generator=g)
+    res = torch.randn(T, cfg.hidden_size, device=DEV, generator=g)
+    plain, _ = ops.add_rmsnorm(x, res, lw.post_attn_norm)
+    perm, _ = ops.add_rmsnorm(x, res, lw.post_attn_norm, want_perm=True)
+    assert torch.equal(plain, perm) and getattr(perm, "_sl_perm", None) is not None
+    w = LinearWeight(*quant.random_nvfp4((768, cfg.hidden_size), g, DEV))
+    if T >= 2:
+        assert torch.equal(ops.linear(perm, w, out_f32=True), ops.linear(plain, w, out_f32=True))
+    close(ops.moe_tp(perm, lw), ops.moe_tp(plain, lw), tol=1e-6, what="moe with emitted operand")
+
+
 def test_moe_large_matches_reference():
     cfg = mini_cfg(hidden_size=1024, moe_intermediate_size=256)
     ops, ref = cuda_ops(cfg), RefOps(cfg)
