@@ -10,6 +10,9 @@ COMMANDS = {
     "nll": "slopllm_b200.cli.nll",
     "mtp-bench": "slopllm_b200.cli.mtp_bench",
     "loader": "slopllm_b200.cli.model_loader",
+    "kernel-bench": "slopllm_b200.cli.kernel_bench",
+    "profile-step": "slopllm_b200.cli.profile_step",
+    "collective-bench": "slopllm_b200.cli.collective_bench",
     "build": "slopllm_b200.build_native",
 }
 

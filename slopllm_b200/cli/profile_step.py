@@ -8,6 +8,8 @@ for kernel profiling and per-rank timing.
 
     python -m slopllm_b200.cli.profile_step --prefill 2048 --tp-shape 8 --layers 5
         one eager prefill chunk (tcgen05 GEMMs, grouped expert GEMMs, prefill attention / indexer)
+    python -m slopllm_b200.cli.profile_step --prefill 4096 --tp-shape 8 --layers 6 --op-times
+        the same chunk with a CUDA-event pair around every backend op (device time per op, no profiler)
     python -m slopllm_b200.cli.profile_step --fused-emulated 8 --batch 8
         the fused GEMM + all-reduce kernels at production shapes with all "ranks" in this process: every rank's
         producer kernel stores into the receive slots of all ranks (here all on one GPU), then each rank's consumer
@@ -42,6 +44,7 @@ def main(argv=None) -> int:
     ap.add_argument("--timed", type=int, default=0, help="time this many graph-replayed steps instead of running eager steps")
     ap.add_argument("--mtp", type=int, default=0)
     ap.add_argument("--prefill", type=int, default=0, help="run one eager prefill chunk of this many tokens instead of decode steps")
+    ap.add_argument("--op-times", action="store_true", help="eager run with a CUDA-event pair around every backend op; prints the breakdown")
     ap.add_argument("--fused-emulated", type=int, default=0, metavar="W", help="fused GEMM+all-reduce kernels with W emulated ranks")
     args = ap.parse_args(argv)
     dev = torch.device("cuda", 0)
@@ -64,22 +67,36 @@ def main(argv=None) -> int:
         if lc.idx is not None:
             lc.idx.copy_(quant.pack_index_rows(torch.randn(n, cfg.index_head_dim, device=dev)))
     last = [5] * B
+    timers = None
+    if args.op_times:
+        from ..utils.tracing import OpTimers
+        timers = OpTimers(eng.model.ops)
     if args.prefill > 0:
         s = eng.kv.new_sequence()
         prompt = torch.randint(2, cfg.vocab_size - 1, (args.prefill,), generator=torch.Generator().manual_seed(0)).tolist()
         for i in range(2):                      # second pass re-uses the allocator's blocks (steady state)
+            if timers is not None:
+                timers.reset()
             toks, _ = eng.prefill([s], [prompt], chunk_size=args.prefill)
             eng.kv.truncate(s, 0)
         torch.cuda.synchronize()
-        print(json.dumps({"mode": "prefill", "tokens": args.prefill, "next": toks}))
+        out = {"mode": "prefill", "tokens": args.prefill, "next": toks}
+        if timers is not None:
+            out["op_times"] = timers.summary()
+        print(json.dumps(out))
         return 0
     if args.timed <= 0:
         for i in range(args.steps):
+            if timers is not None and i == args.steps - 1:
+                timers.reset()                  # keep the last (warm) step only
             torch.cuda.nvtx.range_push(f"decode_step_{i}")
             last = eng.decode_step(seqs, last)
             torch.cuda.nvtx.range_pop()
         torch.cuda.synchronize()
-        print(json.dumps({"mode": "eager", "steps": args.steps, "last": last}))
+        out = {"mode": "eager", "steps": args.steps, "last": last}
+        if timers is not None:
+            out["op_times"] = timers.summary()
+        print(json.dumps(out))
         return 0
     for _ in range(5):
         last = eng.decode_step(seqs, last)

@@ -65,3 +65,61 @@ def torch_profile(path: str, cuda: bool = True) -> Iterator[None]:
     with torch.profiler.profile(activities=acts) as prof:
         yield
     prof.export_chrome_trace(path)
+
+
+class OpTimers:
+    """Device time per backend op: wraps the public methods of an ops object with CUDA event pairs.
+
+    Eager mode only (events cannot be recorded inside a graph capture).  Each rank of a multi-GPU job
+    can carry its own instance, which is how a per-op breakdown of a multi-rank step is taken without
+    a profiler.  `summary()` synchronises once and returns rows sorted by total time."""
+
+    def __init__(self, ops, names=None):
+        self.ops = ops
+        self.events = defaultdict(list)
+        self._orig = {}
+        names = names or [n for n in dir(ops) if not n.startswith("_") and callable(getattr(ops, n, None))
+                          and n not in ("name",)]
+        for n in names:
+            fn = getattr(ops, n)
+            if isinstance(fn, type) or not hasattr(fn, "__call__"):
+                continue
+            self._orig[n] = fn
+            setattr(ops, n, self._wrap(n, fn))
+        self._depth = 0
+
+    def _wrap(self, name, fn):
+        def timed(*a, **k):
+            if self._depth > 0 or not torch.cuda.is_available():      # nested backend calls count towards the outer op
+                return fn(*a, **k)
+            self._depth += 1
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            try:
+                return fn(*a, **k)
+            finally:
+                e1.record()
+                self.events[name].append((e0, e1))
+                self._depth -= 1
+        return timed
+
+    def reset(self) -> None:
+        self.events.clear()
+
+    def restore(self) -> None:
+        for n, fn in self._orig.items():
+            setattr(self.ops, n, fn)
+        self._orig.clear()
+
+    def summary(self):
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+        rows = []
+        for n, evs in self.events.items():
+            ms = sum(a.elapsed_time(b) for a, b in evs)
+            rows.append({"op": n, "calls": len(evs), "total_ms": round(ms, 4), "us_per_call": round(1e3 * ms / max(1, len(evs)), 2)})
+        rows.sort(key=lambda r: -r["total_ms"])
+        tot = sum(r["total_ms"] for r in rows) or 1.0
+        for r in rows:
+            r["share"] = round(r["total_ms"] / tot, 4)
+        return rows
