@@ -162,3 +162,23 @@ def test_op_timers_wrap_and_restore():
     assert t.summary() == [] or all(r["calls"] >= 1 for r in t.summary())     # no CUDA: nothing recorded
     t.restore()
     assert ops.add.__func__ is Ops.add
+
+
+def test_weights_doc_groups_layers_and_experts(tmp_path):
+    import json
+    import torch
+    from slopllm_b200.checkpoint.safetensors_io import save_file
+    from slopllm_b200.cli import weights_doc
+    t = {"model.embed_tokens.weight": torch.zeros(8, 4, dtype=torch.bfloat16)}
+    for layer in range(3):
+        t[f"model.layers.{layer}.input_layernorm.weight"] = torch.zeros(4, dtype=torch.bfloat16)
+        for e in range(2):
+            t[f"model.layers.{layer}.mlp.experts.{e}.down_proj.weight"] = torch.zeros(4, 2, dtype=torch.uint8)
+    save_file(t, str(tmp_path / "model-00001-of-00001.safetensors"))
+    (tmp_path / "config.json").write_text(json.dumps({"model_type": "glm_moe_dsa", "num_hidden_layers": 2}))
+    out = tmp_path / "w.md"
+    assert weights_doc.main(["--model", str(tmp_path), "--output", str(out)]) == 0
+    text = out.read_text()
+    assert "| `model.layers.N.mlp.experts.E.down_proj.weight` | [4, 2] | U8 | 4 | 32 B |" in text
+    assert "| `model.layers.MTP.mlp.experts.E.down_proj.weight` **MTP** | [4, 2] | U8 | 2 | 16 B |" in text
+    assert "**Total tensors**: 10" in text
