@@ -286,6 +286,381 @@ __global__ void __launch_bounds__(256) sparse_mla_mma_kernel(Params p) {
     }
 }
 
+
+// ---------------------------------------------------------------------------------------------------
+// Transposed form (keys on the MMA M dimension, heads on N in tiles of 8) for R % 128 == 0.
+//
+//   S^T[64 keys, 8 heads]   = K8[64, D] Q^T[D, 8]      warp (mt, kh): 16 keys x one half of the D/16 k-steps
+//   O^T[R dims, 8 heads]   += V8^T[R, 64] P'[64, 8]    warp w: R/8 dims
+//
+// With 8 heads per rank (64 heads over 8 GPUs) no MMA row is padding, against half of them with heads on M.
+// The latent part of a cache row stays in its e4m3 code values (exact in f16): the per-(key, group) scale is
+// applied to the fp32 group sums of S and folded into P for the output product, so expanding a row is one
+// convert per pair of elements.  The running maximum is a reference that is only raised when a score exceeds it
+// by more than `kRaise` (one vote per chunk through the barrier that publishes P): exponentials stay below
+// e^kRaise, and the common chunk has three barriers and no single-warp phase.
+constexpr float kRaise = 6.f;
+bool g_transposed_enabled = true;
+
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ uint32_t e4m3x2_to_h2(uint32_t b) {
+    __half2_raw h = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(b & 0xffffu), __NV_E4M3);
+    return (uint32_t)h.x | ((uint32_t)h.y << 16);
+}
+
+constexpr int PS = KC + 8;    // row stride of P in halves
+
+// grid (splits, ceil(h / (8 NT)), T); block 256.  Needs the 16-byte row layout (see the launcher).
+template <int NT>
+__global__ void __launch_bounds__(256) sparse_mla_mma_t_kernel(Params p) {
+    pdl_grid_sync();
+    extern __shared__ __align__(16) unsigned char smraw[];
+    constexpr int NH = 8 * NT;
+    const int D = p.R + p.Dr, DP = D + 8;
+    const int NG = p.R / p.group;
+    __half* qs = reinterpret_cast<__half*>(smraw);            // NH * DP
+    __half* ks = qs + NH * DP;                                // KC * DP
+    __half* ps = ks + KC * DP;                                // NH * PS
+    float* sks = reinterpret_cast<float*>(ps + NH * PS);      // [KC][NG] group scales of the chunk's keys
+    float4* xs = reinterpret_cast<float4*>(sks + KC * NG);    // [4][NT][32] S partial sums of the second k half
+    float* wmax = reinterpret_cast<float*>(xs + 4 * NT * 32); // [4][NH]
+    float* wl = wmax + 4 * NH;                                // [4][NH]
+    float* row_m = wl + 4 * NH;                               // [NH] reference maximum
+    int* s_slots = reinterpret_cast<int*>(row_m + NH);        // [2][KC]
+
+    const int split = blockIdx.x, hg = blockIdx.y, t = blockIdx.z;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, c = lane & 3;
+    const int mt = warp & 3, kh = warp >> 2;
+    const int L = p.lengths[t];
+    const int per = (L + p.splits - 1) / p.splits;
+    const int j_begin = min(L, split * per), j_end = min(L, j_begin + per);
+    const int h0 = hg * NH, nh = min(NH, p.h - h0);
+    const int row_bytes = p.R + 4 * NG + 2 * p.Dr;
+    const int chunks = row_bytes / 16;
+    const int* slots = p.slots + (size_t)t * p.topk;
+
+    for (int i = tid; i < NH * (D / 2); i += blockDim.x) {
+        const int hh = i / (D / 2), d = (i % (D / 2)) * 2;
+        float2 v = make_float2(0.f, 0.f);
+        if (hh < nh) {
+            const uint32_t u = d < p.R ? *reinterpret_cast<const uint32_t*>(p.q_abs + ((size_t)t * p.h + h0 + hh) * p.R + d)
+                                       : *reinterpret_cast<const uint32_t*>(p.q_pe + ((size_t)t * p.h + h0 + hh) * p.Dr + (d - p.R));
+            v = bf162_to_f2(u);
+        }
+        *reinterpret_cast<__half2*>(qs + hh * DP + d) = __floats2half2_rn(v.x * p.sm_scale, v.y * p.sm_scale);
+    }
+    if (tid < NH) row_m[tid] = -INFINITY;
+
+    const int dpw = p.R / 8, MT = dpw / 16;                   // dims per warp, 16-dim tiles per warp (<= 4)
+    const int grp_w = (warp * dpw) / p.group;                 // scale group of this warp's output dims
+    float oacc[4][NT][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) oacc[i][nt][0] = oacc[i][nt][1] = oacc[i][nt][2] = oacc[i][nt][3] = 0.f;
+    float lsum[NT][2];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) lsum[nt][0] = lsum[nt][1] = 0.f;
+
+    auto checked_slot = [&](int s) { return (p.num_slots == 0 || guard_ok(p.guard, 12, s, p.num_slots)) ? s : 0; };
+    constexpr int MAXLD = 12;
+    uint4 buf[MAXLD];
+    auto issue_loads = [&](int c0n, const int* sl) {
+        const int total = min(KC, j_end - c0n) * chunks;
+#pragma unroll
+        for (int n = 0; n < MAXLD; ++n) {
+            const int i = tid + n * 256;
+            if (i < total) {
+                const int j = i / chunks, byte = (i - j * chunks) * 16;
+                buf[n] = ldg_nc_16(p.kv_cache + (size_t)sl[j] * row_bytes + byte);
+            }
+        }
+    };
+    int* s_slots2 = s_slots + KC;
+    if (j_begin < j_end) {
+        if (tid < KC) s_slots[tid] = tid < min(KC, j_end - j_begin) ? checked_slot(slots[j_begin + tid]) : 0;
+        __syncthreads();
+        issue_loads(j_begin, s_slots);
+    }
+    int parity = 0;
+    const int nsteps = D / 16, nope_steps = p.R / 16, spg = p.group / 16, half_steps = (nsteps + 1) / 2;
+    const int st_begin = kh * half_steps, st_end = min(nsteps, st_begin + half_steps);
+
+    for (int c0 = j_begin; c0 < j_end; c0 += KC) {
+        const int kc = min(KC, j_end - c0);
+        __syncthreads();                                      // the previous chunk's products have read ks / ps / sks
+        // ---- expand the prefetched rows: e4m3 codes -> f16, scales aside, rope bf16 -> f16 ----
+        {
+            const int total = kc * chunks;
+#pragma unroll
+            for (int n = 0; n < MAXLD; ++n) {
+                const int i = tid + n * 256;
+                if (i < total) {
+                    const int j = i / chunks, byte = (i - j * chunks) * 16;
+                    const uint32_t w4[4] = {buf[n].x, buf[n].y, buf[n].z, buf[n].w};
+                    if (byte < p.R) {
+                        uint4* dst = reinterpret_cast<uint4*>(ks + j * DP + byte);
+                        dst[0] = make_uint4(e4m3x2_to_h2(w4[0]), e4m3x2_to_h2(w4[0] >> 16), e4m3x2_to_h2(w4[1]), e4m3x2_to_h2(w4[1] >> 16));
+                        dst[1] = make_uint4(e4m3x2_to_h2(w4[2]), e4m3x2_to_h2(w4[2] >> 16), e4m3x2_to_h2(w4[3]), e4m3x2_to_h2(w4[3] >> 16));
+                    } else if (byte < p.R + 4 * NG) {
+                        *reinterpret_cast<uint4*>(sks + j * NG + (byte - p.R) / 4) = buf[n];
+                    } else {
+                        const int d = p.R + (byte - p.R - 4 * NG) / 2;
+                        uint32_t o[4];
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const float2 f = bf162_to_f2(w4[q]);
+                            __half2 hv = __floats2half2_rn(f.x, f.y);
+                            o[q] = *reinterpret_cast<uint32_t*>(&hv);
+                        }
+                        *reinterpret_cast<uint4*>(ks + j * DP + d) = make_uint4(o[0], o[1], o[2], o[3]);
+                    }
+                }
+            }
+        }
+        const int c0n = c0 + KC;
+        int* sl_next = parity ? s_slots : s_slots2;
+        if (c0n < j_end && tid < KC) sl_next[tid] = tid < min(KC, j_end - c0n) ? checked_slot(slots[c0n + tid]) : 0;
+        if (kc < KC) {
+            // rows beyond kc get p = 0: keep their values and scales finite so that 0 * v stays 0
+            for (int i = tid; i < (KC - kc) * (D / 2); i += blockDim.x) {
+                const int j = kc + i / (D / 2), d2 = i % (D / 2);
+                reinterpret_cast<uint32_t*>(ks + j * DP)[d2] = 0u;
+            }
+            for (int i = tid; i < (KC - kc) * NG; i += blockDim.x) sks[kc * NG + i] = 0.f;
+        }
+        __syncthreads();                                      // tile, scales and the next slot list are in place
+        if (c0n < j_end) issue_loads(c0n, sl_next);           // in flight during this chunk's products
+        parity ^= 1;
+
+        // ---- S^T = K Q^T : warp (mt, kh) -> keys 16 mt .. 16 mt + 15, k-steps [st_begin, st_end) ----
+        float sacc[NT][4], acc[2][NT][4];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int q = 0; q < 4; ++q) sacc[nt][q] = acc[0][nt][q] = acc[1][nt][q] = 0.f;
+        const int keyA = 16 * mt + g, keyB = keyA + 8;
+        auto fold = [&](int grp) {
+            const float fa = grp >= 0 ? sks[keyA * NG + grp] : 1.f, fb = grp >= 0 ? sks[keyB * NG + grp] : 1.f;
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                sacc[nt][0] += (acc[0][nt][0] + acc[1][nt][0]) * fa;
+                sacc[nt][1] += (acc[0][nt][1] + acc[1][nt][1]) * fa;
+                sacc[nt][2] += (acc[0][nt][2] + acc[1][nt][2]) * fb;
+                sacc[nt][3] += (acc[0][nt][3] + acc[1][nt][3]) * fb;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) acc[0][nt][q] = acc[1][nt][q] = 0.f;
+            }
+        };
+        {
+            int grp = st_begin < nope_steps ? st_begin / spg : -1;
+            int left = st_begin < nope_steps ? spg - (st_begin - grp * spg) : nsteps;
+            const __half* arow = ks + (16 * mt + (lane & 15)) * DP + (lane >> 4) * 8;
+            const __half* brow = qs + g * DP + 2 * c;
+            for (int st = st_begin; st < st_end; ++st) {
+                if (left == 0) {
+                    fold(grp);
+                    grp = st < nope_steps ? grp + 1 : -1;
+                    left = st < nope_steps ? spg : nsteps;
+                }
+                --left;
+                const int k0 = st * 16;
+                uint32_t a[4];
+                ldmatrix_x4(a, arow + k0);
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    const __half* br = brow + nt * 8 * DP + k0;
+                    const uint32_t b0 = *reinterpret_cast<const uint32_t*>(br), b1 = *reinterpret_cast<const uint32_t*>(br + 8);
+                    if (st & 1) mma16816(acc[1][nt], a, b0, b1); else mma16816(acc[0][nt], a, b0, b1);
+                }
+            }
+            if (st_begin < st_end) fold(grp);
+        }
+        if (kh == 1) {
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) xs[(mt * NT + nt) * 32 + lane] = make_float4(sacc[nt][0], sacc[nt][1], sacc[nt][2], sacc[nt][3]);
+        }
+        __syncthreads();
+        // ---- P = exp(S - reference) on the warps of the first k half ----
+        float e[NT][4];
+        int raise = 0;
+        if (kh == 0) {
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                const float4 o = xs[(mt * NT + nt) * 32 + lane];
+                sacc[nt][0] += o.x; sacc[nt][1] += o.y; sacc[nt][2] += o.z; sacc[nt][3] += o.w;
+                if (keyA >= kc) sacc[nt][0] = sacc[nt][1] = -INFINITY;
+                if (keyB >= kc) sacc[nt][2] = sacc[nt][3] = -INFINITY;
+                const float m0 = row_m[8 * nt + 2 * c], m1 = row_m[8 * nt + 2 * c + 1];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float m = (q & 1) ? m1 : m0, sv = sacc[nt][q];
+                    raise |= (sv > m + kRaise);
+                    e[nt][q] = (sv == -INFINITY || m == -INFINITY) ? 0.f : __expf(fminf(sv - m, 2.f * kRaise));
+                }
+                ps[(8 * nt + 2 * c) * PS + keyA] = __float2half_rn(e[nt][0]);
+                ps[(8 * nt + 2 * c + 1) * PS + keyA] = __float2half_rn(e[nt][1]);
+                ps[(8 * nt + 2 * c) * PS + keyB] = __float2half_rn(e[nt][2]);
+                ps[(8 * nt + 2 * c + 1) * PS + keyB] = __float2half_rn(e[nt][3]);
+            }
+        }
+        if (__syncthreads_or(raise)) {
+            // a score passed the reference by more than kRaise: raise it to the running maximum, rescale, redo P
+            if (kh == 0) {
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    float x0 = fmaxf(sacc[nt][0], sacc[nt][2]), x1 = fmaxf(sacc[nt][1], sacc[nt][3]);
+#pragma unroll
+                    for (int sh = 4; sh < 32; sh <<= 1) {
+                        x0 = fmaxf(x0, __shfl_xor_sync(0xffffffffu, x0, sh));
+                        x1 = fmaxf(x1, __shfl_xor_sync(0xffffffffu, x1, sh));
+                    }
+                    if (g == 0) { wmax[mt * NH + 8 * nt + 2 * c] = x0; wmax[mt * NH + 8 * nt + 2 * c + 1] = x1; }
+                }
+            }
+            __syncthreads();
+            float mnew[NT][2], alpha[NT][2];
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                for (int q = 0; q < 2; ++q) {
+                    const int hh = 8 * nt + 2 * c + q;
+                    const float old = row_m[hh];
+                    float mx = old;
+#pragma unroll
+                    for (int w = 0; w < 4; ++w) mx = fmaxf(mx, wmax[w * NH + hh]);
+                    mnew[nt][q] = mx;
+                    alpha[nt][q] = (old == -INFINITY) ? 0.f : __expf(old - mx);
+                }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    oacc[i][nt][0] *= alpha[nt][0]; oacc[i][nt][1] *= alpha[nt][1];
+                    oacc[i][nt][2] *= alpha[nt][0]; oacc[i][nt][3] *= alpha[nt][1];
+                }
+            if (kh == 0) {
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    lsum[nt][0] *= alpha[nt][0]; lsum[nt][1] *= alpha[nt][1];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const float m = mnew[nt][q & 1], sv = sacc[nt][q];
+                        e[nt][q] = (sv == -INFINITY) ? 0.f : __expf(sv - m);
+                    }
+                    ps[(8 * nt + 2 * c) * PS + keyA] = __float2half_rn(e[nt][0]);
+                    ps[(8 * nt + 2 * c + 1) * PS + keyA] = __float2half_rn(e[nt][1]);
+                    ps[(8 * nt + 2 * c) * PS + keyB] = __float2half_rn(e[nt][2]);
+                    ps[(8 * nt + 2 * c + 1) * PS + keyB] = __float2half_rn(e[nt][3]);
+                }
+            }
+            __syncthreads();                                  // P is final; every thread has read the old reference
+            if (warp == 0 && g == 0) {
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) { row_m[8 * nt + 2 * c] = mnew[nt][0]; row_m[8 * nt + 2 * c + 1] = mnew[nt][1]; }
+            }
+        }
+        if (kh == 0) {
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) { lsum[nt][0] += e[nt][0] + e[nt][2]; lsum[nt][1] += e[nt][1] + e[nt][3]; }
+        }
+        // ---- O^T += V^T P' : warp w -> dims [w dpw, (w + 1) dpw), P' = P x the keys' scale of this warp's group ----
+#pragma unroll
+        for (int k0 = 0; k0 < KC; k0 += 16) {
+            const __half2 f0 = __floats2half2_rn(sks[(k0 + 2 * c) * NG + grp_w], sks[(k0 + 2 * c + 1) * NG + grp_w]);
+            const __half2 f1 = __floats2half2_rn(sks[(k0 + 2 * c + 8) * NG + grp_w], sks[(k0 + 2 * c + 9) * NG + grp_w]);
+            uint32_t b[NT][2];
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                const __half* pr = ps + (8 * nt + g) * PS + k0 + 2 * c;
+                __half2 v0 = __hmul2(*reinterpret_cast<const __half2*>(pr), f0), v1 = __hmul2(*reinterpret_cast<const __half2*>(pr + 8), f1);
+                b[nt][0] = *reinterpret_cast<uint32_t*>(&v0);
+                b[nt][1] = *reinterpret_cast<uint32_t*>(&v1);
+            }
+            const __half* vrow = ks + (k0 + (lane & 7) + ((lane >> 4) & 1) * 8) * DP + warp * dpw + ((lane >> 3) & 1) * 8;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                if (i < MT) {
+                    uint32_t a[4];
+                    ldmatrix_x4_trans(a, vrow + 16 * i);
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) mma16816(oacc[i][nt], a, b[nt][0], b[nt][1]);
+                }
+            }
+        }
+    }
+    // ---- normalise and write the partial ----
+    __syncthreads();
+    if (kh == 0) {
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            float x0 = lsum[nt][0], x1 = lsum[nt][1];
+#pragma unroll
+            for (int sh = 4; sh < 32; sh <<= 1) {
+                x0 += __shfl_xor_sync(0xffffffffu, x0, sh);
+                x1 += __shfl_xor_sync(0xffffffffu, x1, sh);
+            }
+            if (g == 0) { wl[mt * NH + 8 * nt + 2 * c] = x0; wl[mt * NH + 8 * nt + 2 * c + 1] = x1; }
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+        const int hA = 8 * nt + 2 * c, hB = hA + 1;
+        const float lA = wl[hA] + wl[NH + hA] + wl[2 * NH + hA] + wl[3 * NH + hA];
+        const float lB = wl[hB] + wl[NH + hB] + wl[2 * NH + hB] + wl[3 * NH + hB];
+        const float iA = lA > 0.f ? 1.f / lA : 0.f, iB = lB > 0.f ? 1.f / lB : 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            if (i < MT) {
+                const int d = warp * dpw + 16 * i + g;
+                if (hA < nh) {
+                    float* o = p.o_part + (((size_t)t * p.h + h0 + hA) * p.splits + split) * p.R + d;
+                    o[0] = oacc[i][nt][0] * iA; o[8] = oacc[i][nt][2] * iA;
+                }
+                if (hB < nh) {
+                    float* o = p.o_part + (((size_t)t * p.h + h0 + hB) * p.splits + split) * p.R + d;
+                    o[0] = oacc[i][nt][1] * iB; o[8] = oacc[i][nt][3] * iB;
+                }
+            }
+        }
+    }
+    if (tid < nh) {
+        const float l = wl[tid] + wl[NH + tid] + wl[2 * NH + tid] + wl[3 * NH + tid];
+        p.lse_part[((size_t)t * p.h + h0 + tid) * p.splits + split] = l > 0.f ? row_m[tid] + logf(l) : -INFINITY;
+    }
+}
+
+template <int NT>
+int launch_transposed(const Params& p, int T, cudaStream_t s) {
+    constexpr int NH = 8 * NT;
+    const int DP = p.R + p.Dr + 8, NG = p.R / p.group;
+    const size_t smem = (size_t)(NH * DP + KC * DP + NH * PS) * sizeof(__half) + (size_t)(KC * NG) * sizeof(float) +
+                        (size_t)(4 * NT * 32) * sizeof(float4) + (size_t)(9 * NH + 2 * KC) * sizeof(float);
+    static bool attr = false;
+    if (!attr) {
+        cudaFuncSetAttribute(sparse_mla_mma_t_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+        attr = true;
+    }
+    if (smem > 160 * 1024) return -1;
+    dim3 grid(p.splits, (p.h + NH - 1) / NH, T);
+    sl_launch(sparse_mla_mma_t_kernel<NT>, grid, 256, smem, s, p);
+    return (int)cudaGetLastError();
+}
+
+// the transposed kernel's layout conditions: 16-byte fields in the packed row, whole k-steps per scale group, each
+// warp's output dims inside one group, at most 12 16-byte pieces per thread and chunk
+bool transposed_ok(const Params& p) {
+    if (p.R % 128 != 0 || p.R > 512 || p.group <= 0 || p.R % p.group != 0) return false;
+    const int NG = p.R / p.group, row_bytes = p.R + 4 * NG + 2 * p.Dr;
+    return p.group % 16 == 0 && p.group % (p.R / 8) == 0 && NG % 4 == 0 && NG <= 8 && p.Dr % 16 == 0 && row_bytes % 16 == 0 &&
+           KC * (row_bytes / 16) <= 12 * 256;
+}
+
 }  // namespace
 
 // Same contract as sl_sparse_mla_split (csrc/sparse_mla.cu).  Needs R % 64 == 0, (R + Dr) % 16 == 0,
@@ -294,6 +669,7 @@ SL_API int sl_sparse_mla_split_mma(const void* params, int T, cudaStream_t s) {
     const Params* p = static_cast<const Params*>(params);
     if (T == 0) return 0;
     if (p->R % 64 != 0 || p->R > 512 || (p->R + p->Dr) % 16 != 0 || p->Dr % 2 != 0 || p->group % 4 != 0) return -1;
+    if (g_transposed_enabled && transposed_ok(*p)) return p->h <= 8 ? launch_transposed<1>(*p, T, s) : launch_transposed<2>(*p, T, s);
     const int DP = p->R + p->Dr + 8;
     const size_t smem = (size_t)(HB * DP + KC * DP + HB * 72) * sizeof(__half) + (size_t)(8 * HB * 2 + 3 * HB + 2 * KC) * sizeof(float);
     static bool attr = false;
@@ -306,3 +682,6 @@ SL_API int sl_sparse_mla_split_mma(const void* params, int T, cudaStream_t s) {
     sl_launch(sparse_mla_mma_kernel, grid, 256, smem, s, *p);
     return (int)cudaGetLastError();
 }
+
+// 0 selects the heads-on-M kernel for every shape (comparison runs); default 1.
+SL_API void sl_sparse_mla_set_transposed(int on) { g_transposed_enabled = on != 0; }

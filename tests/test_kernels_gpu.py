@@ -244,6 +244,43 @@ def test_sparse_mla_and_v_expand(which):
     close(ops.v_expand(o, w_v), ref.v_expand(o, w_v), what="v_expand")
 
 
+@pytest.mark.parametrize("h,T,q_scale", [(8, 3, 0.3), (8, 40, 4.0), (16, 3, 4.0), (12, 5, 0.3)])
+def test_sparse_mla_keys_on_m(h, T, q_scale):
+    """The keys-on-M sparse MLA kernel (kv_lora_rank a multiple of 128) at the production top-k: full, ragged and
+    empty key lists, one or several key splits, 8 / 12 / 16 heads per CTA; `q_scale` 4 makes later chunks exceed the
+    softmax reference of earlier ones (the rescale path).  Also against the heads-on-M kernel through the switch."""
+    from slopllm_b200.ops import native as N
+    cfg = mini_cfg(num_attention_heads=h, index_topk=2048)
+    ops, ref = cuda_ops(cfg), RefOps(cfg)
+    g = torch.Generator(device=DEV).manual_seed(100 + h + T)
+    Rr, Dr, k = cfg.kv_lora_rank, cfg.qk_rope_head_dim, cfg.index_topk
+    nslots = 4096
+    cache = type("C", (), {})()
+    cache.kv = quant.pack_kv_rows(torch.randn(nslots, Rr, device=DEV, generator=g) * 2.0,
+                                  torch.randn(nslots, Dr, device=DEV, generator=g), cfg.kv_quant_group)
+    q_abs = (torch.randn(T, h, Rr, device=DEV, generator=g) * q_scale).to(torch.bfloat16)
+    q_pe = (torch.randn(T, h, Dr, device=DEV, generator=g) * q_scale).to(torch.bfloat16)
+    slots = torch.full((T, k), -1, dtype=torch.int32, device=DEV)
+    lens = [k, 1000, 0, 65, 64, 1] + [k] * T
+    lengths = torch.tensor(lens[:T], dtype=torch.int32, device=DEV)
+    for t in range(T):
+        n = int(lengths[t])
+        slots[t, :n] = torch.randperm(nslots, device=DEV, generator=g)[:n].to(torch.int32)
+    o, lse = ops.sparse_mla(q_abs, q_pe, cache, slots, lengths)
+    eo, elo = ref.sparse_mla(q_abs, q_pe, cache, slots, lengths)
+    live = lengths > 0
+    close(o, eo, what="sparse mla o (keys on M)")
+    close(lse[live], elo[live], tol=1e-3, what="lse (keys on M)")
+    assert torch.isinf(lse[~live]).all() and (o[~live] == 0).all()
+    N.kernels().sl_sparse_mla_set_transposed(0)
+    try:
+        o2, lse2 = ops.sparse_mla(q_abs, q_pe, cache, slots, lengths)
+    finally:
+        N.kernels().sl_sparse_mla_set_transposed(1)
+    close(o, o2, what="keys-on-M vs heads-on-M")
+    close(lse[live], lse2[live], tol=1e-3, what="lse, keys-on-M vs heads-on-M")
+
+
 @pytest.mark.parametrize("T", [1, 4, 9])
 def test_moe_small_and_dense(T):
     cfg = mini_cfg(hidden_size=2048, moe_intermediate_size=512)
