@@ -8,6 +8,8 @@
 // (`csrc/glm_sparse_mla.cu:34-126`): split-K over the top-k rows, mid_out / mid_lse + combine.
 #include "common.cuh"
 
+#include <type_traits>
+
 namespace {
 
 struct Params {
@@ -288,17 +290,19 @@ __global__ void __launch_bounds__(256) sparse_mla_mma_kernel(Params p) {
 
 
 // ---------------------------------------------------------------------------------------------------
-// Transposed form (keys on the MMA M dimension, heads on N in tiles of 8) for R % 128 == 0.
+// Transposed form (keys on the MMA M dimension, heads on N in tiles of 8) for the 656-byte cache row:
+// 512 e4m3 latent values, 4 fp32 scales (one per 128 values), 64 bf16 rope values.
 //
-//   S^T[64 keys, 8 heads]   = K8[64, D] Q^T[D, 8]      warp (mt, kh): 16 keys x one half of the D/16 k-steps
-//   O^T[R dims, 8 heads]   += V8^T[R, 64] P'[64, 8]    warp w: R/8 dims
+//   S^T[64 keys, 8 heads]   = K8[64, 576] Q^T[576, 8]    warp (mt, kh): 16 keys x 18 of the 36 k-steps
+//   O^T[512 dims, 8 heads] += V8^T[512, 64] P'[64, 8]    warp w: 64 dims
 //
 // With 8 heads per rank (64 heads over 8 GPUs) no MMA row is padding, against half of them with heads on M.
-// The latent part of a cache row stays in its e4m3 code values (exact in f16): the per-(key, group) scale is
-// applied to the fp32 group sums of S and folded into P for the output product, so expanding a row is one
-// convert per pair of elements.  The running maximum is a reference that is only raised when a score exceeds it
-// by more than `kRaise` (one vote per chunk through the barrier that publishes P): exponentials stay below
-// e^kRaise, and the common chunk has three barriers and no single-warp phase.
+// The latent part of a row stays in its e4m3 code values (exact in f16): the per-(key, group) scale is applied
+// to the fp32 group sums of S and folded into P for the output product, so expanding a row is one convert per
+// pair of elements.  The running maximum is a reference that is only raised when a score exceeds it by more
+// than `kRaise` (one vote per chunk through the barrier that publishes P): exponentials stay below e^kRaise,
+// and the common chunk has four barriers and no single-warp phase.  The row geometry is a compile-time
+// constant: a warp gathers whole rows (lane = 16-byte piece of the latent part), so no index needs a division.
 constexpr float kRaise = 6.f;
 bool g_transposed_enabled = true;
 
@@ -306,21 +310,31 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* 
     const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
 }
-__device__ __forceinline__ uint32_t e4m3x2_to_h2(uint32_t b) {
-    __half2_raw h = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(b & 0xffffu), __NV_E4M3);
-    return (uint32_t)h.x | ((uint32_t)h.y << 16);
+// four e4m3 codes -> four halves (a: codes 0 and 1, b: codes 2 and 3)
+__device__ __forceinline__ void e4m3x4_to_h2x2(uint32_t w, uint32_t& a, uint32_t& b) {
+    asm("{ .reg .b16 lo, hi; mov.b32 {lo, hi}, %2; cvt.rn.f16x2.e4m3x2 %0, lo; cvt.rn.f16x2.e4m3x2 %1, hi; }"
+        : "=r"(a), "=r"(b) : "r"(w));
 }
 
-constexpr int PS = KC + 8;    // row stride of P in halves
+namespace tk {                                   // geometry of the transposed kernel
+constexpr int R = 512, GS = 128, NG = R / GS, DR = 64, D = R + DR, DP = D + 8;
+constexpr int ROW_BYTES = R + 4 * NG + 2 * DR;   // 656
+constexpr int TAIL = (4 * NG + 2 * DR) / 16;     // 16-byte pieces after the latent part: 1 of scales, 8 of rope
+constexpr int ROWS_PER_WARP = KC / 8;            // 8
+constexpr int TAIL_ITEMS = KC * TAIL;            // 576 = 2.25 per thread
+constexpr int PS = KC + 8;                       // row stride of P in halves
+constexpr int NSTEPS = D / 16, HALF = NSTEPS / 2, SPG = GS / 16, NOPE_STEPS = R / 16;
+static_assert(R / 16 == 32, "one lane per 16-byte piece of the latent part");
+static_assert(NSTEPS % 2 == 0 && R / 8 == 64, "");
+}  // namespace tk
 
-// grid (splits, ceil(h / (8 NT)), T); block 256.  Needs the 16-byte row layout (see the launcher).
+// grid (splits, ceil(h / (8 NT)), T); block 256.
 template <int NT>
 __global__ void __launch_bounds__(256) sparse_mla_mma_t_kernel(Params p) {
+    using namespace tk;
     pdl_grid_sync();
     extern __shared__ __align__(16) unsigned char smraw[];
     constexpr int NH = 8 * NT;
-    const int D = p.R + p.Dr, DP = D + 8;
-    const int NG = p.R / p.group;
     __half* qs = reinterpret_cast<__half*>(smraw);            // NH * DP
     __half* ks = qs + NH * DP;                                // KC * DP
     __half* ps = ks + KC * DP;                                // NH * PS
@@ -339,24 +353,21 @@ __global__ void __launch_bounds__(256) sparse_mla_mma_t_kernel(Params p) {
     const int per = (L + p.splits - 1) / p.splits;
     const int j_begin = min(L, split * per), j_end = min(L, j_begin + per);
     const int h0 = hg * NH, nh = min(NH, p.h - h0);
-    const int row_bytes = p.R + 4 * NG + 2 * p.Dr;
-    const int chunks = row_bytes / 16;
     const int* slots = p.slots + (size_t)t * p.topk;
 
-    for (int i = tid; i < NH * (D / 2); i += blockDim.x) {
+    for (int i = tid; i < NH * (D / 2); i += 256) {
         const int hh = i / (D / 2), d = (i % (D / 2)) * 2;
         float2 v = make_float2(0.f, 0.f);
         if (hh < nh) {
-            const uint32_t u = d < p.R ? *reinterpret_cast<const uint32_t*>(p.q_abs + ((size_t)t * p.h + h0 + hh) * p.R + d)
-                                       : *reinterpret_cast<const uint32_t*>(p.q_pe + ((size_t)t * p.h + h0 + hh) * p.Dr + (d - p.R));
+            const uint32_t u = d < R ? *reinterpret_cast<const uint32_t*>(p.q_abs + ((size_t)t * p.h + h0 + hh) * R + d)
+                                     : *reinterpret_cast<const uint32_t*>(p.q_pe + ((size_t)t * p.h + h0 + hh) * DR + (d - R));
             v = bf162_to_f2(u);
         }
         *reinterpret_cast<__half2*>(qs + hh * DP + d) = __floats2half2_rn(v.x * p.sm_scale, v.y * p.sm_scale);
     }
     if (tid < NH) row_m[tid] = -INFINITY;
 
-    const int dpw = p.R / 8, MT = dpw / 16;                   // dims per warp, 16-dim tiles per warp (<= 4)
-    const int grp_w = (warp * dpw) / p.group;                 // scale group of this warp's output dims
+    const int grp_w = warp >> 1;                              // scale group of this warp's 64 output dims
     float oacc[4][NT][4];
 #pragma unroll
     for (int i = 0; i < 4; ++i)
@@ -367,84 +378,87 @@ __global__ void __launch_bounds__(256) sparse_mla_mma_t_kernel(Params p) {
     for (int nt = 0; nt < NT; ++nt) lsum[nt][0] = lsum[nt][1] = 0.f;
 
     auto checked_slot = [&](int s) { return (p.num_slots == 0 || guard_ok(p.guard, 12, s, p.num_slots)) ? s : 0; };
-    constexpr int MAXLD = 12;
-    uint4 buf[MAXLD];
-    auto issue_loads = [&](int c0n, const int* sl) {
-        const int total = min(KC, j_end - c0n) * chunks;
+    // gather registers: the latent piece `lane` of this warp's 8 rows, and up to 3 of the chunk's 576 tail pieces
+    uint4 nbuf[ROWS_PER_WARP], tbuf[3];
+    auto issue_loads = [&](int kcn, const int* sl) {
 #pragma unroll
-        for (int n = 0; n < MAXLD; ++n) {
-            const int i = tid + n * 256;
-            if (i < total) {
-                const int j = i / chunks, byte = (i - j * chunks) * 16;
-                buf[n] = ldg_nc_16(p.kv_cache + (size_t)sl[j] * row_bytes + byte);
-            }
+        for (int r = 0; r < ROWS_PER_WARP; ++r) {
+            const int row = warp * ROWS_PER_WARP + r;
+            if (row < kcn) nbuf[r] = ldg_nc_16(p.kv_cache + (size_t)sl[row] * ROW_BYTES + lane * 16);
+        }
+#pragma unroll
+        for (int n = 0; n < 3; ++n) {
+            const int item = tid + n * 256, row = item / TAIL, q = item - row * TAIL;
+            if (item < TAIL_ITEMS && row < kcn) tbuf[n] = ldg_nc_16(p.kv_cache + (size_t)sl[row] * ROW_BYTES + R + q * 16);
         }
     };
     int* s_slots2 = s_slots + KC;
     if (j_begin < j_end) {
-        if (tid < KC) s_slots[tid] = tid < min(KC, j_end - j_begin) ? checked_slot(slots[j_begin + tid]) : 0;
+        const int kc0 = min(KC, j_end - j_begin);
+        if (tid < KC) s_slots[tid] = tid < kc0 ? checked_slot(slots[j_begin + tid]) : 0;
         __syncthreads();
-        issue_loads(j_begin, s_slots);
+        issue_loads(kc0, s_slots);
     }
     int parity = 0;
-    const int nsteps = D / 16, nope_steps = p.R / 16, spg = p.group / 16, half_steps = (nsteps + 1) / 2;
-    const int st_begin = kh * half_steps, st_end = min(nsteps, st_begin + half_steps);
+    const int keyA = 16 * mt + g, keyB = keyA + 8;
+    const __half* arow = ks + (16 * mt + (lane & 15)) * DP + (lane >> 4) * 8;
+    const __half* brow = qs + g * DP + 2 * c;
+    const __half* vrow0 = ks + ((lane & 7) + ((lane >> 4) & 1) * 8) * DP + warp * 64 + ((lane >> 3) & 1) * 8;
 
     for (int c0 = j_begin; c0 < j_end; c0 += KC) {
         const int kc = min(KC, j_end - c0);
         __syncthreads();                                      // the previous chunk's products have read ks / ps / sks
-        // ---- expand the prefetched rows: e4m3 codes -> f16, scales aside, rope bf16 -> f16 ----
-        {
-            const int total = kc * chunks;
+        // ---- expand the prefetched rows: e4m3 codes -> f16, scales aside, rope bf16 -> f16; rows beyond kc are
+        //      zero (their p is 0: values and scales must be finite so that 0 * v stays 0) ----
 #pragma unroll
-            for (int n = 0; n < MAXLD; ++n) {
-                const int i = tid + n * 256;
-                if (i < total) {
-                    const int j = i / chunks, byte = (i - j * chunks) * 16;
-                    const uint32_t w4[4] = {buf[n].x, buf[n].y, buf[n].z, buf[n].w};
-                    if (byte < p.R) {
-                        uint4* dst = reinterpret_cast<uint4*>(ks + j * DP + byte);
-                        dst[0] = make_uint4(e4m3x2_to_h2(w4[0]), e4m3x2_to_h2(w4[0] >> 16), e4m3x2_to_h2(w4[1]), e4m3x2_to_h2(w4[1] >> 16));
-                        dst[1] = make_uint4(e4m3x2_to_h2(w4[2]), e4m3x2_to_h2(w4[2] >> 16), e4m3x2_to_h2(w4[3]), e4m3x2_to_h2(w4[3] >> 16));
-                    } else if (byte < p.R + 4 * NG) {
-                        *reinterpret_cast<uint4*>(sks + j * NG + (byte - p.R) / 4) = buf[n];
-                    } else {
-                        const int d = p.R + (byte - p.R - 4 * NG) / 2;
-                        uint32_t o[4];
+        for (int r = 0; r < ROWS_PER_WARP; ++r) {
+            const int row = warp * ROWS_PER_WARP + r;
+            uint4 lo = make_uint4(0u, 0u, 0u, 0u), hi = lo;
+            if (row < kc) {
+                const uint4 w = nbuf[r];
+                e4m3x4_to_h2x2(w.x, lo.x, lo.y);
+                e4m3x4_to_h2x2(w.y, lo.z, lo.w);
+                e4m3x4_to_h2x2(w.z, hi.x, hi.y);
+                e4m3x4_to_h2x2(w.w, hi.z, hi.w);
+            }
+            uint4* dst = reinterpret_cast<uint4*>(ks + row * DP + lane * 16);
+            dst[0] = lo;
+            dst[1] = hi;
+        }
 #pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            const float2 f = bf162_to_f2(w4[q]);
-                            __half2 hv = __floats2half2_rn(f.x, f.y);
-                            o[q] = *reinterpret_cast<uint32_t*>(&hv);
-                        }
-                        *reinterpret_cast<uint4*>(ks + j * DP + d) = make_uint4(o[0], o[1], o[2], o[3]);
+        for (int n = 0; n < 3; ++n) {
+            const int item = tid + n * 256, row = item / TAIL, q = item - row * TAIL;
+            if (item < TAIL_ITEMS) {
+                const uint4 w = row < kc ? tbuf[n] : make_uint4(0u, 0u, 0u, 0u);
+                if (q == 0) {
+                    *reinterpret_cast<uint4*>(sks + row * NG) = w;
+                } else {
+                    const uint32_t w4[4] = {w.x, w.y, w.z, w.w};
+                    uint32_t o[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float2 f = bf162_to_f2(w4[e]);
+                        __half2 hv = __floats2half2_rn(f.x, f.y);
+                        o[e] = *reinterpret_cast<uint32_t*>(&hv);
                     }
+                    *reinterpret_cast<uint4*>(ks + row * DP + R + (q - 1) * 8) = make_uint4(o[0], o[1], o[2], o[3]);
                 }
             }
         }
-        const int c0n = c0 + KC;
+        const int c0n = c0 + KC, kcn = min(KC, j_end - c0n);
         int* sl_next = parity ? s_slots : s_slots2;
-        if (c0n < j_end && tid < KC) sl_next[tid] = tid < min(KC, j_end - c0n) ? checked_slot(slots[c0n + tid]) : 0;
-        if (kc < KC) {
-            // rows beyond kc get p = 0: keep their values and scales finite so that 0 * v stays 0
-            for (int i = tid; i < (KC - kc) * (D / 2); i += blockDim.x) {
-                const int j = kc + i / (D / 2), d2 = i % (D / 2);
-                reinterpret_cast<uint32_t*>(ks + j * DP)[d2] = 0u;
-            }
-            for (int i = tid; i < (KC - kc) * NG; i += blockDim.x) sks[kc * NG + i] = 0.f;
-        }
+        if (c0n < j_end && tid < KC) sl_next[tid] = tid < kcn ? checked_slot(slots[c0n + tid]) : 0;
         __syncthreads();                                      // tile, scales and the next slot list are in place
-        if (c0n < j_end) issue_loads(c0n, sl_next);           // in flight during this chunk's products
+        if (c0n < j_end) issue_loads(kcn, sl_next);           // in flight during this chunk's products
         parity ^= 1;
 
-        // ---- S^T = K Q^T : warp (mt, kh) -> keys 16 mt .. 16 mt + 15, k-steps [st_begin, st_end) ----
+        // ---- S^T = K Q^T : warp (mt, kh) -> keys 16 mt .. 16 mt + 15, k-steps [18 kh, 18 kh + 18) ----
         float sacc[NT][4], acc[2][NT][4];
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
             for (int q = 0; q < 4; ++q) sacc[nt][q] = acc[0][nt][q] = acc[1][nt][q] = 0.f;
-        const int keyA = 16 * mt + g, keyB = keyA + 8;
-        auto fold = [&](int grp) {
+        auto fold = [&](int grp) {                            // grp < 0: the rope part carries no scale
             const float fa = grp >= 0 ? sks[keyA * NG + grp] : 1.f, fb = grp >= 0 ? sks[keyB * NG + grp] : 1.f;
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
@@ -456,30 +470,25 @@ __global__ void __launch_bounds__(256) sparse_mla_mma_t_kernel(Params p) {
                 for (int q = 0; q < 4; ++q) acc[0][nt][q] = acc[1][nt][q] = 0.f;
             }
         };
-        {
-            int grp = st_begin < nope_steps ? st_begin / spg : -1;
-            int left = st_begin < nope_steps ? spg - (st_begin - grp * spg) : nsteps;
-            const __half* arow = ks + (16 * mt + (lane & 15)) * DP + (lane >> 4) * 8;
-            const __half* brow = qs + g * DP + 2 * c;
-            for (int st = st_begin; st < st_end; ++st) {
-                if (left == 0) {
-                    fold(grp);
-                    grp = st < nope_steps ? grp + 1 : -1;
-                    left = st < nope_steps ? spg : nsteps;
-                }
-                --left;
-                const int k0 = st * 16;
+        auto s_half = [&](auto KH) {
+            constexpr int kh_ = decltype(KH)::value;
+#pragma unroll
+            for (int i = 0; i < HALF; ++i) {
+                const int st = kh_ * HALF + i;
+                if (i > 0 && st <= NOPE_STEPS && st % SPG == 0) fold(st / SPG - 1);
                 uint32_t a[4];
-                ldmatrix_x4(a, arow + k0);
+                ldmatrix_x4(a, arow + st * 16);
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) {
-                    const __half* br = brow + nt * 8 * DP + k0;
+                    const __half* br = brow + nt * 8 * DP + st * 16;
                     const uint32_t b0 = *reinterpret_cast<const uint32_t*>(br), b1 = *reinterpret_cast<const uint32_t*>(br + 8);
-                    if (st & 1) mma16816(acc[1][nt], a, b0, b1); else mma16816(acc[0][nt], a, b0, b1);
+                    mma16816(acc[i & 1][nt], a, b0, b1);
                 }
             }
-            if (st_begin < st_end) fold(grp);
-        }
+            constexpr int last = kh_ * HALF + HALF - 1;
+            fold(last < NOPE_STEPS ? last / SPG : -1);
+        };
+        if (kh == 0) s_half(std::integral_constant<int, 0>{}); else s_half(std::integral_constant<int, 1>{});
         if (kh == 1) {
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) xs[(mt * NT + nt) * 32 + lane] = make_float4(sacc[nt][0], sacc[nt][1], sacc[nt][2], sacc[nt][3]);
@@ -568,7 +577,7 @@ __global__ void __launch_bounds__(256) sparse_mla_mma_t_kernel(Params p) {
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) { lsum[nt][0] += e[nt][0] + e[nt][2]; lsum[nt][1] += e[nt][1] + e[nt][3]; }
         }
-        // ---- O^T += V^T P' : warp w -> dims [w dpw, (w + 1) dpw), P' = P x the keys' scale of this warp's group ----
+        // ---- O^T += V^T P' : warp w -> dims [64 w, 64 w + 64), P' = P x the keys' scale of this warp's group ----
 #pragma unroll
         for (int k0 = 0; k0 < KC; k0 += 16) {
             const __half2 f0 = __floats2half2_rn(sks[(k0 + 2 * c) * NG + grp_w], sks[(k0 + 2 * c + 1) * NG + grp_w]);
@@ -581,15 +590,12 @@ __global__ void __launch_bounds__(256) sparse_mla_mma_t_kernel(Params p) {
                 b[nt][0] = *reinterpret_cast<uint32_t*>(&v0);
                 b[nt][1] = *reinterpret_cast<uint32_t*>(&v1);
             }
-            const __half* vrow = ks + (k0 + (lane & 7) + ((lane >> 4) & 1) * 8) * DP + warp * dpw + ((lane >> 3) & 1) * 8;
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                if (i < MT) {
-                    uint32_t a[4];
-                    ldmatrix_x4_trans(a, vrow + 16 * i);
+                uint32_t a[4];
+                ldmatrix_x4_trans(a, vrow0 + k0 * DP + 16 * i);
 #pragma unroll
-                    for (int nt = 0; nt < NT; ++nt) mma16816(oacc[i][nt], a, b[nt][0], b[nt][1]);
-                }
+                for (int nt = 0; nt < NT; ++nt) mma16816(oacc[i][nt], a, b[nt][0], b[nt][1]);
             }
         }
     }
@@ -616,16 +622,14 @@ __global__ void __launch_bounds__(256) sparse_mla_mma_t_kernel(Params p) {
         const float iA = lA > 0.f ? 1.f / lA : 0.f, iB = lB > 0.f ? 1.f / lB : 0.f;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            if (i < MT) {
-                const int d = warp * dpw + 16 * i + g;
-                if (hA < nh) {
-                    float* o = p.o_part + (((size_t)t * p.h + h0 + hA) * p.splits + split) * p.R + d;
-                    o[0] = oacc[i][nt][0] * iA; o[8] = oacc[i][nt][2] * iA;
-                }
-                if (hB < nh) {
-                    float* o = p.o_part + (((size_t)t * p.h + h0 + hB) * p.splits + split) * p.R + d;
-                    o[0] = oacc[i][nt][1] * iB; o[8] = oacc[i][nt][3] * iB;
-                }
+            const int d = warp * 64 + 16 * i + g;
+            if (hA < nh) {
+                float* o = p.o_part + (((size_t)t * p.h + h0 + hA) * p.splits + split) * R + d;
+                o[0] = oacc[i][nt][0] * iA; o[8] = oacc[i][nt][2] * iA;
+            }
+            if (hB < nh) {
+                float* o = p.o_part + (((size_t)t * p.h + h0 + hB) * p.splits + split) * R + d;
+                o[0] = oacc[i][nt][1] * iB; o[8] = oacc[i][nt][3] * iB;
             }
         }
     }
@@ -637,8 +641,8 @@ __global__ void __launch_bounds__(256) sparse_mla_mma_t_kernel(Params p) {
 
 template <int NT>
 int launch_transposed(const Params& p, int T, cudaStream_t s) {
+    using namespace tk;
     constexpr int NH = 8 * NT;
-    const int DP = p.R + p.Dr + 8, NG = p.R / p.group;
     const size_t smem = (size_t)(NH * DP + KC * DP + NH * PS) * sizeof(__half) + (size_t)(KC * NG) * sizeof(float) +
                         (size_t)(4 * NT * 32) * sizeof(float4) + (size_t)(9 * NH + 2 * KC) * sizeof(float);
     static bool attr = false;
@@ -646,20 +650,13 @@ int launch_transposed(const Params& p, int T, cudaStream_t s) {
         cudaFuncSetAttribute(sparse_mla_mma_t_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
         attr = true;
     }
-    if (smem > 160 * 1024) return -1;
     dim3 grid(p.splits, (p.h + NH - 1) / NH, T);
     sl_launch(sparse_mla_mma_t_kernel<NT>, grid, 256, smem, s, p);
     return (int)cudaGetLastError();
 }
 
-// the transposed kernel's layout conditions: 16-byte fields in the packed row, whole k-steps per scale group, each
-// warp's output dims inside one group, at most 12 16-byte pieces per thread and chunk
-bool transposed_ok(const Params& p) {
-    if (p.R % 128 != 0 || p.R > 512 || p.group <= 0 || p.R % p.group != 0) return false;
-    const int NG = p.R / p.group, row_bytes = p.R + 4 * NG + 2 * p.Dr;
-    return p.group % 16 == 0 && p.group % (p.R / 8) == 0 && NG % 4 == 0 && NG <= 8 && p.Dr % 16 == 0 && row_bytes % 16 == 0 &&
-           KC * (row_bytes / 16) <= 12 * 256;
-}
+// the transposed kernel is compiled for the 656-byte row (512 latent values in groups of 128, 64 rope values)
+bool transposed_ok(const Params& p) { return p.R == tk::R && p.group == tk::GS && p.Dr == tk::DR; }
 
 }  // namespace
 
