@@ -1,6 +1,6 @@
 """Kernel micro-benchmarks at the production shapes of one rank of a TP-8 GLM-5-class model.
 
-    python -m slopllm_b200.cli.kernel_bench [--cases linear,moe,mlp] [--tokens 1,8,32,4096] [--iters 20]
+    python -m slopllm_b200.cli.kernel_bench [--cases linear,mlp,moe,gemm] [--tokens 1,8,32,4096] [--iters 20]
 
 For every (kernel, token count) it prints one JSON line with the device time (CUDA events, median of `--iters`
 runs, three warm-up runs, a 256 MB write between runs so that no operand is served from L2), the algorithmic
@@ -114,6 +114,31 @@ def main(argv=None) -> int:
                 us = time_op(lambda: ops.linear(x, w), args.iters, flush)
                 emit(roofline_row(name + ("_nvfp4" if fp4 else ""), T, us, weight_bytes(n, k, fp4) + 2 * T * (n + k), 2.0 * T * n * k, peaks))
             del w
+    if "gemm" in cases:
+        # the tcgen05 GEMM itself (bf16 weights of every linear's shape) at both tile widths, and the two grouped expert
+        # GEMMs of a prefill chunk (rows sorted by expert, 8 routes per token)
+        from ..ops import tcgen05
+        from ..ops.gemm import grouped_gemm
+        for T in [t for t in tokens if t > 32]:
+            for name, n, k, _ in linear_shapes(cfg, args.tp_shape):
+                w = (torch.randn(n, k, device=dev, generator=g) * 0.02).to(torch.bfloat16)
+                x = torch.randn(T, k, device=dev, generator=g).to(torch.bfloat16)
+                for bn in (128, 256):
+                    us = time_op(lambda: tcgen05.gemm_bf16(x, w, False, bn), args.iters, flush)
+                    emit(roofline_row(f"gemm_bn{bn}_{name}", T, us, 2.0 * (n * k + T * (n + k)), 2.0 * T * n * k, peaks))
+                del w, x
+            E, I, Hh = cfg.n_routed_experts, cfg.moe_intermediate_size // args.tp_shape, cfg.hidden_size
+            nrows = T * cfg.num_experts_per_tok
+            cnt = torch.bincount(torch.randint(0, E, (nrows,), device=dev, generator=g), minlength=E)
+            off = torch.zeros(E + 1, dtype=torch.int32, device=dev)
+            off[1:] = torch.cumsum(cnt, 0).to(torch.int32)
+            for name, n, k in (("grouped_gate_up", 2 * I, Hh), ("grouped_down", Hh, I)):
+                w = (torch.randn(E, n, k, device=dev, generator=g) * 0.02).to(torch.bfloat16)
+                a = torch.randn(nrows, k, device=dev, generator=g).to(torch.bfloat16)
+                for bn in (128, 256):
+                    us = time_op(lambda: grouped_gemm(a, w, off, False, bn), args.iters, flush)
+                    emit(roofline_row(f"{name}_bn{bn}", T, us, 2.0 * (E * n * k + nrows * (n + k)), 2.0 * nrows * n * k, peaks))
+                del w, a
     H = cfg.hidden_size
     if "mlp" in cases:
         lw = random_layer(cfg, 0, 0, dev, torch.bfloat16, 0, args.tp_shape, exact=False)

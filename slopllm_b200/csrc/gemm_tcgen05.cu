@@ -7,11 +7,15 @@
 //            instruction, 4 per 64-wide K block), commits release the ring slots
 //   warps 2-5 epilogue: tcgen05.ld the accumulator (one TMEM lane == one output row per thread)
 //            and store
+// Large GEMMs and grouped GEMMs run persistently (one CTA per SM walks the tiles) with two TMEM accumulators, so a
+// tile's epilogue overlaps the next tile's loads and MMAs; the small-T weight-streaming forms launch one tile per CTA.
 // No cluster multicast is used anywhere.  All mbarrier waits are bounded; on expiry the kernel
 // records an error code, still frees its TMEM and returns.
 //
 // This replaces the reference's cuBLASLt path for batch >= 3 (`csrc/glm_gemv.cu:1642-1770`) and
 // its `mma.sync` grouped kernels (`csrc/glm_mma_moe.cu:110`).
+#include <algorithm>
+
 #include "tcgen05.cuh"
 #include "push.cuh"
 
@@ -32,7 +36,7 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
                                                         int M, int N, int K, int ldc, int out_f32, int transpose_out,
                                                         int* __restrict__ err, int use_push, PushCtx push,
                                                         const int4* __restrict__ tiles, const int* __restrict__ num_tiles,
-                                                        int kb_per_split, long long split_stride) {
+                                                        int kb_per_split, long long split_stride, int tiles_n, int total_tiles) {
     using Cfg = GemmCfg<BN>;
     constexpr int STAGES = Cfg::STAGES;
     extern __shared__ uint8_t smem_raw[];
@@ -41,8 +45,9 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
     uint8_t* sB = smem + STAGES * Cfg::A_BYTES;
     uint64_t* full = reinterpret_cast<uint64_t*>(sB + STAGES * Cfg::B_BYTES);
     uint64_t* empty = full + STAGES;
-    uint64_t* tmem_full = empty + STAGES;
-    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tmem_full + 1);
+    uint64_t* tmem_full = empty + STAGES;      // [2] accumulator buffer written (MMA warp -> epilogue)
+    uint64_t* tmem_empty = tmem_full + 2;      // [2] accumulator buffer read out (epilogue -> MMA warp)
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tmem_empty + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // Set-up touches no global memory, so it runs while the preceding kernel is still finishing.
@@ -50,11 +55,11 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
         tc::tma_prefetch_desc(&tmA);
         tc::tma_prefetch_desc(&tmB);
         for (int s = 0; s < STAGES; ++s) { tc::mbar_init(&full[s], 1); tc::mbar_init(&empty[s], 1); }
-        tc::mbar_init(tmem_full, 1);
+        for (int b = 0; b < 2; ++b) { tc::mbar_init(&tmem_full[b], 1); tc::mbar_init(&tmem_empty[b], 4); }
         tc::mbar_fence_init();
     }
     if (warp == 1) {
-        tc::tmem_alloc(tmem_holder, BN);
+        tc::tmem_alloc(tmem_holder, 2 * BN);   // two accumulators: the epilogue of a tile overlaps the next tile's MMAs
         tc::tmem_relinquish();
     }
     tc::fence_before_sync();
@@ -66,7 +71,7 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
     int pre = 0;
 #if SL_PDL_MODE == 2
     pdl_trigger();
-    if (transpose_out && tiles == nullptr && warp == 0 && lane == 0) {
+    if (transpose_out && tiles == nullptr && tiles_n == 0 && warp == 0 && lane == 0) {
         const int tkb = (K + BK - 1) / BK;
         const int k0 = kb_per_split > 0 ? (int)blockIdx.z * kb_per_split : 0;
         const int nkb = kb_per_split > 0 ? max(0, min(kb_per_split, tkb - k0)) : tkb;
@@ -81,75 +86,94 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
     pdl_grid_sync();
 #endif
 
-    // Plain GEMM: tile (blockIdx.y, blockIdx.x).  Grouped GEMM: blockIdx.x indexes a tile table whose
-    // entries are {first A row, end of the group's A rows, first B row of the group, output column};
-    // rows at or beyond the group's end belong to the next group and are not stored.
-    int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN, b_row0 = n0, m_end = M;
-    bool active = true;
-    if (tiles != nullptr) {
-        active = (int)blockIdx.x < *num_tiles;
-        if (active) {
-            const int4 t = tiles[blockIdx.x];
+    // Tiles of this CTA.  One-tile launch: tile (blockIdx.y, blockIdx.x).  Persistent launch (tiles_n > 0): tiles
+    // blockIdx.x, blockIdx.x + gridDim.x, ... of the row-major tile grid.  Grouped GEMM: the same walk over a tile table
+    // whose entries are {first A row, end of the group's A rows, first B row of the group, output column}; rows at or
+    // beyond the group's end belong to the next group and are not stored.
+    int first = 0, total = 1, stride = 1;
+    if (tiles != nullptr) { total = *num_tiles; first = blockIdx.x; stride = gridDim.x; }
+    else if (tiles_n > 0) { total = total_tiles; first = blockIdx.x; stride = gridDim.x; }
+    auto tile_coords = [&](int tile, int& m0, int& n0, int& b_row0, int& m_end) {
+        if (tiles != nullptr) {
+            const int4 t = tiles[tile];
             m0 = t.x; m_end = t.y; b_row0 = t.z + t.w; n0 = t.w;
+        } else if (tiles_n > 0) {
+            m0 = (tile / tiles_n) * BM; n0 = (tile % tiles_n) * BN; b_row0 = n0; m_end = M;
+        } else {
+            m0 = blockIdx.y * BM; n0 = blockIdx.x * BN; b_row0 = n0; m_end = M;
         }
-    }
+    };
     // split-K: blockIdx.z owns K blocks [kb0, kb0 + num_kb) and its own fp32 output slab
     const int total_kb = (K + BK - 1) / BK;
     const int kb0 = kb_per_split > 0 ? (int)blockIdx.z * kb_per_split : 0;
     const int num_kb = kb_per_split > 0 ? max(0, min(kb_per_split, total_kb - kb0)) : total_kb;
     if (kb_per_split > 0) C = (void*)((float*)C + (size_t)blockIdx.z * split_stride);
 
-    if (!active) {
-        // nothing to compute: fall through to the common TMEM release
-    } else if (warp == 0) {
+    if (warp == 0) {
         if (lane == 0) {
-            for (int kb = 0; kb < num_kb; ++kb) {
-                const int s = kb % STAGES;
-                const uint32_t ph = (kb / STAGES) & 1;
-                if (kb < pre) {           // weight tile already in flight (issued before the dependency wait)
+            int it = 0;                      // K blocks issued so far: ring slot and phase run across tiles
+            bool ok = true;
+            for (int tile = first; tile < total && ok; tile += stride) {
+                int m0, n0, b_row0, m_end;
+                tile_coords(tile, m0, n0, b_row0, m_end);
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (it < pre) {           // weight tile already in flight (issued before the dependency wait)
+                        tc::tma_load_2d(sB + s * Cfg::B_BYTES, &tmB, &full[s], (kb0 + kb) * BK, b_row0);
+                        continue;
+                    }
+                    if (!tc::mbar_wait(&empty[s], ph ^ 1)) { atomicExch(err, 1); ok = false; break; }
+                    tc::mbar_expect_tx(&full[s], Cfg::A_BYTES + Cfg::B_BYTES);
+                    tc::tma_load_2d(sA + s * Cfg::A_BYTES, &tmA, &full[s], (kb0 + kb) * BK, m0);
                     tc::tma_load_2d(sB + s * Cfg::B_BYTES, &tmB, &full[s], (kb0 + kb) * BK, b_row0);
-                    continue;
                 }
-                if (!tc::mbar_wait(&empty[s], ph ^ 1)) { atomicExch(err, 1); break; }
-                tc::mbar_expect_tx(&full[s], Cfg::A_BYTES + Cfg::B_BYTES);
-                tc::tma_load_2d(sA + s * Cfg::A_BYTES, &tmA, &full[s], (kb0 + kb) * BK, m0);
-                tc::tma_load_2d(sB + s * Cfg::B_BYTES, &tmB, &full[s], (kb0 + kb) * BK, b_row0);
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             constexpr uint32_t idesc = tc::idesc_f16(BM, BN, 1);
             bool ok = true;
-            for (int kb = 0; kb < num_kb && ok; ++kb) {
-                const int s = kb % STAGES;
-                const uint32_t ph = (kb / STAGES) & 1;
-                if (!tc::mbar_wait(&full[s], ph)) { atomicExch(err, 2); ok = false; break; }
+            int it = 0, lt = 0;
+            for (int tile = first; tile < total && ok; tile += stride, ++lt) {
+                const int buf = lt & 1;
+                // the epilogue must have read this accumulator's previous tile (passes at once for the first two tiles)
+                if (!tc::mbar_wait(&tmem_empty[buf], ((lt >> 1) & 1) ^ 1)) { atomicExch(err, 4); ok = false; break; }
                 tc::fence_after_sync();
-                const uint32_t a_addr = tc::smem_u32(sA + s * Cfg::A_BYTES), b_addr = tc::smem_u32(sB + s * Cfg::B_BYTES);
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (!tc::mbar_wait(&full[s], ph)) { atomicExch(err, 2); ok = false; break; }
+                    tc::fence_after_sync();
+                    const uint32_t a_addr = tc::smem_u32(sA + s * Cfg::A_BYTES), b_addr = tc::smem_u32(sB + s * Cfg::B_BYTES);
 #pragma unroll
-                for (int k = 0; k < BK / 16; ++k) {
-                    const uint64_t ad = tc::smem_desc_sw128(a_addr + k * 32), bd = tc::smem_desc_sw128(b_addr + k * 32);
-                    tc::mma_f16_ss(tmem_base, ad, bd, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    for (int k = 0; k < BK / 16; ++k) {
+                        const uint64_t ad = tc::smem_desc_sw128(a_addr + k * 32), bd = tc::smem_desc_sw128(b_addr + k * 32);
+                        tc::mma_f16_ss(d_tmem, ad, bd, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    }
+                    tc::mma_commit(&empty[s]);
                 }
-                tc::mma_commit(&empty[s]);
+                if (ok) tc::mma_commit(&tmem_full[buf]);   // arrives when every MMA above has finished (at once if none)
             }
-            tc::mma_commit(tmem_full);       // arrives when every MMA above has finished (at once if there were none)
             pdl_trigger_late();
         }
     } else {
         const int q = warp & 3;               // TMEM lane quarter this warp may access
-        const bool ok = tc::mbar_wait(tmem_full, 0);
-        if (!ok && lane == 0) atomicExch(err, 3);
-        tc::fence_after_sync();
-        const int row = m0 + q * 32 + lane;
         const uint32_t ptag = use_push ? push_tag(push) : 0u;
-        if (ok) {
-#pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                uint32_t r[32];
-                tc::tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + c * 32, r);
-                tc::tmem_ld_wait();
-                const int col = n0 + c * 32;
+        int lt = 0;
+        for (int tile = first; tile < total; tile += stride, ++lt) {
+            const int buf = lt & 1;
+            if (!tc::mbar_wait(&tmem_full[buf], (lt >> 1) & 1)) {
+                if (lane == 0) atomicExch(err, 3);
+                break;
+            }
+            tc::fence_after_sync();
+            int m0, n0, b_row0, m_end;
+            tile_coords(tile, m0, n0, b_row0, m_end);
+            const int row = m0 + q * 32 + lane;
+            const uint32_t t_acc = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN;
+            auto store_chunk = [&](const uint32_t (&r)[32], int col) {
                 if (transpose_out) {
                     // swap-AB use: tile rows are output features, tile columns are token rows;
                     // C is [N, M] row-major (row stride ldc), a warp writes 32 consecutive features
@@ -188,21 +212,53 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
                         }
                     }
                 }
+            };
+            if constexpr (BN >= 64) {
+                // two 32-column chunks per TMEM wait
+#pragma unroll 1
+                for (int c = 0; c < BN / 32; c += 2) {
+                    uint32_t r0[32], r1[32];
+                    tc::tmem_ld_32x32(t_acc + c * 32, r0);
+                    tc::tmem_ld_32x32(t_acc + (c + 1) * 32, r1);
+                    tc::tmem_ld_wait();
+                    store_chunk(r0, n0 + c * 32);
+                    store_chunk(r1, n0 + (c + 1) * 32);
+                }
+            } else {
+                uint32_t r[32];
+                tc::tmem_ld_32x32(t_acc, r);
+                tc::tmem_ld_wait();
+                store_chunk(r, n0);
             }
+            // this warp's quarter of the accumulator is in registers / stored: hand the buffer back
+            tc::fence_before_sync();
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive(&tmem_empty[buf]);
         }
     }
     tc::fence_before_sync();
     __syncthreads();
     if (warp == 1) {
         tc::fence_after_sync();
-        tc::tmem_dealloc(tmem_base, BN);
+        tc::tmem_dealloc(tmem_base, 2 * BN);
     }
+}
+
+int sm_count() {
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    }
+    return n;
 }
 
 template <int BN>
 int launch(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc, int out_f32,
            int transpose_out, int* err, cudaStream_t s, const PushCtx* push = nullptr, const int4* tiles = nullptr,
-           const int* num_tiles = nullptr, int max_tiles = 0, int b_rows = 0, int splits = 1, long long split_stride = 0) {
+           const int* num_tiles = nullptr, int max_tiles = 0, int b_rows = 0, int splits = 1, long long split_stride = 0,
+           bool persistent = false) {
     CUtensorMap tmA, tmB;
     int rc = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)M, (uint64_t)K, (uint64_t)lda * 2, BM, BK);
     if (rc) return rc;
@@ -215,7 +271,14 @@ int launch(const void* A, const void* B, void* C, int M, int N, int K, int lda, 
         attr_set = true;
     }
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-    if (tiles != nullptr) grid = dim3(max_tiles, 1);
+    int tiles_n = 0, total_tiles = 0;
+    if (tiles != nullptr) {
+        grid = dim3(std::min(max_tiles, sm_count()), 1);          // persistent walk over the tile table
+    } else if (persistent) {
+        tiles_n = (int)grid.x;
+        total_tiles = (int)(grid.x * grid.y);
+        grid = dim3(std::min(total_tiles, sm_count()), 1);
+    }
     int kb_per_split = 0;
     if (splits > 1) {
         const int total_kb = (K + BK - 1) / BK;
@@ -223,7 +286,8 @@ int launch(const void* A, const void* B, void* C, int M, int N, int K, int lda, 
         grid.z = (total_kb + kb_per_split - 1) / kb_per_split;
     }
     sl_launch(kern, grid, 192, GemmCfg<BN>::SMEM, s, tmA, tmB, C, M, N, K, ldc, out_f32, transpose_out, err, push ? 1 : 0,
-                                              push ? *push : PushCtx{}, tiles, num_tiles, kb_per_split, split_stride);
+                                              push ? *push : PushCtx{}, tiles, num_tiles, kb_per_split, split_stride, tiles_n,
+                                              total_tiles);
     return (int)cudaGetLastError();
 }
 
@@ -236,9 +300,10 @@ SL_API int sl_gemm_bf16_tcgen05(const void* A, const void* B, void* C, int M, in
     if (M <= 0 || N <= 0 || K <= 0) return 0;
     if (K % 8 != 0 || lda % 8 != 0 || ldb % 8 != 0) return -1;
     if ((out_f32 ? ldc % 4 : ldc % 8) != 0) return -1;
-    if (bn == 64) return launch<64>(A, B, C, M, N, K, lda, ldb, ldc, out_f32, 0, (int*)err, s);
-    if (bn == 256) return launch<256>(A, B, C, M, N, K, lda, ldb, ldc, out_f32, 0, (int*)err, s);
-    return launch<128>(A, B, C, M, N, K, lda, ldb, ldc, out_f32, 0, (int*)err, s);
+    // one CTA per SM walks the tile grid: the epilogue of a tile overlaps the loads and MMAs of the next
+    if (bn == 64) return launch<64>(A, B, C, M, N, K, lda, ldb, ldc, out_f32, 0, (int*)err, s, nullptr, nullptr, nullptr, 0, 0, 1, 0, true);
+    if (bn == 256) return launch<256>(A, B, C, M, N, K, lda, ldb, ldc, out_f32, 0, (int*)err, s, nullptr, nullptr, nullptr, 0, 0, 1, 0, true);
+    return launch<128>(A, B, C, M, N, K, lda, ldb, ldc, out_f32, 0, (int*)err, s, nullptr, nullptr, nullptr, 0, 0, 1, 0, true);
 }
 
 // Weight-streaming form for a few token rows (T <= 32): y[T, N] = x[T, K] * W[N, K]^T computed as

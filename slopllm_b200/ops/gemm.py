@@ -41,14 +41,15 @@ def gemm_large(x: torch.Tensor, w, out_f32: bool = False) -> torch.Tensor:
     return tcgen05.gemm_bf16(x, _weight_bf16(w), out_f32)
 
 
-def grouped_gemm(a: torch.Tensor, b_stack: torch.Tensor, offsets: torch.Tensor, out_f32: bool) -> torch.Tensor:
+def grouped_gemm(a: torch.Tensor, b_stack: torch.Tensor, offsets: torch.Tensor, out_f32: bool, bn: int = 0) -> torch.Tensor:
     """C[r] = A[r] @ B[g(r)]^T where rows [offsets[g], offsets[g+1]) belong to group g.
     a [M, K] bf16, b_stack [G, Nn, K] bf16, offsets int32 [G + 1] on the device."""
     M, K = a.shape
     G, Nn, _ = b_stack.shape
     c = torch.empty(M, Nn, dtype=torch.float32 if out_f32 else torch.bfloat16, device=a.device)
     # short reductions are dominated by the per-tile set-up and the output store: use 128 x 256 tiles there
-    bn = 256 if (K <= 1024 and Nn >= 1024) else 128
+    if bn == 0:
+        bn = 256 if (K <= 1024 and Nn >= 1024) else 128
     ncol = (Nn + bn - 1) // bn
     max_tiles = ((M + 127) // 128 + G) * ncol
     tiles = torch.empty(max_tiles, 4, dtype=torch.int32, device=a.device)
