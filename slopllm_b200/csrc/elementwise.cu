@@ -497,6 +497,64 @@ SL_API int sl_silu_mul(void* out, const void* gu, int T, int I, cudaStream_t s) 
     return SL_LAUNCH_CHECK();
 }
 
+// SwiGLU on f16 rows (the NVFP4 prefill GEMMs run in f16): out[t, i] = silu(gu[t, i]) * gu[t, I + i].
+__global__ void silu_mul_h_kernel(__half* __restrict__ out, const __half* __restrict__ gu, size_t total_pairs, int I) {
+    pdl_grid_sync();
+    const int I2 = I / 2;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total_pairs; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = idx / I2, i = (idx % I2) * 2;
+        const float2 g = __half22float2(*reinterpret_cast<const __half2*>(gu + t * 2 * I + i));
+        const float2 u = __half22float2(*reinterpret_cast<const __half2*>(gu + t * 2 * I + I + i));
+        *reinterpret_cast<__half2*>(out + t * I + i) = __floats2half2_rn(g.x / (1.f + __expf(-g.x)) * u.x, g.y / (1.f + __expf(-g.y)) * u.y);
+    }
+}
+
+SL_API int sl_silu_mul_h(void* out, const void* gu, int T, int I, cudaStream_t s) {
+    if (I % 2 != 0) return -1;
+    const size_t total = (size_t)T * (I / 2);
+    if (total == 0) return 0;
+    int blocks = (int)((total + 255) / 256);
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    sl_launch(silu_mul_h_kernel, blocks, 256, 0, s, (__half*)out, (const __half*)gu, total, I);
+    return SL_LAUNCH_CHECK();
+}
+
+// out[m, :] = f16(x[src[m], :]) for bf16 x (src null: identity).  One warp per 256 columns of a row, 16-byte accesses.
+__global__ void gather_rows_f16_kernel(__half* __restrict__ out, const bf16* __restrict__ x, const int* __restrict__ src, int M, int H,
+                                       int ldx, int rows_x) {
+    pdl_grid_sync();
+    const int per_row = H / 8;                              // 16-byte pieces per row
+    const size_t total = (size_t)M * per_row;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const int m = (int)(idx / per_row), c = (int)(idx % per_row) * 8;
+        const int r = src ? src[m] : m;
+        uint4 o = make_uint4(0u, 0u, 0u, 0u);
+        if (r >= 0 && r < rows_x) {
+            const uint4 v = *reinterpret_cast<const uint4*>(x + (size_t)r * ldx + c);
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+            uint32_t h[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 f = bf162_to_f2(w[i]);
+                __half2 hv = __floats2half2_rn(f.x, f.y);
+                h[i] = *reinterpret_cast<uint32_t*>(&hv);
+            }
+            o = make_uint4(h[0], h[1], h[2], h[3]);
+        }
+        *reinterpret_cast<uint4*>(out + (size_t)m * H + c) = o;
+    }
+}
+
+SL_API int sl_gather_rows_f16(void* out, const void* x, const void* src, int M, int H, int ldx, int rows_x, cudaStream_t s) {
+    if (M <= 0) return 0;
+    if (H % 8 != 0 || ldx % 8 != 0) return -1;
+    const size_t total = (size_t)M * (H / 8);
+    int blocks = (int)((total + 255) / 256);
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    sl_launch(gather_rows_f16_kernel, blocks, 256, 0, s, (__half*)out, (const bf16*)x, (const int*)src, M, H, ldx, rows_x);
+    return SL_LAUNCH_CHECK();
+}
+
 // ---------------------------------------------------------------------------------------------
 // MoE routing: one warp per token (see route.cuh).
 template <int PER>

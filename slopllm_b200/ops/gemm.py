@@ -1,19 +1,82 @@
 """Large-M (prefill) linear layers and grouped expert GEMMs on the tcgen05 tensor cores.
 
 Dense bf16 weights go straight through `sl_gemm_bf16_tcgen05` (TMA-fed, TMEM accumulators).
-NVFP4 weights are first expanded to bf16 by `sl_nvfp4_dequant_bf16` (W4A16, the reference's
-numerics: `csrc/glm_mma_moe_coop.cu:351` also turns FP4 into BF16 before its MMA) and the MoE
-layer runs as two *grouped* GEMMs over the expert-sorted token rows with a device-built tile
-table (reference: sort + `grouped_mma_kernel` + unscatter, `csrc/glm_mma_moe.cu:110-619`).
+NVFP4 weights go through `sl_gemm_w4_tcgen05` / `sl_grouped_gemm_w4_tcgen05`, which expand the
+packed weight tile to f16 on its way into shared memory (W4A16, the reference's numerics:
+`csrc/glm_mma_moe_coop.cu:351` also turns FP4 into a 16-bit type before its MMA); shapes those
+kernels do not take (K not a multiple of 64) fall back to `sl_nvfp4_dequant_bf16` + the bf16 GEMM.
+The MoE layer runs as two *grouped* GEMMs over the expert-sorted token rows with a device-built
+tile table (reference: sort + `grouped_mma_kernel` + unscatter, `csrc/glm_mma_moe.cu:110-619`).
+`SLOPLLM_B200_W4_GEMM=0` forces the expansion path (comparison runs).
 """
 from __future__ import annotations
 
 import torch
 
+import os
+
 from . import native as N
 from . import tcgen05
 
 DEQUANT_BUDGET_BYTES = 3 << 30          # transient bf16 copy of expert weights per grouped launch
+W4_GEMM = os.environ.get("SLOPLLM_B200_W4_GEMM", "1") != "0"
+W4_DENSE_MAX_ROWS = 256                 # plain (non-grouped) NVFP4 linears take the fused kernel up to this many rows
+OUT_BF16, OUT_F32, OUT_F16 = 0, 1, 2
+
+
+def _w4_ok(K: int) -> bool:
+    return W4_GEMM and K % 64 == 0
+
+
+def to_f16_rows(x: torch.Tensor, src_rows: torch.Tensor | None = None, rows: int | None = None) -> torch.Tensor:
+    """f16 copy of bf16 rows, optionally gathered: out[m] = x[src_rows[m]] (rows outside x give zeros)."""
+    M = x.shape[0] if src_rows is None else (src_rows.numel() if rows is None else rows)
+    H = x.shape[1]
+    out = torch.empty(M, H, dtype=torch.float16, device=x.device)
+    N.call("sl_gather_rows_f16", out.data_ptr(), x.data_ptr(), N.ptr(src_rows), M, H, x.stride(0), x.shape[0], N.stream())
+    return out
+
+
+def _out_tensor(M: int, Nn: int, out_kind: int, dev) -> torch.Tensor:
+    dt = {OUT_BF16: torch.bfloat16, OUT_F32: torch.float32, OUT_F16: torch.float16}[out_kind]
+    pad = 4 if out_kind == OUT_F32 else 8
+    ld = (Nn + pad - 1) // pad * pad
+    return torch.empty(M, ld, dtype=dt, device=dev)[:, :Nn]
+
+
+def gemm_w4(x16: torch.Tensor, wq: torch.Tensor, ws: torch.Tensor, gs: torch.Tensor, out_kind: int, split: int = 0) -> torch.Tensor:
+    """y = x16 @ dequant(W)^T with W = NVFP4 [Nn, K/2] + e4m3 [Nn, K/16]; gs holds 1 global scale, or 2 with `split`
+    (output columns below `split` use the first)."""
+    M, K = x16.shape
+    Nn = wq.shape[0]
+    gs = gs.to(torch.float32).reshape(-1).contiguous()
+    y = _out_tensor(M, Nn, out_kind, x16.device)
+    bn = 256 if Nn >= 512 else 128
+    N.call("sl_gemm_w4_tcgen05", x16.data_ptr(), wq.data_ptr(), ws.data_ptr(), gs.data_ptr(), gs.numel(), split, y.data_ptr(),
+           M, Nn, K, x16.stride(0), y.stride(0), out_kind, tcgen05.error_flag(x16.device).data_ptr(), bn, N.stream())
+    return y
+
+
+def grouped_gemm_w4(a16: torch.Tensor, wq: torch.Tensor, ws: torch.Tensor, gs: torch.Tensor, offsets: torch.Tensor, out_kind: int,
+                    split: int = 0, bn: int = 0) -> torch.Tensor:
+    """Grouped form of `gemm_w4`: rows [offsets[g], offsets[g+1]) of a16 use weight matrix g of the stacks
+    wq [G, Nn, K/2], ws [G, Nn, K/16], gs [G] or [G, 2]."""
+    M, K = a16.shape
+    G, Nn, _ = wq.shape
+    gs = gs.to(torch.float32).contiguous()
+    g_per = gs.numel() // G
+    c = _out_tensor(M, Nn, out_kind, a16.device)
+    if bn == 0:
+        bn = 256 if Nn >= 512 else 128
+    ncol = (Nn + bn - 1) // bn
+    max_tiles = ((M + 127) // 128 + G) * ncol
+    tiles = torch.empty(max_tiles, 4, dtype=torch.int32, device=a16.device)
+    ntiles = torch.empty(1, dtype=torch.int32, device=a16.device)
+    N.call("sl_build_group_tiles", tiles.data_ptr(), ntiles.data_ptr(), offsets.data_ptr(), G, Nn, max_tiles, bn, N.stream())
+    N.call("sl_grouped_gemm_w4_tcgen05", a16.data_ptr(), wq.data_ptr(), ws.data_ptr(), gs.data_ptr(), g_per, split, c.data_ptr(),
+           M, Nn, K, a16.stride(0), c.stride(0), out_kind, tiles.data_ptr(), ntiles.data_ptr(), max_tiles,
+           tcgen05.error_flag(a16.device).data_ptr(), bn, N.stream())
+    return c
 
 
 def dequant_bf16(wp: torch.Tensor, scale: torch.Tensor, g: torch.Tensor, g_per: int = 1, split: int = 0) -> torch.Tensor:
@@ -38,6 +101,11 @@ def _weight_bf16(w) -> torch.Tensor:
 
 def gemm_large(x: torch.Tensor, w, out_f32: bool = False) -> torch.Tensor:
     """y = x @ W^T for T > 32 rows."""
+    # One weight matrix shared by many rows: expanding it once (a few MB) and running the bf16 GEMM at 1.0 - 1.2 PFLOP/s beats
+    # the in-kernel expansion, whose converter warps cap it near 0.45 PFLOP/s; the fused kernel wins when a matrix meets few rows.
+    if (w.is_nvfp4 and x.shape[0] <= W4_DENSE_MAX_ROWS and _w4_ok(x.shape[1]) and x.dtype == torch.bfloat16
+            and x.stride(0) % 8 == 0):
+        return gemm_w4(to_f16_rows(x), w.weight, w.scale, w.scale2, OUT_F32 if out_f32 else OUT_BF16)
     return tcgen05.gemm_bf16(x, _weight_bf16(w), out_f32)
 
 
@@ -47,9 +115,9 @@ def grouped_gemm(a: torch.Tensor, b_stack: torch.Tensor, offsets: torch.Tensor, 
     M, K = a.shape
     G, Nn, _ = b_stack.shape
     c = torch.empty(M, Nn, dtype=torch.float32 if out_f32 else torch.bfloat16, device=a.device)
-    # short reductions are dominated by the per-tile set-up and the output store: use 128 x 256 tiles there
+    # 128 x 256 tiles measured faster than 128 x 128 for both expert GEMMs of a prefill chunk
     if bn == 0:
-        bn = 256 if (K <= 1024 and Nn >= 1024) else 128
+        bn = 256 if Nn >= 512 else 128
     ncol = (Nn + bn - 1) // bn
     max_tiles = ((M + 127) // 128 + G) * ncol
     tiles = torch.empty(max_tiles, 4, dtype=torch.int32, device=a.device)
@@ -79,8 +147,22 @@ def moe_large(ops, x, experts, shared, ids, wts) -> torch.Tensor:
     inv = torch.empty_like(order)
     inv[order] = torch.arange(order.numel(), device=dev)
     rows_of = torch.where(mine, inv, torch.full_like(inv, -1)).to(torch.int32).contiguous()
-    xs = xb.index_select(0, torch.div(order, k, rounding_mode="floor"))          # [T*k, H] expert-sorted rows
-    M = xs.shape[0]
+    src_tok = torch.div(order, k, rounding_mode="floor")
+    M = order.numel()
+    if experts.is_nvfp4 and _w4_ok(H) and _w4_ok(I) and xb.stride(0) % 8 == 0:
+        # weights expanded inside the GEMMs: no transient bf16 copy, activations in f16
+        xs16 = to_f16_rows(xb, src_tok.to(torch.int32))                           # [T*k, H] expert-sorted rows
+        h = grouped_gemm_w4(xs16, experts.w13, experts.s13, experts.g13, offsets, OUT_F16, split=I)
+        act16 = torch.empty(M, I, dtype=torch.float16, device=dev)
+        N.call("sl_silu_mul_h", act16.data_ptr(), h.data_ptr(), M, I, N.stream())
+        y = grouped_gemm_w4(act16, experts.w2, experts.s2, experts.g2, offsets, OUT_BF16)
+        out = torch.empty(T, H, dtype=torch.float32, device=dev)
+        wts = wts.to(torch.float32).contiguous()
+        N.call("sl_moe_unsort_reduce", out.data_ptr(), y.data_ptr(), rows_of.data_ptr(), wts.data_ptr(), T, k, H, 0, 1, N.stream())
+        if shared is not None:
+            out += _shared_expert_large(xb, shared)
+        return out
+    xs = xb.index_select(0, src_tok)                                              # [T*k, H] expert-sorted rows
     per_expert = 3 * I * H * 2
     group = max(1, min(E, DEQUANT_BUDGET_BYTES // max(1, per_expert)))
     y = torch.empty(M, H, dtype=torch.bfloat16, device=dev)     # per-route outputs; the weighted un-sort accumulates in fp32
@@ -105,15 +187,21 @@ def moe_large(ops, x, experts, shared, ids, wts) -> torch.Tensor:
     wts = wts.to(torch.float32).contiguous()
     N.call("sl_moe_unsort_reduce", out.data_ptr(), y.data_ptr(), rows_of.data_ptr(), wts.data_ptr(), T, k, H, 0, 1, N.stream())
     if shared is not None:
-        if shared.is_nvfp4:
-            w13 = dequant_bf16(shared.w13[0], shared.s13[0], shared.g13[0], g_per=2, split=shared.inter)
-            w2 = dequant_bf16(shared.w2[0], shared.s2[0], shared.g2[0].reshape(1))
-        else:
-            w13, w2 = shared.w13[0], shared.w2[0]
-        h = tcgen05.gemm_bf16(xb, w13, False)
-        hs = torch.empty(T, shared.inter, dtype=torch.bfloat16, device=dev)
-        if h.stride(0) != h.shape[1]:
-            h = h.contiguous()
-        N.call("sl_silu_mul", hs.data_ptr(), h.data_ptr(), T, shared.inter, N.stream())
-        out += tcgen05.gemm_bf16(hs, w2, True)
+        out += _shared_expert_large(xb, shared)
     return out
+
+
+def _shared_expert_large(xb: torch.Tensor, shared) -> torch.Tensor:
+    """Shared expert over all rows (one weight matrix, many rows: expansion + bf16 GEMM).  Returns fp32 [T, H]."""
+    T = xb.shape[0]
+    if shared.is_nvfp4:
+        w13 = dequant_bf16(shared.w13[0], shared.s13[0], shared.g13[0], g_per=2, split=shared.inter)
+        w2 = dequant_bf16(shared.w2[0], shared.s2[0], shared.g2[0].reshape(1))
+    else:
+        w13, w2 = shared.w13[0], shared.w2[0]
+    h = tcgen05.gemm_bf16(xb, w13, False)
+    hs = torch.empty(T, shared.inter, dtype=torch.bfloat16, device=xb.device)
+    if h.stride(0) != h.shape[1]:
+        h = h.contiguous()
+    N.call("sl_silu_mul", hs.data_ptr(), h.data_ptr(), T, shared.inter, N.stream())
+    return tcgen05.gemm_bf16(hs, w2, True)

@@ -170,6 +170,10 @@ _SIGS = {
     "sl_mhc_post": [vp, vp, vp, vp, vp, i32, i32, vp],
     "sl_mhc_streams": [vp, vp, i32, i32, i32, vp],
     "sl_silu_mul": [vp, vp, i32, i32, vp],
+    "sl_silu_mul_h": [vp, vp, i32, i32, vp],
+    "sl_gather_rows_f16": [vp, vp, vp, i32, i32, i32, i32, vp],
+    "sl_gemm_w4_tcgen05": [vp, vp, vp, vp, i32, i32, vp, i32, i32, i32, i32, i32, i32, vp, i32, vp],
+    "sl_grouped_gemm_w4_tcgen05": [vp, vp, vp, vp, i32, i32, vp, i32, i32, i32, i32, i32, i32, vp, vp, i32, vp, i32, vp],
     "sl_route_topk": [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, f32, vp],
     "sl_topk_to_slots": [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp, vp],
     "sl_rotate_input_ids": [vp, vp, vp, vp, i32, vp],

@@ -339,6 +339,50 @@ def test_moe_large_matches_reference():
     close(ops.moe_tp(x, lw), ref.moe_tp(x, lw), tol=2e-2, what="moe large")
 
 
+@pytest.mark.parametrize("M,N,K", [(300, 512, 1024), (129, 200, 64), (4096, 768, 2048)])
+@pytest.mark.parametrize("out_kind", [0, 1, 2])
+def test_gemm_w4_fused_dequant(M, N, K, out_kind):
+    """NVFP4-weight GEMM that expands the weight tile inside the kernel, against x @ dequant(W)^T in fp32
+    (ragged M and N, one and two global scales, the three output types)."""
+    from slopllm_b200.ops import gemm, tcgen05
+    g = torch.Generator(device=DEV).manual_seed(M + N + K)
+    wq, ws, _ = quant.random_nvfp4((N, K), g, DEV)
+    x = torch.randn(M, K, device=DEV, generator=g).to(torch.bfloat16)
+    for gs, split in ((torch.tensor([0.75], device=DEV), 0), (torch.tensor([0.5, 2.0], device=DEV), 128)):
+        y = gemm.gemm_w4(gemm.to_f16_rows(x), wq, ws, gs, out_kind, split=split)
+        wd = quant.nvfp4_dequantize(wq, ws, torch.ones((), device=DEV), torch.float32)
+        col = torch.full((N,), float(gs[0]), device=DEV) if gs.numel() == 1 else torch.where(
+            torch.arange(N, device=DEV) < split, gs[0], gs[1])
+        ref = (x.float() @ wd.t()) * col
+        assert y.dtype == {0: torch.bfloat16, 1: torch.float32, 2: torch.float16}[out_kind]
+        close(y, ref, tol=1e-2, what=f"w4 gemm {M}x{N}x{K} kind={out_kind} scales={gs.numel()}")
+    assert int(tcgen05.error_flag(x.device)[0]) == 0
+
+
+def test_grouped_gemm_w4_ragged_groups():
+    """Grouped NVFP4-weight GEMM over expert-sorted rows: empty groups, groups shorter and longer than a 128-row tile."""
+    from slopllm_b200.ops import gemm, tcgen05
+    g = torch.Generator(device=DEV).manual_seed(5)
+    G, N, K = 6, 512, 256
+    counts = [0, 130, 7, 0, 256, 91]
+    M = sum(counts)
+    wq, ws, _ = quant.random_nvfp4((G, N, K), g, DEV)
+    gs = torch.rand(G, 2, device=DEV, generator=g) + 0.5
+    a = torch.randn(M, K, device=DEV, generator=g).to(torch.bfloat16)
+    off = torch.tensor([0] + list(torch.tensor(counts).cumsum(0)), dtype=torch.int32, device=DEV)
+    for bn in (128, 256):
+        c = gemm.grouped_gemm_w4(gemm.to_f16_rows(a), wq, ws, gs, off, 1, split=N // 2, bn=bn)
+        r0 = 0
+        for gi, n in enumerate(counts):
+            if n == 0:
+                continue
+            wd = quant.nvfp4_dequantize(wq[gi], ws[gi], torch.ones((), device=DEV), torch.float32)
+            col = torch.where(torch.arange(N, device=DEV) < N // 2, gs[gi, 0], gs[gi, 1])
+            close(c[r0:r0 + n], (a[r0:r0 + n].float() @ wd.t()) * col, tol=1e-2, what=f"grouped w4 group {gi} bn={bn}")
+            r0 += n
+    assert int(tcgen05.error_flag(a.device)[0]) == 0
+
+
 def test_argmax():
     ops = cuda_ops(GlmMoeDsaConfig.tiny())
     x = torch.randn(5, 154880, device=DEV)
