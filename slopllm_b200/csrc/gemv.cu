@@ -544,9 +544,51 @@ __global__ void moe_unsort_reduce_kernel(float* __restrict__ out, const void* __
     }
 }
 
+// Same for bf16 rows with H a multiple of 8: a thread owns 8 columns (16-byte loads, all rows of the token in flight).
+__global__ void __launch_bounds__(256) moe_unsort_reduce_bf16x8_kernel(float* __restrict__ out, const bf16* __restrict__ y,
+                                                                       const int* __restrict__ rows_of, const float* __restrict__ wts,
+                                                                       int k, int H, int accumulate) {
+    pdl_grid_sync();
+    const int t = blockIdx.y;
+    const int n = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+    if (n >= H) return;
+    float v[8];
+    float* o = out + (size_t)t * H + n;
+    if (accumulate) {
+        const float4 a = *reinterpret_cast<const float4*>(o), b = *reinterpret_cast<const float4*>(o + 4);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = 0.f;
+    }
+    for (int j0 = 0; j0 < k; j0 += 8) {
+        uint4 u[8];
+        float w[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int r = j0 + j < k ? rows_of[t * k + j0 + j] : -1;
+            w[j] = r >= 0 ? wts[t * k + j0 + j] : 0.f;
+            u[j] = r >= 0 ? ldg_nc_16(y + (size_t)r * H + n) : make_uint4(0u, 0u, 0u, 0u);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float2 a = bf162_to_f2(u[j].x), b = bf162_to_f2(u[j].y), c = bf162_to_f2(u[j].z), d = bf162_to_f2(u[j].w);
+            v[0] += w[j] * a.x; v[1] += w[j] * a.y; v[2] += w[j] * b.x; v[3] += w[j] * b.y;
+            v[4] += w[j] * c.x; v[5] += w[j] * c.y; v[6] += w[j] * d.x; v[7] += w[j] * d.y;
+        }
+    }
+    *reinterpret_cast<float4*>(o) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(o + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+
 SL_API int sl_moe_unsort_reduce(void* out, const void* y, const void* rows_of, const void* wts, int T, int k, int H, int accumulate,
                                 int y_bf16, cudaStream_t s) {
     if (T == 0) return 0;
+    if (y_bf16 && H % 8 == 0) {
+        sl_launch(moe_unsort_reduce_bf16x8_kernel, dim3((H / 8 + 255) / 256, T), 256, 0, s, (float*)out, (const bf16*)y,
+                  (const int*)rows_of, (const float*)wts, k, H, accumulate);
+        return SL_LAUNCH_CHECK();
+    }
     sl_launch(moe_unsort_reduce_kernel, dim3((H + 255) / 256, T), 256, 0, s, (float*)out, y, (const int*)rows_of,
                                                                      (const float*)wts, k, H, accumulate, y_bf16);
     return SL_LAUNCH_CHECK();

@@ -137,30 +137,32 @@ def moe_large(ops, x, experts, shared, ids, wts) -> torch.Tensor:
     E, I = experts.num_experts, experts.inter
     dev = x.device
     xb = x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16)
-    flat = ids.reshape(-1).to(torch.int64) - experts.expert_offset
-    mine = (flat >= 0) & (flat < E)
-    key = torch.where(mine, flat, torch.full_like(flat, E))
-    order = torch.argsort(key, stable=True)
-    counts = torch.bincount(key, minlength=E + 1)[:E]
-    offsets = torch.zeros(E + 1, dtype=torch.int32, device=dev)
-    offsets[1:] = torch.cumsum(counts, 0).to(torch.int32)
-    inv = torch.empty_like(order)
-    inv[order] = torch.arange(order.numel(), device=dev)
-    rows_of = torch.where(mine, inv, torch.full_like(inv, -1)).to(torch.int32).contiguous()
-    src_tok = torch.div(order, k, rounding_mode="floor")
-    M = order.numel()
+    # stable counting sort of the routes by expert on the device: offsets [E + 1], sorted row -> token, route -> sorted row
+    ids32 = ids.reshape(-1).to(torch.int32).contiguous()
+    M = ids32.numel()
+    scratch = torch.empty(((M + 1023) // 1024) * (E + 1), dtype=torch.int32, device=dev)
+    offsets = torch.empty(E + 1, dtype=torch.int32, device=dev)
+    order = torch.empty(M, dtype=torch.int32, device=dev)
+    rows_of = torch.empty(M, dtype=torch.int32, device=dev)
+    src_tok = torch.empty(M, dtype=torch.int32, device=dev)
+    N.call("sl_moe_sort_routes", ids32.data_ptr(), M, k, experts.expert_offset, E, scratch.data_ptr(), offsets.data_ptr(),
+           order.data_ptr(), rows_of.data_ptr(), src_tok.data_ptr(), N.stream())
+    wts = wts.to(torch.float32).contiguous()
+    # the shared expert writes the fp32 result first, the routed experts accumulate into it
+    out = _shared_expert_large(xb, shared) if shared is not None else None
+    if out is not None and (out.stride(0) != H or out.dtype != torch.float32):
+        out = out.to(torch.float32).contiguous()
+    acc = 0 if out is None else 1
+    if out is None:
+        out = torch.empty(T, H, dtype=torch.float32, device=dev)
     if experts.is_nvfp4 and _w4_ok(H) and _w4_ok(I) and xb.stride(0) % 8 == 0:
         # weights expanded inside the GEMMs: no transient bf16 copy, activations in f16
-        xs16 = to_f16_rows(xb, src_tok.to(torch.int32))                           # [T*k, H] expert-sorted rows
+        xs16 = to_f16_rows(xb, src_tok)                                           # [T*k, H] expert-sorted rows
         h = grouped_gemm_w4(xs16, experts.w13, experts.s13, experts.g13, offsets, OUT_F16, split=I)
         act16 = torch.empty(M, I, dtype=torch.float16, device=dev)
         N.call("sl_silu_mul_h", act16.data_ptr(), h.data_ptr(), M, I, N.stream())
         y = grouped_gemm_w4(act16, experts.w2, experts.s2, experts.g2, offsets, OUT_BF16)
-        out = torch.empty(T, H, dtype=torch.float32, device=dev)
-        wts = wts.to(torch.float32).contiguous()
-        N.call("sl_moe_unsort_reduce", out.data_ptr(), y.data_ptr(), rows_of.data_ptr(), wts.data_ptr(), T, k, H, 0, 1, N.stream())
-        if shared is not None:
-            out += _shared_expert_large(xb, shared)
+        N.call("sl_moe_unsort_reduce", out.data_ptr(), y.data_ptr(), rows_of.data_ptr(), wts.data_ptr(), T, k, H, acc, 1, N.stream())
         return out
     xs = xb.index_select(0, src_tok)                                              # [T*k, H] expert-sorted rows
     per_expert = 3 * I * H * 2
@@ -183,11 +185,7 @@ def moe_large(ops, x, experts, shared, ids, wts) -> torch.Tensor:
         else:                                                                      # keep only this group's rows
             lo, hi = int(offsets[g0]), int(offsets[g1])
             y[lo:hi] = yg[lo:hi]
-    out = torch.empty(T, H, dtype=torch.float32, device=dev)
-    wts = wts.to(torch.float32).contiguous()
-    N.call("sl_moe_unsort_reduce", out.data_ptr(), y.data_ptr(), rows_of.data_ptr(), wts.data_ptr(), T, k, H, 0, 1, N.stream())
-    if shared is not None:
-        out += _shared_expert_large(xb, shared)
+    N.call("sl_moe_unsort_reduce", out.data_ptr(), y.data_ptr(), rows_of.data_ptr(), wts.data_ptr(), T, k, H, acc, 1, N.stream())
     return out
 
 

@@ -171,6 +171,7 @@ _SIGS = {
     "sl_mhc_streams": [vp, vp, i32, i32, i32, vp],
     "sl_silu_mul": [vp, vp, i32, i32, vp],
     "sl_silu_mul_h": [vp, vp, i32, i32, vp],
+    "sl_moe_sort_routes": [vp, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp],
     "sl_gather_rows_f16": [vp, vp, vp, i32, i32, i32, i32, vp],
     "sl_gemm_w4_tcgen05": [vp, vp, vp, vp, i32, i32, vp, i32, i32, i32, i32, i32, i32, vp, i32, vp],
     "sl_grouped_gemm_w4_tcgen05": [vp, vp, vp, vp, i32, i32, vp, i32, i32, i32, i32, i32, i32, vp, vp, i32, vp, i32, vp],

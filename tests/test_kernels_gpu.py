@@ -383,6 +383,32 @@ def test_grouped_gemm_w4_ragged_groups():
     assert int(tcgen05.error_flag(a.device)[0]) == 0
 
 
+@pytest.mark.parametrize("n_tok,k,E,offset", [(5, 4, 16, 0), (700, 8, 256, 0), (300, 8, 32, 64)])
+def test_moe_sort_routes_matches_stable_sort(n_tok, k, E, offset):
+    """Counting sort of routes by expert (prefill MoE) against a stable torch sort; `offset` makes some experts non-local."""
+    from slopllm_b200.ops import native as N
+    g = torch.Generator(device=DEV).manual_seed(n_tok)
+    total_e = E + 2 * offset
+    ids = torch.randint(0, total_e, (n_tok * k,), device=DEV, generator=g, dtype=torch.int32)
+    M = ids.numel()
+    scratch = torch.empty(((M + 1023) // 1024) * (E + 1), dtype=torch.int32, device=DEV)
+    offsets = torch.empty(E + 1, dtype=torch.int32, device=DEV)
+    order, rows_of, src_tok = (torch.empty(M, dtype=torch.int32, device=DEV) for _ in range(3))
+    N.call("sl_moe_sort_routes", ids.data_ptr(), M, k, offset, E, scratch.data_ptr(), offsets.data_ptr(), order.data_ptr(),
+           rows_of.data_ptr(), src_tok.data_ptr(), N.stream())
+    local = ids.long() - offset
+    key = torch.where((local >= 0) & (local < E), local, torch.full_like(local, E))
+    exp_order = torch.argsort(key, stable=True)
+    counts = torch.bincount(key, minlength=E + 1)
+    exp_off = torch.cat([torch.zeros(1, dtype=torch.long, device=DEV), counts.cumsum(0)])[:E + 1]
+    assert torch.equal(order.long(), exp_order)
+    assert torch.equal(offsets.long(), exp_off)
+    assert torch.equal(src_tok.long(), exp_order // k)
+    inv = torch.empty_like(exp_order)
+    inv[exp_order] = torch.arange(M, device=DEV)
+    assert torch.equal(rows_of.long(), torch.where(key < E, inv, torch.full_like(inv, -1)))
+
+
 def test_argmax():
     ops = cuda_ops(GlmMoeDsaConfig.tiny())
     x = torch.randn(5, 154880, device=DEV)
