@@ -115,6 +115,148 @@ __global__ void __launch_bounds__(256) indexer_score_kernel(IndexerScoreParams p
     }
 }
 
+// Prefill form: one CTA scores 8 consecutive query tokens (one per warp) against the same key tiles.  When the 8 tokens
+// belong to one sequence (a prefill chunk) a 64-key page (64 x 132 contiguous bytes) is copied into shared memory once
+// with 16-byte loads and all 8 warps take their B fragments from there, so each key row crosses L2 once per 8 tokens
+// instead of once per token with 4-byte loads; the next page is held in registers while the current one is multiplied.
+// Groups that mix sequences fall back to per-warp loads from the cache.  Same fragment layout and accumulation order as
+// the per-token kernel: the scores are bit-identical.  page_size == 64, keys_per_block a multiple of 64.
+bool g_indexer_tiled = true;
+
+template <int HI, int D>
+__global__ void __launch_bounds__(256) indexer_score_tile_kernel(IndexerScoreParams p, int T, int keys_per_block) {
+    pdl_grid_sync();
+    constexpr int MT = HI / 16, KS = D / 32, RB = D + 4, PAGE = 64;
+    constexpr int PAGE_BYTES = PAGE * RB;                 // 8448 = 528 x 16
+    constexpr int PIECES = PAGE_BYTES / 16, LD = (PIECES + 255) / 256;
+    static_assert(PAGE_BYTES % 16 == 0, "a page is a whole number of 16-byte pieces");
+    __shared__ __align__(16) uint8_t tile[PAGE_BYTES];
+    __shared__ int s_bidx[8], s_nloc[8];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, c = lane & 3;
+    const int t = blockIdx.y * 8 + warp;
+    const bool live = t < T;
+    const int pos = live ? p.positions[t] : -1;
+    // tokens whose visible keys are all selected need no scores
+    const int n_local = (live && pos + 1 > p.top_k) ? local_visible(pos, p.cp_world, p.cp_rank) : 0;
+    if (lane == 0) { s_bidx[warp] = live ? p.batch_idx[t] : -1; s_nloc[warp] = n_local; }
+    __syncthreads();
+    int n_max = 0;
+    bool same = true;
+    int b0 = -1;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        n_max = max(n_max, s_nloc[i]);
+        if (s_nloc[i] > 0) { if (b0 < 0) b0 = s_bidx[i]; else same = same && (s_bidx[i] == b0); }
+    }
+    const int k_begin = blockIdx.x * keys_per_block;
+    if (k_begin >= n_max) return;                          // CTA-uniform
+    const int k_end_cta = min(n_max, k_begin + keys_per_block);
+    const int k_end = min(n_local, k_end_cta);             // this warp's bound (may be below k_begin)
+
+    uint32_t a[MT][KS][4];
+    float w[MT][2];
+    if (n_local > 0) {
+        const uint8_t* q = p.q8 + (size_t)t * HI * D;
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+#pragma unroll
+            for (int s = 0; s < KS; ++s) {
+                const int d0 = c * (D / 4) + s * 8;
+                a[m][s][0] = *reinterpret_cast<const uint32_t*>(q + (size_t)(m * 16 + g) * D + d0);
+                a[m][s][1] = *reinterpret_cast<const uint32_t*>(q + (size_t)(m * 16 + g + 8) * D + d0);
+                a[m][s][2] = *reinterpret_cast<const uint32_t*>(q + (size_t)(m * 16 + g) * D + d0 + 4);
+                a[m][s][3] = *reinterpret_cast<const uint32_t*>(q + (size_t)(m * 16 + g + 8) * D + d0 + 4);
+            }
+            w[m][0] = p.w_eff[(size_t)t * HI + m * 16 + g];
+            w[m][1] = p.w_eff[(size_t)t * HI + m * 16 + g + 8];
+        }
+    } else {
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+#pragma unroll
+            for (int s = 0; s < KS; ++s) a[m][s][0] = a[m][s][1] = a[m][s][2] = a[m][s][3] = 0u;
+            w[m][0] = w[m][1] = 0.f;
+        }
+    }
+    // scores of the 8 keys [j0, j0 + 8) from B fragments at `rows` (row stride RB); keys at or beyond k_end are not written
+    auto score8 = [&](const uint8_t* rows, int j0) {
+        const uint8_t* row = rows + g * RB;
+        uint32_t b[KS][2];
+#pragma unroll
+        for (int s = 0; s < KS; ++s) {
+            b[s][0] = *reinterpret_cast<const uint32_t*>(row + c * (D / 4) + s * 8);
+            b[s][1] = *reinterpret_cast<const uint32_t*>(row + c * (D / 4) + s * 8 + 4);
+        }
+        float part[2] = {0.f, 0.f};
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+            float d[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int s = 0; s < KS; ++s) mma_e4m3_m16n8k32(d, a[m][s], b[s]);
+            part[0] += w[m][0] * fmaxf(d[0], 0.f) + w[m][1] * fmaxf(d[2], 0.f);
+            part[1] += w[m][0] * fmaxf(d[1], 0.f) + w[m][1] * fmaxf(d[3], 0.f);
+        }
+#pragma unroll
+        for (int o = 4; o < 32; o <<= 1) {
+            part[0] += __shfl_xor_sync(0xffffffffu, part[0], o);
+            part[1] += __shfl_xor_sync(0xffffffffu, part[1], o);
+        }
+        if (g == 0) {
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int jj = j0 + 2 * c + i;
+                if (jj < k_end) p.scores[(size_t)t * p.ld_scores + jj] = part[i] * *reinterpret_cast<const float*>(rows + (2 * c + i) * RB + D);
+            }
+        }
+    };
+
+    if (same) {
+        const int* pt = p.page_table + (size_t)b0 * p.pt_stride;
+        uint4 nxt[LD];
+        auto fetch = [&](int j0) {                         // the page of local keys [j0, j0 + 64) into registers
+            const int pidx = j0 / PAGE;
+            bool ok = guard_ok(p.guard, 21, pidx, p.pt_stride);
+            long long base = 0;
+            if (ok) {
+                base = (long long)pt[pidx] * PAGE;
+                if (p.num_slots != 0 && !guard_ok(p.guard, 22, base + PAGE - 1, p.num_slots)) ok = false;
+            }
+            const uint8_t* src = p.idx_cache + (size_t)base * RB;
+#pragma unroll
+            for (int i = 0; i < LD; ++i) {
+                const int piece = threadIdx.x + i * 256;
+                nxt[i] = (ok && piece < PIECES) ? ldg_nc_16(src + piece * 16) : make_uint4(0u, 0u, 0u, 0u);
+            }
+        };
+        fetch(k_begin);
+        for (int j0 = k_begin; j0 < k_end_cta; j0 += PAGE) {
+            __syncthreads();                               // every warp is done with the previous page
+#pragma unroll
+            for (int i = 0; i < LD; ++i) {
+                const int piece = threadIdx.x + i * 256;
+                if (piece < PIECES) *reinterpret_cast<uint4*>(tile + piece * 16) = nxt[i];
+            }
+            __syncthreads();
+            if (j0 + PAGE < k_end_cta) fetch(j0 + PAGE);
+            if (j0 < k_end) {                              // warp-uniform
+#pragma unroll 2
+                for (int nt = 0; nt < PAGE / 8; ++nt)
+                    if (j0 + nt * 8 < k_end) score8(tile + nt * 8 * RB, j0 + nt * 8);
+            }
+        }
+    } else if (n_local > 0) {
+        const int* pt = p.page_table + (size_t)p.batch_idx[t] * p.pt_stride;
+        for (int j0 = k_begin; j0 < k_end; j0 += 8) {
+            const int pidx = j0 / p.page_size;
+            if (!guard_ok(p.guard, 21, pidx, p.pt_stride)) continue;
+            const size_t slot = (size_t)pt[pidx] * p.page_size + (j0 % p.page_size);
+            if (p.num_slots != 0 && !guard_ok(p.guard, 22, (long long)slot + 7, p.num_slots)) continue;
+            score8(p.idx_cache + slot * RB, j0);
+        }
+    }
+}
+
 // Generic CUDA-core scorer for other head counts / dims (small test models).
 __global__ void indexer_score_generic_kernel(IndexerScoreParams p, int keys_per_block) {
     pdl_grid_sync();
@@ -153,7 +295,13 @@ SL_API int sl_indexer_scores(const IndexerScoreParams* p, int T, int max_local, 
     int kpb = 512;
     while (kpb > 64 && (long)((max_local + kpb - 1) / kpb) * T < 296) kpb >>= 1;
     dim3 grid((max_local + kpb - 1) / kpb, T);
-    if (p->Hi == 32 && p->D == 128) {
+    if (p->Hi == 32 && p->D == 128 && p->page_size == 64 && T > 32 && g_indexer_tiled) {
+        // prefill: 8 tokens per CTA share the key pages
+        const int groups = (T + 7) / 8;
+        int kt = 2048;
+        while (kt > 64 && (long)((max_local + kt - 1) / kt) * groups < 296) kt >>= 1;
+        sl_launch(indexer_score_tile_kernel<32, 128>, dim3((max_local + kt - 1) / kt, groups), 256, 0, s, *p, T, kt);
+    } else if (p->Hi == 32 && p->D == 128) {
         sl_launch(indexer_score_kernel<32, 128>, grid, 256, 0, s, *p, kpb);
     } else {
         const size_t smem = (size_t)(p->Hi * p->D + p->Hi) * sizeof(float);
@@ -162,6 +310,9 @@ SL_API int sl_indexer_scores(const IndexerScoreParams* p, int T, int max_local, 
     }
     return SL_LAUNCH_CHECK();
 }
+
+// 0 keeps the per-token kernel for every shape (comparison runs); default 1.
+SL_API void sl_indexer_set_tiled(int on) { g_indexer_tiled = on != 0; }
 
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t order_key(float f) {

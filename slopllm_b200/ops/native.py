@@ -35,6 +35,9 @@ def kernels() -> C.CDLL:
     lib.sl_set_pdl.argtypes = [i32]
     lib.sl_set_pdl.restype = None
     lib.sl_set_pdl(0 if os.environ.get("SLOPLLM_B200_PDL", "1") == "0" else 1)
+    lib.sl_indexer_set_tiled.argtypes = [i32]
+    lib.sl_indexer_set_tiled.restype = None
+    lib.sl_indexer_set_tiled(0 if os.environ.get("SLOPLLM_B200_INDEXER_TILED", "1") == "0" else 1)
     lib.sl_sparse_mla_set_transposed.argtypes = [i32]
     lib.sl_sparse_mla_set_transposed.restype = None
     lib.sl_sparse_mla_set_transposed(0 if os.environ.get("SLOPLLM_B200_MLA_TRANSPOSED", "1") == "0" else 1)

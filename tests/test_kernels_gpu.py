@@ -217,6 +217,40 @@ def test_indexer_topk(which, ctx, cp):
         assert torch.all(valid[1:] > valid[:-1])
 
 
+@pytest.mark.parametrize("cp", [(1, 0), (2, 1)])
+def test_indexer_prefill_tiles_match_per_token_kernel(cp):
+    """More than 32 query rows take the prefill scorer (8 tokens per CTA share key pages in shared memory; a group that mixes
+    sequences loads per warp): same selection as the fp32 reference, same positions and scores as the per-token kernel."""
+    from slopllm_b200.ops import native as N
+    cfg = mini_cfg()
+    ops, ref = cuda_ops(cfg), RefOps(cfg)
+    W, r = cp
+    ctx = 1500
+    n_pages = -(-ctx // (64 * W)) + 1
+    positions = list(range(ctx - 36, ctx)) + [ctx - 1, 900, cfg.index_topk - 1, 10]        # 36 rows of sequence 0, 4 of sequence 1
+    st = _state(cfg, positions, [0] * 36 + [1] * 4, n_pages, 2, W, r)
+    g = torch.Generator(device=DEV).manual_seed(77)
+    Di, Hi, T = cfg.index_head_dim, cfg.index_n_heads, len(positions)
+    cache = type("C", (), {})()
+    cache.idx = quant.pack_index_rows(torch.randn(2 * n_pages * 64, Di, device=DEV, generator=g))
+    q = torch.randn(T, Hi, Di, device=DEV, generator=g)
+    hw = torch.rand(T, Hi, device=DEV, generator=g)
+    q8f, weff = R.indexer_quantize_q(q, hw, Di ** -0.5)
+    q8 = q8f.to(torch.float8_e4m3fn).view(torch.uint8)
+    pos, sc = ops.indexer_topk(q8, weff, cache, st)
+    N.kernels().sl_indexer_set_tiled(0)
+    try:
+        st.extra.clear()
+        pos2, sc2 = ops.indexer_topk(q8, weff, cache, st)
+    finally:
+        N.kernels().sl_indexer_set_tiled(1)
+    assert torch.equal(pos, pos2) and torch.equal(sc, sc2)
+    epos, _ = ref.indexer_topk(q8f, weff, cache, st)
+    for t in range(T):
+        a, b = set(pos[t][pos[t] >= 0].tolist()), set(epos[t][epos[t] >= 0].tolist())
+        assert len(a) == len(b) and len(a ^ b) <= max(2, len(b) // 100), (t, len(a), len(b), len(a ^ b))
+
+
 @pytest.mark.parametrize("which", ["tiny", "mini"])
 def test_sparse_mla_and_v_expand(which):
     cfg = GlmMoeDsaConfig.tiny() if which == "tiny" else mini_cfg()

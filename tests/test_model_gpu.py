@@ -88,3 +88,38 @@ def test_engine_graph_equals_eager_and_mtp_consistent():
     # CUDA-core ones: allow the greedy paths to part late on a near-tie
     plain = [[runs[True][i][b] for i in range(5)] for b in range(2)]
     assert [s[:5] for s in streams] == plain
+
+
+def _poison_free_memory(dev, chunks: int = 6, mib: int = 256) -> None:
+    """Fill memory that the caching allocator will hand out next with NaN patterns (0xFF bytes), then free it."""
+    held = [torch.full((mib << 20,), 0xFF, dtype=torch.uint8, device=dev) for _ in range(chunks)]
+    torch.cuda.synchronize()
+    del held
+
+
+@pytest.mark.parametrize("graph", [False, True])
+def test_dirty_scratch_gives_identical_tokens(graph):
+    """Scratch hygiene (the reference's `tests/python/test_cuda_resets.py`): a run whose fresh allocations come back full of
+    NaN bit patterns must produce the tokens of a clean run, eager and graph-replayed: no kernel reads what it did not write."""
+    cfg = _mini()
+    dev = torch.device("cuda")
+    ctx = ParallelContext(device=dev)
+    w = random_model(cfg, 0, dev, torch.bfloat16)
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, cfg.vocab_size, (130,), generator=g).tolist() for _ in range(2)]
+    runs = []
+    for rep in range(2):
+        if rep:
+            _poison_free_memory(dev)
+        eng = Engine(cfg, GlmMoeDsaModel(cfg, w, ctx), num_pages=24, max_batch=2, max_seq_len=512, cuda_graph=graph)
+        seqs = [eng.kv.new_sequence() for _ in range(2)]
+        last, _ = eng.prefill(seqs, prompts, chunk_size=64)
+        toks = [list(last)]
+        for _ in range(6):
+            last = eng.decode_step(seqs, last)
+            toks.append(list(last))
+        eng.check_device_errors()
+        runs.append(toks)
+        del eng, seqs
+        torch.cuda.synchronize()
+    assert runs[0] == runs[1]
