@@ -6,6 +6,9 @@ for kernel profiling and per-rank timing.
     python -m slopllm_b200.cli.profile_step --batch 8 --context 4096 --tp-shape 8 --layers 78 --timed 30
         CUDA-graph replay timed with CUDA events: the per-rank kernel chain of a TP-8 step
 
+    python -m slopllm_b200.cli.profile_step --batch 1 --context 4096 --tp-shape 8 --layers 78 --mtp 3 --timed 20
+        speculative steps (3 drafts + verification + reseed) instead of plain decode steps; without --timed they run eagerly
+
     python -m slopllm_b200.cli.profile_step --prefill 2048 --tp-shape 8 --layers 5
         one eager prefill chunk (tcgen05 GEMMs, grouped expert GEMMs, prefill attention / indexer)
     python -m slopllm_b200.cli.profile_step --prefill 4096 --tp-shape 8 --layers 6 --op-times
@@ -81,6 +84,28 @@ def main(argv=None) -> int:
             eng.kv.truncate(s, 0)
         torch.cuda.synchronize()
         out = {"mode": "prefill", "tokens": args.prefill, "next": toks}
+        if timers is not None:
+            out["op_times"] = timers.summary()
+        print(json.dumps(out))
+        return 0
+    if args.mtp > 0:
+        # speculative steps: D drafts from the MTP layer, one verification pass of the main model, reseed
+        hs = [torch.zeros(1, cfg.hidden_size, dtype=torch.bfloat16, device=dev) for _ in seqs]
+        seed = eng.mtp_seed(seqs, last, hs)
+        n = args.timed if args.timed > 0 else args.steps
+        for _ in range(5 if args.timed > 0 else 0):
+            _, last, seed = eng.mtp_decode_step(seqs, last, seed)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for i in range(n):
+            if timers is not None and i == n - 1:
+                timers.reset()
+            _, last, seed = eng.mtp_decode_step(seqs, last, seed)
+        b.record()
+        torch.cuda.synchronize()
+        out = {"mode": "mtp-graph" if args.timed > 0 else "mtp-eager", "mtp": args.mtp, "batch": B, "steps": n,
+               "ms_per_step": a.elapsed_time(b) / n, "last": last}
         if timers is not None:
             out["op_times"] = timers.summary()
         print(json.dumps(out))
