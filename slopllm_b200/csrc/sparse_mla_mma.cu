@@ -24,6 +24,8 @@ struct Params {
     float* lse_part;          // [T, h, splits]
     int num_slots;            // rows of kv_cache (0 = unknown: no check)
     int* guard;               // index self-check record (see guard_ok), may be null
+    bf16* o_final;            // keys-on-M kernel with splits == 1: final output [T, h, R] (then o_part / lse_part are not written)
+    float* lse_final;         // [T, h], may be null
 };
 
 constexpr int HB = 16;        // heads per CTA (one MMA row tile)
@@ -623,6 +625,17 @@ __global__ void __launch_bounds__(256) sparse_mla_mma_t_kernel(Params p) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const int d = warp * 64 + 16 * i + g;
+            if (p.o_final != nullptr) {                       // one split: this is the result, no combine pass
+                if (hA < nh) {
+                    bf16* o = p.o_final + ((size_t)t * p.h + h0 + hA) * R + d;
+                    o[0] = __float2bfloat16(oacc[i][nt][0] * iA); o[8] = __float2bfloat16(oacc[i][nt][2] * iA);
+                }
+                if (hB < nh) {
+                    bf16* o = p.o_final + ((size_t)t * p.h + h0 + hB) * R + d;
+                    o[0] = __float2bfloat16(oacc[i][nt][1] * iB); o[8] = __float2bfloat16(oacc[i][nt][3] * iB);
+                }
+                continue;
+            }
             if (hA < nh) {
                 float* o = p.o_part + (((size_t)t * p.h + h0 + hA) * p.splits + split) * R + d;
                 o[0] = oacc[i][nt][0] * iA; o[8] = oacc[i][nt][2] * iA;
@@ -635,7 +648,12 @@ __global__ void __launch_bounds__(256) sparse_mla_mma_t_kernel(Params p) {
     }
     if (tid < nh) {
         const float l = wl[tid] + wl[NH + tid] + wl[2 * NH + tid] + wl[3 * NH + tid];
-        p.lse_part[((size_t)t * p.h + h0 + tid) * p.splits + split] = l > 0.f ? row_m[tid] + logf(l) : -INFINITY;
+        const float lse = l > 0.f ? row_m[tid] + logf(l) : -INFINITY;
+        if (p.o_final != nullptr) {
+            if (p.lse_final != nullptr) p.lse_final[(size_t)t * p.h + h0 + tid] = lse;
+        } else {
+            p.lse_part[((size_t)t * p.h + h0 + tid) * p.splits + split] = lse;
+        }
     }
 }
 
@@ -666,7 +684,11 @@ SL_API int sl_sparse_mla_split_mma(const void* params, int T, cudaStream_t s) {
     const Params* p = static_cast<const Params*>(params);
     if (T == 0) return 0;
     if (p->R % 64 != 0 || p->R > 512 || (p->R + p->Dr) % 16 != 0 || p->Dr % 2 != 0 || p->group % 4 != 0) return -1;
-    if (g_transposed_enabled && transposed_ok(*p)) return p->h <= 8 ? launch_transposed<1>(*p, T, s) : launch_transposed<2>(*p, T, s);
+    if (g_transposed_enabled && transposed_ok(*p)) {
+        if (p->o_final != nullptr && p->splits != 1) return -1;
+        return p->h <= 8 ? launch_transposed<1>(*p, T, s) : launch_transposed<2>(*p, T, s);
+    }
+    if (p->o_final != nullptr) return -1;                     // only the keys-on-M kernel writes the final output itself
     const int DP = p->R + p->Dr + 8;
     const size_t smem = (size_t)(HB * DP + KC * DP + HB * 72) * sizeof(__half) + (size_t)(8 * HB * 2 + 3 * HB + 2 * KC) * sizeof(float);
     static bool attr = false;
@@ -682,3 +704,10 @@ SL_API int sl_sparse_mla_split_mma(const void* params, int T, cudaStream_t s) {
 
 // 0 selects the heads-on-M kernel for every shape (comparison runs); default 1.
 SL_API void sl_sparse_mla_set_transposed(int on) { g_transposed_enabled = on != 0; }
+
+// 1 when a launch with these row parameters and one split may be given `o_final` (the keys-on-M kernel takes it).
+SL_API int sl_sparse_mla_direct_ok(int R, int group, int Dr) {
+    Params p{};
+    p.R = R; p.group = group; p.Dr = Dr;
+    return (g_transposed_enabled && transposed_ok(p)) ? 1 : 0;
+}

@@ -312,6 +312,21 @@ class CudaOps:
         return o, lse
 
     def sparse_mla(self, q_abs, q_pe, layer_cache, slots, lengths):
+        c = self.cfg
+        T, h, Rr = q_abs.shape
+        if (self._mla_splits(T, h) == 1 and Rr % 64 == 0 and (Rr + c.qk_rope_head_dim) % 16 == 0
+                and N.kernels().sl_sparse_mla_direct_ok(Rr, c.kv_quant_group, c.qk_rope_head_dim)):
+            # enough query rows to fill the GPU without key splits: the attention kernel writes the result itself
+            dev = q_abs.device
+            o = torch.empty(T, h, Rr, dtype=torch.bfloat16, device=dev)
+            lse = torch.empty(T, h, dtype=torch.float32, device=dev)
+            p = N.SparseMlaParams(q_abs=q_abs.data_ptr(), q_pe=q_pe.data_ptr(), kv_cache=layer_cache.kv.data_ptr(),
+                                  slots=slots.data_ptr(), lengths=lengths.data_ptr(), h=h, R=Rr, Dr=c.qk_rope_head_dim,
+                                  group=c.kv_quant_group, topk=slots.shape[1], splits=1, sm_scale=c.softmax_scale,
+                                  o_part=0, lse_part=0, num_slots=layer_cache.kv.shape[0], guard=self._guard(dev),
+                                  o_final=o.data_ptr(), lse_final=lse.data_ptr())
+            N.call("sl_sparse_mla_split_mma", C.byref(p), T, N.stream())
+            return o, lse
         o_part, lse_part = self.sparse_mla_partials(q_abs, q_pe, layer_cache, slots, lengths)
         return self.combine([o_part], [lse_part])
 

@@ -278,11 +278,12 @@ def test_sparse_mla_and_v_expand(which):
     close(ops.v_expand(o, w_v), ref.v_expand(o, w_v), what="v_expand")
 
 
-@pytest.mark.parametrize("h,T,q_scale", [(8, 3, 0.3), (8, 40, 4.0), (16, 3, 4.0), (12, 5, 0.3)])
+@pytest.mark.parametrize("h,T,q_scale", [(8, 3, 0.3), (8, 40, 4.0), (16, 3, 4.0), (12, 5, 0.3), (8, 320, 1.0)])
 def test_sparse_mla_keys_on_m(h, T, q_scale):
     """The keys-on-M sparse MLA kernel (kv_lora_rank a multiple of 128) at the production top-k: full, ragged and
     empty key lists, one or several key splits, 8 / 12 / 16 heads per CTA; `q_scale` 4 makes later chunks exceed the
-    softmax reference of earlier ones (the rescale path).  Also against the heads-on-M kernel through the switch."""
+    softmax reference of earlier ones (the rescale path); 320 rows need no key split, so the kernel writes the final
+    output itself.  Also against the heads-on-M kernel through the switch."""
     from slopllm_b200.ops import native as N
     cfg = mini_cfg(num_attention_heads=h, index_topk=2048)
     ops, ref = cuda_ops(cfg), RefOps(cfg)
