@@ -17,7 +17,6 @@ from typing import Dict, List, Optional
 import torch
 
 from ..ops import recurrent as RC
-from ..ops import reference as R
 from ..parallel.dist import ParallelContext
 
 WEIGHT_PREFIX = "model.language_model."

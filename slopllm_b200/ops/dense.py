@@ -87,7 +87,6 @@ def paged_attention(q, k_cache, v_cache, positions, batch_idx, page_table, page_
     n_kv = k_cache.shape[1]
     if q.is_cuda:
         N = _native()
-        from .cuda_ops import CudaOps  # noqa: F401  (combine kernel lives in the same library)
         p = AttnParams(q=q.data_ptr(), k_cache=k_cache.data_ptr(), v_cache=v_cache.data_ptr(), positions=positions.data_ptr(),
                        batch_idx=batch_idx.data_ptr(), page_table=page_table.data_ptr(), pt_stride=page_table.stride(0),
                        page_size=page_size, qo_indptr=N.ptr(qo_indptr), n_heads=n_heads, n_kv=n_kv, hd=hd, sm_scale=sm_scale)

@@ -129,9 +129,10 @@ def grouped_gemm(a: torch.Tensor, b_stack: torch.Tensor, offsets: torch.Tensor, 
 
 
 def moe_large(ops, x, experts, shared, ids, wts) -> torch.Tensor:
-    """Expert MLP for many tokens: routes sorted by expert, gate/up and down as grouped GEMMs over
-    the sorted rows (experts in groups that bound the transient bf16 weight copy), SiLU·mul in
-    between, weighted un-sort at the end.  Returns fp32 [T, H] (this rank's partial sum)."""
+    """Expert MLP for many tokens: routes sorted by expert on the device, gate/up and down as grouped GEMMs over
+    the sorted rows (NVFP4 experts: weights expanded inside the GEMM; otherwise bf16 weights, expanded in groups
+    that bound the transient copy), SiLU·mul in between, weighted un-sort into the shared expert's result.
+    Returns fp32 [T, H] (this rank's partial sum)."""
     T, H = x.shape
     k = ids.shape[1]
     E, I = experts.num_experts, experts.inter

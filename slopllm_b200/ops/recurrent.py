@@ -5,7 +5,6 @@ CPU tensors run the fp32 definitions in `ops/reference.py` (the oracle of the GP
 from __future__ import annotations
 
 import ctypes as C
-from typing import Optional
 
 import torch
 
