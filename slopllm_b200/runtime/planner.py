@@ -2,13 +2,18 @@
 `sparseMlaChunksPerBlock`)."""
 from __future__ import annotations
 
+import os
+
 NUM_SMS = 148
+# waves of sparse-MLA CTAs the key split aims for (2: about 300 CTAs for the 148 SMs x 2 resident CTAs)
+MLA_WAVES = int(os.environ.get("SLOPLLM_B200_MLA_WAVES", "2"))
 
 
-def sparse_mla_splits(tokens: int, heads: int, topk: int, heads_per_cta: int = 16, chunk: int = 64, waves: int = 2,
+def sparse_mla_splits(tokens: int, heads: int, topk: int, heads_per_cta: int = 16, chunk: int = 64, waves: int = 0,
                       max_splits: int = 64) -> int:
     """Number of key splits for the sparse-MLA kernel: enough CTAs (tokens x head groups x splits) for `waves`
     waves over the SMs, never less than one 64-key chunk per split."""
+    waves = waves or MLA_WAVES
     groups = (heads + heads_per_cta - 1) // heads_per_cta
     want = max(1, (NUM_SMS * waves) // max(1, tokens * groups))
     return int(max(1, min(want, max(1, topk // chunk), max_splits)))
