@@ -10,6 +10,9 @@ ranks, a captured graph of `--iters` repetitions of
     library: the same GEMM writing locally + NCCL all-reduce + the fused add+RMSNorm kernel
 and reports microseconds per repetition next to the roofline time of the op: the slower of
 weight bytes / measured HBM bandwidth and pushed bytes / NVLink bandwidth per direction.
+Token counts above 32 (e.g. `--tokens 4096,8192` with `SLOPLLM_B200_BULK_AR=1`) compare the bulk path - reduce-scatter
+from the GEMM epilogue, owner reduce + all-gather push, wait + add + RMSNorm - with GEMM + NCCL + add + RMSNorm; its
+roofline is the slower of FLOPs / measured bf16 GEMM throughput and 2 (W-1)/W T H 2 bytes / NVLink bandwidth.
 Shapes are GLM-5 class at TP = world: K = 64 * 256 / world, N = hidden 6144, NVFP4 weights.
 """
 from __future__ import annotations
@@ -56,6 +59,7 @@ def main(argv=None) -> int:
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--hbm-gbs", type=float, default=6550.0, help="measured copy bandwidth used as the HBM roofline")
     ap.add_argument("--nvlink-gbs", type=float, default=770.0, help="measured peer copy bandwidth per direction")
+    ap.add_argument("--bf16-tflops", type=float, default=1590.0, help="measured bf16 GEMM throughput (tensor roofline of large T)")
     args = ap.parse_args(argv)
     ctx = init_from_env()
     W, dev = ctx.world, ctx.device
@@ -86,8 +90,12 @@ def main(argv=None) -> int:
         us_f = _time_graph(run_fused, args.iters)
         us_l = _time_graph(run_lib, args.iters)
         weight_bytes = H * K // 2 + H * K // 16
-        push_bytes = T * H * 4 * (W - 1)
-        roof_us = max(weight_bytes / (args.hbm_gbs * 1e3), push_bytes / (args.nvlink_gbs * 1e3))
+        if T <= 32:
+            push_bytes = T * H * 4 * (W - 1)                       # fp32 rows to every peer
+            roof_us = max(weight_bytes / (args.hbm_gbs * 1e3), push_bytes / (args.nvlink_gbs * 1e3))
+        else:
+            push_bytes = 2 * (W - 1) * (T // W) * H * 2            # bf16: partial rows to their owners, sums to every peer
+            roof_us = max(2.0 * T * H * K / (args.bf16_tflops * 1e6), push_bytes / (args.nvlink_gbs * 1e3))
         rows.append({"tokens": T, "fused_us": round(us_f, 2), "library_us": round(us_l, 2), "speedup": round(us_l / us_f, 2),
                      "roofline_us": round(roof_us, 2), "fused_fraction_of_roofline": round(roof_us / us_f, 3),
                      "weight_bytes": weight_bytes, "nvlink_bytes_out_per_rank": push_bytes})

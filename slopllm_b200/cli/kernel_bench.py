@@ -1,6 +1,6 @@
 """Kernel micro-benchmarks at the production shapes of one rank of a TP-8 GLM-5-class model.
 
-    python -m slopllm_b200.cli.kernel_bench [--cases linear,mlp,moe,gemm] [--tokens 1,8,32,4096] [--iters 20]
+    python -m slopllm_b200.cli.kernel_bench [--cases linear,mlp,moe,gemm,fp8] [--tokens 1,8,32,4096] [--iters 20]
 
 For every (kernel, token count) it prints one JSON line with the device time (CUDA events, median of `--iters`
 runs, three warm-up runs, a 256 MB write between runs so that no operand is served from L2), the algorithmic
@@ -139,6 +139,18 @@ def main(argv=None) -> int:
                     us = time_op(lambda: grouped_gemm(a, w, off, False, bn), args.iters, flush)
                     emit(roofline_row(f"{name}_bn{bn}", T, us, 2.0 * (E * n * k + nrows * (n + k)), 2.0 * nrows * n * k, peaks))
                 del w, a
+    if "fp8" in cases:
+        # FP8 block-scaled projections of a Qwen3-8B-class dense model kept in FP8 (one byte per weight streamed)
+        from ..models.weights import LinearWeight
+        from ..ops import dense as D
+        for name, n, k in (("fp8_qkv", 6144, 4096), ("fp8_o_proj", 4096, 4096), ("fp8_gate_up", 24576, 4096), ("fp8_down", 4096, 12288)):
+            q, sc = D.fp8_block_quantize(torch.randn(n, k, device=dev, generator=g) * 0.05)
+            w = LinearWeight(q, fp8_scale=sc)
+            for T in tokens:
+                x = torch.randn(T, k, device=dev, generator=g).to(torch.bfloat16)
+                us = time_op(lambda: ops.linear(x, w), args.iters, flush)
+                emit(roofline_row(name, T, us, n * k + 4 * sc.numel() + 2 * T * (n + k), 2.0 * T * n * k, peaks))
+            del w, q
     H = cfg.hidden_size
     if "mlp" in cases:
         lw = random_layer(cfg, 0, 0, dev, torch.bfloat16, 0, args.tp_shape, exact=False)

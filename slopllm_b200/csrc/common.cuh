@@ -230,6 +230,10 @@ __device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v) {
 __device__ __forceinline__ void st_relaxed_sys_u32(uint32_t* p, uint32_t v) {
     asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
+// Arrival counter in (possibly another GPU's) memory: add with release semantics at system scope, no return value.
+__device__ __forceinline__ void red_release_sys_add_u32(uint32_t* p, uint32_t v) {
+    asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 __device__ __forceinline__ uint32_t ld_relaxed_sys_u32(const uint32_t* p) {
     uint32_t v;
     asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");

@@ -160,7 +160,7 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
         }
     } else {
         const int q = warp & 3;               // TMEM lane quarter this warp may access
-        const uint32_t ptag = use_push ? push_tag(push) : 0u;
+        const uint32_t ptag = use_push == 1 ? push_tag(push) : 0u;
         int lt = 0;
         for (int tile = first; tile < total; tile += stride, ++lt) {
             const int buf = lt & 1;
@@ -183,6 +183,24 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
                                 push_store_all(push, col + i, row, __uint_as_float(r[i]), ptag);
                             } else if (out_f32) ((float*)C)[(size_t)(col + i) * ldc + row] = __uint_as_float(r[i]);
                             else ((bf16*)C)[(size_t)(col + i) * ldc + row] = __float2bfloat16(__uint_as_float(r[i]));
+                        }
+                    }
+                } else if (use_push == 2) {
+                    // reduce-scatter producer: this rank's bf16 partial row goes to the rank that owns the row
+                    // (rows [o * slot_rows, (o + 1) * slot_rows) belong to rank o), into slot `rank` of its staging
+                    // area [world][slot_rows][row_len]; the host guarantees N % 32 == 0
+                    if (row < m_end && col < N) {
+                        const int owner = row / push.slot_rows;
+                        bf16* dst = reinterpret_cast<bf16*>(push.bufs[owner]) +
+                                    ((size_t)push.rank * push.slot_rows + (row - owner * push.slot_rows)) * push.row_len + col;
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            uint4 v;
+                            v.x = f2_to_bf162(__uint_as_float(r[8 * i + 0]), __uint_as_float(r[8 * i + 1]));
+                            v.y = f2_to_bf162(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3]));
+                            v.z = f2_to_bf162(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5]));
+                            v.w = f2_to_bf162(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]));
+                            reinterpret_cast<uint4*>(dst)[i] = v;
                         }
                     }
                 } else if (row < m_end && col < N) {
@@ -234,6 +252,17 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
             tc::fence_before_sync();
             __syncwarp();
             if (lane == 0) tc::mbar_arrive(&tmem_empty[buf]);
+            if (use_push == 2) {
+                // tell the owner of this warp's 32 rows how many of their columns have landed (it expects
+                // world * row_len per 32-row group): every lane orders its own stores, one lane adds
+                const int row0 = m0 + q * 32;
+                __threadfence_system();
+                __syncwarp();
+                if (lane == 0 && row0 < m_end) {
+                    const int owner = row0 / push.slot_rows;
+                    red_release_sys_add_u32(push.flags[owner] + (row0 - owner * push.slot_rows) / 32, (uint32_t)min(BN, N - n0));
+                }
+            }
         }
     }
     tc::fence_before_sync();
@@ -258,7 +287,7 @@ template <int BN>
 int launch(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc, int out_f32,
            int transpose_out, int* err, cudaStream_t s, const PushCtx* push = nullptr, const int4* tiles = nullptr,
            const int* num_tiles = nullptr, int max_tiles = 0, int b_rows = 0, int splits = 1, long long split_stride = 0,
-           bool persistent = false) {
+           bool persistent = false, int push_mode = 1) {
     CUtensorMap tmA, tmB;
     int rc = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)M, (uint64_t)K, (uint64_t)lda * 2, BM, BK);
     if (rc) return rc;
@@ -285,7 +314,7 @@ int launch(const void* A, const void* B, void* C, int M, int N, int K, int lda, 
         kb_per_split = (total_kb + splits - 1) / splits;
         grid.z = (total_kb + kb_per_split - 1) / kb_per_split;
     }
-    sl_launch(kern, grid, 192, GemmCfg<BN>::SMEM, s, tmA, tmB, C, M, N, K, ldc, out_f32, transpose_out, err, push ? 1 : 0,
+    sl_launch(kern, grid, 192, GemmCfg<BN>::SMEM, s, tmA, tmB, C, M, N, K, ldc, out_f32, transpose_out, err, push ? push_mode : 0,
                                               push ? *push : PushCtx{}, tiles, num_tiles, kb_per_split, split_stride, tiles_n,
                                               total_tiles);
     return (int)cudaGetLastError();
@@ -304,6 +333,21 @@ SL_API int sl_gemm_bf16_tcgen05(const void* A, const void* B, void* C, int M, in
     if (bn == 64) return launch<64>(A, B, C, M, N, K, lda, ldb, ldc, out_f32, 0, (int*)err, s, nullptr, nullptr, nullptr, 0, 0, 1, 0, true);
     if (bn == 256) return launch<256>(A, B, C, M, N, K, lda, ldb, ldc, out_f32, 0, (int*)err, s, nullptr, nullptr, nullptr, 0, 0, 1, 0, true);
     return launch<128>(A, B, C, M, N, K, lda, ldb, ldc, out_f32, 0, (int*)err, s, nullptr, nullptr, nullptr, 0, 0, 1, 0, true);
+}
+
+// GEMM whose epilogue is the producer half of a reduce-scatter (prefill-sized M): tile rows are stored as bf16
+// straight into the staging area of the rank that owns them (rank o owns rows [o * slot_rows, (o + 1) * slot_rows)),
+// over NVLink for the peers, and each epilogue warp then adds the number of columns it delivered to the owner's
+// counter of that 32-row group.  `rs->bufs[o]` = rank o's staging [world][slot_rows][row_len] (bf16), `rs->flags[o]`
+// = its arrival counters [slot_rows / 32].  The consumer is sl_rs_reduce_ag (csrc/bulk_collective.cu).  Replaces
+// GEMM + `p2p_reduce_scatter_write_kernel` (`csrc/glm_p2p.cu:560`) of the reference.
+SL_API int sl_gemm_bf16_tcgen05_rs(const void* A, const void* B, int M, int N, int K, int lda, int ldb, void* err, int bn,
+                                   const PushCtx* rs, cudaStream_t s) {
+    if (M <= 0 || N <= 0 || K <= 0) return 0;
+    if (rs == nullptr || K % 8 != 0 || lda % 8 != 0 || ldb % 8 != 0) return -1;
+    if (N % 32 != 0 || N != rs->row_len || rs->slot_rows % 32 != 0 || M != rs->slot_rows * rs->world) return -1;
+    if (bn == 256) return launch<256>(A, B, nullptr, M, N, K, lda, ldb, 0, 0, 0, (int*)err, s, rs, nullptr, nullptr, 0, 0, 1, 0, true, 2);
+    return launch<128>(A, B, nullptr, M, N, K, lda, ldb, 0, 0, 0, (int*)err, s, rs, nullptr, nullptr, 0, 0, 1, 0, true, 2);
 }
 
 // Weight-streaming form for a few token rows (T <= 32): y[T, N] = x[T, K] * W[N, K]^T computed as

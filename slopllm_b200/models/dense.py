@@ -298,6 +298,9 @@ class DenseModel:
 
 # ---- weights: random init (tests, benchmarks) and HF safetensors loading ------------------------------------
 
+FP8_LINEAR_DEFAULT = False      # keep FP8 checkpoints' projections in FP8 (True) or expand them to bf16 at load
+
+
 def _lin(t: torch.Tensor) -> LinearWeight:
     return LinearWeight(t.contiguous())
 
@@ -351,9 +354,53 @@ def random_dense_model(cfg: DenseConfig, seed: int = 0, device="cpu", dtype=torc
     return assemble_dense_weights(cfg, tensors, device, dtype, rank, world), tensors
 
 
-def assemble_dense_weights(cfg: DenseConfig, tensors: Dict[str, torch.Tensor], device, dtype, rank: int = 0, world: int = 1) -> DenseWeights:
-    """Checkpoint tensors (HF names) -> fused, TP-sharded runtime weights."""
+def _fp8_rows(w: LinearWeight, lo: int, hi: int) -> LinearWeight:
+    if w.is_fp8 and (lo % 128 or (hi % 128 and hi != w.out_features)):
+        w = LinearWeight(w.dequant(torch.bfloat16))             # shard edge inside a scale block: expand
+    return w.rows(lo, hi)
+
+
+def _fp8_cols(w: LinearWeight, lo: int, hi: int) -> LinearWeight:
+    if w.is_fp8 and (lo % 128 or (hi % 128 and hi != w.in_features)):
+        w = LinearWeight(w.dequant(torch.bfloat16))
+    return w.cols(lo, hi)
+
+
+def _fp8_cat(ws) -> LinearWeight:
+    """Stack weights along the output features; stays FP8 when every part but the last ends on a scale-block edge."""
+    if all(w.is_fp8 for w in ws) and all(w.out_features % 128 == 0 for w in ws[:-1]):
+        w8 = torch.cat([w.weight.view(torch.uint8) for w in ws], 0).view(torch.float8_e4m3fn)
+        return LinearWeight(w8, fp8_scale=torch.cat([w.fp8_scale for w in ws], 0))
+    return LinearWeight(torch.cat([w.dequant(torch.bfloat16) if w.is_fp8 else w.weight for w in ws], 0))
+
+
+def assemble_dense_weights(cfg: DenseConfig, tensors: Dict[str, torch.Tensor], device, dtype, rank: int = 0, world: int = 1,
+                           keep_fp8: Optional[bool] = None) -> DenseWeights:
+    """Checkpoint tensors (HF names) -> fused, TP-sharded runtime weights.  With `keep_fp8` (default: the
+    `SLOPLLM_B200_FP8_LINEAR` switch) the FP8 block-quantised projections of attention and MLP stay in FP8 and are served by
+    the FP8 kernels (`csrc/fp8_linear.cu`; reference `csrc/glm_gemv.cu:323-500`); otherwise they are expanded to `dtype` here."""
+    from ..config import env_flag
     pfx, hd, H = cfg.weight_prefix, cfg.head_dim, cfg.hidden_size
+    keep_fp8 = env_flag("FP8_LINEAR", FP8_LINEAR_DEFAULT) if keep_fp8 is None else keep_fp8
+
+    def getw(name) -> LinearWeight:
+        t = tensors[name]
+        scale_name = name + "_scale_inv"
+        if scale_name in tensors and keep_fp8:
+            t8 = t.view(torch.float8_e4m3fn) if t.dtype == torch.uint8 else t
+            return LinearWeight(t8, fp8_scale=tensors[scale_name].to(torch.float32))
+        return LinearWeight(get(name))
+
+    def wrows(w: LinearWeight, units: Optional[int] = None, per_unit: int = 1) -> LinearWeight:
+        n = (w.out_features if units is None else units) // world
+        return _fp8_rows(w, rank * n * per_unit, (rank + 1) * n * per_unit)
+
+    def wcols(w: LinearWeight) -> LinearWeight:
+        n = w.in_features // world
+        return _fp8_cols(w, rank * n, (rank + 1) * n)
+
+    def fin(w: LinearWeight) -> LinearWeight:
+        return w.to(device, dtype)
 
     def get(name):
         t = tensors[name]
@@ -381,16 +428,16 @@ def assemble_dense_weights(cfg: DenseConfig, tensors: Dict[str, torch.Tensor], d
     layers = []
     for i, kind in enumerate(cfg.layer_types):
         lp = f"{pfx}layers.{i}."
-        w13 = torch.cat([rows(get(lp + "mlp.gate_proj.weight")), rows(get(lp + "mlp.up_proj.weight"))], 0)
+        w13 = _fp8_cat([wrows(getw(lp + "mlp.gate_proj.weight")), wrows(getw(lp + "mlp.up_proj.weight"))])
         lw = DenseLayer(kind=kind, input_norm=norm(lp + "input_layernorm.weight"), post_attn_norm=norm(lp + "post_attention_layernorm.weight"),
-                        mlp_w13=_lin(dev(w13)), mlp_w2=_lin(dev(cols(get(lp + "mlp.down_proj.weight")))))
+                        mlp_w13=fin(w13), mlp_w2=fin(wcols(getw(lp + "mlp.down_proj.weight"))))
         if kind == "full_attention":
             qs = hd * (2 if cfg.attn_output_gate else 1)
-            q = head_rows(get(lp + "self_attn.q_proj.weight"), cfg.num_attention_heads, qs)
-            k = head_rows(get(lp + "self_attn.k_proj.weight"), cfg.num_key_value_heads, hd)
-            v = head_rows(get(lp + "self_attn.v_proj.weight"), cfg.num_key_value_heads, hd)
-            lw.w_qkv = _lin(dev(torch.cat([q, k, v], 0)))
-            lw.o_proj = _lin(dev(cols(get(lp + "self_attn.o_proj.weight"))))
+            q = wrows(getw(lp + "self_attn.q_proj.weight"), cfg.num_attention_heads, qs)
+            k = wrows(getw(lp + "self_attn.k_proj.weight"), cfg.num_key_value_heads, hd)
+            v = wrows(getw(lp + "self_attn.v_proj.weight"), cfg.num_key_value_heads, hd)
+            lw.w_qkv = fin(_fp8_cat([q, k, v]))
+            lw.o_proj = fin(wcols(getw(lp + "self_attn.o_proj.weight")))
             lw.q_norm = norm(lp + "self_attn.q_norm.weight") if lp + "self_attn.q_norm.weight" in tensors else None
             lw.k_norm = norm(lp + "self_attn.k_norm.weight") if lp + "self_attn.k_norm.weight" in tensors else None
         else:

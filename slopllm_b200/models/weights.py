@@ -18,15 +18,21 @@ from ..ops import quant
 
 @dataclass
 class LinearWeight:
-    """`y = x @ W^T` weight, bf16/f32 dense or NVFP4 (packed u8 + e4m3 block scale + f32 global)."""
+    """`y = x @ W^T` weight: bf16/f32 dense, NVFP4 (packed u8 + e4m3 block scale + f32 global), or FP8 e4m3 with one
+    fp32 scale per 128 x 128 block (`fp8_scale` [ceil(N/128), ceil(K/128)], the `weight_scale_inv` of FP8 checkpoints)."""
 
     weight: torch.Tensor
     scale: Optional[torch.Tensor] = None
     scale2: Optional[torch.Tensor] = None
+    fp8_scale: Optional[torch.Tensor] = None
 
     @property
     def is_nvfp4(self) -> bool:
         return self.scale is not None
+
+    @property
+    def is_fp8(self) -> bool:
+        return self.fp8_scale is not None
 
     @property
     def out_features(self) -> int:
@@ -39,12 +45,17 @@ class LinearWeight:
     def dequant(self, dtype=torch.float32) -> torch.Tensor:
         if self.is_nvfp4:
             return quant.nvfp4_dequantize(self.weight, self.scale, self.scale2, dtype)
+        if self.is_fp8:
+            return quant.fp8_block_dequantize(self.weight, self.fp8_scale).to(dtype)
         return self.weight.to(dtype)
 
     def rows(self, lo: int, hi: int) -> "LinearWeight":
         """Column-parallel shard (split of the output features)."""
         if self.is_nvfp4:
             return LinearWeight(self.weight[lo:hi].contiguous(), self.scale[lo:hi].contiguous(), self.scale2)
+        if self.is_fp8:
+            assert lo % 128 == 0 and (hi % 128 == 0 or hi == self.weight.shape[0])
+            return LinearWeight(self.weight[lo:hi].contiguous(), fp8_scale=self.fp8_scale[lo // 128:(hi + 127) // 128].contiguous())
         return LinearWeight(self.weight[lo:hi].contiguous())
 
     def cols(self, lo: int, hi: int) -> "LinearWeight":
@@ -53,14 +64,18 @@ class LinearWeight:
             assert lo % 16 == 0 and hi % 16 == 0
             return LinearWeight(self.weight[:, lo // 2:hi // 2].contiguous(),
                                 self.scale[:, lo // 16:hi // 16].contiguous(), self.scale2)
+        if self.is_fp8:
+            assert lo % 128 == 0 and (hi % 128 == 0 or hi == self.weight.shape[1])
+            return LinearWeight(self.weight[:, lo:hi].contiguous(), fp8_scale=self.fp8_scale[:, lo // 128:(hi + 127) // 128].contiguous())
         return LinearWeight(self.weight[:, lo:hi].contiguous())
 
     def to(self, device=None, dtype=None) -> "LinearWeight":
         w = self.weight.to(device=device)
-        if not self.is_nvfp4 and dtype is not None:
+        if not self.is_nvfp4 and not self.is_fp8 and dtype is not None:
             w = w.to(dtype)
         return LinearWeight(w, None if self.scale is None else self.scale.to(device),
-                            None if self.scale2 is None else self.scale2.to(device))
+                            None if self.scale2 is None else self.scale2.to(device),
+                            None if self.fp8_scale is None else self.fp8_scale.to(device))
 
     @staticmethod
     def cat(parts: List["LinearWeight"]) -> "LinearWeight":

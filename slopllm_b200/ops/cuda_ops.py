@@ -109,6 +109,19 @@ class CudaOps:
             x = x.contiguous()
         T, K = x.shape
         Nn = w.out_features
+        if getattr(w, "is_fp8", False):
+            return self._linear_fp8(x, w, out_f32, sink)
+        if sink is not None and hasattr(sink, "rs"):
+            # prefill-sized partial sum: the GEMM's epilogue sends each tile row to the rank that owns it
+            from . import tcgen05
+            from .gemm import _weight_bf16, gemm_large
+            wb = _weight_bf16(w)
+            if (T == sink.rows and Nn == sink.rs.row_len and K % 8 == 0 and x.stride(0) % 8 == 0 and wb.stride(-1) == 1
+                    and wb.stride(0) % 8 == 0):
+                N.call("sl_gemm_bf16_tcgen05_rs", x.data_ptr(), wb.data_ptr(), T, Nn, K, x.stride(0), wb.stride(0),
+                       tcgen05.error_flag(x.device).data_ptr(), 256 if Nn >= 512 else 128, C.byref(sink.rs), N.stream())
+                return sink
+            return sink.push_tensor(gemm_large(x, w, True))
         if sink is not None:
             sink.pushed_rows = T
             if w.is_nvfp4 and K % 128 == 0 and x.stride(0) % 8 == 0:
@@ -155,6 +168,28 @@ class CudaOps:
             N.call("sl_gemv_bf16", y.data_ptr(), x.data_ptr(), w.weight.data_ptr(), T, Nn, K, x.stride(0), int(out_f32),
                    N.stream())
         return y
+
+    FP8_GEMV_MAX_T = 8         # token rows served by the FP8 weight-streaming kernel in one pass over the weights
+
+    def _linear_fp8(self, x, w, out_f32: bool, sink=None):
+        """FP8 block-scaled weight (e4m3 + one scale per 128 x 128 block).  Up to `FP8_GEMV_MAX_T` rows stream the FP8
+        bytes directly; more rows expand the matrix to bf16 once and take the tensor-core GEMM paths."""
+        from ..models.weights import LinearWeight
+        T, K = x.shape
+        Nn = w.out_features
+        w8, sc = w.weight, w.fp8_scale
+        ok = K % 16 == 0 and w8.is_contiguous() and sc.dtype == torch.float32 and sc.is_contiguous()
+        if sink is None and ok and T <= self.FP8_GEMV_MAX_T and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0:
+            y = torch.empty(T, Nn, dtype=torch.float32 if out_f32 else torch.bfloat16, device=x.device)
+            N.call("sl_linear_fp8_block", x.data_ptr(), w8.data_ptr(), sc.data_ptr(), y.data_ptr(), T, Nn, K, x.stride(0), Nn,
+                   sc.shape[1], int(out_f32), N.stream())
+            return y
+        if ok:
+            wb = torch.empty(Nn, K, dtype=torch.bfloat16, device=x.device)
+            N.call("sl_fp8_block_dequant_bf16", wb.data_ptr(), w8.data_ptr(), sc.data_ptr(), Nn, K, sc.shape[1], N.stream())
+        else:
+            wb = w.dequant(torch.bfloat16)
+        return self.linear(x, LinearWeight(wb), out_f32=out_f32, sink=sink)
 
     def merge_attention_partials(self, o, lse):
         return R.merge_attention_partials(o, lse)

@@ -122,11 +122,8 @@ def fp8_block_dequant(w8: torch.Tensor, scale_inv: torch.Tensor, block: int = 12
     """w8 [N, K] float8_e4m3fn (or its uint8 bytes), scale_inv [ceil(N/b), ceil(K/b)] -> bf16 [N, K].
     Reference: `fp8_block_dequant_*` GEMV/GEMM family (`csrc/glm_gemv.cu`), expanded once at load
     here so that the bf16 tensor-core kernels serve these checkpoints."""
-    if w8.dtype == torch.uint8:
-        w8 = w8.view(torch.float8_e4m3fn)
-    N_, K = w8.shape
-    s = scale_inv.to(torch.float32).repeat_interleave(block, 0)[:N_].repeat_interleave(block, 1)[:, :K]
-    return (w8.to(torch.float32) * s).to(torch.bfloat16)
+    from .quant import fp8_block_dequantize
+    return fp8_block_dequantize(w8, scale_inv, block).to(torch.bfloat16)
 
 
 def fp8_block_quantize(w: torch.Tensor, block: int = 128):

@@ -112,6 +112,16 @@ def fp8_dequantize_block(q: torch.Tensor, scale: torch.Tensor, block: int = 128)
 
 # ---- packed sparse-MLA cache rows -------------------------------------------------------
 
+def fp8_block_dequantize(w8: torch.Tensor, scale_inv: torch.Tensor, block: int = 128) -> torch.Tensor:
+    """FP8 weight matrix w8 [N, K] (float8_e4m3fn or its bytes) with one scale per block x block tile
+    (scale_inv [ceil(N/block), ceil(K/block)]) -> fp32 [N, K]."""
+    if w8.dtype == torch.uint8:
+        w8 = w8.view(torch.float8_e4m3fn)
+    n, k = w8.shape
+    s = scale_inv.to(torch.float32).repeat_interleave(block, 0)[:n].repeat_interleave(block, 1)[:, :k]
+    return w8.to(torch.float32) * s
+
+
 def pack_kv_rows(ckv: torch.Tensor, kpe: torch.Tensor, group: int = 128) -> torch.Tensor:
     """[T, R] latent + [T, Dr] rope key -> u8 rows `[T, R + 4*R/group + 2*Dr]`.
 

@@ -15,6 +15,11 @@ Three receive buffers rotate A, B, A, B, ..., C within one forward pass (C = the
 so a rank can never overwrite a slot that a slower peer is still reading: between two uses of
 the same buffer every rank has passed a wait that needs all peers' later flags.
 
+Prefill-sized partial sums (more than `MAX_ROWS` rows) take the bulk path when `SLOPLLM_B200_BULK_AR=1`: the tcgen05 GEMM's
+epilogue stores its bf16 tile rows into the staging area of the rank that owns them (reduce-scatter inside the GEMM,
+tile by tile), the owner sums and stores the result on every rank (all-gather), and the residual add + RMSNorm kernel
+waits for the rows it needs (`BulkSink`, `csrc/bulk_collective.cu`).  It is off by default: the default is NCCL.
+
 Plain peer loads/stores only (no multimem, no TMA multicast).  `Comm` (NCCL) stays available as
 the fallback and A/B baseline (`fused=False`).  Reference: `csrc/glm_p2p.cu`,
 `src/parallel_ops.ts:246-324, 2912-2975`.
@@ -54,7 +59,17 @@ class GatherPushCtx(C.Structure):
                 ("world", i32), ("slot_bytes", C.c_size_t)]
 
 
+class BulkCtx(C.Structure):
+    _fields_ = [("stage", vp * MAX_RANKS), ("rs_count", vp * MAX_RANKS), ("full", vp * MAX_RANKS), ("ag_count", vp * MAX_RANKS),
+                ("rs_done", vp), ("ag_done", vp), ("status", vp), ("rank", i32), ("world", i32), ("slot_rows", i32),
+                ("row_len", i32), ("max_spins", u32)]
+
+
 N._SIGS.update({
+    "sl_gemm_bf16_tcgen05_rs": [vp, vp, i32, i32, i32, i32, i32, vp, i32, C.POINTER(PushCtx), vp],
+    "sl_rs_push_rows": [C.POINTER(BulkCtx), vp, i32, i32, vp],
+    "sl_rs_reduce_ag": [C.POINTER(BulkCtx), vp],
+    "sl_bulk_add_rmsnorm": [C.POINTER(BulkCtx), vp, vp, vp, vp, C.c_float, vp],
     "sl_ar_add_rmsnorm": [C.POINTER(RecvCtx), vp, vp, vp, vp, i32, i32, C.c_float, vp, vp],
     "sl_push_rows": [C.POINTER(PushCtx), vp, i32, i32, vp],
     "sl_flag_barrier": [C.POINTER(vp), vp, i32, i32, u32, u32, vp, vp],
@@ -89,6 +104,37 @@ class PushSink:
         return self
 
 
+class BulkSink:
+    """Destination of one prefill-sized partial sum [T, H]: row t goes to the staging area of rank t // (T / world).
+    `rs` is the view of it that the GEMM epilogue takes, `ctx` the one of the collective kernels."""
+
+    def __init__(self, owner: "SymmetricRegion", lane: int, rows: int):
+        self.owner, self.lane, self.rows = owner, lane, rows
+        W, H, R = owner.world, owner.row_len, rows // owner.world
+        off = owner.lay["bulk"][lane]
+        st = owner.bulk_state.data_ptr() + 4 * lane * owner.bulk_words
+        self.ctx = BulkCtx(rs_done=st, ag_done=st + 4 * (owner.bulk_rows // 32), status=owner.status_ptr, rank=owner.rank,
+                           world=W, slot_rows=R, row_len=H, max_spins=owner.wait_spins)
+        self.rs = PushCtx(epoch=0, block_counter=0, rank=owner.rank, world=W, slot_rows=R, row_len=H)
+        for r in range(W):
+            base = owner.peer_ptrs[r]
+            self.ctx.stage[r] = self.rs.bufs[r] = base + off["stage"]
+            self.ctx.rs_count[r] = self.rs.flags[r] = base + off["rs_count"]
+            self.ctx.full[r] = base + off["full"]
+            self.ctx.ag_count[r] = base + off["ag_count"]
+        self.pushed_rows = rows
+
+    def push_tensor(self, x: torch.Tensor) -> "BulkSink":
+        """Producers without a fused epilogue: send an existing fp32 / bf16 [T, H] tensor to the owners of its rows."""
+        if x.dtype not in (torch.float32, torch.bfloat16):
+            x = x.to(torch.float32)
+        if x.stride(-1) != 1 or x.stride(0) % 8 != 0:
+            x = x.contiguous()
+        assert x.shape[0] == self.rows and x.shape[1] == self.owner.row_len
+        N.call("sl_rs_push_rows", C.byref(self.ctx), x.data_ptr(), x.stride(0), int(x.dtype == torch.float32), N.stream())
+        return self
+
+
 class SymmetricRegion:
     """Symmetric receive buffers + flags, and this rank's local epoch / counter words.
 
@@ -98,9 +144,10 @@ class SymmetricRegion:
     """
 
     NUM_BUFS = 3
+    BULK_LANES = 3
 
     def __init__(self, rank: int, world: int, slot_rows: int, row_len: int, local: torch.Tensor, peer_ptrs: List[int],
-                 gather_bytes: int = 0, cp_shape=None, wait_spins: int = 4_000_000):
+                 gather_bytes: int = 0, cp_shape=None, wait_spins: int = 4_000_000, bulk_rows: int = 0):
         assert world <= MAX_RANKS
         self.rank, self.world, self.slot_rows, self.row_len = rank, world, slot_rows, row_len
         self.local = local
@@ -108,8 +155,12 @@ class SymmetricRegion:
         dev = local.device
         self.state = torch.zeros(64, dtype=torch.int32, device=dev)      # epochs, counters, status
         self.wait_spins = wait_spins
-        lay = self.layout(world, slot_rows, row_len, gather_bytes, cp_shape)
+        lay = self.layout(world, slot_rows, row_len, gather_bytes, cp_shape, bulk_rows)
         self.lay = lay
+        # bulk all-reduce lanes: local "blocks past their wait" words, [lane][bulk_rows / 32 group words + 8 source words]
+        self.bulk_rows = bulk_rows
+        self.bulk_words = bulk_rows // 32 + MAX_RANKS
+        self.bulk_state = torch.zeros(max(1, self.BULK_LANES * self.bulk_words), dtype=torch.int32, device=dev)
         st = self.state.data_ptr()
         self.status_ptr = st + 4 * 48
         self.push_ctx, self.recv_ctx = [], []
@@ -146,7 +197,7 @@ class SymmetricRegion:
         self.gather_bytes = gather_bytes
 
     @classmethod
-    def layout(cls, world, slot_rows, row_len, gather_bytes=0, cp_shape=None) -> dict:
+    def layout(cls, world, slot_rows, row_len, gather_bytes=0, cp_shape=None, bulk_rows=0) -> dict:
         off = 0
 
         def take(n):
@@ -163,6 +214,11 @@ class SymmetricRegion:
             hl = h // world
             lay["cp_o"] = take(2 * world * Tmax * hl * R * 4)                          # two halves (epoch parity)
             lay["cp_lse"] = take(2 * world * Tmax * hl * 4)
+        lay["bulk"] = []
+        if bulk_rows:
+            for _ in range(cls.BULK_LANES):                                            # one lane per stream that runs prefill chunks
+                lay["bulk"].append({"stage": take(bulk_rows * row_len * 2), "full": take(bulk_rows * row_len * 2),
+                                    "rs_count": take(4 * (bulk_rows // 32)), "ag_count": take(4 * MAX_RANKS)})
         lay["total"] = off
         return lay
 
@@ -179,13 +235,20 @@ class SymmetricRegion:
 class NvlinkComm(Comm):
     """Communicator whose hot collectives run inside our kernels over peer memory."""
 
-    MAX_ROWS = 32          # token rows served by the fused decode path; larger steps use NCCL
+    MAX_ROWS = 32          # token rows served by the fused decode path; larger steps use the bulk path or NCCL
+    BULK_ROWS = 8192       # largest prefill chunk the bulk path takes (two bf16 [BULK_ROWS, H] areas per lane and rank)
 
     def __init__(self, ctx: ParallelContext, cfg=None, region: Optional[SymmetricRegion] = None):
         super().__init__(ctx)
         self.cfg = cfg
         self._toggle = 0
         self.region = region or self._make_region(ctx, cfg)
+        self._lanes = {}       # stream -> bulk lane, in order of first use (the same order on every rank)
+
+    @staticmethod
+    def bulk_rows_from_env() -> int:
+        from ..config import env_flag, env_int
+        return env_int("BULK_AR_ROWS", NvlinkComm.BULK_ROWS) if env_flag("BULK_AR") else 0
 
     @staticmethod
     def _make_region(ctx: ParallelContext, cfg) -> SymmetricRegion:
@@ -196,7 +259,8 @@ class NvlinkComm(Comm):
         H = cfg.hidden_size
         cp_shape = (NvlinkComm.MAX_ROWS, cfg.num_attention_heads, cfg.kv_lora_rank) if ctx.cp else None
         gather_bytes = 1 << 20
-        lay = SymmetricRegion.layout(ctx.world, NvlinkComm.MAX_ROWS, H, gather_bytes, cp_shape)
+        bulk_rows = NvlinkComm.bulk_rows_from_env()
+        lay = SymmetricRegion.layout(ctx.world, NvlinkComm.MAX_ROWS, H, gather_bytes, cp_shape, bulk_rows)
         if env_str("SYMM") == "torch":
             import torch.distributed._symmetric_memory as symm
             buf = symm.empty(lay["total"], dtype=torch.uint8, device=ctx.device)
@@ -228,7 +292,8 @@ class NvlinkComm(Comm):
             keep = everyone
         torch.cuda.synchronize()
         dist.barrier()
-        region = SymmetricRegion(ctx.rank, ctx.world, NvlinkComm.MAX_ROWS, H, buf, ptrs, gather_bytes, cp_shape)
+        region = SymmetricRegion(ctx.rank, ctx.world, NvlinkComm.MAX_ROWS, H, buf, ptrs, gather_bytes, cp_shape,
+                                 bulk_rows=bulk_rows)
         region._keep = keep
         return region
 
@@ -236,17 +301,51 @@ class NvlinkComm(Comm):
     def begin_forward(self) -> None:
         self._toggle = 0
 
-    def partial_sink(self, rows: int, final: bool = False) -> Optional[PushSink]:
-        if rows > self.MAX_ROWS:
+    def _bulk_sink(self, rows: int) -> Optional[BulkSink]:
+        """Bulk lane of the current stream, if this row count can take the bulk path: every rank owns the same number
+        of rows, a multiple of 32.  Each stream that runs prefill chunks (the default stream, the two streams of phased
+        prefill) gets its own staging areas, because the protocol relies on stream order between consecutive uses."""
+        rg = self.region
+        if not rg.bulk_rows or rows > rg.bulk_rows or rows % (32 * rg.world) != 0 or rg.row_len % 32 != 0:
             return None
+        key = torch.cuda.current_stream(self.ctx.device).cuda_stream if self.ctx.device.type == "cuda" else 0
+        lane = self._lanes.get(key)
+        if lane is None:
+            if len(self._lanes) >= rg.BULK_LANES:
+                return None
+            lane = self._lanes[key] = len(self._lanes)
+        return BulkSink(rg, lane, rows)
+
+    def partial_sink(self, rows: int, final: bool = False):
+        if rows > self.MAX_ROWS:
+            return self._bulk_sink(rows)
         if final:
             return PushSink(self.region, 2)
         s = PushSink(self.region, self._toggle)
         self._toggle ^= 1
         return s
 
+    # -- bulk all-reduce: owner step and consumer (separate so that a test can run W emulated ranks phase by phase) ----
+    def bulk_reduce(self, sink: BulkSink) -> None:
+        """Owner step: sum this rank's rows over all ranks' staged partials and store the sums on every rank."""
+        N.call("sl_rs_reduce_ag", C.byref(sink.ctx), N.stream())
+
+    def bulk_finish(self, sink: BulkSink, residual, weight, eps):
+        """Consumer: wait for every owner's rows, then residual add + RMSNorm.  Returns (normed bf16, residual' fp32)."""
+        T, H = sink.rows, self.region.row_len
+        out = torch.empty(T, H, dtype=torch.bfloat16, device=self.ctx.device)
+        res = torch.empty(T, H, dtype=torch.float32, device=self.ctx.device)
+        if residual is not None and (residual.dtype != torch.float32 or not residual.is_contiguous()):
+            residual = residual.to(torch.float32).contiguous()
+        N.call("sl_bulk_add_rmsnorm", C.byref(sink.ctx), out.data_ptr(), res.data_ptr(), N.ptr(residual), weight.data_ptr(),
+               float(eps), N.stream())
+        return out, res
+
     # -- fused all-reduce consumer ----------------------------------------------------------------
     def allreduce_add_rmsnorm(self, ops, partial, residual, weight, eps, want_perm: bool = False):
+        if isinstance(partial, BulkSink):
+            self.bulk_reduce(partial)
+            return self.bulk_finish(partial, residual, weight, eps)
         if not isinstance(partial, PushSink):
             return super().allreduce_add_rmsnorm(ops, partial, residual, weight, eps, want_perm)
         T, H = partial.pushed_rows, self.region.row_len

@@ -170,11 +170,13 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _mgpu_worker(rank, world, port, q, cp=False):
+def _mgpu_worker(rank, world, port, q, cp=False, bulk=False):
     import dataclasses
     import traceback
     os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
                       MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    if bulk:        # prefill chunks of 64 rows (32 per rank) take the reduce-scatter / all-gather kernels
+        os.environ["SLOPLLM_B200_BULK_AR"] = "1"
     try:
         import torch.distributed as dist
         from slopllm_b200.models.glm_moe_dsa import GlmMoeDsaModel
@@ -216,16 +218,17 @@ def _mgpu_worker(rank, world, port, q, cp=False):
 
 
 @pytest.mark.multigpu
-@pytest.mark.parametrize("cp", [False, True])
-def test_tp2_fused_equals_nccl_on_two_gpus(cp):
+@pytest.mark.parametrize("cp,bulk", [(False, False), (True, False), (False, True)])
+def test_tp2_fused_equals_nccl_on_two_gpus(cp, bulk):
     """Prefill + graph-captured decode on two GPUs, in-kernel NVLink collectives against NCCL; with `cp` the KV is
-    sharded by token and the indexer top-k / attention partials are merged across the ranks."""
+    sharded by token and the indexer top-k / attention partials are merged across the ranks; with `bulk` the prefill
+    chunks' all-reduces run as reduce-scatter from the GEMM epilogue + all-gather over peer memory."""
     import torch.multiprocessing as mp
     world = 2
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_mgpu_worker, args=(r, world, port, q, cp), daemon=True) for r in range(world)]
+    procs = [ctx.Process(target=_mgpu_worker, args=(r, world, port, q, cp, bulk), daemon=True) for r in range(world)]
     for p in procs:
         p.start()
     res = {}

@@ -144,3 +144,83 @@ def test_dense_engine_gpu_matches_oracle(hybrid):
     prompt = torch.randint(2, cfg.vocab_size, (150,), generator=torch.Generator().manual_seed(7)).tolist()
     errs = teacher_forced_errors(cfg, w_gpu, tensors, "cuda", prompt, 4, chunk=64)
     assert max(errs) < 6e-2, errs
+
+
+def _fp8_checkpoint(cfg, seed=3):
+    """Random checkpoint whose attention / MLP projections are FP8 block-quantised (`weight` + `weight_scale_inv`),
+    and the same checkpoint with those projections expanded back to fp32 (what the oracle sees)."""
+    from slopllm_b200.ops import dense as D
+    _, tensors = random_dense_model(cfg, seed=seed, device="cpu", dtype=torch.float32)
+    q8, plain = {}, {}
+    for name, t in tensors.items():
+        if name.endswith("_proj.weight") and "layers." in name and "linear_attn" not in name:
+            q, s = D.fp8_block_quantize(t.to(torch.float32) * 8.0)          # spread the values over the e4m3 range
+            q8[name], q8[name + "_scale_inv"] = q, s / 8.0
+            plain[name] = D.fp8_block_dequant(q, s / 8.0).to(torch.float32)
+        else:
+            q8[name] = plain[name] = t
+    return q8, plain
+
+
+@pytest.mark.parametrize("world", [1, 2])
+def test_fp8_weights_kept_match_expanded(world):
+    """Keeping the FP8 projections in FP8 (sharded on scale-block edges, expanded where a shard edge cuts a block)
+    gives the same weights as expanding them at load."""
+    from slopllm_b200.models.dense import assemble_dense_weights
+    cfg = DenseConfig.tiny()
+    q8, _ = _fp8_checkpoint(cfg)
+    kept_fp8 = 0
+    for rank in range(world):
+        a = assemble_dense_weights(cfg, q8, "cpu", torch.float32, rank, world, keep_fp8=True)
+        b = assemble_dense_weights(cfg, q8, "cpu", torch.float32, rank, world, keep_fp8=False)
+        for la, lb in zip(a.layers, b.layers):
+            for f in ("w_qkv", "o_proj", "mlp_w13", "mlp_w2"):
+                wa, wb = getattr(la, f), getattr(lb, f)
+                assert not wb.is_fp8
+                kept_fp8 += int(wa.is_fp8)
+                # the expanded path rounds to bf16 once
+                assert torch.equal(wa.dequant(torch.float32).to(torch.bfloat16), wb.weight.to(torch.bfloat16)), (rank, f)
+    assert kept_fp8 > 0
+
+
+def test_fp8_kept_engine_matches_oracle_cpu():
+    from slopllm_b200.models.dense import assemble_dense_weights
+    cfg = DenseConfig.tiny()
+    q8, plain = _fp8_checkpoint(cfg)
+    w = assemble_dense_weights(cfg, q8, "cpu", torch.float32, keep_fp8=True)
+    assert w.layers[0].w_qkv.is_fp8 and w.layers[0].mlp_w2.is_fp8
+    prompt = torch.randint(2, cfg.vocab_size, (40,), generator=torch.Generator().manual_seed(5)).tolist()
+    errs = teacher_forced_errors(cfg, w, plain, "cpu", prompt, 2, chunk=32)
+    assert max(errs) < 2e-2, errs
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("T", [1, 2, 3, 8, 20, 100])
+@pytest.mark.parametrize("out_f32", [False, True])
+def test_fp8_linear_kernels(T, out_f32):
+    """FP8 weight streaming (up to 8 rows) and the expand + GEMM path (more rows) against the fp32 definition."""
+    from slopllm_b200.models.weights import LinearWeight
+    from slopllm_b200.ops import dense as D
+    from slopllm_b200.ops.cuda_ops import CudaOps
+    g = torch.Generator().manual_seed(T)
+    N_, K = 1300, 1408                   # neither a multiple of 128 x 8 nor of 512: ragged last scale blocks and K tail
+    q, s = D.fp8_block_quantize(torch.randn(N_, K, generator=g))
+    w = LinearWeight(q.cuda(), fp8_scale=s.cuda())
+    x = torch.randn(T, K, generator=g).to(torch.bfloat16).cuda()
+    ops = CudaOps(DenseConfig.tiny())
+    y = ops.linear(x, w, out_f32=out_f32)
+    assert y.dtype == (torch.float32 if out_f32 else torch.bfloat16) and y.shape == (T, N_)
+    want = R.linear(x.cpu(), LinearWeight(q, fp8_scale=s))
+    assert ((y.float().cpu() - want).abs().max() / want.abs().max()).item() < 1e-2
+
+
+@pytest.mark.gpu
+def test_fp8_kept_engine_gpu_matches_oracle():
+    from slopllm_b200.models.dense import assemble_dense_weights
+    cfg = DenseConfig.tiny()
+    q8, plain = _fp8_checkpoint(cfg)
+    w = assemble_dense_weights(cfg, q8, "cuda", torch.bfloat16, keep_fp8=True)
+    assert w.layers[0].w_qkv.is_fp8
+    prompt = torch.randint(2, cfg.vocab_size, (150,), generator=torch.Generator().manual_seed(7)).tolist()
+    errs = teacher_forced_errors(cfg, w, plain, "cuda", prompt, 4, chunk=64)
+    assert max(errs) < 6e-2, errs
