@@ -202,6 +202,8 @@ _SIGS = {
     "sl_grouped_gemm_bf16_tcgen05": [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, vp, vp, i32, vp, i32, vp],
     "sl_build_group_tiles": [vp, vp, vp, i32, i32, i32, i32, vp],
     "sl_nvfp4_dequant_bf16": [vp, vp, vp, vp, i32, i32, i32, i32, i32, vp],
+    "sl_linear_fp8_block": [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp],
+    "sl_fp8_block_dequant_bf16": [vp, vp, vp, i32, i32, i32, vp],
     "sl_moe_unsort_reduce": [vp, vp, vp, vp, i32, i32, i32, i32, i32, vp],
     "sl_gemm_bf16_tcgen05": [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp, i32, vp],
 }

@@ -91,3 +91,39 @@ def test_meta_ops_runs_the_model_without_memory():
     s = ops.summary()
     assert s["calls"]["linear"] >= 3 * cfg.num_hidden_layers and s["total_flops"] > 0 and s["total_weight_bytes"] > 0
     assert s["calls"]["moe"] == cfg.num_hidden_layers - cfg.first_k_dense_replace
+
+
+def test_every_called_kernel_entry_point_is_declared_and_exported():
+    """Each `N.call("sl_...")` in the package names an entry point with a registered ctypes signature whose arity
+    matches the C prototype's parameter count, and the built kernel library exports it."""
+    import os
+    import re
+
+    import slopllm_b200
+    import slopllm_b200.checkpoint.csf_gpu  # noqa: F401  (registers its signature on import or first use)
+    import slopllm_b200.ops.cuda_ops  # noqa: F401
+    import slopllm_b200.parallel.nvlink  # noqa: F401
+    from slopllm_b200.ops import native as N
+    root = os.path.dirname(slopllm_b200.__file__)
+    called = set()
+    for d, _, files in os.walk(root):
+        for f in files:
+            if f.endswith(".py"):
+                called |= set(re.findall(r'\.call\(\s*"(sl_\w+)"', open(os.path.join(d, f)).read()))
+    assert len(called) > 40
+    lazy = {"sl_csf_decode"}                                   # registered by csf_gpu on first use
+    assert not [n for n in sorted(called - lazy) if n not in N._SIGS]
+    # prototypes in the CUDA sources: SL_API int name(args...)
+    protos = {}
+    for f in os.listdir(os.path.join(root, "csrc")):
+        if f.endswith(".cu"):
+            src = open(os.path.join(root, "csrc", f)).read()
+            for m in re.finditer(r"SL_API\s+\w[\w\s\*]*?\b(sl_\w+)\s*\(([^)]*)\)", src):
+                args = [a for a in m.group(2).split(",") if a.strip() and a.strip() != "void"]
+                protos[m.group(1)] = len(args)
+    for n in sorted(called - lazy):
+        assert n in protos, n
+        assert len(N._SIGS[n]) == protos[n], (n, len(N._SIGS[n]), protos[n])
+    if os.path.exists(N.KERNELS_SO):
+        lib = N.kernels()
+        assert not [n for n in sorted(called) if not hasattr(lib, n)]
