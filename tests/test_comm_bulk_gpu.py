@@ -35,13 +35,13 @@ def _comms(W, H, bulk_rows):
     return cfg, [NvlinkComm(ParallelContext(r, W, torch.device(DEV)), cfg, region=regions[r]) for r in range(W)]
 
 
-@pytest.mark.parametrize("W,T", [(2, 256), (4, 512), (8, 256)])
+@pytest.mark.parametrize("W,T", [(2, 256), (4, 512), (8, 256), (2, 1024)])   # the last: more rows than resident waiting blocks
 def test_bulk_allreduce_emulated_ranks(W, T):
     from slopllm_b200.ops import tcgen05
     from slopllm_b200.ops.cuda_ops import CudaOps
     from slopllm_b200.parallel.nvlink import BulkSink
     H, K = 1024, 512
-    cfg, comms = _comms(W, H, 512)
+    cfg, comms = _comms(W, H, max(512, T))
     ops = CudaOps(cfg)
     g = torch.Generator(device=DEV).manual_seed(W * 1000 + T)
     norm_w = torch.rand(H, device=DEV, generator=g).to(torch.bfloat16)
