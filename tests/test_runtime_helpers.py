@@ -127,3 +127,47 @@ def test_every_called_kernel_entry_point_is_declared_and_exported():
     if os.path.exists(N.KERNELS_SO):
         lib = N.kernels()
         assert not [n for n in sorted(called) if not hasattr(lib, n)]
+
+
+def test_bulk_allreduce_host_logic(monkeypatch):
+    """Host side of the prefill-sized all-reduce on CPU buffers with the kernel calls recorded instead of launched:
+    which row counts take the path, lane per stream, pointer tables of the GEMM view and of the collective view, and the
+    launch sequence of producer / owner step / consumer."""
+    import torch
+
+    from slopllm_b200.config import GlmMoeDsaConfig
+    from slopllm_b200.ops import native as N
+    from slopllm_b200.parallel import nvlink as NV
+    from slopllm_b200.parallel.dist import ParallelContext
+    calls = []
+    monkeypatch.setattr(N, "call", lambda name, *a: calls.append((name, a)))
+    monkeypatch.setattr(N, "stream", lambda: 0)
+    W, H, rows = 4, 1024, 512
+    lay = NV.SymmetricRegion.layout(W, 32, H, 0, None, rows)
+    assert len(lay["bulk"]) == NV.SymmetricRegion.BULK_LANES
+    # areas of one lane and of different lanes do not overlap and are 256-byte aligned
+    spans = sorted((off, off + size) for lane in lay["bulk"] for off, size in
+                   ((lane["stage"], rows * H * 2), (lane["full"], rows * H * 2), (lane["rs_count"], 4 * rows // 32),
+                    (lane["ag_count"], 4 * 8)))
+    assert all(a % 256 == 0 for a, _ in spans) and all(spans[i][1] <= spans[i + 1][0] for i in range(len(spans) - 1))
+    assert spans[-1][1] <= lay["total"]
+    bufs = [torch.zeros(lay["total"], dtype=torch.uint8) for _ in range(W)]
+    ptrs = [b.data_ptr() for b in bufs]
+    regions = [NV.SymmetricRegion(r, W, 32, H, bufs[r], ptrs, bulk_rows=rows) for r in range(W)]
+    comm = NV.NvlinkComm(ParallelContext(2, W, torch.device("cpu")), GlmMoeDsaConfig.tiny(), region=regions[2])
+    assert comm.partial_sink(16).__class__.__name__ == "PushSink"            # decode-sized: tagged-word path
+    assert comm.partial_sink(100) is None and comm.partial_sink(rows * 2) is None and comm.partial_sink(64) is None
+    sink = comm.partial_sink(256)
+    assert isinstance(sink, NV.BulkSink) and sink.lane == 0
+    assert (sink.ctx.rank, sink.ctx.world, sink.ctx.slot_rows, sink.ctx.row_len) == (2, W, 64, H)
+    assert (sink.rs.rank, sink.rs.world, sink.rs.slot_rows, sink.rs.row_len) == (2, W, 64, H)
+    for r in range(W):
+        assert sink.ctx.stage[r] == sink.rs.bufs[r] == ptrs[r] + lay["bulk"][0]["stage"]
+        assert sink.ctx.rs_count[r] == sink.rs.flags[r] == ptrs[r] + lay["bulk"][0]["rs_count"]
+        assert sink.ctx.full[r] == ptrs[r] + lay["bulk"][0]["full"] and sink.ctx.ag_count[r] == ptrs[r] + lay["bulk"][0]["ag_count"]
+    sink.push_tensor(torch.zeros(256, H))
+    comm.allreduce_add_rmsnorm(None, sink, None, torch.ones(H, dtype=torch.bfloat16), 1e-5)
+    assert [c[0] for c in calls] == ["sl_rs_push_rows", "sl_rs_reduce_ag", "sl_bulk_add_rmsnorm"]
+    # without the switch no lanes are laid out and every prefill-sized sum keeps the library path
+    plain = NV.SymmetricRegion(0, W, 32, H, torch.zeros(NV.SymmetricRegion.layout(W, 32, H)["total"], dtype=torch.uint8), ptrs)
+    assert NV.NvlinkComm(ParallelContext(0, W, torch.device("cpu")), GlmMoeDsaConfig.tiny(), region=plain).partial_sink(256) is None
