@@ -145,6 +145,8 @@ class SymmetricRegion:
 
     NUM_BUFS = 3
     BULK_LANES = 3
+    GUARD_BYTES = 256
+    GUARD_PATTERN = 0xA5
 
     def __init__(self, rank: int, world: int, slot_rows: int, row_len: int, local: torch.Tensor, peer_ptrs: List[int],
                  gather_bytes: int = 0, cp_shape=None, wait_spins: int = 4_000_000, bulk_rows: int = 0):
@@ -157,6 +159,7 @@ class SymmetricRegion:
         self.wait_spins = wait_spins
         lay = self.layout(world, slot_rows, row_len, gather_bytes, cp_shape, bulk_rows)
         self.lay = lay
+        self.write_canaries()
         # bulk all-reduce lanes: local "blocks past their wait" words, [lane][bulk_rows / 32 group words + 8 source words]
         self.bulk_rows = bulk_rows
         self.bulk_words = bulk_rows // 32 + MAX_RANKS
@@ -199,13 +202,17 @@ class SymmetricRegion:
     @classmethod
     def layout(cls, world, slot_rows, row_len, gather_bytes=0, cp_shape=None, bulk_rows=0) -> dict:
         off = 0
+        guards = []
 
         def take(n):
+            # every area is followed by a guard zone that no kernel may write (see check_canaries)
             nonlocal off
             o = off
             off += (n + 255) // 256 * 256
+            guards.append(off)
+            off += cls.GUARD_BYTES
             return o
-        lay = {"flags": [take(4 * MAX_RANKS * 2) for _ in range(8)], "data": []}
+        lay = {"flags": [take(4 * MAX_RANKS * 2) for _ in range(8)], "data": [], "guards": guards}
         for _ in range(cls.NUM_BUFS):
             lay["data"].append(take(world * slot_rows * row_len * 8))      # {fp32 value, tag} per element
         lay["gather"] = take(2 * world * gather_bytes) if gather_bytes else 0          # two halves (epoch parity)
@@ -224,6 +231,20 @@ class SymmetricRegion:
 
     def local_view(self, offset: int, nbytes: int) -> torch.Tensor:
         return self.local[offset:offset + nbytes]
+
+    def write_canaries(self) -> None:
+        for g in self.lay["guards"]:
+            self.local[g:g + self.GUARD_BYTES] = self.GUARD_PATTERN
+
+    def check_canaries(self) -> None:
+        """Raise if a guard zone behind one of this rank's areas was written: some kernel (here or on a peer) stored
+        past the end of a receive slot, a staging area or a counter array.  Tests call it after every collective test;
+        `SLOPLLM_B200_CHECKS=1` makes `check_status` call it after every step (it synchronises)."""
+        for i, g in enumerate(self.lay["guards"]):
+            zone = self.local[g:g + self.GUARD_BYTES]
+            if not bool((zone == self.GUARD_PATTERN).all()):
+                bad = int((zone != self.GUARD_PATTERN).nonzero()[0])
+                raise RuntimeError(f"rank {self.rank}: guard zone {i} of the symmetric region (offset {g}) was overwritten at byte {bad}")
 
     def check_status(self) -> None:
         st = self.state[48:52].tolist()
@@ -244,6 +265,8 @@ class NvlinkComm(Comm):
         self._toggle = 0
         self.region = region or self._make_region(ctx, cfg)
         self._lanes = {}       # stream -> bulk lane, in order of first use (the same order on every rank)
+        from ..config import env_flag
+        self._checks = env_flag("CHECKS")
 
     @staticmethod
     def bulk_rows_from_env() -> int:
@@ -407,3 +430,5 @@ class NvlinkComm(Comm):
 
     def check_status(self) -> None:
         self.region.check_status()
+        if self._checks:
+            self.region.check_canaries()

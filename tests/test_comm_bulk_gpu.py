@@ -72,7 +72,8 @@ def test_bulk_allreduce_emulated_ranks(W, T):
             comms[r].check_status()
     torch.cuda.synchronize()
     tcgen05.check_errors(DEV)
-    for c in comms:      # every arrival counter is back at zero
+    for c in comms:      # nothing was stored past the end of an area; every arrival counter is back at zero
+        c.region.check_canaries()
         assert int(c.region.bulk_state.abs().sum()) == 0
         lane = c.region.lay["bulk"][0]
         assert int(c.region.local_view(lane["rs_count"], 4 * 16).view(torch.int32).abs().sum()) == 0

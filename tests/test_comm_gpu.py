@@ -61,6 +61,8 @@ def test_fused_allreduce_emulated_ranks(W, T):
     from slopllm_b200.ops import tcgen05
     torch.cuda.synchronize()
     tcgen05.check_errors(DEV)
+    for rg in regions:                 # no producer stored past the end of a receive slot
+        rg.check_canaries()
 
 
 def test_moe_down_push_emulated():

@@ -171,3 +171,24 @@ def test_bulk_allreduce_host_logic(monkeypatch):
     # without the switch no lanes are laid out and every prefill-sized sum keeps the library path
     plain = NV.SymmetricRegion(0, W, 32, H, torch.zeros(NV.SymmetricRegion.layout(W, 32, H)["total"], dtype=torch.uint8), ptrs)
     assert NV.NvlinkComm(ParallelContext(0, W, torch.device("cpu")), GlmMoeDsaConfig.tiny(), region=plain).partial_sink(256) is None
+
+
+def test_symmetric_region_guard_zones_detect_overruns():
+    import pytest
+    import torch
+
+    from slopllm_b200.parallel.nvlink import SymmetricRegion
+    W, H = 2, 256
+    lay = SymmetricRegion.layout(W, 32, H, 1024, (32, 8, 64), 64)
+    assert len(lay["guards"]) >= 8 + 3 + 1 + 2 + 4 * SymmetricRegion.BULK_LANES
+    buf = torch.zeros(lay["total"], dtype=torch.uint8)
+    rg = SymmetricRegion(0, W, 32, H, buf, [buf.data_ptr()] * W, gather_bytes=1024, cp_shape=(32, 8, 64), bulk_rows=64)
+    rg.check_canaries()
+    # every area ends where its guard zone begins: a store one byte past the last receive slot lands in a guard
+    end_of_data2 = lay["data"][2] + W * 32 * H * 8
+    assert end_of_data2 in lay["guards"]
+    buf[end_of_data2] = 1
+    with pytest.raises(RuntimeError, match="guard zone"):
+        rg.check_canaries()
+    rg.write_canaries()
+    rg.check_canaries()
