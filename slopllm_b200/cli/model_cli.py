@@ -16,7 +16,7 @@ from typing import List, Optional
 
 import torch
 
-from ..config import EngineConfig, GlmMoeDsaConfig, SamplingParams
+from ..config import EngineConfig, GlmMoeDsaConfig, SamplingParams, env_flag
 from ..parallel.dist import ParallelContext, init_from_env
 
 
@@ -35,9 +35,10 @@ def add_model_args(ap: argparse.ArgumentParser) -> None:
     ap.add_argument("--max-host-pages", type=int, default=0, help="pinned-host prefix tier size in pages (0: off)")
     ap.add_argument("--max-model-len", type=int, default=65536)
     ap.add_argument("--no-cuda-graph", action="store_true")
-    ap.add_argument("--phased-prefill", dest="phased_prefill", action="store_true", default=False,
+    ap.add_argument("--phased-prefill", dest="phased_prefill", action="store_true", default=env_flag("PHASED_PREFILL"),
                     help="run large prefill chunks as two halves on two streams (multi-rank jobs); off by default: over "
-                         "NVLink the all-reduce is short and two half-size GEMM streams measured slower than one")
+                         "NVLink the all-reduce is short and two half-size GEMM streams measured slower than one; "
+                         "SLOPLLM_B200_PHASED_PREFILL=1 changes the default")
     ap.add_argument("--no-phased-prefill", dest="phased_prefill", action="store_false")
     ap.add_argument("--no-fused-collectives", action="store_true", help="NCCL collectives instead of the in-kernel NVLink ones")
     ap.add_argument("--cpu", action="store_true", help="run on the CPU reference ops (plumbing / debugging)")

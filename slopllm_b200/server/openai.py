@@ -22,7 +22,7 @@ import uuid
 from typing import Dict, List, Optional, Tuple
 
 from .. import __version__
-from ..config import EngineConfig, SamplingParams
+from ..config import EngineConfig, SamplingParams, env_flag, env_str
 from ..scheduler.scheduler import GenerationRequest, GenerationScheduler
 from .parsers import ChatModelParser, GlmParser, check_stop_sequences, resolve_control_tokens, starts_in_reasoning
 
@@ -193,7 +193,11 @@ class OpenAIServer:
             cont = bool(kw.pop("continue_final_message", False))
             ids = self.tok.apply_chat_template(params["messages"], tokenize=True, add_generation_prompt=not cont,
                                                continue_final_message=cont, tools=params.get("tools"), **kw)
-            return list(ids["input_ids"] if isinstance(ids, dict) else ids)
+            ids = list(ids["input_ids"] if isinstance(ids, dict) else ids)
+            if env_flag("CHAT_DEBUG"):      # the rendered prompt as the model sees it (reference: SLOPLLM_CHAT_DEBUG)
+                import sys
+                print(f"[chat] {len(ids)} prompt tokens:\n{self.tok.decode(ids)}", file=sys.stderr, flush=True)
+            return ids
         return list(self.tok.encode(params.get("prompt", ""), add_special_tokens=False))
 
     def _sampling(self, p: dict) -> SamplingParams:
@@ -232,8 +236,9 @@ class OpenAIServer:
         if not isinstance(messages, list) or not messages:
             raise HttpError(400, "messages must be a non-empty array", param="messages")
         kwargs = dict(params.get("chat_template_kwargs") or {})
-        if params.get("reasoning_effort") is not None:
-            kwargs["reasoning_effort"] = params["reasoning_effort"]
+        effort = params.get("reasoning_effort") or env_str("REASONING_EFFORT")      # request field, else the server default
+        if effort:
+            kwargs.setdefault("reasoning_effort", effort)
         sp = self._sampling(params)
         stops = params.get("stop") or []
         stops = [stops] if isinstance(stops, str) else [s for s in stops if isinstance(s, str)]
