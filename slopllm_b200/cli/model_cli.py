@@ -28,6 +28,8 @@ def add_model_args(ap: argparse.ArgumentParser) -> None:
     ap.add_argument("--arena", type=float, default=92.0, help="GiB of device memory the weights + KV cache may take per GPU")
     ap.add_argument("--cp", action="store_true", help="context parallelism (KV tokens interleaved across ranks)")
     ap.add_argument("--ep", action="store_true", help="expert parallelism for the routed experts")
+    ap.add_argument("--dp", type=int, default=1, help="data parallelism: the job's ranks form this many independent model "
+                                                      "replicas (each tensor-parallel over ranks / dp GPUs) behind one front end")
     ap.add_argument("--mtp", type=int, nargs="?", const=3, default=0, help="speculative drafts per step (bare flag: 3)")
     ap.add_argument("--batch-size", type=int, default=8)
     ap.add_argument("--chunk-size", type=int, default=8192)
@@ -62,8 +64,11 @@ def _context(args) -> ParallelContext:
     gpus: List[int] = [int(x) for x in args.gpus.split(",") if x != ""] if args.gpus else list(range(world))
     if len(gpus) != world:
         raise SystemExit(f"--gpus names {len(gpus)} devices but the job has {world} rank(s): start one rank per GPU with torchrun")
+    dp = max(1, getattr(args, "dp", 1))
+    if world % dp != 0:
+        raise SystemExit(f"--dp {dp} does not divide the job's {world} rank(s)")
     if world > 1:
-        return init_from_env("gloo" if args.cpu else None, cp=args.cp, ep=args.ep)
+        return init_from_env("gloo" if args.cpu else None, cp=args.cp, ep=args.ep, dp=dp)
     dev = torch.device("cpu") if args.cpu or not torch.cuda.is_available() else torch.device("cuda", gpus[0] if gpus else 0)
     if dev.type == "cuda":
         torch.cuda.set_device(dev)

@@ -25,6 +25,7 @@ def parse_args(argv=None):
     ap.add_argument("--admin-api-key", default=None)
     ap.add_argument("--served-model-name", default="")
     ap.add_argument("--no-warmup", action="store_true")
+    ap.add_argument("--dp-port", type=int, default=29640, help="port of the store that carries requests to the other replicas (--dp)")
     # sampling defaults applied when a request does not set them (reference `src/openai-server.ts:51-103`)
     ap.add_argument("--max-tokens", type=int, default=65536)
     ap.add_argument("--temperature", type=float, default=0.6)
@@ -67,20 +68,38 @@ def main(argv=None) -> int:
                                             repetition_penalty=args.repetition_penalty, presence_penalty=args.presence_penalty,
                                             repetition_penalty_window=args.repetition_penalty_window)
     rt.scheduler.start()
-    if rt.ctx.rank != 0:
-        rt.scheduler._thread.join()              # followers mirror rank 0 until it broadcasts stop
+    ctx = rt.ctx
+    if ctx.rank != 0:
+        rt.scheduler._thread.join()              # followers mirror their replica's first rank until it broadcasts stop
         return 0
+    front = rt.scheduler
+    proxies = []
+    if ctx.dp_world > 1:
+        # replicas other than the front end's are fed through mailboxes on a store that job rank 0 hosts
+        from ..scheduler.data_parallel import DataParallelRouter, ReplicaAgent, ReplicaProxy
+        from ..utils.health import make_store
+        store = make_store(ctx.global_rank, ctx.global_world, port=args.dp_port)
+        if ctx.dp_rank != 0:
+            agent = ReplicaAgent(store, ctx.dp_rank, rt.scheduler).start()
+            agent._thread.join()                 # until the front end sends "stop"
+            rt.scheduler.stop()
+            return 0
+        proxies = [ReplicaProxy(store, d).start() for d in range(1, ctx.dp_world)]
+        front = DataParallelRouter([rt.scheduler] + proxies, page_tokens=rt.engine.kv.tokens_per_page)
     from ..server.openai import OpenAIServer, serve
     if not args.no_warmup:
         print(f"warm-up took {warm_up(rt):.1f} s", file=sys.stderr)
     name = args.served_model_name or (args.model.rstrip("/").split("/")[-1] if args.model else args.random_init)
-    server = OpenAIServer(rt.scheduler, rt.tokenizer, rt.engine_cfg, model_name=name, max_model_len=args.max_model_len)
-    print(f"listening on http://{args.host}:{args.port}  model={name}  ranks={rt.ctx.world}  mtp={args.mtp}", file=sys.stderr)
+    server = OpenAIServer(front, rt.tokenizer, rt.engine_cfg, model_name=name, max_model_len=args.max_model_len)
+    print(f"listening on http://{args.host}:{args.port}  model={name}  ranks={ctx.global_world or ctx.world}  "
+          f"replicas={ctx.dp_world}  mtp={args.mtp}", file=sys.stderr)
     try:
         asyncio.run(serve(server))
     except KeyboardInterrupt:
         pass
     finally:
+        for p in proxies:
+            p.stop()
         rt.scheduler.stop()
     return 0
 

@@ -23,6 +23,18 @@ class ParallelContext:
     cp: bool = False           # context parallelism: KV rows interleaved across ranks
     ep: bool = False           # expert parallelism for routed experts
     group: Optional[object] = None
+    # data parallelism: the job's ranks are cut into `dp_world` replicas of `world` ranks each; `rank` / `world` / `group`
+    # describe this rank's replica, `global_rank` / `global_world` the whole job (None: the replica is the job)
+    dp_rank: int = 0
+    dp_world: int = 1
+    global_rank: Optional[int] = None
+    global_world: Optional[int] = None
+
+    def peer(self, i: int) -> int:
+        """Job-wide rank of member `i` of this replica (what point-to-point calls and `src=` arguments take)."""
+        if self.group is None or self.dp_world == 1:
+            return i
+        return dist.get_global_rank(self.group, i)
 
     @property
     def is_distributed(self) -> bool:
@@ -38,8 +50,9 @@ class ParallelContext:
 
 
 def init_from_env(backend: Optional[str] = None, cp: bool = False, ep: bool = False,
-                  timeout_s: float = 600.0) -> ParallelContext:
-    """Initialise from torchrun's RANK / LOCAL_RANK / WORLD_SIZE / MASTER_* variables."""
+                  timeout_s: float = 600.0, dp: int = 1) -> ParallelContext:
+    """Initialise from torchrun's RANK / LOCAL_RANK / WORLD_SIZE / MASTER_* variables.  With `dp` > 1 the ranks form
+    `dp` model replicas of WORLD_SIZE / dp consecutive ranks; the returned context is that of this rank's replica."""
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", str(rank)))
@@ -53,6 +66,17 @@ def init_from_env(backend: Optional[str] = None, cp: bool = False, ep: bool = Fa
         kw = {"device_id": device} if use_cuda else {}
         dist.init_process_group(backend or ("nccl" if use_cuda else "gloo"), rank=rank, world_size=world,
                                 timeout=timedelta(seconds=timeout_s), **kw)
+    if dp > 1:
+        if world % dp != 0:
+            raise ValueError(f"{world} ranks cannot form {dp} replicas of equal size")
+        tp = world // dp
+        mine = None
+        for d in range(dp):                      # every rank creates every group, in the same order
+            g = dist.new_group(ranks=list(range(d * tp, (d + 1) * tp)))
+            if d == rank // tp:
+                mine = g
+        return ParallelContext(rank % tp, tp, device, cp, ep, mine if tp > 1 else None, dp_rank=rank // tp, dp_world=dp,
+                               global_rank=rank, global_world=world)
     return ParallelContext(rank, world, device, cp, ep, dist.group.WORLD if world > 1 else None)
 
 
@@ -123,8 +147,8 @@ class Comm:
             if peer == self.ctx.rank:
                 recv[peer].copy_(send[peer])
                 continue
-            reqs.append(dist.isend(send[peer].contiguous(), peer, group=self.ctx.group))
-            reqs.append(dist.irecv(recv[peer], peer, group=self.ctx.group))
+            reqs.append(dist.isend(send[peer].contiguous(), self.ctx.peer(peer), group=self.ctx.group))
+            reqs.append(dist.irecv(recv[peer], self.ctx.peer(peer), group=self.ctx.group))
         for r in reqs:
             r.wait()
         return recv  # type: ignore[return-value]

@@ -288,7 +288,7 @@ class NvlinkComm(Comm):
             import torch.distributed._symmetric_memory as symm
             buf = symm.empty(lay["total"], dtype=torch.uint8, device=ctx.device)
             buf.zero_()
-            hdl = symm.rendezvous(buf, group=dist.group.WORLD)
+            hdl = symm.rendezvous(buf, group=ctx.group or dist.group.WORLD)
             ptrs = [int(p) for p in hdl.buffer_ptrs]
             keep = hdl
         else:
@@ -302,7 +302,7 @@ class NvlinkComm(Comm):
             N.check(lib.sl_ipc_export(buf.data_ptr(), handle, C.byref(offset)), "sl_ipc_export")
             mine = (bytes(handle), int(offset.value))
             everyone = [None] * ctx.world
-            dist.all_gather_object(everyone, mine)
+            dist.all_gather_object(everyone, mine, group=ctx.group)
             ptrs = []
             for r, (hb, off) in enumerate(everyone):
                 if r == ctx.rank:
@@ -314,7 +314,7 @@ class NvlinkComm(Comm):
                 ptrs.append(int(out.value))
             keep = everyone
         torch.cuda.synchronize()
-        dist.barrier()
+        dist.barrier(group=ctx.group)
         region = SymmetricRegion(ctx.rank, ctx.world, NvlinkComm.MAX_ROWS, H, buf, ptrs, gather_bytes, cp_shape,
                                  bulk_rows=bulk_rows)
         region._keep = keep

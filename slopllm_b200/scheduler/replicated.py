@@ -22,8 +22,9 @@ from .scheduler import CacheFlushEvent, GenerationRequest
 
 
 class ReplicaChannel:
-    def __init__(self, rank: int, world: int, group=None, idle_wait_s: float = 0.02):
+    def __init__(self, rank: int, world: int, group=None, idle_wait_s: float = 0.02, src: int = 0):
         self.rank, self.world, self.group = rank, world, group
+        self.src = src                                          # job-wide rank of this replica's rank 0
         self.idle_wait_s = idle_wait_s
         self.live: Dict[str, GenerationRequest] = {}          # requests known to this rank, by id
         self.inbox: "queue.Queue" = queue.Queue()             # rank 0: what the front end submitted since the last step
@@ -58,7 +59,7 @@ class ReplicaChannel:
     def exchange(self, sched) -> None:
         payload = [self._collect(sched) if self.rank == 0 else None]
         if self.world > 1:
-            dist.broadcast_object_list(payload, src=0, group=self.group)
+            dist.broadcast_object_list(payload, src=self.src, group=self.group)
         wire = payload[0]
         if wire["stop"]:
             sched._stop.set()
@@ -82,7 +83,17 @@ class ReplicaChannel:
 
 
 def make_channel(ctx, idle_wait_s: float = 0.02) -> Optional[ReplicaChannel]:
-    """A channel over a dedicated gloo group when the job has more than one rank."""
-    if ctx.world <= 1 or not dist.is_initialized():
+    """A channel over a dedicated gloo group of this replica's ranks when the replica has more than one rank.  Under data
+    parallelism every rank of the job creates every replica's group (group creation is collective over the job)."""
+    if not dist.is_initialized() or (ctx.world <= 1 and ctx.dp_world <= 1):
         return None
-    return ReplicaChannel(ctx.rank, ctx.world, dist.new_group(backend="gloo"), idle_wait_s)
+    if ctx.dp_world <= 1:
+        return ReplicaChannel(ctx.rank, ctx.world, dist.new_group(backend="gloo"), idle_wait_s)
+    mine = None
+    for d in range(ctx.dp_world):
+        g = dist.new_group(ranks=list(range(d * ctx.world, (d + 1) * ctx.world)), backend="gloo")
+        if d == ctx.dp_rank:
+            mine = g
+    if ctx.world <= 1:
+        return None
+    return ReplicaChannel(ctx.rank, ctx.world, mine, idle_wait_s, src=ctx.dp_rank * ctx.world)
