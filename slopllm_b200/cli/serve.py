@@ -25,6 +25,8 @@ def parse_args(argv=None):
     ap.add_argument("--admin-api-key", default=None)
     ap.add_argument("--served-model-name", default="")
     ap.add_argument("--no-warmup", action="store_true")
+    ap.add_argument("--health-port", type=int, default=0, help="multi-rank jobs: port of the heartbeat store (0: no rank-failure monitor)")
+    ap.add_argument("--health-timeout", type=float, default=10.0, help="seconds without a heartbeat after which a rank counts as lost")
     ap.add_argument("--dp-port", type=int, default=29640, help="port of the store that carries requests to the other replicas (--dp)")
     # sampling defaults applied when a request does not set them (reference `src/openai-server.ts:51-103`)
     ap.add_argument("--max-tokens", type=int, default=65536)
@@ -67,8 +69,19 @@ def main(argv=None) -> int:
     rt.engine_cfg.sampling = SamplingParams(temperature=args.temperature, top_p=args.top_p, top_k=args.top_k,
                                             repetition_penalty=args.repetition_penalty, presence_penalty=args.presence_penalty,
                                             repetition_penalty_window=args.repetition_penalty_window)
-    rt.scheduler.start()
     ctx = rt.ctx
+    monitor = None
+    if args.health_port and (ctx.global_world or ctx.world) > 1:
+        # heartbeats of all ranks in a store on job rank 0: a silent rank makes /health answer 503 and the schedulers fail
+        # their requests instead of launching collectives that could not complete
+        from ..utils.health import HealthMonitor, make_store as make_health_store
+        g_rank, g_world = (ctx.global_rank, ctx.global_world) if ctx.global_world else (ctx.rank, ctx.world)
+        hstore = make_health_store(g_rank, g_world, port=args.health_port)
+        hstore.set(f"ready/{g_rank}", "1")
+        hstore.wait([f"ready/{r}" for r in range(g_world)])          # a rank that is still loading is not a dead rank
+        monitor = HealthMonitor(hstore, g_rank, g_world, interval_s=0.5, timeout_s=args.health_timeout).start()
+        rt.scheduler.health = monitor
+    rt.scheduler.start()
     if ctx.rank != 0:
         rt.scheduler._thread.join()              # followers mirror their replica's first rank until it broadcasts stop
         return 0
@@ -90,7 +103,8 @@ def main(argv=None) -> int:
     if not args.no_warmup:
         print(f"warm-up took {warm_up(rt):.1f} s", file=sys.stderr)
     name = args.served_model_name or (args.model.rstrip("/").split("/")[-1] if args.model else args.random_init)
-    server = OpenAIServer(front, rt.tokenizer, rt.engine_cfg, model_name=name, max_model_len=args.max_model_len)
+    server = OpenAIServer(front, rt.tokenizer, rt.engine_cfg, model_name=name, max_model_len=args.max_model_len,
+                          healthy=(monitor.is_healthy if monitor is not None else (lambda: True)))
     print(f"listening on http://{args.host}:{args.port}  model={name}  ranks={ctx.global_world or ctx.world}  "
           f"replicas={ctx.dp_world}  mtp={args.mtp}", file=sys.stderr)
     try:

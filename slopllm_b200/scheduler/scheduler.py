@@ -82,6 +82,7 @@ class ServerMetrics:
     prefill_time_seconds_count: int = 0
     prefill_time_seconds_sum: float = 0.0
     collective_timeouts_total: int = 0
+    rank_failures_total: int = 0
     phase_seconds: Dict[str, float] = field(default_factory=dict)
     phase_count: Dict[str, int] = field(default_factory=dict)
 
@@ -164,8 +165,11 @@ class _Row:
 
 class GenerationScheduler:
     def __init__(self, engine: EngineLike, max_batch: int = 8, chunk_size: int = 8192, eos_token_ids: Seq[int] = (),
-                 host_tier: Optional[HostTier] = None, decode_latency_ms: float = 0.0, replica_channel=None):
+                 host_tier: Optional[HostTier] = None, decode_latency_ms: float = 0.0, replica_channel=None, health=None):
         self.engine = engine
+        # rank-failure monitor (utils/health.py): while it reports a lost peer no step is launched (its collectives could
+        # never complete) and requests are failed at once instead of queueing behind a dead replica
+        self.health = health
         # multi-process serving: rank 0 owns the request queue and broadcasts every step's events so that all
         # ranks admit, cancel and flush in the same step (see scheduler/replicated.py)
         self.replica = replica_channel
@@ -180,6 +184,7 @@ class GenerationScheduler:
         self._free_rows = list(range(max_batch))[::-1]
         self._stop = threading.Event()
         self._thread: Optional[threading.Thread] = None
+        self._was_unhealthy = False
 
     # ---- public -------------------------------------------------------------------------------------
     def _inbox(self) -> "queue.Queue":
@@ -211,8 +216,38 @@ class GenerationScheduler:
         if self._thread:
             self._thread.join(timeout=30)
 
+    def _fail_unhealthy(self) -> None:
+        """A peer is gone: end every admitted and every waiting request with an error, answer pending cache flushes."""
+        err = RuntimeError(self.health.state.reason or "a rank of this replica is not responding")
+        if self.rows:
+            self._fail_all(err)
+        for q in ([self.replica.inbox] if self.replica is not None else []) + [self.events]:
+            while True:
+                try:
+                    ev = q.get_nowait()
+                except queue.Empty:
+                    break
+                if ev is None:
+                    self._stop.set()
+                elif isinstance(ev, CacheFlushEvent):
+                    ev.done.set()
+                else:
+                    ev.error, ev.finish_reason = f"RankFailure: {err}", "error"
+                    self.metrics.request_error_total += 1
+                    if ev.on_finish:
+                        ev.on_finish(ev)
+        self.metrics.running_requests = 0
+
     def run(self) -> None:
         while not self._stop.is_set():
+            if self.health is not None and not self.health.is_healthy():
+                if not self._was_unhealthy:
+                    self.metrics.rank_failures_total += 1
+                self._was_unhealthy = True
+                self._fail_unhealthy()
+                time.sleep(0.02)
+                continue
+            self._was_unhealthy = False
             if self.replica is not None:
                 self.replica.exchange(self)
                 if self._stop.is_set():
@@ -224,6 +259,7 @@ class GenerationScheduler:
                 if ev is None:
                     break
                 self.events.put(ev)               # re-queue; step() drains in order
+                continue                          # (the wait may have been long: look at the health monitor first)
             self.step()
 
     # ---- one iteration ----------------------------------------------------------------------------------

@@ -71,6 +71,7 @@ def render_metrics(m, pending: int, kv, batch_size: int, chunk_size: int, max_mo
         f"vllm:request_prefill_time_seconds_count {m.prefill_time_seconds_count}",
         "# TYPE glm:phase_seconds_total counter", "# TYPE glm:phase_count_total counter",
         "# TYPE glm:collective_timeouts_total counter", f"glm:collective_timeouts_total {m.collective_timeouts_total}",
+        "# TYPE glm:rank_failures_total counter", f"glm:rank_failures_total {getattr(m, 'rank_failures_total', 0)}",
     ]
     for key, sec in m.phase_seconds.items():
         phase, b = key.split("/b")

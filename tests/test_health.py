@@ -5,7 +5,7 @@ import time
 
 import pytest
 
-from slopllm_b200.utils.health import FaultInjector, HealthMonitor, RankFailure, make_store
+from slopllm_b200.utils.health import FaultInjector, HealthMonitor, HealthState, RankFailure, make_store
 from slopllm_b200.utils.tracing import PhaseTimers, nvtx_range
 
 from mp_util import _free_port, run_ranks
@@ -130,3 +130,49 @@ def test_phase_timers_and_nvtx_noop():
     t.record("decode", 4, 0.5)
     text = t.prometheus()
     assert 'phase="decode",batch_size="4"' in text and "phase_seconds_count" in text and t.count[("decode", 4)] == 2
+
+
+def test_scheduler_thread_refuses_to_step_while_a_peer_is_lost():
+    """With a monitor attached, the scheduler loop launches nothing while the monitor reports a lost rank: running and
+    queued requests end with an error at once, pending cache flushes are answered, and service resumes after reset()."""
+    import threading
+    from slopllm_b200.config import SamplingParams
+    from slopllm_b200.scheduler.scheduler import GenerationRequest, GenerationScheduler
+    from test_scheduler import FakeEngine
+
+    class Mon:
+        def __init__(self):
+            self.ok = True
+            self.state = HealthState(False, [1], "no heartbeat from rank(s) [1]")
+
+        def is_healthy(self):
+            return self.ok
+
+    mon, eng = Mon(), FakeEngine()
+    sched = GenerationScheduler(eng, max_batch=2, chunk_size=64, health=mon)
+    sched.start()
+    try:
+        def req(i, n):
+            done = threading.Event()
+            r = GenerationRequest(id=str(i), input_ids=list(range(5, 15)), max_tokens=n, sampling=SamplingParams(temperature=0.0),
+                                  on_finish=lambda r: done.set())
+            r.done = done
+            return r
+        a = req(0, 3)
+        sched.submit(a)
+        assert a.done.wait(10) and a.finish_reason == "length"
+        mon.ok = False
+        time.sleep(0.1)
+        steps_before = len(eng.decode_batches)
+        b = req(1, 3)
+        sched.submit(b)
+        flush = sched.flush_gpu_cache()
+        assert b.done.wait(10) and b.finish_reason == "error" and "heartbeat" in b.error
+        assert flush.done.wait(10)
+        assert len(eng.decode_batches) == steps_before and sched.metrics.rank_failures_total == 1
+        mon.ok = True
+        c = req(2, 3)
+        sched.submit(c)
+        assert c.done.wait(10) and c.finish_reason == "length"
+    finally:
+        sched.stop()
