@@ -41,18 +41,23 @@ def parse_args(argv=None):
     return ap.parse_args(argv)
 
 
-def warm_up(rt, tokens: int = 32) -> float:
-    """A short greedy request through the scheduler so that the first user request finds the decode graphs captured."""
+def warm_up(rt, tokens: int = 32, remote=()) -> float:
+    """A short greedy request through the scheduler (and through every remote replica's proxy) so that the first user
+    request finds the decode graphs captured."""
     import threading
     from ..config import SamplingParams
     from ..scheduler.scheduler import GenerationRequest
-    done = threading.Event()
-    req = GenerationRequest(id="warmup", input_ids=[1] * 16, max_tokens=tokens, sampling=SamplingParams(temperature=0.0),
-                            on_finish=lambda r: done.set())
     t0 = time.time()
-    rt.scheduler.submit(req)
-    done.wait(timeout=600)
-    rt.scheduler.flush_gpu_cache().done.wait(timeout=60)
+    waits = []
+    for i, target in enumerate([rt.scheduler, *remote]):
+        done = threading.Event()
+        target.submit(GenerationRequest(id=f"warmup-{i}", input_ids=[1] * 16, max_tokens=tokens,
+                                        sampling=SamplingParams(temperature=0.0), on_finish=lambda r, d=done: d.set()))
+        waits.append(done)
+    for done in waits:
+        done.wait(timeout=600)
+    for target in [rt.scheduler, *remote]:
+        target.flush_gpu_cache().done.wait(timeout=60)
     return time.time() - t0
 
 
@@ -101,7 +106,7 @@ def main(argv=None) -> int:
         front = DataParallelRouter([rt.scheduler] + proxies, page_tokens=rt.engine.kv.tokens_per_page)
     from ..server.openai import OpenAIServer, serve
     if not args.no_warmup:
-        print(f"warm-up took {warm_up(rt):.1f} s", file=sys.stderr)
+        print(f"warm-up took {warm_up(rt, remote=proxies):.1f} s", file=sys.stderr)
     name = args.served_model_name or (args.model.rstrip("/").split("/")[-1] if args.model else args.random_init)
     server = OpenAIServer(front, rt.tokenizer, rt.engine_cfg, model_name=name, max_model_len=args.max_model_len,
                           healthy=(monitor.is_healthy if monitor is not None else (lambda: True)))
