@@ -137,6 +137,9 @@ def reattach(engine, ctx: ParallelContext, cfg=None, fused: bool = True) -> None
     stay as they are; the caller decides what happens to the requests that were in flight."""
     from .fused import make_comm
     model = engine.model
+    old = getattr(model, "comm", None)
+    if old is not None and hasattr(old, "close"):
+        old.close()                       # peer mappings of the previous generation
     model.ctx = ctx
     model.comm = make_comm(ctx, cfg if cfg is not None else getattr(model, "cfg", None), fused=fused)
     if getattr(model, "ops", None) is not None and hasattr(model.ops, "ctx"):

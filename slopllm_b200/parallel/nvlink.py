@@ -303,7 +303,7 @@ class NvlinkComm(Comm):
             mine = (bytes(handle), int(offset.value))
             everyone = [None] * ctx.world
             dist.all_gather_object(everyone, mine, group=ctx.group)
-            ptrs = []
+            ptrs, opened = [], []
             for r, (hb, off) in enumerate(everyone):
                 if r == ctx.rank:
                     ptrs.append(buf.data_ptr())
@@ -312,7 +312,8 @@ class NvlinkComm(Comm):
                 hbuf = (C.c_ubyte * 64).from_buffer_copy(hb)
                 N.check(lib.sl_ipc_open(hbuf, off, C.byref(out)), f"sl_ipc_open(rank {r})")
                 ptrs.append(int(out.value))
-            keep = everyone
+                opened.append((int(out.value), int(off)))
+            keep = (everyone, opened)
         torch.cuda.synchronize()
         dist.barrier(group=ctx.group)
         region = SymmetricRegion(ctx.rank, ctx.world, NvlinkComm.MAX_ROWS, H, buf, ptrs, gather_bytes, cp_shape,
@@ -432,3 +433,15 @@ class NvlinkComm(Comm):
         self.region.check_status()
         if self._checks:
             self.region.check_canaries()
+
+    def close(self) -> None:
+        """Unmap the peers' regions (CUDA IPC mappings opened by `_make_region`).  Call it when the communicator is
+        replaced - after a lost rank its peers' mappings point into a process that no longer exists - with no kernel of
+        this communicator in flight."""
+        keep = getattr(self.region, "_keep", None)
+        if isinstance(keep, tuple) and len(keep) == 2:
+            lib = N.kernels()
+            lib.sl_ipc_close.argtypes = [vp, C.c_ulonglong]
+            for ptr, off in keep[1]:
+                lib.sl_ipc_close(ptr, off)
+            self.region._keep = None
