@@ -149,8 +149,7 @@ class GlmMoeDsaModel:
         elif st.slots is None:
             raise RuntimeError(f"layer {layer} shares indexer slots but no full-indexer layer ran before it")
         if ctx.cp and ctx.world > 1:
-            q_abs = comm.all_gather(q_abs, dim=1)
-            q_pe = comm.all_gather(q_pe, dim=1)
+            q_abs, q_pe = comm.all_gather_many([q_abs, q_pe], dim=1)          # both query parts in one collective
             if hasattr(ops, "sparse_mla_partials"):
                 o = comm.cp_merge_partials(ops, *ops.sparse_mla_partials(q_abs, q_pe, lc, st.slots, st.lengths))
             else:

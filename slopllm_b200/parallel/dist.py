@@ -119,6 +119,26 @@ class Comm:
         dist.all_gather(parts, x.contiguous(), group=self.ctx.group)
         return parts
 
+    def all_gather_many(self, xs: List[torch.Tensor], dim: int = -1) -> List[torch.Tensor]:
+        """Several tensors gathered by ONE collective: their bytes travel as one packed buffer (segments padded to 16
+        bytes) and each result is the concatenation of the ranks' parts along `dim`.  Reference: `allGatherTwo`
+        (`src/parallel_ops.ts:2666-2712`, `p2p_allgather_two_write_kernel`), which gathers the two query-side tensors of
+        a context-parallel layer in one launch."""
+        if self.ctx.world == 1:
+            return list(xs)
+        segs, sizes = [], []
+        for x in xs:
+            b = x.contiguous().view(torch.uint8).reshape(-1)
+            pad = (-b.numel()) % 16
+            segs.append(b if pad == 0 else torch.cat([b, b.new_zeros(pad)]))
+            sizes.append((b.numel(), b.numel() + pad))
+        parts = self.all_gather_list(torch.cat(segs))
+        outs, off = [], 0
+        for x, (n, padded) in zip(xs, sizes):
+            outs.append(torch.cat([p[off:off + n].view(x.dtype).reshape(x.shape) for p in parts], dim=dim))
+            off += padded
+        return outs
+
     def all_to_all(self, send: List[torch.Tensor]) -> List[torch.Tensor]:
         """send[i] goes to rank i; shapes may differ per pair but must be known to both
         sides (callers exchange counts first)."""

@@ -66,3 +66,23 @@ def test_ep2_matches_single():
     ref = _greedy(0, 1, False, False, 40, 6)
     out = run_ranks(_greedy, 2, False, True, 40, 6)
     assert out[0] == out[1] == ref
+
+
+def _gather_many(rank, world):
+    import torch
+    from slopllm_b200.parallel.dist import Comm, init_from_env
+    comm = Comm(init_from_env("gloo"))
+    a = torch.full((3, 2, 5), float(rank + 1), dtype=torch.bfloat16)        # 60 bytes: segment padded to 64
+    b = torch.arange(7, dtype=torch.float32).reshape(1, 7) + 10 * rank       # 28 bytes
+    c = torch.tensor([[rank, -rank]], dtype=torch.int32)
+    ga, gb, gc = comm.all_gather_many([a, b, c], dim=1)
+    one = comm.all_gather(a, dim=1)
+    return ga.shape, bool(torch.equal(ga, one)), gb.tolist(), gc.tolist()
+
+
+def test_all_gather_many_packs_several_tensors_into_one_collective():
+    from mp_util import run_ranks
+    for shape, same, gb, gc in run_ranks(_gather_many, 2):
+        assert tuple(shape) == (3, 4, 5) and same
+        assert gb == [[0, 1, 2, 3, 4, 5, 6, 10, 11, 12, 13, 14, 15, 16]]
+        assert gc == [[0, 0, 1, -1]]
