@@ -172,6 +172,13 @@ class DenseCache:
             self.k[i][b] = self.k[i][a]
             self.v[i][b] = self.v[i][a]
 
+    def page_tensors(self):
+        """Slot-indexed tensors in a fixed order (host prefix tier); None for hybrid models, whose recurrent and
+        convolution state belongs to a sequence, not to its pages."""
+        if self.conv:
+            return None
+        return [t for i in sorted(self.k) for t in (self.k[i], self.v[i])]
+
     def reset_state(self, slot: int) -> None:
         for i in self.conv:
             self.conv[i][slot].zero_()

@@ -88,6 +88,50 @@ class Engine:
             if lc.idx is not None:
                 lc.idx[b] = lc.idx[a]
 
+    # -- page IO for the pinned-host prefix tier (reference `copyPrefixFrom`, `src/paged_kv.ts:308-370`) ---------------
+    def _page_tensors(self) -> Optional[List[torch.Tensor]]:
+        """The cache tensors whose first dimension is the slot (page * PAGE_SIZE + offset), in a fixed order; None when
+        the cache also holds per-sequence state that pages do not capture (recurrent layers)."""
+        c = self.cache
+        if hasattr(c, "page_tensors"):
+            return c.page_tensors()
+        out = []
+        for lc in c.layers:
+            out.append(lc.kv)
+            if lc.idx is not None:
+                out.append(lc.idx)
+        return out
+
+    def supports_host_tier(self) -> bool:
+        return self._page_tensors() is not None
+
+    def read_page(self, page: int) -> torch.Tensor:
+        """All layers' rows of one page as a single byte buffer on the host (pinned when the cache is on a GPU): the
+        layers' slices are packed on the device, so the page crosses PCIe / C2C in one copy."""
+        sl = slice(page * PAGE_SIZE, (page + 1) * PAGE_SIZE)
+        packed = torch.cat([t[sl].reshape(-1).view(torch.uint8) for t in self._page_tensors()])
+        if not packed.is_cuda:
+            return packed
+        host = torch.empty(packed.numel(), dtype=torch.uint8, pin_memory=True)
+        host.copy_(packed, non_blocking=True)
+        torch.cuda.current_stream(self.device).synchronize()        # the blob may be read (or the page reused) right away
+        return host
+
+    def write_page(self, page: int, blob: torch.Tensor) -> None:
+        """Inverse of `read_page` into page `page` (one host-to-device copy, then per-layer scatter on the device)."""
+        sl = slice(page * PAGE_SIZE, (page + 1) * PAGE_SIZE)
+        tensors = self._page_tensors()
+        total = sum(t[sl].numel() * t.element_size() for t in tensors)
+        if blob.numel() != total:
+            raise ValueError(f"page blob of {blob.numel()} bytes does not match this cache's page size of {total} bytes")
+        dev = blob.to(self.device, non_blocking=True)
+        off = 0
+        for t in tensors:
+            dst = t[sl]
+            n = dst.numel() * dst.element_size()
+            dst.copy_(dev[off:off + n].view(t.dtype).reshape(dst.shape))
+            off += n
+
     def _buffers(self, B: int, tpr: int) -> StepBuffers:
         key = (B, tpr)
         if key not in self._bufs:

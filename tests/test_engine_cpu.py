@@ -69,3 +69,78 @@ def test_phased_prefill_matches_plain_prefill():
         outs.append((tok, nxt, hid[0]))
     assert outs[0][0] == outs[1][0] and outs[0][1] == outs[1][1]
     assert torch.allclose(outs[0][2], outs[1][2], atol=1e-4, rtol=1e-4)
+
+
+def test_host_tier_restores_pages_of_the_real_engine():
+    """Pinned-host prefix tier with the real engine's page IO: a finished conversation is evicted to the host, the GPU tier
+    is flushed, and the same prompt comes back with its prefix restored from host pages and the same greedy tokens."""
+    import torch
+    from slopllm_b200.config import GlmMoeDsaConfig, SamplingParams
+    from slopllm_b200.models.glm_moe_dsa import GlmMoeDsaModel
+    from slopllm_b200.models.weights import random_model
+    from slopllm_b200.runtime.engine import Engine
+    from slopllm_b200.scheduler.scheduler import GenerationRequest, GenerationScheduler, HostTier
+    cfg = GlmMoeDsaConfig.tiny()
+    eng = Engine(cfg, GlmMoeDsaModel(cfg, random_model(cfg, 0)), num_pages=8, max_batch=1, max_seq_len=512, cuda_graph=False)
+    assert eng.supports_host_tier()
+    # page IO round trip: every layer's rows of the page, and nothing else, come back
+    for lc in eng.cache.layers:
+        lc.kv.random_(0, 255)
+        if lc.idx is not None:
+            lc.idx.random_(0, 255)
+    want = [(lc.kv[64:128].clone(), None if lc.idx is None else lc.idx[64:128].clone()) for lc in eng.cache.layers]
+    blob = eng.read_page(1)
+    assert blob.dtype == torch.uint8 and blob.numel() == sum(64 * (lc.kv.shape[1] + (lc.idx.shape[1] if lc.idx is not None else 0))
+                                                            for lc in eng.cache.layers)
+    eng.write_page(5, blob)
+    for lc, (kv, idx) in zip(eng.cache.layers, want):
+        assert torch.equal(lc.kv[320:384], kv) and (idx is None or torch.equal(lc.idx[320:384], idx))
+        assert torch.equal(lc.kv[64:128], kv)
+    import pytest
+    with pytest.raises(ValueError):
+        eng.write_page(5, blob[:-16])
+    # scheduler level
+    tier = HostTier(8, eng.kv.tokens_per_page, eng.read_page, eng.write_page)
+    sched = GenerationScheduler(eng, max_batch=1, chunk_size=256, host_tier=tier)
+    prompt = torch.randint(2, cfg.vocab_size, (150,), generator=torch.Generator().manual_seed(11)).tolist()
+
+    def run(i):
+        r = GenerationRequest(id=str(i), input_ids=list(prompt), max_tokens=4, sampling=SamplingParams(temperature=0.0))
+        sched.submit(r)
+        for _ in range(100):
+            sched.step()
+            if r.finish_reason:
+                sched.step()
+                return r
+        raise AssertionError("request did not finish")
+    first = run(0)
+    assert first.cached_tokens == 0 and len(first.generated) == 4
+    ev = sched.flush_gpu_cache()                   # staged pages go to the host tier, the GPU tier is emptied
+    sched.step()
+    assert ev.done.is_set() and tier.used_pages == 2 and not eng.kv.staged
+    for lc in eng.cache.layers:                    # whatever the GPU pages held is gone
+        lc.kv.zero_()
+        if lc.idx is not None:
+            lc.idx.zero_()
+    again = run(1)
+    assert again.cached_tokens == 128              # two pages restored from the host
+    assert again.generated == first.generated
+
+
+def test_dense_cache_page_io_and_hybrid_refusal():
+    import torch
+    from slopllm_b200.models.dense import DenseConfig, DenseModel, random_dense_model
+    from slopllm_b200.runtime.engine import Engine
+    cfg = DenseConfig.tiny()
+    w, _ = random_dense_model(cfg, seed=1, device="cpu", dtype=torch.float32)
+    eng = Engine(cfg, DenseModel(cfg, w), num_pages=4, max_batch=1, max_seq_len=256, cuda_graph=False)
+    assert eng.supports_host_tier()
+    for t in eng.cache.page_tensors():
+        t.normal_()
+    blob = eng.read_page(2)
+    eng.write_page(0, blob)
+    for t in eng.cache.page_tensors():
+        assert torch.equal(t[0:64], t[128:192])
+    hyb = DenseConfig.tiny(hybrid=True)
+    wh, _ = random_dense_model(hyb, seed=1, device="cpu", dtype=torch.float32)
+    assert not Engine(hyb, DenseModel(hyb, wh), num_pages=4, max_batch=1, max_seq_len=256, cuda_graph=False).supports_host_tier()
