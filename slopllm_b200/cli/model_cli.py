@@ -25,7 +25,9 @@ def add_model_args(ap: argparse.ArgumentParser) -> None:
     ap.add_argument("--random-init", default="", metavar="SPEC",
                     help="no checkpoint: random weights of 'tiny', 'glm5[:layers]', 'qwen3-tiny' or 'qwen35-tiny'")
     ap.add_argument("--gpus", default="", help="comma-separated device list; its length must equal the number of ranks")
-    ap.add_argument("--arena", type=float, default=92.0, help="GiB of device memory the weights + KV cache may take per GPU")
+    ap.add_argument("--arena", type=float, default=0.0,
+                    help="GiB of device memory this process may allocate per GPU (weights + KV cache + step buffers); a larger "
+                         "request fails with an out-of-memory error instead of taking the GPU.  0: no cap")
     ap.add_argument("--cp", action="store_true", help="context parallelism (KV tokens interleaved across ranks)")
     ap.add_argument("--ep", action="store_true", help="expert parallelism for the routed experts")
     ap.add_argument("--dp", type=int, default=1, help="data parallelism: the job's ranks form this many independent model "
@@ -75,6 +77,24 @@ def _context(args) -> ParallelContext:
     return ParallelContext(device=dev, cp=args.cp, ep=args.ep)
 
 
+def arena_fraction(arena_gb: float, total_bytes: int) -> float:
+    """Share of the device's memory that `--arena` GiB amounts to (1.0: no cap)."""
+    if arena_gb <= 0 or total_bytes <= 0:
+        return 1.0
+    return min(1.0, arena_gb * (1 << 30) / total_bytes)
+
+
+def apply_arena_cap(device: torch.device, arena_gb: float) -> float:
+    """Cap this process's allocations on `device` at `--arena` GiB (the reference sizes one arena per GPU up front,
+    `src/glm_ops.ts:1019-1103`; here the caching allocator gets the same bound).  Returns the fraction applied."""
+    if device.type != "cuda":
+        return 1.0
+    frac = arena_fraction(arena_gb, torch.cuda.get_device_properties(device).total_memory)
+    if frac < 1.0:
+        torch.cuda.set_per_process_memory_fraction(frac, device)
+    return frac
+
+
 def _random_model(spec: str, ctx: ParallelContext, mtp: int):
     from ..parallel.fused import make_comm
     dtype = torch.bfloat16 if ctx.device.type == "cuda" else torch.float32
@@ -107,6 +127,7 @@ def build_runtime(args, with_scheduler: bool = True) -> Runtime:
     from ..utils.model_path import resolve_model_path
 
     ctx = _context(args)
+    apply_arena_cap(ctx.device, args.arena)
     if args.no_fused_collectives:
         os.environ["SLOPLLM_B200_FUSED"] = "0"
     model_dir: Optional[str] = None

@@ -228,7 +228,7 @@ class EngineConfig:
 
     model: str = ""
     gpus: List[int] = field(default_factory=lambda: [0])
-    arena_gb: float = 92.0
+    arena_gb: float = 0.0              # 0: no cap on this process's device allocations
     cp: bool = False
     ep: bool = False                   # expert-parallel MoE instead of TP-sliced experts
     mtp: int = 0                       # number of draft tokens (0 = off; bare --mtp = 3)

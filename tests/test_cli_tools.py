@@ -182,3 +182,12 @@ def test_weights_doc_groups_layers_and_experts(tmp_path):
     assert "| `model.layers.N.mlp.experts.E.down_proj.weight` | [4, 2] | U8 | 4 | 32 B |" in text
     assert "| `model.layers.MTP.mlp.experts.E.down_proj.weight` **MTP** | [4, 2] | U8 | 2 | 16 B |" in text
     assert "**Total tensors**: 10" in text
+
+
+def test_arena_flag_is_a_per_process_allocation_cap():
+    import torch
+    from slopllm_b200.cli.model_cli import apply_arena_cap, arena_fraction
+    total = 180 << 30
+    assert arena_fraction(0.0, total) == 1.0 and arena_fraction(360.0, total) == 1.0
+    assert abs(arena_fraction(90.0, total) - 0.5) < 1e-9
+    assert apply_arena_cap(torch.device("cpu"), 90.0) == 1.0          # nothing to cap on the CPU
