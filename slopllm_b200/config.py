@@ -245,8 +245,7 @@ class EngineConfig:
     port: int = 8000
     api_key: Optional[str] = None
     admin_api_key: Optional[str] = None
-    fused_collectives: bool = True     # in-kernel NVLink collectives (else NCCL fallback)
-    wait_timeout_ms: int = 1000        # bound on every device-side flag wait
+    fused_collectives: bool = True     # in-kernel NVLink collectives (else NCCL); `make_comm` also honours SLOPLLM_B200_FUSED=0
 
     def __post_init__(self) -> None:
         if self.max_pages <= 0:

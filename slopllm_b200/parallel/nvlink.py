@@ -316,8 +316,10 @@ class NvlinkComm(Comm):
             keep = (everyone, opened)
         torch.cuda.synchronize()
         dist.barrier(group=ctx.group)
+        from ..config import env_int
+        # bound of every device-side wait, in polls (a poll is 0.03 - 0.3 us; the default is on the order of a second)
         region = SymmetricRegion(ctx.rank, ctx.world, NvlinkComm.MAX_ROWS, H, buf, ptrs, gather_bytes, cp_shape,
-                                 bulk_rows=bulk_rows)
+                                 wait_spins=env_int("WAIT_SPINS", 4_000_000), bulk_rows=bulk_rows)
         region._keep = keep
         return region
 

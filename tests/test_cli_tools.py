@@ -191,3 +191,24 @@ def test_arena_flag_is_a_per_process_allocation_cap():
     assert arena_fraction(0.0, total) == 1.0 and arena_fraction(360.0, total) == 1.0
     assert abs(arena_fraction(90.0, total) - 0.5) < 1e-9
     assert apply_arena_cap(torch.device("cpu"), 90.0) == 1.0          # nothing to cap on the CPU
+
+
+def test_fused_switch_selects_library_collectives(monkeypatch):
+    """`make_comm` gives the plain communicator on CPU, for one rank, with fused=False and with SLOPLLM_B200_FUSED=0."""
+    import torch
+    from slopllm_b200.parallel import fused as F
+    from slopllm_b200.parallel.dist import Comm, ParallelContext
+    assert type(F.make_comm(ParallelContext())) is Comm
+    made = []
+
+    class FakeNvlink(Comm):
+        def __init__(self, ctx, cfg):
+            super().__init__(ctx)
+            made.append(ctx)
+    import slopllm_b200.parallel.nvlink as NV
+    monkeypatch.setattr(NV, "NvlinkComm", FakeNvlink)
+    ctx = ParallelContext(0, 2, torch.device("cuda", 0))
+    assert type(F.make_comm(ctx)) is FakeNvlink and len(made) == 1
+    assert type(F.make_comm(ctx, fused=False)) is Comm
+    monkeypatch.setenv("SLOPLLM_B200_FUSED", "0")
+    assert type(F.make_comm(ctx)) is Comm and len(made) == 1
