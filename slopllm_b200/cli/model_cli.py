@@ -70,7 +70,8 @@ def _context(args) -> ParallelContext:
     if world % dp != 0:
         raise SystemExit(f"--dp {dp} does not divide the job's {world} rank(s)")
     if world > 1:
-        return init_from_env("gloo" if args.cpu else None, cp=args.cp, ep=args.ep, dp=dp)
+        local = int(os.environ.get("LOCAL_RANK", os.environ.get("RANK", "0")))
+        return init_from_env("gloo" if args.cpu else None, cp=args.cp, ep=args.ep, dp=dp, device_index=gpus[local % len(gpus)])
     dev = torch.device("cpu") if args.cpu or not torch.cuda.is_available() else torch.device("cuda", gpus[0] if gpus else 0)
     if dev.type == "cuda":
         torch.cuda.set_device(dev)

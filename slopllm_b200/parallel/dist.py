@@ -50,14 +50,15 @@ class ParallelContext:
 
 
 def init_from_env(backend: Optional[str] = None, cp: bool = False, ep: bool = False,
-                  timeout_s: float = 600.0, dp: int = 1) -> ParallelContext:
+                  timeout_s: float = 600.0, dp: int = 1, device_index: Optional[int] = None) -> ParallelContext:
     """Initialise from torchrun's RANK / LOCAL_RANK / WORLD_SIZE / MASTER_* variables.  With `dp` > 1 the ranks form
-    `dp` model replicas of WORLD_SIZE / dp consecutive ranks; the returned context is that of this rank's replica."""
+    `dp` model replicas of WORLD_SIZE / dp consecutive ranks; the returned context is that of this rank's replica.
+    `device_index` overrides LOCAL_RANK as this rank's CUDA device (`--gpus 4,5,6,7`)."""
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", str(rank)))
     use_cuda = torch.cuda.is_available() and backend != "gloo"
-    device = torch.device("cuda", local) if use_cuda else torch.device("cpu")
+    device = torch.device("cuda", local if device_index is None else device_index) if use_cuda else torch.device("cpu")
     if use_cuda:
         torch.cuda.set_device(device)
     if world > 1 and not dist.is_initialized():
