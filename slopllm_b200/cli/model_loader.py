@@ -224,6 +224,14 @@ def make_control_server(ex: Executor, model_args: dict, port: int, on_quit=None)
                     return self._json(400, {"error": "cmd must be a non-empty list"})
                 ex.spawn([str(c) for c in cmd])
                 self._json(200, ex.status())
+            elif self.path == "/fork":
+                # run one of this interpreter's modules as the executor (the reference forks a script of its own runtime,
+                # `src/run_model_loader.ts:302-375`): {"module": "slopllm_b200.cli.serve", "args": ["--port", "8000"]}
+                module = body.get("module")
+                if not isinstance(module, str) or not module:
+                    return self._json(400, {"error": "module must be a dotted module name"})
+                ex.spawn([sys.executable, "-m", module, *[str(a) for a in body.get("args") or []]])
+                self._json(200, ex.status())
             elif self.path == "/stop":
                 ex.stop()
                 self._json(200, ex.status())

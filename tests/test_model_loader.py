@@ -71,6 +71,13 @@ def test_loader_keeps_weights_across_executor_restarts(tmp_path):
         time.sleep(1.0)
         assert json.loads(_get(port, "/status"))["running"] is True
         assert _post(port, "/stop")["running"] is False
+        # /fork runs a module of this interpreter as the executor
+        st = _post(port, "/fork", {"module": "platform"})
+        assert st["cmd"][:3] == [sys.executable, "-m", "platform"]
+        t0 = time.time()
+        while json.loads(_get(port, "/status"))["running"] and time.time() - t0 < 30:
+            time.sleep(0.1)
+        assert "Linux" in _get(port, "/follow?live=0")
     finally:
         ex.stop()
         srv.shutdown()
