@@ -165,11 +165,23 @@ def load_model(model_dir: str, device="cpu", dtype=torch.float32, tp_rank: int =
     head_name = "lm_head.weight" if rd.has("lm_head.weight") else "model.embed_tokens.weight"
     lm = rd.dense(head_name, rows=(tp_rank * Vr, (tp_rank + 1) * Vr))
     n = cfg.num_hidden_layers + (cfg.num_nextn_predict_layers if with_mtp else 0)
-    layers = []
+    present = []
     for i in range(n):
         if not rd.has(f"model.layers.{i}.input_layernorm.weight"):
             break
-        layers.append(load_layer(rd, cfg, i, tp_rank, tp_world, ep))
+        present.append(i)
+    # Layers are read by a small pool of threads (`SLOPLLM_B200_LOAD_BATCH_SIZE`, default 8, as the reference's
+    # `SLOPLLM_LOAD_BATCH_SIZE`, `src/chat_model.ts:602-699`): paging the mmap'd shards in and cutting this rank's strided
+    # windows out of them overlaps with the uploads of the layers that are already in host memory.  A CSF container opens
+    # its shards lazily, so it is read by one thread.
+    from ..config import env_int
+    workers = max(1, min(env_int("LOAD_BATCH_SIZE", 8), len(present)))
+    if workers > 1 and src.csf is None:
+        from concurrent.futures import ThreadPoolExecutor
+        with ThreadPoolExecutor(max_workers=workers, thread_name_prefix="load") as pool:
+            layers = list(pool.map(lambda i: load_layer(rd, cfg, i, tp_rank, tp_world, ep), present))
+    else:
+        layers = [load_layer(rd, cfg, i, tp_rank, tp_world, ep) for i in present]
     w = ModelWeights(embed=embed, layers=layers, final_norm=rd.dense("model.norm.weight"), lm_head=LinearWeight(lm),
                      vocab_offset=tp_rank * Vr)
     if src.csf is not None and rd.device.type == "cuda":
