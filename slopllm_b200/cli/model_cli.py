@@ -161,8 +161,3 @@ def build_runtime(args, with_scheduler: bool = True) -> Runtime:
                                     decode_latency_ms=ecfg.decode_latency_ms, replica_channel=make_channel(ctx))
     tok = load_tokenizer(model_dir, vocab)
     return Runtime(cfg, model, engine, sched, tok, ctx, ecfg, model_type)
-
-
-def default_sampling(args) -> SamplingParams:
-    return SamplingParams(temperature=getattr(args, "temperature", 0.6), top_p=getattr(args, "top_p", 0.95),
-                          top_k=getattr(args, "top_k", 20))

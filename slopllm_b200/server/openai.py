@@ -19,7 +19,7 @@ import asyncio
 import json
 import time
 import uuid
-from typing import Dict, List, Optional, Tuple
+from typing import Dict, List, Optional
 
 from .. import __version__
 from ..config import EngineConfig, SamplingParams, env_flag, env_str
@@ -379,7 +379,3 @@ class OpenAIServer:
 async def serve(server: OpenAIServer) -> None:
     await server.start()
     await asyncio.Event().wait()
-
-
-def _unused() -> Tuple:
-    return ()
