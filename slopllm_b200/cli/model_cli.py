@@ -16,7 +16,7 @@ from typing import List, Optional
 
 import torch
 
-from ..config import EngineConfig, GlmMoeDsaConfig, SamplingParams, env_flag
+from ..config import EngineConfig, GlmMoeDsaConfig, env_flag
 from ..parallel.dist import ParallelContext, init_from_env
 
 
