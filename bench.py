@@ -219,34 +219,39 @@ def main():
     details = {"prefill_tok_s": B * P / (prefill_ms / 1e3), "prefill_ms": prefill_ms, "weights_init_s": t_init,
                "weights_gb_per_rank": weights.nbytes() / 1e9}
     if not args.skip_details:
-        r1 = timed_decode(seqs[:1], r8["last"][:1], "bs1")
-        details["bs1"] = {"tok_s": 1e3 / r1["ms_per_step"], "ms_per_step": r1["ms_per_step"],
-                          "e2e_tok_s": 1e3 / r1["e2e_ms_per_step"], "launches_per_step": r1["launches_per_step"],
-                          "vs_ref_mtp3_tok_s": (1e3 / r1["ms_per_step"]) / BASELINE_BS1_TOK_S if L == 78 else None}
-        if args.mtp > 0:
-            for grp, name, ref in ((seqs[:1], "bs1", BASELINE_BS1_STEPS_S), (seqs, f"bs{B}", BASELINE_BS8_STEPS_S)):
-                lt = r1["last"] if name == "bs1" else r8["last"]
-                hs = [torch.zeros(1, cfg.hidden_size, dtype=torch.bfloat16, device=dev) for _ in grp]
-                seed = eng.mtp_seed(grp, lt, hs)
-                acc_tokens = 0
-                for _ in range(Wu):
-                    _, lt, seed = eng.mtp_decode_step(grp, lt, seed)
-                sync_barrier()
-                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                a.record()
-                for _ in range(K):
-                    acc, lt, seed = eng.mtp_decode_step(grp, lt, seed)
-                    acc_tokens += sum(len(x) for x in acc)
-                b.record()
-                sync_barrier()
-                ms = max_over_ranks(a.elapsed_time(b)) / K
-                details[f"mtp{args.mtp}_{name}"] = {
-                    "steps_s": 1e3 / ms, "ms_per_step": ms, "tok_s": acc_tokens / (ms * K / 1e3),
-                    "accept_len": acc_tokens / (K * len(grp)),
-                    # the reference's figure is tok/s divided by the accept length, i.e. sequence-steps per second
-                    "seq_steps_s": len(grp) * 1e3 / ms,
-                    "vs_ref_steps_s": (len(grp) * 1e3 / ms) / ref if L == 78 else None,
-                    "note": "random-init weights: drafts are almost never accepted, so tok/s ~= steps/s * batch"}
+        # the side measurements must not cost the headline line: a failure here is recorded, not raised
+        try:
+            r1 = timed_decode(seqs[:1], r8["last"][:1], "bs1")
+            details["bs1"] = {"tok_s": 1e3 / r1["ms_per_step"], "ms_per_step": r1["ms_per_step"],
+                              "e2e_tok_s": 1e3 / r1["e2e_ms_per_step"], "launches_per_step": r1["launches_per_step"],
+                              "vs_ref_mtp3_tok_s": (1e3 / r1["ms_per_step"]) / BASELINE_BS1_TOK_S if L == 78 else None}
+            if args.mtp > 0:
+                for grp, name, ref in ((seqs[:1], "bs1", BASELINE_BS1_STEPS_S), (seqs, f"bs{B}", BASELINE_BS8_STEPS_S)):
+                    lt = r1["last"] if name == "bs1" else r8["last"]
+                    hs = [torch.zeros(1, cfg.hidden_size, dtype=torch.bfloat16, device=dev) for _ in grp]
+                    seed = eng.mtp_seed(grp, lt, hs)
+                    acc_tokens = 0
+                    for _ in range(Wu):
+                        _, lt, seed = eng.mtp_decode_step(grp, lt, seed)
+                    sync_barrier()
+                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    a.record()
+                    for _ in range(K):
+                        acc, lt, seed = eng.mtp_decode_step(grp, lt, seed)
+                        acc_tokens += sum(len(x) for x in acc)
+                    b.record()
+                    sync_barrier()
+                    ms = max_over_ranks(a.elapsed_time(b)) / K
+                    details[f"mtp{args.mtp}_{name}"] = {
+                        "steps_s": 1e3 / ms, "ms_per_step": ms, "tok_s": acc_tokens / (ms * K / 1e3),
+                        "accept_len": acc_tokens / (K * len(grp)),
+                        # the reference's figure is tok/s divided by the accept length, i.e. sequence-steps per second
+                        "seq_steps_s": len(grp) * 1e3 / ms,
+                        "vs_ref_steps_s": (len(grp) * 1e3 / ms) / ref if L == 78 else None,
+                        "note": "random-init weights: drafts are almost never accepted, so tok/s ~= steps/s * batch"}
+        except Exception as err:  # noqa: BLE001
+            details["error"] = f"{type(err).__name__}: {err}"
+
     from slopllm_b200.ops import tcgen05
     tcgen05.check_errors(dev)
     comm.check_status()
