@@ -191,3 +191,55 @@ def test_two_replicas_of_two_ranks_serve_one_front_end():
     front, leader1 = res[0], res[2]
     assert front["routed"] == [1, 1] and front["local_served"] == 1 and leader1["served"] == 1
     assert len(front["tokens"][0]) == 5 and front["tokens"][0] == front["tokens"][1]
+
+
+def test_serve_cli_with_two_replicas_on_cpu():
+    """`serve --dp 2` under torchrun on two CPU ranks: both replicas answer chat completions through the one front end,
+    the metrics page adds the replicas up, and the rank-failure monitor runs alongside."""
+    import json
+    import subprocess
+    import sys
+    import urllib.request
+    port, dp_port, health_port, master = _free_port(), _free_port(), _free_port(), _free_port()
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+           "--master-port", str(master), "-m", "slopllm_b200.cli.serve", "--random-init", "tiny", "--cpu", "--dp", "2",
+           "--gpus", "0,1", "--batch-size", "2", "--chunk-size", "64", "--max-pages", "64", "--port", str(port),
+           "--dp-port", str(dp_port), "--health-port", str(health_port)]
+    proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    try:
+        up = False
+        for _ in range(240):
+            try:
+                with urllib.request.urlopen(f"http://127.0.0.1:{port}/health", timeout=2) as r:
+                    up = r.status == 200
+                    break
+            except Exception:  # noqa: BLE001
+                assert proc.poll() is None, proc.stdout.read()
+                time.sleep(0.5)
+        assert up
+
+        def chat(i, out):
+            body = {"model": "tiny", "messages": [{"role": "user", "content": f"hello {i}"}], "max_tokens": 4, "temperature": 0}
+            req = urllib.request.Request(f"http://127.0.0.1:{port}/v1/chat/completions", data=json.dumps(body).encode(),
+                                         headers={"Content-Type": "application/json"})
+            with urllib.request.urlopen(req, timeout=120) as r:
+                out[i] = json.loads(r.read())
+        out = {}
+        threads = [threading.Thread(target=chat, args=(i, out)) for i in range(4)]
+        for t in threads:
+            t.start()
+        for t in threads:
+            t.join(150)
+        assert len(out) == 4 and all(o["usage"]["completion_tokens"] == 4 for o in out.values())
+        time.sleep(1.0)                                     # the remote replica's metric snapshot is periodic
+        with urllib.request.urlopen(f"http://127.0.0.1:{port}/metrics", timeout=10) as r:
+            metrics = r.read().decode()
+        assert 'num_gpu_blocks="128"' in metrics            # 64 pages on each of the two replicas
+        success = int(float([ln for ln in metrics.splitlines() if ln.startswith("vllm:request_success_total")][0].split()[1]))
+        assert success >= 4
+    finally:
+        proc.terminate()
+        try:
+            proc.wait(timeout=30)
+        except subprocess.TimeoutExpired:
+            proc.kill()
