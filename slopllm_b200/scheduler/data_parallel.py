@@ -41,6 +41,15 @@ class Mailbox:
         seq = int(self.store.add(f"{self.name}/n", 1))
         self.store.set(f"{self.name}/{seq}", pickle.dumps(obj))
 
+    def wait_next(self, timeout_s: float) -> bool:
+        """Block until the next message has been stored, or `timeout_s` has passed (False)."""
+        from datetime import timedelta
+        try:
+            self.store.wait([f"{self.name}/{self._read + 1}"], timedelta(seconds=timeout_s))
+            return True
+        except Exception:  # noqa: BLE001  (the store raises on a wait that ran out)
+            return False
+
     def drain(self) -> List[object]:
         n = int(self.store.add(f"{self.name}/n", 0))
         out = []
@@ -72,6 +81,7 @@ class ReplicaAgent:
         self._done: List[GenerationRequest] = []
         self._flushes: List[tuple] = []
         self._lock = threading.Lock()
+        self._wake = threading.Event()                           # set by the scheduler thread when there is something to report
         self._stop = threading.Event()
         self._thread: Optional[threading.Thread] = None
 
@@ -89,10 +99,12 @@ class ReplicaAgent:
     def _on_token(self, rid: str, tok: int) -> None:
         with self._lock:
             self._pending.setdefault(rid, []).append(int(tok))
+        self._wake.set()
 
     def _on_finish(self, req: GenerationRequest) -> None:
         with self._lock:
             self._done.append(req)
+        self._wake.set()
 
     def _handle(self, msg: dict) -> bool:
         op = msg["op"]
@@ -142,7 +154,8 @@ class ReplicaAgent:
             if time.time() - last_metrics >= self.metrics_every_s:
                 self.outbox.put(self._metrics())
                 last_metrics = time.time()
-            time.sleep(self.poll_s)
+            self._wake.wait(self.poll_s)                         # tokens are reported as they appear, commands within poll_s
+            self._wake.clear()
         self._report()
 
 
@@ -234,7 +247,7 @@ class ReplicaProxy:
             for r in gone:                                       # the client went away: tell the replica once
                 r.cancel_seen = True
                 self.inbox.put({"op": "cancel", "id": r.id})
-            time.sleep(self.poll_s)
+            self.outbox.wait_next(max(self.poll_s, 0.02))        # wakes as soon as the replica stores its next message
 
 
 class DataParallelRouter:
