@@ -22,6 +22,7 @@ from ..config import PAGE_SIZE
 from ..ops import dense as D
 from ..ops import get_ops, recurrent as RC
 from ..parallel.dist import Comm, ParallelContext
+from ..utils.tracing import traced
 from .weights import LinearWeight
 
 
@@ -245,6 +246,7 @@ class DenseModel:
             return None, 1
         return torch.tensor([0, T], dtype=torch.int32, device=st.input_ids.device), T
 
+    @traced(lambda self, i, *a, **k: f"layer{i}.attention")
     def _full_attention(self, i: int, lw: DenseLayer, x, st, cache: DenseCache):
         cfg, ops = self.cfg, self.ops
         T = x.shape[0]
@@ -264,6 +266,7 @@ class DenseModel:
             o = (o.to(torch.float32) * torch.sigmoid(gate.to(torch.float32))).to(o.dtype)
         return ops.linear(o.reshape(T, hl * cfg.head_dim), lw.o_proj, out_f32=True)
 
+    @traced(lambda self, i, *a, **k: f"layer{i}.linear_attention")
     def _linear_attention(self, i: int, lw: DenseLayer, x, st, cache: DenseCache):
         cfg, ops = self.cfg, self.ops
         T = x.shape[0]
@@ -281,6 +284,7 @@ class DenseModel:
         gated = RC.rmsnorm_gated(o.reshape(T * lh, dv), z.reshape(T * lh, dv), lw.gdn_norm, cfg.rms_norm_eps)
         return ops.linear(gated.reshape(T, zdim), lw.out_proj, out_f32=True)
 
+    @traced("mlp")
     def _mlp(self, lw: DenseLayer, y):
         return self.ops.dense_mlp(y, lw)
 

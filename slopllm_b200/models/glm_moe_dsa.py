@@ -21,6 +21,7 @@ import torch
 
 from ..config import GlmMoeDsaConfig, PAGE_SIZE
 from ..parallel.dist import Comm, ParallelContext
+from ..utils.tracing import traced
 from .weights import LayerWeights, ModelWeights
 
 
@@ -124,6 +125,7 @@ class GlmMoeDsaModel:
         return LayerCache(flat(lc.kv), flat(lc.idx) if lc.idx is not None else None), st2
 
     # -- attention -------------------------------------------------------------------------
+    @traced("attention")
     def attention(self, layer: int, lw: LayerWeights, x: torch.Tensor, st: StepState, cache: KVCacheTensors):
         ops, comm, ctx = self.ops, self.comm, self.ctx
         lc = cache.layers[layer]
@@ -160,6 +162,7 @@ class GlmMoeDsaModel:
         return ops.linear(ops.v_expand(o, lw.w_v), lw.o_proj, out_f32=True, sink=comm.partial_sink(x.shape[0]))
 
     # -- MLP ----------------------------------------------------------------------------------
+    @traced("mlp")
     def mlp(self, lw: LayerWeights, y: torch.Tensor, final: bool = False):
         ops, ctx = self.ops, self.ctx
         if lw.experts is not None and ctx.ep and ctx.world > 1:
@@ -209,6 +212,7 @@ class GlmMoeDsaModel:
         return out
 
     # -- stack -----------------------------------------------------------------------------------
+    @traced(lambda self, layer, *a, **k: f"layer{layer}")
     def _layer(self, layer: int, lw: LayerWeights, partial, residual, st, cache, first: bool, last: bool = False):
         ops, comm = self.ops, self.comm
         if first:

@@ -21,6 +21,7 @@ from ..kv.paged import PagedKVCache, Sequence
 from ..models.glm_moe_dsa import GlmMoeDsaModel, KVCacheTensors, StepState
 from ..ops import reference as R
 from ..parallel.dist import ParallelContext
+from ..utils.tracing import traced
 from .graphs import CaptureManager
 
 
@@ -156,6 +157,7 @@ class Engine:
                          cp_world=self.ctx.cp_world, cp_rank=self.ctx.cp_rank, max_kv_len=max_kv_len)
 
     # ---- prefill -------------------------------------------------------------------------------------------
+    @traced("prefill")
     def prefill(self, seqs: Seq[Sequence], prompts: Seq[Seq[int]], chunk_size: int = 8192,
                 want_hidden: bool = False, rows: Optional[Seq[int]] = None, limits: Optional[Seq[int]] = None):
         """Chunked prefill of each prompt's uncached tail (up to `limits[b]` tokens when given:
@@ -249,6 +251,7 @@ class Engine:
                          max_kv_len=max_kv_len)
 
     # ---- plain decode -----------------------------------------------------------------------------------------
+    @traced("decode_step")
     def decode_step(self, seqs: Seq[Sequence], last_tokens: Seq[int], rows: Optional[Seq[int]] = None) -> List[int]:
         """One token per sequence: append `last_tokens`, run the model, return the next tokens
         (greedy, or drawn by the sampling workspace for its `rows`).  Graph-captured per
@@ -325,6 +328,7 @@ class Engine:
         st = self._eager_state(list(last_tokens), positions, list(range(B)), seqs, max_kv_len=max(positions) + 1)
         return self.model.forward_mtp(st, self.cache, torch.cat(list(last_hiddens), 0))
 
+    @traced("mtp_decode_step")
     def mtp_decode_step(self, seqs: Seq[Sequence], last_tokens: Seq[int], seed: torch.Tensor,
                         rows: Optional[Seq[int]] = None):
         """One speculative step with D = self.mtp drafts per sequence.  Greedy rows compare

@@ -7,6 +7,7 @@ Reference: `recordPhase` (`src/generation-scheduler.ts:438-447`), `profilerStart
 """
 from __future__ import annotations
 
+import functools
 import os
 import time
 from collections import defaultdict
@@ -28,6 +29,20 @@ def nvtx_range(name: str) -> Iterator[None]:
             torch.cuda.nvtx.range_pop()
     else:
         yield
+
+
+def traced(label):
+    """Method decorator: an NVTX range around every call while `SLOPLLM_B200_NVTX=1` (otherwise one module attribute
+    test per call).  `label` is the range name, or a function of the call's arguments that returns it."""
+    def deco(fn):
+        @functools.wraps(fn)
+        def wrapper(*a, **k):
+            if not NVTX:
+                return fn(*a, **k)
+            with nvtx_range(label(*a, **k) if callable(label) else label):
+                return fn(*a, **k)
+        return wrapper
+    return deco
 
 
 class PhaseTimers:

@@ -176,3 +176,40 @@ def test_scheduler_thread_refuses_to_step_while_a_peer_is_lost():
         assert c.done.wait(10) and c.finish_reason == "length"
     finally:
         sched.stop()
+
+
+def test_nvtx_ranges_cover_engine_steps_and_layers(monkeypatch):
+    """With the switch on, prefill / decode steps, every layer and its attention / MLP halves run inside named ranges."""
+    from contextlib import contextmanager
+
+    import torch
+    from slopllm_b200.config import GlmMoeDsaConfig
+    from slopllm_b200.models.glm_moe_dsa import GlmMoeDsaModel
+    from slopllm_b200.models.weights import random_model
+    from slopllm_b200.runtime.engine import Engine
+    from slopllm_b200.utils import tracing
+    seen, depth = [], [0]
+
+    @contextmanager
+    def record(name):
+        seen.append((depth[0], name))
+        depth[0] += 1
+        try:
+            yield
+        finally:
+            depth[0] -= 1
+    cfg = GlmMoeDsaConfig.tiny()
+    eng = Engine(cfg, GlmMoeDsaModel(cfg, random_model(cfg, 0)), num_pages=8, max_batch=1, max_seq_len=256, cuda_graph=False)
+    s = eng.kv.new_sequence()
+    prompt = list(range(3, 40))
+    last, _ = eng.prefill([s], [prompt], chunk_size=64)
+    assert not seen                                              # off by default: nothing is recorded
+    monkeypatch.setattr(tracing, "NVTX", True)
+    monkeypatch.setattr(tracing, "nvtx_range", record)
+    eng.decode_step([s], last)
+    names = [n for _, n in seen]
+    assert names[0] == "decode_step" and seen[0][0] == 0
+    for i in range(cfg.num_hidden_layers):
+        at = names.index(f"layer{i}")
+        assert names[at + 1] == "attention" and "mlp" in names[at + 1:at + 4] and seen[at + 1][0] == seen[at][0] + 1
+    assert torch.is_tensor(torch.zeros(1))
