@@ -2,7 +2,7 @@
 
 * `_lib/libslopllm_kernels.so`  - every sm_100a CUDA kernel (`csrc/*.cu`)
 * `_lib/libslopllm_runtime.so`  - host-side C++ runtime (`csrc/runtime/*.cpp`): heap and page
-  allocators, prefix matching, CSF scale codec, mmap reader
+  allocators, prefix matching, checkpoint mappings with multi-threaded strided window copies
 
 Run `python -m slopllm_b200.build_native` (or `__graft_entry__.build()`).
 """

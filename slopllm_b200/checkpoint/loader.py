@@ -28,12 +28,21 @@ class _Reader:
     def has(self, name: str) -> bool:
         return self.src.has(name)
 
-    def dense(self, name: str, rows=None, cols=None, dtype=None) -> torch.Tensor:
+    def _window(self, name: str, rows=None, cols=None) -> torch.Tensor:
+        """This rank's window of a stored tensor as a contiguous host tensor: cut out of the mapping by the C++ runtime
+        (threads, pinned destination for a GPU load) when it can, else a slice of the mapped tensor."""
+        w = self.src.window(name, rows, cols, pin=self.device.type == "cuda") if hasattr(self.src, "window") else None
+        if w is not None:
+            return w
         t = self.src.tensor(name)
         if rows is not None:
             t = t[rows[0]:rows[1]]
         if cols is not None:
             t = t[:, cols[0]:cols[1]]
+        return t
+
+    def dense(self, name: str, rows=None, cols=None, dtype=None) -> torch.Tensor:
+        t = self._window(name, rows, cols)
         dt = self.dtype if dtype is None else dtype
         return t.to(device=self.device, dtype=dt).contiguous()
 
@@ -46,23 +55,14 @@ class _Reader:
             r0, r1 = rows or (0, R)
             c0, c1 = cols or (0, Cn)
             return decode_csf_scales(fixed, exc, R, Cn, r0, r1 - r0, c0, c1 - c0, self.device)
-        t = self.src.tensor(name)
-        if rows is not None:
-            t = t[rows[0]:rows[1]]
-        if cols is not None:
-            t = t[:, cols[0]:cols[1]]
-        return t.contiguous().to(self.device)
+        return self._window(name, rows, cols).contiguous().to(self.device)
 
     def linear(self, prefix: str, rows=None, cols=None) -> LinearWeight:
         """Linear `prefix.weight` (+ NVFP4 aux tensors).  rows / cols are in logical elements."""
         if self.has(prefix + ".weight_scale"):
             pc = None if cols is None else (cols[0] // 2, cols[1] // 2)
             sc = None if cols is None else (cols[0] // 16, cols[1] // 16)
-            w = self.src.tensor(prefix + ".weight")
-            if rows is not None:
-                w = w[rows[0]:rows[1]]
-            if pc is not None:
-                w = w[:, pc[0]:pc[1]]
+            w = self._window(prefix + ".weight", rows, pc)
             g = self.src.tensor(prefix + ".weight_scale_2").to(torch.float32).reshape(()) if self.has(prefix + ".weight_scale_2") \
                 else torch.ones(())
             return LinearWeight(w.contiguous().to(self.device), self.scale(prefix + ".weight_scale", rows, sc), g.to(self.device))

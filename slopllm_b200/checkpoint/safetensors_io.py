@@ -9,6 +9,7 @@ import json
 import mmap
 import os
 import struct
+import threading
 from dataclasses import dataclass
 from typing import Dict, Iterable, List, Optional, Tuple
 
@@ -42,6 +43,8 @@ class TensorMeta:
 
 
 class SafetensorsFile:
+    PIN_MIN_BYTES = 256 << 10
+
     def __init__(self, path: str):
         self.path = path
         self._f = open(path, "rb")
@@ -67,6 +70,8 @@ class SafetensorsFile:
                 raise ValueError(f"{path}: tensor {name} extent {e - b} does not match its shape/dtype ({want} bytes)")
             self.tensors[name] = meta
         self._mm: Optional[mmap.mmap] = None
+        self._native = None               # C++ mapping of the same file, opened on the first window() call
+        self._native_lock = threading.Lock()
 
     def _map(self) -> mmap.mmap:
         if self._mm is None:
@@ -97,7 +102,42 @@ class SafetensorsFile:
         t = torch.from_numpy(raw)
         return t.view(dt).reshape(m.shape) if dt != torch.uint8 else t.reshape(m.shape)
 
+    def window(self, name: str, rows: Optional[Tuple[int, int]] = None, cols: Optional[Tuple[int, int]] = None,
+               pin: bool = False, threads: int = 4) -> Optional[torch.Tensor]:
+        """Contiguous copy of rows [r0, r1) x columns [c0, c1) of a 2-D tensor (1-D: rows only), made by the C++
+        runtime's strided multi-threaded copy straight out of the mapping into a fresh (optionally pinned) host tensor.
+        This is what a tensor-parallel rank uploads.  Returns None when the native runtime is not built or the tensor
+        has another rank; callers then slice `tensor()`."""
+        m = self.tensors[name]
+        if len(m.shape) not in (1, 2) or m.nbytes == 0:
+            return None
+        try:
+            from ..runtime.native_runtime import MappedFile
+            with self._native_lock:                       # loader threads share the file object
+                if self._native is None:
+                    self._native = MappedFile(self.path)
+        except Exception:  # noqa: BLE001  (library not built: the Python mapping serves the read)
+            return None
+        dt, esz = _DTYPES[m.dtype]
+        R = m.shape[0]
+        Cn = m.shape[1] if len(m.shape) == 2 else 1
+        r0, r1 = rows or (0, R)
+        c0, c1 = cols or (0, Cn)
+        if not (0 <= r0 <= r1 <= R and 0 <= c0 <= c1 <= Cn) or (len(m.shape) == 1 and cols is not None):
+            raise IndexError(f"{name}: window rows {rows} cols {cols} outside shape {m.shape}")
+        shape = (r1 - r0, c1 - c0) if len(m.shape) == 2 else (r1 - r0,)
+        nbytes = (r1 - r0) * (c1 - c0) * esz
+        # small windows (norm weights, per-expert scales) are not worth a pinned block
+        out = torch.empty(shape, dtype=dt, pin_memory=pin and nbytes >= self.PIN_MIN_BYTES and torch.cuda.is_available())
+        if out.numel():
+            self._native.copy_rows(self.data_offset + m.begin + (r0 * Cn + c0) * esz, Cn * esz, (c1 - c0) * esz, r1 - r0,
+                                   out.data_ptr(), threads)
+        return out
+
     def close(self) -> None:
+        if self._native is not None:
+            self._native.close()
+            self._native = None
         if self._mm is not None:
             try:
                 self._mm.close()

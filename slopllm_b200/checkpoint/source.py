@@ -50,6 +50,13 @@ class CheckpointSource:
             return self.csf.tensor(name)
         return self._files[self._where[name]].tensor(name)
 
+    def window(self, name: str, rows=None, cols=None, pin: bool = False) -> Optional[torch.Tensor]:
+        """Contiguous host copy of a row / column window of a tensor stored in a plain safetensors shard, made by the C++
+        runtime (`SafetensorsFile.window`); None when the tensor lives in a CSF container or the runtime is not built."""
+        if self.csf is not None or name not in self._where:
+            return None
+        return self._files[self._where[name]].window(name, rows, cols, pin=pin)
+
     def csf_planes(self, name: str) -> Optional[Tuple[np.ndarray, np.ndarray, Tuple[int, int]]]:
         """(fixed, exceptions, (rows, columns)) of a replaced scale tensor, else None."""
         if self.csf is None or not self.csf.is_compressed(name):

@@ -33,6 +33,11 @@ def _lib():
         lib.rt_heap_largest_free.restype = C.c_uint64
         lib.rt_heap_largest_free.argtypes = [C.c_void_p]
         lib.rt_heap_num_free_ranges.argtypes = [C.c_void_p]
+        lib.rt_mmap_open.restype = C.c_void_p
+        lib.rt_mmap_open.argtypes = [C.c_char_p, C.POINTER(C.c_uint64)]
+        lib.rt_mmap_close.argtypes = [C.c_void_p]
+        lib.rt_mmap_advise.argtypes = [C.c_void_p, C.c_uint64, C.c_uint64]
+        lib.rt_mmap_copy_rows.argtypes = [C.c_void_p, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_void_p, C.c_int]
         lib._sl_typed = True
     return lib
 
@@ -101,3 +106,37 @@ class Heap:
     @property
     def num_free_ranges(self) -> int:
         return self._lib.rt_heap_num_free_ranges(self._h)
+
+
+class MappedFile:
+    """Read-only mapping of a checkpoint shard in the C++ runtime (`csrc/runtime/mmap_loader.cpp`): strided windows are
+    copied into a caller-provided buffer (normally pinned host memory) by several threads."""
+
+    def __init__(self, path: str):
+        size = C.c_uint64(0)
+        self._h = _lib().rt_mmap_open(path.encode(), C.byref(size))
+        if not self._h:
+            raise OSError(f"cannot map {path}")
+        self.path, self.size = path, int(size.value)
+
+    def advise(self, offset: int, length: int) -> None:
+        """Start reading a range ahead of its use (MADV_WILLNEED)."""
+        _lib().rt_mmap_advise(self._h, offset, length)
+
+    def copy_rows(self, offset: int, row_stride: int, row_bytes: int, rows: int, dst_ptr: int, threads: int = 4) -> None:
+        """dst[r * row_bytes ...] = file[offset + r * row_stride ...] for r < rows."""
+        rc = _lib().rt_mmap_copy_rows(self._h, offset, row_stride, row_bytes, rows, dst_ptr, threads)
+        if rc != 0:
+            raise ValueError(f"{self.path}: window (offset {offset}, {rows} rows of {row_bytes} bytes every {row_stride}) "
+                             f"is outside the file of {self.size} bytes")
+
+    def close(self) -> None:
+        if self._h:
+            _lib().rt_mmap_close(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:  # noqa: BLE001  (interpreter shutdown)
+            pass

@@ -227,3 +227,37 @@ def test_csf_gpu_decode_matches_cpu_codec():
     with pytest.raises(CsfContractError) as ei:
         check_decode_status("cuda")
     assert "row base" in str(ei.value) and "unsorted" in str(ei.value)
+
+
+def test_native_mmap_windows_match_slices(tmp_path):
+    """The C++ runtime's strided window copy against plain slicing of the mapped tensors, and its bounds checks."""
+    import pytest
+    from slopllm_b200.checkpoint.safetensors_io import SafetensorsFile, save_file
+    from slopllm_b200.runtime.native_runtime import MappedFile
+    a = torch.randn(300, 200).to(torch.bfloat16)
+    b = torch.arange(1000, dtype=torch.int32)
+    c = torch.randint(0, 255, (4096, 1024), dtype=torch.uint8)          # 4 MiB: split over the copy threads
+    path = str(tmp_path / "x.safetensors")
+    save_file({"a": a, "b": b, "c": c, "s": torch.ones(())}, path)
+    f = SafetensorsFile(path)
+    assert torch.equal(f.window("a"), a) and f.window("a").is_contiguous()
+    assert torch.equal(f.window("a", (10, 77), (16, 100)), a[10:77, 16:100])
+    assert torch.equal(f.window("a", cols=(100, 200)), a[:, 100:200])
+    assert torch.equal(f.window("b", (5, 900)), b[5:900])
+    assert torch.equal(f.window("c", (1, 4000), (8, 1000), threads=8), c[1:4000, 8:1000])
+    assert f.window("a", (5, 5)).shape == (0, 200)
+    assert f.window("s") is None                                         # 0-d: the caller reads tensor()
+    with pytest.raises(IndexError):
+        f.window("a", (0, 301))
+    f.close()
+    m = MappedFile(path)
+    buf = torch.empty(64, dtype=torch.uint8)
+    with pytest.raises(ValueError):
+        m.copy_rows(m.size - 32, 64, 64, 1, buf.data_ptr())              # runs past the end of the file
+    with pytest.raises(ValueError):
+        m.copy_rows(0, 8, 16, 4, buf.data_ptr())                         # rows would overlap
+    m.copy_rows(m.size - 64, 64, 64, 1, buf.data_ptr())
+    m.advise(0, m.size)
+    m.close()
+    with pytest.raises(OSError):
+        MappedFile(str(tmp_path / "missing.safetensors"))
