@@ -16,6 +16,9 @@ import time
 from .model_cli import add_model_args, build_runtime
 
 
+BUILTIN_SAMPLING = {"temperature": 0.6, "top_p": 0.95, "top_k": 20, "repetition_penalty": 1.0, "max_tokens": 65536}
+
+
 def parse_args(argv=None):
     ap = argparse.ArgumentParser(prog="slopllm_b200.cli.serve", description=__doc__.split("\n")[0])
     add_model_args(ap)
@@ -29,11 +32,12 @@ def parse_args(argv=None):
     ap.add_argument("--health-timeout", type=float, default=10.0, help="seconds without a heartbeat after which a rank counts as lost")
     ap.add_argument("--dp-port", type=int, default=29640, help="port of the store that carries requests to the other replicas (--dp)")
     # sampling defaults applied when a request does not set them (reference `src/openai-server.ts:51-103`)
-    ap.add_argument("--max-tokens", type=int, default=65536)
-    ap.add_argument("--temperature", type=float, default=0.6)
-    ap.add_argument("--top-p", type=float, default=0.95)
-    ap.add_argument("--top-k", type=int, default=20)
-    ap.add_argument("--repetition-penalty", type=float, default=1.0)
+    # not given: the checkpoint's generation_config.json / config.json value, else 65536 / 0.6 / 0.95 / 20 / 1.0
+    ap.add_argument("--max-tokens", type=int, default=None)
+    ap.add_argument("--temperature", type=float, default=None)
+    ap.add_argument("--top-p", type=float, default=None)
+    ap.add_argument("--top-k", type=int, default=None)
+    ap.add_argument("--repetition-penalty", type=float, default=None)
     ap.add_argument("--presence-penalty", type=float, default=0.0)
     ap.add_argument("--repetition-penalty-window", type=int, default=64)
     ap.add_argument("--decode-latency", type=float, default=0.0, help="minimum milliseconds per decode step (rate limit)")
@@ -67,6 +71,12 @@ def main(argv=None) -> int:
         args.mtp = 0
     rt = build_runtime(args)
     from ..config import SamplingParams
+    from ..utils.generation_config import apply_generation_defaults
+    from ..utils.model_path import resolve_model_path
+    origin = apply_generation_defaults(args, resolve_model_path(args.model) if args.model else None, BUILTIN_SAMPLING)
+    if any(v == "checkpoint" for v in origin.values()) and rt.ctx.rank == 0 and rt.ctx.dp_rank == 0:
+        print("sampling defaults from the checkpoint: " + ", ".join(f"{k}={getattr(args, k)}" for k, v in origin.items()
+                                                                    if v == "checkpoint"), file=sys.stderr)
     rt.engine_cfg.max_tokens = args.max_tokens
     rt.engine_cfg.phased_prefill = args.phased_prefill
     rt.engine_cfg.decode_latency_ms = args.decode_latency

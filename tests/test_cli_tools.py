@@ -212,3 +212,30 @@ def test_fused_switch_selects_library_collectives(monkeypatch):
     assert type(F.make_comm(ctx, fused=False)) is Comm
     monkeypatch.setenv("SLOPLLM_B200_FUSED", "0")
     assert type(F.make_comm(ctx)) is Comm and len(made) == 1
+
+
+def test_generation_defaults_from_the_checkpoint(tmp_path):
+    """Flags win, then generation_config.json, then config.json, then the built-in values."""
+    import json
+    from types import SimpleNamespace
+    from slopllm_b200.cli.serve import BUILTIN_SAMPLING, parse_args
+    from slopllm_b200.utils.generation_config import (apply_generation_defaults, load_generation_defaults,
+                                                      max_position_embeddings)
+    (tmp_path / "config.json").write_text(json.dumps({"temperature": 0.9, "top_k": 50, "max_position_embeddings": 202752,
+                                                      "repetition_penalty": None}))
+    (tmp_path / "generation_config.json").write_text(json.dumps({"temperature": 1.0, "top_p": 0.8, "do_sample": True}))
+    d = load_generation_defaults(str(tmp_path))
+    assert d == {"temperature": 1.0, "top_p": 0.8, "top_k": 50}
+    assert max_position_embeddings(str(tmp_path)) == 202752 and max_position_embeddings(None) is None
+    (tmp_path / "mm").mkdir()
+    (tmp_path / "mm" / "config.json").write_text(json.dumps({"text_config": {"max_position_embeddings": 4096}}))
+    assert max_position_embeddings(str(tmp_path / "mm")) == 4096
+    args = parse_args(["--random-init", "tiny", "--top-p", "0.5"])
+    assert args.temperature is None and args.top_p == 0.5
+    origin = apply_generation_defaults(args, str(tmp_path), BUILTIN_SAMPLING)
+    assert (args.temperature, args.top_p, args.top_k, args.repetition_penalty, args.max_tokens) == (1.0, 0.5, 50, 1.0, 65536)
+    assert origin == {"temperature": "checkpoint", "top_p": "flag", "top_k": "checkpoint", "repetition_penalty": "default",
+                      "max_tokens": "default"}
+    bare = SimpleNamespace(temperature=None, top_p=None, top_k=None, repetition_penalty=None, max_tokens=None)
+    apply_generation_defaults(bare, None, BUILTIN_SAMPLING)
+    assert (bare.temperature, bare.top_p, bare.top_k) == (0.6, 0.95, 20)
