@@ -31,14 +31,17 @@ CORS = {"Access-Control-Allow-Origin": "*", "Access-Control-Allow-Headers": "aut
 
 
 class HttpError(Exception):
-    def __init__(self, status: int, message: str, etype: str = "invalid_request_error", param: Optional[str] = None):
+    def __init__(self, status: int, message: str, etype: str = "invalid_request_error", param: Optional[str] = None,
+                 code: Optional[str] = None):
         super().__init__(message)
-        self.status, self.message, self.etype, self.param = status, message, etype, param
+        self.status, self.message, self.etype, self.param, self.code = status, message, etype, param, code
 
     def body(self) -> dict:
         err = {"message": self.message, "type": self.etype}
         if self.param:
             err["param"] = self.param
+        if self.code:
+            err["code"] = self.code
         return {"error": err}
 
 
@@ -78,6 +81,32 @@ def render_metrics(m, pending: int, kv, batch_size: int, chunk_size: int, max_mo
         lab = f'{{phase="{phase}",batch_size="{b}"}}'
         lines += [f"glm:phase_seconds_total{lab} {sec}", f"glm:phase_count_total{lab} {m.phase_count.get(key, 0)}"]
     return "\n".join(lines) + "\n"
+
+
+def normalize_messages(messages: List[dict]) -> List[dict]:
+    """What the chat template expects: `content` is never null, and the `arguments` of an assistant message's tool calls
+    are objects (clients send them as JSON strings).  Reference: `normalizeMessages` (`src/openai-server.ts:174-194`)."""
+    out = []
+    for m in messages:
+        m = dict(m)
+        if m.get("content") is None:
+            m["content"] = ""
+        calls = m.get("tool_calls")
+        if calls:
+            fixed = []
+            for c in calls:
+                c = dict(c)
+                fn = dict(c.get("function") or {})
+                if isinstance(fn.get("arguments"), str):
+                    try:
+                        fn["arguments"] = json.loads(fn["arguments"])
+                    except ValueError:
+                        raise HttpError(400, "tool call arguments must contain valid JSON", param="messages")
+                c["function"] = fn
+                fixed.append(c)
+            m["tool_calls"] = fixed
+        out.append(m)
+    return out
 
 
 class OpenAIServer:
@@ -140,7 +169,7 @@ class OpenAIServer:
         if admin and not key:
             raise HttpError(403, "admin endpoints need --admin-api-key", "permission_error")
         if key and headers.get("authorization", "") != f"Bearer {key}":
-            raise HttpError(401, "invalid API key", "authentication_error")
+            raise HttpError(401, "invalid or missing API key", "authentication_error", param="Authorization", code="invalid_api_key")
 
     async def _route(self, method, path, headers, body, writer) -> None:
         try:
@@ -233,10 +262,27 @@ class OpenAIServer:
 
     # ---- chat completions ------------------------------------------------------------------------------------------
     async def _chat(self, params: dict, writer) -> None:
+        if not isinstance(params, dict):
+            raise HttpError(400, "the request body must be a JSON object")
+        if params.get("model") is not None and params["model"] != self.model_name:
+            raise HttpError(404, f"The model '{params['model']}' does not exist", param="model", code="model_not_found")
         messages = params.get("messages")
-        if not isinstance(messages, list) or not messages:
-            raise HttpError(400, "messages must be a non-empty array", param="messages")
+        if not isinstance(messages, list) or not messages or not all(isinstance(m, dict) for m in messages):
+            raise HttpError(400, "messages must be a non-empty array of objects", param="messages")
+        params = dict(params, messages=normalize_messages(messages))
+        messages = params["messages"]
+        if params.get("tools") is not None and not isinstance(params["tools"], list):
+            raise HttpError(400, "tools must be an array", param="tools")
+        if params.get("chat_template_kwargs") is not None and not isinstance(params["chat_template_kwargs"], dict):
+            raise HttpError(400, "chat_template_kwargs must be an object", param="chat_template_kwargs")
         kwargs = dict(params.get("chat_template_kwargs") or {})
+        # top-level spellings of the two template switches (the request field wins over chat_template_kwargs)
+        if params.get("continue_final_message") is not None:
+            kwargs["continue_final_message"] = bool(params["continue_final_message"])
+        if params.get("enable_thinking") is not None:
+            if not isinstance(params["enable_thinking"], bool):
+                raise HttpError(400, "enable_thinking must be a boolean", param="enable_thinking")
+            kwargs["enable_thinking"] = params["enable_thinking"]
         effort = params.get("reasoning_effort") or env_str("REASONING_EFFORT")      # request field, else the server default
         if effort:
             kwargs.setdefault("reasoning_effort", effort)

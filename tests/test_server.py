@@ -132,6 +132,24 @@ def test_server_endpoints():
         assert st == 200 and "gpu_pages_freed" in json.loads(body)
         st, body = await _http(port, "POST", "/v1/chat/completions", {"messages": []}, auth)
         assert st == 400
+        # request validation: unknown model, malformed tools / template kwargs / switches, tool-call arguments
+        user = [{"role": "user", "content": "x"}]
+        st, body = await _http(port, "POST", "/v1/chat/completions", {"model": "other", "messages": user}, auth)
+        assert st == 404 and json.loads(body)["error"]["code"] == "model_not_found"
+        for bad in ({"tools": {"a": 1}}, {"chat_template_kwargs": [1]}, {"enable_thinking": "yes"}):
+            st, body = await _http(port, "POST", "/v1/chat/completions", {"messages": user, **bad}, auth)
+            assert st == 400, bad
+        call = {"role": "assistant", "content": None, "tool_calls": [{"id": "c1", "type": "function",
+                                                                       "function": {"name": "f", "arguments": "{not json"}}]}
+        st, body = await _http(port, "POST", "/v1/chat/completions", {"messages": user + [call]}, auth)
+        assert st == 400 and "valid JSON" in json.loads(body)["error"]["message"]
+        call["tool_calls"][0]["function"]["arguments"] = '{"a": 1}'
+        st, body = await _http(port, "POST", "/v1/chat/completions",
+                               {"model": "test-model", "messages": user + [call, {"role": "tool", "content": "2"}],
+                                "enable_thinking": False, "max_tokens": 4, "temperature": 0}, auth)
+        assert st == 200
+        st, body = await _http(port, "GET", "/v1/models", headers={"Authorization": "Bearer nope"})
+        assert st == 401 and json.loads(body)["error"]["code"] == "invalid_api_key"
         st, body = await _http(port, "POST", "/v1/chat/completions", {"messages": [{"role": "user", "content": "x"}], "top_p": "a"}, auth)
         assert st == 400
         await srv.close()
