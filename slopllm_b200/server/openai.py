@@ -303,7 +303,9 @@ class OpenAIServer:
         max_tokens = params.get("max_tokens") or params.get("max_completion_tokens") or self.cfg.max_tokens
         max_tokens = max(1, min(int(max_tokens), self.max_model_len - len(ids)))
         stream = params.get("stream") is True
-        include_usage = bool((params.get("stream_options") or {}).get("include_usage"))
+        stream_options = params.get("stream_options") if isinstance(params.get("stream_options"), dict) else {}
+        include_usage = bool(stream_options.get("include_usage"))
+        continuous_usage = stream_options.get("continuous_usage_stats") is True      # usage in every streamed chunk
 
         loop = asyncio.get_running_loop()
         q: asyncio.Queue = asyncio.Queue()
@@ -328,9 +330,16 @@ class OpenAIServer:
         def chunk(delta: dict, finish=None, usage=None) -> bytes:
             obj = {"id": req.id, "object": "chat.completion.chunk", "created": created, "model": self.model_name,
                    "choices": [{"index": 0, "delta": delta, "finish_reason": finish}]}
+            if usage is None and continuous_usage:
+                usage = stream_usage()
             if usage is not None:
                 obj["usage"] = usage
             return b"data: " + json.dumps(obj).encode() + b"\n\n"
+
+        def stream_usage() -> dict:
+            n = len(req.generated)
+            return {"prompt_tokens": req.prompt_tokens or len(ids), "completion_tokens": n,
+                    "total_tokens": (req.prompt_tokens or len(ids)) + n}
 
         def usage_obj() -> dict:
             return {"prompt_tokens": req.prompt_tokens, "completion_tokens": len(req.generated),
@@ -366,9 +375,10 @@ class OpenAIServer:
 
         try:
             if stream:
-                hdr = {"Content-Type": "text/event-stream", "Cache-Control": "no-cache", "Connection": "close", **CORS}
+                hdr = {"Content-Type": "text/event-stream", "Cache-Control": "no-cache", "Connection": "close",
+                       "X-Accel-Buffering": "no", **CORS}             # reverse proxies must not buffer the event stream
                 writer.write(("HTTP/1.1 200 OK\r\n" + "".join(f"{k}: {v}\r\n" for k, v in hdr.items()) + "\r\n").encode())
-                writer.write(chunk({"role": "assistant"}))
+                writer.write(chunk({"role": "assistant", "content": ""}))
             final: Optional[GenerationRequest] = None
             while final is None:
                 kind, val = await q.get()
@@ -387,6 +397,11 @@ class OpenAIServer:
                 if stream:
                     for d in deltas:
                         writer.write(chunk(d))
+                    if continuous_usage and not deltas and kind != "end":
+                        # a token that produced no visible text (inside a tool call, a held-back stop prefix) still counts
+                        obj = {"id": req.id, "object": "chat.completion.chunk", "created": created, "model": self.model_name,
+                               "choices": [], "usage": stream_usage()}
+                        writer.write(b"data: " + json.dumps(obj).encode() + b"\n\n")
                     try:
                         await writer.drain()
                     except ConnectionError:

@@ -121,10 +121,20 @@ def test_server_endpoints():
         assert text == "Hi there " and body.decode().rstrip().endswith("data: [DONE]")
         assert [c for c in chunks if c["choices"] and c["choices"][0]["finish_reason"]][0]["choices"][0]["finish_reason"] == "stop"
         assert any("usage" in c and not c["choices"] for c in chunks)
+        assert chunks[0]["choices"][0]["delta"] == {"role": "assistant", "content": ""} and "usage" not in chunks[0]
+        # usage in every chunk on request
+        st, body = await _http(port, "POST", "/v1/chat/completions",
+                               {"messages": [{"role": "user", "content": "hi"}], "stream": True, "max_tokens": 6,
+                                "stream_options": {"continuous_usage_stats": True}}, auth)
+        cont = [json.loads(l[6:]) for l in body.decode().split("\n\n") if l.startswith("data: {")]
+        assert all("usage" in c for c in cont) and cont[-1]["usage"]["completion_tokens"] == 6
+        counts = [c["usage"]["completion_tokens"] for c in cont]
+        assert counts == sorted(counts) and cont[0]["usage"]["total_tokens"] == cont[0]["usage"]["prompt_tokens"]
         # second identical prompt is served from the prefix cache? (prompt shorter than a page: no) - metrics still count
         st, body = await _http(port, "GET", "/metrics")
         m = body.decode()
-        assert "vllm:generation_tokens_total" in m and "vllm:request_success_total 1" in m or "vllm:request_success_total 2" in m
+        assert "vllm:generation_tokens_total" in m
+        assert any(f"vllm:request_success_total {n}" in m for n in (2, 3))         # the stop-string request retires as cancelled
         assert 'vllm:cache_config_info{block_size="64"' in m
         st, body = await _http(port, "POST", "/admin/flush_gpu_cache", {}, auth)
         assert st == 401
