@@ -119,7 +119,8 @@ def main(argv=None) -> int:
         print(f"warm-up took {warm_up(rt, remote=proxies):.1f} s", file=sys.stderr)
     name = args.served_model_name or (args.model.rstrip("/").split("/")[-1] if args.model else args.random_init)
     server = OpenAIServer(front, rt.tokenizer, rt.engine_cfg, model_name=name, max_model_len=args.max_model_len,
-                          healthy=(monitor.is_healthy if monitor is not None else (lambda: True)))
+                          healthy=(monitor.is_healthy if monitor is not None else (lambda: True)),
+                          log=lambda line: print(line, file=sys.stderr, flush=True))
     print(f"listening on http://{args.host}:{args.port}  model={name}  ranks={ctx.global_world or ctx.world}  "
           f"replicas={ctx.dp_world}  mtp={args.mtp}", file=sys.stderr)
     try:

@@ -111,13 +111,14 @@ def normalize_messages(messages: List[dict]) -> List[dict]:
 
 class OpenAIServer:
     def __init__(self, scheduler: GenerationScheduler, tokenizer, cfg: EngineConfig, model_name: str = "glm",
-                 max_model_len: int = 65536, healthy=lambda: True):
+                 max_model_len: int = 65536, healthy=lambda: True, log=None):
         self.sched = scheduler
         self.tok = tokenizer
         self.cfg = cfg
         self.model_name = model_name
         self.max_model_len = max_model_len
         self.healthy = healthy
+        self.log = log                    # callable(str) for the per-request performance line, or None
         self.control = resolve_control_tokens(tokenizer)
         self.pending = 0
         self._server: Optional[asyncio.AbstractServer] = None
@@ -260,6 +261,19 @@ class OpenAIServer:
                                                  **{k: v for k, v in kwargs.items() if k != "continue_final_message"}))
         return GlmParser(lambda ids: self.tok.decode(list(ids)), self.control, think)
 
+    def _log_request(self, req: GenerationRequest) -> None:
+        """One line per finished request: prompt / cached / prefilled tokens, prefill and decode rates (the reference's
+        `logRequestPerformance`, `src/openai-server.ts:242-256`).  `log=None` at construction silences it."""
+        if self.log is None:
+            return
+        decoded = max(0, len(req.generated) - 1)
+        decode_s = (time.time() - req.first_token_at) if req.first_token_at else 0.0
+        prefill_tps = req.prefill_tokens / req.prefill_seconds if req.prefill_seconds > 0 else 0.0
+        decode_tps = decoded / decode_s if decode_s > 0 else 0.0
+        self.log(f"Request {req.id}: prompt_tokens={req.prompt_tokens} cached_tokens={req.cached_tokens} "
+                 f"prefill_tokens={req.prefill_tokens} prefill_tokens_per_second={prefill_tps:.1f} "
+                 f"output_tokens={len(req.generated)} decode_tokens_per_second={decode_tps:.1f} finish={req.finish_reason}")
+
     # ---- chat completions ------------------------------------------------------------------------------------------
     async def _chat(self, params: dict, writer) -> None:
         if not isinstance(params, dict):
@@ -315,7 +329,7 @@ class OpenAIServer:
         created = int(time.time())
         self.pending += 1
         self.sched.submit(req)
-        state = {"content": "", "sent": 0, "reasoning": "", "tools": [], "stopped": False}
+        state = {"content": "", "sent": 0, "reasoning": "", "tools": [], "stopped": False, "ntok": 0}
 
         def held_back(text: str) -> int:
             """Length of the longest tail of `text` that could still grow into a stop string."""
@@ -337,7 +351,7 @@ class OpenAIServer:
             return b"data: " + json.dumps(obj).encode() + b"\n\n"
 
         def stream_usage() -> dict:
-            n = len(req.generated)
+            n = state["ntok"]                              # tokens delivered to this response so far
             return {"prompt_tokens": req.prompt_tokens or len(ids), "completion_tokens": n,
                     "total_tokens": (req.prompt_tokens or len(ids)) + n}
 
@@ -386,6 +400,7 @@ class OpenAIServer:
                     final = val
                     events = parser.finish() if not state["stopped"] else []
                 else:
+                    state["ntok"] += 1
                     events = parser.on_token(val) if not state["stopped"] else []
                 deltas = apply(events)
                 if kind == "end" and not state["stopped"] and state["sent"] < len(state["content"]):
@@ -407,6 +422,7 @@ class OpenAIServer:
                     except ConnectionError:
                         req.cancel()                      # client went away
                         return
+            self._log_request(req)
             if final.error and not state["stopped"]:
                 raise HttpError(500, final.error, "server_error")
             finish = "tool_calls" if parser.produced_tool_calls else ("stop" if state["stopped"] else final.finish_reason or "stop")

@@ -92,7 +92,8 @@ def test_server_endpoints():
     sched.start()
 
     async def run():
-        srv = OpenAIServer(sched, tok, cfg, model_name="test-model", max_model_len=4096)
+        lines = []
+        srv = OpenAIServer(sched, tok, cfg, model_name="test-model", max_model_len=4096, log=lines.append)
         await srv.start()
         port = srv.port
         auth = {"Authorization": "Bearer k"}
@@ -162,6 +163,7 @@ def test_server_endpoints():
         assert st == 401 and json.loads(body)["error"]["code"] == "invalid_api_key"
         st, body = await _http(port, "POST", "/v1/chat/completions", {"messages": [{"role": "user", "content": "x"}], "top_p": "a"}, auth)
         assert st == 400
+        assert len(lines) >= 3 and all("decode_tokens_per_second=" in ln and "prompt_tokens=" in ln for ln in lines)
         await srv.close()
 
     asyncio.run(run())
