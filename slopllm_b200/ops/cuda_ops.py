@@ -243,7 +243,13 @@ class CudaOps:
         N.call("sl_q_post_absorb", C.byref(p), q_abs.data_ptr(), lw.w_kn.data_ptr(), T, c.kv_lora_rank, N.stream())
         return q_abs, q_pe, q8, w_eff
 
+    IDX_SCORE_BUDGET = 2 << 30     # bytes of the transient fp32 score matrix [rows, keys]; more query rows go in blocks
+
     def indexer_topk(self, q8, w_eff, layer_cache, st):
+        """Scores of every query token against its sequence's indexer keys, then the top-k positions.  The score matrix is
+        sized by the longest sequence of the step, not by the cache capacity, and a prefill chunk against a very long
+        context is scored in blocks of query rows so that the matrix stays within `IDX_SCORE_BUDGET` (reference: the
+        sizing rules checked by `tests/test_indexer_sizing.ts`)."""
         c = self.cfg
         T = q8.shape[0]
         dev = q8.device
@@ -252,30 +258,45 @@ class CudaOps:
         pos = torch.empty(T, c.index_topk, dtype=torch.int32, device=dev)
         score = torch.empty(T, c.index_topk, dtype=torch.float32, device=dev)
         ld = max(8, (max_local + 7) // 8 * 8)
+        rows_per = self.score_rows_per_block(T, ld)
         scores = st.extra.get("idx_scores")
-        if scores is None or scores.shape[0] < T or scores.shape[1] < ld:
-            scores = torch.empty(T, ld, dtype=torch.float32, device=dev)
+        if scores is None or scores.shape[0] < rows_per or scores.shape[1] < ld:
+            scores = torch.empty(rows_per, ld, dtype=torch.float32, device=dev)
             st.extra["idx_scores"] = scores
-        if st.max_kv_len > c.index_topk:
-            sp = N.IndexerScoreParams(
-                q8=q8.data_ptr(), w_eff=w_eff.data_ptr(), idx_cache=layer_cache.idx.data_ptr(),
-                page_table=st.page_table.data_ptr(), pt_stride=st.page_table.stride(0), batch_idx=st.batch_idx.data_ptr(),
-                positions=st.positions.data_ptr(), Hi=c.index_n_heads, D=c.index_head_dim, page_size=st.page_size,
-                cp_world=W, cp_rank=r, top_k=c.index_topk, scores=scores.data_ptr(), ld_scores=scores.stride(0),
-                num_slots=layer_cache.idx.shape[0], guard=self._guard(dev))
-            N.call("sl_indexer_scores", C.byref(sp), T, max_local, N.stream())
-        tp = N.TopkSelectParams(scores=scores.data_ptr(), ld_scores=scores.stride(0), positions=st.positions.data_ptr(),
-                                top_k=c.index_topk, cp_world=W, cp_rank=r, out_pos=pos.data_ptr(), out_score=score.data_ptr())
+        slots = lengths = None
         if W == 1:
             # without context parallelism the selected positions are final: look the slots up in the same kernel
             slots = torch.empty(T, c.index_topk, dtype=torch.int32, device=dev)
             lengths = torch.empty(T, dtype=torch.int32, device=dev)
-            tp.slots, tp.lengths = slots.data_ptr(), lengths.data_ptr()
-            tp.page_table, tp.batch_idx = st.page_table.data_ptr(), st.batch_idx.data_ptr()
-            tp.pt_stride, tp.page_size = st.page_table.stride(0), st.page_size
             st.extra["fused_slots"] = (pos, slots, lengths)
-        N.call("sl_topk_select", C.byref(tp), T, N.stream())
+        for t0 in range(0, T, rows_per):
+            t1 = min(T, t0 + rows_per)
+            n = t1 - t0
+            positions, batch_idx = st.positions[t0:t1], st.batch_idx[t0:t1]
+            if st.max_kv_len > c.index_topk:
+                sp = N.IndexerScoreParams(
+                    q8=q8[t0:t1].data_ptr(), w_eff=w_eff[t0:t1].data_ptr(), idx_cache=layer_cache.idx.data_ptr(),
+                    page_table=st.page_table.data_ptr(), pt_stride=st.page_table.stride(0), batch_idx=batch_idx.data_ptr(),
+                    positions=positions.data_ptr(), Hi=c.index_n_heads, D=c.index_head_dim, page_size=st.page_size,
+                    cp_world=W, cp_rank=r, top_k=c.index_topk, scores=scores.data_ptr(), ld_scores=scores.stride(0),
+                    num_slots=layer_cache.idx.shape[0], guard=self._guard(dev))
+                N.call("sl_indexer_scores", C.byref(sp), n, max_local, N.stream())
+            tp = N.TopkSelectParams(scores=scores.data_ptr(), ld_scores=scores.stride(0), positions=positions.data_ptr(),
+                                    top_k=c.index_topk, cp_world=W, cp_rank=r, out_pos=pos[t0:t1].data_ptr(),
+                                    out_score=score[t0:t1].data_ptr())
+            if W == 1:
+                tp.slots, tp.lengths = slots[t0:t1].data_ptr(), lengths[t0:t1].data_ptr()
+                tp.page_table, tp.batch_idx = st.page_table.data_ptr(), batch_idx.data_ptr()
+                tp.pt_stride, tp.page_size = st.page_table.stride(0), st.page_size
+            N.call("sl_topk_select", C.byref(tp), n, N.stream())
         return pos, score
+
+    @classmethod
+    def score_rows_per_block(cls, T: int, ld: int) -> int:
+        """Query rows scored per launch: all of them while [T, ld] fp32 fits the budget, else a multiple of 8 rows."""
+        if T * ld * 4 <= cls.IDX_SCORE_BUDGET:
+            return max(1, T)
+        return max(8, cls.IDX_SCORE_BUDGET // (ld * 4) // 8 * 8)
 
     def topk_select_plain(self, scores: torch.Tensor, k: int) -> torch.Tensor:
         """Indices of the k largest entries of each row (ascending index order, ties to the lower index, -1 padded

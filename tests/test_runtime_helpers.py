@@ -192,3 +192,16 @@ def test_symmetric_region_guard_zones_detect_overruns():
         rg.check_canaries()
     rg.write_canaries()
     rg.check_canaries()
+
+
+def test_indexer_score_matrix_is_sized_by_context_and_blocked_by_budget():
+    """Rows of queries scored per launch: the whole step while [T, keys] fp32 fits the budget (every decode step, every
+    prefill chunk at ordinary context), blocks of a multiple of 8 rows beyond it (reference `tests/test_indexer_sizing.ts`:
+    the score matrix must not be sized by the cache capacity)."""
+    from slopllm_b200.ops.cuda_ops import CudaOps
+    budget = CudaOps.IDX_SCORE_BUDGET
+    assert CudaOps.score_rows_per_block(8, 4096) == 8
+    assert CudaOps.score_rows_per_block(8192, 16384) == 8192                 # 128K context over 8 CP ranks
+    rows = CudaOps.score_rows_per_block(8192, 1 << 20)                       # 1M keys on one rank
+    assert rows % 8 == 0 and 8 <= rows < 8192 and rows * (1 << 20) * 4 <= budget
+    assert CudaOps.score_rows_per_block(8192, 1 << 28) == 8                  # never below one 8-row tile
