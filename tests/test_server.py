@@ -168,3 +168,86 @@ def test_server_endpoints():
 
     asyncio.run(run())
     sched.stop()
+
+
+# Model outputs in the GLM protocol, one per shape of response the parser has to take apart (the reference keeps captured
+# outputs of the same shapes in `tests/glm_parser_corpus.ts`; these are written for this test).  The opening <think> belongs
+# to the prompt, so every output starts inside the reasoning block.
+PARSER_CORPUS = [
+    {"name": "plain response",
+     "output": "The user asks for one word.\n\n1. Output: DONE\n2. Nothing else.</think>DONE",
+     "reasoning": "The user asks for one word.\n\n1. Output: DONE\n2. Nothing else.", "content": "DONE", "calls": []},
+    {"name": "content followed by a string argument tool call",
+     "output": "Need the forecast for Oslo.</think>Let me look that up.<tool_call>get_weather<arg_key>city</arg_key>"
+               "<arg_value>Oslo</arg_value></tool_call>",
+     "reasoning": "Need the forecast for Oslo.", "content": "Let me look that up.",
+     "calls": [("get_weather", {"city": "Oslo"})]},
+    {"name": "mixed scalar and array arguments",
+     "output": "Timer: 25 minutes, weekdays only, loud.</think>Setting it.<tool_call>set_timer<arg_key>label</arg_key>"
+               "<arg_value>focus</arg_value><arg_key>minutes</arg_key><arg_value>25</arg_value><arg_key>days</arg_key>"
+               "<arg_value>[\"Mon\", \"Tue\", \"Wed\"]</arg_value><arg_key>volume</arg_key><arg_value>0.8</arg_value>"
+               "<arg_key>repeat</arg_key><arg_value>true</arg_value><arg_key>note</arg_key><arg_value>null</arg_value></tool_call>",
+     "reasoning": "Timer: 25 minutes, weekdays only, loud.", "content": "Setting it.",
+     "calls": [("set_timer", {"label": "focus", "minutes": 25, "days": ["Mon", "Tue", "Wed"], "volume": 0.8, "repeat": True,
+                              "note": None})]},
+    {"name": "array arguments without visible content",
+     "output": "Search both topics.</think><tool_call>search<arg_key>topics</arg_key><arg_value>[\"tcgen05\", \"TMEM\"]"
+               "</arg_value><arg_key>limit</arg_key><arg_value>5</arg_value></tool_call>",
+     "reasoning": "Search both topics.", "content": "", "calls": [("search", {"topics": ["tcgen05", "TMEM"], "limit": 5})]},
+    {"name": "adjacent tool calls",
+     "output": "Two cities.</think><tool_call>get_weather<arg_key>city</arg_key><arg_value>Oslo</arg_value></tool_call>"
+               "<tool_call>get_weather<arg_key>city</arg_key><arg_value>Lima</arg_value></tool_call>",
+     "reasoning": "Two cities.", "content": "", "calls": [("get_weather", {"city": "Oslo"}), ("get_weather", {"city": "Lima"})]},
+    {"name": "tool without arguments",
+     "output": "Just ask the clock.</think><tool_call>get_time</tool_call>",
+     "reasoning": "Just ask the clock.", "content": "", "calls": [("get_time", {})]},
+    {"name": "nested object argument with newlines around the markers",
+     "output": "Submit the job:\n- name: \"nightly\"\n- retries: 2</think>Submitting.<tool_call>submit_job\n<arg_key>spec</arg_key>\n"
+               "<arg_value>{\"name\": \"nightly\", \"retry\": {\"max\": 2, \"backoff\": [1, 5]}, \"tags\": []}</arg_value>\n</tool_call>",
+     "reasoning": "Submit the job:\n- name: \"nightly\"\n- retries: 2", "content": "Submitting.",
+     "calls": [("submit_job", {"spec": {"name": "nightly", "retry": {"max": 2, "backoff": [1, 5]}, "tags": []}})]},
+    {"name": "multi-byte text split across tokens",
+     "output": "Grüße – 日本語 ✓</think>Ça marche: “naïve” café 🚀<tool_call>say<arg_key>text</arg_key><arg_value>héllo wörld</arg_value></tool_call>",
+     "reasoning": "Grüße – 日本語 ✓", "content": "Ça marche: “naïve” café 🚀", "calls": [("say", {"text": "héllo wörld"})]},
+]
+
+
+def test_glm_parser_corpus_token_by_token():
+    """Every corpus entry, fed one token at a time (byte tokens: multi-byte characters arrive in pieces), comes apart into
+    exactly its reasoning text, its visible content and its tool calls, with no parse error."""
+    tok = ByteTokenizer()
+    ctl = resolve_control_tokens(tok)
+    for entry in PARSER_CORPUS:
+        p = GlmParser(lambda ids: tok.decode(list(ids)), ctl, starts_in_reasoning=True)
+        events = []
+        for t in tok.encode(entry["output"]):
+            events += p.on_token(t)
+        events += p.finish()
+        assert not [e for e in events if e.type == "parse_error"], entry["name"]
+        assert "".join(e.text for e in events if e.type == "reasoning_delta") == entry["reasoning"], entry["name"]
+        assert "".join(e.text for e in events if e.type == "content_delta") == entry["content"], entry["name"]
+        calls = [(e.name, json.loads(e.arguments)) for e in events if e.type == "tool_call"]
+        assert calls == entry["calls"], entry["name"]
+        assert [e.index for e in events if e.type == "tool_call"] == list(range(len(calls))), entry["name"]
+        assert p.produced_tool_calls == bool(calls)
+
+
+def test_glm_parser_truncated_tool_call_and_content_mode():
+    tok = ByteTokenizer()
+    ctl = resolve_control_tokens(tok)
+    # generation ends inside a tool call: reported, not silently dropped
+    p = GlmParser(lambda ids: tok.decode(list(ids)), ctl, starts_in_reasoning=True)
+    events = []
+    for t in tok.encode("ok</think>Calling.<tool_call>get_weather<arg_key>city</arg_key><arg_value>Os"):
+        events += p.on_token(t)
+    events += p.finish()
+    assert "".join(e.text for e in events if e.type == "content_delta") == "Calling."
+    assert not [e for e in events if e.type == "tool_call"] and [e for e in events if e.type == "parse_error"]
+    # thinking disabled by the template: the output starts as content, and a stray </think> never opens reasoning
+    p = GlmParser(lambda ids: tok.decode(list(ids)), ctl, starts_in_reasoning=False)
+    events = []
+    for t in tok.encode("Plain answer."):
+        events += p.on_token(t)
+    events += p.finish()
+    assert "".join(e.text for e in events if e.type == "content_delta") == "Plain answer."
+    assert not [e for e in events if e.type == "reasoning_delta"]
