@@ -251,3 +251,54 @@ def test_glm_parser_truncated_tool_call_and_content_mode():
     events += p.finish()
     assert "".join(e.text for e in events if e.type == "content_delta") == "Plain answer."
     assert not [e for e in events if e.type == "reasoning_delta"]
+
+
+def test_parser_continuation_of_an_assistant_prefix():
+    """`continue_final_message`: the parser consumes the existing assistant text so that its state (inside or past the
+    reasoning block) carries over, and none of the prefix comes back as new output."""
+    tok = ByteTokenizer()
+    ctl = resolve_control_tokens(tok)
+    dec = lambda ids: tok.decode(list(ids))          # noqa: E731
+    # the prefix already closed its reasoning: what follows is content
+    p = GlmParser(dec, ctl, starts_in_reasoning=False)
+    p.continue_from(tok.encode("<think>done thinking</think>The answer is"))
+    events = []
+    for t in tok.encode(" 42."):
+        events += p.on_token(t)
+    events += p.finish()
+    assert "".join(e.text for e in events if e.type == "content_delta") == " 42."
+    assert not [e for e in events if e.type == "reasoning_delta"]
+    # the prefix is still inside an open reasoning block: the continuation is reasoning until </think>
+    p = GlmParser(dec, ctl, starts_in_reasoning=False)
+    p.continue_from(tok.encode("<think>first, consider"))
+    events = []
+    for t in tok.encode(" the units</think>Metres."):
+        events += p.on_token(t)
+    events += p.finish()
+    assert "".join(e.text for e in events if e.type == "reasoning_delta") == " the units"
+    assert "".join(e.text for e in events if e.type == "content_delta") == "Metres."
+
+
+def test_server_continues_a_partial_assistant_message():
+    tok = ByteTokenizer()
+    eng = ScriptEngine(tok.encode(" and more.") + [tok.eos_token_id])
+    cfg = EngineConfig(host="127.0.0.1", port=0, batch_size=2, chunk_size=256)
+    sched = GenerationScheduler(eng, max_batch=2, chunk_size=256, eos_token_ids=[tok.eos_token_id])
+    sched.start()
+
+    async def run():
+        srv = OpenAIServer(sched, tok, cfg, model_name="m", max_model_len=4096)
+        await srv.start()
+        msgs = [{"role": "user", "content": "go on"}, {"role": "assistant", "content": "Some text"}]
+        for body in ({"messages": msgs, "continue_final_message": True},
+                     {"messages": msgs, "chat_template_kwargs": {"continue_final_message": True}}):
+            st, raw = await _http(srv.port, "POST", "/v1/chat/completions", {**body, "temperature": 0})
+            out = json.loads(raw)
+            assert st == 200 and out["choices"][0]["message"]["content"] == " and more."        # the prefix is not repeated
+        # the rendered prompt ends with the partial message (no fresh assistant header after it)
+        ids = srv._tokenize({"messages": msgs}, {"continue_final_message": True})
+        assert tok.decode(ids).endswith("Some text")
+        await srv.close()
+
+    asyncio.run(run())
+    sched.stop()
