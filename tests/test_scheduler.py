@@ -171,3 +171,41 @@ def test_cancel_and_too_long_prompt():
     r.cancel()
     _drain(s)
     assert r.finish_reason == "cancelled" and len(r.generated) < 100
+
+
+def test_sequence_page_edges_truncate_and_copy_on_write():
+    """Page-edge cases of the KV bookkeeping (reference `tests/test_report_tokens.ts`, `test_sequence_truncate.ts`):
+    speculative over-allocation across a page edge and its truncation, re-growing afterwards, truncation into a page
+    that is shared with a donor (the next write must un-share it), and reporting never exceeding what is allocated."""
+    copies = []
+    kv = PagedKVCache(8, copy_page=lambda a, b: copies.append((a, b)))
+    tpp = kv.tokens_per_page
+    s = kv.new_sequence()
+    kv.append_tokens(s, range(tpp - 1))                    # one token short of the page edge
+    kv.report_tokens(s)
+    assert len(s.pages) == 1 and s.reported == tpp - 1
+    kv.append_tokens(s, [7, 8, 9, 10])                     # a speculative step reserves 4 positions across the edge
+    assert len(s.pages) == 2 and s.length == tpp + 3 and s.reported == tpp - 1
+    kv.report_tokens(s, upto=10 ** 9)                      # never beyond the allocation
+    assert s.reported == s.length
+    free_before = kv.free_pages
+    kv.truncate(s, tpp)                                    # two drafts accepted: exactly fills page 0, page 1 goes back
+    assert len(s.pages) == 1 and s.length == s.reported == tpp and kv.free_pages == free_before + 1
+    kv.truncate(s, tpp + 5)                                # growing through truncate is a no-op
+    assert s.length == tpp
+    kv.append_tokens(s, [11])                              # the next token opens a fresh page
+    assert len(s.pages) == 2 and s.token_ids[-1] == 11
+    kv.report_tokens(s)
+    # a second request shares page 0, is cut back into it, and must copy before writing there
+    kv.stage(s)
+    prompt = list(range(tpp - 1)) + [7] + [500, 501]
+    t, cached = kv.start_request(prompt)
+    assert cached == tpp and t.pages[0] == s.pages[0] and kv.pool.refcount(t.pages[0]) == 2
+    kv.append_tokens(t, prompt[cached:])
+    kv.truncate(t, tpp - 10)                               # back inside the shared page
+    assert len(t.pages) == 1 and t.pages[0] == s.pages[0] and not copies
+    kv.append_tokens(t, [900])
+    assert copies == [(s.pages[0], t.pages[0])] and t.pages[0] != s.pages[0] and kv.pool.refcount(s.pages[0]) == 1
+    kv.free_sequence(t)
+    kv.flush_staged()
+    kv.assert_clear()
