@@ -37,7 +37,9 @@ def add_model_args(ap: argparse.ArgumentParser) -> None:
     ap.add_argument("--chunk-size", type=int, default=8192)
     ap.add_argument("--max-pages", type=int, default=0, help="KV pages of 64 tokens (0: batch-size * ceil(chunk-size / 64))")
     ap.add_argument("--max-host-pages", type=int, default=0, help="pinned-host prefix tier size in pages (0: off)")
-    ap.add_argument("--max-model-len", type=int, default=65536)
+    ap.add_argument("--max-model-len", type=int, default=None,
+                    help="longest sequence (prompt + output) a request may reach; default: the checkpoint's "
+                         "max_position_embeddings, 65536 without a checkpoint")
     ap.add_argument("--no-cuda-graph", action="store_true")
     ap.add_argument("--phased-prefill", dest="phased_prefill", action="store_true", default=env_flag("PHASED_PREFILL"),
                     help="run large prefill chunks as two halves on two streams (multi-rank jobs); off by default: over "
@@ -138,8 +140,13 @@ def build_runtime(args, with_scheduler: bool = True) -> Runtime:
         if not args.model:
             raise SystemExit("give --model DIR|HUB_ID or --random-init SPEC")
         model_dir = resolve_model_path(args.model)
+        if getattr(args, "max_model_len", None) is None:
+            from ..utils.generation_config import max_position_embeddings
+            args.max_model_len = max_position_embeddings(model_dir)
         model_type, reg, _ = inspect_model(model_dir, cp=args.cp, mtp=args.mtp)
         cfg, model = reg.load(model_dir, ctx, args.mtp)
+    if getattr(args, "max_model_len", None) is None:
+        args.max_model_len = 65536
     ecfg = EngineConfig(model=args.model or args.random_init, gpus=list(range(ctx.world)), arena_gb=args.arena, cp=args.cp, ep=args.ep,
                         mtp=args.mtp, batch_size=args.batch_size, chunk_size=args.chunk_size, max_pages=args.max_pages,
                         max_host_pages=args.max_host_pages, cuda_graph=not args.no_cuda_graph,
