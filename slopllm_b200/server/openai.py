@@ -313,7 +313,10 @@ class OpenAIServer:
         except Exception as e:  # noqa: BLE001
             raise HttpError(400, f"unable to prepare chat prompt: {e}")
         if len(ids) >= self.max_model_len:
-            raise HttpError(400, f"prompt has {len(ids)} tokens, the model context is {self.max_model_len}")
+            # (the reference drops the oldest prompt tokens here, `src/openai-server.ts:704-707`; an explicit error lets the
+            # client decide what to cut)
+            raise HttpError(400, f"prompt has {len(ids)} tokens, the model context is {self.max_model_len}", param="messages",
+                            code="context_length_exceeded")
         max_tokens = params.get("max_tokens") or params.get("max_completion_tokens") or self.cfg.max_tokens
         max_tokens = max(1, min(int(max_tokens), self.max_model_len - len(ids)))
         stream = params.get("stream") is True
