@@ -111,7 +111,7 @@ def main():
     args = parse()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "reference is a Node.js/N-API addon compiled only for sm_120a "
-                          "with an empty vendor/flashinfer submodule; `pip install /root/reference` fails: no setup.py/pyproject.toml"}))
+                          "with an empty vendor/flashinfer submodule; `pip install` of the reference tree fails: no setup.py/pyproject.toml"}))
         return 0
 
     import torch

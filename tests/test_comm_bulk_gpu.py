@@ -45,8 +45,8 @@ def test_bulk_allreduce_emulated_ranks(W, T):
     ops = CudaOps(cfg)
     g = torch.Generator(device=DEV).manual_seed(W * 1000 + T)
     norm_w = torch.rand(H, device=DEV, generator=g).to(torch.bfloat16)
-    # round 0: bf16 weights, GEMM epilogue is the producer; round 1: NVFP4 weights (expanded, same epilogue), no residual;
-    # round 2: an existing fp32 tensor is pushed.  Three uses of the same lane also exercise the counter resets.
+    # use 0: bf16 weights, GEMM epilogue is the producer; use 1: NVFP4 weights (expanded, same epilogue), no residual;
+    # use 2: an existing fp32 tensor is pushed.  Three uses of the same lane also exercise the counter resets.
     for rnd in range(3):
         res = torch.randn(T, H, device=DEV, generator=g) if rnd != 1 else None
         xs = [torch.randn(T, K, device=DEV, generator=g).to(torch.bfloat16) for _ in range(W)]
