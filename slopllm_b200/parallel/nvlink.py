@@ -159,6 +159,9 @@ class SymmetricRegion:
         self.wait_spins = wait_spins
         lay = self.layout(world, slot_rows, row_len, gather_bytes, cp_shape, bulk_rows)
         self.lay = lay
+        if local.numel() * local.element_size() < lay["total"]:
+            raise ValueError(f"symmetric region of {local.numel() * local.element_size()} bytes is smaller than its layout "
+                             f"({lay['total']} bytes): allocate it from SymmetricRegion.layout with the same arguments")
         self.write_canaries()
         # bulk all-reduce lanes: local "blocks past their wait" words, [lane][bulk_rows / 32 group words + 8 source words]
         self.bulk_rows = bulk_rows
