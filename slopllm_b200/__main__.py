@@ -11,6 +11,7 @@ COMMANDS = {
     "mtp-bench": "slopllm_b200.cli.mtp_bench",
     "loader": "slopllm_b200.cli.model_loader",
     "weights-doc": "slopllm_b200.cli.weights_doc",
+    "plan": "slopllm_b200.cli.plan",
     "kernel-bench": "slopllm_b200.cli.kernel_bench",
     "profile-step": "slopllm_b200.cli.profile_step",
     "collective-bench": "slopllm_b200.cli.collective_bench",

@@ -239,3 +239,36 @@ def test_generation_defaults_from_the_checkpoint(tmp_path):
     bare = SimpleNamespace(temperature=None, top_p=None, top_k=None, repetition_penalty=None, max_tokens=None)
     apply_generation_defaults(bare, None, BUILTIN_SAMPLING)
     assert (bare.temperature, bare.top_p, bare.top_k) == (0.6, 0.95, 20)
+
+
+def test_memory_plan_matches_real_weights_and_caches():
+    """The analytic sizing against weights and caches that were really built (tiny and a mid-size shape, TP 1 / 2, experts
+    split by column or by expert), then the plan arithmetic and the `plan` command."""
+    import json
+    import torch
+    from slopllm_b200.cli import plan as plan_cli
+    from slopllm_b200.config import GlmMoeDsaConfig
+    from slopllm_b200.models.glm_moe_dsa import KVCacheTensors
+    from slopllm_b200.models.weights import random_model
+    from slopllm_b200.utils.sizing import GIB, kv_page_bytes, model_weight_bytes, plan_memory
+    mid = GlmMoeDsaConfig(hidden_size=512, intermediate_size=1024, moe_intermediate_size=256, num_hidden_layers=3,
+                          num_nextn_predict_layers=1, vocab_size=2048, num_attention_heads=8, q_lora_rank=256,
+                          n_routed_experts=16, num_experts_per_tok=4, n_group=4, topk_group=2, index_topk=64,
+                          first_k_dense_replace=1, quant_o_proj=True, quant_dense_mlp=True)
+    for cfg in (GlmMoeDsaConfig.tiny(), mid):
+        for tp, ep in ((1, False), (2, False), (2, True)):
+            w = random_model(cfg, 0, "cpu", torch.bfloat16, 0, tp, ep=ep, with_mtp=True)
+            est = model_weight_bytes(cfg, tp, ep, True)
+            assert abs(est - w.nbytes()) <= 0.002 * w.nbytes(), (tp, ep, est, w.nbytes())
+        assert KVCacheTensors.allocate(cfg, 4, "cpu").nbytes() == 4 * kv_page_bytes(cfg, True)
+    glm5 = GlmMoeDsaConfig.glm5(78)
+    p8 = plan_memory(glm5, world=8, cp=True, mtp=3, max_pages=8192)
+    assert 50 * GIB < p8.weights_bytes < 60 * GIB and p8.tokens_per_page == 512 and p8.requested_fits
+    assert p8.max_pages == (p8.budget_bytes - p8.weights_bytes - p8.workspace_bytes) // p8.page_bytes
+    p1 = plan_memory(glm5, world=1)
+    assert p1.weights_bytes > 180 * GIB and p1.max_pages == 0 and not p1.requested_fits      # the model needs several GPUs
+    small = plan_memory(glm5, world=8, arena_gb=70.0, max_pages=8192)
+    assert small.max_pages < 8192 and not small.requested_fits
+    assert plan_cli.main(["--random-init", "glm5", "--world", "8", "--cp", "--mtp", "--max-pages", "8192"]) == 0
+    assert plan_cli.main(["--random-init", "glm5", "--world", "1"]) == 1
+    assert json.dumps(p8.to_dict())
