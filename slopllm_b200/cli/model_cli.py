@@ -98,6 +98,28 @@ def apply_arena_cap(device: torch.device, arena_gb: float) -> float:
     return frac
 
 
+def check_memory_plan(args, ctx: ParallelContext, model_dir: str, model_type: str) -> Optional[str]:
+    """Before the weights are read: does this rank's share of the model plus the KV pages asked for fit the memory the
+    process may use?  A plan that does not fit is reported on stderr (rank 0) and returned; loading still goes ahead, the
+    estimate of the workspace is deliberately generous."""
+    if model_type != "glm_moe_dsa" or ctx.device.type != "cuda":
+        return None
+    import sys
+    from ..checkpoint.loader import load_config
+    from ..utils.sizing import GIB, plan_memory
+    total = torch.cuda.get_device_properties(ctx.device).total_memory
+    p = plan_memory(load_config(model_dir), world=ctx.world, cp=args.cp, ep=args.ep, mtp=args.mtp, batch_size=args.batch_size,
+                    chunk_size=args.chunk_size, max_pages=args.max_pages, arena_gb=args.arena, device_gb=total / GIB)
+    if p.requested_fits:
+        return None
+    msg = (f"memory plan: {p.weights_bytes / GIB:.1f} GiB of weights per rank + about {p.workspace_bytes / GIB:.1f} GiB of "
+           f"workspace leave room for {p.max_pages} KV pages, {p.requested_pages} were asked for "
+           f"(`python -m slopllm_b200 plan` shows the arithmetic)")
+    if ctx.rank == 0 and ctx.dp_rank == 0:
+        print(msg, file=sys.stderr)
+    return msg
+
+
 def _random_model(spec: str, ctx: ParallelContext, mtp: int):
     from ..parallel.fused import make_comm
     dtype = torch.bfloat16 if ctx.device.type == "cuda" else torch.float32
@@ -144,6 +166,7 @@ def build_runtime(args, with_scheduler: bool = True) -> Runtime:
             from ..utils.generation_config import max_position_embeddings
             args.max_model_len = max_position_embeddings(model_dir)
         model_type, reg, _ = inspect_model(model_dir, cp=args.cp, mtp=args.mtp)
+        check_memory_plan(args, ctx, model_dir, model_type)
         cfg, model = reg.load(model_dir, ctx, args.mtp)
     if getattr(args, "max_model_len", None) is None:
         args.max_model_len = 65536
