@@ -46,21 +46,33 @@ def parse_args(argv=None):
 
 
 def warm_up(rt, tokens: int = 32, remote=()) -> float:
-    """A short greedy request through the scheduler (and through every remote replica's proxy) so that the first user
-    request finds the decode graphs captured."""
+    """Requests through the scheduler (and through every remote replica's proxy) before the port opens: one short greedy
+    request, then a full batch whose prompts together fill a prefill chunk, so that the first users find the decode graphs
+    of batch 1 and of the full batch captured and the allocator already at its serving high-water mark (reference: the
+    peak warm-up of `src/openai-server.ts:476-539`).  The prefix caches are flushed afterwards."""
     import threading
     from ..config import SamplingParams
     from ..scheduler.scheduler import GenerationRequest
     t0 = time.time()
-    waits = []
-    for i, target in enumerate([rt.scheduler, *remote]):
-        done = threading.Event()
-        target.submit(GenerationRequest(id=f"warmup-{i}", input_ids=[1] * 16, max_tokens=tokens,
-                                        sampling=SamplingParams(temperature=0.0), on_finish=lambda r, d=done: d.set()))
-        waits.append(done)
-    for done in waits:
-        done.wait(timeout=600)
-    for target in [rt.scheduler, *remote]:
+    targets = [rt.scheduler, *remote]
+    B = max(1, rt.engine_cfg.batch_size)
+    per_prompt = max(16, min(1024, rt.engine_cfg.chunk_size // B))
+    vocab = getattr(rt.cfg, "vocab_size", 2)
+    for round_, (count, plen) in enumerate(((1, 16), (B, per_prompt))):
+        if round_ == 1 and B == 1:
+            break
+        waits = []
+        for i, target in enumerate(targets):
+            for j in range(count):
+                done = threading.Event()
+                # different first tokens: the batch must not collapse onto one shared prefix
+                ids = [1 + (j * 7 + n) % max(1, vocab - 1) for n in range(plen)]
+                target.submit(GenerationRequest(id=f"warmup-{round_}-{i}-{j}", input_ids=ids, max_tokens=tokens,
+                                                sampling=SamplingParams(temperature=0.0), on_finish=lambda r, d=done: d.set()))
+                waits.append(done)
+        for done in waits:
+            done.wait(timeout=600)
+    for target in targets:
         target.flush_gpu_cache().done.wait(timeout=60)
     return time.time() - t0
 
