@@ -19,9 +19,11 @@ from typing import List, Optional
 
 import torch
 
-from ..config import GlmMoeDsaConfig, PAGE_SIZE
+from ..config import GlmMoeDsaConfig, PAGE_SIZE, env_flag
 from ..parallel.dist import Comm, ParallelContext
 from ..utils.tracing import traced
+
+EP_ALL_TO_ALL = env_flag("EP_A2A")      # expert parallelism by token dispatch / combine instead of masked partial sums
 from .weights import LayerWeights, ModelWeights
 
 
@@ -166,11 +168,32 @@ class GlmMoeDsaModel:
     def mlp(self, lw: LayerWeights, y: torch.Tensor, final: bool = False):
         ops, ctx = self.ops, self.ctx
         if lw.experts is not None and ctx.ep and ctx.world > 1:
-            return self._moe_ep(lw, y)
+            if EP_ALL_TO_ALL:
+                return self._moe_ep(lw, y)
+            out = self._moe_ep_partial(lw, y)
+            sink = self.comm.partial_sink(y.shape[0], final=final)
+            return out if sink is None else sink.push_tensor(out)
         sink = self.comm.partial_sink(y.shape[0], final=final)
         if lw.experts is None:
             return ops.dense_mlp(y, lw, sink=sink)
         return ops.moe_tp(y, lw, sink=sink)
+
+    def _moe_ep_partial(self, lw: LayerWeights, y: torch.Tensor):
+        """Expert parallelism without a dispatch: the normed hidden rows are replicated on every rank of the replica, so
+        each rank routes all of them, runs the routes that land on the experts it owns (full-width experts, the others
+        masked out) plus its column slice of the shared expert, and returns that as its partial sum; the all-reduce that
+        follows every MLP anyway adds the ranks' contributions up.  No all-to-all, no host synchronisation, fixed shapes:
+        the step stays capturable in a CUDA graph and its partial sum can go through the fused NVLink all-reduce.
+        (`SLOPLLM_B200_EP_A2A=1` selects the token-split dispatch / combine form below instead.)"""
+        ops, ctx = self.ops, self.ctx
+        ids, wts = ops.route(y, lw)
+        lo = lw.experts.expert_offset
+        mine = (ids >= lo) & (ids < lo + lw.experts.num_experts)
+        out = ops.moe_local_experts(y, lw.experts, torch.where(mine, ids, torch.full_like(ids, -1)),
+                                    torch.where(mine, wts, torch.zeros_like(wts)))
+        if lw.shared is not None:
+            out = out + ops.shared_expert(y, lw).to(out.dtype)
+        return out
 
     def _moe_ep(self, lw: LayerWeights, y: torch.Tensor):
         """Expert parallelism: tokens are split across ranks, each token's hidden row is

@@ -63,8 +63,22 @@ def test_cp2_gather_kv_mode_matches_single():
 
 
 def test_ep2_matches_single():
+    """Expert parallelism as masked partial sums (the default: no dispatch, every rank runs its own experts on the replicated
+    rows and the following all-reduce adds the ranks up)."""
     ref = _greedy(0, 1, False, False, 40, 6)
     out = run_ranks(_greedy, 2, False, True, 40, 6)
+    assert out[0] == out[1] == ref
+
+
+def _greedy_a2a(rank, world, prompt_len, new):
+    import slopllm_b200.models.glm_moe_dsa as M
+    M.EP_ALL_TO_ALL = True                      # token-split dispatch / combine all-to-all
+    return _greedy(rank, world, False, True, prompt_len, new)
+
+
+def test_ep2_all_to_all_variant_matches_single():
+    ref = _greedy(0, 1, False, False, 40, 6)
+    out = run_ranks(_greedy_a2a, 2, 40, 6)
     assert out[0] == out[1] == ref
 
 
