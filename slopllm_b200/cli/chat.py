@@ -40,9 +40,10 @@ def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="slopllm_b200.cli.chat")
     add_model_args(ap)
     ap.add_argument("--max-tokens", type=int, default=512)
-    ap.add_argument("--temperature", type=float, default=0.6)
-    ap.add_argument("--top-p", type=float, default=0.95)
-    ap.add_argument("--top-k", type=int, default=20)
+    # not given: the checkpoint's generation_config.json / config.json value, else 0.6 / 0.95 / 20
+    ap.add_argument("--temperature", type=float, default=None)
+    ap.add_argument("--top-p", type=float, default=None)
+    ap.add_argument("--top-k", type=int, default=None)
     ap.add_argument("--prompt", default="", help="answer this one prompt and exit")
     ap.add_argument("--no-thinking", action="store_true")
     args = ap.parse_args(argv)
@@ -51,7 +52,13 @@ def main(argv=None) -> int:
     if rt.ctx.rank != 0:
         rt.scheduler._thread.join()
         return 0
-    sampling = SamplingParams(temperature=args.temperature, top_p=args.top_p, top_k=args.top_k)
+    from ..utils.generation_config import apply_generation_defaults
+    from ..utils.model_path import resolve_model_path
+    args.repetition_penalty = None
+    apply_generation_defaults(args, resolve_model_path(args.model) if args.model else None,
+                              {"temperature": 0.6, "top_p": 0.95, "top_k": 20, "repetition_penalty": 1.0, "max_tokens": 512})
+    sampling = SamplingParams(temperature=args.temperature, top_p=args.top_p, top_k=args.top_k,
+                              repetition_penalty=args.repetition_penalty)
     history = []
     try:
         while True:
