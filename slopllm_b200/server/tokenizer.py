@@ -77,13 +77,15 @@ class ByteTokenizer:
 
 
 def load_tokenizer(model_dir: Optional[str], vocab_size: int = 512):
-    """HF tokenizer of `model_dir` (or of SLOPLLM_B200_TOKENIZER_REPO) when available, else bytes."""
+    """The Hugging Face tokenizer of `model_dir` (or of SLOPLLM_B200_TOKENIZER_REPO).  The byte tokenizer is only for
+    directories without a `tokenizer.json` (random-init models, test fixtures): a checkpoint whose tokenizer exists but
+    cannot be loaded is an error, not a reason to serve bytes."""
     from ..config import env_str
     path = env_str("TOKENIZER_REPO") or model_dir
     if path and os.path.exists(os.path.join(path, "tokenizer.json")):
         try:
             from transformers import AutoTokenizer
             return AutoTokenizer.from_pretrained(path, local_files_only=True)
-        except Exception:  # noqa: BLE001
-            pass
+        except Exception as e:  # noqa: BLE001
+            raise RuntimeError(f"{path} has a tokenizer.json but it could not be loaded: {type(e).__name__}: {e}") from e
     return ByteTokenizer(vocab_size)

@@ -302,3 +302,12 @@ def test_server_continues_a_partial_assistant_message():
 
     asyncio.run(run())
     sched.stop()
+
+
+def test_broken_tokenizer_is_an_error_not_a_byte_fallback(tmp_path):
+    import pytest
+    from slopllm_b200.server.tokenizer import load_tokenizer
+    assert isinstance(load_tokenizer(str(tmp_path), 300), ByteTokenizer)          # no tokenizer.json: bytes (fixtures)
+    (tmp_path / "tokenizer.json").write_text("{ not a tokenizer")
+    with pytest.raises(RuntimeError, match="could not be loaded"):
+        load_tokenizer(str(tmp_path), 300)
