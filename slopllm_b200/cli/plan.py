@@ -19,8 +19,13 @@ from ..utils.sizing import GIB, plan_memory
 def _config(args) -> GlmMoeDsaConfig:
     if args.model:
         from ..checkpoint.loader import load_config
+        from ..models.registry import inspect_model
         from ..utils.model_path import resolve_model_path
-        return load_config(resolve_model_path(args.model))
+        model_dir = resolve_model_path(args.model)
+        model_type, _, _ = inspect_model(model_dir)
+        if model_type != "glm_moe_dsa":
+            raise SystemExit(f"plan: the sizing arithmetic covers glm_moe_dsa checkpoints; {args.model} is {model_type}")
+        return load_config(model_dir)
     spec = args.random_init or "glm5"
     if spec.startswith("glm5"):
         return GlmMoeDsaConfig.glm5(num_layers=int(spec.split(":")[1]) if ":" in spec else 78)
