@@ -22,11 +22,17 @@ def _config(args) -> GlmMoeDsaConfig:
         from ..models.registry import inspect_model
         from ..utils.model_path import resolve_model_path
         model_dir = resolve_model_path(args.model)
-        model_type, _, _ = inspect_model(model_dir)
+        model_type, _, raw = inspect_model(model_dir)
+        if model_type in ("qwen3", "qwen3_5"):
+            from ..models.dense import DenseConfig
+            return DenseConfig.from_hf_dict(raw)
         if model_type != "glm_moe_dsa":
-            raise SystemExit(f"plan: the sizing arithmetic covers glm_moe_dsa checkpoints; {args.model} is {model_type}")
+            raise SystemExit(f"plan: the sizing arithmetic covers glm_moe_dsa, qwen3 and qwen3_5; {args.model} is {model_type}")
         return load_config(model_dir)
     spec = args.random_init or "glm5"
+    if spec.startswith("qwen"):
+        from ..models.dense import DenseConfig
+        return DenseConfig.tiny(hybrid=spec.startswith("qwen35"))
     if spec.startswith("glm5"):
         return GlmMoeDsaConfig.glm5(num_layers=int(spec.split(":")[1]) if ":" in spec else 78)
     return GlmMoeDsaConfig.tiny()
@@ -35,7 +41,7 @@ def _config(args) -> GlmMoeDsaConfig:
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="slopllm_b200.cli.plan", description=__doc__.split("\n")[0])
     ap.add_argument("--model", default="", help="checkpoint directory or hub id (only config.json is read)")
-    ap.add_argument("--random-init", default="", help="glm5[:layers] or tiny instead of a checkpoint")
+    ap.add_argument("--random-init", default="", help="glm5[:layers], tiny, qwen3 or qwen35 instead of a checkpoint")
     ap.add_argument("--world", type=int, default=1, help="GPUs of one replica")
     ap.add_argument("--cp", action="store_true")
     ap.add_argument("--ep", action="store_true")
@@ -48,9 +54,14 @@ def main(argv=None) -> int:
     ap.add_argument("--context", type=int, default=0, help="longest sequence assumed for the workspace estimate")
     args = ap.parse_args(argv)
     cfg = _config(args)
-    p = plan_memory(cfg, world=args.world, cp=args.cp, ep=args.ep, mtp=args.mtp, batch_size=args.batch_size,
-                    chunk_size=args.chunk_size, max_pages=args.max_pages, arena_gb=args.arena, device_gb=args.device_gb,
-                    context=args.context)
+    if not isinstance(cfg, GlmMoeDsaConfig):
+        from ..utils.sizing import plan_dense
+        p = plan_dense(cfg, world=args.world, batch_size=args.batch_size, chunk_size=args.chunk_size, max_pages=args.max_pages,
+                       arena_gb=args.arena, device_gb=args.device_gb)
+    else:
+        p = plan_memory(cfg, world=args.world, cp=args.cp, ep=args.ep, mtp=args.mtp, batch_size=args.batch_size,
+                        chunk_size=args.chunk_size, max_pages=args.max_pages, arena_gb=args.arena, device_gb=args.device_gb,
+                        context=args.context)
     g = lambda b: f"{b / GIB:8.2f} GiB"       # noqa: E731
     print(f"replica of {args.world} GPU(s): tp={p.tp} cp={p.cp} ep={p.ep} mtp={args.mtp}   (per rank)")
     print(f"  weights                 {g(p.weights_bytes)}")

@@ -1,4 +1,5 @@
-"""Memory plan of a glm_moe_dsa deployment, computed from the configuration alone (no weights, no GPU).
+"""Memory plan of a deployment (glm_moe_dsa, and the dense Qwen3 / Qwen3.5 families), computed from the configuration alone
+(no weights, no GPU).
 
 `plan_memory` answers the questions that come before a launch: how many bytes of weights does one rank hold under a given
 tensor / expert / context parallelism, what does one KV page cost, how many pages fit next to the weights in the device
@@ -136,3 +137,54 @@ def plan_memory(cfg: GlmMoeDsaConfig, world: int = 1, cp: bool = False, ep: bool
     return MemoryPlan(tp=tp, cp=cpw, ep=ep, weights_bytes=weights, page_bytes=page, tokens_per_page=tpp, workspace_bytes=work,
                       budget_bytes=budget, max_pages=int(fit), max_tokens=int(fit) * tpp, requested_pages=requested,
                       requested_fits=requested <= fit)
+
+
+# ---- dense families (Qwen3, Qwen3.5) -----------------------------------------------------------------------------------
+
+def dense_weight_bytes(cfg, tp: int = 1, elem: int = 2, fp8: bool = False) -> int:
+    """Per-rank weight bytes of a Qwen3 / Qwen3.5 decoder: attention and Gated-DeltaNet projections head-sharded, MLP
+    column / row sharded, embedding whole, lm_head vocabulary-sharded.  `fp8`: the attention and MLP projections stay FP8
+    (one byte per weight + one fp32 scale per 128 x 128 block)."""
+    H, I, hd = cfg.hidden_size, cfg.intermediate_size, cfg.head_dim
+
+    def lin(n, k, quant=False):
+        return n * k + (-(-n // 128)) * (-(-k // 128)) * 4 if quant else n * k * elem
+    b = cfg.vocab_size * H * elem + H * elem
+    b += (cfg.vocab_size // tp) * H * elem                         # the head's shard is materialised even when it is tied
+    for kind in cfg.layer_types:
+        b += 2 * H * elem                                           # the two layer norms
+        b += lin(2 * I // tp, H, fp8) + lin(H, I // tp, fp8)
+        if kind == "full_attention":
+            qs = hd * (2 if cfg.attn_output_gate else 1)
+            hq, hk = cfg.num_attention_heads // tp, max(1, cfg.num_key_value_heads // tp)
+            b += lin(hq * qs + 2 * hk * hd, H, fp8) + lin(H, hq * hd, fp8) + 2 * hd * elem      # qkv, o_proj, q/k norms
+        else:
+            lh, dk, dv = cfg.linear_num_key_heads // tp, cfg.linear_key_head_dim, cfg.linear_value_head_dim
+            conv_dim = lh * (2 * dk + dv)
+            b += lin(conv_dim + lh * dv + 2 * lh, H) + lin(H, lh * dv)                          # in-projection, out-projection
+            b += conv_dim * cfg.linear_conv_kernel_dim * elem + 2 * lh * 4 + dv * elem          # conv, A_log, dt_bias, norm
+    return b
+
+
+def dense_kv_page_bytes(cfg, tp: int = 1, elem: int = 2) -> int:
+    """Bytes of one 64-token page on one rank: K and V rows of every full-attention layer (recurrent layers keep their
+    state per sequence, not per page)."""
+    n_kv = max(1, cfg.num_key_value_heads // tp)
+    full = sum(1 for k in cfg.layer_types if k == "full_attention")
+    return full * 2 * n_kv * cfg.head_dim * elem * PAGE_SIZE
+
+
+def plan_dense(cfg, world: int = 1, batch_size: int = 8, chunk_size: int = 8192, max_pages: int = 0, arena_gb: float = 0.0,
+               device_gb: float = 180.0, fp8: bool = False, reserve_gb: float = 4.0) -> MemoryPlan:
+    """`plan_memory` for the dense families (tensor parallel only; the workspace estimate is the residual / activation rows
+    plus the MLP's gate-up rows of one chunk)."""
+    weights = dense_weight_bytes(cfg, world, fp8=fp8)
+    page = max(1, dense_kv_page_bytes(cfg, world))
+    requested = max_pages if max_pages > 0 else batch_size * -(-chunk_size // PAGE_SIZE)
+    work = chunk_size * (cfg.hidden_size * 12 + 2 * (cfg.intermediate_size // world) * 4
+                         + (cfg.num_attention_heads // world) * cfg.head_dim * 8)
+    budget = int(((arena_gb if arena_gb > 0 else device_gb) - reserve_gb) * GIB)
+    fit = max(0, (budget - weights - work) // page)
+    return MemoryPlan(tp=world, cp=1, ep=False, weights_bytes=weights, page_bytes=page, tokens_per_page=PAGE_SIZE,
+                      workspace_bytes=work, budget_bytes=budget, max_pages=int(fit), max_tokens=int(fit) * PAGE_SIZE,
+                      requested_pages=requested, requested_fits=requested <= fit)

@@ -272,3 +272,30 @@ def test_memory_plan_matches_real_weights_and_caches():
     assert plan_cli.main(["--random-init", "glm5", "--world", "8", "--cp", "--mtp", "--max-pages", "8192"]) == 0
     assert plan_cli.main(["--random-init", "glm5", "--world", "1"]) == 1
     assert json.dumps(p8.to_dict())
+
+
+def test_memory_plan_for_dense_families():
+    import torch
+    from slopllm_b200.cli import plan as plan_cli
+    from slopllm_b200.models.dense import DenseCache, DenseConfig, random_dense_model
+    from slopllm_b200.runtime.workspace import walk_tensors
+    from slopllm_b200.utils.sizing import dense_kv_page_bytes, dense_weight_bytes, plan_dense
+    for hybrid in (False, True):
+        cfg = DenseConfig.tiny(hybrid=hybrid)
+        for tp in (1, 2):
+            w, _ = random_dense_model(cfg, 0, "cpu", torch.bfloat16, 0, tp)
+            seen, total = set(), [0]
+
+            def add(t):
+                if t.data_ptr() not in seen:
+                    seen.add(t.data_ptr())
+                    total[0] += t.numel() * t.element_size()
+            walk_tensors(w, add)
+            assert dense_weight_bytes(cfg, tp) == total[0], (hybrid, tp)
+            c = DenseCache(cfg, 4, "cpu", tp=tp)
+            kv = sum(x.numel() * x.element_size() for x in list(c.k.values()) + list(c.v.values()))
+            assert kv == 4 * dense_kv_page_bytes(cfg, tp)
+    p = plan_dense(DenseConfig.tiny(), world=1, max_pages=64)
+    assert p.requested_fits and p.tokens_per_page == 64 and p.max_pages > 64
+    assert dense_weight_bytes(DenseConfig.tiny(), 1, fp8=True) < dense_weight_bytes(DenseConfig.tiny(), 1)
+    assert plan_cli.main(["--random-init", "qwen3", "--max-pages", "64"]) == 0
