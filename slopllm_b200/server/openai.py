@@ -178,7 +178,11 @@ class OpenAIServer:
                 return self._send(writer, 204, b"")
             if method == "GET" and path == "/health":
                 ok = self.healthy()
-                return self._send(writer, 200 if ok else 503, {"status": "ok" if ok else "unhealthy"})
+                body = {"status": "ok" if ok else "unhealthy"}
+                state = getattr(getattr(self.healthy, "__self__", None), "state", None)      # a HealthMonitor's bound method
+                if not ok and state is not None:
+                    body.update(reason=state.reason, failed_ranks=list(state.failed_ranks))
+                return self._send(writer, 200 if ok else 503, body)
             if method == "GET" and path == "/version":
                 return self._send(writer, 200, {"version": __version__})
             if method == "GET" and path == "/metrics":

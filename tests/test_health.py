@@ -213,3 +213,46 @@ def test_nvtx_ranges_cover_engine_steps_and_layers(monkeypatch):
         at = names.index(f"layer{i}")
         assert names[at + 1] == "attention" and "mlp" in names[at + 1:at + 4] and seen[at + 1][0] == seen[at][0] + 1
     assert torch.is_tensor(torch.zeros(1))
+
+
+def test_health_endpoint_reports_the_lost_ranks():
+    import asyncio
+    import json
+    from slopllm_b200.config import EngineConfig
+    from slopllm_b200.scheduler.scheduler import GenerationScheduler
+    from slopllm_b200.server.openai import OpenAIServer
+    from slopllm_b200.server.tokenizer import ByteTokenizer
+    from test_scheduler import FakeEngine
+
+    class Store(dict):
+        def set(self, k, v):
+            self[k] = v.encode() if isinstance(v, str) else v
+
+        def get(self, k):
+            return self[k]
+    now = [100.0]
+    store = Store()
+    mon = HealthMonitor(store, 0, 2, timeout_s=2.0, clock=lambda: now[0])
+    store.set("hb/1", repr(100.0))
+    sched = GenerationScheduler(FakeEngine(), max_batch=1, chunk_size=64, health=mon)
+
+    async def run():
+        srv = OpenAIServer(sched, ByteTokenizer(), EngineConfig(host="127.0.0.1", port=0), healthy=mon.is_healthy)
+        await srv.start()
+
+        async def get():
+            r, w = await asyncio.open_connection("127.0.0.1", srv.port)
+            w.write(b"GET /health HTTP/1.1\r\nHost: x\r\n\r\n")
+            await w.drain()
+            raw = await r.read()
+            w.close()
+            head, _, payload = raw.partition(b"\r\n\r\n")
+            return int(head.split()[1]), json.loads(payload)
+        mon.check_peers()
+        assert await get() == (200, {"status": "ok"})
+        now[0] = 110.0                                   # rank 1 has been silent for 10 s
+        mon.check_peers()
+        st, body = await get()
+        assert st == 503 and body["status"] == "unhealthy" and body["failed_ranks"] == [1] and "heartbeat" in body["reason"]
+        await srv.close()
+    asyncio.run(run())
