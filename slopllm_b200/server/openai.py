@@ -110,6 +110,9 @@ def normalize_messages(messages: List[dict]) -> List[dict]:
 
 
 class OpenAIServer:
+    READ_TIMEOUT_S = 30.0            # for the request head and for its body
+    MAX_BODY_BYTES = 64 << 20
+
     def __init__(self, scheduler: GenerationScheduler, tokenizer, cfg: EngineConfig, model_name: str = "glm",
                  max_model_len: int = 65536, healthy=lambda: True, log=None):
         self.sched = scheduler
@@ -138,7 +141,8 @@ class OpenAIServer:
 
     async def _client(self, reader: asyncio.StreamReader, writer: asyncio.StreamWriter) -> None:
         try:
-            head = await reader.readuntil(b"\r\n\r\n")
+            # a client that never finishes its request must not hold a connection for ever
+            head = await asyncio.wait_for(reader.readuntil(b"\r\n\r\n"), self.READ_TIMEOUT_S)
             lines = head.decode("latin1").split("\r\n")
             method, path, _ = lines[0].split(" ", 2)
             headers = {}
@@ -147,9 +151,13 @@ class OpenAIServer:
                     k, v = ln.split(":", 1)
                     headers[k.strip().lower()] = v.strip()
             n = int(headers.get("content-length", "0") or 0)
-            body = await reader.readexactly(n) if n else b""
+            if n > self.MAX_BODY_BYTES:
+                self._send(writer, 413, HttpError(413, f"request body of {n} bytes exceeds {self.MAX_BODY_BYTES}").body())
+                await writer.drain()
+                return
+            body = await asyncio.wait_for(reader.readexactly(n), self.READ_TIMEOUT_S) if n else b""
             await self._route(method, path.split("?")[0], headers, body, writer)
-        except (asyncio.IncompleteReadError, ConnectionError, ValueError):
+        except (asyncio.IncompleteReadError, asyncio.LimitOverrunError, asyncio.TimeoutError, ConnectionError, ValueError):
             pass
         finally:
             try:
@@ -161,7 +169,7 @@ class OpenAIServer:
     def _send(writer, status: int, body, ctype="application/json", extra: Optional[Dict[str, str]] = None) -> None:
         data = body if isinstance(body, (bytes, bytearray)) else (json.dumps(body) if not isinstance(body, str) else body).encode()
         reason = {200: "OK", 204: "No Content", 400: "Bad Request", 401: "Unauthorized", 403: "Forbidden", 404: "Not Found",
-                  405: "Method Not Allowed", 500: "Internal Server Error", 503: "Service Unavailable"}.get(status, "OK")
+                  405: "Method Not Allowed", 413: "Payload Too Large", 500: "Internal Server Error", 503: "Service Unavailable"}.get(status, "OK")
         hdr = {"Content-Type": ctype, "Content-Length": str(len(data)), "Connection": "close", **CORS, **(extra or {})}
         writer.write((f"HTTP/1.1 {status} {reason}\r\n" + "".join(f"{k}: {v}\r\n" for k, v in hdr.items()) + "\r\n").encode() + data)
 

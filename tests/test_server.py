@@ -164,6 +164,18 @@ def test_server_endpoints():
         st, body = await _http(port, "POST", "/v1/chat/completions", {"messages": [{"role": "user", "content": "x"}], "top_p": "a"}, auth)
         assert st == 400
         assert len(lines) >= 3 and all("decode_tokens_per_second=" in ln and "prompt_tokens=" in ln for ln in lines)
+        # a request that never completes its head is dropped after the read timeout; an oversized body is refused
+        srv.READ_TIMEOUT_S = 0.3
+        r, w = await asyncio.open_connection("127.0.0.1", port)
+        w.write(b"POST /v1/chat/completions HTTP/1.1\r\nHost: x\r\n")          # no blank line
+        await w.drain()
+        assert await asyncio.wait_for(r.read(), 5) == b""                            # the server closed the connection
+        w.close()
+        r, w = await asyncio.open_connection("127.0.0.1", port)
+        w.write(b"POST /v1/chat/completions HTTP/1.1\r\nHost: x\r\nContent-Length: 999999999999\r\n\r\n")
+        await w.drain()
+        assert (await asyncio.wait_for(r.read(), 5)).startswith(b"HTTP/1.1 413")
+        w.close()
         await srv.close()
 
     asyncio.run(run())
