@@ -135,10 +135,15 @@ def main(argv=None) -> int:
                           log=lambda line: print(line, file=sys.stderr, flush=True))
     print(f"listening on http://{args.host}:{args.port}  model={name}  ranks={ctx.global_world or ctx.world}  "
           f"replicas={ctx.dp_world}  mtp={args.mtp}", file=sys.stderr)
+    import signal
+
+    def _terminate(signum, frame):                       # `docker stop`, `kill`: same orderly exit as Ctrl-C
+        raise KeyboardInterrupt
+    signal.signal(signal.SIGTERM, _terminate)
     try:
         asyncio.run(serve(server))
     except KeyboardInterrupt:
-        pass
+        print("shutting down: stopping the schedulers of every rank and replica", file=sys.stderr)
     finally:
         for p in proxies:
             p.stop()
