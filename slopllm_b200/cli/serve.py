@@ -10,8 +10,8 @@ from __future__ import annotations
 
 import argparse
 import asyncio
-import sys
 import os
+import sys
 import time
 
 from .model_cli import add_model_args, build_runtime
