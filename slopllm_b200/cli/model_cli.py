@@ -102,14 +102,22 @@ def check_memory_plan(args, ctx: ParallelContext, model_dir: str, model_type: st
     """Before the weights are read: does this rank's share of the model plus the KV pages asked for fit the memory the
     process may use?  A plan that does not fit is reported on stderr (rank 0) and returned; loading still goes ahead, the
     estimate of the workspace is deliberately generous."""
-    if model_type != "glm_moe_dsa" or ctx.device.type != "cuda":
+    if model_type not in ("glm_moe_dsa", "qwen3", "qwen3_5") or ctx.device.type != "cuda":
         return None
     import sys
-    from ..checkpoint.loader import load_config
-    from ..utils.sizing import GIB, plan_memory
+    from ..utils.sizing import GIB, plan_dense, plan_memory
     total = torch.cuda.get_device_properties(ctx.device).total_memory
-    p = plan_memory(load_config(model_dir), world=ctx.world, cp=args.cp, ep=args.ep, mtp=args.mtp, batch_size=args.batch_size,
-                    chunk_size=args.chunk_size, max_pages=args.max_pages, arena_gb=args.arena, device_gb=total / GIB)
+    if model_type == "glm_moe_dsa":
+        from ..checkpoint.loader import load_config
+        p = plan_memory(load_config(model_dir), world=ctx.world, cp=args.cp, ep=args.ep, mtp=args.mtp, batch_size=args.batch_size,
+                        chunk_size=args.chunk_size, max_pages=args.max_pages, arena_gb=args.arena, device_gb=total / GIB)
+    else:
+        import json
+        from ..models.dense import DenseConfig
+        with open(os.path.join(model_dir, "config.json")) as f:
+            dcfg = DenseConfig.from_hf_dict(json.load(f))
+        p = plan_dense(dcfg, world=ctx.world, batch_size=args.batch_size, chunk_size=args.chunk_size, max_pages=args.max_pages,
+                       arena_gb=args.arena, device_gb=total / GIB)
     if p.requested_fits:
         return None
     msg = (f"memory plan: {p.weights_bytes / GIB:.1f} GiB of weights per rank + about {p.workspace_bytes / GIB:.1f} GiB of "
