@@ -205,3 +205,23 @@ def test_indexer_score_matrix_is_sized_by_context_and_blocked_by_budget():
     rows = CudaOps.score_rows_per_block(8192, 1 << 20)                       # 1M keys on one rank
     assert rows % 8 == 0 and 8 <= rows < 8192 and rows * (1 << 20) * 4 <= budget
     assert CudaOps.score_rows_per_block(8192, 1 << 28) == 8                  # never below one 8-row tile
+
+
+def test_runtime_library_exports_what_the_python_side_declares():
+    """Every `rt_*` function that `runtime/native_runtime.py` types is defined in the C++ runtime sources and exported by the
+    built library."""
+    import os
+    import re
+
+    import slopllm_b200
+    from slopllm_b200.ops import native as N
+    root = os.path.dirname(slopllm_b200.__file__)
+    declared = set(re.findall(r"lib\.(rt_\w+)", open(os.path.join(root, "runtime", "native_runtime.py")).read()))
+    defined = set()
+    for f in os.listdir(os.path.join(root, "csrc", "runtime")):
+        if f.endswith(".cpp"):
+            defined |= set(re.findall(r"RT_API\s+[\w\s\*]*?\b(rt_\w+)\s*\(", open(os.path.join(root, "csrc", "runtime", f)).read()))
+    assert len(declared) >= 18 and declared <= defined, sorted(declared - defined)
+    if os.path.exists(N.RUNTIME_SO):
+        lib = N.runtime()
+        assert not [n for n in sorted(declared) if not hasattr(lib, n)]
