@@ -14,20 +14,9 @@
 // on CUDA cores) and the MoE small-batch kernels (`:738-990`).
 #include "push.cuh"
 #include "route.cuh"
+#include "w4_frag.cuh"
 
 namespace {
-
-__device__ __forceinline__ void mma_f16_m16n8k16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-
-__device__ __forceinline__ __half2 e4m3x2_to_half2(uint16_t v) {
-    __half2_raw h = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)v, __NV_E4M3);
-    return *reinterpret_cast<__half2*>(&h);
-}
 
 // ---- activation staging --------------------------------------------------------------------------
 // x[T, K] bf16 -> f16 in fragment order in global scratch: 16-byte unit(token, group, j, c) holds
@@ -50,27 +39,6 @@ __global__ void permute_x_kernel(uint4* __restrict__ xp, const bf16* __restrict_
         const int group = u / 16, within = u % 16, c = within / 4, j = within % 4;
         xp[((size_t)tok * (K / 128) + group) * 16 + j * 4 + c] = v;
     }
-}
-
-// Expand one lane's 16 bytes (32 codes) of a row into 16 half2, scaled by the two block scales.
-__device__ __forceinline__ void expand_row(const uint4& w, uint16_t sc, __half2 (&out)[16]) {
-    const __half2 s = e4m3x2_to_half2(sc);
-    const __half2 s0 = __half2half2(__low2half(s)), s1 = __half2half2(__high2half(s));
-    const uint32_t words[4] = {w.x, w.y, w.z, w.w};
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-        __half2 h[4];
-        e2m1x8_to_half2x4(words[q], h);
-        const __half2 sq = q < 2 ? s0 : s1;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) out[q * 4 + i] = __hmul2(h[i], sq);
-    }
-}
-
-__device__ __forceinline__ uint4 ldg_ca_16(const void* p) {
-    uint4 v;
-    asm volatile("ld.global.ca.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-    return v;
 }
 
 // One warp: MT tiles of 16 rows x NT*8 tokens over the groups kpart, kpart+ksplit, ... of the row's K.
@@ -239,6 +207,15 @@ static int dispatch_linear(void* y, const void* x, void* xp, const void* Wp, con
     if (T <= 16) return launch_linear<1, 2>(y, x, xp, Wp, S, g, T, N, K, ldx, out_f32, push, s);
     if (T <= 24) return launch_linear<2, 3>(y, x, xp, Wp, S, g, T, N, K, ldx, out_f32, push, s);
     return launch_linear<2, 4>(y, x, xp, Wp, S, g, T, N, K, ldx, out_f32, push, s);
+}
+
+// xp = permuted f16 copy of x[T, K] (bf16, row stride ldx), rows T .. ceil(T/8)*8 - 1 zero.  K % 128 == 0, ldx % 8 == 0.
+SL_API int sl_permute_x(void* xp, const void* x, int T, int K, int ldx, cudaStream_t s) {
+    if (T == 0) return 0;
+    if (K % 128 != 0 || ldx % 8 != 0) return -1;
+    const int tpad = (T + 7) / 8 * 8, units = tpad * (K / 8);
+    sl_launch(permute_x_kernel, (units + 255) / 256, 256, 0, s, (uint4*)xp, (const bf16*)x, T, tpad, K, ldx);
+    return (int)cudaGetLastError();
 }
 
 // y[T, N] = g * x[T, K] . dequant(Wp, S)^T for 1 <= T <= 32.  K % 128 == 0, ldx % 8 == 0.

@@ -275,17 +275,20 @@ def random_layer(cfg: GlmMoeDsaConfig, layer: int, seed: int, device, dtype, tp_
         g = _gen(seed * 1000003 + layer * 64 + r, device)
         gdev = device
         hh, rr, WW = hl, 0, 1      # generate local shapes directly
+    # tensors that every rank holds in full (q_a / kv_a, indexer, router, MTP eh_proj) must be identical on all ranks:
+    # they come from a generator that does not depend on the rank (slot 63 of the layer's seed range; ranks use 0..7)
+    gr = g if exact else _gen(seed * 1000003 + layer * 64 + 63, device)
     ones = lambda n: torch.ones(n, device=gdev, dtype=dtype)
 
-    parts = [_dense((cfg.q_lora_rank, H), g, gdev, dtype), _dense((R, H), g, gdev, dtype), _dense((Dr, H), g, gdev, dtype)]
+    parts = [_dense((cfg.q_lora_rank, H), gr, gdev, dtype), _dense((R, H), gr, gdev, dtype), _dense((Dr, H), gr, gdev, dtype)]
     wq_b = _dense((hh * (Dn + Dr), cfg.q_lora_rank), g, gdev, dtype)
     w_kn = _dense((hh, Dn, R), g, gdev, dtype)
     w_v = _dense((hh, R, Dv), g, gdev, dtype)
     o_proj = _rand_linear(H, hh * Dv, g, gdev, dtype, cfg.quant_o_proj)
     idx_parts = None
     if full_idx:
-        idx_parts = [_dense((Di, H), g, gdev, dtype), _dense((Hi, H), g, gdev, dtype)]
-        idx_wq_b = _dense((Hi * Di, cfg.q_lora_rank), g, gdev, dtype)
+        idx_parts = [_dense((Di, H), gr, gdev, dtype), _dense((Hi, H), gr, gdev, dtype)]
+        idx_wq_b = _dense((Hi * Di, cfg.q_lora_rank), gr, gdev, dtype)
     if exact and W > 1:
         wq_b = wq_b.reshape(h, Dn + Dr, -1)[r * hl:(r + 1) * hl].reshape(hl * (Dn + Dr), -1)
         w_kn, w_v = w_kn[r * hl:(r + 1) * hl], w_v[r * hl:(r + 1) * hl]
@@ -302,7 +305,7 @@ def random_layer(cfg: GlmMoeDsaConfig, layer: int, seed: int, device, dtype, tp_
     )
     if cfg.is_moe_layer(layer):
         E, I = cfg.n_routed_experts, cfg.moe_intermediate_size
-        lw.router_w = _dense((E, H), g, gdev, dtype, std=0.1)
+        lw.router_w = _dense((E, H), gr, gdev, dtype, std=0.1)
         lw.router_bias = torch.zeros(E, device=gdev, dtype=torch.float32)
         if exact:
             ex = _rand_experts(E, I, H, g, gdev, dtype, cfg.quant_experts)
@@ -333,7 +336,7 @@ def random_layer(cfg: GlmMoeDsaConfig, layer: int, seed: int, device, dtype, tp_
         lw.mlp_w13, lw.mlp_w2 = w13, w2
     if is_mtp:
         lw.enorm, lw.hnorm, lw.shared_head_norm = ones(H), ones(H), ones(H)
-        lw.eh_proj = LinearWeight(_dense((H, 2 * H), g, gdev, dtype))
+        lw.eh_proj = LinearWeight(_dense((H, 2 * H), gr, gdev, dtype))
     return layer_to(lw, device, dtype)
 
 

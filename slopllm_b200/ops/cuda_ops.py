@@ -53,6 +53,8 @@ class CudaOps:
         self.ctx = ctx
         N.kernels()            # fail loudly when the native library is missing
         self._counters = {}
+        from ..config import env_str
+        self._persist_moe = env_str("MOE_PERSIST") != "0"
 
     # -- helpers ----------------------------------------------------------------------------
     @staticmethod
@@ -475,6 +477,10 @@ class CudaOps:
         I = experts.inter
         routes = T * k + (T if shared is not None else 0)
         max_items = T * k + (T + 7) // 8
+        if self._persist_moe and (shared is None or shared.inter == I) and N.fn("sl_moe_persist_ok")(
+                T, k, H, I, router.router_w.shape[0] if router is not None else 0, experts.num_experts,
+                int(router is not None)):
+            return self._moe_persist(x, experts, shared, ids, wts, sink, router, routes, max_items)
         xp = self._perm_of(x, T, H)
         xp_ready = xp is not None
         if not xp_ready:
@@ -501,6 +507,65 @@ class CudaOps:
         N.call("sl_moe_grouped_mma", C.byref(a), C.cast(C.byref(rargs), C.c_void_p) if rargs is not None else None, None,
                N.stream())
         return out
+
+    def _moe_persist(self, x, experts, shared, ids, wts, sink, router, routes, max_items):
+        """The whole decode MoE layer in one persistent kernel (`csrc/moe_persist.cu`): router tiles, plan, gate/up, down and
+        the weighted sum are tiles of one ordered queue with completion counters instead of five launches."""
+        T, H = x.shape
+        dev = x.device
+        c = self.cfg
+        k, I = ids.shape[1], experts.inter
+        xp = self._perm_of(x, T, H)
+        if xp is None:
+            xp = torch.empty(((T + 7) // 8) * 8 * H, dtype=torch.float16, device=dev)
+            N.call("sl_permute_x", xp.data_ptr(), x.data_ptr(), T, H, x.stride(0), N.stream())
+        E = router.router_w.shape[0] if router is not None else 0
+        slabs = torch.empty(4 * T * max(E, 1), dtype=torch.float32, device=dev)
+        act = torch.empty((routes + 8) * I, dtype=torch.float16, device=dev)
+        y_route = torch.empty(routes, H, dtype=torch.float32, device=dev)
+        plan = torch.empty(max_items * 9 + 1, dtype=torch.int32, device=dev)
+        out = None if sink is not None else torch.empty(T, H, dtype=torch.float32, device=dev)
+        sync = self._persist_sync(dev)
+        a = N.MoePersistArgs(
+            x=x.data_ptr(), ldx=x.stride(0), xp=xp.data_ptr(), router_w=N.ptr(router.router_w) if router is not None else 0,
+            bias=N.ptr(router.router_bias) if router is not None else 0, E=E, n_group=c.n_group, topk_group=c.topk_group,
+            norm=int(c.norm_topk_prob), scale=float(c.routed_scaling_factor), T=T, top_k=k, H=H, I=I,
+            expert_offset=experts.expert_offset, num_local=experts.num_experts,
+            w13=experts.w13.data_ptr(), s13=experts.s13.data_ptr(), g13=experts.g13.data_ptr(),
+            sw13=N.ptr(shared.w13) if shared else 0, ss13=N.ptr(shared.s13) if shared else 0, sg13=N.ptr(shared.g13) if shared else 0,
+            w2=experts.w2.data_ptr(), s2=experts.s2.data_ptr(), g2=experts.g2.data_ptr(),
+            sw2=N.ptr(shared.w2) if shared else 0, ss2=N.ptr(shared.s2) if shared else 0, sg2=N.ptr(shared.g2) if shared else 0,
+            slabs=slabs.data_ptr(), act_perm=act.data_ptr(), y_route=y_route.data_ptr(), plan=plan.data_ptr(),
+            ids=ids.data_ptr(), wts=wts.data_ptr(), sync=sync.data_ptr(), status=sync.data_ptr() + 4 * self.PERSIST_STATUS_WORD,
+            out=N.ptr(out), max_items=max_items, gsub=0)
+        if sink is not None:
+            sink.pushed_rows = T
+            N.call("sl_moe_persist", C.byref(a), C.cast(C.byref(sink.push), C.c_void_p), N.stream())
+            return sink
+        N.call("sl_moe_persist", C.byref(a), None, N.stream())
+        return out
+
+    PERSIST_SYNC_WORDS = 512          # tile queue + completion counters of the persistent kernels (zero between launches)
+    PERSIST_STATUS_WORD = 512         # followed by four status words {code, site, expected, seen}
+
+    def _persist_sync(self, dev) -> torch.Tensor:
+        key = ("persist", dev.type, dev.index)
+        t = self._counters.get(key)
+        if t is None:
+            t = torch.zeros(self.PERSIST_SYNC_WORDS + 4, dtype=torch.int32, device=dev)
+            self._counters[key] = t
+        return t
+
+    def check_persistent_status(self) -> None:
+        """Raise if a persistent kernel gave up on one of its bounded waits since the last call (and reset its counters,
+        which a kernel that gave up leaves as they were)."""
+        for key, t in self._counters.items():
+            if not (isinstance(key, tuple) and key[0] == "persist"):
+                continue
+            st = t[self.PERSIST_STATUS_WORD:].tolist()
+            if st[0]:
+                t.zero_()
+                raise N.NativeError(f"persistent kernel wait expired at site {st[1]} (expected {st[2]}, saw {st[3]})")
 
     @staticmethod
     def _guard(dev) -> int:

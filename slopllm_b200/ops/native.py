@@ -132,6 +132,15 @@ class MoeGroupedArgs(C.Structure):
                 ("act_perm", vp), ("y_route", vp), ("plan", vp), ("max_items", i32), ("out", vp), ("xp_ready", i32)]
 
 
+class MoePersistArgs(C.Structure):
+    _fields_ = [("x", vp), ("ldx", i32), ("xp", vp), ("router_w", vp), ("bias", vp), ("E", i32), ("n_group", i32),
+                ("topk_group", i32), ("norm", i32), ("scale", f32), ("T", i32), ("top_k", i32), ("H", i32), ("I", i32),
+                ("expert_offset", i32), ("num_local", i32), ("w13", vp), ("s13", vp), ("g13", vp), ("sw13", vp), ("ss13", vp),
+                ("sg13", vp), ("w2", vp), ("s2", vp), ("g2", vp), ("sw2", vp), ("ss2", vp), ("sg2", vp), ("slabs", vp),
+                ("act_perm", vp), ("y_route", vp), ("plan", vp), ("ids", vp), ("wts", vp), ("sync", vp), ("status", vp),
+                ("out", vp), ("max_items", i32), ("gsub", i32)]
+
+
 class MoeRouterArgs(C.Structure):
     _fields_ = [("router_w", vp), ("bias", vp), ("E", i32), ("n_group", i32), ("topk_group", i32), ("norm", i32),
                 ("scale", f32), ("slabs", vp), ("counter", vp)]
@@ -197,6 +206,9 @@ _SIGS = {
     "sl_spec_reject": [C.POINTER(SpecRejectParams), i32, vp],
     "sl_advance_counter": [vp, u32, vp],
     "sl_moe_grouped_mma": [C.POINTER(MoeGroupedArgs), vp, vp, vp],
+    "sl_moe_persist": [C.POINTER(MoePersistArgs), vp, vp],
+    "sl_moe_persist_ok": [i32, i32, i32, i32, i32, i32, i32],
+    "sl_permute_x": [vp, vp, i32, i32, i32, vp],
     "sl_linear_nvfp4_mma": [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp],
     "sl_linear_smallT_bf16_tcgen05": [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp, vp, i32, vp],
     "sl_grouped_gemm_bf16_tcgen05": [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, vp, vp, i32, vp, i32, vp],

@@ -342,9 +342,39 @@ def test_moe_fused_router_glm5_routing(T):
     unfused = ops._moe_small(x, lw.experts, lw.shared, ids, wts)
     close(fused, unfused, tol=2e-3, what="fused vs unfused router")
     close(fused, ref.moe_tp(x, lw), tol=2e-2, what="fused router vs reference")
-    # the kernel must leave its ticket counter at zero for the next call
+    # the kernels must leave their counters at zero for the next call
     assert int(ops._zero_counter(x.device).item()) == 0
+    assert int(ops._persist_sync(x.device).abs().sum().item()) == 0
     close(ops.moe_tp(x, lw), fused, tol=1e-6, what="second call")
+
+
+@pytest.mark.parametrize("T,H,I,E,k,ng,tg", [
+    (1, 1024, 256, 256, 8, 8, 4), (8, 1024, 256, 256, 8, 8, 4), (32, 1024, 256, 256, 8, 8, 4),
+    (5, 2048, 512, 16, 4, 4, 2), (19, 2048, 1024, 16, 4, 1, 1), (8, 3072, 128, 32, 4, 1, 1),
+    (8, 6144, 256, 256, 8, 8, 4), (4, 6144, 2048, 32, 8, 1, 1)])
+def test_moe_persistent_kernel_matches_five_launch_path(T, H, I, E, k, ng, tg):
+    """The one-launch persistent MoE layer (tile queue + completion counters) against the five-launch path with the
+    same arithmetic, against the fp32 reference, and twice in a row (its counters must be back at zero)."""
+    cfg = mini_cfg(hidden_size=H, moe_intermediate_size=I, n_routed_experts=E, num_experts_per_tok=k, n_group=ng, topk_group=tg)
+    ops, ref = cuda_ops(cfg), RefOps(cfg)
+    assert ops._persist_moe
+    lw = random_layer(cfg, 1, 0, DEV, torch.bfloat16)
+    x = torch.randn(T, H, device=DEV, generator=torch.Generator(device=DEV).manual_seed(T)).to(torch.bfloat16)
+    fused = ops.moe_tp(x, lw)
+    torch.cuda.synchronize()
+    ops.check_persistent_status()
+    sync = ops._persist_sync(x.device)
+    assert int(sync.abs().sum().item()) == 0, sync[:16].tolist()
+    ops._persist_moe = False
+    old = ops.moe_tp(x, lw)
+    ops._persist_moe = True
+    close(fused, old, tol=2e-3, what="persistent vs five-launch")
+    close(fused, ref.moe_tp(x, lw), tol=2e-2, what="persistent vs reference")
+    close(ops.moe_tp(x, lw), fused, tol=1e-6, what="second call")
+    # given routes (no router stage): the form that expert parallelism and the small-batch path call
+    ids, wts = ops.route(x, lw)
+    close(ops._moe_small(x, lw.experts, lw.shared, ids, wts), fused, tol=2e-3, what="given routes")
+    ops.check_persistent_status()
 
 
 @pytest.mark.parametrize("T", [1, 5, 8, 19])
