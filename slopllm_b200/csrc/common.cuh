@@ -66,6 +66,8 @@ __device__ __forceinline__ void prefetch_l2_rows(const void* base, int rows, siz
 
 // Process-wide switch (sl_set_pdl); on by default.
 extern int g_sl_pdl_enabled;
+// Kernels launched through sl_launch since the library was loaded (sl_kernel_launches): what a captured step really costs.
+extern unsigned long long g_sl_kernel_launches;
 
 template <typename... KArgs, typename... Args>
 inline cudaError_t sl_launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args&&... args) {
@@ -79,6 +81,7 @@ inline cudaError_t sl_launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = g_sl_pdl_enabled ? 1 : 0;
+    ++g_sl_kernel_launches;
     return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
 }
 

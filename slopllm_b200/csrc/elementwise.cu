@@ -9,6 +9,8 @@
 #include "route.cuh"
 
 int g_sl_pdl_enabled = 1;
+unsigned long long g_sl_kernel_launches = 0;
+SL_API unsigned long long sl_kernel_launches() { return g_sl_kernel_launches; }
 // Turns programmatic dependent launch of the library's kernels on or off (process-wide).
 SL_API void sl_set_pdl(int enabled) { g_sl_pdl_enabled = enabled ? 1 : 0; }
 

@@ -60,6 +60,11 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m
         "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
         ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2) : "memory");
 }
+// Untiled bulk copy global -> shared (no multicast): both addresses 16-byte aligned, `bytes` a multiple of 16.
+__device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(smem_dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
@@ -93,6 +98,23 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
     return d;
 }
 
+// Rows of 16 bytes, 8-row groups of 128 contiguous bytes, no swizzle: the source of a `tcgen05.cp` of scale factors.
+__device__ __forceinline__ uint64_t smem_desc_rows16(uint32_t addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)1 << 16;                            // leading byte offset: 16 bytes (one column of core matrices only)
+    d |= (uint64_t)(128 >> 4) << 32;                   // stride byte offset: next 8-row group
+    d |= (uint64_t)1 << 46;                            // descriptor version (sm_100)
+    return d;                                          // layout type 0: no swizzle
+}
+
+// kind::mxf4nvf4 (E2M1 operands, UE4M3 scale per 16 elements, K = 64 per instruction), fp32 accumulation, both
+// operands K-major.  Bits: a/b format E2M1 = 1 at [7,10) / [10,13), N >> 3 at [17,23), scale format UE4M3 = 0 at [23],
+// M >> 4 at [24,29), scale-factor ids (byte offsets inside a TMEM column) zero.
+__host__ __device__ constexpr uint32_t idesc_nvf4(int M, int N) {
+    return (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
 // kind::f16 with bf16 (1) or f16 (0) inputs and fp32 accumulation, both operands K-major.
 __host__ __device__ constexpr uint32_t idesc_f16(int M, int N, int ab_format) {
     return (1u << 4) | ((uint32_t)ab_format << 7) | ((uint32_t)ab_format << 10) | ((uint32_t)(N >> 3) << 17) |
@@ -122,6 +144,22 @@ __device__ __forceinline__ void mma_f8_ss(uint32_t tmem_d, uint64_t adesc, uint6
         "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n"
         "}\n"
         ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// D[tmem] (+)= (A x scale_a) * (B x scale_b) with packed E2M1 operands in shared memory and UE4M3 scales (one per 16
+// elements) in TMEM: `sfa` / `sfb` are the TMEM columns holding the scales of this instruction's 64 reduction indices.
+__device__ __forceinline__ void mma_nvf4_ss(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t sfa, uint32_t sfb,
+                                            uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;\n"
+        "}\n"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb) : "memory");
+}
+// Scale factors shared memory -> TMEM: 32 rows x 16 bytes, written to the same 4 columns of all four lane quarters.
+__device__ __forceinline__ void cp_sf_32x128b(uint32_t tmem_dst, uint64_t sdesc) {
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem_dst), "l"(sdesc) : "memory");
 }
 // Arrive on an mbarrier once all previously issued MMAs of this thread have completed.
 __device__ __forceinline__ void mma_commit(uint64_t* bar) {
@@ -174,5 +212,36 @@ static inline int make_tmap_2d(CUtensorMap* map, const void* base, CUtensorMapDa
     cuuint32_t estr[2] = {1, 1};
     CUresult r = enc(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : -102;
+}
+
+// Unswizzled 3D tensor [planes, rows, 16 bytes] (plane stride rows * 16 bytes); box = [box_planes, box_rows, 16 bytes].
+static inline int make_tmap_3d_rows16(CUtensorMap* map, const void* base, uint64_t planes, uint64_t rows, uint32_t box_planes,
+                                      uint32_t box_rows) {
+    PFN_encodeTiled enc = get_encode_tiled();
+    if (enc == nullptr) return -100;
+    if (((uintptr_t)base & 15) != 0) return -101;
+    cuuint64_t dims[3] = {16, rows, planes};
+    cuuint64_t strides[2] = {16, rows * 16};
+    cuuint32_t box[3] = {16, box_rows, box_planes};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : -102;
+}
+
+// Same tensor, unswizzled box of [box_rows, box_cols] elements (box_cols * elem_bytes a multiple of 16).
+static inline int make_tmap_2d_plain(CUtensorMap* map, const void* base, CUtensorMapDataType dt, int elem_bytes, uint64_t rows,
+                                     uint64_t cols, uint64_t row_stride_bytes, uint32_t box_rows, uint32_t box_cols) {
+    PFN_encodeTiled enc = get_encode_tiled();
+    if (enc == nullptr) return -100;
+    if (((uintptr_t)base & 15) != 0 || (row_stride_bytes & 15) != 0 || (box_cols * elem_bytes) % 16 != 0) return -101;
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {row_stride_bytes};
+    cuuint32_t box[2] = {box_cols, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? 0 : -102;
 }

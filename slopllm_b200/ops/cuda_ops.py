@@ -54,7 +54,11 @@ class CudaOps:
         N.kernels()            # fail loudly when the native library is missing
         self._counters = {}
         from ..config import env_str
-        self._persist_moe = env_str("MOE_PERSIST") != "0"
+        # one-launch persistent decode MoE (csrc/moe_persist.cu): opt-in.  Its NVFP4 -> f16 expansion is bound by the
+        # conversion rate of the CUDA cores just like the five-launch path, which it does not yet beat below 32 rows
+        self._persist_moe = env_str("MOE_PERSIST") == "1"
+        self._persist_gsub = 0         # gate/up sub-tiles per tile of the persistent MoE kernel (0: the kernel's default)
+        self._persist_trace = None     # u64 [SMs, 96, 4] tile timeline, filled when set (profiling)
 
     # -- helpers ----------------------------------------------------------------------------
     @staticmethod
@@ -536,8 +540,8 @@ class CudaOps:
             w2=experts.w2.data_ptr(), s2=experts.s2.data_ptr(), g2=experts.g2.data_ptr(),
             sw2=N.ptr(shared.w2) if shared else 0, ss2=N.ptr(shared.s2) if shared else 0, sg2=N.ptr(shared.g2) if shared else 0,
             slabs=slabs.data_ptr(), act_perm=act.data_ptr(), y_route=y_route.data_ptr(), plan=plan.data_ptr(),
-            ids=ids.data_ptr(), wts=wts.data_ptr(), sync=sync.data_ptr(), status=sync.data_ptr() + 4 * self.PERSIST_STATUS_WORD,
-            out=N.ptr(out), max_items=max_items, gsub=0)
+            ids=ids.data_ptr(), wts=wts.data_ptr(), sync=sync.data_ptr(), status=self._guard(dev) + 16,
+            out=N.ptr(out), max_items=max_items, gsub=self._persist_gsub, trace=N.ptr(self._persist_trace))
         if sink is not None:
             sink.pushed_rows = T
             N.call("sl_moe_persist", C.byref(a), C.cast(C.byref(sink.push), C.c_void_p), N.stream())
@@ -546,26 +550,24 @@ class CudaOps:
         return out
 
     PERSIST_SYNC_WORDS = 512          # tile queue + completion counters of the persistent kernels (zero between launches)
-    PERSIST_STATUS_WORD = 512         # followed by four status words {code, site, expected, seen}
 
     def _persist_sync(self, dev) -> torch.Tensor:
         key = ("persist", dev.type, dev.index)
         t = self._counters.get(key)
         if t is None:
-            t = torch.zeros(self.PERSIST_SYNC_WORDS + 4, dtype=torch.int32, device=dev)
+            from . import tcgen05
+            t = torch.zeros(self.PERSIST_SYNC_WORDS, dtype=torch.int32, device=dev)
             self._counters[key] = t
+            tcgen05.on_error_reset(dev, t.zero_)        # a kernel that gave up leaves its counters as they were
         return t
 
     def check_persistent_status(self) -> None:
-        """Raise if a persistent kernel gave up on one of its bounded waits since the last call (and reset its counters,
-        which a kernel that gave up leaves as they were)."""
-        for key, t in self._counters.items():
-            if not (isinstance(key, tuple) and key[0] == "persist"):
-                continue
-            st = t[self.PERSIST_STATUS_WORD:].tolist()
-            if st[0]:
-                t.zero_()
-                raise N.NativeError(f"persistent kernel wait expired at site {st[1]} (expected {st[2]}, saw {st[3]})")
+        """Raise if a kernel recorded an expired wait or a failed self-check since the last call (status words 8..11 of the
+        device's error block belong to the persistent kernels)."""
+        from . import tcgen05
+        for key in list(self._counters):
+            if isinstance(key, tuple) and key[0] == "persist":
+                tcgen05.check_errors(torch.device(key[1], key[2]))
 
     @staticmethod
     def _guard(dev) -> int:

@@ -1,0 +1,104 @@
+"""NVFP4 x NVFP4 products on the block-scaled tensor-core path (`csrc/gemm_fp4_tcgen05.cu`): weights stay packed E2M1
+with their UE4M3 block scales, activation rows are quantised to the same format on the fly (W4A4), and
+`tcgen05.mma.kind::mxf4nvf4` applies both sets of scales inside the instruction.
+
+The reference keeps activations in 16 bits and expands the weights before its MMA (`csrc/glm_mma_moe_coop.cu:351`);
+this path trades a small, bounded activation error for tensor-core rates that the expansion cannot reach.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from . import native as N
+from . import tcgen05
+
+vp, i32 = N.vp, N.i32
+N._SIGS.update({
+    "sl_fp4_build_tiles": [vp, vp, vp, i32, i32, i32, i32, i32, vp],
+    "sl_gemm_fp4_tcgen05": [vp, vp, vp, i32, vp, vp, vp, i32, vp, i32, i32, i32, i32, i32, vp, vp, i32, vp, vp],
+    "sl_nvfp4_sf_tiles": [vp, vp, i32, i32, i32, vp],
+    "sl_nvfp4_quantize_rows": [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp],
+})
+
+OUT_BF16, OUT_F32 = 0, 1
+
+
+def shapes_ok(rows: int, K: int) -> bool:
+    """Weight matrices the block-scaled kernel takes: whole 128-row tiles, reduction length a multiple of 256."""
+    return rows % 128 == 0 and K % 256 == 0 and K > 0
+
+
+def sf_tiles(scale: torch.Tensor) -> torch.Tensor:
+    """Row-major e4m3 block scales [..., rows, K/16] -> the 512-byte tile layout the kernel loads (one uint8 tensor)."""
+    s8 = scale.contiguous().view(torch.uint8)
+    *lead, rows, kb = s8.shape
+    mats = 1
+    for d in lead:
+        mats *= d
+    out = torch.empty(mats * rows * kb, dtype=torch.uint8, device=s8.device)
+    N.call("sl_nvfp4_sf_tiles", out.data_ptr(), s8.data_ptr(), mats, rows, kb * 16, N.stream())
+    return out
+
+
+def quantize_rows(x: torch.Tensor, src: Optional[torch.Tensor] = None, rows: Optional[int] = None,
+                  terms: int = 1) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """bf16 rows -> (codes u8 [M * terms, K/2], scales u8 [K/64, M * terms, 16] (four e4m3 scales, then padding),
+    global scales f32 [M * terms]).
+    With `src` output row m quantises x[src[m]] (a gather, e.g. into expert-sorted order); with `terms` > 1 rows
+    m + j * M hold the j-th residual of row m, so that the sum of the terms approaches the 16-bit value."""
+    assert x.dtype == torch.bfloat16 and x.stride(-1) == 1
+    M = x.shape[0] if src is None else (src.numel() if rows is None else rows)
+    K = x.shape[1]
+    dev = x.device
+    q = torch.empty(M * terms, K // 2, dtype=torch.uint8, device=dev)
+    sf = torch.zeros(K // 64, M * terms, 16, dtype=torch.uint8, device=dev)
+    g = torch.empty(M * terms, dtype=torch.float32, device=dev)
+    N.call("sl_nvfp4_quantize_rows", q.data_ptr(), sf.data_ptr(), g.data_ptr(), x.data_ptr(), N.ptr(src), M, x.shape[0], K,
+           x.stride(0), terms, N.stream())
+    return q, sf, g
+
+
+def scales_row_major(sf: torch.Tensor) -> torch.Tensor:
+    """The quantiser's scale layout [K/64, rows, 16] -> row-major e4m3 bytes [rows, K/16]."""
+    return sf[:, :, :4].permute(1, 0, 2).reshape(sf.shape[1], -1).contiguous()
+
+
+def pick_bn(rows_per_group: float) -> int:
+    return 128 if rows_per_group > 64 else (64 if rows_per_group > 32 else 32)
+
+
+def grouped_gemm_fp4(wq: torch.Tensor, sfa: torch.Tensor, gA: torch.Tensor, xq: torch.Tensor, sfb: torch.Tensor, gB: torch.Tensor,
+                     offsets: torch.Tensor, Nn: int, pair: bool, out_kind: int = OUT_BF16, bn: int = 0) -> torch.Tensor:
+    """out[r, :Nn] for token rows r in [offsets[g], offsets[g+1]) = X[r] . W[g]^T (pair: silu(gate) * up).
+    wq [G, Nn (pair: 2 Nn), K/2] packed weights, sfa their scale tiles (`sf_tiles`), gA [G] (pair: [G, 2]) fp32;
+    xq / sfb / gB from `quantize_rows`; offsets int32 [G + 1] on the device."""
+    G = wq.shape[0]
+    K = wq.shape[-1] * 2
+    M = xq.shape[0]
+    dev = xq.device
+    if bn == 0:
+        bn = pick_bn(M / max(1, G))
+    pad = 4 if out_kind == OUT_F32 else 8
+    ld = (Nn + pad - 1) // pad * pad
+    out = torch.empty(M, ld, dtype=torch.float32 if out_kind == OUT_F32 else torch.bfloat16, device=dev)[:, :Nn]
+    max_tiles = ((M + bn - 1) // bn + G) * (Nn // 128)
+    tile_bytes = N.kernels().sl_fp4_tile_bytes()
+    tiles = torch.empty(max_tiles * tile_bytes, dtype=torch.uint8, device=dev)
+    ntiles = torch.empty(1, dtype=torch.int32, device=dev)
+    N.call("sl_fp4_build_tiles", tiles.data_ptr(), ntiles.data_ptr(), offsets.data_ptr(), G, Nn, int(pair), bn, max_tiles, N.stream())
+    gA = gA.to(torch.float32).contiguous()
+    w_rows = wq.shape[0] * wq.shape[1]
+    N.call("sl_gemm_fp4_tcgen05", wq.data_ptr(), sfa.data_ptr(), gA.data_ptr(), w_rows, xq.data_ptr(), sfb.data_ptr(), gB.data_ptr(),
+           M, out.data_ptr(), out.stride(0), out_kind, K, int(pair), bn, tiles.data_ptr(), ntiles.data_ptr(), max_tiles,
+           tcgen05.error_flag(dev).data_ptr(), N.stream())
+    return out
+
+
+def gemm_fp4(wq: torch.Tensor, sfa: torch.Tensor, gA: torch.Tensor, xq: torch.Tensor, sfb: torch.Tensor, gB: torch.Tensor,
+             out_kind: int = OUT_BF16, bn: int = 0) -> torch.Tensor:
+    """Plain product: one weight matrix wq [Nn, K/2], all token rows."""
+    M = xq.shape[0]
+    offsets = torch.tensor([0, M], dtype=torch.int32, device=xq.device)
+    return grouped_gemm_fp4(wq.unsqueeze(0), sfa, gA.reshape(1), xq, sfb, gB, offsets, wq.shape[0], False, out_kind, bn or pick_bn(M))

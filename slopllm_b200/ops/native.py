@@ -25,6 +25,10 @@ class NativeError(RuntimeError):
     pass
 
 
+class CollectiveTimeout(RuntimeError):
+    """A device-side bounded wait expired (a peer did not publish its flag in time)."""
+
+
 @lru_cache(maxsize=None)
 def kernels() -> C.CDLL:
     if not os.path.exists(KERNELS_SO):
@@ -138,7 +142,7 @@ class MoePersistArgs(C.Structure):
                 ("expert_offset", i32), ("num_local", i32), ("w13", vp), ("s13", vp), ("g13", vp), ("sw13", vp), ("ss13", vp),
                 ("sg13", vp), ("w2", vp), ("s2", vp), ("g2", vp), ("sw2", vp), ("ss2", vp), ("sg2", vp), ("slabs", vp),
                 ("act_perm", vp), ("y_route", vp), ("plan", vp), ("ids", vp), ("wts", vp), ("sync", vp), ("status", vp),
-                ("out", vp), ("max_items", i32), ("gsub", i32)]
+                ("out", vp), ("max_items", i32), ("gsub", i32), ("trace", vp)]
 
 
 class MoeRouterArgs(C.Structure):
@@ -235,6 +239,14 @@ _launches = 0
 def launch_count() -> int:
     """Number of native kernel-launching calls made so far by this process."""
     return _launches
+
+
+def kernel_count() -> int:
+    """Number of CUDA kernels the library has launched so far (one native call may launch several)."""
+    f = kernels().sl_kernel_launches
+    f.restype = C.c_ulonglong
+    f.argtypes = []
+    return int(f())
 
 
 def call(name: str, *args) -> None:

@@ -6,24 +6,43 @@ import torch
 from . import native as N
 
 _err = {}
+_reset_hooks = {}
+
+ERROR_WORDS = 16        # [0] tcgen05 expired wait, [4..7] index self-check, [8..11] persistent-kernel wait, [12..15] collective wait
 
 
 def error_flag(device) -> torch.Tensor:
-    """Per-device int32 word that kernels set when one of their bounded waits expires."""
+    """Per-device block of int32 status words that kernels write when a bounded wait expires or an index self-check
+    fails: one place, so that the engine reads everything back with the step's result in a single copy."""
     key = torch.device(device).index or 0
     if key not in _err:
-        _err[key] = torch.zeros(8, dtype=torch.int32, device=device)     # [0] expired wait, [4..7] index self-check record
+        _err[key] = torch.zeros(ERROR_WORDS, dtype=torch.int32, device=device)
     return _err[key]
 
 
-def check_errors(device) -> None:
-    words = error_flag(device).tolist()
+def on_error_reset(device, hook) -> None:
+    """`hook()` runs when an error of this device is reported (kernels that gave up leave their counters as they were)."""
+    _reset_hooks.setdefault(torch.device(device).index or 0, []).append(hook)
+
+
+def raise_for(words, device) -> None:
+    """Turn a host copy of the status block into an exception (and clear the device block)."""
+    if not any(words[i] for i in (0, 4, 8, 12)):
+        return
+    error_flag(device).zero_()
+    for hook in _reset_hooks.get(torch.device(device).index or 0, []):
+        hook()
+    if words[12]:
+        raise N.CollectiveTimeout(f"device wait on a peer expired at site {words[13]} (expected flag {words[14]}, saw {words[15]})")
+    if words[8]:
+        raise N.NativeError(f"persistent kernel wait expired at site {words[9]} (expected {words[10]}, saw {words[11]})")
     if words[0]:
-        error_flag(device).zero_()
         raise N.NativeError(f"tcgen05 kernel reported an expired wait (site {words[0]})")
-    if words[4]:
-        error_flag(device).zero_()
-        raise N.NativeError(f"index self-check failed at site {words[4]}: value {words[5]} outside [0, {words[6]}) in block {words[7]}")
+    raise N.NativeError(f"index self-check failed at site {words[4]}: value {words[5]} outside [0, {words[6]}) in block {words[7]}")
+
+
+def check_errors(device) -> None:
+    raise_for(error_flag(device).tolist(), device)
 
 
 def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out_f32: bool = False, bn: int = 0) -> torch.Tensor:

@@ -83,8 +83,7 @@ N._SIGS.update({
 })
 
 
-class CollectiveTimeout(RuntimeError):
-    """A device-side bounded wait expired (a peer did not publish its flag in time)."""
+CollectiveTimeout = N.CollectiveTimeout      # a device-side bounded wait expired (a peer did not publish its flag in time)
 
 
 class PushSink:
@@ -149,7 +148,8 @@ class SymmetricRegion:
     GUARD_PATTERN = 0xA5
 
     def __init__(self, rank: int, world: int, slot_rows: int, row_len: int, local: torch.Tensor, peer_ptrs: List[int],
-                 gather_bytes: int = 0, cp_shape=None, wait_spins: int = 4_000_000, bulk_rows: int = 0):
+                 gather_bytes: int = 0, cp_shape=None, wait_spins: int = 4_000_000, bulk_rows: int = 0,
+                 status: Optional[torch.Tensor] = None):
         assert world <= MAX_RANKS
         self.rank, self.world, self.slot_rows, self.row_len = rank, world, slot_rows, row_len
         self.local = local
@@ -168,7 +168,10 @@ class SymmetricRegion:
         self.bulk_words = bulk_rows // 32 + MAX_RANKS
         self.bulk_state = torch.zeros(max(1, self.BULK_LANES * self.bulk_words), dtype=torch.int32, device=dev)
         st = self.state.data_ptr()
-        self.status_ptr = st + 4 * 48
+        # {code, site, expected, seen} of an expired wait: words of this region, or (a serving process) the four words of
+        # the device's error block that the engine reads back with every step's result
+        self.status = status if status is not None else self.state[48:52]
+        self.status_ptr = self.status.data_ptr()
         self.push_ctx, self.recv_ctx = [], []
         for b in range(self.NUM_BUFS):
             pc = PushCtx(epoch=st + 4 * b, block_counter=st + 4 * (8 + b), rank=rank, world=world, slot_rows=slot_rows,
@@ -250,9 +253,9 @@ class SymmetricRegion:
                 raise RuntimeError(f"rank {self.rank}: guard zone {i} of the symmetric region (offset {g}) was overwritten at byte {bad}")
 
     def check_status(self) -> None:
-        st = self.state[48:52].tolist()
+        st = self.status.tolist()
         if st[0]:
-            self.state[48:52].zero_()
+            self.status.zero_()
             raise CollectiveTimeout(f"rank {self.rank}: device wait expired at site {st[1]} (expected flag {st[2]}, saw {st[3]})")
 
 
@@ -321,8 +324,10 @@ class NvlinkComm(Comm):
         dist.barrier(group=ctx.group)
         from ..config import env_int
         # bound of every device-side wait, in polls (a poll is 0.03 - 0.3 us; the default is on the order of a second)
+        from ..ops import tcgen05
         region = SymmetricRegion(ctx.rank, ctx.world, NvlinkComm.MAX_ROWS, H, buf, ptrs, gather_bytes, cp_shape,
-                                 wait_spins=env_int("WAIT_SPINS", 4_000_000), bulk_rows=bulk_rows)
+                                 wait_spins=env_int("WAIT_SPINS", 4_000_000), bulk_rows=bulk_rows,
+                                 status=tcgen05.error_flag(ctx.device)[12:16])
         region._keep = keep
         return region
 

@@ -75,6 +75,7 @@ class Engine:
         self._phase_streams = None
         self._bufs = {}
         self._out_host = {}
+        self._err_host = None                # pinned copy of the device's status words, read back with every step result
         self.h2d_bytes = 0
         self.d2h_bytes = 0
 
@@ -196,6 +197,7 @@ class Engine:
             else:
                 tokens.append(int(self._greedy(last_hidden)[0]))
             hiddens.append(last_hidden)
+        self.check_device_errors()           # (the token reads above already synchronised the stream)
         return tokens, (hiddens if want_hidden else None)
 
     def _forward_phased(self, ids, positions, s: Sequence, start: int, n: int) -> torch.Tensor:
@@ -308,13 +310,24 @@ class Engine:
         return all_i.gather(0, best).squeeze(0)
 
     def _readback(self, key, dev_t: torch.Tensor) -> torch.Tensor:
+        """Step result device -> pinned host, and with it (same stream, same synchronisation) the device's status words:
+        an expired bounded wait of a collective or a persistent kernel, or a failed index self-check, raises here, in the
+        step that produced it, so that the scheduler rolls the batch back instead of publishing tokens computed from
+        stale data."""
         host = self._out_host.get(key)
         if host is None or host.shape != dev_t.shape or host.dtype != dev_t.dtype:
             host = torch.empty(dev_t.shape, dtype=dev_t.dtype, pin_memory=self.device.type == "cuda")
             self._out_host[key] = host
         host.copy_(dev_t, non_blocking=True)
         if self.device.type == "cuda":
+            from ..ops import tcgen05
+            if self._err_host is None:
+                self._err_host = torch.zeros(tcgen05.ERROR_WORDS, dtype=torch.int32, pin_memory=True)
+            self._err_host.copy_(tcgen05.error_flag(self.device), non_blocking=True)
             torch.cuda.current_stream().synchronize()
+            self.d2h_bytes += self._err_host.numel() * 4
+            if bool(self._err_host.any()):
+                tcgen05.raise_for(self._err_host.tolist(), self.device)
         self.d2h_bytes += host.numel() * host.element_size()
         return host
 

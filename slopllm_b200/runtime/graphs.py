@@ -20,7 +20,8 @@ class GraphEntry:
     calls: int = 0
     graph: Optional[Any] = None
     outputs: Any = None
-    launches: int = 0                 # native kernel launches recorded while capturing
+    launches: int = 0                 # native library calls recorded while capturing
+    kernels: int = 0                  # CUDA kernels of the library recorded while capturing (a call may launch several)
     extra: dict = field(default_factory=dict)
 
 
@@ -51,13 +52,14 @@ class CaptureManager:
         g = torch.cuda.CUDAGraph()
         if self.pool is None:
             self.pool = torch.cuda.graph_pool_handle()
-        before = N.launch_count()
+        before, kbefore = N.launch_count(), N.kernel_count()
         with torch.cuda.graph(g, pool=self.pool):
             e.outputs = fn()
         e.launches = N.launch_count() - before
+        e.kernels = N.kernel_count() - kbefore
         e.graph = g
         if self.debug:
-            print(f"[capture] captured key={key} kernel launches={e.launches}")
+            print(f"[capture] captured key={key} library calls={e.launches} kernels={e.kernels}")
         g.replay()
         return e.outputs
 

@@ -78,7 +78,9 @@ class ReplicaChannel:
             r = self.live.get(rid)
             if r is not None:
                 r.cancelled = r.cancel_seen = True
-        for rid in [rid for rid, r in self.live.items() if r.finish_reason]:
+        # a request leaves the table when the scheduler has retired it, not when a finish reason appears: until then a
+        # cancellation of it may still have to travel to the other ranks
+        for rid in [rid for rid, r in self.live.items() if r.retired]:
             del self.live[rid]
 
 

@@ -52,12 +52,18 @@ class GenerationRequest:
     prefill_tokens: int = 0
     prefill_seconds: float = 0.0
     cancelled: bool = False                  # set by the client side at any time
+    cancel_reason: str = ""                  # finish reason the row gets when the cancellation is acted on ("" = "cancelled")
     cancel_seen: bool = False                # what the scheduler acts on (copied at step boundaries, on every rank alike)
+    retired: bool = False                    # the scheduler has let go of the request (finished, failed or refused)
     submitted_at: float = field(default_factory=time.time)
     first_token_at: Optional[float] = None
 
-    def cancel(self) -> None:
-        """Client went away: the row is dropped at the next step."""
+    def cancel(self, reason: str = "") -> None:
+        """Client side (any thread): the client went away, or it has seen a stop string (`reason="stop"`).  Only this flag
+        is written here; the scheduler drops the row, on every rank in the same step, once the cancellation has reached
+        all ranks, and assigns `finish_reason` then."""
+        if reason and not self.cancel_reason:
+            self.cancel_reason = reason
         self.cancelled = True
 
 
@@ -124,12 +130,10 @@ class HostTier:
 
     def save(self, seq: Sequence) -> None:
         n = seq.reported // self.tpp
-        if self.max_pages <= 0 or n == 0:
-            return
+        if self.max_pages <= 0 or n == 0 or n > self.max_pages:
+            return                            # (a sequence larger than the whole tier must not cost the tier its entries)
         while self.entries and self.used_pages + n > self.max_pages:
             self.entries.remove(max(self.entries, key=lambda e: len(e["pages"])))     # largest victim first
-        if n > self.max_pages:
-            return
         self.entries.append({"tokens": list(seq.token_ids[: n * self.tpp]), "pages": [self.read_page(p) for p in seq.pages[:n]]})
 
     def match(self, prompt: Seq[int]):
@@ -164,6 +168,8 @@ class _Row:
 
 
 class GenerationScheduler:
+    ADMIT_LOOKAHEAD_TOKENS = 512      # output tokens whose pages are reserved when a request is admitted
+
     def __init__(self, engine: EngineLike, max_batch: int = 8, chunk_size: int = 8192, eos_token_ids: Seq[int] = (),
                  host_tier: Optional[HostTier] = None, decode_latency_ms: float = 0.0, replica_channel=None, health=None):
         self.engine = engine
@@ -232,7 +238,7 @@ class GenerationScheduler:
                 elif isinstance(ev, CacheFlushEvent):
                     ev.done.set()
                 else:
-                    ev.error, ev.finish_reason = f"RankFailure: {err}", "error"
+                    ev.error, ev.finish_reason, ev.retired = f"RankFailure: {err}", "error", True
                     self.metrics.request_error_total += 1
                     if ev.on_finish:
                         ev.on_finish(ev)
@@ -291,7 +297,8 @@ class GenerationScheduler:
                 keep.append(r)
                 continue
             if req.cancel_seen and not req.finish_reason:
-                req.finish_reason = "cancelled"
+                req.finish_reason = req.cancel_reason or "cancelled"
+            req.retired = True
             self.engine.kv.stage(r.seq)           # keep the pages for prefix reuse
             self._free_rows.append(r.row)
             if req.finish_reason in ("stop", "length"):
@@ -344,27 +351,38 @@ class GenerationScheduler:
         prompt = req.input_ids
         req.prompt_tokens = len(prompt)
         if not prompt:
-            req.error, req.finish_reason = "empty prompt", "error"
+            req.error, req.finish_reason, req.retired = "empty prompt", "error", True
             if req.on_finish:
                 req.on_finish(req)
             return
-        need = kv.pages_for(len(prompt) + req.max_tokens + self.engine.mtp + 1)
+        # pages reserved at admission: the prompt plus a bounded look-ahead of output (a request may ask for tens of
+        # thousands of tokens and stop after ten; its later pages are found step by step, see `_make_room`)
+        need = kv.pages_for(len(prompt) + min(req.max_tokens, self.ADMIT_LOOKAHEAD_TOKENS) + self.engine.mtp + 1)
+        offload = self.host_tier.save if self.host_tier else None
+        seq = None
         try:
             seq, cached = kv.start_request(prompt)
-            # host tier: a longer prefix there is restored into fresh pages
-            if self.host_tier is not None and cached < len(prompt) - 1:
+            resumed = cached % kv.tokens_per_page != 0        # a staged sequence continues in its own partial last page
+            # host tier: a longer prefix there is restored into fresh pages (not behind a resumed partial page, whose
+            # tokens the host pages would not line up with)
+            if self.host_tier is not None and not resumed and cached < len(prompt) - 1:
                 entry, pages = self.host_tier.match(prompt)
                 if entry is not None and pages * kv.tokens_per_page > cached:
-                    self._restore_from_host(seq, entry, pages, prompt)
-                    cached = seq.length
+                    extra = pages - len(seq.pages)
+                    if kv.free_pages < extra:
+                        kv.evict_staged(extra, offload=offload)
+                    if kv.free_pages >= extra:
+                        self._restore_from_host(seq, entry, pages, prompt)
+                        cached = seq.length
             missing = max(0, need - len(seq.pages))
             if kv.free_pages < missing:
-                kv.evict_staged(missing, offload=self.host_tier.save if self.host_tier else None)
+                kv.evict_staged(missing, offload=offload)
             if kv.free_pages < kv.pages_for(len(prompt)) - len(seq.pages):
-                kv.free_sequence(seq)
                 raise PageAllocationError(f"prompt of {len(prompt)} tokens does not fit in the KV cache")
         except PageAllocationError as err:
-            req.error, req.finish_reason = str(err), "error"
+            if seq is not None:
+                kv.free_sequence(seq)                         # gives back the shared pages it had taken a reference on
+            req.error, req.finish_reason, req.retired = str(err), "error", True
             self.metrics.request_error_total += 1
             if req.on_finish:
                 req.on_finish(req)
@@ -427,6 +445,7 @@ class GenerationScheduler:
         seqs = [r.seq for r in active]
         last = [r.last_token for r in active]
         rows = [r.row for r in active]
+        self._make_room(seqs)
         t0 = time.time()
         if self.engine.mtp > 0:
             import torch
@@ -451,6 +470,14 @@ class GenerationScheduler:
             for r, t in zip(active, new):
                 r.last_token = t
                 self._publish(r, [t])
+
+    def _make_room(self, seqs) -> None:
+        """Pages the next step will take beyond what the rows hold: found among the staged sequences (largest first, saved
+        to the host tier) before the step, so that a long generation grows past its admission reserve."""
+        kv = self.engine.kv
+        grow = sum(max(0, kv.pages_for(s.length + self.engine.mtp + 2) - len(s.pages)) for s in seqs)
+        if grow and kv.free_pages < grow:
+            kv.evict_staged(grow, offload=self.host_tier.save if self.host_tier else None)
 
     def _hidden_for(self, r: _Row):
         if r.last_hidden is None:
@@ -477,7 +504,7 @@ class GenerationScheduler:
         if "CollectiveTimeout" in type(err).__name__:
             self.metrics.collective_timeouts_total += 1
         for r in self.rows:
-            r.req.error, r.req.finish_reason = msg, "error"
+            r.req.error, r.req.finish_reason, r.req.retired = msg, "error", True
             self.metrics.request_error_total += 1
             if r.req.on_finish:
                 r.req.on_finish(r.req)

@@ -421,9 +421,10 @@ class OpenAIServer:
                 if kind == "end" and not state["stopped"] and state["sent"] < len(state["content"]):
                     deltas.append({"content": state["content"][state["sent"]:]})      # text held for a stop string that never came
                     state["sent"] = len(state["content"])
-                if state["stopped"] and not req.finish_reason:
-                    req.finish_reason = "stop"            # stop string hit: the row retires at the next step
-                    req.cancel()
+                if state["stopped"] and not req.cancelled:
+                    # stop string hit.  Only the client-side flag is set from this thread: the scheduler retires the row
+                    # (finish reason "stop") in the step in which every rank has learnt of it
+                    req.cancel(reason="stop")
                 if stream:
                     for d in deltas:
                         writer.write(chunk(d))
