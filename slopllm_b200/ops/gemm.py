@@ -21,6 +21,9 @@ from . import tcgen05
 DEQUANT_BUDGET_BYTES = 3 << 30          # transient bf16 copy of expert weights per grouped launch
 W4_GEMM = os.environ.get("SLOPLLM_B200_W4_GEMM", "1") != "0"
 W4_DENSE_MAX_ROWS = 256                 # plain (non-grouped) NVFP4 linears take the fused kernel up to this many rows
+# prefill MoE on the block-scaled FP4 tensor cores: activations are quantised to NVFP4 on the fly (W4A4).
+# SLOPLLM_B200_MOE_A4=0 keeps 16-bit activations (W4A16, the reference's numerics) on the expansion kernels.
+MOE_A4 = os.environ.get("SLOPLLM_B200_MOE_A4", "1") != "0"
 OUT_BF16, OUT_F32, OUT_F16 = 0, 1, 2
 
 
@@ -128,6 +131,34 @@ def grouped_gemm(a: torch.Tensor, b_stack: torch.Tensor, offsets: torch.Tensor, 
     return c
 
 
+def _sf_tiles_of(experts):
+    """Scale tiles of an expert stack for the block-scaled kernel, made once and kept with the weights."""
+    from . import fp4
+    t = getattr(experts, "_sf_tiles", None)
+    if t is None:
+        t = (fp4.sf_tiles(experts.s13), fp4.sf_tiles(experts.s2))
+        experts._sf_tiles = t
+    return t
+
+
+def fp4_moe_ok(experts, H: int) -> bool:
+    from . import fp4
+    I = experts.inter
+    return bool(MOE_A4 and experts.is_nvfp4 and fp4.shapes_ok(I, H) and fp4.shapes_ok(H, I) and I % 128 == 0)
+
+
+def experts_fp4(experts, x, src_rows, plan, out_kind: int = OUT_BF16) -> torch.Tensor:
+    """SwiGLU experts over expert-sorted rows on the block-scaled path: gather + NVFP4 quantisation of the token rows
+    (row m of the sorted order = x[src_rows[m]]), gate/up with the SiLU * mul epilogue, re-quantisation of the
+    activations, down projection.  Returns [rows, H] (bf16 or fp32)."""
+    from . import fp4
+    sf13, sf2 = _sf_tiles_of(experts)
+    xq, sfx, gx = fp4.quantize_rows(x, src_rows, plan=plan)
+    act = fp4.grouped_gemm_fp4(experts.w13, sf13, experts.g13, xq, sfx, gx, plan, experts.inter, True, fp4.OUT_BF16)
+    aq, sfa, ga = fp4.quantize_rows(act, plan=plan)
+    return fp4.grouped_gemm_fp4(experts.w2, sf2, experts.g2, aq, sfa, ga, plan, experts.hidden, False, out_kind)
+
+
 def moe_large(ops, x, experts, shared, ids, wts) -> torch.Tensor:
     """Expert MLP for many tokens: routes sorted by expert on the device, gate/up and down as grouped GEMMs over
     the sorted rows (NVFP4 experts: weights expanded inside the GEMM; otherwise bf16 weights, expanded in groups
@@ -149,13 +180,20 @@ def moe_large(ops, x, experts, shared, ids, wts) -> torch.Tensor:
     N.call("sl_moe_sort_routes", ids32.data_ptr(), M, k, experts.expert_offset, E, scratch.data_ptr(), offsets.data_ptr(),
            order.data_ptr(), rows_of.data_ptr(), src_tok.data_ptr(), N.stream())
     wts = wts.to(torch.float32).contiguous()
+    use_fp4 = fp4_moe_ok(experts, H) and xb.stride(-1) == 1
     # the shared expert writes the fp32 result first, the routed experts accumulate into it
-    out = _shared_expert_large(xb, shared) if shared is not None else None
+    out = _shared_expert_large(xb, shared, use_fp4) if shared is not None else None
     if out is not None and (out.stride(0) != H or out.dtype != torch.float32):
         out = out.to(torch.float32).contiguous()
     acc = 0 if out is None else 1
     if out is None:
         out = torch.empty(T, H, dtype=torch.float32, device=dev)
+    if use_fp4:
+        # tokens gathered into expert order and quantised in one pass; both expert GEMMs on tcgen05 kind::mxf4nvf4
+        from . import fp4
+        y = experts_fp4(experts, xb, src_tok, fp4.group_plan(offsets, E, M))
+        N.call("sl_moe_unsort_reduce", out.data_ptr(), y.data_ptr(), rows_of.data_ptr(), wts.data_ptr(), T, k, H, acc, 1, N.stream())
+        return out
     if experts.is_nvfp4 and _w4_ok(H) and _w4_ok(I) and xb.stride(0) % 8 == 0:
         # weights expanded inside the GEMMs: no transient bf16 copy, activations in f16
         xs16 = to_f16_rows(xb, src_tok)                                           # [T*k, H] expert-sorted rows
@@ -190,9 +228,13 @@ def moe_large(ops, x, experts, shared, ids, wts) -> torch.Tensor:
     return out
 
 
-def _shared_expert_large(xb: torch.Tensor, shared) -> torch.Tensor:
-    """Shared expert over all rows (one weight matrix, many rows: expansion + bf16 GEMM).  Returns fp32 [T, H]."""
+def _shared_expert_large(xb: torch.Tensor, shared, use_fp4: bool = False) -> torch.Tensor:
+    """Shared expert over all rows (one weight matrix, many rows: the block-scaled FP4 path, or expansion + bf16 GEMM).
+    Returns fp32 [T, H]."""
     T = xb.shape[0]
+    if use_fp4 and fp4_moe_ok(shared, xb.shape[1]):
+        from . import fp4
+        return experts_fp4(shared, xb, None, fp4.single_group(T, xb.device), OUT_F32)
     if shared.is_nvfp4:
         w13 = dequant_bf16(shared.w13[0], shared.s13[0], shared.g13[0], g_per=2, split=shared.inter)
         w2 = dequant_bf16(shared.w2[0], shared.s2[0], shared.g2[0].reshape(1))

@@ -51,6 +51,7 @@ class ElasticGroup:
         self.backend = backend or ("nccl" if self.device.type == "cuda" else "gloo")
         self.cp, self.ep, self.timeout_s = cp, ep, timeout_s
         self.generation = -1
+        self._tried = -1              # newest generation this rank entered or tried to enter
         self.ctx: Optional[ParallelContext] = None
 
     # -- generation counter ------------------------------------------------------------------------------------
@@ -60,12 +61,20 @@ class ElasticGroup:
 
     def _enter(self, generation: int) -> ParallelContext:
         self._leave()
+        self._tried = max(self._tried, generation)
+        # c10d names the default group's rendezvous keys after a per-process group counter that a *failed*
+        # init_process_group leaves advanced; a process that has tried before must count like one that has not
+        world_state = getattr(dist.distributed_c10d, "_world", None)
+        if world_state is not None and not dist.is_initialized():
+            world_state.group_count = 0
         prefix = dist.PrefixStore(f"gen{generation}/", self.store)
         kw = {"device_id": self.device} if self.device.type == "cuda" else {}
         try:
             dist.init_process_group(self.backend, store=prefix, rank=self.rank, world_size=self.world,
                                     timeout=timedelta(seconds=self.timeout_s), **kw)
         except Exception as e:  # noqa: BLE001  (c10d raises DistStoreError / RuntimeError on a rendezvous that timed out)
+            # the attempt's rendezvous keys stay under this prefix: nobody may try to assemble this generation again
+            self.store.set(f"elastic/spent/{generation}", "1")
             raise RecoveryTimeout(f"rank {self.rank}: generation {generation} did not assemble within {self.timeout_s} s: {e}") from e
         self.generation = generation
         self.store.set(f"elastic/member/{generation}/{self.rank}", "1")
@@ -99,18 +108,32 @@ class ElasticGroup:
             if self.store.check([f"elastic/member/{g}/{self.rank}"]):
                 dead = g
                 break
-        return self._enter(self._wait_for_generation_above(dead))
+        # a generation whose assembly already failed for somebody is skipped: the survivors will open another one
+        while True:
+            g = self._wait_for_generation_above(dead)
+            if self.store.check([f"elastic/spent/{g}"]):
+                dead = g
+                continue
+            return self._enter(g)
 
     def recover(self, on_new_context: Optional[Callable[[ParallelContext], None]] = None) -> ParallelContext:
-        """A survivor: open the next generation (only the first survivor's increment counts: the counter is advanced
-        with compare-and-set semantics through a claim key) and enter it.  `on_new_context` rebuilds what was attached
-        to the old group (communicator, graphs)."""
-        nxt = self.generation + 1
-        # one claim key per generation: the first `add` returns 1 and that rank advances the counter
-        if int(self.store.add(f"elastic/claim/{nxt}", 1)) == 1:
-            self.store.add(GENERATION_KEY, 1)
-        self._wait_for_generation_above(self.generation)
-        ctx = self._enter(nxt)
+        """A survivor: open a generation that nobody has tried yet and enter it.  Every entrant (survivors here, a
+        replacement in `join`) enters the value of the store's counter, so they cannot end up in different generations.
+        The counter is moved by one rank only: the first to claim the next number (an `add` on a per-number claim key).
+        After a `RecoveryTimeout` the generation that failed to assemble is spent (its prefix still holds the rendezvous
+        keys of the attempt): the next call opens a fresh one.  `on_new_context` rebuilds what was attached to the old
+        group (communicator, graphs)."""
+        tried = max(self._tried, self.generation)
+        cur = self.current_generation()
+        if cur <= tried:
+            nxt = tried + 1
+            # one claim key per generation: the first `add` returns 1 and that rank advances the counter to it
+            if int(self.store.add(f"elastic/claim/{nxt}", 1)) == 1:
+                cur = self.current_generation()
+                if cur < nxt:
+                    self.store.add(GENERATION_KEY, nxt - cur)
+        gen = self._wait_for_generation_above(tried)
+        ctx = self._enter(gen)
         if on_new_context is not None:
             on_new_context(ctx)
         return ctx

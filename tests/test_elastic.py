@@ -115,3 +115,67 @@ def test_reattach_swaps_communicator_and_drops_graphs():
     reattach(engine, new)
     assert model.ctx is new and model.ops.ctx is new and model.comm is not old_comm and model.comm.ctx is new
     assert not graphs.entries
+
+
+def _retry_member(rank, world, port, role, q):
+    """Survivor: the first recovery finds nobody (short timeout), the second one meets the replacement."""
+    import traceback
+    try:
+        import torch.distributed as dist
+
+        from slopllm_b200.parallel.dist import Comm
+        from slopllm_b200.parallel.elastic import ElasticGroup, RecoveryTimeout
+        from slopllm_b200.utils.health import make_store
+        torch.set_num_threads(1)
+        out = {"role": role}
+        if role == "survivor":
+            store = make_store(0, world, port=port)
+            eg = ElasticGroup(store, 0, world, timeout_s=2.0)
+            eg.generation = eg._tried = 0                  # generation 0 was running; rank 1 is gone
+            try:
+                eg.recover()
+                out["first_attempt"] = "assembled"
+            except RecoveryTimeout:
+                out["first_attempt"] = "timeout"
+            out["after_timeout"] = eg.current_generation()
+            store.set("retry/go", "1")                     # now the replacement may come
+            eg.timeout_s = 30.0
+            ctx = eg.recover()
+        else:
+            store = make_store(1, world, port=port)
+            store.wait(["retry/go"])
+            eg = ElasticGroup(store, 1, world, timeout_s=30.0)
+            store.set("elastic/member/0/1", "1")           # this rank number lived in generation 0
+            ctx = eg.join()
+        out["generation"] = eg.generation
+        out["sum"] = Comm(ctx).all_reduce(torch.full((2,), float(rank + 1))).tolist()
+        dist.barrier()
+        eg.shutdown()
+        q.put((rank, out, None))
+    except Exception:  # noqa: BLE001
+        q.put((rank, None, traceback.format_exc()))
+
+
+def test_second_recovery_uses_a_fresh_generation_after_a_timeout():
+    mpc = mp.get_context("spawn")
+    q = mpc.Queue()
+    port = _free_port()
+    procs = [mpc.Process(target=_retry_member, args=(0, 2, port, "survivor", q)),
+             mpc.Process(target=_retry_member, args=(1, 2, port, "replacement", q))]
+    for p in procs:
+        p.start()
+    res = {}
+    try:
+        for _ in range(2):
+            rank, out, err = q.get(timeout=120)
+            assert err is None, err
+            res[rank] = out
+    finally:
+        for p in procs:
+            p.join(timeout=20)
+            if p.is_alive():
+                p.kill()
+    assert res[0]["first_attempt"] == "timeout" and res[0]["after_timeout"] == 1
+    # generation 1 was spent by the failed attempt: both meet in generation 2
+    assert res[0]["generation"] == 2 and res[1]["generation"] == 2
+    assert res[0]["sum"] == [3.0, 3.0] and res[1]["sum"] == [3.0, 3.0]

@@ -17,10 +17,11 @@ def close(a, b, tol, what=""):
     assert err <= tol, f"{what}: max rel-to-peak error {err:.4g} > {tol}"
 
 
-def deq_rows(q, sf, g):
-    """fp32 value of quantised activation rows (codes, scales in the quantiser's layout, per-row global scale)."""
+def deq_rows(q, sf, g, bn=128):
+    """fp32 value of quantised (ungrouped) activation rows: codes, scale tiles for GEMM tiles of `bn` rows, global scales."""
     from slopllm_b200.ops import fp4
-    return quant.nvfp4_dequantize(q, fp4.scales_row_major(sf).view(torch.float8_e4m3fn), 1.0) * g.unsqueeze(-1)
+    rows, K = q.shape[0], q.shape[1] * 2
+    return quant.nvfp4_dequantize(q, fp4.scales_row_major(sf, rows, K, bn).view(torch.float8_e4m3fn), 1.0) * g.unsqueeze(-1)
 
 
 def test_scale_tile_layout():
@@ -44,9 +45,10 @@ def test_quantize_rows_represents_the_input(terms):
     x = (torch.randn(M, K, device=DEV) * torch.rand(M, 1, device=DEV) * 3).to(torch.bfloat16)
     x[5] = 0
     src = torch.randperm(M, device=DEV).to(torch.int32)
-    q, sf, g = fp4.quantize_rows(x, src, terms=terms)
+    q, sf, g = fp4.quantize_rows(x, src, terms=terms, bn=32)
     xs = x[src.long()].float()
-    rep = sum(deq_rows(q[j * M:(j + 1) * M], sf[:, j * M:(j + 1) * M], g[j * M:(j + 1) * M]) for j in range(terms))
+    allrows = deq_rows(q, sf, g, 32)                    # rows m + j * M: the j-th term of row m
+    rep = sum(allrows[j * M:(j + 1) * M] for j in range(terms))
     rel = ((rep - xs).norm(dim=1) / xs.norm(dim=1).clamp(min=1e-6))
     assert float(rel.max()) < (0.15 if terms == 1 else 2e-3), float(rel.max())
     assert float(rep[src.long() == 5].abs().max()) == 0.0
@@ -64,11 +66,11 @@ def test_gemm_fp4_plain(M, Nn, K, bn):
     wq, ws, _ = quant.random_nvfp4((Nn, K), g, DEV)
     gA = torch.tensor([0.37], device=DEV)
     x = torch.randn(M, K, device=DEV, generator=g).to(torch.bfloat16)
-    xq, sfb, gB = fp4.quantize_rows(x)
+    xq, sfb, gB = fp4.quantize_rows(x, bn=bn)
     y = fp4.gemm_fp4(wq, fp4.sf_tiles(ws), gA, xq, sfb, gB, fp4.OUT_F32, bn)
     torch.cuda.synchronize()
     tcgen05.check_errors(DEV)
-    ref = deq_rows(xq, sfb, gB) @ quant.nvfp4_dequantize(wq, ws, 0.37).t()
+    ref = deq_rows(xq, sfb, gB, bn) @ quant.nvfp4_dequantize(wq, ws, 0.37).t()
     close(y, ref, 2e-3, "fp4 gemm vs fp32 product of the quantised operands")
     # and the whole W4A4 path stays near the 16-bit activation product
     ref16 = x.float() @ quant.nvfp4_dequantize(wq, ws, 0.37).t()
@@ -86,12 +88,16 @@ def test_gemm_fp4_grouped_ragged(pair):
     wq, ws, _ = quant.random_nvfp4((G, rows, K), g, DEV)
     gA = (torch.rand(G, 2 if pair else 1, device=DEV, generator=g) + 0.5).squeeze(-1)
     x = torch.randn(M, K, device=DEV, generator=g).to(torch.bfloat16)
-    xq, sfb, gB = fp4.quantize_rows(x)
     off = torch.tensor([0] + list(torch.tensor(counts).cumsum(0)), dtype=torch.int32, device=DEV)
-    y = fp4.grouped_gemm_fp4(wq, fp4.sf_tiles(ws), gA, xq, sfb, gB, off, Nn, pair, fp4.OUT_F32, 64)
+    plan = fp4.group_plan(off, G, M, 64)
+    xq, sfb, gB = fp4.quantize_rows(x, plan=plan)
+    y = fp4.grouped_gemm_fp4(wq, fp4.sf_tiles(ws), gA, xq, sfb, gB, plan, Nn, pair, fp4.OUT_F32)
     torch.cuda.synchronize()
     tcgen05.check_errors(DEV)
-    xd = deq_rows(xq, sfb, gB)
+    # the same rows quantised without groups give the same codes and scales (only the scale tiles move)
+    xq2, sfb2, gB2 = fp4.quantize_rows(x, bn=64)
+    assert torch.equal(xq, xq2) and torch.equal(gB, gB2)
+    xd = deq_rows(xq2, sfb2, gB2, 64)
     ref = torch.empty(M, Nn, device=DEV)
     at = 0
     for e, n in enumerate(counts):

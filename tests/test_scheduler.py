@@ -209,3 +209,126 @@ def test_sequence_page_edges_truncate_and_copy_on_write():
     kv.free_sequence(t)
     kv.flush_staged()
     kv.assert_clear()
+
+
+def test_collective_timeout_rolls_back_and_is_counted():
+    """A device wait that expired surfaces as CollectiveTimeout from the step's readback: the batch ends with an error,
+    the timeout counter moves and the scheduler keeps serving."""
+    from slopllm_b200.ops.native import CollectiveTimeout
+
+    class TimeoutEngine(FakeEngine):
+        def decode_step(self, seqs, last, rows=None):
+            if len(self.decode_batches) == 1:
+                self.decode_batches.append(None)
+                raise CollectiveTimeout("device wait on a peer expired at site 3 (expected flag 9, saw 8)")
+            return super().decode_step(seqs, last, rows)
+
+    eng = TimeoutEngine()
+    s = GenerationScheduler(eng, max_batch=2, chunk_size=64)
+    a = _req(0, [1, 2, 3], 8)
+    s.submit(a)
+    _drain(s)
+    assert a.finish_reason == "error" and "CollectiveTimeout" in a.error and a.retired
+    assert s.metrics.collective_timeouts_total == 1
+    eng.kv.assert_clear()
+    b = _req(1, [9], 2)
+    s.submit(b)
+    _drain(s)
+    assert b.generated == [10, 11]
+
+
+def test_host_restore_evicts_first_and_frees_on_failure():
+    """Full pool + a host-tier match: staged sequences are evicted before the host pages are restored; when nothing can
+    be evicted the request fails without leaking the pages it shared."""
+    eng = FakeEngine(pages=6)
+    store = {}
+    host = HostTier(16, 64, read_page=lambda p: ("blob", p), write_page=lambda p, blob: store.__setitem__(p, blob))
+    s = GenerationScheduler(eng, max_batch=2, chunk_size=512, host_tier=host)
+    r1 = _req(0, range(200), 2)                 # 4 pages, staged afterwards
+    s.submit(r1)
+    _drain(s)
+    for sq in list(eng.kv.staged.values()):
+        host.save(sq)                           # the host tier holds its 3 whole pages
+    eng.kv.flush_staged()
+    r2 = _req(1, range(5000, 5300), 2)          # 5 pages of another prompt, staged: the pool is nearly full
+    s.submit(r2)
+    _drain(s)
+    assert eng.kv.free_pages <= 1 and eng.kv.staged
+    r3 = _req(2, list(range(200)) + [7, 8], 2)  # host match of 3 pages: needs eviction first
+    s.submit(r3)
+    _drain(s)
+    assert r3.finish_reason == "length" and r3.cached_tokens == 192 and len(store) == 3
+    eng.kv.flush_staged()
+    eng.kv.assert_clear()
+    # nothing to evict and no room: the request is refused and leaves no reference behind
+    blocker = eng.kv.new_sequence()
+    eng.kv.append_tokens(blocker, [0] * (64 * 5))
+    r4 = _req(3, list(range(200)) + [7, 8], 2)
+    s.submit(r4)
+    s.step()
+    assert r4.finish_reason == "error" and r4.retired
+    eng.kv.free_sequence(blocker)
+    eng.kv.assert_clear()
+
+
+def test_resumed_partial_page_skips_the_host_tier():
+    """A staged sequence that ends mid-page is resumed in place; a longer host-tier match must not be restored behind its
+    partial page (the host pages would not line up with the tokens the sequence already holds)."""
+    eng = FakeEngine(pages=16)
+    writes = []
+    host = HostTier(16, 64, read_page=lambda p: ("blob", p), write_page=lambda p, blob: writes.append(p))
+    s = GenerationScheduler(eng, max_batch=1, chunk_size=512, host_tier=host)
+    long = _req(0, range(300), 1)
+    s.submit(long)
+    _drain(s)
+    for sq in list(eng.kv.staged.values()):
+        host.save(sq)                           # 4 whole pages (256 tokens) on the host
+    eng.kv.flush_staged()
+    short = _req(1, range(100), 1)              # staged with 101 tokens: a partial second page
+    s.submit(short)
+    _drain(s)
+    donor_len = next(iter(eng.kv.staged.values())).reported
+    assert donor_len % 64 != 0
+    writes.clear()                              # (the short prompt itself restored one whole page from the host)
+    r = _req(2, list(range(100)) + [100] + list(range(101, 300)), 1)
+    s.submit(r)
+    _drain(s)
+    assert r.cached_tokens == donor_len and not writes
+    assert r.finish_reason == "length"
+
+
+def test_host_tier_keeps_its_entries_when_a_sequence_is_too_large():
+    host = HostTier(2, 64, read_page=lambda p: p, write_page=lambda p, b: None)
+    kv = PagedKVCache(16)
+    a = kv.new_sequence()
+    kv.append_tokens(a, list(range(128)))
+    kv.report_tokens(a)
+    host.save(a)
+    assert host.used_pages == 2
+    b = kv.new_sequence()
+    kv.append_tokens(b, list(range(1000, 1000 + 64 * 5)))
+    kv.report_tokens(b)
+    host.save(b)                                # 5 pages > the tier's 2: refused, and a's pages stay
+    assert host.used_pages == 2 and host.entries[0]["tokens"][:3] == [0, 1, 2]
+
+
+def test_admission_reserves_a_bounded_lookahead_and_grows_later():
+    """A request with a huge max_tokens must not evict every staged prefix at admission; its pages are found as it grows."""
+    eng = FakeEngine(pages=16)
+    s = GenerationScheduler(eng, max_batch=1, chunk_size=512)
+    first = _req(0, range(300), 1)              # leaves a staged prefix of 5 pages
+    s.submit(first)
+    _drain(s)
+    staged_before = len(eng.kv.staged)
+    assert staged_before == 1
+    big = _req(1, range(2000, 2010), 65536)     # asks for 64K tokens, 1024 pages: far more than the pool
+    s.submit(big)
+    s.step()
+    assert len(eng.kv.staged) == staged_before and not big.finish_reason       # admitted, nothing evicted yet
+    for _ in range(64 * 11):                    # grow past the free pages: the staged prefix goes when it is needed
+        s.step()
+        if big.finish_reason:
+            break
+    assert not eng.kv.staged and len(big.generated) > 64 * 10
+    big.cancel()
+    _drain(s)
