@@ -119,8 +119,11 @@ __global__ void __launch_bounds__(192) gemm_fp4_kernel(const __grid_constant__ C
         if (lane == 0) {
             int it = 0;
             bool ok = true;
+            Fp4Tile t_next{};
+            if ((int)blockIdx.x < total) t_next = p.tiles[blockIdx.x];
             for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
-                const Fp4Tile t = p.tiles[tile];
+                const Fp4Tile t = t_next;
+                if (tile + (int)gridDim.x < total) t_next = p.tiles[tile + gridDim.x];      // in flight while this tile's loads are issued
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
                     const int s = it % STAGES;
                     if (!tc::mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1)) { atomicExch(p.err, 11); ok = false; break; }
@@ -177,60 +180,76 @@ __global__ void __launch_bounds__(192) gemm_fp4_kernel(const __grid_constant__ C
         }
     } else {
         const int q = warp & 3;               // TMEM lane quarter of this warp
+        // Everything the epilogue of a tile reads from global memory (its table entry, the weights' global scales, the
+        // token rows' global scales) is fetched one tile ahead, while the previous tile is being stored: with a short
+        // reduction (one or two stages per tile) those dependent loads would otherwise be the tile's critical path.
+        struct Pre { Fp4Tile t; float ga, gu; float gb[BN / 32]; };
+        auto prefetch = [&](int tile, Pre& pre) {
+            pre.t = p.tiles[tile];
+            pre.ga = PAIR ? __ldg(p.gA + 2 * pre.t.group) : __ldg(p.gA + pre.t.group);
+            pre.gu = PAIR ? __ldg(p.gA + 2 * pre.t.group + 1) : 0.f;
+#pragma unroll
+            for (int c = 0; c < BN / 32; ++c)
+                pre.gb[c] = (c * 32 + lane < pre.t.b_valid) ? __ldg(p.gB + pre.t.b_row0 + c * 32 + lane) : 0.f;
+        };
+        Pre cur;
+        if ((int)blockIdx.x < total) prefetch(blockIdx.x, cur);
         int lt = 0;
         for (int tile = blockIdx.x; tile < total; tile += gridDim.x, ++lt) {
             const int buf = NBUF == 2 ? (lt & 1) : 0;
             const uint32_t par = NBUF == 2 ? ((lt >> 1) & 1) : (lt & 1);
+            Pre nxt = cur;
+            if (tile + (int)gridDim.x < total) prefetch(tile + gridDim.x, nxt);
             if (!tc::mbar_wait(&tmem_full[buf], par)) {
                 if (lane == 0) atomicExch(p.err, 13);
                 break;
             }
             tc::fence_after_sync();
-            const Fp4Tile t = p.tiles[tile];
+            const Fp4Tile& t = cur.t;
             const int n = t.out_n0 + q * 32 + lane;                      // output column = weight row of this lane
             const uint32_t t_acc = tmem_base + ((uint32_t)(q * 32) << 16) + buf * Cfg::ACC_COLS;
-            const float ga = PAIR ? __ldg(p.gA + 2 * t.group) : __ldg(p.gA + t.group);
-            const float gu = PAIR ? __ldg(p.gA + 2 * t.group + 1) : 0.f;
-#pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
-                if (c0 >= t.b_valid) break;
-                // the 32 token rows of this chunk: lane i holds token c0 + i's global scale
-                const int my_tok = t.b_row0 + c0 + lane;
-                const float my_gb = (c0 + lane < t.b_valid) ? __ldg(p.gB + my_tok) : 0.f;
-                uint32_t r0[32], r1[32];
-                tc::tmem_ld_32x32(t_acc + c0, r0);
-                if (PAIR) tc::tmem_ld_32x32(t_acc + BN + c0, r1);
-                tc::tmem_ld_wait();
-                const int lim = min(32, t.b_valid - c0);
-                if (p.out_kind == 1) {
-                    float* dst = (float*)p.out + (size_t)(t.b_row0 + c0) * p.ldo + n;
+            const float ga = cur.ga, gu = cur.gu;
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const float gb = __shfl_sync(0xffffffffu, my_gb, i);
-                        float v = __uint_as_float(r0[i]) * ga * gb;
-                        if (PAIR) {
-                            const float u = __uint_as_float(r1[i]) * gu * gb;
-                            v = v / (1.f + __expf(-v)) * u;
-                        }
-                        if (i < lim) dst[(size_t)i * p.ldo] = v;
-                    }
-                } else {
-                    bf16* dst = (bf16*)p.out + (size_t)(t.b_row0 + c0) * p.ldo + n;
+            for (int c = 0; c < BN / 32; ++c) {
+                const int c0 = c * 32;
+                if (c0 < t.b_valid) {                                    // (uniform over the warp)
+                    const float my_gb = cur.gb[c];                       // lane i holds token c0 + i's global scale
+                    uint32_t r0[32], r1[32];
+                    tc::tmem_ld_32x32(t_acc + c0, r0);
+                    if (PAIR) tc::tmem_ld_32x32(t_acc + BN + c0, r1);
+                    tc::tmem_ld_wait();
+                    const int lim = min(32, t.b_valid - c0);
+                    if (p.out_kind == 1) {
+                        float* dst = (float*)p.out + (size_t)(t.b_row0 + c0) * p.ldo + n;
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const float gb = __shfl_sync(0xffffffffu, my_gb, i);
-                        float v = __uint_as_float(r0[i]) * ga * gb;
-                        if (PAIR) {
-                            const float u = __uint_as_float(r1[i]) * gu * gb;
-                            v = v / (1.f + __expf(-v)) * u;
+                        for (int i = 0; i < 32; ++i) {
+                            const float gb = __shfl_sync(0xffffffffu, my_gb, i);
+                            float v = __uint_as_float(r0[i]) * ga * gb;
+                            if (PAIR) {
+                                const float u = __uint_as_float(r1[i]) * gu * gb;
+                                v = v / (1.f + __expf(-v)) * u;
+                            }
+                            if (i < lim) dst[(size_t)i * p.ldo] = v;
                         }
-                        if (i < lim) dst[(size_t)i * p.ldo] = __float2bfloat16(v);
+                    } else {
+                        bf16* dst = (bf16*)p.out + (size_t)(t.b_row0 + c0) * p.ldo + n;
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            const float gb = __shfl_sync(0xffffffffu, my_gb, i);
+                            float v = __uint_as_float(r0[i]) * ga * gb;
+                            if (PAIR) {
+                                const float u = __uint_as_float(r1[i]) * gu * gb;
+                                v = v / (1.f + __expf(-v)) * u;
+                            }
+                            if (i < lim) dst[(size_t)i * p.ldo] = __float2bfloat16(v);
+                        }
                     }
                 }
             }
             tc::fence_before_sync();
             __syncwarp();
             if (lane == 0) tc::mbar_arrive(&tmem_empty[buf]);
+            cur = nxt;
         }
     }
     tc::fence_before_sync();
@@ -432,6 +451,44 @@ __global__ void __launch_bounds__(256) nvfp4_quantize_rows_kernel(const QuantPar
     }
 }
 
+// Quantised rows gathered into another order without quantising them again: out row m = source row src[m] (codes,
+// global scale, and the scale words moved from the source's tile layout, one group of `src_bn`-row tiles, to the padded
+// rows of `offsets` / `pad`).  One block per output row, one thread per 64 reduction indices.
+struct GatherParams {
+    uint8_t* q; uint8_t* sf; float* g;
+    const uint8_t* q_src; const uint8_t* sf_src; const float* g_src; const int* src;
+    int rows, src_rows, K, src_bn;
+    const int* offsets; const int* pad; int groups, bn;
+};
+
+__global__ void __launch_bounds__(256) nvfp4_gather_rows_kernel(const GatherParams p) {
+    pdl_grid_sync();
+    const int m = blockIdx.x, ks = threadIdx.x;
+    const int KT = p.K / 64;
+    if (ks >= KT) return;
+    const int sr = p.src[m];
+    const bool valid = sr >= 0 && sr < p.src_rows;
+    int lo = 0, hi = p.groups;
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (__ldg(p.offsets + mid) <= m) lo = mid; else hi = mid;
+    }
+    const int prow = __ldg(p.pad + lo) + (m - __ldg(p.offsets + lo));
+    uint4 c0 = make_uint4(0, 0, 0, 0), c1 = c0;
+    uint32_t sc = 0;
+    if (valid) {
+        const uint4* qs = reinterpret_cast<const uint4*>(p.q_src + (size_t)sr * (p.K / 2) + (size_t)ks * 32);
+        c0 = __ldg(qs); c1 = __ldg(qs + 1);
+        const int st = sr / p.src_bn, r = sr % p.src_bn;
+        sc = __ldg(reinterpret_cast<const uint32_t*>(p.sf_src + ((size_t)st * KT + ks) * 512 + (r % 32) * 16 + (r / 32) * 4));
+    }
+    uint4* qd = reinterpret_cast<uint4*>(p.q + (size_t)m * (p.K / 2) + (size_t)ks * 32);
+    qd[0] = c0; qd[1] = c1;
+    const int tile = prow / p.bn, r = prow % p.bn;
+    *reinterpret_cast<uint32_t*>(p.sf + ((size_t)tile * KT + ks) * 512 + (r % 32) * 16 + (r / 32) * 4) = sc;
+    if (ks == 0) p.g[m] = valid ? __ldg(p.g_src + sr) : 1.f;
+}
+
 template <int PAIR>
 int dispatch_bn(int bn, const void* W, int w_rows, const void* X, int x_rows, const Fp4Params& p, int max_tiles, cudaStream_t s) {
     switch (bn) {
@@ -489,6 +546,19 @@ SL_API int sl_nvfp4_sf_tiles(void* dst, const void* src, int mats, int rows, int
     const size_t words = (size_t)mats * rows * (K / 64);
     const int blocks = (int)std::min<size_t>((words + 255) / 256, 148 * 16);
     sl_launch(sf_tiles_kernel, blocks, 256, 0, s, (uint8_t*)dst, (const uint8_t*)src, words, rows, K / 16);
+    return (int)cudaGetLastError();
+}
+
+// Already quantised rows (q_src / sf_src / g_src: `src_rows` ungrouped rows whose scale tiles were written for `src_bn`-row
+// tiles) gathered into grouped order: out row m = source row src[m], scales placed by `offsets` / `pad` / `bn`.
+SL_API int sl_nvfp4_gather_rows(void* q, void* sf, void* g, const void* q_src, const void* sf_src, const void* g_src, const void* src,
+                                int rows, int src_rows, int K, int src_bn, const void* offsets, const void* pad, int groups, int bn,
+                                cudaStream_t s) {
+    if (rows <= 0) return 0;
+    if (K % 64 != 0 || K > 16384 || src == nullptr || offsets == nullptr || pad == nullptr) return -1;
+    GatherParams p{(uint8_t*)q, (uint8_t*)sf, (float*)g, (const uint8_t*)q_src, (const uint8_t*)sf_src, (const float*)g_src,
+                   (const int*)src, rows, src_rows, K, src_bn, (const int*)offsets, (const int*)pad, groups, bn};
+    sl_launch(nvfp4_gather_rows_kernel, rows, (K / 64 + 31) / 32 * 32, 0, s, p);
     return (int)cudaGetLastError();
 }
 

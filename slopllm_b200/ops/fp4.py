@@ -21,6 +21,7 @@ N._SIGS.update({
     "sl_fp4_build_tiles": [vp, vp, vp, vp, i32, i32, i32, i32, i32, vp],
     "sl_gemm_fp4_tcgen05": [vp, vp, vp, i32, vp, vp, vp, i32, vp, i32, i32, i32, i32, i32, vp, vp, i32, vp, vp],
     "sl_nvfp4_sf_tiles": [vp, vp, i32, i32, i32, vp],
+    "sl_nvfp4_gather_rows": [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp, vp, i32, i32, vp],
     "sl_nvfp4_quantize_rows": [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp, vp, i32, i32, vp],
 })
 
@@ -71,11 +72,21 @@ def group_plan(offsets: torch.Tensor, groups: int, rows: int, bn: int = 0) -> Gr
     return GroupPlan(offsets, pad, groups, rows, bn)
 
 
+_single = {}
+
+
 def single_group(rows: int, device, bn: int = 0) -> GroupPlan:
+    """Plan of one group that holds all rows (plain products); kept per shape, so repeated calls upload nothing."""
     bn = bn or pick_bn(rows)
-    padded = (rows + bn - 1) // bn * bn
-    return GroupPlan(torch.tensor([0, rows], dtype=torch.int32, device=device), torch.tensor([0, padded], dtype=torch.int32, device=device),
-                     1, rows, bn)
+    key = (rows, bn, str(device))
+    plan = _single.get(key)
+    if plan is None:
+        padded = (rows + bn - 1) // bn * bn
+        plan = GroupPlan(torch.tensor([0, rows], dtype=torch.int32, device=device),
+                         torch.tensor([0, padded], dtype=torch.int32, device=device), 1, rows, bn)
+        if len(_single) < 256:
+            _single[key] = plan
+    return plan
 
 
 def quantize_rows(x: torch.Tensor, src: Optional[torch.Tensor] = None, rows: Optional[int] = None, terms: int = 1,
@@ -100,6 +111,20 @@ def quantize_rows(x: torch.Tensor, src: Optional[torch.Tensor] = None, rows: Opt
            x.stride(0), terms, N.ptr(plan.offsets) if plan else 0, N.ptr(plan.pad) if plan else 0, plan.groups if plan else 1, bn,
            N.stream())
     return q, sf, g
+
+
+def gather_rows(q: torch.Tensor, sf: torch.Tensor, g: torch.Tensor, src_bn: int, src: torch.Tensor, plan: GroupPlan):
+    """Rows already quantised (ungrouped, scale tiles for `src_bn`-row tiles) gathered into the grouped order of `plan`:
+    row m of the result is source row src[m].  Quantising each token once and copying its 4-bit row to every expert it was
+    routed to moves a quarter of the bytes that quantising the gathered 16-bit rows would."""
+    M, K = src.numel(), q.shape[1] * 2
+    dev = q.device
+    qo = torch.empty(M, K // 2, dtype=torch.uint8, device=dev)
+    sfo = torch.zeros(plan.max_row_tiles * (K // 64) * 512, dtype=torch.uint8, device=dev)
+    go = torch.empty(M, dtype=torch.float32, device=dev)
+    N.call("sl_nvfp4_gather_rows", qo.data_ptr(), sfo.data_ptr(), go.data_ptr(), q.data_ptr(), sf.data_ptr(), g.data_ptr(),
+           src.data_ptr(), M, q.shape[0], K, src_bn, plan.offsets.data_ptr(), plan.pad.data_ptr(), plan.groups, plan.bn, N.stream())
+    return qo, sfo, go
 
 
 def scales_row_major(sf: torch.Tensor, rows: int, K: int, bn: int) -> torch.Tensor:

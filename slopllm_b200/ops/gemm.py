@@ -147,13 +147,13 @@ def fp4_moe_ok(experts, H: int) -> bool:
     return bool(MOE_A4 and experts.is_nvfp4 and fp4.shapes_ok(I, H) and fp4.shapes_ok(H, I) and I % 128 == 0)
 
 
-def experts_fp4(experts, x, src_rows, plan, out_kind: int = OUT_BF16) -> torch.Tensor:
-    """SwiGLU experts over expert-sorted rows on the block-scaled path: gather + NVFP4 quantisation of the token rows
-    (row m of the sorted order = x[src_rows[m]]), gate/up with the SiLU * mul epilogue, re-quantisation of the
-    activations, down projection.  Returns [rows, H] (bf16 or fp32)."""
+def experts_fp4(experts, xq3, plan, out_kind: int = OUT_BF16) -> torch.Tensor:
+    """SwiGLU experts over expert-sorted, NVFP4-quantised rows `xq3` = (codes, scale tiles, global scales) laid out for
+    `plan`: gate/up with the SiLU * mul epilogue, re-quantisation of the activations, down projection.
+    Returns [rows, H] (bf16 or fp32)."""
     from . import fp4
     sf13, sf2 = _sf_tiles_of(experts)
-    xq, sfx, gx = fp4.quantize_rows(x, src_rows, plan=plan)
+    xq, sfx, gx = xq3
     act = fp4.grouped_gemm_fp4(experts.w13, sf13, experts.g13, xq, sfx, gx, plan, experts.inter, True, fp4.OUT_BF16)
     aq, sfa, ga = fp4.quantize_rows(act, plan=plan)
     return fp4.grouped_gemm_fp4(experts.w2, sf2, experts.g2, aq, sfa, ga, plan, experts.hidden, False, out_kind)
@@ -190,8 +190,12 @@ def moe_large(ops, x, experts, shared, ids, wts) -> torch.Tensor:
         out = torch.empty(T, H, dtype=torch.float32, device=dev)
     if use_fp4:
         # tokens gathered into expert order and quantised in one pass; both expert GEMMs on tcgen05 kind::mxf4nvf4
+        # every token row is quantised once; the experts get copies of the 4-bit rows in expert order
         from . import fp4
-        y = experts_fp4(experts, xb, src_tok, fp4.group_plan(offsets, E, M))
+        plan = fp4.group_plan(offsets, E, M)
+        xq_tok = getattr(xb, "_sl_fp4", None) or fp4.quantize_rows(xb, bn=128)
+        xb._sl_fp4 = None
+        y = experts_fp4(experts, fp4.gather_rows(*xq_tok, 128, src_tok, plan), plan)
         N.call("sl_moe_unsort_reduce", out.data_ptr(), y.data_ptr(), rows_of.data_ptr(), wts.data_ptr(), T, k, H, acc, 1, N.stream())
         return out
     if experts.is_nvfp4 and _w4_ok(H) and _w4_ok(I) and xb.stride(0) % 8 == 0:
@@ -234,7 +238,9 @@ def _shared_expert_large(xb: torch.Tensor, shared, use_fp4: bool = False) -> tor
     T = xb.shape[0]
     if use_fp4 and fp4_moe_ok(shared, xb.shape[1]):
         from . import fp4
-        return experts_fp4(shared, xb, None, fp4.single_group(T, xb.device), OUT_F32)
+        xq_tok = fp4.quantize_rows(xb, bn=128)
+        xb._sl_fp4 = xq_tok                              # the routed experts of the same layer reuse it
+        return experts_fp4(shared, xq_tok, fp4.single_group(T, xb.device, 128), OUT_F32)
     if shared.is_nvfp4:
         w13 = dequant_bf16(shared.w13[0], shared.s13[0], shared.g13[0], g_per=2, split=shared.inter)
         w2 = dequant_bf16(shared.w2[0], shared.s2[0], shared.g2[0].reshape(1))

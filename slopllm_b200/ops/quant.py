@@ -82,6 +82,20 @@ def nvfp4_quantize(w: torch.Tensor, global_scale=None):
     return pack_nibbles(codes), scale, g.reshape(())
 
 
+def nvfp4_fake_quant_rows(x: torch.Tensor) -> torch.Tensor:
+    """What a row of activations becomes on the W4A4 path: NVFP4 with one global scale per row (amax / (6 * 448)), e4m3
+    scales per 16 values, E2M1 codes, back in fp32 (the definition `sl_nvfp4_quantize_rows` is tested against)."""
+    xf = x.to(torch.float32)
+    K = xf.shape[-1]
+    g = (xf.abs().amax(-1, keepdim=True) / (FP8_MAX * FP4_MAX))
+    g = torch.where(g > 0, g, torch.ones_like(g))
+    blocks = xf.reshape(*xf.shape[:-1], K // NVFP4_BLOCK, NVFP4_BLOCK)
+    scale = (blocks.abs().amax(-1) / FP4_MAX / g).to(torch.float8_e4m3fn).to(torch.float32)
+    dq = (scale * g).unsqueeze(-1)
+    codes = _round_to_e2m1_codes(torch.where(dq > 0, blocks / dq.clamp(min=1e-30), torch.zeros_like(blocks)))
+    return (e2m1_table(x.device)[codes] * dq).reshape(xf.shape)
+
+
 def fp8_quantize_block(x: torch.Tensor, block: int = 128, pow2: bool = False):
     """Per-`block` e4m3 quantisation along the last dim.  Returns (fp8 tensor, f32 scales).
 

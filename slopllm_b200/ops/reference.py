@@ -124,19 +124,27 @@ def _stable_topk(x: torch.Tensor, k: int) -> torch.Tensor:
 
 
 def moe_experts(x: torch.Tensor, experts, ids: torch.Tensor, weights: torch.Tensor,
-                col_slice: Optional[Tuple[int, int]] = None) -> torch.Tensor:
+                col_slice: Optional[Tuple[int, int]] = None, a4: bool = False) -> torch.Tensor:
     """Σ_k w_k · down_e(silu(gate_e x) · up_e x) over the routed experts of each token.
 
     `experts` is an :class:`ExpertWeights` (possibly TP-sliced on the intermediate dim, in
-    which case the result is this rank's partial sum).
+    which case the result is this rank's partial sum).  `a4` emulates the W4A4 path of the block-scaled tensor-core
+    kernels: the token rows and the intermediate activations go through NVFP4 (as bf16 rows) before each product.
     """
     xf = x.to(torch.float32)
+    if a4:
+        xf = quant.nvfp4_fake_quant_rows(x.to(torch.bfloat16))
     out = torch.zeros(x.shape[0], experts.hidden, dtype=torch.float32, device=x.device)
     for e in torch.unique(ids).tolist():
         tok, slot = (ids == e).nonzero(as_tuple=True)
         w13, w2 = experts.dequant_expert(int(e))
         h = silu_mul(xf[tok] @ w13.t())
-        out.index_add_(0, tok, (h @ w2.t()) * weights[tok, slot].unsqueeze(-1))
+        if a4:
+            h = quant.nvfp4_fake_quant_rows(h.to(torch.bfloat16))
+        y = h @ w2.t()
+        if a4:
+            y = y.to(torch.bfloat16).to(torch.float32)
+        out.index_add_(0, tok, y * weights[tok, slot].unsqueeze(-1))
     return out
 
 

@@ -110,3 +110,17 @@ def test_gemm_fp4_grouped_ragged(pair):
             ref[at:at + n] = h * gA[e]
         at += n
     close(y, ref, 3e-3, "grouped fp4 gemm")
+
+
+def test_gather_of_quantised_rows_equals_quantising_the_gathered_rows():
+    from slopllm_b200.ops import fp4
+    T, K, G = 50, 512, 4
+    g = torch.Generator(device=DEV).manual_seed(9)
+    x = torch.randn(T, K, device=DEV, generator=g).to(torch.bfloat16)
+    src = torch.randint(0, T, (173,), device=DEV, generator=g).to(torch.int32)
+    off = torch.tensor([0, 60, 60, 100, 173], dtype=torch.int32, device=DEV)
+    plan = fp4.group_plan(off, G, 173, 64)
+    a = fp4.quantize_rows(x, src, plan=plan)
+    b = fp4.gather_rows(*fp4.quantize_rows(x, bn=128), 128, src, plan)
+    for u, v in zip(a, b):
+        assert torch.equal(u, v)

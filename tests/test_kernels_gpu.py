@@ -396,12 +396,28 @@ def test_norm_emits_permuted_operand(T):
     close(ops.moe_tp(perm, lw), ops.moe_tp(plain, lw), tol=1e-6, what="moe with emitted operand")
 
 
-def test_moe_large_matches_reference():
+def test_moe_large_matches_reference(monkeypatch):
+    """Prefill-sized MoE.  With 16-bit activations (SLOPLLM_B200_MOE_A4=0: the expansion kernels) against the fp32
+    reference; on the default block-scaled FP4 path against the reference with the same NVFP4 activation rows."""
+    from slopllm_b200.ops import gemm
     cfg = mini_cfg(hidden_size=1024, moe_intermediate_size=256)
     ops, ref = cuda_ops(cfg), RefOps(cfg)
     lw = random_layer(cfg, 1, 0, DEV, torch.bfloat16)
-    x = torch.randn(200, cfg.hidden_size, device=DEV, generator=torch.Generator(device=DEV).manual_seed(2)).to(torch.bfloat16)
-    close(ops.moe_tp(x, lw), ref.moe_tp(x, lw), tol=2e-2, what="moe large")
+    x = torch.randn(200, cfg.hidden_size, device=DEV, generator=torch.Generator(device=DEV).manual_seed(4)).to(torch.bfloat16)
+    exact = ref.moe_tp(x, lw)
+    monkeypatch.setattr(gemm, "MOE_A4", False)
+    close(ops.moe_tp(x, lw), exact, tol=2e-2, what="moe large, 16-bit activations")
+    monkeypatch.setattr(gemm, "MOE_A4", True)
+    assert gemm.fp4_moe_ok(lw.experts, cfg.hidden_size)
+    y4 = ops.moe_tp(x, lw)
+    ids, w = ref.route(x, lw)
+    T = x.shape[0]
+    emul = R.moe_experts(x, lw.experts, ids, w, a4=True) + R.moe_experts(
+        x, lw.shared, torch.zeros(T, 1, dtype=torch.int32, device=DEV), torch.ones(T, 1, device=DEV), a4=True)
+    close(y4, emul, tol=2e-2, what="moe large, NVFP4 activations vs the emulation")
+    close(y4, exact, tol=0.2, what="moe large, NVFP4 activations vs 16-bit activations")
+    rel = ((y4.float() - exact).norm() / exact.norm()).item()
+    assert rel < 0.15, rel
 
 
 @pytest.mark.parametrize("M,N,K", [(300, 512, 1024), (129, 200, 64), (4096, 768, 2048)])
