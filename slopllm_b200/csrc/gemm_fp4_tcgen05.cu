@@ -71,6 +71,10 @@ struct Fp4Params {
     int pair_rows, pair_blks;      // PAIR: distance from a gate row to its up row, in rows and in 128-row scale blocks
     const Fp4Tile* tiles; const int* num_tiles;
     int* err;
+    // expert-parallel combine: when set, output row m (bf16) is not stored at out[m] but at scatter_base[meta.x] +
+    // meta.y * ldo, meta = row_meta[m] = {home rank of the row's token, its route slot there} (peer memory, plain stores)
+    const int2* row_meta;
+    bf16* scatter_base[8];
 };
 
 template <int BN, int PAIR>
@@ -183,14 +187,21 @@ __global__ void __launch_bounds__(192) gemm_fp4_kernel(const __grid_constant__ C
         // Everything the epilogue of a tile reads from global memory (its table entry, the weights' global scales, the
         // token rows' global scales) is fetched one tile ahead, while the previous tile is being stored: with a short
         // reduction (one or two stages per tile) those dependent loads would otherwise be the tile's critical path.
-        struct Pre { Fp4Tile t; float ga, gu; float gb[BN / 32]; };
+        struct Pre { Fp4Tile t; float ga, gu; float gb[BN / 32]; unsigned long long dst[BN / 32]; };
         auto prefetch = [&](int tile, Pre& pre) {
             pre.t = p.tiles[tile];
             pre.ga = PAIR ? __ldg(p.gA + 2 * pre.t.group) : __ldg(p.gA + pre.t.group);
             pre.gu = PAIR ? __ldg(p.gA + 2 * pre.t.group + 1) : 0.f;
 #pragma unroll
-            for (int c = 0; c < BN / 32; ++c)
-                pre.gb[c] = (c * 32 + lane < pre.t.b_valid) ? __ldg(p.gB + pre.t.b_row0 + c * 32 + lane) : 0.f;
+            for (int c = 0; c < BN / 32; ++c) {
+                const bool in = c * 32 + lane < pre.t.b_valid;
+                pre.gb[c] = in ? __ldg(p.gB + pre.t.b_row0 + c * 32 + lane) : 0.f;
+                pre.dst[c] = 0ull;
+                if (p.row_meta != nullptr && in) {
+                    const int2 mt = __ldg(p.row_meta + pre.t.b_row0 + c * 32 + lane);
+                    pre.dst[c] = (unsigned long long)(p.scatter_base[mt.x & 7] + (size_t)mt.y * p.ldo);
+                }
+            }
         };
         Pre cur;
         if ((int)blockIdx.x < total) prefetch(blockIdx.x, cur);
@@ -230,6 +241,19 @@ __global__ void __launch_bounds__(192) gemm_fp4_kernel(const __grid_constant__ C
                                 v = v / (1.f + __expf(-v)) * u;
                             }
                             if (i < lim) dst[(size_t)i * p.ldo] = v;
+                        }
+                    } else if (p.row_meta != nullptr) {
+                        const unsigned long long my_dst = cur.dst[c];    // lane i holds where token c0 + i's row goes
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            const float gb = __shfl_sync(0xffffffffu, my_gb, i);
+                            bf16* row = reinterpret_cast<bf16*>(__shfl_sync(0xffffffffu, my_dst, i));
+                            float v = __uint_as_float(r0[i]) * ga * gb;
+                            if (PAIR) {
+                                const float u = __uint_as_float(r1[i]) * gu * gb;
+                                v = v / (1.f + __expf(-v)) * u;
+                            }
+                            if (i < lim) row[n] = __float2bfloat16(v);
                         }
                     } else {
                         bf16* dst = (bf16*)p.out + (size_t)(t.b_row0 + c0) * p.ldo + n;
@@ -364,6 +388,7 @@ struct QuantParams {
     const bf16* x; const int* src;
     int rows, x_rows, K, ldx, terms;
     const int* offsets; const int* pad; int groups, bn;
+    const int* num_rows;           // optional: rows at or beyond *num_rows are skipped (receive buffers with spare capacity)
 };
 
 __device__ __forceinline__ float e2m1_value(uint32_t code) {
@@ -377,6 +402,7 @@ __global__ void __launch_bounds__(256) nvfp4_quantize_rows_kernel(const QuantPar
     pdl_grid_sync();
     __shared__ float scratch[33];
     const int m = blockIdx.x, ks = threadIdx.x;
+    if (p.num_rows != nullptr && m >= __ldg(p.num_rows)) return;
     const int KT = p.K / 64;
     const int sr = p.src ? p.src[m] : m;
     const bool valid = sr >= 0 && sr < p.x_rows && ks < KT;
@@ -539,6 +565,24 @@ SL_API int sl_gemm_fp4_tcgen05(const void* W, const void* sfa, const void* gA, i
     return pair_rows > 0 ? dispatch_bn<1>(bn, W, w_rows, X, x_rows, p, max_tiles, s) : dispatch_bn<0>(bn, W, w_rows, X, x_rows, p, max_tiles, s);
 }
 
+// The same product with the expert-parallel combine epilogue: bf16 output row m goes to
+// scatter_base[row_meta[m].x] + row_meta[m].y * ldo (`scatter_base`: W pointers, peer mappings of the home ranks'
+// combine buffers).
+SL_API int sl_gemm_fp4_tcgen05_scatter(const void* W, const void* sfa, const void* gA, int w_rows, const void* X, const void* sfb,
+                                       const void* gB, int x_rows, const void* row_meta, void* const* scatter_base, int world, int ldo,
+                                       int K, int bn, const void* tiles, const void* num_tiles, int max_tiles, void* err,
+                                       cudaStream_t s) {
+    if (w_rows <= 0 || x_rows <= 0 || max_tiles <= 0) return 0;
+    if (K % 256 != 0 || K <= 0 || row_meta == nullptr || world < 1 || world > 8) return -1;
+    Fp4Params p{};
+    p.sfa = (const uint8_t*)sfa; p.sfb = (const uint8_t*)sfb; p.gA = (const float*)gA; p.gB = (const float*)gB; p.out = nullptr; p.K = K;
+    p.ldo = ldo; p.out_kind = 0; p.pair_rows = 0; p.pair_blks = 0;
+    p.tiles = (const Fp4Tile*)tiles; p.num_tiles = (const int*)num_tiles; p.err = (int*)err;
+    p.row_meta = (const int2*)row_meta;
+    for (int r = 0; r < 8; ++r) p.scatter_base[r] = (bf16*)scatter_base[r < world ? r : 0];
+    return dispatch_bn<0>(bn, W, w_rows, X, x_rows, p, max_tiles, s);
+}
+
 // Row-major block scales [mats][rows][K/16] -> the tile layout the kernel above loads (rows % 128 == 0, K % 64 == 0).
 SL_API int sl_nvfp4_sf_tiles(void* dst, const void* src, int mats, int rows, int K, cudaStream_t s) {
     if (mats <= 0 || rows <= 0) return 0;
@@ -564,16 +608,18 @@ SL_API int sl_nvfp4_gather_rows(void* q, void* sf, void* g, const void* q_src, c
 
 // bf16 rows -> NVFP4 rows (+ residual terms).  q [rows * terms, K/2], g [rows * terms], sf = scale tiles
 // [padded rows / bn][K/64][512]; `src` (int32 [rows], may be null) gathers: output row m quantises x[src[m]].
-// `offsets` / `pad` (may be null: one group, no padding) place the scales of grouped rows, see sl_fp4_group_pad.
+// `offsets` / `pad` (may be null: one group, no padding) place the scales of grouped rows, see sl_fp4_group_pad;
+// `num_rows` (device int, may be null) limits the rows that are really quantised.
 // K % 64 == 0, K <= 16384, ldx % 8 == 0, x 16-byte aligned.
 SL_API int sl_nvfp4_quantize_rows(void* q, void* sf, void* g, const void* x, const void* src, int rows, int x_rows, int K, int ldx,
-                                  int terms, const void* offsets, const void* pad, int groups, int bn, cudaStream_t s) {
+                                  int terms, const void* offsets, const void* pad, int groups, int bn, const void* num_rows,
+                                  cudaStream_t s) {
     if (rows <= 0) return 0;
     if (K % 64 != 0 || K > 16384 || terms < 1 || terms > 4 || ldx % 8 != 0 || ((uintptr_t)x & 15) != 0) return -1;
     if (bn != 32 && bn != 64 && bn != 128) return -1;
     if ((offsets != nullptr) != (pad != nullptr) || (offsets != nullptr && terms != 1)) return -1;
     QuantParams p{(uint8_t*)q, (uint8_t*)sf, (float*)g, (const bf16*)x, (const int*)src, rows, x_rows, K, ldx, terms,
-                  (const int*)offsets, (const int*)pad, groups, bn};
+                  (const int*)offsets, (const int*)pad, groups, bn, (const int*)num_rows};
     const int threads = (K / 64 + 31) / 32 * 32;
     sl_launch(nvfp4_quantize_rows_kernel, rows, threads, 0, s, p);
     return (int)cudaGetLastError();

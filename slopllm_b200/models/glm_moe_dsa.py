@@ -23,7 +23,8 @@ from ..config import GlmMoeDsaConfig, PAGE_SIZE, env_flag
 from ..parallel.dist import Comm, ParallelContext
 from ..utils.tracing import traced
 
-EP_ALL_TO_ALL = env_flag("EP_A2A")      # expert parallelism by token dispatch / combine instead of masked partial sums
+EP_ALL_TO_ALL = env_flag("EP_A2A")      # expert parallelism by token dispatch / combine over NCCL instead of masked partial sums
+EP_FUSED_MIN_T = 33                     # from this many token rows on `--ep` dispatches / combines in kernels over peer memory
 from .weights import LayerWeights, ModelWeights
 
 
@@ -170,6 +171,10 @@ class GlmMoeDsaModel:
         if lw.experts is not None and ctx.ep and ctx.world > 1:
             if EP_ALL_TO_ALL:
                 return self._moe_ep(lw, y)
+            if y.shape[0] >= EP_FUSED_MIN_T and self._ep_exchange_for(lw, y) is not None:
+                out = self._moe_ep_fused(lw, y)
+                sink = self.comm.partial_sink(y.shape[0], final=final)
+                return out if sink is None else sink.push_tensor(out)
             out = self._moe_ep_partial(lw, y)
             sink = self.comm.partial_sink(y.shape[0], final=final)
             return out if sink is None else sink.push_tensor(out)
@@ -193,6 +198,44 @@ class GlmMoeDsaModel:
                                     torch.where(mine, wts, torch.zeros_like(wts)))
         if lw.shared is not None:
             out = out + ops.shared_expert(y, lw).to(out.dtype)
+        return out
+
+    EP_MAX_TOKENS = 8192       # most token rows of one forward that the fused exchange's buffers are sized for
+
+    def _ep_exchange_for(self, lw: LayerWeights, y: torch.Tensor):
+        """The peer-memory exchange of this model (made on first use), or None where the fused path does not apply: not on
+        CUDA, weights not NVFP4 or of shapes the block-scaled kernels do not take, more rows than the buffers hold."""
+        if getattr(self, "_ep_exchange", None) is not None:
+            return self._ep_exchange if y.shape[0] <= self.EP_MAX_TOKENS else None
+        if getattr(self, "_ep_unavailable", False) or not y.is_cuda or env_flag("EP_NO_FUSED"):
+            return None
+        from ..ops.gemm import fp4_moe_ok
+        if not fp4_moe_ok(lw.experts, self.cfg.hidden_size) or y.shape[0] > self.EP_MAX_TOKENS:
+            self._ep_unavailable = not fp4_moe_ok(lw.experts, self.cfg.hidden_size)
+            return None
+        from ..parallel.ep import make_exchange
+        self._ep_exchange = make_exchange(self.ctx, self.cfg, self.EP_MAX_TOKENS)
+        return self._ep_exchange
+
+    def _moe_ep_fused(self, lw: LayerWeights, y: torch.Tensor):
+        """Expert parallelism with the exchange in kernels: each rank is home to a slice of the rows, stores the 4-bit copy
+        of every routed row into its expert's owner over NVLink, the owners run their experts as block-scaled grouped GEMMs
+        whose epilogue stores the results back into the home rank, which sums them with the routing weights
+        (`parallel/ep.py`).  The result holds the home rows only (plus this rank's slice of the shared expert for all
+        rows), so the all-reduce that follows also acts as the all-gather of the rows."""
+        ops, ctx = self.ops, self.ctx
+        W, r = ctx.world, ctx.rank
+        T = y.shape[0]
+        per = -(-T // W)
+        lo, hi = min(T, r * per), min(T, (r + 1) * per)
+        yb = y if y.dtype == torch.bfloat16 else y.to(torch.bfloat16)
+        x_loc = yb[lo:hi].contiguous()
+        ids, wts = ops.route(x_loc, lw) if hi > lo else (torch.zeros(0, self.cfg.num_experts_per_tok, dtype=torch.int32, device=y.device),
+                                                         torch.zeros(0, self.cfg.num_experts_per_tok, device=y.device))
+        out = ops.shared_expert(yb, lw).to(torch.float32) if lw.shared is not None else torch.zeros(T, y.shape[1], dtype=torch.float32, device=y.device)
+        if not out.is_contiguous():
+            out = out.contiguous()
+        self._ep_exchange.moe(x_loc, lw.experts, ids, wts, out[lo:hi], accumulate=True)
         return out
 
     def _moe_ep(self, lw: LayerWeights, y: torch.Tensor):

@@ -22,7 +22,8 @@ N._SIGS.update({
     "sl_gemm_fp4_tcgen05": [vp, vp, vp, i32, vp, vp, vp, i32, vp, i32, i32, i32, i32, i32, vp, vp, i32, vp, vp],
     "sl_nvfp4_sf_tiles": [vp, vp, i32, i32, i32, vp],
     "sl_nvfp4_gather_rows": [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp, vp, i32, i32, vp],
-    "sl_nvfp4_quantize_rows": [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp, vp, i32, i32, vp],
+    "sl_nvfp4_quantize_rows": [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp, vp, i32, i32, vp, vp],
+    "sl_gemm_fp4_tcgen05_scatter": [vp, vp, vp, i32, vp, vp, vp, i32, vp, vp, i32, i32, i32, i32, vp, vp, i32, vp, vp],
 })
 
 OUT_BF16, OUT_F32 = 0, 1
@@ -90,7 +91,8 @@ def single_group(rows: int, device, bn: int = 0) -> GroupPlan:
 
 
 def quantize_rows(x: torch.Tensor, src: Optional[torch.Tensor] = None, rows: Optional[int] = None, terms: int = 1,
-                  plan: Optional[GroupPlan] = None, bn: int = 128) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+                  plan: Optional[GroupPlan] = None, bn: int = 128,
+                  num_rows: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """bf16 rows -> (codes u8 [M * terms, K/2], scale tiles u8, global scales f32 [M * terms]).
     With `src` output row m quantises x[src[m]] (a gather, e.g. into expert-sorted order); with `terms` > 1 rows
     m + j * M hold the j-th residual of row m, so that the sum of the terms approaches the 16-bit value.  The scale tiles
@@ -109,7 +111,7 @@ def quantize_rows(x: torch.Tensor, src: Optional[torch.Tensor] = None, rows: Opt
     g = torch.empty(M * terms, dtype=torch.float32, device=dev)
     N.call("sl_nvfp4_quantize_rows", q.data_ptr(), sf.data_ptr(), g.data_ptr(), x.data_ptr(), N.ptr(src), M, x.shape[0], K,
            x.stride(0), terms, N.ptr(plan.offsets) if plan else 0, N.ptr(plan.pad) if plan else 0, plan.groups if plan else 1, bn,
-           N.stream())
+           N.ptr(num_rows), N.stream())
     return q, sf, g
 
 

@@ -134,6 +134,50 @@ class BulkSink:
         return self
 
 
+def symmetric_alloc(ctx: ParallelContext, nbytes: int):
+    """A zeroed buffer of `nbytes` on every rank, each mapped into every rank's address space.  Returns (this rank's
+    tensor, the W addresses at which the ranks' buffers are mapped here, what must stay alive / be closed).  CUDA IPC
+    handles travel over the process group; `SLOPLLM_B200_SYMM=torch` uses torch's symmetric-memory rendezvous instead."""
+    from ..config import env_str
+    if env_str("SYMM") == "torch":
+        import torch.distributed._symmetric_memory as symm
+        buf = symm.empty(nbytes, dtype=torch.uint8, device=ctx.device)
+        buf.zero_()
+        hdl = symm.rendezvous(buf, group=ctx.group or dist.group.WORLD)
+        return buf, [int(p) for p in hdl.buffer_ptrs], hdl
+    buf = torch.zeros(nbytes, dtype=torch.uint8, device=ctx.device)
+    torch.cuda.synchronize()
+    handle = (C.c_ubyte * 64)()
+    offset = C.c_ulonglong(0)
+    lib = N.kernels()
+    lib.sl_ipc_export.argtypes = [vp, vp, C.POINTER(C.c_ulonglong)]
+    lib.sl_ipc_open.argtypes = [vp, C.c_ulonglong, C.POINTER(vp)]
+    N.check(lib.sl_ipc_export(buf.data_ptr(), handle, C.byref(offset)), "sl_ipc_export")
+    mine = (bytes(handle), int(offset.value))
+    everyone = [None] * ctx.world
+    dist.all_gather_object(everyone, mine, group=ctx.group)
+    ptrs, opened = [], []
+    for r, (hb, off) in enumerate(everyone):
+        if r == ctx.rank:
+            ptrs.append(buf.data_ptr())
+            continue
+        out = vp()
+        hbuf = (C.c_ubyte * 64).from_buffer_copy(hb)
+        N.check(lib.sl_ipc_open(hbuf, off, C.byref(out)), f"sl_ipc_open(rank {r})")
+        ptrs.append(int(out.value))
+        opened.append((int(out.value), int(off)))
+    return buf, ptrs, (everyone, opened)
+
+
+def symmetric_close(keep) -> None:
+    """Unmap what `symmetric_alloc` opened (CUDA IPC mappings of the peers' buffers)."""
+    if isinstance(keep, tuple) and len(keep) == 2:
+        lib = N.kernels()
+        lib.sl_ipc_close.argtypes = [vp, C.c_ulonglong]
+        for ptr, off in keep[1]:
+            lib.sl_ipc_close(ptr, off)
+
+
 class SymmetricRegion:
     """Symmetric receive buffers + flags, and this rank's local epoch / counter words.
 
@@ -290,36 +334,7 @@ class NvlinkComm(Comm):
         gather_bytes = 1 << 20
         bulk_rows = NvlinkComm.bulk_rows_from_env()
         lay = SymmetricRegion.layout(ctx.world, NvlinkComm.MAX_ROWS, H, gather_bytes, cp_shape, bulk_rows)
-        if env_str("SYMM") == "torch":
-            import torch.distributed._symmetric_memory as symm
-            buf = symm.empty(lay["total"], dtype=torch.uint8, device=ctx.device)
-            buf.zero_()
-            hdl = symm.rendezvous(buf, group=ctx.group or dist.group.WORLD)
-            ptrs = [int(p) for p in hdl.buffer_ptrs]
-            keep = hdl
-        else:
-            buf = torch.zeros(lay["total"], dtype=torch.uint8, device=ctx.device)
-            torch.cuda.synchronize()
-            handle = (C.c_ubyte * 64)()
-            offset = C.c_ulonglong(0)
-            lib = N.kernels()
-            lib.sl_ipc_export.argtypes = [vp, vp, C.POINTER(C.c_ulonglong)]
-            lib.sl_ipc_open.argtypes = [vp, C.c_ulonglong, C.POINTER(vp)]
-            N.check(lib.sl_ipc_export(buf.data_ptr(), handle, C.byref(offset)), "sl_ipc_export")
-            mine = (bytes(handle), int(offset.value))
-            everyone = [None] * ctx.world
-            dist.all_gather_object(everyone, mine, group=ctx.group)
-            ptrs, opened = [], []
-            for r, (hb, off) in enumerate(everyone):
-                if r == ctx.rank:
-                    ptrs.append(buf.data_ptr())
-                    continue
-                out = vp()
-                hbuf = (C.c_ubyte * 64).from_buffer_copy(hb)
-                N.check(lib.sl_ipc_open(hbuf, off, C.byref(out)), f"sl_ipc_open(rank {r})")
-                ptrs.append(int(out.value))
-                opened.append((int(out.value), int(off)))
-            keep = (everyone, opened)
+        buf, ptrs, keep = symmetric_alloc(ctx, lay["total"])
         torch.cuda.synchronize()
         dist.barrier(group=ctx.group)
         from ..config import env_int
@@ -449,9 +464,6 @@ class NvlinkComm(Comm):
         replaced - after a lost rank its peers' mappings point into a process that no longer exists - with no kernel of
         this communicator in flight."""
         keep = getattr(self.region, "_keep", None)
-        if isinstance(keep, tuple) and len(keep) == 2:
-            lib = N.kernels()
-            lib.sl_ipc_close.argtypes = [vp, C.c_ulonglong]
-            for ptr, off in keep[1]:
-                lib.sl_ipc_close(ptr, off)
+        if keep is not None:
+            symmetric_close(keep)
             self.region._keep = None

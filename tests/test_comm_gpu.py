@@ -252,3 +252,80 @@ def test_tp2_fused_equals_nccl_on_two_gpus(cp, bulk):
         return
     # fused and library collectives sum in different orders: allow a late near-tie flip
     assert res[0][True][:4] == res[0][False][:4]
+
+
+def _ep_worker(rank, world, port, q):
+    """Expert parallelism on real GPUs: prefill chunks of 64 rows take the peer-memory dispatch / combine kernels
+    (`parallel/ep.py`); the same run with that path switched off (every rank computes its experts for all rows and the
+    all-reduce sums) must produce the same tokens."""
+    import traceback
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
+                      MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    try:
+        import torch.distributed as dist
+        from slopllm_b200.models.glm_moe_dsa import GlmMoeDsaModel
+        from slopllm_b200.models.weights import random_model
+        from slopllm_b200.parallel.dist import init_from_env
+        from slopllm_b200.parallel.fused import make_comm
+        from slopllm_b200.runtime.engine import Engine
+        ctx = init_from_env(ep=True)
+        cfg = GlmMoeDsaConfig(hidden_size=1024, intermediate_size=2048, moe_intermediate_size=512, num_hidden_layers=3,
+                              num_nextn_predict_layers=0, vocab_size=2048, num_attention_heads=8, q_lora_rank=256,
+                              n_routed_experts=16, num_experts_per_tok=4, n_group=4, topk_group=2, index_topk=64,
+                              first_k_dense_replace=1, quant_o_proj=True, quant_dense_mlp=True)
+        w = random_model(cfg, 0, ctx.device, torch.bfloat16, ctx.rank, ctx.world, ep=True, with_mtp=False)
+        g = torch.Generator().manual_seed(1)
+        prompts = [torch.randint(0, cfg.vocab_size, (100,), generator=g).tolist() for _ in range(2)]
+        out = {}
+        for fused_ep in (False, True):
+            comm = make_comm(ctx, cfg, fused=True)
+            model = GlmMoeDsaModel(cfg, w, ctx, comm=comm)
+            model._ep_unavailable = not fused_ep
+            eng = Engine(cfg, model, num_pages=16, max_batch=2, max_seq_len=512)
+            seqs = [eng.kv.new_sequence() for _ in range(2)]
+            last, _ = eng.prefill(seqs, prompts, chunk_size=64)
+            toks = [list(last)]
+            for _ in range(4):
+                last = eng.decode_step(seqs, last)
+                toks.append(list(last))
+            comm.check_status()
+            if fused_ep:
+                assert model._ep_exchange is not None
+                model._ep_exchange.check_status()
+                out["rounds"] = int(model._ep_exchange.state[0])
+            out[fused_ep] = toks
+        dist.barrier()
+        torch.cuda.synchronize()
+        q.put((rank, out, None))
+    except Exception:  # noqa: BLE001
+        q.put((rank, None, traceback.format_exc()))
+    q.close()
+    q.join_thread()
+    os._exit(0)
+
+
+@pytest.mark.multigpu
+def test_ep_dispatch_combine_on_two_gpus():
+    import torch.multiprocessing as mp
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_ep_worker, args=(r, world, port, q), daemon=True) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = {}
+    try:
+        for _ in range(world):
+            rank, out, err = q.get(timeout=300)
+            assert err is None, err
+            res[rank] = out
+    finally:
+        for p in procs:
+            p.join(timeout=20)
+            if p.is_alive():
+                p.kill()
+    assert res[0] == res[1]                               # the ranks agree on every token
+    assert res[0]["rounds"] == 2 * 2 * 2                  # 2 MoE layers x 2 prompts x 2 chunks went through the exchange
+    # the home rank quantises a row exactly as every rank does on the other path: same tokens (allow a late near-tie)
+    assert res[0][True][:3] == res[0][False][:3]
