@@ -194,7 +194,8 @@ def build_runtime(args, with_scheduler: bool = True) -> Runtime:
         eos = list(getattr(cfg, "eos_token_ids", None) or getattr(cfg, "eos_token_id", None) or [])
         tier = None
         if ecfg.max_host_pages > 0 and engine.supports_host_tier():
-            tier = HostTier(ecfg.max_host_pages, engine.kv.tokens_per_page, engine.read_page, engine.write_page)
+            tier = HostTier(ecfg.max_host_pages, engine.kv.tokens_per_page, engine.read_page, engine.write_page,
+                            read_pages=engine.read_pages, write_pages=engine.write_pages)
         sched = GenerationScheduler(engine, max_batch=ecfg.batch_size, chunk_size=ecfg.chunk_size, eos_token_ids=eos, host_tier=tier,
                                     decode_latency_ms=ecfg.decode_latency_ms, replica_channel=make_channel(ctx))
     tok = load_tokenizer(model_dir, vocab)

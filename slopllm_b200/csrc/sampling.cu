@@ -5,7 +5,7 @@
 // (candidate sampling), `:644-706` (spec_reject_linear), `:54-70` (lowbias32 counter RNG).
 #include "common.cuh"
 
-#define SL_MAX_CAND 64
+#define SL_MAX_CAND 256
 
 __device__ __forceinline__ uint32_t lowbias32(uint32_t x) {
     x ^= x >> 16; x *= 0x7feb352du;
@@ -95,7 +95,7 @@ struct SampleParams {
     const float *temperature, *top_p, *rep_penalty, *presence_penalty;   // [B]
     const int* top_k;                    // [B] (<= 0: max_k)
     const int64_t* history; const int* hist_len; int window;             // [B, window]
-    int max_k;                           // candidate capacity (<= 64)
+    int max_k;                           // candidate capacity (<= 256)
     const uint32_t* counter;             // device word: RNG counter (advanced by sl_advance_counter)
     uint32_t stream;
     const int* row_ids;                  // RNG row id per batch row (null = row index)
@@ -233,7 +233,9 @@ SL_API int sl_sample(const SampleParams* p, int B, cudaStream_t s) {
 }
 
 // ---------------------------------------------------------------------------------------------
-// Linear-chain speculative rejection sampling; one thread per row (D <= 8, C <= 64).
+// Linear-chain speculative rejection sampling; one thread per row (D <= 8, C <= 256).  Candidate lists are sorted by
+// probability, so everything behind the last non-zero entry is skipped: the sums are the same to the bit (adding zeros
+// changes nothing) and the work follows the number of live candidates (top-k, top-p), not the capacity.
 struct SpecRejectParams {
     const int64_t* draft_tokens;                                     // [B, D]
     const int64_t* draft_ids; const float* draft_probs;              // [B, D, C]
@@ -268,8 +270,12 @@ __global__ void spec_reject_kernel(SpecRejectParams p, int B) {
         const float* tp = p.target_probs + ((size_t)b * (D + 1) + i) * C;
         const int64_t* did = p.draft_ids + ((size_t)b * D + i) * C;
         const float* dp = p.draft_probs + ((size_t)b * D + i) * C;
+        int Ct = C, Cd = C;                        // live prefixes of the two lists
+        while (Ct > 1 && tp[Ct - 1] <= 0.f) --Ct;
+        while (Cd > 1 && dp[Cd - 1] <= 0.f) --Cd;
         float pt = 0.f, pd = 0.f;
-        for (int c = 0; c < C; ++c) { if (tid_[c] == x) pt += tp[c]; if (did[c] == x) pd += dp[c]; }
+        for (int c = 0; c < Ct; ++c) if (tid_[c] == x) pt += tp[c];
+        for (int c = 0; c < Cd; ++c) if (did[c] == x) pd += dp[c];
         const double ua = uniform_from_counter(*p.counter, (uint32_t)b, 2u * i + 1u);
         if (pd > 0.f && ua < (double)fminf(1.f, pt / pd)) {
             p.out_tokens[(size_t)b * (D + 1) + i] = x;
@@ -277,15 +283,15 @@ __global__ void spec_reject_kernel(SpecRejectParams p, int B) {
         }
         float res[SL_MAX_CAND];
         float rs = 0.f;
-        for (int c = 0; c < C; ++c) {
+        for (int c = 0; c < Ct; ++c) {
             float d = 0.f;
-            for (int e = 0; e < C; ++e) if (did[e] == tid_[c]) d += dp[e];
+            for (int e = 0; e < Cd; ++e) if (did[e] == tid_[c]) d += dp[e];
             res[c] = fmaxf(tp[c] - d, 0.f);
             rs += res[c];
         }
-        if (rs <= 0.f) for (int c = 0; c < C; ++c) res[c] = tp[c];
+        if (rs <= 0.f) for (int c = 0; c < Ct; ++c) res[c] = tp[c];
         int64_t tok;
-        pick_from(tid_, res, C, uniform_from_counter(*p.counter, (uint32_t)b, 2u * i + 2u), &tok);
+        pick_from(tid_, res, Ct, uniform_from_counter(*p.counter, (uint32_t)b, 2u * i + 2u), &tok);
         p.out_tokens[(size_t)b * (D + 1) + i] = tok;
         break;
     }

@@ -119,6 +119,43 @@ class Engine:
         torch.cuda.current_stream(self.device).synchronize()        # the blob may be read (or the page reused) right away
         return host
 
+    def read_pages(self, pages: Seq[int]) -> List[torch.Tensor]:
+        """`read_page` for many pages with one gather per cache tensor, one device-to-host copy and one synchronisation
+        in total (the reference batches its page copies the same way, `src/paged_kv.ts:308-370`)."""
+        if not pages:
+            return []
+        tensors = self._page_tensors()
+        idx = torch.as_tensor(list(pages), dtype=torch.int64, device=self.device)
+        parts = [t.view(-1, PAGE_SIZE, *t.shape[1:]).index_select(0, idx).reshape(len(pages), -1).view(torch.uint8) for t in tensors]
+        packed = torch.cat(parts, dim=1)                                      # [pages, bytes per page]
+        if not packed.is_cuda:
+            return list(packed.unbind(0))
+        host = torch.empty(packed.shape, dtype=torch.uint8, pin_memory=True)
+        host.copy_(packed, non_blocking=True)
+        torch.cuda.current_stream(self.device).synchronize()
+        return list(host.unbind(0))
+
+    def write_pages(self, pages: Seq[int], blobs: Seq[torch.Tensor]) -> None:
+        """Inverse of `read_pages`: one host-to-device copy, one scatter per cache tensor."""
+        if not pages:
+            return
+        tensors = self._page_tensors()
+        per_page = sum(t[:PAGE_SIZE].numel() * t.element_size() for t in tensors)
+        for b in blobs:
+            if b.numel() != per_page:
+                raise ValueError(f"page blob of {b.numel()} bytes does not match this cache's page size of {per_page} bytes")
+        host = torch.stack([b.reshape(-1) for b in blobs])
+        if self.device.type == "cuda" and not host.is_pinned():
+            host = host.pin_memory()
+        dev = host.to(self.device, non_blocking=True)
+        idx = torch.as_tensor(list(pages), dtype=torch.int64, device=self.device)
+        off = 0
+        for t in tensors:
+            n = t[:PAGE_SIZE].numel() * t.element_size()
+            rows = dev[:, off:off + n].contiguous().view(t.dtype).reshape(len(pages), PAGE_SIZE, *t.shape[1:])
+            t.view(-1, PAGE_SIZE, *t.shape[1:]).index_copy_(0, idx, rows)
+            off += n
+
     def write_page(self, page: int, blob: torch.Tensor) -> None:
         """Inverse of `read_page` into page `page` (one host-to-device copy, then per-layer scatter on the device)."""
         sl = slice(page * PAGE_SIZE, (page + 1) * PAGE_SIZE)
@@ -164,39 +201,61 @@ class Engine:
         """Chunked prefill of each prompt's uncached tail (up to `limits[b]` tokens when given:
         the scheduler spreads a long prompt over several steps).  Returns (next token per
         sequence, last hidden per sequence or None); the token is meaningful only for
-        sequences whose whole prompt is now cached.  Sequences are processed one after the
-        other in chunks of at most `chunk_size` tokens."""
+        sequences whose whole prompt is now cached.
+
+        Every forward pass takes up to `chunk_size` tokens and packs them from as many sequences as fit, in order: a
+        long prompt fills chunks alone, several short tails share one (the reference's `planPrefill(batchSize, lens)`,
+        `src/execution-workspace.ts:648-783`, `src/glm51_model.ts:1158-1188`)."""
+        B = len(seqs)
+        upto = [len(p) if limits is None else min(len(p), limits[b]) for b, p in enumerate(prompts)]
+        last_hidden: List[Optional[torch.Tensor]] = [None] * B
+        while True:
+            spans, budget = [], chunk_size
+            for b in range(B):
+                start = seqs[b].length
+                if start >= upto[b] or budget <= 0:
+                    continue
+                n = min(budget, upto[b] - start)
+                spans.append((b, start, n))
+                budget -= n
+            if not spans:
+                break
+            ids: List[int] = []
+            positions: List[int] = []
+            bidx: List[int] = []
+            group = [seqs[b] for b, _, _ in spans]
+            for gi, (b, start, n) in enumerate(spans):
+                tok = list(prompts[b][start:start + n])
+                self.kv.append_tokens(seqs[b], tok)
+                ids += tok
+                positions += range(start, start + n)
+                bidx += [gi] * n
+            st = self._eager_state(ids, positions, bidx, group, max_kv_len=max(start + n for _, start, n in spans))
+            self._prepare(st, group)
+            if len(spans) == 1 and self.phased_prefill and spans[0][2] >= self.phased_min_tokens:
+                _, start, n = spans[0]
+                hidden = self._forward_phased(ids, positions, group[0], start, n)
+            else:
+                hidden = self.model.forward_hidden(st, self.cache)
+            if self.mtp and getattr(self.cfg, "num_nextn_predict_layers", 0):
+                self._prefill_mtp(st, hidden, [(prompts[b], start, n) for b, start, n in spans])
+            off = 0
+            for b, start, n in spans:
+                self.kv.report_tokens(seqs[b])
+                last_hidden[b] = hidden[off + n - 1:off + n]
+                off += n
         tokens, hiddens = [], []
-        for b, (s, prompt) in enumerate(zip(seqs, prompts)):
-            start = s.length
-            last_hidden = None
-            upto = len(prompt) if limits is None else min(len(prompt), limits[b])
-            while start < upto:
-                n = min(chunk_size, upto - start)
-                ids = list(prompt[start:start + n])
-                self.kv.append_tokens(s, ids)
-                positions = list(range(start, start + n))
-                st = self._eager_state(ids, positions, [0] * n, [s], max_kv_len=start + n)
-                self._prepare(st, [s])
-                if self.phased_prefill and n >= self.phased_min_tokens:
-                    hidden = self._forward_phased(ids, positions, s, start, n)
-                else:
-                    hidden = self.model.forward_hidden(st, self.cache)
-                if self.mtp and getattr(self.cfg, "num_nextn_predict_layers", 0):
-                    self._prefill_mtp(st, hidden, prompt, start, n)
-                self.kv.report_tokens(s)
-                last_hidden = hidden[-1:]
-                start += n
-            if upto < len(prompt) or last_hidden is None:
+        for b in range(B):
+            if upto[b] < len(prompts[b]) or last_hidden[b] is None:
                 tokens.append(-1)
-                hiddens.append(last_hidden)
+                hiddens.append(last_hidden[b])
                 continue
             row = None if rows is None else rows[b]
             if row is not None and self.sampler is not None and not self.sampler.all_greedy([row]):
-                tokens.append(int(self._select(last_hidden, [row])[0]))
+                tokens.append(int(self._select(last_hidden[b], [row])[0]))
             else:
-                tokens.append(int(self._greedy(last_hidden)[0]))
-            hiddens.append(last_hidden)
+                tokens.append(int(self._greedy(last_hidden[b])[0]))
+            hiddens.append(last_hidden[b])
         self.check_device_errors()           # (the token reads above already synchronised the stream)
         return tokens, (hiddens if want_hidden else None)
 
@@ -211,11 +270,15 @@ class Engine:
             streams = self._phase_streams
         return torch.cat(self.model.forward_hidden_phased(sts, self.cache, streams), 0)
 
-    def _prefill_mtp(self, st: StepState, hidden, prompt, start: int, n: int) -> None:
-        """Fill the MTP layer's KV over the chunk: position i pairs (h_i, token_{i+1})."""
-        nxt = list(prompt[start + 1:start + n + 1])
-        if len(nxt) < n:
-            nxt.append(0)            # the pair at the last prompt position is redone at decode time
+    def _prefill_mtp(self, st: StepState, hidden, spans) -> None:
+        """Fill the MTP layer's KV over the chunk: position i pairs (h_i, token_{i+1}).  `spans` = (prompt, start, n) of
+        every sequence packed into the chunk, in order."""
+        nxt: List[int] = []
+        for prompt, start, n in spans:
+            part = list(prompt[start + 1:start + n + 1])
+            if len(part) < n:
+                part.append(0)       # the pair at the last prompt position is redone at decode time
+            nxt += part
         st2 = StepState(input_ids=torch.as_tensor(nxt, dtype=torch.int64, device=self.device), positions=st.positions,
                         batch_idx=st.batch_idx, page_table=st.page_table, cp_world=st.cp_world, cp_rank=st.cp_rank,
                         max_kv_len=st.max_kv_len)

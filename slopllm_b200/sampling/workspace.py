@@ -17,7 +17,7 @@ from ..config import SamplingParams
 from ..ops import reference as R
 
 MAX_ROWS = 256
-MAX_CAND = 64
+MAX_CAND = 256        # candidate-set capacity per row (reference: `src/sampling.ts:25-64`)
 
 
 class SamplingWorkspace:

@@ -118,10 +118,14 @@ class HostTier:
     """
 
     def __init__(self, max_pages: int, tokens_per_page: int, read_page: Callable[[int], object],
-                 write_page: Callable[[int, object], None]):
+                 write_page: Callable[[int, object], None], read_pages: Optional[Callable] = None,
+                 write_pages: Optional[Callable] = None):
         self.max_pages = max_pages
         self.tpp = tokens_per_page
         self.read_page, self.write_page = read_page, write_page
+        # batched forms (all pages of a sequence in one copy and one synchronisation); without them: page by page
+        self.read_pages = read_pages or (lambda pages: [read_page(p) for p in pages])
+        self.write_pages = write_pages or (lambda pages, blobs: [write_page(p, b) for p, b in zip(pages, blobs)])
         self.entries: List[dict] = []            # {"tokens": [...], "pages": [blob, ...]}
 
     @property
@@ -134,7 +138,7 @@ class HostTier:
             return                            # (a sequence larger than the whole tier must not cost the tier its entries)
         while self.entries and self.used_pages + n > self.max_pages:
             self.entries.remove(max(self.entries, key=lambda e: len(e["pages"])))     # largest victim first
-        self.entries.append({"tokens": list(seq.token_ids[: n * self.tpp]), "pages": [self.read_page(p) for p in seq.pages[:n]]})
+        self.entries.append({"tokens": list(seq.token_ids[: n * self.tpp]), "pages": list(self.read_pages(list(seq.pages[:n])))})
 
     def match(self, prompt: Seq[int]):
         best, best_pages = None, 0
@@ -402,39 +406,47 @@ class GenerationScheduler:
         if pages <= have:
             return
         new_pages = kv._alloc(pages - have)
-        for i, p in enumerate(new_pages):
-            self.host_tier.write_page(p, entry["pages"][have + i])
+        self.host_tier.write_pages(new_pages, entry["pages"][have:pages])
         seq.pages.extend(new_pages)
         seq.token_ids = list(prompt[: pages * kv.tokens_per_page])
         seq.reported = len(seq.token_ids)
         seq.shared_prefix_tokens = seq.reported
 
     def _prefill(self) -> None:
+        """One prefill call per step: the rows whose prompts are not cached yet share the step's token budget, in
+        admission order, and the engine packs their chunks into one forward pass where they fit (a long prompt fills the
+        budget alone and continues next step)."""
         budget = self.chunk_size
+        todo = []
         for r in self.rows:
             if r.prompt_done or budget <= 0:
                 continue
-            req = r.req
-            prompt = req.input_ids
-            remaining = len(prompt) - r.seq.length
-            take = min(remaining, budget)
-            t0 = time.time()
-            upto = r.seq.length + take
-            toks, hid = self.engine.prefill([r.seq], [prompt], chunk_size=self.chunk_size,
-                                            want_hidden=self.engine.mtp > 0, rows=[r.row], limits=[upto])
-            dt = time.time() - t0
+            take = min(len(r.req.input_ids) - r.seq.length, budget)
+            if take <= 0:
+                continue
+            todo.append((r, take, r.seq.length + take))
             budget -= take
+        if not todo:
+            return
+        t0 = time.time()
+        toks, hid = self.engine.prefill([r.seq for r, _, _ in todo], [r.req.input_ids for r, _, _ in todo],
+                                        chunk_size=self.chunk_size, want_hidden=self.engine.mtp > 0,
+                                        rows=[r.row for r, _, _ in todo], limits=[upto for _, _, upto in todo])
+        dt = time.time() - t0
+        self.metrics.record_phase("prefill", len(todo), dt)
+        total = sum(take for _, take, _ in todo)
+        for i, (r, take, upto) in enumerate(todo):
+            req = r.req
             req.prefill_tokens += take
-            req.prefill_seconds += dt
-            self.metrics.record_phase("prefill", 1, dt)
-            if upto == len(prompt):
+            req.prefill_seconds += dt * take / max(1, total)
+            if upto == len(req.input_ids):
                 r.prompt_done = True
-                r.last_token = toks[0]
-                r.last_hidden = hid[0] if hid else None
+                r.last_token = toks[i]
+                r.last_hidden = hid[i] if hid else None
                 self.metrics.prefill_time_seconds_count += 1
                 self.metrics.prefill_time_seconds_sum += req.prefill_seconds
                 req.first_token_at = time.time()
-                self._publish(r, [toks[0]])
+                self._publish(r, [toks[i]])
 
     def _decode(self) -> None:
         active = [r for r in self.rows if r.prompt_done and not r.req.finish_reason and not r.req.cancel_seen]

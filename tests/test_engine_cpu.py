@@ -99,8 +99,15 @@ def test_host_tier_restores_pages_of_the_real_engine():
     import pytest
     with pytest.raises(ValueError):
         eng.write_page(5, blob[:-16])
+    # batched form: several pages in one gather / one copy, same bytes as page by page
+    blobs = eng.read_pages([1, 5, 2])
+    assert torch.equal(blobs[0], blob) and torch.equal(blobs[1], eng.read_page(5)) and torch.equal(blobs[2], eng.read_page(2))
+    eng.write_pages([6, 7], [blobs[2], blobs[0]])
+    assert torch.equal(eng.read_page(6), blobs[2]) and torch.equal(eng.read_page(7), blob)
+    with pytest.raises(ValueError):
+        eng.write_pages([6], [blob[:-16]])
     # scheduler level
-    tier = HostTier(8, eng.kv.tokens_per_page, eng.read_page, eng.write_page)
+    tier = HostTier(8, eng.kv.tokens_per_page, eng.read_page, eng.write_page, read_pages=eng.read_pages, write_pages=eng.write_pages)
     sched = GenerationScheduler(eng, max_batch=1, chunk_size=256, host_tier=tier)
     prompt = torch.randint(2, cfg.vocab_size, (150,), generator=torch.Generator().manual_seed(11)).tolist()
 

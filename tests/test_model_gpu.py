@@ -38,8 +38,12 @@ def _run(cfg, device, dtype, prompt, new):
     return torch.cat(outs), toks
 
 
-@pytest.mark.parametrize("which", ["tiny", "mini"])
-def test_gpu_model_matches_cpu_reference(which):
+@pytest.mark.parametrize("which", ["tiny", "mini", "mini-a4"])
+def test_gpu_model_matches_cpu_reference(which, monkeypatch):
+    """`mini` keeps the prefill MoE on 16-bit activations (the reference's numerics); `mini-a4` is the default path, whose
+    prompt rows go through NVFP4 before the expert GEMMs: a looser bound, and the greedy paths may part earlier."""
+    from slopllm_b200.ops import gemm
+    monkeypatch.setattr(gemm, "MOE_A4", which == "mini-a4")
     cfg = GlmMoeDsaConfig.tiny() if which == "tiny" else _mini()
     g = torch.Generator().manual_seed(0)
     prompt = torch.randint(0, cfg.vocab_size, (100,), generator=g).tolist()
@@ -52,8 +56,8 @@ def test_gpu_model_matches_cpu_reference(which):
             break
         same += 1
     rel = ((got[:same + 1] - ref[:same + 1]).abs().max() / ref.abs().max()).item()
-    assert rel < 0.1, rel
-    assert same >= 3, (rt, gt)
+    assert rel < (0.3 if which == "mini-a4" else 0.1), rel
+    assert same >= (1 if which == "mini-a4" else 3), (rt, gt)
 
 
 def test_engine_graph_equals_eager_and_mtp_consistent():

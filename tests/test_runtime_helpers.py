@@ -102,6 +102,8 @@ def test_every_called_kernel_entry_point_is_declared_and_exported():
     import slopllm_b200
     import slopllm_b200.checkpoint.csf_gpu  # noqa: F401  (registers its signature on import or first use)
     import slopllm_b200.ops.cuda_ops  # noqa: F401
+    import slopllm_b200.ops.fp4  # noqa: F401
+    import slopllm_b200.parallel.ep  # noqa: F401
     import slopllm_b200.parallel.nvlink  # noqa: F401
     from slopllm_b200.ops import native as N
     root = os.path.dirname(slopllm_b200.__file__)

@@ -332,3 +332,25 @@ def test_admission_reserves_a_bounded_lookahead_and_grows_later():
     assert not eng.kv.staged and len(big.generated) > 64 * 10
     big.cancel()
     _drain(s)
+
+
+def test_one_prefill_call_packs_several_rows_under_the_budget():
+    """Three prompts of 30 / 50 / 40 tokens with a chunk budget of 100: the first step prefills 30 + 50 + 20 in one engine
+    call, the second the remaining 20 of the third row (the reference's multi-row prefill chunks)."""
+    calls = []
+
+    class Packing(FakeEngine):
+        def prefill(self, seqs, prompts, chunk_size=8192, want_hidden=False, rows=None, limits=None):
+            calls.append([(s.length, lim) for s, lim in zip(seqs, limits)])
+            return super().prefill(seqs, prompts, chunk_size, want_hidden, rows, limits)
+
+    eng = Packing(pages=64)
+    s = GenerationScheduler(eng, max_batch=4, chunk_size=100)
+    reqs = [_req(0, range(30), 2), _req(1, range(100, 150), 2), _req(2, range(200, 240), 2)]
+    for r in reqs:
+        s.submit(r)
+    _drain(s)
+    assert calls[0] == [(0, 30), (0, 50), (0, 20)]
+    assert calls[1] == [(20, 40)]
+    assert [r.generated for r in reqs] == [[30, 31], [150, 151], [240, 241]]
+    assert reqs[2].prefill_tokens == 40
