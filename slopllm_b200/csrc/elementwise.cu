@@ -345,10 +345,11 @@ SL_API int sl_q_post(const QPostParams* p, int T, cudaStream_t s) {
 // grid (Hh, N/32, ceil(T/TT)); block 256 = 8 warps.  A warp reads 8 matrix rows x 32 columns
 // per load instruction (8 columns per lane, 16 bytes), four loads in flight; the partial sums
 // of a lane's row group meet by shuffle, those of the 8 warps in shared memory.
-template <int TT>
-__device__ __forceinline__ void bmv_body(bf16* __restrict__ y, const void* __restrict__ x, const bf16* __restrict__ M, int T,
-                                         int Hh, int K, int N, int xs_t, int xs_h, int n_slabs, long long slab_stride, int h,
-                                         int n0, int t0) {
+// `stage(xs)` fills xs[TT][K] (fp32) with the rows t0 .. t0+TT-1 of head h (zero beyond T); when `xp` is given the
+// result is also written as f16 in the fragment order of the NVFP4 streaming kernels (rows up to `tpad`).
+template <int TT, typename Stage>
+__device__ __forceinline__ void bmv_core(bf16* __restrict__ y, uint4* __restrict__ xp, const bf16* __restrict__ M, int T,
+                                         int Hh, int K, int N, int h, int n0, int t0, Stage stage) {
     extern __shared__ float xs[];            // [TT][K], then red[8][TT][32]
     float* red = xs + TT * K;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -360,10 +361,7 @@ __device__ __forceinline__ void bmv_body(bf16* __restrict__ y, const void* __res
     int k = warp * 8 + kr;
 #pragma unroll
     for (int q = 0; q < 4; ++q) u[q] = (n < N && k + q * 64 < K) ? ldg_nc_16(Mp + (size_t)(k + q * 64) * N) : make_uint4(0, 0, 0, 0);
-    for (int i = tid; i < TT * K; i += blockDim.x) {
-        const int tt = i / K, kk = i % K;
-        xs[i] = (t0 + tt < T) ? load_act(x, n_slabs, slab_stride, (size_t)(t0 + tt) * xs_t + (size_t)h * xs_h + kk) : 0.f;
-    }
+    stage(xs);
     __syncthreads();
     float acc[TT][8];
 #pragma unroll
@@ -409,8 +407,124 @@ __device__ __forceinline__ void bmv_body(bf16* __restrict__ y, const void* __res
 #pragma unroll
             for (int w = 0; w < 8; ++w) v += red[(w * TT + tt) * 32 + c];
             y[((size_t)(t0 + tt) * Hh + h) * N + n0 + c] = __float2bfloat16(v);
+            red[tt * 32 + c] = v;            // warp 0's slot (only this thread reads or writes column c of row tt)
         }
     }
+    if (xp == nullptr) return;
+    __syncthreads();
+    // the same values (rounded to bf16 first, as a separate staging pass would see them) as f16 units of 8
+    const int Kt = Hh * N;
+    for (int i = tid; i < TT * 4; i += blockDim.x) {
+        const int tt = i / 4, c8 = (i % 4) * 8, tok = t0 + tt;
+        if (n0 + c8 >= N) continue;
+        uint32_t w[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            float a = 0.f, b = 0.f;
+            if (tok < T) {
+                a = __bfloat162float(__float2bfloat16(red[tt * 32 + c8 + 2 * q]));
+                b = __bfloat162float(__float2bfloat16(red[tt * 32 + c8 + 2 * q + 1]));
+            }
+            const __half2 hh = __floats2half2_rn(a, b);
+            w[q] = *reinterpret_cast<const uint32_t*>(&hh);
+        }
+        const int u = (h * N + n0 + c8) / 8, group = u / 16, within = u % 16, cc = within / 4, j = within % 4;
+        xp[((size_t)tok * (Kt / 128) + group) * 16 + j * 4 + cc] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+}
+
+template <int TT>
+__device__ __forceinline__ void bmv_body(bf16* __restrict__ y, const void* __restrict__ x, const bf16* __restrict__ M, int T,
+                                         int Hh, int K, int N, int xs_t, int xs_h, int n_slabs, long long slab_stride, int h,
+                                         int n0, int t0) {
+    bmv_core<TT>(y, nullptr, M, T, Hh, K, N, h, n0, t0, [&](float* xs) {
+        for (int i = threadIdx.x; i < TT * K; i += blockDim.x) {
+            const int tt = i / K, kk = i % K;
+            xs[i] = (t0 + tt < T) ? load_act(x, n_slabs, slab_stride, (size_t)(t0 + tt) * xs_t + (size_t)h * xs_h + kk) : 0.f;
+        }
+    });
+}
+
+// Attention output at decode: the merge of the key-split partial results (softmax weights from the partial
+// log-sum-exps) is the staging step of the value expansion, so (o_part, lse_part) -> y = merge(o_part) x w_v[h] is one
+// launch, and the rows leave in the operand order of the output projection as well.
+// o_part [T, Hh, np, K] fp32, lse_part [T, Hh, np]; np <= 64; K % 4 == 0.
+struct CombineExpandParams {
+    const float* o_part; const float* lse_part;
+    const bf16* w_v;          // [Hh, K, N]
+    bf16* y;                  // [T, Hh * N]
+    uint4* xp;                // fragment-ordered f16 copy [tpad, Hh * N], or null
+    int T, tpad, Hh, K, N, np;
+};
+
+template <int TT>
+__global__ void __launch_bounds__(256) combine_vexpand_kernel(CombineExpandParams p) {
+    pdl_grid_sync();
+    __shared__ float wsh[TT][64];
+    __shared__ float s_inv[TT];
+    const int h = blockIdx.x, n0 = blockIdx.y * 32, t0 = blockIdx.z * TT;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (warp < TT) {
+        const int t = t0 + warp;
+        float l0 = -INFINITY, l1 = -INFINITY;
+        if (t < p.T) {
+            const float* lp = p.lse_part + ((size_t)t * p.Hh + h) * p.np;
+            if (lane < p.np) l0 = lp[lane];
+            if (lane + 32 < p.np) l1 = lp[lane + 32];
+        }
+        const float mx = warp_max(fmaxf(l0, l1));
+        const float w0 = l0 == -INFINITY ? 0.f : __expf(l0 - mx), w1 = l1 == -INFINITY ? 0.f : __expf(l1 - mx);
+        const float den = warp_sum(w0) + warp_sum(w1);      // the order of the stand-alone merge kernel's sum
+        wsh[warp][lane] = w0;
+        wsh[warp][lane + 32] = w1;
+        if (lane == 0) s_inv[warp] = den > 0.f ? 1.f / den : 0.f;
+    }
+    __syncthreads();
+    bmv_core<TT>(p.y, p.xp, p.w_v, p.T, p.Hh, p.K, p.N, h, n0, t0, [&](float* xs) {
+        const int k4 = p.K / 4;
+        for (int i = tid; i < TT * k4; i += 256) {
+            const int tt = i / k4, d = (i % k4) * 4, t = t0 + tt;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (t < p.T) {
+                const float* op = p.o_part + ((size_t)t * p.Hh + h) * p.np * p.K + d;
+                for (int i0 = 0; i0 < p.np; i0 += 8) {
+                    float4 v[8];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) v[u] = *reinterpret_cast<const float4*>(op + (size_t)min(i0 + u, p.np - 1) * p.K);
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        const float w = i0 + u < p.np ? wsh[tt][i0 + u] : 0.f;
+                        acc.x += w * v[u].x; acc.y += w * v[u].y; acc.z += w * v[u].z; acc.w += w * v[u].w;
+                    }
+                }
+                // the merged row is rounded to bf16, as the stand-alone merge kernel stores it
+                const float inv = s_inv[tt];
+                acc.x = __bfloat162float(__float2bfloat16(acc.x * inv)); acc.y = __bfloat162float(__float2bfloat16(acc.y * inv));
+                acc.z = __bfloat162float(__float2bfloat16(acc.z * inv)); acc.w = __bfloat162float(__float2bfloat16(acc.w * inv));
+            }
+            *reinterpret_cast<float4*>(xs + tt * p.K + d) = acc;
+        }
+    });
+}
+
+template <int TT>
+static int launch_combine_vexpand(const CombineExpandParams* p, cudaStream_t s) {
+    const int rows = p->xp != nullptr ? p->tpad : p->T;
+    dim3 grid(p->Hh, (p->N + 31) / 32, (rows + TT - 1) / TT);
+    const size_t smem = (size_t)(TT * p->K + 8 * TT * 32) * sizeof(float);
+    auto kern = combine_vexpand_kernel<TT>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    sl_launch(kern, grid, 256, smem, s, *p);
+    return SL_LAUNCH_CHECK();
+}
+
+SL_API int sl_combine_vexpand(const CombineExpandParams* p, cudaStream_t s) {
+    if (p->T == 0) return 0;
+    if (p->N % 8 != 0 || p->K % 4 != 0 || p->np < 1 || p->np > 64) return -1;
+    if (p->xp != nullptr && ((p->Hh * p->N) % 128 != 0 || p->tpad % 8 != 0 || p->tpad < p->T)) return -1;
+    if (p->T == 1) return launch_combine_vexpand<1>(p, s);
+    if (p->T == 2) return launch_combine_vexpand<2>(p, s);
+    return launch_combine_vexpand<4>(p, s);
 }
 
 template <int TT>

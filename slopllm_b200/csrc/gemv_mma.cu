@@ -22,23 +22,25 @@ namespace {
 // x[T, K] bf16 -> f16 in fragment order in global scratch: 16-byte unit(token, group, j, c) holds
 // x[token][group*128 + c*32 + j*8 .. +7] at unit index (token*G + group)*16 + j*4 + c, G = K/128.
 // Rows T..tpad-1 are zero.
+__device__ __forceinline__ void permute_x_unit(uint4* __restrict__ xp, const bf16* __restrict__ x, int i, int T, int K, int ldx) {
+    const int tok = i / (K / 8), u = i % (K / 8);
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (tok < T) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(x + (size_t)tok * ldx + u * 8);
+        const float2 f0 = bf162_to_f2(raw.x), f1 = bf162_to_f2(raw.y), f2 = bf162_to_f2(raw.z), f3 = bf162_to_f2(raw.w);
+        __half2 h0 = __floats2half2_rn(f0.x, f0.y), h1 = __floats2half2_rn(f1.x, f1.y);
+        __half2 h2 = __floats2half2_rn(f2.x, f2.y), h3 = __floats2half2_rn(f3.x, f3.y);
+        v.x = *reinterpret_cast<uint32_t*>(&h0); v.y = *reinterpret_cast<uint32_t*>(&h1);
+        v.z = *reinterpret_cast<uint32_t*>(&h2); v.w = *reinterpret_cast<uint32_t*>(&h3);
+    }
+    const int group = u / 16, within = u % 16, c = within / 4, j = within % 4;
+    xp[((size_t)tok * (K / 128) + group) * 16 + j * 4 + c] = v;
+}
+
 __global__ void permute_x_kernel(uint4* __restrict__ xp, const bf16* __restrict__ x, int T, int tpad, int K, int ldx) {
     pdl_grid_sync();
     const int units = tpad * (K / 8);
-    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < units; i += gridDim.x * blockDim.x) {
-        const int tok = i / (K / 8), u = i % (K / 8);
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (tok < T) {
-            const uint4 raw = *reinterpret_cast<const uint4*>(x + (size_t)tok * ldx + u * 8);
-            const float2 f0 = bf162_to_f2(raw.x), f1 = bf162_to_f2(raw.y), f2 = bf162_to_f2(raw.z), f3 = bf162_to_f2(raw.w);
-            __half2 h0 = __floats2half2_rn(f0.x, f0.y), h1 = __floats2half2_rn(f1.x, f1.y);
-            __half2 h2 = __floats2half2_rn(f2.x, f2.y), h3 = __floats2half2_rn(f3.x, f3.y);
-            v.x = *reinterpret_cast<uint32_t*>(&h0); v.y = *reinterpret_cast<uint32_t*>(&h1);
-            v.z = *reinterpret_cast<uint32_t*>(&h2); v.w = *reinterpret_cast<uint32_t*>(&h3);
-        }
-        const int group = u / 16, within = u % 16, c = within / 4, j = within % 4;
-        xp[((size_t)tok * (K / 128) + group) * 16 + j * 4 + c] = v;
-    }
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < units; i += gridDim.x * blockDim.x) permute_x_unit(xp, x, i, T, K, ldx);
 }
 
 // One warp: MT tiles of 16 rows x NT*8 tokens over the groups kpart, kpart+ksplit, ... of the row's K.
@@ -252,69 +254,107 @@ struct MoePlanView {
     int* num_items;        // [1]
 };
 
-// One block.  Routed routes r = t*top_k + j (expert ids[r]); shared routes r = T*top_k + t.
-// Called by every thread of one block (<= 512 threads, a multiple of 32); `sh` is 2 * (T * top_k + 8) ints of
-// shared memory and `ids` may point to global or shared memory.  Items are numbered in the order of their first
-// route, so the plan does not depend on thread timing.
-__device__ void moe_plan_body(MoePlanView pv, const int* ids, int T, int top_k, int expert_offset, int num_local,
-                              int has_shared, int max_items, int* sh) {
-    const int n = T * top_k;
-    int* ex = sh;                                  // expert of each routed route (-1 if not local)
-    int* slot_of = sh + n + 8;                     // item of each chunk leader
-    __shared__ int s_items;
-    __shared__ int wcnt[16];
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = blockDim.x >> 5;
-    for (int r = tid; r < n; r += blockDim.x) {
-        const int e = ids[r] - expert_offset;
-        ex[r] = (e >= 0 && e < num_local) ? e : -1;
+// ---- router GEMV + routing + plan (+ activation staging) in one launch ---------------------------------------
+// grid (E/4): a block multiplies 4 router rows by every token.  Warp w takes the 256-wide K steps w, w+8, ... of all
+// four rows (the rows of its first three steps are in registers before the kernel waits for its predecessor: the
+// weights do not depend on it), reads the tokens' values straight from global memory, folds the lanes' partial sums
+// with one transposing butterfly (31 shuffles for 32 sums) and meets the other warps in shared memory in a fixed
+// order, so every rank computes bit-identical logits.  The block that finishes last (ticket counter) routes every
+// token (one warp per token) and builds the work-item plan; all blocks share the conversion of the activations to the
+// fragment order of the expert kernels.  Replaces the reference's router GEMV + `route_top8` + host-side plan
+// (`csrc/glm_gemv.cu:1642`, `csrc/glm_ops.cu:2343`).
+struct RouterFusedParams {
+    const bf16* x; int ldx;                 // [T, H]
+    const bf16* router_w;                   // [E, H]
+    const float* bias;                      // [E] or null
+    int T, H, E, top_k, n_group, topk_group, norm;
+    float scale;
+    float* logits;                          // [T][E] scratch
+    unsigned int* counter;                  // zero before the first use; the kernel leaves it zero
+    int* ids; float* wts;                   // [T, top_k]
+    MoePlanView pv;
+    int expert_offset, num_local, has_shared, max_items;
+    uint4* xp; int tpad;                    // fragment-ordered copy of x to write (null: the caller has one)
+};
+
+// Sums v[i] over the 32 lanes for 32 values at once: afterwards lane l holds the total of v[l] in v[0].
+__device__ __forceinline__ void warp_transpose_sum32(float (&v)[32]) {
+    const int lane = threadIdx.x & 31;
+#pragma unroll
+    for (int o = 16, n = 32; o > 0; o >>= 1, n >>= 1) {
+        const bool hi = lane & o;
+#pragma unroll
+        for (int i = 0; i < n / 2; ++i) {
+            const float a = v[i], b = v[i + n / 2];
+            v[i] = (hi ? b : a) + __shfl_xor_sync(0xffffffffu, hi ? a : b, o);
+        }
     }
+}
+
+// Plan for n = T * top_k <= 512 routes by one block of 256 threads in a few steps: the rank of a route among the
+// routes of its expert comes from a warp match plus per-warp counts, the leaders of each chunk of 8 claim item slots
+// in route order (so the plan does not depend on thread timing), members look their item up in a table.
+// `sh`: (13 * E + 16) ints of shared memory; `ids` may be shared or global.
+__device__ void moe_plan_fast(MoePlanView pv, const int* ids, int T, int top_k, int expert_offset, int num_local,
+                              int has_shared, int max_items, int* sh) {
+    const int n = T * top_k, E = num_local;
+    int* cnt = sh;                                 // [8][E] routes of expert e in warp w of the current pass
+    int* run = cnt + 8 * E;                        // [E] routes of expert e in earlier passes
+    int* slot_tab = run + E;                       // [E][4] item of chunk c of expert e
+    __shared__ int s_items;
+    __shared__ int wcnt[8];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    for (int i = tid; i < 9 * E; i += 256) sh[i] = 0;
     if (tid == 0) s_items = 0;
-    for (int i = tid; i < max_items * kItemRoutes; i += blockDim.x) pv.item_routes[i] = -1;
     __syncthreads();
-    // leaders (first route of each chunk of 8 routes of an expert) claim item slots in route order
-    for (int base = 0; base < n; base += blockDim.x) {
+    for (int base = 0; base < n; base += 256) {
         const int r = base + tid;
+        int e = -1;
+        if (r < n) {
+            const int le = ids[r] - expert_offset;
+            e = (le >= 0 && le < num_local) ? le : -1;
+        }
+        const unsigned same = __match_any_sync(0xffffffffu, e);
+        const int rank_in_warp = __popc(same & ((1u << lane) - 1));
+        if (e >= 0 && rank_in_warp == 0) cnt[warp * E + e] = __popc(same);
+        __syncthreads();
         int before = -1;
-        if (r < n && ex[r] >= 0) {
-            before = 0;
-            const int e = ex[r];
-            for (int q = 0; q < r; ++q) before += (ex[q] == e);
+        if (e >= 0) {
+            before = run[e] + rank_in_warp;
+            for (int w = 0; w < warp; ++w) before += cnt[w * E + e];
         }
         const bool leader = before >= 0 && (before % kItemRoutes) == 0;
         const unsigned m = __ballot_sync(0xffffffffu, leader);
         if (lane == 0) wcnt[warp] = __popc(m);
         __syncthreads();
         int slot = s_items, total = 0;
-        for (int w = 0; w < nw; ++w) {
+#pragma unroll
+        for (int w = 0; w < 8; ++w) {
             if (w < warp) slot += wcnt[w];
             total += wcnt[w];
         }
         slot += __popc(m & ((1u << lane) - 1));
         if (leader) {
-            if (slot < max_items) { pv.item_expert[slot] = ex[r]; pv.item_routes[slot * kItemRoutes] = r; }
-            slot_of[r] = slot;
+            if (slot < max_items) { pv.item_expert[slot] = e; pv.item_routes[slot * kItemRoutes] = r; }
+            if (before / kItemRoutes < 4) slot_tab[e * 4 + before / kItemRoutes] = slot;
         }
         __syncthreads();
+        if (before >= 0 && !leader && before / kItemRoutes < 4) {
+            const int it = slot_tab[e * 4 + before / kItemRoutes];
+            if (it < max_items) pv.item_routes[it * kItemRoutes + before % kItemRoutes] = r;
+        }
         if (tid == 0) s_items += total;
         __syncthreads();
-    }
-    // members find their leader: same expert, start of their chunk
-    for (int r = tid; r < n; r += blockDim.x) {
-        const int e = ex[r];
-        if (e < 0) continue;
-        int before = 0;
-        for (int q = 0; q < r; ++q) before += (ex[q] == e);
-        const int within = before % kItemRoutes;
-        if (within == 0) continue;                 // is a leader
-        const int want = before - within;
-        int lead = -1, seen = 0;
-        for (int q = 0; q < r; ++q) {
-            if (ex[q] == e) { if (seen == want) { lead = q; break; } ++seen; }
+        if (base + 256 < n) {
+            for (int i = tid; i < E; i += 256) {
+                int c = 0;
+#pragma unroll
+                for (int w = 0; w < 8; ++w) { c += cnt[w * E + i]; cnt[w * E + i] = 0; }
+                run[i] += c;
+            }
+            __syncthreads();
         }
-        const int slot = slot_of[lead];
-        if (slot < max_items) pv.item_routes[slot * kItemRoutes + within] = r;
     }
-    __syncthreads();
     if (tid == 0) {
         int items = s_items;
         if (has_shared) {
@@ -330,98 +370,99 @@ __device__ void moe_plan_body(MoePlanView pv, const int* ids, int T, int top_k, 
     }
 }
 
-__global__ void __launch_bounds__(512) moe_plan_kernel(MoePlanView pv, const int* __restrict__ ids, int T, int top_k,
+__global__ void __launch_bounds__(256) moe_plan_kernel(MoePlanView pv, const int* __restrict__ ids, int T, int top_k,
                                                        int expert_offset, int num_local, int has_shared, int max_items) {
     pdl_grid_sync();
     extern __shared__ int sh[];
-    moe_plan_body(pv, ids, T, top_k, expert_offset, num_local, has_shared, max_items, sh);
+    for (int i = threadIdx.x; i < max_items * kItemRoutes; i += 256) pv.item_routes[i] = -1;
+    __syncthreads();
+    moe_plan_fast(pv, ids, T, top_k, expert_offset, num_local, has_shared, max_items, sh);
 }
-
-// ---- router GEMV + routing + plan in one launch --------------------------------------------------------------
-// grid (E/32, H/256): block (nb, kc) multiplies 32 router rows by the 256-wide K chunk kc for every token and
-// stores the partial logits in slab kc.  The block that finishes last (ticket counter) adds the slabs up, routes
-// every token (one warp per token) and builds the work-item plan, so the MoE layer needs no further launch before
-// its expert GEMMs.  Replaces the reference's router GEMV + `route_top8` + host-side plan
-// (`csrc/glm_gemv.cu:1642`, `csrc/glm_ops.cu:2343`).
-struct RouterFusedParams {
-    const bf16* x; int ldx;                 // [T, H]
-    const bf16* router_w;                   // [E, H]
-    const float* bias;                      // [E] or null
-    int T, H, E, top_k, n_group, topk_group, norm;
-    float scale;
-    float* slabs;                           // [H/256][T][E]
-    unsigned int* counter;                  // zero before the first use; the kernel leaves it zero
-    int* ids; float* wts;                   // [T, top_k]
-    MoePlanView pv;
-    int expert_offset, num_local, has_shared, max_items;
-};
 
 template <int PER>
 __global__ void __launch_bounds__(256) router_route_plan_kernel(RouterFusedParams p) {
-    pdl_grid_sync();
-    extern __shared__ float dyn[];           // phase 1: x chunk [T][256] fp32; phase 2: plan scratch + ids
+    extern __shared__ int dyn[];             // phase 1: [8 warps][32] partial sums; phase 2: plan tables + ids
     __shared__ int s_last;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int n0 = blockIdx.x * 32, kc = blockIdx.y, k0 = kc * 256;
-    for (int i = tid; i < p.T * 256; i += blockDim.x) {
-        const int t = i >> 8, k = i & 255;
-        dyn[i] = __bfloat162float(p.x[(size_t)t * p.ldx + k0 + k]);
-    }
-    // this warp's four weight rows, 8 K values per lane
-    uint4 wv[4];
+    const int e0 = blockIdx.x * 4;
+    const int steps = p.H / 256;
+    constexpr int NPRE = 3;
+    uint4 wv[NPRE][4];
 #pragma unroll
-    for (int r = 0; r < 4; ++r) {
-        const int n = n0 + warp * 4 + r;
-        wv[r] = n < p.E ? ldg_nc_16(p.router_w + (size_t)n * p.H + k0 + lane * 8) : make_uint4(0, 0, 0, 0);
-    }
-    __syncthreads();
-    float wf[4][8];
+    for (int r = 0; r < NPRE; ++r) {
+        const int st = r * 8 + warp;
 #pragma unroll
-    for (int r = 0; r < 4; ++r) {
-        const float2 a = bf162_to_f2(wv[r].x), b = bf162_to_f2(wv[r].y), c = bf162_to_f2(wv[r].z), d = bf162_to_f2(wv[r].w);
-        wf[r][0] = a.x; wf[r][1] = a.y; wf[r][2] = b.x; wf[r][3] = b.y; wf[r][4] = c.x; wf[r][5] = c.y; wf[r][6] = d.x; wf[r][7] = d.y;
+        for (int j = 0; j < 4; ++j)
+            wv[r][j] = (st < steps && e0 + j < p.E) ? ldg_nc_16(p.router_w + (size_t)(e0 + j) * p.H + st * 256 + lane * 8)
+                                                    : make_uint4(0, 0, 0, 0);
     }
-    for (int t = 0; t < p.T; ++t) {
-        const float4 x0 = *reinterpret_cast<const float4*>(dyn + t * 256 + lane * 8);
-        const float4 x1 = *reinterpret_cast<const float4*>(dyn + t * 256 + lane * 8 + 4);
-        float acc[4];
+    pdl_grid_sync();
+    // the plan's route table starts empty; the last block fills it after the ticket
+    for (int i = blockIdx.x * 256 + tid; i < p.max_items * kItemRoutes; i += gridDim.x * 256) p.pv.item_routes[i] = -1;
+    float* red = reinterpret_cast<float*>(dyn);
+    for (int t0 = 0; t0 < p.T; t0 += 8) {
+        float acc[32];                       // [4 rows][8 tokens]
 #pragma unroll
-        for (int r = 0; r < 4; ++r) {
-            acc[r] = wf[r][0] * x0.x + wf[r][1] * x0.y + wf[r][2] * x0.z + wf[r][3] * x0.w + wf[r][4] * x1.x + wf[r][5] * x1.y +
-                     wf[r][6] * x1.z + wf[r][7] * x1.w;
-            acc[r] = warp_sum(acc[r]);
+        for (int i = 0; i < 32; ++i) acc[i] = 0.f;
+        auto round = [&](const uint4 (&w4)[4], int st) {
+            uint4 xv[8];
+#pragma unroll
+            for (int t = 0; t < 8; ++t)
+                xv[t] = t0 + t < p.T ? *reinterpret_cast<const uint4*>(p.x + (size_t)(t0 + t) * p.ldx + st * 256 + lane * 8)
+                                     : make_uint4(0, 0, 0, 0);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 a = bf162_to_f2(w4[j].x), b = bf162_to_f2(w4[j].y), c = bf162_to_f2(w4[j].z), d = bf162_to_f2(w4[j].w);
+#pragma unroll
+                for (int t = 0; t < 8; ++t) {
+                    const float2 xa = bf162_to_f2(xv[t].x), xb = bf162_to_f2(xv[t].y), xc = bf162_to_f2(xv[t].z), xd = bf162_to_f2(xv[t].w);
+                    acc[j * 8 + t] += a.x * xa.x + a.y * xa.y + b.x * xb.x + b.y * xb.y + c.x * xc.x + c.y * xc.y + d.x * xd.x + d.y * xd.y;
+                }
+            }
+        };
+#pragma unroll
+        for (int r = 0; r < NPRE; ++r)
+            if (r * 8 + warp < steps) round(wv[r], r * 8 + warp);
+        for (int r = NPRE; r * 8 + warp < steps; ++r) {
+            const int st = r * 8 + warp;
+            uint4 w4[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                w4[j] = e0 + j < p.E ? ldg_nc_16(p.router_w + (size_t)(e0 + j) * p.H + st * 256 + lane * 8) : make_uint4(0, 0, 0, 0);
+            round(w4, st);
         }
-        if (lane < 4) {
-            const int n = n0 + warp * 4 + lane;
-            const float v = lane == 0 ? acc[0] : lane == 1 ? acc[1] : lane == 2 ? acc[2] : acc[3];
-            if (n < p.E) p.slabs[((size_t)kc * p.T + t) * p.E + n] = v;
+        warp_transpose_sum32(acc);
+        __syncthreads();                     // the previous token group's sums have been read
+        red[warp * 32 + lane] = acc[0];
+        __syncthreads();
+        if (tid < 32) {
+            float v = 0.f;
+#pragma unroll
+            for (int w = 0; w < 8; ++w) v += red[w * 32 + tid];
+            const int j = tid >> 3, t = t0 + (tid & 7);
+            if (t < p.T && e0 + j < p.E) p.logits[(size_t)t * p.E + e0 + j] = v;
         }
+    }
+    if (p.xp != nullptr) {
+        const int units = p.tpad * (p.H / 8);
+        for (int i = blockIdx.x * 256 + tid; i < units; i += gridDim.x * 256) permute_x_unit(p.xp, p.x, i, p.T, p.H, p.ldx);
     }
     // ---- last block to finish takes over ----
     __threadfence();
     __syncthreads();
     if (tid == 0) {
-        const unsigned int total = gridDim.x * gridDim.y;
         const unsigned int ticket = atomicAdd(p.counter, 1u);
-        s_last = ticket == total - 1;
+        s_last = ticket == gridDim.x - 1;
         if (s_last) *p.counter = 0u;
     }
     __syncthreads();
     if (!s_last) return;
     __threadfence();
-    int* plan_sh = reinterpret_cast<int*>(dyn);
-    int* s_ids = plan_sh + 2 * (p.T * p.top_k + 8);
-    const int ks = p.H / 256;
+    int* s_ids = dyn + 13 * p.num_local + 16;
     for (int t = warp; t < p.T; t += 8) {
         float lg[PER];
 #pragma unroll
-        for (int i = 0; i < PER; ++i) lg[i] = 0.f;
-        for (int s = 0; s < ks; ++s) {
-            const float* src = p.slabs + ((size_t)s * p.T + t) * p.E + lane * PER;
-#pragma unroll
-            for (int i = 0; i < PER; ++i)
-                if (lane * PER + i < p.E) lg[i] += __ldcg(src + i);
-        }
+        for (int i = 0; i < PER; ++i) lg[i] = lane * PER + i < p.E ? __ldcg(p.logits + (size_t)t * p.E + lane * PER + i) : 0.f;
         int id; float w;
         route_warp<PER>(lg, p.bias, p.E, p.top_k, p.n_group, p.topk_group, p.norm, p.scale, id, w);
         if (lane < p.top_k) {
@@ -431,7 +472,7 @@ __global__ void __launch_bounds__(256) router_route_plan_kernel(RouterFusedParam
         }
     }
     __syncthreads();
-    moe_plan_body(p.pv, s_ids, p.T, p.top_k, p.expert_offset, p.num_local, p.has_shared, p.max_items, plan_sh);
+    moe_plan_fast(p.pv, s_ids, p.T, p.top_k, p.expert_offset, p.num_local, p.has_shared, p.max_items, dyn);
 }
 
 struct MoeGroupedParams {
@@ -594,7 +635,7 @@ struct MoeRouterArgs {
     const void* bias;        // f32 [E] or null
     int E, n_group, topk_group, norm;
     float scale;
-    void* slabs;             // f32 [H/256, T, E] scratch
+    void* slabs;             // f32 [T, E] scratch (the logits)
     void* counter;           // u32, zero before the first use (the kernel leaves it zero)
 };
 
@@ -615,6 +656,7 @@ SL_API int sl_moe_grouped_mma(const MoeGroupedArgs* a, const MoeRouterArgs* r, c
     const int n_routed = a->T * a->top_k;
     int* plan = (int*)a->plan;
     MoePlanView pv{plan, plan + a->max_items, plan + a->max_items * (1 + kItemRoutes)};
+    bool xp_done = false;
     if (r != nullptr) {
         if (a->H % 256 != 0 || r->E > 512 || a->top_k > 32 || r->n_group > 32 || r->n_group < 1 || r->E % r->n_group != 0) return -1;
         int PER = 1;
@@ -625,14 +667,16 @@ SL_API int sl_moe_grouped_mma(const MoeGroupedArgs* a, const MoeRouterArgs* r, c
             const int lpg = gsz / PER;
             if (lpg & (lpg - 1)) return -1;
         }
+        const int tpad8 = (a->T + 7) / 8 * 8;
         RouterFusedParams rp{(const bf16*)a->x, a->ldx, (const bf16*)r->router_w, (const float*)r->bias, a->T, a->H, r->E,
                              a->top_k, r->n_group, r->topk_group, r->norm, r->scale, (float*)r->slabs,
                              (unsigned int*)r->counter, (int*)a->ids, (float*)a->wts, pv, a->expert_offset, a->num_local,
-                             has_shared, a->max_items};
-        size_t smem = (size_t)a->T * 256 * sizeof(float);
-        const size_t smem2 = (size_t)(3 * n_routed + 16) * sizeof(int);
+                             has_shared, a->max_items, a->xp_ready ? nullptr : (uint4*)a->xp, tpad8};
+        size_t smem = (size_t)8 * 32 * sizeof(float);
+        const size_t smem2 = (size_t)(13 * a->num_local + 16 + n_routed) * sizeof(int);
         if (smem2 > smem) smem = smem2;
-        const dim3 grid((r->E + 31) / 32, a->H / 256);
+        if (smem > 48 * 1024 || a->num_local < 1) return -1;
+        const dim3 grid((r->E + 3) / 4);
         switch (PER) {
             case 1: launch_router<1>(rp, grid, smem, s); break;
             case 2: launch_router<2>(rp, grid, smem, s); break;
@@ -640,13 +684,16 @@ SL_API int sl_moe_grouped_mma(const MoeGroupedArgs* a, const MoeRouterArgs* r, c
             case 8: launch_router<8>(rp, grid, smem, s); break;
             default: launch_router<16>(rp, grid, smem, s); break;
         }
+        xp_done = true;
     } else {
-        sl_launch(moe_plan_kernel, 1, 512, (size_t)2 * (n_routed + 8) * sizeof(int), s, pv, (const int*)a->ids, a->T, a->top_k,
+        const size_t smem = (size_t)(13 * a->num_local + 16) * sizeof(int);
+        if (smem > 48 * 1024 || a->num_local < 1) return -1;
+        sl_launch(moe_plan_kernel, 1, 256, smem, s, pv, (const int*)a->ids, a->T, a->top_k,
                   a->expert_offset, a->num_local, has_shared, a->max_items);
     }
     const int tpad = (a->T + 7) / 8 * 8;
     const int units = tpad * (a->H / 8);
-    if (!a->xp_ready)
+    if (!a->xp_ready && !xp_done)
         sl_launch(permute_x_kernel, (units + 255) / 256, 256, 0, s, (uint4*)a->xp, (const bf16*)a->x, a->T, tpad, a->H, a->ldx);
     MoeGroupedParams p{pv.item_expert, pv.item_routes, pv.num_items, a->T, a->top_k, a->H, a->I,
                        (const uint8_t*)a->w13, (const uint8_t*)a->s13, (const float*)a->g13,

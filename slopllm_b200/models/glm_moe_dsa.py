@@ -144,8 +144,8 @@ class GlmMoeDsaModel:
                 st.slots, st.lengths = fst.slots, fst.lengths           # flat-buffer slots are valid for the sharing layers too
             elif st.slots is None:
                 raise RuntimeError(f"layer {layer} shares indexer slots but no full-indexer layer ran before it")
-            o, _ = ops.sparse_mla(q_abs, q_pe, flat_lc, st.slots, st.lengths)
-            return ops.linear(ops.v_expand(o, lw.w_v), lw.o_proj, out_f32=True, sink=comm.partial_sink(x.shape[0]))
+            return ops.linear(self._attn_values(q_abs, q_pe, flat_lc, st, lw), lw.o_proj, out_f32=True,
+                              sink=comm.partial_sink(x.shape[0]))
         if lw.has_indexer:
             pos, score = ops.indexer_topk(q8, w_eff, lc, st)
             if ctx.cp and ctx.world > 1:
@@ -160,9 +160,15 @@ class GlmMoeDsaModel:
             else:
                 o, lse = ops.sparse_mla(q_abs, q_pe, lc, st.slots, st.lengths)
                 o = comm.cp_merge_heads(ops, o, lse)
-        else:
-            o, _ = ops.sparse_mla(q_abs, q_pe, lc, st.slots, st.lengths)
-        return ops.linear(ops.v_expand(o, lw.w_v), lw.o_proj, out_f32=True, sink=comm.partial_sink(x.shape[0]))
+            return ops.linear(ops.v_expand(o, lw.w_v), lw.o_proj, out_f32=True, sink=comm.partial_sink(x.shape[0]))
+        return ops.linear(self._attn_values(q_abs, q_pe, lc, st, lw), lw.o_proj, out_f32=True, sink=comm.partial_sink(x.shape[0]))
+
+    def _attn_values(self, q_abs, q_pe, lc, st, lw):
+        ops = self.ops
+        if hasattr(ops, "attn_values"):
+            return ops.attn_values(q_abs, q_pe, lc, st.slots, st.lengths, lw.w_v)
+        o, _ = ops.sparse_mla(q_abs, q_pe, lc, st.slots, st.lengths)
+        return ops.v_expand(o, lw.w_v)
 
     # -- MLP ----------------------------------------------------------------------------------
     @traced("mlp")

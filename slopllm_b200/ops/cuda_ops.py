@@ -57,6 +57,7 @@ class CudaOps:
         # one-launch persistent decode MoE (csrc/moe_persist.cu): opt-in.  Its NVFP4 -> f16 expansion is bound by the
         # conversion rate of the CUDA cores just like the five-launch path, which it does not yet beat below 32 rows
         self._persist_moe = env_str("MOE_PERSIST") == "1"
+        self._fused_attn_out = env_str("FUSED_ATTN_OUT") != "0"     # merge of the key splits inside the value expansion
         self._persist_gsub = 0         # gate/up sub-tiles per tile of the persistent MoE kernel (0: the kernel's default)
         self._persist_trace = None     # u64 [SMs, 96, 4] tile timeline, filled when set (profiling)
 
@@ -392,6 +393,30 @@ class CudaOps:
         o_part, lse_part = self.sparse_mla_partials(q_abs, q_pe, layer_cache, slots, lengths)
         return self.combine([o_part], [lse_part])
 
+    def attn_values(self, q_abs, q_pe, layer_cache, slots, lengths, w_v):
+        """Sparse attention followed by the value expansion, [T, h * Dv].  At decode the merge of the key splits is the
+        staging step of the expansion (one launch instead of merge + product + operand staging for the output
+        projection, whose fragment-ordered copy rides along with the result)."""
+        T, h, Rr = q_abs.shape
+        splits = self._mla_splits(T, h)
+        Dv = w_v.shape[2]
+        if not self._fused_attn_out or T > DECODE_MAX_T or splits < 2 or splits > 64 or Rr % 4 != 0 or Dv % 8 != 0:
+            o, _ = self.sparse_mla(q_abs, q_pe, layer_cache, slots, lengths)
+            return self.v_expand(o, w_v)
+        o_part, lse_part = self.sparse_mla_partials(q_abs, q_pe, layer_cache, slots, lengths)
+        dev = q_abs.device
+        out = torch.empty(T, h * Dv, dtype=torch.bfloat16, device=dev)
+        tpad = (T + 7) // 8 * 8
+        perm = None
+        if T >= TENSOR_MIN_T and (h * Dv) % 128 == 0:
+            perm = torch.empty(tpad * h * Dv, dtype=torch.float16, device=dev)
+        p = N.CombineExpandParams(o_part=o_part.data_ptr(), lse_part=lse_part.data_ptr(), w_v=w_v.data_ptr(), y=out.data_ptr(),
+                                  xp=N.ptr(perm), T=T, tpad=tpad, Hh=h, K=Rr, N=Dv, np=splits)
+        N.call("sl_combine_vexpand", C.byref(p), N.stream())
+        if perm is not None:
+            out._sl_perm = perm
+        return out
+
     def v_expand(self, o, w_v):
         T, hl, Rr = o.shape
         Dv = w_v.shape[2]
@@ -472,7 +497,7 @@ class CudaOps:
             E = router.router_w.shape[0]
             ids = torch.empty(T, k, dtype=torch.int32, device=dev)
             wts = torch.empty(T, k, dtype=torch.float32, device=dev)
-            slabs = torch.empty(H // 256, T, E, dtype=torch.float32, device=dev)
+            slabs = torch.empty(T, E, dtype=torch.float32, device=dev)          # the router's logits
             counter = self._zero_counter(dev)
             rargs = N.MoeRouterArgs(router_w=router.router_w.data_ptr(), bias=N.ptr(router.router_bias), E=E,
                                     n_group=c.n_group, topk_group=c.topk_group, norm=int(c.norm_topk_prob),

@@ -117,6 +117,11 @@ class CombineParams(C.Structure):
                 ("parity_o_stride", i64), ("parity_lse_stride", i64)]
 
 
+class CombineExpandParams(C.Structure):
+    _fields_ = [("o_part", vp), ("lse_part", vp), ("w_v", vp), ("y", vp), ("xp", vp), ("T", i32), ("tpad", i32), ("Hh", i32),
+                ("K", i32), ("N", i32), ("np", i32)]
+
+
 class MoeGateUpParams(C.Structure):
     _fields_ = [("x", vp), ("ldx", i32), ("ids", vp), ("T", i32), ("top_k", i32), ("H", i32), ("I", i32),
                 ("expert_offset", i32), ("num_local", i32), ("w13", vp), ("s13", vp), ("g13", vp), ("sw13", vp),
@@ -205,6 +210,7 @@ _SIGS = {
     "sl_sparse_mla_split": [C.POINTER(SparseMlaParams), i32, vp],
     "sl_sparse_mla_split_mma": [C.POINTER(SparseMlaParams), i32, vp],
     "sl_mla_combine": [C.POINTER(CombineParams), i32, vp],
+    "sl_combine_vexpand": [C.POINTER(CombineExpandParams), vp],
     "sl_argmax": [vp, vp, i32, i32, i32, i32, i64, vp, vp, vp, vp],
     "sl_sample": [C.POINTER(SampleParams), i32, vp],
     "sl_spec_reject": [C.POINTER(SpecRejectParams), i32, vp],

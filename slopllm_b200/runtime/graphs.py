@@ -53,8 +53,18 @@ class CaptureManager:
         if self.pool is None:
             self.pool = torch.cuda.graph_pool_handle()
         before, kbefore = N.launch_count(), N.kernel_count()
-        with torch.cuda.graph(g, pool=self.pool):
-            e.outputs = fn()
+        # Collected garbage may own CUDA graphs or memory pools of engines that are gone; destroying those while a
+        # capture is open invalidates it.  Collect now, and keep the collector off until the capture has ended.
+        import gc
+        gc.collect()
+        gc_was_on = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(g, pool=self.pool):
+                e.outputs = fn()
+        finally:
+            if gc_was_on:
+                gc.enable()
         e.launches = N.launch_count() - before
         e.kernels = N.kernel_count() - kbefore
         e.graph = g

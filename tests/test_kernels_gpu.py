@@ -316,6 +316,45 @@ def test_sparse_mla_keys_on_m(h, T, q_scale):
     close(lse[live], lse2[live], tol=1e-3, what="lse, keys-on-M vs heads-on-M")
 
 
+@pytest.mark.parametrize("T,h", [(1, 8), (3, 8), (8, 8), (13, 4), (32, 8)])
+def test_attention_output_merge_fused_with_value_expansion(T, h):
+    """Decode attention output in one launch (merge of the key splits as the staging step of the value expansion, plus
+    the fragment-ordered copy for the output projection) equals merge kernel + product + staging kernel bit for bit,
+    and the fp32 definition within rounding."""
+    from slopllm_b200.ops import native as N
+    cfg = mini_cfg(num_attention_heads=h, index_topk=2048)
+    ops, ref = cuda_ops(cfg), RefOps(cfg)
+    g = torch.Generator(device=DEV).manual_seed(7 * T + h)
+    Rr, Dr, k, Dv = cfg.kv_lora_rank, cfg.qk_rope_head_dim, cfg.index_topk, cfg.v_head_dim
+    nslots = 4096
+    cache = type("C", (), {})()
+    cache.kv = quant.pack_kv_rows(torch.randn(nslots, Rr, device=DEV, generator=g), torch.randn(nslots, Dr, device=DEV, generator=g),
+                                  cfg.kv_quant_group)
+    q_abs = (torch.randn(T, h, Rr, device=DEV, generator=g) * 0.5).to(torch.bfloat16)
+    q_pe = (torch.randn(T, h, Dr, device=DEV, generator=g) * 0.5).to(torch.bfloat16)
+    slots = torch.full((T, k), -1, dtype=torch.int32, device=DEV)
+    lens = ([k, 70, 0, 1, 1500] * 8)[:T]
+    lengths = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    for t in range(T):
+        slots[t, :lens[t]] = torch.randperm(nslots, device=DEV, generator=g)[:lens[t]].to(torch.int32)
+    w_v = (torch.randn(h, Rr, Dv, device=DEV, generator=g) * 0.05).to(torch.bfloat16)
+    assert ops._mla_splits(T, h) > 1
+    fused = ops.attn_values(q_abs, q_pe, cache, slots, lengths, w_v)
+    o, _ = ops.sparse_mla(q_abs, q_pe, cache, slots, lengths)
+    plain = ops.v_expand(o, w_v)
+    assert torch.equal(fused, plain)
+    eo, _ = ref.sparse_mla(q_abs, q_pe, cache, slots, lengths)
+    close(fused, ref.v_expand(eo, w_v), what="attention values")
+    if T >= 2:
+        K = h * Dv
+        tpad = (T + 7) // 8 * 8
+        want = torch.empty(tpad * K, dtype=torch.float16, device=DEV)
+        N.call("sl_permute_x", want.data_ptr(), plain.data_ptr(), T, K, plain.stride(0), N.stream())
+        assert torch.equal(fused._sl_perm, want)
+    else:
+        assert getattr(fused, "_sl_perm", None) is None
+
+
 @pytest.mark.parametrize("T", [1, 4, 9])
 def test_moe_small_and_dense(T):
     cfg = mini_cfg(hidden_size=2048, moe_intermediate_size=512)
@@ -346,6 +385,22 @@ def test_moe_fused_router_glm5_routing(T):
     assert int(ops._zero_counter(x.device).item()) == 0
     assert int(ops._persist_sync(x.device).abs().sum().item()) == 0
     close(ops.moe_tp(x, lw), fused, tol=1e-6, what="second call")
+
+
+@pytest.mark.parametrize("T,H,E,k", [(32, 2048, 64, 12), (30, 6144, 32, 16), (7, 7168, 128, 6), (20, 1024, 38, 4)])
+def test_moe_router_plan_shapes(T, H, E, k):
+    """The fused router kernel beyond the production shape: more than 256 routes (the plan takes several passes), more
+    K steps than a warp keeps in registers, an expert count that leaves the last block partly empty, few experts with
+    many routes each (several chunks of 8 per expert)."""
+    cfg = mini_cfg(hidden_size=H, moe_intermediate_size=128, n_routed_experts=E, num_experts_per_tok=k, n_group=1, topk_group=1)
+    ops, ref = cuda_ops(cfg), RefOps(cfg)
+    lw = random_layer(cfg, 1, 0, DEV, torch.bfloat16)
+    x = torch.randn(T, H, device=DEV, generator=torch.Generator(device=DEV).manual_seed(T + E)).to(torch.bfloat16)
+    fused = ops.moe_tp(x, lw)
+    ids, wts = ops.route(x, lw)
+    close(fused, ops._moe_small(x, lw.experts, lw.shared, ids, wts), tol=2e-3, what="fused vs unfused router")
+    close(fused, ref.moe_tp(x, lw), tol=2e-2, what="fused router vs reference")
+    assert int(ops._zero_counter(x.device).item()) == 0
 
 
 @pytest.mark.parametrize("T,H,I,E,k,ng,tg", [
