@@ -13,6 +13,8 @@ for kernel profiling and per-rank timing.
         one eager prefill chunk (tcgen05 GEMMs, grouped expert GEMMs, prefill attention / indexer)
     python -m slopllm_b200.cli.profile_step --prefill 4096 --tp-shape 8 --layers 6 --op-times
         the same chunk with a CUDA-event pair around every backend op (device time per op, no profiler)
+    python -m slopllm_b200.cli.profile_step --prefill 4096 --context 65536 --tp-shape 8 --layers 6 --op-times
+        a chunk that extends a sequence with 65536 cached tokens (the indexer scans all of them)
     python -m slopllm_b200.cli.profile_step --fused-emulated 8 --batch 8
         the fused GEMM + all-reduce kernels at production shapes with all "ranks" in this process: every rank's
         producer kernel stores into the receive slots of all ranks (here all on one GPU), then each rank's consumer
@@ -40,7 +42,7 @@ from ..runtime.engine import Engine
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="slopllm_b200.cli.profile_step")
     ap.add_argument("--batch", type=int, default=1)
-    ap.add_argument("--context", type=int, default=3000)
+    ap.add_argument("--context", type=int, default=None, help="cached tokens per sequence (decode default 3000, prefill default 0)")
     ap.add_argument("--tp-shape", type=int, default=1)
     ap.add_argument("--layers", type=int, default=5, help="3 dense + MoE layers (layer 3 has a full indexer, layer 4 shares it)")
     ap.add_argument("--steps", type=int, default=3)
@@ -50,6 +52,8 @@ def main(argv=None) -> int:
     ap.add_argument("--op-times", action="store_true", help="eager run with a CUDA-event pair around every backend op; prints the breakdown")
     ap.add_argument("--fused-emulated", type=int, default=0, metavar="W", help="fused GEMM+all-reduce kernels with W emulated ranks")
     args = ap.parse_args(argv)
+    if args.context is None:
+        args.context = 0 if args.prefill > 0 else 3000
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
     if args.fused_emulated:
@@ -57,9 +61,9 @@ def main(argv=None) -> int:
     cfg = GlmMoeDsaConfig.glm5(num_layers=args.layers)
     w = random_model(cfg, 0, dev, torch.bfloat16, 0, args.tp_shape, exact=False, with_mtp=args.mtp > 0)
     B = args.batch
-    pages = args.prefill // 64 + 8 if args.prefill > 0 else B * (args.context // 64 + 8) + 8
+    pages = (args.prefill + args.context) // 64 + 8 if args.prefill > 0 else B * (args.context // 64 + 8) + 8
     eng = Engine(cfg, GlmMoeDsaModel(cfg, w, ParallelContext(device=dev)), num_pages=pages, max_batch=B,
-                 max_seq_len=max(args.context, args.prefill) + 1024, cuda_graph=args.timed > 0, mtp=args.mtp)
+                 max_seq_len=args.context + args.prefill + 1024, cuda_graph=args.timed > 0, mtp=args.mtp)
     seqs = [eng.kv.new_sequence() for _ in range(B)] if args.prefill <= 0 else []
     for s in seqs:
         eng.kv.append_tokens(s, [1] * args.context)
@@ -76,12 +80,15 @@ def main(argv=None) -> int:
         timers = OpTimers(eng.model.ops)
     if args.prefill > 0:
         s = eng.kv.new_sequence()
+        if args.context > 0:                    # the chunk extends a sequence whose first `context` tokens are cached
+            eng.kv.append_tokens(s, [1] * args.context)
+            eng.kv.report_tokens(s)
         prompt = torch.randint(2, cfg.vocab_size - 1, (args.prefill,), generator=torch.Generator().manual_seed(0)).tolist()
         for i in range(2):                      # second pass re-uses the allocator's blocks (steady state)
             if timers is not None:
                 timers.reset()
-            toks, _ = eng.prefill([s], [prompt], chunk_size=args.prefill)
-            eng.kv.truncate(s, 0)
+            toks, _ = eng.prefill([s], [[1] * args.context + prompt], chunk_size=args.prefill)
+            eng.kv.truncate(s, args.context)
         torch.cuda.synchronize()
         out = {"mode": "prefill", "tokens": args.prefill, "next": toks}
         if timers is not None:

@@ -255,8 +255,8 @@ struct MoePlanView {
 };
 
 // ---- router GEMV + routing + plan (+ activation staging) in one launch ---------------------------------------
-// grid (E/4): a block multiplies 4 router rows by every token.  Warp w takes the 256-wide K steps w, w+8, ... of all
-// four rows (the rows of its first three steps are in registers before the kernel waits for its predecessor: the
+// grid (E/ROWS): a block multiplies ROWS (4 or 2) router rows by every token.  Warp w takes the 256-wide K steps w, w+8, ...
+// of those rows (the rows of its first three steps are in registers before the kernel waits for its predecessor: the
 // weights do not depend on it), reads the tokens' values straight from global memory, folds the lanes' partial sums
 // with one transposing butterfly (31 shuffles for 32 sums) and meets the other warps in shared memory in a fixed
 // order, so every rank computes bit-identical logits.  The block that finishes last (ticket counter) routes every
@@ -379,20 +379,21 @@ __global__ void __launch_bounds__(256) moe_plan_kernel(MoePlanView pv, const int
     moe_plan_fast(pv, ids, T, top_k, expert_offset, num_local, has_shared, max_items, sh);
 }
 
-template <int PER>
+template <int PER, int ROWS>
 __global__ void __launch_bounds__(256) router_route_plan_kernel(RouterFusedParams p) {
+    constexpr int TG = 32 / ROWS;            // tokens per pass: ROWS x TG sums fill one transposing reduction
     extern __shared__ int dyn[];             // phase 1: [8 warps][32] partial sums; phase 2: plan tables + ids
     __shared__ int s_last;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int e0 = blockIdx.x * 4;
+    const int e0 = blockIdx.x * ROWS;
     const int steps = p.H / 256;
     constexpr int NPRE = 3;
-    uint4 wv[NPRE][4];
+    uint4 wv[NPRE][ROWS];
 #pragma unroll
     for (int r = 0; r < NPRE; ++r) {
         const int st = r * 8 + warp;
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
+        for (int j = 0; j < ROWS; ++j)
             wv[r][j] = (st < steps && e0 + j < p.E) ? ldg_nc_16(p.router_w + (size_t)(e0 + j) * p.H + st * 256 + lane * 8)
                                                     : make_uint4(0, 0, 0, 0);
     }
@@ -400,23 +401,33 @@ __global__ void __launch_bounds__(256) router_route_plan_kernel(RouterFusedParam
     // the plan's route table starts empty; the last block fills it after the ticket
     for (int i = blockIdx.x * 256 + tid; i < p.max_items * kItemRoutes; i += gridDim.x * 256) p.pv.item_routes[i] = -1;
     float* red = reinterpret_cast<float*>(dyn);
-    for (int t0 = 0; t0 < p.T; t0 += 8) {
-        float acc[32];                       // [4 rows][8 tokens]
+    for (int t0 = 0; t0 < p.T; t0 += TG) {
+        float acc[32];                       // [ROWS][TG]
 #pragma unroll
         for (int i = 0; i < 32; ++i) acc[i] = 0.f;
-        auto round = [&](const uint4 (&w4)[4], int st) {
-            uint4 xv[8];
+        auto round = [&](const uint4 (&wr)[ROWS], int st) {
+            float wf[ROWS][8];
 #pragma unroll
-            for (int t = 0; t < 8; ++t)
-                xv[t] = t0 + t < p.T ? *reinterpret_cast<const uint4*>(p.x + (size_t)(t0 + t) * p.ldx + st * 256 + lane * 8)
-                                     : make_uint4(0, 0, 0, 0);
+            for (int j = 0; j < ROWS; ++j) {
+                const float2 a = bf162_to_f2(wr[j].x), b = bf162_to_f2(wr[j].y), c = bf162_to_f2(wr[j].z), d = bf162_to_f2(wr[j].w);
+                wf[j][0] = a.x; wf[j][1] = a.y; wf[j][2] = b.x; wf[j][3] = b.y; wf[j][4] = c.x; wf[j][5] = c.y; wf[j][6] = d.x; wf[j][7] = d.y;
+            }
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const float2 a = bf162_to_f2(w4[j].x), b = bf162_to_f2(w4[j].y), c = bf162_to_f2(w4[j].z), d = bf162_to_f2(w4[j].w);
+            for (int h = 0; h < TG / 8; ++h) {    // eight tokens at a time: 8 loads in flight
+                if (t0 + h * 8 >= p.T) break;
+                uint4 xv[8];
+#pragma unroll
+                for (int t = 0; t < 8; ++t)
+                    xv[t] = t0 + h * 8 + t < p.T
+                                ? *reinterpret_cast<const uint4*>(p.x + (size_t)(t0 + h * 8 + t) * p.ldx + st * 256 + lane * 8)
+                                : make_uint4(0, 0, 0, 0);
 #pragma unroll
                 for (int t = 0; t < 8; ++t) {
                     const float2 xa = bf162_to_f2(xv[t].x), xb = bf162_to_f2(xv[t].y), xc = bf162_to_f2(xv[t].z), xd = bf162_to_f2(xv[t].w);
-                    acc[j * 8 + t] += a.x * xa.x + a.y * xa.y + b.x * xb.x + b.y * xb.y + c.x * xc.x + c.y * xc.y + d.x * xd.x + d.y * xd.y;
+#pragma unroll
+                    for (int j = 0; j < ROWS; ++j)
+                        acc[j * TG + h * 8 + t] += wf[j][0] * xa.x + wf[j][1] * xa.y + wf[j][2] * xb.x + wf[j][3] * xb.y +
+                                                   wf[j][4] * xc.x + wf[j][5] * xc.y + wf[j][6] * xd.x + wf[j][7] * xd.y;
                 }
             }
         };
@@ -425,11 +436,11 @@ __global__ void __launch_bounds__(256) router_route_plan_kernel(RouterFusedParam
             if (r * 8 + warp < steps) round(wv[r], r * 8 + warp);
         for (int r = NPRE; r * 8 + warp < steps; ++r) {
             const int st = r * 8 + warp;
-            uint4 w4[4];
+            uint4 wr[ROWS];
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
-                w4[j] = e0 + j < p.E ? ldg_nc_16(p.router_w + (size_t)(e0 + j) * p.H + st * 256 + lane * 8) : make_uint4(0, 0, 0, 0);
-            round(w4, st);
+            for (int j = 0; j < ROWS; ++j)
+                wr[j] = e0 + j < p.E ? ldg_nc_16(p.router_w + (size_t)(e0 + j) * p.H + st * 256 + lane * 8) : make_uint4(0, 0, 0, 0);
+            round(wr, st);
         }
         warp_transpose_sum32(acc);
         __syncthreads();                     // the previous token group's sums have been read
@@ -439,7 +450,7 @@ __global__ void __launch_bounds__(256) router_route_plan_kernel(RouterFusedParam
             float v = 0.f;
 #pragma unroll
             for (int w = 0; w < 8; ++w) v += red[w * 32 + tid];
-            const int j = tid >> 3, t = t0 + (tid & 7);
+            const int j = tid / TG, t = t0 + tid % TG;
             if (t < p.T && e0 + j < p.E) p.logits[(size_t)t * p.E + e0 + j] = v;
         }
     }
@@ -459,16 +470,30 @@ __global__ void __launch_bounds__(256) router_route_plan_kernel(RouterFusedParam
     if (!s_last) return;
     __threadfence();
     int* s_ids = dyn + 13 * p.num_local + 16;
-    for (int t = warp; t < p.T; t += 8) {
-        float lg[PER];
+    // warp w routes tokens w, w+8, w+16, w+24 together (their shuffle chains interleave)
+    if (warp < p.T) {
+        float lg[4][PER];
 #pragma unroll
-        for (int i = 0; i < PER; ++i) lg[i] = lane * PER + i < p.E ? __ldcg(p.logits + (size_t)t * p.E + lane * PER + i) : 0.f;
-        int id; float w;
-        route_warp<PER>(lg, p.bias, p.E, p.top_k, p.n_group, p.topk_group, p.norm, p.scale, id, w);
-        if (lane < p.top_k) {
-            p.ids[(size_t)t * p.top_k + lane] = id;
-            p.wts[(size_t)t * p.top_k + lane] = w;
-            s_ids[t * p.top_k + lane] = id;
+        for (int n = 0; n < 4; ++n) {
+            const int t = min(warp + 8 * n, p.T - 1);
+#pragma unroll
+            for (int i = 0; i < PER; ++i) lg[n][i] = lane * PER + i < p.E ? __ldcg(p.logits + (size_t)t * p.E + lane * PER + i) : 0.f;
+        }
+        int id[4];
+        float w[4];
+        if (p.T > 8) {
+            route_warp_n<PER, 4>(lg, p.bias, p.E, p.top_k, p.n_group, p.topk_group, p.norm, p.scale, id, w);
+        } else {
+            route_warp<PER>(lg[0], p.bias, p.E, p.top_k, p.n_group, p.topk_group, p.norm, p.scale, id[0], w[0]);
+        }
+#pragma unroll
+        for (int n = 0; n < 4; ++n) {
+            const int t = warp + 8 * n;
+            if (t < p.T && lane < p.top_k) {
+                p.ids[(size_t)t * p.top_k + lane] = id[n];
+                p.wts[(size_t)t * p.top_k + lane] = w[n];
+                s_ids[t * p.top_k + lane] = id[n];
+            }
         }
     }
     __syncthreads();
@@ -640,9 +665,15 @@ struct MoeRouterArgs {
 };
 
 template <int PER>
-static void launch_router(const RouterFusedParams& rp, dim3 grid, size_t smem, cudaStream_t s) {
-    auto kern = router_route_plan_kernel<PER>;
-    sl_launch(kern, grid, 256, smem, s, rp);
+static void launch_router(const RouterFusedParams& rp, size_t smem, cudaStream_t s) {
+    // few tokens: 4 rows per block (8-token passes); more: 2 rows per block (16-token passes, twice the blocks)
+    if (rp.T <= 8) {
+        auto kern = router_route_plan_kernel<PER, 4>;
+        sl_launch(kern, dim3((rp.E + 3) / 4), 256, smem, s, rp);
+    } else {
+        auto kern = router_route_plan_kernel<PER, 2>;
+        sl_launch(kern, dim3((rp.E + 1) / 2), 256, smem, s, rp);
+    }
 }
 
 // Decode-time MoE layer for T <= 32 tokens: (router, routing,) plan, gate/up, down, weighted reduce (optionally
@@ -676,13 +707,12 @@ SL_API int sl_moe_grouped_mma(const MoeGroupedArgs* a, const MoeRouterArgs* r, c
         const size_t smem2 = (size_t)(13 * a->num_local + 16 + n_routed) * sizeof(int);
         if (smem2 > smem) smem = smem2;
         if (smem > 48 * 1024 || a->num_local < 1) return -1;
-        const dim3 grid((r->E + 3) / 4);
         switch (PER) {
-            case 1: launch_router<1>(rp, grid, smem, s); break;
-            case 2: launch_router<2>(rp, grid, smem, s); break;
-            case 4: launch_router<4>(rp, grid, smem, s); break;
-            case 8: launch_router<8>(rp, grid, smem, s); break;
-            default: launch_router<16>(rp, grid, smem, s); break;
+            case 1: launch_router<1>(rp, smem, s); break;
+            case 2: launch_router<2>(rp, smem, s); break;
+            case 4: launch_router<4>(rp, smem, s); break;
+            case 8: launch_router<8>(rp, smem, s); break;
+            default: launch_router<16>(rp, smem, s); break;
         }
         xp_done = true;
     } else {

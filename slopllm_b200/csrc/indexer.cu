@@ -7,7 +7,7 @@
 // stable gather, sort by index).  Here scoring runs on the FP8 tensor path with fp32
 // scores, the select is a 4x8-bit radix descent over order-preserving keys, and the gather
 // emits ascending positions directly (no separate sort).
-#include "common.cuh"
+#include "indexer.cuh"
 
 __device__ __forceinline__ void mma_e4m3_m16n8k32(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
     asm volatile(
@@ -15,21 +15,6 @@ __device__ __forceinline__ void mma_e4m3_m16n8k32(float (&d)[4], const uint32_t 
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
-
-struct IndexerScoreParams {
-    const uint8_t* q8;        // [T, Hi, D] e4m3
-    const float* w_eff;       // [T, Hi]
-    const uint8_t* idx_cache; // [slots, D + 4]
-    const int* page_table; int pt_stride;
-    const int* batch_idx; const int* positions;
-    int Hi, D, page_size, cp_world, cp_rank, top_k;
-    float* scores; int ld_scores;     // [T, ld_scores]
-    int num_slots;                    // rows of idx_cache (0 = unknown: no check)
-    int* guard;                       // index self-check record (see guard_ok), may be null
-};
-
-// Visible local keys of a query at global position p: local key j is global j*W + r.
-__device__ __forceinline__ int local_visible(int p, int W, int r) { return p >= r ? (p - r) / W + 1 : 0; }
 
 // grid (key tiles of 8 warps x 8 keys x ITER, T); Hi == 32, D == 128.
 // The 128-byte key row is consumed with a fixed permutation of the reduction index that is
@@ -295,6 +280,10 @@ SL_API int sl_indexer_scores(const IndexerScoreParams* p, int T, int max_local, 
     int kpb = 512;
     while (kpb > 64 && (long)((max_local + kpb - 1) / kpb) * T < 296) kpb >>= 1;
     dim3 grid((max_local + kpb - 1) / kpb, T);
+    {
+        const int rc = indexer_scores_tcgen05(p, T, max_local, s);
+        if (rc != -2) return rc;
+    }
     if (p->Hi == 32 && p->D == 128 && p->page_size == 64 && T > 32 && g_indexer_tiled) {
         // prefill: 8 tokens per CTA share the key pages
         const int groups = (T + 7) / 8;
@@ -368,19 +357,23 @@ __device__ __forceinline__ void radix_pick_bin(const uint32_t* hist, uint32_t* w
     __syncthreads();
 }
 
-// One block per query token.  If the query sees at most top_k keys in total, all local
-// keys are emitted.  Otherwise: radix descent for the k'-th largest key (k' = min(top_k,
-// n_local)), then an in-order gather of keys above the threshold plus the first ties.
-// Scores of up to 8192 keys stay in registers between the passes.
+// One block per query token.  If the query sees at most top_k keys in total, all local keys are emitted.
+// Otherwise: radix descent for the k'-th largest key (k' = min(top_k, n_local)) over four 8-bit digits, then an
+// in-order gather of keys above the threshold plus the first ties.
+//   * digit histograms are private to a warp (32 x 256 counters in shared memory) and lanes that hit the same bin
+//     are merged with a warp match first, so the scan needs no atomics and does not serialise on the few bins that
+//     similar scores share;
+//   * the gather gives every warp one contiguous segment of the row: a counting walk, one scan over the 32 warps'
+//     totals, and an emitting walk with warp-local running offsets, instead of block-wide barriers per 1024 keys.
+// The row (at most a few hundred KB) stays in L1 / L2 between the six walks.
 __global__ void __launch_bounds__(1024) topk_select_kernel(TopkSelectParams p) {
     pdl_grid_sync();
+    __shared__ uint32_t whist[32][256];
     __shared__ uint32_t hist[256];
     __shared__ uint32_t wtot[8];
     __shared__ uint32_t s_prefix, s_remaining;
-    __shared__ int wsum[32], wsum2[32];
-    __shared__ int s_base, s_eq_used;
-    constexpr int ITEMS = 8;
-    const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = blockDim.x >> 5;
+    __shared__ int wgt[32], weq[32];
+    const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int pos = p.n_fixed > 0 ? p.n_fixed - 1 : p.positions[t];
     const int n = p.n_fixed > 0 ? p.n_fixed : local_visible(pos, p.cp_world, p.cp_rank);
     int* opos = p.out_pos + (size_t)t * p.top_k;
@@ -397,33 +390,45 @@ __global__ void __launch_bounds__(1024) topk_select_kernel(TopkSelectParams p) {
         return;
     }
     const float* sc = p.scores + (size_t)t * p.ld_scores;
-    const bool cached = n <= ITEMS * (int)blockDim.x;
-    uint32_t keys[ITEMS];
-    if (cached) {
-#pragma unroll
-        for (int q = 0; q < ITEMS; ++q) {
-            const int i = tid + q * blockDim.x;
-            keys[q] = i < n ? order_key(sc[i]) : 0u;
-        }
-    }
+    const bool vec = (((uintptr_t)sc) & 15) == 0 && p.ld_scores % 4 == 0;      // whole groups of 4 stay inside the row
     const int kk = min(p.top_k, n);
     uint32_t mask = 0;
     if (tid == 0) { s_prefix = 0; s_remaining = (uint32_t)kk; }
     for (int shift = 24; shift >= 0; shift -= 8) {
-        for (int i = tid; i < 256; i += blockDim.x) hist[i] = 0;
+        for (int i = tid; i < 32 * 256; i += 1024) (&whist[0][0])[i] = 0;
         __syncthreads();
         const uint32_t prefix = s_prefix;
-        if (cached) {
-#pragma unroll
-            for (int q = 0; q < ITEMS; ++q) {
-                const int i = tid + q * blockDim.x;
-                if (i < n && (keys[q] & mask) == prefix) atomicAdd(&hist[(keys[q] >> shift) & 255u], 1u);
+        uint32_t* mine = whist[warp];
+        auto visit = [&](bool live, float v) {
+            const uint32_t key = order_key(v);
+            const bool hit = live && (key & mask) == prefix;
+            const unsigned hm = __ballot_sync(0xffffffffu, hit);
+            if (hit) {
+                const uint32_t bin = (key >> shift) & 255u;
+                const unsigned peers = __match_any_sync(hm, bin);
+                if (lane == __ffs(peers) - 1) mine[bin] += __popc(peers);
+            }
+            __syncwarp();
+        };
+        // every lane of a warp makes the same number of trips (the visits vote)
+        if (vec) {
+            for (int b0 = warp * 128; b0 < n; b0 += 4096) {
+                const int i0 = b0 + lane * 4;
+                const float4 v = i0 < n ? *reinterpret_cast<const float4*>(sc + i0) : make_float4(0.f, 0.f, 0.f, 0.f);
+                visit(i0 < n, v.x); visit(i0 + 1 < n, v.y); visit(i0 + 2 < n, v.z); visit(i0 + 3 < n, v.w);
             }
         } else {
-            for (int i = tid; i < n; i += blockDim.x) {
-                const uint32_t key = order_key(sc[i]);
-                if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1u);
+            for (int b0 = warp * 32; b0 < n; b0 += 1024) {
+                const int i = b0 + lane;
+                visit(i < n, i < n ? sc[i] : 0.f);
             }
+        }
+        __syncthreads();
+        if (tid < 256) {
+            uint32_t c = 0;
+#pragma unroll 8
+            for (int w = 0; w < 32; ++w) c += whist[w][tid];
+            hist[tid] = c;
         }
         __syncthreads();
         radix_pick_bin(hist, wtot, &s_prefix, &s_remaining, prefix, shift);
@@ -431,55 +436,53 @@ __global__ void __launch_bounds__(1024) topk_select_kernel(TopkSelectParams p) {
     }
     const uint32_t thr = s_prefix;
     const int need_eq = (int)s_remaining;      // how many keys equal to thr are taken (lowest index first)
-    if (tid == 0) { s_base = 0; s_eq_used = 0; }
+    // warp w owns keys [w * seg, (w + 1) * seg)
+    const int seg = ((n + 31) / 32 + 31) / 32 * 32;
+    const int lo = min(n, warp * seg), hi = min(n, lo + seg);
+    int cgt = 0, ceq = 0;
+    for (int i0 = lo; i0 < hi; i0 += 32) {
+        const int i = i0 + lane;
+        const uint32_t key = i < hi ? order_key(sc[i]) : 0u;
+        cgt += __popc(__ballot_sync(0xffffffffu, i < hi && key > thr));
+        ceq += __popc(__ballot_sync(0xffffffffu, i < hi && key == thr));
+    }
+    if (lane == 0) { wgt[warp] = cgt; weq[warp] = ceq; }
     __syncthreads();
-    for (int c0 = 0, q = 0; c0 < n; c0 += blockDim.x, ++q) {
-        const int i = c0 + tid;
-        uint32_t key = 0;
-        if (i < n) {
-            if (cached) {
-                // q is uniform; select the register without dynamic indexing
-#pragma unroll
-                for (int r = 0; r < ITEMS; ++r) if (r == q) key = keys[r];
-            } else {
-                key = order_key(sc[i]);
-            }
-        }
-        const bool gt = (i < n) && key > thr, eq = (i < n) && key == thr;
+    int base = 0, eq_used = 0;
+    for (int w = 0; w < warp; ++w) {
+        const int e = weq[w];
+        base += wgt[w] + max(0, min(e, need_eq - eq_used));
+        eq_used += e;
+    }
+    const unsigned lt = (1u << lane) - 1;
+    for (int i0 = lo; i0 < hi; i0 += 32) {
+        const int i = i0 + lane;
+        const float v = i < hi ? sc[i] : 0.f;
+        const uint32_t key = i < hi ? order_key(v) : 0u;
+        const bool gt = i < hi && key > thr, eq = i < hi && key == thr;
         const unsigned meq = __ballot_sync(0xffffffffu, eq);
-        if (lane == 0) wsum[warp] = __popc(meq);
-        __syncthreads();
-        int eq_before = s_eq_used, eq_total = 0;
-        for (int w = 0; w < nw; ++w) {
-            if (w < warp) eq_before += wsum[w];
-            eq_total += wsum[w];
-        }
-        eq_before += __popc(meq & ((1u << lane) - 1));
-        const bool take = gt || (eq && eq_before < need_eq);
+        const bool take = gt || (eq && eq_used + __popc(meq & lt) < need_eq);
         const unsigned mt = __ballot_sync(0xffffffffu, take);
-        if (lane == 0) wsum2[warp] = __popc(mt);
-        __syncthreads();
-        int off = s_base, tk_total = 0;
-        for (int w = 0; w < nw; ++w) {
-            if (w < warp) off += wsum2[w];
-            tk_total += wsum2[w];
-        }
-        off += __popc(mt & ((1u << lane) - 1));
+        const int off = base + __popc(mt & lt);
         if (take && off < p.top_k) {
             opos[off] = i * p.cp_world + p.cp_rank;
-            osc[off] = sc[i];
+            osc[off] = v;
             if (oslot != nullptr) oslot[off] = pt[i / p.page_size] * p.page_size + i % p.page_size;
         }
-        __syncthreads();
-        if (tid == 0) { s_base += tk_total; s_eq_used += eq_total; }
-        __syncthreads();
+        base += __popc(mt);
+        eq_used += __popc(meq);
     }
-    for (int i = s_base + tid; i < p.top_k; i += blockDim.x) {
+    // the last warp's running total is the number selected
+    __shared__ int s_total;
+    if (warp == 31 && lane == 0) s_total = base;
+    __syncthreads();
+    const int total = s_total;
+    for (int i = total + tid; i < p.top_k; i += blockDim.x) {
         opos[i] = -1;
         osc[i] = 0.f;
         if (oslot != nullptr) oslot[i] = -1;
     }
-    if (oslot != nullptr && tid == 0) p.lengths[t] = min(s_base, p.top_k);
+    if (oslot != nullptr && tid == 0) p.lengths[t] = min(total, p.top_k);
 }
 
 SL_API int sl_topk_select(const TopkSelectParams* p, int T, cudaStream_t s) {

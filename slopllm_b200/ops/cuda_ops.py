@@ -286,7 +286,8 @@ class CudaOps:
                     page_table=st.page_table.data_ptr(), pt_stride=st.page_table.stride(0), batch_idx=batch_idx.data_ptr(),
                     positions=positions.data_ptr(), Hi=c.index_n_heads, D=c.index_head_dim, page_size=st.page_size,
                     cp_world=W, cp_rank=r, top_k=c.index_topk, scores=scores.data_ptr(), ld_scores=scores.stride(0),
-                    num_slots=layer_cache.idx.shape[0], guard=self._guard(dev))
+                    num_slots=layer_cache.idx.shape[0], guard=self._guard(dev),
+                    one_sequence=int(bool(st.extra.get("one_sequence", False))), err=self._guard(dev) - 16)
                 N.call("sl_indexer_scores", C.byref(sp), n, max_local, N.stream())
             tp = N.TopkSelectParams(scores=scores.data_ptr(), ld_scores=scores.stride(0), positions=positions.data_ptr(),
                                     top_k=c.index_topk, cp_world=W, cp_rank=r, out_pos=pos[t0:t1].data_ptr(),

@@ -42,6 +42,9 @@ def kernels() -> C.CDLL:
     lib.sl_indexer_set_tiled.argtypes = [i32]
     lib.sl_indexer_set_tiled.restype = None
     lib.sl_indexer_set_tiled(0 if os.environ.get("SLOPLLM_B200_INDEXER_TILED", "1") == "0" else 1)
+    lib.sl_indexer_set_tcgen05.argtypes = [i32]
+    lib.sl_indexer_set_tcgen05.restype = None
+    lib.sl_indexer_set_tcgen05(0 if os.environ.get("SLOPLLM_B200_INDEXER_TCGEN05", "1") == "0" else 1)
     lib.sl_sparse_mla_direct_ok.argtypes = [i32, i32, i32]
     lib.sl_sparse_mla_direct_ok.restype = i32
     lib.sl_sparse_mla_set_transposed.argtypes = [i32]
@@ -96,7 +99,8 @@ class QPostParams(C.Structure):
 class IndexerScoreParams(C.Structure):
     _fields_ = [("q8", vp), ("w_eff", vp), ("idx_cache", vp), ("page_table", vp), ("pt_stride", i32),
                 ("batch_idx", vp), ("positions", vp), ("Hi", i32), ("D", i32), ("page_size", i32), ("cp_world", i32),
-                ("cp_rank", i32), ("top_k", i32), ("scores", vp), ("ld_scores", i32), ("num_slots", i32), ("guard", vp)]
+                ("cp_rank", i32), ("top_k", i32), ("scores", vp), ("ld_scores", i32), ("num_slots", i32), ("guard", vp),
+                ("one_sequence", i32), ("err", vp)]
 
 
 class TopkSelectParams(C.Structure):

@@ -309,11 +309,14 @@ class Engine:
         dev = self.device
         width = max(self.pt_width, max(len(s.pages) for s in seqs))
         pt = torch.tensor(self.kv.page_table_rows(seqs, width), dtype=torch.int32, device=dev)
-        return StepState(input_ids=torch.as_tensor(ids, dtype=torch.int64, device=dev),
-                         positions=torch.as_tensor(positions, dtype=torch.int32, device=dev),
-                         batch_idx=torch.as_tensor(batch_idx, dtype=torch.int32, device=dev), page_table=pt,
-                         logits_idx=logits_idx, cp_world=self.ctx.cp_world, cp_rank=self.ctx.cp_rank,
-                         max_kv_len=max_kv_len)
+        st = StepState(input_ids=torch.as_tensor(ids, dtype=torch.int64, device=dev),
+                       positions=torch.as_tensor(positions, dtype=torch.int32, device=dev),
+                       batch_idx=torch.as_tensor(batch_idx, dtype=torch.int32, device=dev), page_table=pt,
+                       logits_idx=logits_idx, cp_world=self.ctx.cp_world, cp_rank=self.ctx.cp_rank,
+                       max_kv_len=max_kv_len)
+        # rows of one sequence share one page table: the prefill index scorer on the tensor cores takes that case
+        st.extra["one_sequence"] = len(batch_idx) > 0 and min(batch_idx) == max(batch_idx)
+        return st
 
     # ---- plain decode -----------------------------------------------------------------------------------------
     @traced("decode_step")

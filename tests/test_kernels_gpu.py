@@ -251,6 +251,50 @@ def test_indexer_prefill_tiles_match_per_token_kernel(cp):
         assert len(a) == len(b) and len(a ^ b) <= max(2, len(b) // 100), (t, len(a), len(b), len(a ^ b))
 
 
+@pytest.mark.parametrize("cp,ctx,T", [((1, 0), 3000, 100), ((1, 0), 9000, 257), ((2, 1), 5000, 64), ((1, 0), 2049, 40)])
+def test_indexer_prefill_scorer_on_tcgen05(cp, ctx, T):
+    """A prefill chunk of one sequence takes the tensor-core scorer (keys on the 128 MMA rows, 8 tokens x 32 heads on the
+    columns, relu / head weights / key scale folded per TMEM lane): same scores as the mma.sync kernels up to the order
+    of the fp32 sums, same selection as the fp32 reference.  Ragged last token block and key tile, rows below the
+    top-k threshold, logical != physical pages, a context-parallel rank."""
+    from slopllm_b200.ops import native as N, tcgen05
+    cfg = mini_cfg()
+    ops, ref = cuda_ops(cfg), RefOps(cfg)
+    W, r = cp
+    n_pages = -(-ctx // (64 * W)) + 1
+    positions = list(range(ctx - T, ctx))
+    st = _state(cfg, positions, [0] * T, n_pages, 1, W, r)
+    st.extra["one_sequence"] = True
+    g = torch.Generator(device=DEV).manual_seed(ctx + T)
+    Di, Hi = cfg.index_head_dim, cfg.index_n_heads
+    assert (Di, Hi) == (128, 32)
+    cache = type("C", (), {})()
+    cache.idx = quant.pack_index_rows(torch.randn(n_pages * 64, Di, device=DEV, generator=g))
+    q = torch.randn(T, Hi, Di, device=DEV, generator=g)
+    hw = torch.rand(T, Hi, device=DEV, generator=g) - 0.3                  # some negative head weights
+    q8f, weff = R.indexer_quantize_q(q, hw, Di ** -0.5)
+    q8 = q8f.to(torch.float8_e4m3fn).view(torch.uint8)
+    pos, sc = ops.indexer_topk(q8, weff, cache, st)
+    scores_tc = st.extra["idx_scores"].clone()
+    tcgen05.check_errors(DEV)
+    N.kernels().sl_indexer_set_tcgen05(0)
+    try:
+        st.extra.pop("idx_scores")
+        pos2, sc2 = ops.indexer_topk(q8, weff, cache, st)
+        scores_mma = st.extra["idx_scores"]
+    finally:
+        N.kernels().sl_indexer_set_tcgen05(1)
+    for t in range(T):
+        p = positions[t]
+        n_vis = ((p - r) // W + 1 if p >= r else 0) if p + 1 > cfg.index_topk else 0
+        a, b = scores_tc[t, :n_vis], scores_mma[t, :n_vis]
+        assert torch.allclose(a, b, rtol=1e-4, atol=1e-4 * float(b.abs().max() if n_vis else 1.0)), (t, n_vis)
+    epos, _ = ref.indexer_topk(q8f, weff, cache, st)
+    for t in range(T):
+        a, b = set(pos[t][pos[t] >= 0].tolist()), set(epos[t][epos[t] >= 0].tolist())
+        assert len(a) == len(b) and len(a ^ b) <= max(2, len(b) // 100), (t, len(a), len(b), len(a ^ b))
+
+
 @pytest.mark.parametrize("which", ["tiny", "mini"])
 def test_sparse_mla_and_v_expand(which):
     cfg = GlmMoeDsaConfig.tiny() if which == "tiny" else mini_cfg()
