@@ -25,8 +25,9 @@ def parse_args(argv=None):
     add_model_args(ap)
     ap.add_argument("--host", default="127.0.0.1")
     ap.add_argument("--port", type=int, default=8000)
-    ap.add_argument("--api-key", default=None)
-    ap.add_argument("--admin-api-key", default=None)
+    ap.add_argument("--api-key", default=os.environ.get("SLOPLLM_B200_API_KEY") or None,
+                    help="bearer token clients must send (default: $SLOPLLM_B200_API_KEY, unset = open)")
+    ap.add_argument("--admin-api-key", default=os.environ.get("SLOPLLM_B200_ADMIN_API_KEY") or None)
     ap.add_argument("--served-model-name", default="")
     ap.add_argument("--no-warmup", action="store_true")
     ap.add_argument("--health-port", type=int, default=0, help="multi-rank jobs: port of the heartbeat store (0: no rank-failure monitor)")

@@ -36,7 +36,8 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
                                                         int M, int N, int K, int ldc, int out_f32, int transpose_out,
                                                         int* __restrict__ err, int use_push, PushCtx push,
                                                         const int4* __restrict__ tiles, const int* __restrict__ num_tiles,
-                                                        int kb_per_split, long long split_stride, int tiles_n, int total_tiles) {
+                                                        int kb_per_split, long long split_stride, int tiles_n, int total_tiles,
+                                                        int a_group_cols, int a_group_stride) {
     using Cfg = GemmCfg<BN>;
     constexpr int STAGES = Cfg::STAGES;
     extern __shared__ uint8_t smem_raw[];
@@ -116,6 +117,8 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
             for (int tile = first; tile < total && ok; tile += stride) {
                 int m0, n0, b_row0, m_end;
                 tile_coords(tile, m0, n0, b_row0, m_end);
+                // batched product (one B matrix per group of output columns): the group's A columns start here
+                const int a_c0 = a_group_cols > 0 ? (n0 / a_group_cols) * a_group_stride : 0;
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
@@ -125,7 +128,7 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
                     }
                     if (!tc::mbar_wait(&empty[s], ph ^ 1)) { atomicExch(err, 1); ok = false; break; }
                     tc::mbar_expect_tx(&full[s], Cfg::A_BYTES + Cfg::B_BYTES);
-                    tc::tma_load_2d(sA + s * Cfg::A_BYTES, &tmA, &full[s], (kb0 + kb) * BK, m0);
+                    tc::tma_load_2d(sA + s * Cfg::A_BYTES, &tmA, &full[s], a_c0 + (kb0 + kb) * BK, m0);
                     tc::tma_load_2d(sB + s * Cfg::B_BYTES, &tmB, &full[s], (kb0 + kb) * BK, b_row0);
                 }
             }
@@ -287,9 +290,9 @@ template <int BN>
 int launch(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc, int out_f32,
            int transpose_out, int* err, cudaStream_t s, const PushCtx* push = nullptr, const int4* tiles = nullptr,
            const int* num_tiles = nullptr, int max_tiles = 0, int b_rows = 0, int splits = 1, long long split_stride = 0,
-           bool persistent = false, int push_mode = 1) {
+           bool persistent = false, int push_mode = 1, int a_group_cols = 0, int a_group_stride = 0, int a_cols = 0) {
     CUtensorMap tmA, tmB;
-    int rc = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)M, (uint64_t)K, (uint64_t)lda * 2, BM, BK);
+    int rc = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)M, (uint64_t)(a_cols ? a_cols : K), (uint64_t)lda * 2, BM, BK);
     if (rc) return rc;
     rc = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)(b_rows ? b_rows : N), (uint64_t)K, (uint64_t)ldb * 2, BN, BK);
     if (rc) return rc;
@@ -316,11 +319,33 @@ int launch(const void* A, const void* B, void* C, int M, int N, int K, int lda, 
     }
     sl_launch(kern, grid, 192, GemmCfg<BN>::SMEM, s, tmA, tmB, C, M, N, K, ldc, out_f32, transpose_out, err, push ? push_mode : 0,
                                               push ? *push : PushCtx{}, tiles, num_tiles, kb_per_split, split_stride, tiles_n,
-                                              total_tiles);
+                                              total_tiles, a_group_cols, a_group_stride);
     return (int)cudaGetLastError();
 }
 
 }  // namespace
+
+// Head-batched product for the MLA absorb / value-expansion steps of a prefill chunk:
+//   C[t, g * n_per + n] = sum_k A[t, g * a_stride + k] * B[g * n_per + n, k]       g < groups, k < K
+// A [M, >= (groups - 1) * a_stride + K] bf16 (row stride lda), B [groups * n_per, K] bf16 (each group's matrix stored
+// output-major), C [M, groups * n_per] (row stride ldc).  The persistent tile walk of the plain GEMM, with the A tile's
+// column origin taken from the output tile's group; n_per must be a multiple of the tile width.
+// Replaces the reference's cuBLAS strided-batched calls (`csrc/glm_ops.cu`, absorb and v-expand).
+SL_API int sl_gemm_bf16_tcgen05_batched(const void* A, const void* B, void* C, int M, int groups, int n_per, int K, int lda,
+                                        int a_stride, int ldb, int ldc, int out_f32, void* err, cudaStream_t s) {
+    if (M <= 0 || groups <= 0 || n_per <= 0 || K <= 0) return 0;
+    if (K % BK != 0 || lda % 8 != 0 || ldb % 8 != 0 || a_stride % 8 != 0) return -1;        // a K tail would read the next group's columns
+    if ((out_f32 ? ldc % 4 : ldc % 8) != 0) return -1;
+    const int a_cols = (groups - 1) * a_stride + K;
+    const int N = groups * n_per;
+    if (n_per % 256 == 0)
+        return launch<256>(A, B, C, M, N, K, lda, ldb, ldc, out_f32, 0, (int*)err, s, nullptr, nullptr, nullptr, 0, 0, 1, 0, true, 1, n_per, a_stride, a_cols);
+    if (n_per % 128 == 0)
+        return launch<128>(A, B, C, M, N, K, lda, ldb, ldc, out_f32, 0, (int*)err, s, nullptr, nullptr, nullptr, 0, 0, 1, 0, true, 1, n_per, a_stride, a_cols);
+    if (n_per % 64 == 0)
+        return launch<64>(A, B, C, M, N, K, lda, ldb, ldc, out_f32, 0, (int*)err, s, nullptr, nullptr, nullptr, 0, 0, 1, 0, true, 1, n_per, a_stride, a_cols);
+    return -1;
+}
 
 // A [M, K] bf16 (row stride lda), B [N, K] bf16 (row stride ldb), C [M, N] (row stride ldc; bf16 or fp32).
 // `err` is a device int the kernel sets to non-zero if one of its bounded waits expired.

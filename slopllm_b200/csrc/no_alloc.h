@@ -24,7 +24,9 @@
 //     process exits.
 //   * The first call on each device looks up the array's device address
 //     (cudaGetSymbolAddress) with that device current.  Make that first call outside any
-//     stream capture; later calls only launch kernels.
+//     stream capture; later calls only launch kernels.  The address is kept in a plain per-device table:
+//     let one host thread make the first call on a device before several host threads call concurrently
+//     (two racing first calls would both store the same address, but the store is not synchronised).
 //   * All calls share the one array, which keeps whatever the previous call left in it; each
 //     call overwrites every partial it later reads, so nothing needs clearing.  Two calls that
 //     overlap on the GPU (different streams, no dependency) race on the array: serialise them.

@@ -44,7 +44,52 @@ __global__ void prefetch_l2_kernel(const uint8_t* __restrict__ p, size_t nbytes)
         asm volatile("prefetch.global.L2 [%0];" ::"l"(p + off));
 }
 
+constexpr int kPrefetchRanges = 12;
+struct PrefetchList {
+    const uint8_t* ptr[kPrefetchRanges];
+    unsigned long long lines[kPrefetchRanges];      // 128-byte lines of each range
+    int count;
+    int keep;                                       // 1: mark the lines evict-last (streaming traffic passes them by)
+};
+
+// One launch for several weight tensors of the next layer: the lines of all ranges are numbered consecutively and
+// spread over the grid.
+__global__ void prefetch_l2_multi_kernel(PrefetchList l) {
+    pdl_grid_sync();
+    unsigned long long total = 0;
+    for (int i = 0; i < l.count; ++i) total += l.lines[i];
+    for (unsigned long long n = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; n < total;
+         n += (unsigned long long)gridDim.x * blockDim.x) {
+        unsigned long long k = n;
+        int i = 0;
+        while (k >= l.lines[i]) { k -= l.lines[i]; ++i; }
+        const uint8_t* a = l.ptr[i] + k * 128;
+        if (l.keep) asm volatile("prefetch.global.L2::evict_last [%0];" ::"l"(a));
+        else asm volatile("prefetch.global.L2 [%0];" ::"l"(a));
+    }
+}
+
 }  // namespace
+
+// Up to 12 byte ranges in one launch (`ptr[i]`, `bytes[i]`); `keep` marks the lines evict-last.
+SL_API int sl_prefetch_l2_multi(const void* const* ptrs, const unsigned long long* bytes, int count, int keep, cudaStream_t s) {
+    if (count <= 0) return 0;
+    if (count > kPrefetchRanges) return -1;
+    PrefetchList l{};
+    unsigned long long total = 0;
+    for (int i = 0; i < count; ++i) {
+        l.ptr[i] = (const uint8_t*)ptrs[i];
+        l.lines[i] = (bytes[i] + 127) / 128;
+        total += l.lines[i];
+    }
+    l.count = count;
+    l.keep = keep;
+    if (total == 0) return 0;
+    unsigned blocks = (unsigned)((total + 255) / 256);
+    if (blocks > 148 * 2) blocks = 148 * 2;
+    sl_launch(prefetch_l2_multi_kernel, blocks, 256, 0, s, l);
+    return SL_LAUNCH_CHECK();
+}
 
 // x [rows, K] bf16 -> q [rows, K] e4m3 bytes, scales [rows, ceil(K / 128)] fp32.
 SL_API int sl_quantize_fp8(void* q, void* scales, const void* x, int rows, int K, cudaStream_t s) {

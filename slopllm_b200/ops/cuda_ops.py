@@ -243,9 +243,11 @@ class CudaOps:
             # prefill: the absorb product is a plain batched GEMM (one per head): library bmm, as in the reference
             # (`glm_bmm`, `csrc/glm_ops.cu`); the rotary / quantisation part keeps its own kernel
             N.call("sl_q_post", C.byref(p), T, N.stream())
-            q_nope = qb[:, :hl * c.qk_head_dim].view(T, hl, c.qk_head_dim)[..., :c.qk_nope_head_dim]
-            q_abs = torch.bmm(q_nope.transpose(0, 1), lw.w_kn).transpose(0, 1).contiguous()
-            return q_abs, q_pe, q8, w_eff
+            q_abs = self._head_batched_gemm(qb, c.qk_head_dim, c.qk_nope_head_dim, lw, "w_kn")
+            if q_abs is None:         # shapes the tile walk does not take: library batched product
+                q_nope = qb[:, :hl * c.qk_head_dim].view(T, hl, c.qk_head_dim)[..., :c.qk_nope_head_dim]
+                q_abs = torch.bmm(q_nope.transpose(0, 1), lw.w_kn).transpose(0, 1).contiguous()
+            return q_abs.view(T, hl, c.kv_lora_rank), q_pe, q8, w_eff
         q_abs = torch.empty(T, hl, c.kv_lora_rank, dtype=torch.bfloat16, device=dev)
         N.call("sl_q_post_absorb", C.byref(p), q_abs.data_ptr(), lw.w_kn.data_ptr(), T, c.kv_lora_rank, N.stream())
         return q_abs, q_pe, q8, w_eff
@@ -418,12 +420,42 @@ class CudaOps:
             out._sl_perm = perm
         return out
 
+    def _head_batched_gemm(self, a, a_stride: int, K: int, owner, w):
+        """out[t, h * n + j] = sum_k a[t, h * a_stride + k] * W[h, k, j] on the persistent tcgen05 GEMM (`W` [heads, K, n];
+        its output-major copy [heads * n, K] is made once and kept on the tensor's owner).  None when the shape is not one
+        the tile walk takes.  Replaces the library bmm of the absorb and value-expansion steps of a prefill chunk
+        (the reference calls cuBLAS strided-batched there, `csrc/glm_ops.cu` `glm_bmm`)."""
+        from . import tcgen05
+        if isinstance(w, str):
+            name, w = w, getattr(owner, w)
+            wt = getattr(owner, "_" + name + "_t", None)
+        else:
+            name, wt = None, getattr(w, "_sl_out_major", None)
+        heads, Kw, n = w.shape
+        if (Kw != K or K % 64 != 0 or n % 64 != 0 or a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or a.stride(-1) != 1
+                or a.stride(0) % 8 != 0 or a_stride % 8 != 0):
+            return None
+        if wt is None:
+            wt = w.transpose(1, 2).contiguous().view(heads * n, K)
+            if name is not None:
+                setattr(owner, "_" + name + "_t", wt)
+            else:
+                w._sl_out_major = wt
+        T = a.shape[0]
+        out = torch.empty(T, heads * n, dtype=torch.bfloat16, device=a.device)
+        N.call("sl_gemm_bf16_tcgen05_batched", a.data_ptr(), wt.data_ptr(), out.data_ptr(), T, heads, n, K, a.stride(0), a_stride,
+               K, heads * n, 0, tcgen05.error_flag(a.device).data_ptr(), N.stream())
+        return out
+
     def v_expand(self, o, w_v):
         T, hl, Rr = o.shape
         Dv = w_v.shape[2]
         o = self._bf16(o).contiguous()
         if T > DECODE_MAX_T:
-            # prefill: plain batched GEMM over the heads (library bmm; the reference uses cuBLAS strided-batched here too)
+            # prefill: one tcgen05 GEMM walks the (token tile, head) grid; the head's matrix is stored output-major once
+            out = self._head_batched_gemm(o.view(T, hl * Rr), Rr, Rr, None, w_v)
+            if out is not None:
+                return out
             return torch.bmm(o.transpose(0, 1), w_v).transpose(0, 1).reshape(T, hl * Dv)
         out = torch.empty(T, hl * Dv, dtype=torch.bfloat16, device=o.device)
         N.call("sl_bmv", out.data_ptr(), o.data_ptr(), w_v.data_ptr(), T, hl, Rr, Dv, hl * Rr, Rr, 0, 0, N.stream())

@@ -39,6 +39,28 @@ def prefetch_l2(t: torch.Tensor, stream=None) -> None:
     N.call("sl_prefetch_l2", t.data_ptr(), t.numel() * t.element_size(), s)
 
 
+class PrefetchSet:
+    """Byte ranges of several tensors, packed once for `sl_prefetch_l2_multi` (at most 12 tensors; CPU tensors and
+    None are skipped).  `launch(stream)` issues one kernel that pulls them all into L2."""
+
+    def __init__(self, tensors, keep: bool = True):
+        import ctypes as C
+        ts = [t for t in tensors if t is not None and t.is_cuda and t.numel() > 0][:12]
+        self.tensors = ts                                    # keeps the storage alive
+        self.count = len(ts)
+        self.keep = int(keep)
+        self.nbytes = sum(t.numel() * t.element_size() for t in ts)
+        self._ptrs = (C.c_void_p * max(1, self.count))(*[t.data_ptr() for t in ts])
+        self._bytes = (C.c_ulonglong * max(1, self.count))(*[t.numel() * t.element_size() for t in ts])
+
+    def launch(self, stream=None) -> None:
+        if self.count == 0:
+            return
+        N = _native()
+        s = N.stream() if stream is None else stream.cuda_stream
+        N.call("sl_prefetch_l2_multi", self._ptrs, self._bytes, self.count, self.keep, s)
+
+
 def gather_topk_ckv(kv_cache: torch.Tensor, slots: torch.Tensor, lengths: torch.Tensor, R: int, Dr: int, group: int):
     """Distinct selected rows of the packed cache as dense bf16 [U, R + Dr] (ascending slot order) and the
     fan-out table where[t, j] = row of slots[t, j] in that buffer (-1 for unused entries).

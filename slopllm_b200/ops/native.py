@@ -179,11 +179,13 @@ _SIGS = {
     "sl_attn_pre": [C.POINTER(AttnPreParams), i32, vp],
     "sl_q_post": [C.POINTER(QPostParams), i32, vp],
     "sl_q_post_absorb": [C.POINTER(QPostParams), vp, vp, i32, i32, vp],
+    "sl_gemm_bf16_tcgen05_batched": [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp, vp],
     "sl_bmv": [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i64, vp],
     "sl_smallT_splits": [i32, i32, i32],
     "sl_gather_fetch": [vp, vp, vp, i32, C.c_size_t, C.c_size_t, vp],
     "sl_quantize_fp8": [vp, vp, vp, i32, i32, vp],
     "sl_prefetch_l2": [vp, C.c_size_t, vp],
+    "sl_prefetch_l2_multi": [vp, vp, i32, i32, vp],
     "sl_gather_mark": [vp, vp, vp, i32, i32, vp],
     "sl_gather_rows": [vp, vp, vp, vp, i32, i32, i32, i32, vp],
     "sl_gather_fanout": [vp, vp, vp, vp, i32, i32, vp],

@@ -25,6 +25,9 @@ from ..utils.tracing import traced
 from .graphs import CaptureManager
 
 
+STEP_ARENA_BYTES = 16 << 20        # static step inputs / their pinned mirrors and results; larger shapes fall back
+
+
 @dataclass
 class StepBuffers:
     """Static device buffers (+ pinned host mirror) for one (batch, tokens-per-row) shape."""
@@ -36,11 +39,24 @@ class StepBuffers:
     dev: torch.Tensor              # device int32 [n]
 
     @classmethod
-    def create(cls, B: int, tpr: int, width: int, device) -> "StepBuffers":
+    def create(cls, B: int, tpr: int, width: int, device, host_arena=None, dev_arena=None) -> "StepBuffers":
+        """With arenas (`runtime/workspace.py`) the pinned mirror and the device buffer are carved from the engine's two
+        step arenas and stay for the engine's life (a captured graph keeps reading the device one); a shape that no
+        longer fits gets buffers of its own."""
         n = 3 * B * tpr + B * width
-        pin = device.type == "cuda"
-        host = torch.zeros(n, dtype=torch.int32, pin_memory=pin)
-        return cls(B, tpr, width, host, torch.zeros(n, dtype=torch.int32, device=device))
+        host = dev = None
+        if host_arena is not None and dev_arena is not None:
+            try:
+                host = host_arena.alloc((n,), torch.int32, name=f"step_host_{B}x{tpr}").zero_()
+                dev = dev_arena.alloc((n,), torch.int32, name=f"step_dev_{B}x{tpr}").zero_()
+                host_arena.freeze()
+                dev_arena.freeze()
+            except MemoryError:
+                host = dev = None
+        if host is None:
+            host = torch.zeros(n, dtype=torch.int32, pin_memory=device.type == "cuda")
+            dev = torch.zeros(n, dtype=torch.int32, device=device)
+        return cls(B, tpr, width, host, dev)
 
     def views(self, t: torch.Tensor):
         T = self.B * self.tpr
@@ -75,6 +91,11 @@ class Engine:
         self._phase_streams = None
         self._bufs = {}
         self._out_host = {}
+        # static step inputs (device) and their pinned mirrors + result read-back buffers (host): two small arenas with
+        # the reference's explicit workspace model, so a step's host <-> device traffic touches two allocations only
+        from .workspace import Workspace
+        self.step_arena = Workspace(STEP_ARENA_BYTES, self.device)
+        self.host_arena = Workspace(STEP_ARENA_BYTES, "cpu", pinned=self.device.type == "cuda")
         self._err_host = None                # pinned copy of the device's status words, read back with every step result
         self.h2d_bytes = 0
         self.d2h_bytes = 0
@@ -174,7 +195,7 @@ class Engine:
     def _buffers(self, B: int, tpr: int) -> StepBuffers:
         key = (B, tpr)
         if key not in self._bufs:
-            self._bufs[key] = StepBuffers.create(B, tpr, self.pt_width, self.device)
+            self._bufs[key] = StepBuffers.create(B, tpr, self.pt_width, self.device, self.host_arena, self.step_arena)
         return self._bufs[key]
 
     def _upload(self, buf: StepBuffers, ids, positions, batch_idx, seqs: Seq[Sequence]) -> None:
@@ -382,7 +403,11 @@ class Engine:
         stale data."""
         host = self._out_host.get(key)
         if host is None or host.shape != dev_t.shape or host.dtype != dev_t.dtype:
-            host = torch.empty(dev_t.shape, dtype=dev_t.dtype, pin_memory=self.device.type == "cuda")
+            try:
+                host = self.host_arena.alloc(tuple(dev_t.shape), dev_t.dtype, name=f"result_{key}")
+                self.host_arena.freeze()
+            except MemoryError:
+                host = torch.empty(dev_t.shape, dtype=dev_t.dtype, pin_memory=self.device.type == "cuda")
             self._out_host[key] = host
         host.copy_(dev_t, non_blocking=True)
         if self.device.type == "cuda":

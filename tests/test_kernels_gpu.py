@@ -295,6 +295,32 @@ def test_indexer_prefill_scorer_on_tcgen05(cp, ctx, T):
         assert len(a) == len(b) and len(a ^ b) <= max(2, len(b) // 100), (t, len(a), len(b), len(a ^ b))
 
 
+@pytest.mark.parametrize("T,h", [(100, 8), (257, 4), (4096, 8)])
+def test_head_batched_products_on_tcgen05(T, h):
+    """Prefill absorb (q_nope x W_kn per head, K = 192 taken from the 256-wide head slice of the projection) and value
+    expansion (o x W_v per head) on the persistent tcgen05 GEMM with a per-head operand origin, against torch in fp32."""
+    from slopllm_b200.ops import tcgen05
+    cfg = mini_cfg(num_attention_heads=h)
+    ops = cuda_ops(cfg)
+    g = torch.Generator(device=DEV).manual_seed(T + h)
+    Dn, Dr, Rr, Dv = cfg.qk_nope_head_dim, cfg.qk_rope_head_dim, cfg.kv_lora_rank, cfg.v_head_dim
+    qb = torch.randn(T, h * (Dn + Dr) + 64, device=DEV, generator=g).to(torch.bfloat16)      # wider than the heads (indexer columns)
+    owner = type("L", (), {})()
+    owner.w_kn = (torch.randn(h, Dn, Rr, device=DEV, generator=g) * 0.05).to(torch.bfloat16)
+    q_abs = ops._head_batched_gemm(qb, Dn + Dr, Dn, owner, "w_kn")
+    assert q_abs is not None and owner._w_kn_t.shape == (h * Rr, Dn)
+    q_nope = qb[:, :h * (Dn + Dr)].view(T, h, Dn + Dr)[..., :Dn].float()
+    want = torch.einsum("thd,hdr->thr", q_nope, owner.w_kn.float()).reshape(T, h * Rr)
+    close(q_abs, want, tol=2e-2, what="absorb")
+    o = (torch.randn(T, h, Rr, device=DEV, generator=g) * 0.3).to(torch.bfloat16)
+    w_v = (torch.randn(h, Rr, Dv, device=DEV, generator=g) * 0.05).to(torch.bfloat16)
+    out = ops.v_expand(o, w_v)
+    assert getattr(w_v, "_sl_out_major", None) is not None
+    close(out, torch.einsum("thr,hrv->thv", o.float(), w_v.float()).reshape(T, h * Dv), tol=2e-2, what="v_expand")
+    close(ops.v_expand(o, w_v), out, tol=1e-6, what="second call (kept copy)")
+    tcgen05.check_errors(DEV)
+
+
 @pytest.mark.parametrize("which", ["tiny", "mini"])
 def test_sparse_mla_and_v_expand(which):
     cfg = GlmMoeDsaConfig.tiny() if which == "tiny" else mini_cfg()
