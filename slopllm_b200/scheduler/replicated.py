@@ -62,6 +62,7 @@ class ReplicaChannel:
             dist.broadcast_object_list(payload, src=self.src, group=self.group)
         wire = payload[0]
         if wire["stop"]:
+            self._drop_retired()
             sched._stop.set()
             return
         for i, kind in enumerate(wire["flush"]):
@@ -78,8 +79,11 @@ class ReplicaChannel:
             r = self.live.get(rid)
             if r is not None:
                 r.cancelled = r.cancel_seen = True
-        # a request leaves the table when the scheduler has retired it, not when a finish reason appears: until then a
-        # cancellation of it may still have to travel to the other ranks
+        self._drop_retired()
+
+    def _drop_retired(self) -> None:
+        """A request leaves the table when the scheduler has retired it, not when a finish reason appears: until then a
+        cancellation of it may still have to travel to the other ranks."""
         for rid in [rid for rid, r in self.live.items() if r.retired]:
             del self.live[rid]
 
