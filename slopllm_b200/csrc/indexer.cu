@@ -392,17 +392,23 @@ __global__ void __launch_bounds__(1024) topk_select_kernel(TopkSelectParams p) {
     const float* sc = p.scores + (size_t)t * p.ld_scores;
     const bool vec = (((uintptr_t)sc) & 15) == 0 && p.ld_scores % 4 == 0;      // whole groups of 4 stay inside the row
     const int kk = min(p.top_k, n);
+    // warp w owns keys [lo, hi) in every walk (segments are whole groups of 128 keys)
+    const int seg = ((n + 31) / 32 + 127) / 128 * 128;
+    const int lo = min(n, warp * seg), hi = min(n, lo + seg);
     uint32_t mask = 0;
+    int above24 = 0;                               // last digit's walk: keys of this lane whose upper 24 bits exceed the threshold's
     if (tid == 0) { s_prefix = 0; s_remaining = (uint32_t)kk; }
+    uint32_t* mine = whist[warp];
     for (int shift = 24; shift >= 0; shift -= 8) {
         for (int i = tid; i < 32 * 256; i += 1024) (&whist[0][0])[i] = 0;
         __syncthreads();
         const uint32_t prefix = s_prefix;
-        uint32_t* mine = whist[warp];
         auto visit = [&](bool live, float v) {
             const uint32_t key = order_key(v);
             const bool hit = live && (key & mask) == prefix;
+            if (shift == 0 && live && (key & mask) > prefix) ++above24;
             const unsigned hm = __ballot_sync(0xffffffffu, hit);
+            if (hm == 0) return;                   // warp-uniform: nothing of this group is still a candidate
             if (hit) {
                 const uint32_t bin = (key >> shift) & 255u;
                 const unsigned peers = __match_any_sync(hm, bin);
@@ -412,15 +418,15 @@ __global__ void __launch_bounds__(1024) topk_select_kernel(TopkSelectParams p) {
         };
         // every lane of a warp makes the same number of trips (the visits vote)
         if (vec) {
-            for (int b0 = warp * 128; b0 < n; b0 += 4096) {
+            for (int b0 = lo; b0 < hi; b0 += 128) {
                 const int i0 = b0 + lane * 4;
-                const float4 v = i0 < n ? *reinterpret_cast<const float4*>(sc + i0) : make_float4(0.f, 0.f, 0.f, 0.f);
-                visit(i0 < n, v.x); visit(i0 + 1 < n, v.y); visit(i0 + 2 < n, v.z); visit(i0 + 3 < n, v.w);
+                const float4 v = i0 < hi ? *reinterpret_cast<const float4*>(sc + i0) : make_float4(0.f, 0.f, 0.f, 0.f);
+                visit(i0 < hi, v.x); visit(i0 + 1 < hi, v.y); visit(i0 + 2 < hi, v.z); visit(i0 + 3 < hi, v.w);
             }
         } else {
-            for (int b0 = warp * 32; b0 < n; b0 += 1024) {
+            for (int b0 = lo; b0 < hi; b0 += 32) {
                 const int i = b0 + lane;
-                visit(i < n, i < n ? sc[i] : 0.f);
+                visit(i < hi, i < hi ? sc[i] : 0.f);
             }
         }
         __syncthreads();
@@ -436,17 +442,25 @@ __global__ void __launch_bounds__(1024) topk_select_kernel(TopkSelectParams p) {
     }
     const uint32_t thr = s_prefix;
     const int need_eq = (int)s_remaining;      // how many keys equal to thr are taken (lowest index first)
-    // warp w owns keys [w * seg, (w + 1) * seg)
-    const int seg = ((n + 31) / 32 + 31) / 32 * 32;
-    const int lo = min(n, warp * seg), hi = min(n, lo + seg);
-    int cgt = 0, ceq = 0;
-    for (int i0 = lo; i0 < hi; i0 += 32) {
-        const int i = i0 + lane;
-        const uint32_t key = i < hi ? order_key(sc[i]) : 0u;
-        cgt += __popc(__ballot_sync(0xffffffffu, i < hi && key > thr));
-        ceq += __popc(__ballot_sync(0xffffffffu, i < hi && key == thr));
+    // this warp's keys above / at the threshold: those decided by the upper 24 bits, plus the last digit's private
+    // histogram (it still holds exactly this warp's candidates by low byte)
+    {
+        const int tl = (int)(thr & 255u);
+        int g = above24, e = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int bin = lane * 8 + i;
+            const int c = (int)mine[bin];
+            g += bin > tl ? c : 0;
+            e += bin == tl ? c : 0;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            g += __shfl_xor_sync(0xffffffffu, g, o);
+            e += __shfl_xor_sync(0xffffffffu, e, o);
+        }
+        if (lane == 0) { wgt[warp] = g; weq[warp] = e; }
     }
-    if (lane == 0) { wgt[warp] = cgt; weq[warp] = ceq; }
     __syncthreads();
     int base = 0, eq_used = 0;
     for (int w = 0; w < warp; ++w) {

@@ -308,6 +308,7 @@ class NvlinkComm(Comm):
 
     MAX_ROWS = 32          # token rows served by the fused decode path; larger steps use the bulk path or NCCL
     BULK_ROWS = 8192       # largest prefill chunk the bulk path takes (two bf16 [BULK_ROWS, H] areas per lane and rank)
+    CP_PUSH_ROWS = 8192    # largest step whose context-parallel attention partials are merged through peer memory
 
     def __init__(self, ctx: ParallelContext, cfg=None, region: Optional[SymmetricRegion] = None):
         super().__init__(ctx)
@@ -330,7 +331,12 @@ class NvlinkComm(Comm):
         instead)."""
         from ..config import env_str
         H = cfg.hidden_size
-        cp_shape = (NvlinkComm.MAX_ROWS, cfg.num_attention_heads, cfg.kv_lora_rank) if ctx.cp else None
+        # context parallelism: the attention partials of up to CP_PUSH_ROWS query rows are pushed to the ranks that own their
+        # heads (two halves of [world, rows, heads / world, R] fp32 per rank: 2.1 GB at 8 ranks, 8192 rows, 64 heads);
+        # larger chunks fall back to the library all-to-all
+        from ..config import env_int as _env_int
+        cp_rows = max(NvlinkComm.MAX_ROWS, _env_int("CP_PUSH_ROWS", NvlinkComm.CP_PUSH_ROWS))
+        cp_shape = (cp_rows, cfg.num_attention_heads, cfg.kv_lora_rank) if ctx.cp else None
         gather_bytes = 1 << 20
         bulk_rows = NvlinkComm.bulk_rows_from_env()
         lay = SymmetricRegion.layout(ctx.world, NvlinkComm.MAX_ROWS, H, gather_bytes, cp_shape, bulk_rows)

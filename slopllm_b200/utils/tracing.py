@@ -93,15 +93,24 @@ class OpTimers:
         self.ops = ops
         self.events = defaultdict(list)
         self._orig = {}
-        names = names or [n for n in dir(ops) if not n.startswith("_") and callable(getattr(ops, n, None))
+        self._depth = 0
+        self._others = []
+        self.attach(ops, names)
+
+    def attach(self, obj, names=None, prefix: str = "") -> None:
+        """Time another object's public methods under the same nesting rule (e.g. the communicator next to the ops:
+        a collective that calls a backend op inside counts once, as the collective)."""
+        names = names or [n for n in dir(obj) if not n.startswith("_") and callable(getattr(obj, n, None))
                           and n not in ("name",)]
         for n in names:
-            fn = getattr(ops, n)
+            fn = getattr(obj, n)
             if isinstance(fn, type) or not hasattr(fn, "__call__"):
                 continue
-            self._orig[n] = fn
-            setattr(ops, n, self._wrap(n, fn))
-        self._depth = 0
+            if obj is self.ops:
+                self._orig[n] = fn
+            else:
+                self._others.append((obj, n, fn))
+            setattr(obj, n, self._wrap(prefix + n, fn))
 
     def _wrap(self, name, fn):
         def timed(*a, **k):
@@ -125,6 +134,9 @@ class OpTimers:
         for n, fn in self._orig.items():
             setattr(self.ops, n, fn)
         self._orig.clear()
+        for obj, n, fn in self._others:
+            setattr(obj, n, fn)
+        self._others.clear()
 
     def summary(self):
         if torch.cuda.is_available():

@@ -227,3 +227,56 @@ def test_runtime_library_exports_what_the_python_side_declares():
     if os.path.exists(N.RUNTIME_SO):
         lib = N.runtime()
         assert not [n for n in sorted(declared) if not hasattr(lib, n)]
+
+
+def test_op_timers_attach_counts_a_collective_once():
+    """`OpTimers.attach` times a second object (the communicator) under the same nesting rule: a collective that calls
+    a backend op inside is one entry, the op on its own another; `restore` puts both objects back."""
+    from slopllm_b200.utils.tracing import OpTimers
+
+    class Ops:
+        def combine(self, x):
+            return x + 1
+
+    class Comm:
+        def __init__(self, ops):
+            self.ops = ops
+
+        def cp_merge(self, x):
+            return self.ops.combine(x) * 2
+
+    ops = Ops()
+    comm = Comm(ops)
+    orig_ops, orig_comm = ops.combine.__func__, comm.cp_merge.__func__
+    t = OpTimers(ops)
+    t.attach(comm, ["cp_merge"], prefix="comm.")
+    assert comm.cp_merge(1) == 4 and ops.combine(1) == 2
+    if torch.cuda.is_available():
+        names = {r["op"]: r["calls"] for r in t.summary()}
+        assert names == {"comm.cp_merge": 1, "combine": 1}
+    t.restore()
+    assert ops.combine.__func__ is orig_ops and comm.cp_merge.__func__ is orig_comm
+
+
+def test_engine_step_buffers_live_in_the_workspace_arenas():
+    """The engine's static step inputs, their host mirrors and the result read-back buffers are carved from its two
+    arenas (`runtime/workspace.py`) and frozen; a shape that does not fit falls back to buffers of its own."""
+    from slopllm_b200.config import GlmMoeDsaConfig
+    from slopllm_b200.models.glm_moe_dsa import GlmMoeDsaModel
+    from slopllm_b200.models.weights import random_model
+    from slopllm_b200.runtime import engine as E
+    cfg = GlmMoeDsaConfig.tiny()
+    eng = E.Engine(cfg, GlmMoeDsaModel(cfg, random_model(cfg, 0)), num_pages=8, max_batch=2, max_seq_len=256, cuda_graph=False)
+    buf = eng._buffers(2, 1)
+    lo, hi = eng.step_arena.buffer.data_ptr(), eng.step_arena.buffer.data_ptr() + eng.step_arena.nbytes
+    assert lo <= buf.dev.data_ptr() < hi
+    assert eng.host_arena.buffer.data_ptr() <= buf.host.data_ptr() < eng.host_arena.buffer.data_ptr() + eng.host_arena.nbytes
+    assert buf.dev.data_ptr() in eng.step_arena.frozen and int(buf.dev.abs().sum()) == 0
+    names = [n for n, _, _ in eng.step_arena.layout()]
+    assert "step_dev_2x1" in names
+    s = eng.kv.new_sequence()
+    last, _ = eng.prefill([s], [[1, 2, 3, 4, 5]], chunk_size=64)
+    eng.decode_step([s], last)
+    assert any(n.startswith("result_") for n, _, _ in eng.host_arena.layout())
+    big = E.StepBuffers.create(64, 4, 1 << 20, eng.device, eng.host_arena, eng.step_arena)      # larger than the arena
+    assert not (lo <= big.dev.data_ptr() < hi)
