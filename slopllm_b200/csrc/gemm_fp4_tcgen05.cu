@@ -43,7 +43,7 @@ struct Fp4Tile {
     int b_row0, b_valid;           // first token row, number of valid token rows (<= BN)
     int out_n0, group;             // output column of weight row 0 of the tile, group (expert) for the global scales
     int sfb_tile;                  // scale tile of the token rows (padded row / BN)
-    int pad_;
+    int tab0;                      // column-row table mode: entry of this tile's first token column (see Fp4Params::col_rows)
 };
 
 template <int BN, int PAIR>
@@ -75,11 +75,19 @@ struct Fp4Params {
     // meta.y * ldo, meta = row_meta[m] = {home rank of the row's token, its route slot there} (peer memory, plain stores)
     const int2* row_meta;
     bf16* scatter_base[8];
+    // column-row table (decode MoE): token column c of a tile is stored at output row col_rows[tile.tab0 + c], a negative
+    // entry drops the column.  The token operand can then be the same few rows for every tile (all tokens of the step)
+    // while each expert's tile keeps only the tokens routed to it, or a compact per-expert block whose rows scatter back
+    // to their routes.  bf16 or f32 rows (out_kind).
+    const int* col_rows;
+    // second weight set, used by tiles whose group is negative (the shared expert, stored apart from the expert stack)
+    const uint8_t* sfa2;
+    const float* gA2;
 };
 
 template <int BN, int PAIR>
 __global__ void __launch_bounds__(192) gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                                                       const Fp4Params p) {
+                                                       const __grid_constant__ CUtensorMap tmA2, const Fp4Params p) {
     using Cfg = Fp4Cfg<BN, PAIR>;
     constexpr int STAGES = Cfg::STAGES, NA = Cfg::NA, NBUF = Cfg::NBUF;
     extern __shared__ uint8_t smem_raw[];
@@ -100,6 +108,7 @@ __global__ void __launch_bounds__(192) gemm_fp4_kernel(const __grid_constant__ C
     if (warp == 0 && lane == 0) {
         tc::tma_prefetch_desc(&tmA);
         tc::tma_prefetch_desc(&tmB);
+        tc::tma_prefetch_desc(&tmA2);
         for (int s = 0; s < STAGES; ++s) { tc::mbar_init(&full[s], 1); tc::mbar_init(&empty[s], 1); }
         for (int b = 0; b < 2; ++b) { tc::mbar_init(&tmem_full[b], 1); tc::mbar_init(&tmem_empty[b], 4); }
         tc::mbar_fence_init();
@@ -132,11 +141,13 @@ __global__ void __launch_bounds__(192) gemm_fp4_kernel(const __grid_constant__ C
                     const int s = it % STAGES;
                     if (!tc::mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1)) { atomicExch(p.err, 11); ok = false; break; }
                     tc::mbar_expect_tx(&full[s], Cfg::TX);
-                    tc::tma_load_2d(sA(s, 0), &tmA, &full[s], kb * BKB, t.a_row0);
-                    tc::bulk_load_1d(sSFA(s, 0), p.sfa + ((size_t)t.sfa_blk0 * KT + (size_t)kb * KSTEPS) * 512, Cfg::SF_BYTES, &full[s]);
+                    const CUtensorMap* ta = t.group < 0 ? &tmA2 : &tmA;
+                    const uint8_t* sfa = t.group < 0 ? p.sfa2 : p.sfa;
+                    tc::tma_load_2d(sA(s, 0), ta, &full[s], kb * BKB, t.a_row0);
+                    tc::bulk_load_1d(sSFA(s, 0), sfa + ((size_t)t.sfa_blk0 * KT + (size_t)kb * KSTEPS) * 512, Cfg::SF_BYTES, &full[s]);
                     if (PAIR) {
-                        tc::tma_load_2d(sA(s, 1), &tmA, &full[s], kb * BKB, t.a_row0 + p.pair_rows);
-                        tc::bulk_load_1d(sSFA(s, 1), p.sfa + ((size_t)(t.sfa_blk0 + p.pair_blks) * KT + (size_t)kb * KSTEPS) * 512, Cfg::SF_BYTES,
+                        tc::tma_load_2d(sA(s, 1), ta, &full[s], kb * BKB, t.a_row0 + p.pair_rows);
+                        tc::bulk_load_1d(sSFA(s, 1), sfa + ((size_t)(t.sfa_blk0 + p.pair_blks) * KT + (size_t)kb * KSTEPS) * 512, Cfg::SF_BYTES,
                                          &full[s]);
                     }
                     tc::tma_load_2d(sB(s), &tmB, &full[s], kb * BKB, t.b_row0);
@@ -190,8 +201,9 @@ __global__ void __launch_bounds__(192) gemm_fp4_kernel(const __grid_constant__ C
         struct Pre { Fp4Tile t; float ga, gu; float gb[BN / 32]; unsigned long long dst[BN / 32]; };
         auto prefetch = [&](int tile, Pre& pre) {
             pre.t = p.tiles[tile];
-            pre.ga = PAIR ? __ldg(p.gA + 2 * pre.t.group) : __ldg(p.gA + pre.t.group);
-            pre.gu = PAIR ? __ldg(p.gA + 2 * pre.t.group + 1) : 0.f;
+            const float* ga_p = pre.t.group < 0 ? p.gA2 : p.gA + (PAIR ? 2 : 1) * pre.t.group;
+            pre.ga = __ldg(ga_p);
+            pre.gu = PAIR ? __ldg(ga_p + 1) : 0.f;
 #pragma unroll
             for (int c = 0; c < BN / 32; ++c) {
                 const bool in = c * 32 + lane < pre.t.b_valid;
@@ -200,6 +212,9 @@ __global__ void __launch_bounds__(192) gemm_fp4_kernel(const __grid_constant__ C
                 if (p.row_meta != nullptr && in) {
                     const int2 mt = __ldg(p.row_meta + pre.t.b_row0 + c * 32 + lane);
                     pre.dst[c] = (unsigned long long)(p.scatter_base[mt.x & 7] + (size_t)mt.y * p.ldo);
+                } else if (p.col_rows != nullptr && in) {
+                    const int row = __ldg(p.col_rows + pre.t.tab0 + c * 32 + lane);
+                    if (row >= 0) pre.dst[c] = (unsigned long long)((char*)p.out + (size_t)row * p.ldo * (p.out_kind == 1 ? 4 : 2));
                 }
             }
         };
@@ -230,7 +245,23 @@ __global__ void __launch_bounds__(192) gemm_fp4_kernel(const __grid_constant__ C
                     if (PAIR) tc::tmem_ld_32x32(t_acc + BN + c0, r1);
                     tc::tmem_ld_wait();
                     const int lim = min(32, t.b_valid - c0);
-                    if (p.out_kind == 1) {
+                    if (p.col_rows != nullptr) {
+                        const unsigned long long my_dst = cur.dst[c];    // lane i holds where token column c0 + i goes (0: nowhere)
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            const float gb = __shfl_sync(0xffffffffu, my_gb, i);
+                            const unsigned long long row = __shfl_sync(0xffffffffu, my_dst, i);
+                            float v = __uint_as_float(r0[i]) * ga * gb;
+                            if (PAIR) {
+                                const float u = __uint_as_float(r1[i]) * gu * gb;
+                                v = v / (1.f + __expf(-v)) * u;
+                            }
+                            if (i < lim && row != 0ull) {
+                                if (p.out_kind == 1) reinterpret_cast<float*>(row)[n] = v;
+                                else reinterpret_cast<bf16*>(row)[n] = __float2bfloat16(v);
+                            }
+                        }
+                    } else if (p.out_kind == 1) {
                         float* dst = (float*)p.out + (size_t)(t.b_row0 + c0) * p.ldo + n;
 #pragma unroll
                         for (int i = 0; i < 32; ++i) {
@@ -295,11 +326,15 @@ int fp4_sm_count() {
 }
 
 template <int BN, int PAIR>
-int launch_fp4(const void* W, int w_rows, const void* X, int x_rows, const Fp4Params& p, int max_tiles, cudaStream_t s) {
+int launch_fp4(const void* W, int w_rows, const void* X, int x_rows, const Fp4Params& p, int max_tiles, cudaStream_t s,
+               const void* W2 = nullptr, int w2_rows = 0) {
     using Cfg = Fp4Cfg<BN, PAIR>;
-    CUtensorMap tmA, tmB;
+    CUtensorMap tmA, tmB, tmA2;
     const uint64_t kb = (uint64_t)p.K / 2;
     int rc = make_tmap_2d(&tmA, W, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)w_rows, kb, kb, BM, BKB);
+    if (rc) return rc;
+    // tiles of a negative group read the second weight set; without one the map repeats the first (never used)
+    rc = make_tmap_2d(&tmA2, W2 ? W2 : W, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)(W2 ? w2_rows : w_rows), kb, kb, BM, BKB);
     if (rc) return rc;
     rc = make_tmap_2d(&tmB, X, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)x_rows, kb, kb, BN, BKB);
     if (rc) return rc;
@@ -310,7 +345,7 @@ int launch_fp4(const void* W, int w_rows, const void* X, int x_rows, const Fp4Pa
         attr_set = true;
     }
     const int grid = std::min(max_tiles, fp4_sm_count());
-    sl_launch(kern, grid, 192, Cfg::SMEM, s, tmA, tmB, p);
+    sl_launch(kern, grid, 192, Cfg::SMEM, s, tmA, tmB, tmA2, p);
     return (int)cudaGetLastError();
 }
 
@@ -352,7 +387,7 @@ __global__ void __launch_bounds__(256) fp4_build_tiles_kernel(Fp4Tile* __restric
             t.out_n0 = m * BM;
             t.group = g;
             t.sfb_tile = pad[g] / bn + b;
-            t.pad_ = 0;
+            t.tab0 = 0;
             tiles[at] = t;
         }
     }
@@ -516,12 +551,147 @@ __global__ void __launch_bounds__(256) nvfp4_gather_rows_kernel(const GatherPara
 }
 
 template <int PAIR>
-int dispatch_bn(int bn, const void* W, int w_rows, const void* X, int x_rows, const Fp4Params& p, int max_tiles, cudaStream_t s) {
+int dispatch_bn(int bn, const void* W, int w_rows, const void* X, int x_rows, const Fp4Params& p, int max_tiles, cudaStream_t s,
+                const void* W2 = nullptr, int w2_rows = 0) {
     switch (bn) {
-        case 32: return launch_fp4<32, PAIR>(W, w_rows, X, x_rows, p, max_tiles, s);
-        case 64: return launch_fp4<64, PAIR>(W, w_rows, X, x_rows, p, max_tiles, s);
-        case 128: return launch_fp4<128, PAIR>(W, w_rows, X, x_rows, p, max_tiles, s);
+        case 32: return launch_fp4<32, PAIR>(W, w_rows, X, x_rows, p, max_tiles, s, W2, w2_rows);
+        case 64: return launch_fp4<64, PAIR>(W, w_rows, X, x_rows, p, max_tiles, s, W2, w2_rows);
+        case 128: return launch_fp4<128, PAIR>(W, w_rows, X, x_rows, p, max_tiles, s, W2, w2_rows);
         default: return -1;
+    }
+}
+
+// ---- decode-time MoE: plan and tile tables for up to 32 token rows ---------------------------------------------------------
+// Every expert that some token chose gets a slot (in order of its first route); slot s owns rows [32 s, 32 s + 32) of the
+// activation buffer, one per token routed to it (in token order).  The shared expert, if any, takes the slot after the
+// last routed one with all T tokens.
+//   gate/up GEMM  tiles {slot, 128-row block of I}: token operand = ALL T token rows (the same for every tile);
+//                 tab1[32 s + t] = 32 s + (rank of token t among the slot's tokens), or -1 if t did not choose it
+//   down GEMM     tiles {slot, 128-row block of H}: token operand = the slot's 32 activation rows;
+//                 tab2[32 s + j] = route of the slot's j-th token (t * top_k + choice; T * top_k + t for the shared expert)
+// so neither GEMM needs its rows sorted or gathered: the first drops the columns a slot does not own, the second scatters
+// its columns back to per-route rows.  One block of 256 threads; `sh` = 10 E + 16 ints.
+struct Fp4DecodePlan {
+    const int* ids;                 // [T, top_k] expert ids
+    int T, top_k, expert_offset, num_local, has_shared;
+    int I, H;                       // expert intermediate / hidden size (multiples of 128)
+    Fp4Tile* tiles1; int* ntiles1;  // gate/up tiles, at most (max_slots + 1) * I / 128
+    Fp4Tile* tiles2; int* ntiles2;  // down tiles, at most (max_slots + 1) * H / 128
+    int* tab1; int* tab2;           // [(max_slots + 1) * 32]
+    int* num_rows;                  // activation rows in use: 32 * slots
+    int max_slots;
+};
+
+__global__ void __launch_bounds__(256) fp4_decode_plan_kernel(const Fp4DecodePlan p) {
+    pdl_grid_sync();
+    extern __shared__ int sh[];
+    const int E = p.num_local, n = p.T * p.top_k;
+    int* cnt = sh;                                 // [8][E] routes of expert e in warp w of the current pass
+    int* run = cnt + 8 * E;                        // [E] routes of expert e in earlier passes
+    int* slot_of = run + E;                        // [E] slot of expert e (-1: untouched)
+    __shared__ int s_slots;
+    __shared__ int wcnt[8];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    for (int i = tid; i < 9 * E; i += 256) sh[i] = 0;
+    for (int i = tid; i < E; i += 256) slot_of[i] = -1;
+    for (int i = tid; i < (p.max_slots + 1) * 32; i += 256) { p.tab1[i] = -1; p.tab2[i] = -1; }
+    if (tid == 0) s_slots = 0;
+    __syncthreads();
+    for (int base = 0; base < n; base += 256) {
+        const int r = base + tid;
+        int e = -1;
+        if (r < n) {
+            const int le = p.ids[r] - p.expert_offset;
+            e = (le >= 0 && le < E) ? le : -1;
+        }
+        const unsigned same = __match_any_sync(0xffffffffu, e);
+        const int rank_in_warp = __popc(same & ((1u << lane) - 1));
+        if (e >= 0 && rank_in_warp == 0) cnt[warp * E + e] = __popc(same);
+        __syncthreads();
+        int before = -1;
+        if (e >= 0) {
+            before = run[e] + rank_in_warp;
+            for (int w = 0; w < warp; ++w) before += cnt[w * E + e];
+        }
+        const bool first = before == 0;            // the expert's first route claims its slot, in route order
+        const unsigned m = __ballot_sync(0xffffffffu, first);
+        if (lane == 0) wcnt[warp] = __popc(m);
+        __syncthreads();
+        int slot = s_slots, total = 0;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) {
+            if (w < warp) slot += wcnt[w];
+            total += wcnt[w];
+        }
+        slot += __popc(m & ((1u << lane) - 1));
+        if (first && slot < p.max_slots) slot_of[e] = slot;
+        __syncthreads();
+        if (before >= 0 && before < 32) {
+            const int sl = slot_of[e];
+            if (sl >= 0) {
+                const int t = r / p.top_k;
+                p.tab1[sl * 32 + t] = sl * 32 + before;
+                p.tab2[sl * 32 + before] = r;
+            }
+        }
+        if (tid == 0) s_slots = min(p.max_slots, s_slots + total);
+        __syncthreads();
+        for (int i = tid; i < E; i += 256) {
+            int c = 0;
+#pragma unroll
+            for (int w = 0; w < 8; ++w) { c += cnt[w * E + i]; cnt[w * E + i] = 0; }
+            run[i] += c;
+        }
+        __syncthreads();
+    }
+    const int slots = s_slots;
+    const int all = slots + (p.has_shared ? 1 : 0);
+    if (p.has_shared) {
+        for (int t = tid; t < p.T; t += 256) {
+            p.tab1[slots * 32 + t] = slots * 32 + t;
+            p.tab2[slots * 32 + t] = n + t;
+        }
+    }
+    const int mt1 = p.I / BM, mt2 = p.H / BM;
+    // slot -> expert: the inverse of slot_of, built in shared memory on top of cnt (free by now)
+    int* exp_of = cnt;
+    for (int e = tid; e < E; e += 256)
+        if (slot_of[e] >= 0) exp_of[slot_of[e]] = e;
+    __syncthreads();
+    for (int i = tid; i < all * mt1; i += 256) {
+        const int sl = i / mt1, m = i % mt1;
+        const bool shd = sl >= slots;
+        const int e = shd ? 0 : exp_of[sl];
+        Fp4Tile t;
+        t.a_row0 = e * 2 * p.I + m * BM;           // gate rows; the up rows follow I rows later
+        t.sfa_blk0 = e * (2 * p.I / BM) + m;
+        t.b_row0 = 0;
+        t.b_valid = p.T;
+        t.out_n0 = m * BM;
+        t.group = shd ? -1 : e;
+        t.sfb_tile = 0;
+        t.tab0 = sl * 32;
+        p.tiles1[i] = t;
+    }
+    for (int i = tid; i < all * mt2; i += 256) {
+        const int sl = i / mt2, m = i % mt2;
+        const bool shd = sl >= slots;
+        const int e = shd ? 0 : exp_of[sl];
+        Fp4Tile t;
+        t.a_row0 = e * p.H + m * BM;
+        t.sfa_blk0 = e * (p.H / BM) + m;
+        t.b_row0 = sl * 32;
+        t.b_valid = shd ? p.T : min(32, run[e]);
+        t.out_n0 = m * BM;
+        t.group = shd ? -1 : e;
+        t.sfb_tile = sl;
+        t.tab0 = sl * 32;
+        p.tiles2[i] = t;
+    }
+    if (tid == 0) {
+        *p.ntiles1 = all * mt1;
+        *p.ntiles2 = all * mt2;
+        *p.num_rows = all * 32;
     }
 }
 
@@ -563,6 +733,40 @@ SL_API int sl_gemm_fp4_tcgen05(const void* W, const void* sfa, const void* gA, i
     p.ldo = ldo; p.out_kind = out_kind; p.pair_rows = pair_rows; p.pair_blks = pair_rows / BM;
     p.tiles = (const Fp4Tile*)tiles; p.num_tiles = (const int*)num_tiles; p.err = (int*)err;
     return pair_rows > 0 ? dispatch_bn<1>(bn, W, w_rows, X, x_rows, p, max_tiles, s) : dispatch_bn<0>(bn, W, w_rows, X, x_rows, p, max_tiles, s);
+}
+
+// Plan + tile tables of the decode-time MoE layer on this kernel (see fp4_decode_plan_kernel).  T <= 32, T * top_k <= 512,
+// num_local <= 1024; `max_slots` bounds the experts that can be touched (min(num_local, T * top_k)).
+SL_API int sl_fp4_decode_plan(const void* ids, int T, int top_k, int expert_offset, int num_local, int has_shared, int I, int H,
+                              void* tiles1, void* ntiles1, void* tiles2, void* ntiles2, void* tab1, void* tab2, void* num_rows,
+                              int max_slots, cudaStream_t s) {
+    if (T <= 0) return 0;
+    if (T > 32 || T * top_k > 512 || num_local < 1 || num_local > 1024 || I % BM != 0 || H % BM != 0 || max_slots < 1) return -1;
+    Fp4DecodePlan p{(const int*)ids, T, top_k, expert_offset, num_local, has_shared, I, H, (Fp4Tile*)tiles1, (int*)ntiles1,
+                    (Fp4Tile*)tiles2, (int*)ntiles2, (int*)tab1, (int*)tab2, (int*)num_rows, max_slots};
+    const size_t smem = (size_t)(10 * num_local + 16) * sizeof(int);
+    if (smem > 48 * 1024) return -1;
+    sl_launch(fp4_decode_plan_kernel, 1, 256, smem, s, p);
+    return (int)cudaGetLastError();
+}
+
+// The product with the column-row table epilogue (decode MoE): token column c of a tile goes to output row
+// col_rows[tile.tab0 + c] (bf16 or f32 rows of `ldo` elements; negative: dropped).  Tiles of a negative group take the
+// second weight set (W2 / sfa2 / gA2: the shared expert).
+SL_API int sl_gemm_fp4_tcgen05_tab(const void* W, const void* sfa, const void* gA, int w_rows, const void* W2, const void* sfa2,
+                                   const void* gA2, int w2_rows, const void* X, const void* sfb, const void* gB, int x_rows,
+                                   void* out, int ldo, int out_kind, const void* col_rows, int K, int pair_rows, int bn,
+                                   const void* tiles, const void* num_tiles, int max_tiles, void* err, cudaStream_t s) {
+    if (w_rows <= 0 || x_rows <= 0 || max_tiles <= 0) return 0;
+    if (K % 256 != 0 || K <= 0 || pair_rows % BM != 0 || col_rows == nullptr || out == nullptr) return -1;
+    Fp4Params p{};
+    p.sfa = (const uint8_t*)sfa; p.sfb = (const uint8_t*)sfb; p.gA = (const float*)gA; p.gB = (const float*)gB; p.out = out; p.K = K;
+    p.ldo = ldo; p.out_kind = out_kind; p.pair_rows = pair_rows; p.pair_blks = pair_rows / BM;
+    p.tiles = (const Fp4Tile*)tiles; p.num_tiles = (const int*)num_tiles; p.err = (int*)err;
+    p.col_rows = (const int*)col_rows;
+    p.sfa2 = (const uint8_t*)(sfa2 ? sfa2 : sfa); p.gA2 = (const float*)(gA2 ? gA2 : gA);
+    return pair_rows > 0 ? dispatch_bn<1>(bn, W, w_rows, X, x_rows, p, max_tiles, s, W2, w2_rows)
+                         : dispatch_bn<0>(bn, W, w_rows, X, x_rows, p, max_tiles, s, W2, w2_rows);
 }
 
 // The same product with the expert-parallel combine epilogue: bf16 output row m goes to

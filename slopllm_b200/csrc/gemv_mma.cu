@@ -637,6 +637,19 @@ int pick_ksplit(int K, int min_groups_per_warp) {
 
 }  // namespace
 
+// out[t, :] = sum_j wts[t, j] * y_route[t * top_k + j, :] (+ y_route[T * top_k + t, :] for the shared expert), fp32, or
+// pushed to every rank's receive slot (producer half of the fused all-reduce): the last stage of the decode MoE layer on
+// its own, for callers that computed `y_route` with other kernels (the block-scaled FP4 GEMMs).
+SL_API int sl_moe_route_reduce(const void* y_route, const void* ids, const void* wts, int T, int top_k, int H, int expert_offset,
+                               int num_local, int has_shared, void* out, const PushCtx* push, cudaStream_t s) {
+    if (T == 0) return 0;
+    if (push != nullptr && (T > push->slot_rows || H > push->row_len)) return -1;
+    if (push == nullptr && out == nullptr) return -1;
+    sl_launch(moe_route_reduce_kernel, dim3((H + 255) / 256, T), 256, 0, s, (const float*)y_route, (const int*)ids, (const float*)wts, T,
+              top_k, H, expert_offset, num_local, has_shared, (float*)out, push ? 1 : 0, push ? *push : PushCtx{});
+    return (int)cudaGetLastError();
+}
+
 struct MoeGroupedArgs {
     const void* x; int ldx;
     const void* ids; const void* wts;
@@ -721,6 +734,7 @@ SL_API int sl_moe_grouped_mma(const MoeGroupedArgs* a, const MoeRouterArgs* r, c
         sl_launch(moe_plan_kernel, 1, 256, smem, s, pv, (const int*)a->ids, a->T, a->top_k,
                   a->expert_offset, a->num_local, has_shared, a->max_items);
     }
+    if (a->w13 == nullptr) return (int)cudaGetLastError();      // routing + plan only (the expert GEMMs run elsewhere)
     const int tpad = (a->T + 7) / 8 * 8;
     const int units = tpad * (a->H / 8);
     if (!a->xp_ready && !xp_done)

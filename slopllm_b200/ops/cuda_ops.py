@@ -58,6 +58,7 @@ class CudaOps:
         # conversion rate of the CUDA cores just like the five-launch path, which it does not yet beat below 32 rows
         self._persist_moe = env_str("MOE_PERSIST") == "1"
         self._fused_attn_out = env_str("FUSED_ATTN_OUT") != "0"     # merge of the key splits inside the value expansion
+        self._fp4_decode_force = env_str("MOE_FP4_DECODE")          # "0" / "1": never / always the FP4 GEMMs for decode-sized MoE
         self._persist_gsub = 0         # gate/up sub-tiles per tile of the persistent MoE kernel (0: the kernel's default)
         self._persist_trace = None     # u64 [SMs, 96, 4] tile timeline, filled when set (profiling)
 
@@ -642,8 +643,116 @@ class CudaOps:
             self._counters[key] = t
         return t
 
+    def _route_fused(self, x, lw):
+        """(ids, wts) of up to 32 token rows from the fused router kernel alone (router product + grouped top-k in one
+        launch); falls back to the two-launch `route` for shapes that kernel does not take."""
+        T, H = x.shape
+        c = self.cfg
+        k, E = c.num_experts_per_tok, lw.router_w.shape[0]
+        if not (T <= DECODE_MAX_T and H % 256 == 0 and E <= 512 and x.stride(-1) == 1 and x.stride(0) % 8 == 0
+                and lw.router_w.dtype == torch.bfloat16 and T * k <= 480):
+            return self.route(x, lw)
+        dev = x.device
+        ids = torch.empty(T, k, dtype=torch.int32, device=dev)
+        wts = torch.empty(T, k, dtype=torch.float32, device=dev)
+        logits = torch.empty(T, E, dtype=torch.float32, device=dev)
+        max_items = T * k + (T + 7) // 8
+        plan = torch.empty(max_items * 9 + 1, dtype=torch.int32, device=dev)
+        rargs = N.MoeRouterArgs(router_w=lw.router_w.data_ptr(), bias=N.ptr(lw.router_bias), E=E, n_group=c.n_group,
+                                topk_group=c.topk_group, norm=int(c.norm_topk_prob), scale=float(c.routed_scaling_factor),
+                                slabs=logits.data_ptr(), counter=self._zero_counter(dev).data_ptr())
+        a = N.MoeGroupedArgs(x=x.data_ptr(), ldx=x.stride(0), ids=ids.data_ptr(), wts=wts.data_ptr(), T=T, top_k=k, H=H,
+                             I=lw.experts.inter, expert_offset=lw.experts.expert_offset, num_local=lw.experts.num_experts,
+                             plan=plan.data_ptr(), max_items=max_items, xp_ready=1)
+        try:
+            N.call("sl_moe_grouped_mma", C.byref(a), C.byref(rargs), None, N.stream())
+        except N.NativeError:
+            return self.route(x, lw)
+        return ids, wts
+
+    # -- decode MoE on the block-scaled FP4 tensor-core GEMMs -----------------------------------------------------
+    FP4_DECODE_MIN_WORK = 16384       # token rows x expert intermediate size from which the FP4 form streams faster
+
+    def _fp4_decode_ok(self, T: int, lw) -> bool:
+        """The weight-streaming kernels expand FP4 -> f16 on the CUDA cores, which bounds them near 3.3 TB/s of weights
+        per GPU; the tcgen05 kind::mxf4nvf4 GEMMs read the packed weights at the HBM rate but cost six launches and 4-bit
+        activations.  They win once the step streams enough bytes per expert (whole layer in a CUDA graph, streaming ->
+        FP4): TP 1: 356 -> 303 us at 8 rows, 635 -> 481 at 16, 1011 -> 717 at 32; TP 2: equal at 8, 350 -> 285 at 16,
+        543 -> 417 at 32; TP 4: 303 -> 289 at 32 and behind below; TP 8: behind at every size (187 vs 246 us at 32 rows).
+        SLOPLLM_B200_MOE_FP4_DECODE=0 / 1 forces the choice."""
+        from . import gemm
+        ex = lw.experts
+        if T < 2 or T > DECODE_MAX_T or not gemm.fp4_moe_ok(ex, self.cfg.hidden_size):
+            return False
+        if lw.shared is not None and (lw.shared.inter != ex.inter or not lw.shared.is_nvfp4):
+            return False
+        if T * self.cfg.num_experts_per_tok > 512 or ex.num_experts > 1024:
+            return False
+        force = self._fp4_decode_force
+        if force in ("0", "1"):
+            return force == "1"
+        return T * ex.inter >= self.FP4_DECODE_MIN_WORK
+
+    def _moe_fp4_decode(self, x, lw, ids, wts, sink=None):
+        """Expert MLP of a few token rows on `tcgen05.mma.kind::mxf4nvf4` (W4A4): the token rows are quantised once and are
+        the narrow operand of EVERY expert tile of the gate/up GEMM, whose epilogue keeps the tokens routed to that expert;
+        the activations land in 32-row blocks per touched expert, are quantised, and the down GEMM's epilogue scatters its
+        columns to per-route rows, which the weighted reduce (+ push) sums.  No sort, no gather."""
+        from . import fp4, gemm, tcgen05
+        ex, sh = lw.experts, lw.shared
+        T, H = x.shape
+        k = ids.shape[1]
+        I, E = ex.inter, ex.num_experts
+        dev = x.device
+        sf13, sf2 = gemm._sf_tiles_of(ex)
+        ssf13, ssf2 = gemm._sf_tiles_of(sh) if sh is not None else (None, None)
+        max_slots = min(E, T * k)
+        rows = (max_slots + 1) * 32
+        tb = N.kernels().sl_fp4_tile_bytes()
+        mt1, mt2 = (max_slots + 1) * (I // 128), (max_slots + 1) * (H // 128)
+        tiles1 = torch.empty(mt1 * tb, dtype=torch.uint8, device=dev)
+        tiles2 = torch.empty(mt2 * tb, dtype=torch.uint8, device=dev)
+        meta = torch.empty(3, dtype=torch.int32, device=dev)                  # tiles of each GEMM, activation rows in use
+        tab1 = torch.empty(rows, dtype=torch.int32, device=dev)
+        tab2 = torch.empty(rows, dtype=torch.int32, device=dev)
+        ids = ids.to(torch.int32).contiguous()
+        N.call("sl_fp4_decode_plan", ids.data_ptr(), T, k, ex.expert_offset, E, int(sh is not None), I, H, tiles1.data_ptr(),
+               meta.data_ptr(), tiles2.data_ptr(), meta.data_ptr() + 4, tab1.data_ptr(), tab2.data_ptr(), meta.data_ptr() + 8,
+               max_slots, N.stream())
+        xq, sfx, gx = fp4.quantize_rows(self._bf16(x), bn=32)
+        err = tcgen05.error_flag(dev).data_ptr()
+        act = torch.empty(rows, I, dtype=torch.bfloat16, device=dev)
+        g13 = ex.g13.to(torch.float32).contiguous()
+        N.call("sl_gemm_fp4_tcgen05_tab", ex.w13.data_ptr(), sf13.data_ptr(), g13.data_ptr(), E * 2 * I,
+               N.ptr(sh.w13) if sh is not None else 0, N.ptr(ssf13), N.ptr(sh.g13) if sh is not None else 0, 2 * I,
+               xq.data_ptr(), sfx.data_ptr(), gx.data_ptr(), T, act.data_ptr(), I, 0, tab1.data_ptr(), H, I, 32,
+               tiles1.data_ptr(), meta.data_ptr(), mt1, err, N.stream())
+        aq, sfa, ga = fp4.quantize_rows(act, bn=32, num_rows=meta[2:3])
+        routes = T * k + (T if sh is not None else 0)
+        y_route = torch.empty(routes, H, dtype=torch.float32, device=dev)
+        g2 = ex.g2.to(torch.float32).contiguous()
+        N.call("sl_gemm_fp4_tcgen05_tab", ex.w2.data_ptr(), sf2.data_ptr(), g2.data_ptr(), E * H,
+               N.ptr(sh.w2) if sh is not None else 0, N.ptr(ssf2), N.ptr(sh.g2) if sh is not None else 0, H,
+               aq.data_ptr(), sfa.data_ptr(), ga.data_ptr(), rows, y_route.data_ptr(), H, 1, tab2.data_ptr(), I, 0, 32,
+               tiles2.data_ptr(), meta.data_ptr() + 4, mt2, err, N.stream())
+        wts = wts.to(torch.float32).contiguous()
+        if sink is not None:
+            sink.pushed_rows = T
+            N.call("sl_moe_route_reduce", y_route.data_ptr(), ids.data_ptr(), wts.data_ptr(), T, k, H, ex.expert_offset, E,
+                   int(sh is not None), 0, C.byref(sink.push), N.stream())
+            return sink
+        out = torch.empty(T, H, dtype=torch.float32, device=dev)
+        N.call("sl_moe_route_reduce", y_route.data_ptr(), ids.data_ptr(), wts.data_ptr(), T, k, H, ex.expert_offset, E,
+               int(sh is not None), out.data_ptr(), 0, N.stream())
+        return out
+
     def moe_tp(self, x, lw, sink=None):
         T, H = x.shape
+        if (x.is_cuda and lw.experts.is_nvfp4 and lw.router_w.dtype == torch.bfloat16 and not self._persist_moe
+                and self._fp4_decode_ok(T, lw)):
+            x = self._bf16(x)
+            ids, wts = self._route_fused(x, lw)
+            return self._moe_fp4_decode(x, lw, ids, wts, sink)
         fused_ok = (T <= DECODE_MAX_T and lw.experts.is_nvfp4 and H % 256 == 0 and lw.experts.inter % 128 == 0
                     and T * self.cfg.num_experts_per_tok <= 480 and lw.router_w.dtype == torch.bfloat16
                     and (lw.shared is None or lw.shared.inter == lw.experts.inter))

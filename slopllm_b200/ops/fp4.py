@@ -24,6 +24,8 @@ N._SIGS.update({
     "sl_nvfp4_gather_rows": [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp, vp, i32, i32, vp],
     "sl_nvfp4_quantize_rows": [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp, vp, i32, i32, vp, vp],
     "sl_gemm_fp4_tcgen05_scatter": [vp, vp, vp, i32, vp, vp, vp, i32, vp, vp, i32, i32, i32, i32, vp, vp, i32, vp, vp],
+    "sl_fp4_decode_plan": [vp, i32, i32, i32, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp, i32, vp],
+    "sl_gemm_fp4_tcgen05_tab": [vp, vp, vp, i32, vp, vp, vp, i32, vp, vp, vp, i32, vp, i32, i32, vp, i32, i32, i32, vp, vp, i32, vp, vp],
 })
 
 OUT_BF16, OUT_F32 = 0, 1

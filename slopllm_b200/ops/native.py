@@ -225,6 +225,7 @@ _SIGS = {
     "sl_moe_persist": [C.POINTER(MoePersistArgs), vp, vp],
     "sl_moe_persist_ok": [i32, i32, i32, i32, i32, i32, i32],
     "sl_permute_x": [vp, vp, i32, i32, i32, vp],
+    "sl_moe_route_reduce": [vp, vp, vp, i32, i32, i32, i32, i32, i32, vp, vp, vp],
     "sl_linear_nvfp4_mma": [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp],
     "sl_linear_smallT_bf16_tcgen05": [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp, vp, i32, vp],
     "sl_grouped_gemm_bf16_tcgen05": [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, vp, vp, i32, vp, i32, vp],

@@ -338,6 +338,12 @@ class NvlinkComm(Comm):
         cp_rows = max(NvlinkComm.MAX_ROWS, _env_int("CP_PUSH_ROWS", NvlinkComm.CP_PUSH_ROWS))
         cp_shape = (cp_rows, cfg.num_attention_heads, cfg.kv_lora_rank) if ctx.cp else None
         gather_bytes = 1 << 20
+        if ctx.cp:
+            # the two all-gathers of a context-parallel layer at prefill size: candidate scores [rows, top_k] fp32 and the
+            # packed query parts [rows, heads / world, R + rope] bf16 (two halves of `world` slots each: 1.2 GB at 8 ranks)
+            hl = max(1, cfg.num_attention_heads // ctx.world)
+            per_row = max(4 * cfg.index_topk, 2 * hl * (cfg.kv_lora_rank + cfg.qk_rope_head_dim) + 32)
+            gather_bytes = max(gather_bytes, (cp_rows * per_row + 255) // 256 * 256)
         bulk_rows = NvlinkComm.bulk_rows_from_env()
         lay = SymmetricRegion.layout(ctx.world, NvlinkComm.MAX_ROWS, H, gather_bytes, cp_shape, bulk_rows)
         buf, ptrs, keep = symmetric_alloc(ctx, lay["total"])

@@ -444,6 +444,7 @@ def test_moe_fused_router_glm5_routing(T):
     cfg = mini_cfg(hidden_size=1024, moe_intermediate_size=256, n_routed_experts=256, num_experts_per_tok=8, n_group=8,
                    topk_group=4)
     ops, ref = cuda_ops(cfg), RefOps(cfg)
+    ops._fp4_decode_force = "0"                       # this test pins the weight-streaming path (16-bit activations)
     lw = random_layer(cfg, 1, 0, DEV, torch.bfloat16)
     x = torch.randn(T, cfg.hidden_size, device=DEV, generator=torch.Generator(device=DEV).manual_seed(T)).to(torch.bfloat16)
     fused = ops.moe_tp(x, lw)
@@ -473,6 +474,41 @@ def test_moe_router_plan_shapes(T, H, E, k):
     assert int(ops._zero_counter(x.device).item()) == 0
 
 
+@pytest.mark.parametrize("T,H,I,E,k,shared", [(8, 1024, 256, 16, 4, True), (32, 2048, 512, 64, 8, True), (2, 1024, 256, 8, 2, False),
+                                              (19, 6144, 256, 256, 8, True), (32, 1024, 256, 8, 8, True)])
+def test_moe_decode_on_fp4_gemms(T, H, I, E, k, shared, monkeypatch):
+    """Decode-sized MoE on the block-scaled FP4 GEMMs (all tokens as the narrow operand of every expert tile, column-row
+    tables instead of sort / gather, shared expert from a second weight set) against the fp32 definition with emulated
+    4-bit activations, and against the weight-streaming path within the activation quantisation error."""
+    from slopllm_b200.ops import gemm
+    monkeypatch.setattr(gemm, "MOE_A4", True)
+    cfg = mini_cfg(hidden_size=H, moe_intermediate_size=I, n_routed_experts=E, num_experts_per_tok=k, n_group=1, topk_group=1,
+                   n_shared_experts=1 if shared else 0)
+    ops, ref = cuda_ops(cfg), RefOps(cfg)
+    lw = random_layer(cfg, 1, 0, DEV, torch.bfloat16)
+    x = torch.randn(T, H, device=DEV, generator=torch.Generator(device=DEV).manual_seed(T + E)).to(torch.bfloat16)
+    ids, wts = ops.route(x, lw)
+    ops._fp4_decode_force = "1"
+    assert ops._fp4_decode_ok(T, lw)
+    got = ops._moe_fp4_decode(x, lw, ids, wts)
+    from slopllm_b200.ops import tcgen05
+    tcgen05.check_errors(DEV)
+    stream = ops._moe_small(x, lw.experts, lw.shared, ids, wts)
+    rel = float((got - stream).norm() / stream.norm())
+    assert rel < 0.2, rel                                  # 4-bit activations against 16-bit ones
+    want = R.moe_experts(x.float(), lw.experts, ids, wts, a4=True)
+    if lw.shared is not None:
+        want = want + R.moe_experts(x.float(), lw.shared, torch.zeros(T, 1, dtype=torch.int32, device=DEV),
+                                    torch.ones(T, 1, device=DEV), a4=True)
+    rel = float((got - want).norm() / want.norm())
+    assert rel < 0.05, rel
+    # through the public op, twice (the second call finds used scratch)
+    a = ops.moe_tp(x, lw)
+    b = ops.moe_tp(x, lw)
+    assert torch.equal(a, b)
+    close(a, got, tol=2e-3, what="public op (router in the fused kernel) vs given routes")
+
+
 @pytest.mark.parametrize("T,H,I,E,k,ng,tg", [
     (1, 1024, 256, 256, 8, 8, 4), (8, 1024, 256, 256, 8, 8, 4), (32, 1024, 256, 256, 8, 8, 4),
     (5, 2048, 512, 16, 4, 4, 2), (19, 2048, 1024, 16, 4, 1, 1), (8, 3072, 128, 32, 4, 1, 1),
@@ -483,6 +519,7 @@ def test_moe_persistent_kernel_matches_five_launch_path(T, H, I, E, k, ng, tg):
     cfg = mini_cfg(hidden_size=H, moe_intermediate_size=I, n_routed_experts=E, num_experts_per_tok=k, n_group=ng, topk_group=tg)
     ops, ref = cuda_ops(cfg), RefOps(cfg)
     ops._persist_moe = True
+    ops._fp4_decode_force = "0"                       # both forms compared here keep 16-bit activations
     lw = random_layer(cfg, 1, 0, DEV, torch.bfloat16)
     x = torch.randn(T, H, device=DEV, generator=torch.Generator(device=DEV).manual_seed(T)).to(torch.bfloat16)
     fused = ops.moe_tp(x, lw)
