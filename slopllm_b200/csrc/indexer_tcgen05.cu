@@ -36,6 +36,20 @@ constexpr int RAW_BYTES = 2 * PAGE_BYTES;          // 16896
 constexpr int THREADS = 14 * 32;
 constexpr int EPI_WARP0 = 6, EPI_WARPS = 8;
 
+// packed pairs of fp32 in one 64-bit register and their fused multiply-add (two lanes per instruction)
+__device__ __forceinline__ unsigned long long pack2(float a, float b) {
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+    return r;
+}
+__device__ __forceinline__ unsigned long long fma2(unsigned long long a, unsigned long long b, unsigned long long c) {
+    unsigned long long r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+__device__ __forceinline__ float lo2(unsigned long long v) { return __uint_as_float((uint32_t)v); }
+__device__ __forceinline__ float hi2(unsigned long long v) { return __uint_as_float((uint32_t)(v >> 32)); }
+
 struct Smem {
     static constexpr int Q = 0;
     static constexpr int A = Q + MAX_GROUPS * Q_GROUP_BYTES;                 // 131072
@@ -210,19 +224,17 @@ indexer_score_tc_kernel(const __grid_constant__ CUtensorMap tmQ, IndexerScorePar
                         const int tl0 = g * TOK_GROUP + half * 4 + pair * 2;
                         const float4* w0 = reinterpret_cast<const float4*>(sW + tl0 * HI);
                         const float4* w1 = reinterpret_cast<const float4*>(sW + (tl0 + 1) * HI);
-                        float a0 = 0.f, a1 = 0.f;
+                        // two heads per packed FMA (fma.rn.f32x2): even heads accumulate in the low half, odd heads in the high
+                        unsigned long long p0 = 0ull, p1 = 0ull;
 #pragma unroll
                         for (int h4 = 0; h4 < HI / 4; ++h4) {
                             const float4 u = w0[h4], v = w1[h4];
-                            a0 = fmaf(u.x, fmaxf(__uint_as_float(r0[4 * h4]), 0.f), a0);
-                            a0 = fmaf(u.y, fmaxf(__uint_as_float(r0[4 * h4 + 1]), 0.f), a0);
-                            a0 = fmaf(u.z, fmaxf(__uint_as_float(r0[4 * h4 + 2]), 0.f), a0);
-                            a0 = fmaf(u.w, fmaxf(__uint_as_float(r0[4 * h4 + 3]), 0.f), a0);
-                            a1 = fmaf(v.x, fmaxf(__uint_as_float(r1[4 * h4]), 0.f), a1);
-                            a1 = fmaf(v.y, fmaxf(__uint_as_float(r1[4 * h4 + 1]), 0.f), a1);
-                            a1 = fmaf(v.z, fmaxf(__uint_as_float(r1[4 * h4 + 2]), 0.f), a1);
-                            a1 = fmaf(v.w, fmaxf(__uint_as_float(r1[4 * h4 + 3]), 0.f), a1);
+                            p0 = fma2(pack2(u.x, u.y), pack2(fmaxf(__uint_as_float(r0[4 * h4]), 0.f), fmaxf(__uint_as_float(r0[4 * h4 + 1]), 0.f)), p0);
+                            p0 = fma2(pack2(u.z, u.w), pack2(fmaxf(__uint_as_float(r0[4 * h4 + 2]), 0.f), fmaxf(__uint_as_float(r0[4 * h4 + 3]), 0.f)), p0);
+                            p1 = fma2(pack2(v.x, v.y), pack2(fmaxf(__uint_as_float(r1[4 * h4]), 0.f), fmaxf(__uint_as_float(r1[4 * h4 + 1]), 0.f)), p1);
+                            p1 = fma2(pack2(v.z, v.w), pack2(fmaxf(__uint_as_float(r1[4 * h4 + 2]), 0.f), fmaxf(__uint_as_float(r1[4 * h4 + 3]), 0.f)), p1);
                         }
+                        const float a0 = lo2(p0) + hi2(p0), a1 = lo2(p1) + hi2(p1);
                         if (j < sNloc[tl0]) p.scores[(size_t)(t0 + tl0) * p.ld_scores + j] = a0 * ks;
                         if (j < sNloc[tl0 + 1]) p.scores[(size_t)(t0 + tl0 + 1) * p.ld_scores + j] = a1 * ks;
                     }
