@@ -344,8 +344,8 @@ def main():
             details["batch8_prefix"] = {"error": f"{type(err).__name__}: {err}"}
 
     # =================================== 128K prefill under context parallelism (full model, 8 GPUs) ===================================
-    if args.skip_cp or not full_model or (W < 8 and not (args.tiny and W > 1)):
-        details["prefill_128k_cp"] = None if args.skip_cp else {"skipped": f"needs the full model on 8 GPUs (have {L} layers on {W})"}
+    if args.skip_cp or not full_model or (W < 4 and not (args.tiny and W > 1)):
+        details["prefill_128k_cp"] = None if args.skip_cp else {"skipped": f"needs the full model on 4 or 8 GPUs (have {L} layers on {W})"}
     else:
         try:
             details["prefill_128k_cp"] = cp_run(args, ctx, dev, L, weights, sync_barrier, max_over_ranks, Rig)

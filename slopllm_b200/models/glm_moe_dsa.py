@@ -92,10 +92,15 @@ class GlmMoeDsaModel:
         self.ctx = ctx or ParallelContext(device=weights.embed.device)
         self.ops = ops or get_ops(cfg, weights.embed.device, self.ctx)
         self.comm = comm or Comm(self.ctx)
-        # context-parallel fallback: gather every layer's KV rows into a flat replicated buffer and attend like a
-        # TP rank (no top-k / partial merge); SLOPLLM_B200_CP_GATHER_KV=1
+        # context parallelism, two forms over the same token-interleaved cache.  Merge: every rank scores and attends over
+        # its own shard for all heads, top-k candidates and attention partials are merged across the ranks.  Gather: each
+        # layer's rows are all-gathered into a flat buffer and every rank attends like a TP rank over its own heads.
+        # On NVLink the gather is cheap (a few tens of MB per layer and chunk) and the 8-head attention kernel is far
+        # more efficient than the 64-head one the merge form needs, so prefill-sized steps gather (128K tokens on
+        # 4 x B200: 16.8 s against 23.2 s); decode steps, whose per-step gather would move the whole context, merge.
+        # SLOPLLM_B200_CP_GATHER_KV=1 / 0 forces one form for every step.
         from ..config import env_str
-        self.cp_gather_kv = env_str("CP_GATHER_KV") == "1"
+        self.cp_gather_mode = env_str("CP_GATHER_KV")
         # SLOPLLM_B200_L2_PREFETCH=1: decode steps pull the next layer's attention / router weights into L2 on a side
         # stream while the current layer's experts stream.  Off by default: on B200 it measured 3 % slower at batch 1 and
         # batch 8 (7.82 vs 7.57 ms and 12.67 vs 12.21 ms per 78-layer step of one TP-8 rank), the extra grid costs more
@@ -105,6 +110,13 @@ class GlmMoeDsaModel:
         self._pf_stream = None
 
     # -- context parallelism, gather-KV mode ------------------------------------------------
+    CP_GATHER_MIN_ROWS = 33        # steps of at least this many rows gather the KV rows (CUDA, no override)
+
+    def _cp_gathers(self, st: StepState) -> bool:
+        if self.cp_gather_mode in ("0", "1"):
+            return self.cp_gather_mode == "1"
+        return st.input_ids.is_cuda and st.input_ids.shape[0] >= self.CP_GATHER_MIN_ROWS
+
     def _gathered_view(self, lc: LayerCache, st: StepState):
         """Flat replicated copy of the step's sequences' rows of one layer, and a StepState that addresses it.
 
@@ -143,7 +155,7 @@ class GlmMoeDsaModel:
         cq, idx_w = ops.attn_pre(qkv, lw, st, lc)
         qb = ops.linear(cq, lw.w_q_b, defer_reduce=True)
         q_abs, q_pe, q8, w_eff = ops.q_post(qb, lw, st, idx_w)
-        if ctx.cp and ctx.world > 1 and self.cp_gather_kv:
+        if ctx.cp and ctx.world > 1 and self._cp_gathers(st):
             flat_lc, fst = self._gathered_view(lc, st)
             if lw.has_indexer:
                 pos, _ = ops.indexer_topk(q8, w_eff, flat_lc, fst)
