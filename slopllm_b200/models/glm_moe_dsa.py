@@ -117,7 +117,7 @@ class GlmMoeDsaModel:
             return self.cp_gather_mode == "1"
         return st.input_ids.is_cuda and st.input_ids.shape[0] >= self.CP_GATHER_MIN_ROWS
 
-    def _gathered_view(self, lc: LayerCache, st: StepState):
+    def _gathered_view(self, lc: LayerCache, st: StepState, with_index: bool = True):
         """Flat replicated copy of the step's sequences' rows of one layer, and a StepState that addresses it.
 
         Every rank reads its local rows (local index i of sequence b = global position i*W + r) through the page
@@ -144,7 +144,7 @@ class GlmMoeDsaModel:
         st2 = StepState(input_ids=st.input_ids, positions=st.positions, batch_idx=st.batch_idx, page_table=table.contiguous(),
                         logits_idx=st.logits_idx, page_size=ps, cp_world=1, cp_rank=0, slots=st.slots, lengths=st.lengths,
                         max_kv_len=st.max_kv_len, extra=st.extra)
-        return LayerCache(flat(lc.kv), flat(lc.idx) if lc.idx is not None else None), st2
+        return LayerCache(flat(lc.kv), flat(lc.idx) if (lc.idx is not None and with_index) else None), st2
 
     # -- attention -------------------------------------------------------------------------
     @traced("attention")
@@ -156,9 +156,17 @@ class GlmMoeDsaModel:
         qb = ops.linear(cq, lw.w_q_b, defer_reduce=True)
         q_abs, q_pe, q8, w_eff = ops.q_post(qb, lw, st, idx_w)
         if ctx.cp and ctx.world > 1 and self._cp_gathers(st):
-            flat_lc, fst = self._gathered_view(lc, st)
+            # the index keys stay sharded when the communicator can return every rank's winners: each rank scores its own
+            # shard, the candidates' scores and positions are gathered and re-selected (1 / W of the scoring work per rank)
+            sharded_index = lw.has_indexer and hasattr(comm, "cp_merge_topk_all")
+            flat_lc, fst = self._gathered_view(lc, st, with_index=not sharded_index)
             if lw.has_indexer:
-                pos, _ = ops.indexer_topk(q8, w_eff, flat_lc, fst)
+                if sharded_index:
+                    pos, score = ops.indexer_topk(q8, w_eff, lc, st)
+                    st.extra.pop("fused_slots", None)
+                    pos = comm.cp_merge_topk_all(ops, pos, score, self.cfg.index_topk)
+                else:
+                    pos, _ = ops.indexer_topk(q8, w_eff, flat_lc, fst)
                 fst.slots, fst.lengths = ops.topk_to_slots(pos, fst)
                 st.slots, st.lengths = fst.slots, fst.lengths           # flat-buffer slots are valid for the sharing layers too
             elif st.slots is None:

@@ -225,6 +225,27 @@ class Comm:
         hl = o.shape[1] // W
         return merged[:, r * hl:(r + 1) * hl].contiguous()
 
+    def cp_merge_topk_all(self, ops, pos: torch.Tensor, score: torch.Tensor, top_k: int) -> torch.Tensor:
+        """Global top-k over the ranks' local candidate lists, returned in full on every rank: [T, k] global positions of
+        ALL selected keys (-1 padded).  Both the candidates' scores and their positions travel (the gather form of
+        context parallelism attends over a replicated copy of the rows, so every rank needs every winner)."""
+        W = self.ctx.world
+        if W == 1:
+            return pos
+        T, k = pos.shape
+        s = torch.where(pos >= 0, score.to(torch.float32), torch.full_like(score, float("-inf"), dtype=torch.float32))
+        alls = torch.cat(self.all_gather_list(s.contiguous()), dim=1)                    # [T, W*k]
+        allp = torch.cat(self.all_gather_list(pos.to(torch.int32).contiguous()), dim=1)  # [T, W*k]
+        if hasattr(ops, "topk_select_plain") and alls.is_cuda:
+            idx = ops.topk_select_plain(alls, top_k).to(torch.int64)                     # ascending candidate index, -1 padded
+        else:
+            order = torch.sort(alls, dim=1, descending=True, stable=True).indices[:, :top_k]
+            idx = torch.sort(order, dim=1).values
+        ok = idx >= 0
+        out = allp.gather(1, torch.where(ok, idx, torch.zeros_like(idx)))
+        # a winner that is a padding candidate (score -inf: fewer than k real candidates overall) carries position -1 already
+        return torch.where(ok, out, torch.full_like(out, -1)).to(torch.int32).contiguous()
+
     def cp_merge_topk(self, ops, pos: torch.Tensor, score: torch.Tensor, top_k: int) -> torch.Tensor:
         """Global top-k over the ranks' local candidate lists (global positions + scores, -1 padded).
 
