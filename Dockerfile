@@ -5,7 +5,7 @@
 # Stage 2 (runtime): CUDA runtime libraries, Python with PyTorch, and the built tree only.
 #
 #   docker build -t slopllm-b200 .
-#   docker run --gpus all --ipc host --network host -v $HF_HOME:/root/.cache/huggingface slopllm-b200
+#   docker run --gpus all --ipc host --network host -v $HF_HOME:/hf-cache slopllm-b200
 #
 # The kernels target Blackwell B200 only (tcgen05 / TMEM / TMA); there is no other code path.
 ARG CUDA_VERSION=12.9.1
@@ -36,7 +36,8 @@ COPY --from=builder /opt/venv /opt/venv
 COPY --from=builder /opt/slopllm_b200 /opt/slopllm_b200
 ENV PATH=/opt/venv/bin:$PATH \
     PYTHONPATH=/opt/slopllm_b200 \
-    PYTHONUNBUFFERED=1
+    PYTHONUNBUFFERED=1 \
+    HF_HOME=/hf-cache
 WORKDIR /opt/slopllm_b200
 EXPOSE 8000
 # One process per GPU over NCCL / NVLink; rank 0 listens.  Override CMD (or use docker-compose.yml) for other layouts.
