@@ -28,13 +28,15 @@ typedef __nv_bfloat162 bf162;
 //      their prologue under this kernel's epilogue
 //   2  at kernel entry, and the weight-streaming kernels prefetch their first weight rows into L2 before they wait
 //      for the predecessor (weights do not depend on it), so consecutive kernels' memory streams overlap
+//   3  at kernel entry, nothing else: the successor's blocks become resident as soon as there is room and park in their
+//      dependency wait
 #ifndef SL_PDL_MODE
 #define SL_PDL_MODE 0
 #endif
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_grid_sync() {
-#if SL_PDL_MODE == 2
+#if SL_PDL_MODE >= 2
     pdl_trigger();
 #endif
     pdl_wait();
