@@ -6,27 +6,13 @@
 //
 // Covers what the reference gets from the vendored `sparse_mla_sm120` decode / prefill kernels
 // (`csrc/glm_sparse_mla.cu:34-126`): split-K over the top-k rows, mid_out / mid_lse + combine.
-#include "common.cuh"
+#include "sparse_mla.cuh"
 
 #include <type_traits>
 
 namespace {
 
-struct Params {
-    const bf16* q_abs;        // [T, h, R]
-    const bf16* q_pe;         // [T, h, Dr]
-    const uint8_t* kv_cache;  // [slots, row_bytes]
-    const int* slots;         // [T, topk]
-    const int* lengths;       // [T]
-    int h, R, Dr, group, topk, splits;
-    float sm_scale;
-    float* o_part;            // [T, h, splits, R]
-    float* lse_part;          // [T, h, splits]
-    int num_slots;            // rows of kv_cache (0 = unknown: no check)
-    int* guard;               // index self-check record (see guard_ok), may be null
-    bf16* o_final;            // keys-on-M kernel with splits == 1: final output [T, h, R] (then o_part / lse_part are not written)
-    float* lse_final;         // [T, h], may be null
-};
+using Params = SparseMlaParams;
 
 constexpr int HB = 16;        // heads per CTA (one MMA row tile)
 constexpr int KC = 64;        // keys per chunk (8 warps x 8 keys)
@@ -686,6 +672,10 @@ SL_API int sl_sparse_mla_split_mma(const void* params, int T, cudaStream_t s) {
     if (p->R % 64 != 0 || p->R > 512 || (p->R + p->Dr) % 16 != 0 || p->Dr % 2 != 0 || p->group % 4 != 0) return -1;
     if (g_transposed_enabled && transposed_ok(*p)) {
         if (p->o_final != nullptr && p->splits != 1) return -1;
+        if (p->o_final != nullptr) {
+            const int r = sparse_mla_tcgen05(p, T, s);
+            if (r != -2) return r;
+        }
         return p->h <= 8 ? launch_transposed<1>(*p, T, s) : launch_transposed<2>(*p, T, s);
     }
     if (p->o_final != nullptr) return -1;                     // only the keys-on-M kernel writes the final output itself

@@ -391,7 +391,7 @@ class CudaOps:
                                   slots=slots.data_ptr(), lengths=lengths.data_ptr(), h=h, R=Rr, Dr=c.qk_rope_head_dim,
                                   group=c.kv_quant_group, topk=slots.shape[1], splits=1, sm_scale=c.softmax_scale,
                                   o_part=0, lse_part=0, num_slots=layer_cache.kv.shape[0], guard=self._guard(dev),
-                                  o_final=o.data_ptr(), lse_final=lse.data_ptr())
+                                  o_final=o.data_ptr(), lse_final=lse.data_ptr(), err=self._guard(dev) - 16)
             N.call("sl_sparse_mla_split_mma", C.byref(p), T, N.stream())
             return o, lse
         o_part, lse_part = self.sparse_mla_partials(q_abs, q_pe, layer_cache, slots, lengths)

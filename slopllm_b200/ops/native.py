@@ -50,6 +50,9 @@ def kernels() -> C.CDLL:
     lib.sl_sparse_mla_set_transposed.argtypes = [i32]
     lib.sl_sparse_mla_set_transposed.restype = None
     lib.sl_sparse_mla_set_transposed(0 if os.environ.get("SLOPLLM_B200_MLA_TRANSPOSED", "1") == "0" else 1)
+    lib.sl_sparse_mla_set_tcgen05.argtypes = [i32]
+    lib.sl_sparse_mla_set_tcgen05.restype = None
+    lib.sl_sparse_mla_set_tcgen05(0 if os.environ.get("SLOPLLM_B200_MLA_TCGEN05", "1") == "0" else 1)
     return lib
 
 
@@ -112,7 +115,7 @@ class TopkSelectParams(C.Structure):
 class SparseMlaParams(C.Structure):
     _fields_ = [("q_abs", vp), ("q_pe", vp), ("kv_cache", vp), ("slots", vp), ("lengths", vp), ("h", i32), ("R", i32),
                 ("Dr", i32), ("group", i32), ("topk", i32), ("splits", i32), ("sm_scale", f32), ("o_part", vp),
-                ("lse_part", vp), ("num_slots", i32), ("guard", vp), ("o_final", vp), ("lse_final", vp)]
+                ("lse_part", vp), ("num_slots", i32), ("guard", vp), ("o_final", vp), ("lse_final", vp), ("err", vp)]
 
 
 class CombineParams(C.Structure):

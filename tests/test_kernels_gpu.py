@@ -386,6 +386,51 @@ def test_sparse_mla_keys_on_m(h, T, q_scale):
     close(lse[live], lse2[live], tol=1e-3, what="lse, keys-on-M vs heads-on-M")
 
 
+@pytest.mark.parametrize("h,T,q_scale,kv_scale", [(8, 160, 1.0, 2.0), (8, 300, 4.0, 2.0), (16, 150, 1.0, 0.05), (4, 310, 0.3, 30.0)])
+def test_sparse_mla_prefill_on_tcgen05(h, T, q_scale, kv_scale):
+    """Prefill-sized sparse MLA (no key split) runs on tcgen05 straight from the e4m3 cache rows: query and
+    probabilities as two e4m3 terms, code tiles read K-major for the scores and MN-major for the values.  Full, ragged,
+    one-key and empty key lists; `q_scale` 4 raises the softmax reference in later tiles (accumulators folded into
+    registers); small and large cache scales; 4, 8 and 16 heads (one or two head groups).  Against the fp32 definition and
+    against the mma.sync kernel through the switch."""
+    from slopllm_b200.ops import native as N
+    from slopllm_b200.ops import tcgen05
+    cfg = mini_cfg(num_attention_heads=h, index_topk=2048)
+    ops, ref = cuda_ops(cfg), RefOps(cfg)
+    g = torch.Generator(device=DEV).manual_seed(900 + h + T)
+    Rr, Dr, k = cfg.kv_lora_rank, cfg.qk_rope_head_dim, cfg.index_topk
+    nslots = 4096
+    cache = type("C", (), {})()
+    lat = torch.randn(nslots, Rr, device=DEV, generator=g) * kv_scale
+    lat[:, 128:256] *= 0.1                       # group scales of one row differ by an order of magnitude
+    cache.kv = quant.pack_kv_rows(lat, torch.randn(nslots, Dr, device=DEV, generator=g), cfg.kv_quant_group)
+    q_abs = (torch.randn(T, h, Rr, device=DEV, generator=g) * q_scale / max(kv_scale, 1.0)).to(torch.bfloat16)
+    q_pe = (torch.randn(T, h, Dr, device=DEV, generator=g) * q_scale).to(torch.bfloat16)
+    slots = torch.full((T, k), -1, dtype=torch.int32, device=DEV)
+    lens = ([k, 1000, 0, 129, 128, 1, 127, 300] * (T // 8 + 1))[:T]
+    lengths = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    for t in range(T):
+        n = lens[t]
+        slots[t, :n] = torch.randperm(nslots, device=DEV, generator=g)[:n].to(torch.int32)
+    assert ops._mla_splits(T, h) == 1
+    launches = N.kernel_count()
+    o, lse = ops.sparse_mla(q_abs, q_pe, cache, slots, lengths)
+    assert N.kernel_count() == launches + 1
+    tcgen05.check_errors(torch.device(DEV))
+    eo, elo = ref.sparse_mla(q_abs, q_pe, cache, slots, lengths)
+    live = lengths > 0
+    close(o, eo, what="sparse mla o (tcgen05)")
+    close(lse[live], elo[live], tol=2e-3, what="lse (tcgen05)")
+    assert torch.isinf(lse[~live]).all() and (o[~live] == 0).all()
+    N.kernels().sl_sparse_mla_set_tcgen05(0)
+    try:
+        o2, lse2 = ops.sparse_mla(q_abs, q_pe, cache, slots, lengths)
+    finally:
+        N.kernels().sl_sparse_mla_set_tcgen05(1)
+    close(o, o2, what="tcgen05 vs mma.sync")
+    close(lse[live], lse2[live], tol=2e-3, what="lse, tcgen05 vs mma.sync")
+
+
 @pytest.mark.parametrize("T,h", [(1, 8), (3, 8), (8, 8), (13, 4), (32, 8)])
 def test_attention_output_merge_fused_with_value_expansion(T, h):
     """Decode attention output in one launch (merge of the key splits as the staging step of the value expansion, plus
