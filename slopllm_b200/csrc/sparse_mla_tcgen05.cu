@@ -16,7 +16,7 @@
 //            split into two e4m3 terms (q * 2^e = hi + lo / 16; columns h and 8 + h) with a per-head power-of-two
 //            scale.  One accumulator per code group (the key's group scale is applied to the group sums by the thread
 //            that owns the key's TMEM lane) and one `kind::f16` accumulator for the rope part: 5 x 16 columns.
-//   softmax  thread j owns key j: s = sum_g scale[g] (hi_g + lo_g / 16) / 2^e + rope, in log2 units.  The running
+//   softmax  two threads own key j (four heads each): s = sum_g scale[g] (hi_g + lo_g / 16) / 2^e + rope, in log2 units.  The running
 //            maximum is a reference that is only raised when a value exceeds it by more than 2^8; exponentials are
 //            taken relative to it.  The value scale is folded into P (P_g = p * scale[g]); to keep P_g inside the
 //            e4m3 range whatever the scales are, the reference tracks s + log2(max_g scale[g]).  P_g is again two
@@ -37,7 +37,7 @@
 namespace {
 
 constexpr int R = 512, NG = 4, GS = 128, DR = 64, ROW_BYTES = R + 4 * NG + 2 * DR;   // 656
-constexpr int TILE = 128, NH = 8, NCOL = 2 * NH, THREADS = 128;
+constexpr int TILE = 128, NH = 8, NCOL = 2 * NH, THREADS = 256, HPT = NH / 2, ROWS_PER_WARP = TILE / (THREADS / 32);
 constexpr int K8_TILE = TILE * GS;               // 16384: one code group of one key tile
 constexpr int STAGE_K8 = NG * K8_TILE;           // 65536
 constexpr int KR_TILE = TILE * 2 * DR;           // 16384
@@ -101,7 +101,10 @@ __global__ void __launch_bounds__(THREADS, 2) sparse_mla_tc_kernel(SparseMlaPara
     uint64_t* bar_pv = bar_s + 1;
     uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bar_pv + 1);
 
+    // thread = (key of the tile | latent dim of a group, half of the heads): both halves of the block read the same
+    // TMEM lanes (lane quarter = warp % 4) and different columns
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int key = tid & (TILE - 1), wq = warp & 3, hb = (tid >> 7) * HPT;
     if (tid == 0) {
         tc::mbar_init(bar_s, 1);
         tc::mbar_init(bar_pv, 1);
@@ -117,7 +120,7 @@ __global__ void __launch_bounds__(THREADS, 2) sparse_mla_tc_kernel(SparseMlaPara
     __syncthreads();
     tc::fence_after_sync();
     const uint32_t tmem_base = *tmem_holder;
-    const uint32_t t_lane = tmem_base + ((uint32_t)(warp * 32) << 16);
+    const uint32_t t_lane = tmem_base + ((uint32_t)(wq * 32) << 16);
     pdl_grid_sync();
 
     constexpr uint32_t IDESC_S = tc::idesc_f8(TILE, NCOL);
@@ -127,20 +130,21 @@ __global__ void __launch_bounds__(THREADS, 2) sparse_mla_tc_kernel(SparseMlaPara
     uint32_t n_s = 0, n_pv = 0;                                    // phases of the two barriers consumed so far
     bool ok = true;
 
+    // a warp copies 16 whole rows of the tile; per-lane parts of the addresses are fixed
+    uint8_t* const g_dst = sK8 + (lane >> 3) * K8_TILE + warp * ROWS_PER_WARP * 128;
+    uint8_t* const g_tail = lane == 0 ? sSC + warp * ROWS_PER_WARP * 16 : sKR + warp * ROWS_PER_WARP * 128;
+    const int g_tail_pitch = lane == 0 ? 16 : 128;
+    const uint8_t* const g_src = p.kv_cache + lane * 16;
     auto gather = [&](int tile) {
-        const int* sl = s_slots + tile * TILE + warp * 32;
-        uint8_t* k8 = sK8 + (lane >> 3) * K8_TILE;
-        const int cc = lane & 7;
-#pragma unroll 8
-        for (int r = 0; r < 32; ++r) {
-            const int row = warp * 32 + r, slot = sl[r], sw = row & 7;
+        const int* sl = s_slots + tile * TILE + warp * ROWS_PER_WARP;
+#pragma unroll
+        for (int r = 0; r < ROWS_PER_WARP; ++r) {
+            const int slot = sl[r];
             const uint32_t sz = slot >= 0 ? 16u : 0u;
-            const uint8_t* src = p.kv_cache + (size_t)(slot >= 0 ? slot : 0) * ROW_BYTES;
-            cp_async16(k8 + row * 128 + ((cc ^ sw) << 4), src + lane * 16, sz);
-            if (lane < 9) {
-                uint8_t* dst = lane == 0 ? sSC + row * 16 : sKR + row * 128 + (((lane - 1) ^ sw) << 4);
-                cp_async16(dst, src + R + lane * 16, sz);          // piece 0 of the tail: scales; pieces 1 .. 8: rope
-            }
+            const uint8_t* src = g_src + (size_t)(slot >= 0 ? slot : 0) * ROW_BYTES;
+            cp_async16(g_dst + r * 128 + (((lane & 7) ^ (r & 7)) << 4), src, sz);
+            if (lane < 9)                                          // piece 0 of the tail: scales; pieces 1 .. 8: rope
+                cp_async16(g_tail + r * g_tail_pitch + (lane == 0 ? 0 : (((lane - 1) ^ (r & 7)) << 4)), src + R, sz);
         }
         cp_async_commit();
     };
@@ -153,7 +157,7 @@ __global__ void __launch_bounds__(THREADS, 2) sparse_mla_tc_kernel(SparseMlaPara
         const int ntiles = (L + TILE - 1) / TILE;
         __syncthreads();                                           // the previous item is done with Q, the reference and the sums
 
-        // the token's slots, padded with -1 to whole tiles; a warp later gathers rows whose slots other warps loaded
+        // the token's slots, padded with -1 to whole tiles
         for (int j = tid; j < ntiles * TILE; j += THREADS) {
             int sl = j < L ? slots[j] : -1;
             if (sl >= 0 && p.num_slots != 0 && !guard_ok(p.guard, 14, sl, p.num_slots)) sl = -1;
@@ -161,10 +165,9 @@ __global__ void __launch_bounds__(THREADS, 2) sparse_mla_tc_kernel(SparseMlaPara
         }
         __syncthreads();
         if (ntiles > 0) gather(0);                                 // in flight while the query operands are prepared
-        // ---- query operands: two heads per warp; lane = 16 latent values = one 16-byte piece of e4m3 codes ----
-#pragma unroll
-        for (int hw = 0; hw < NH / 4; ++hw) {
-            const int hh = warp * (NH / 4) + hw;
+        // ---- query operands: one head per warp; lane = 16 latent values = one 16-byte piece of e4m3 codes ----
+        {
+            const int hh = warp;
             uint4 hi = make_uint4(0u, 0u, 0u, 0u), lo = hi;
             float inv = 1.f;
             if (hh < nh) {
@@ -227,15 +230,33 @@ __global__ void __launch_bounds__(THREADS, 2) sparse_mla_tc_kernel(SparseMlaPara
             if (lane == 0) { s_invq[hh] = inv; s_mref[hh] = -INFINITY; }
         }
 
-        float o_reg[NG * NCOL];
+        float o_reg[NG][2][HPT];                                   // [group][hi | lo term][head of this thread]
 #pragma unroll
-        for (int c = 0; c < NG * NCOL; ++c) o_reg[c] = 0.f;
-        float lsum[NH];
+        for (int g = 0; g < NG; ++g)
 #pragma unroll
-        for (int h = 0; h < NH; ++h) lsum[h] = 0.f;
+            for (int hh = 0; hh < HPT; ++hh) o_reg[g][0][hh] = o_reg[g][1][hh] = 0.f;
+        float lsum[HPT];
+#pragma unroll
+        for (int hh = 0; hh < HPT; ++hh) lsum[hh] = 0.f;
         bool have_acc = false;
+        auto fold_acc = [&]() {                                    // accumulators (dim `key` of each group) into registers
+            uint32_t acc[NG][2][HPT];
+#pragma unroll
+            for (int g = 0; g < NG; ++g) {
+                tc::tmem_ld_32x4(t_lane + COL_O + g * NCOL + hb, acc[g][0]);
+                tc::tmem_ld_32x4(t_lane + COL_O + g * NCOL + NH + hb, acc[g][1]);
+            }
+            tc::tmem_ld_wait();
+#pragma unroll
+            for (int g = 0; g < NG; ++g)
+#pragma unroll
+                for (int hh = 0; hh < HPT; ++hh) {
+                    o_reg[g][0][hh] += __uint_as_float(acc[g][0][hh]);
+                    o_reg[g][1][hh] += __uint_as_float(acc[g][1][hh]);
+                }
+        };
 
-        __syncthreads();                                           // slots, query operands, reference
+        __syncthreads();                                           // query operands, reference
         for (int i = 0; i < ntiles && ok; ++i) {
             if (i > 0) gather(i);                                  // the previous tile's value product has been waited for
             cp_async_wait_all();
@@ -261,95 +282,99 @@ __global__ void __launch_bounds__(THREADS, 2) sparse_mla_tc_kernel(SparseMlaPara
             ++n_s;
             if (!ok) { if (tid == 0) atomicExch(p.err, 32); break; }
 
-            // ---- scores of key `tid` of the tile for the 8 heads ----
-            float u[NH];
+            // ---- scores of key `key` of the tile for this thread's four heads ----
+            float u[HPT];
             float4 sc;
             float inv_scmax;
             {
-                uint32_t d[NG + 1][NCOL];
+                uint32_t dh[NG][HPT], dl[NG][HPT], dr[HPT];
 #pragma unroll
-                for (int a = 0; a <= NG; ++a) tc::tmem_ld_32x16(t_lane + COL_S + a * NCOL, d[a]);
+                for (int g = 0; g < NG; ++g) {
+                    tc::tmem_ld_32x4(t_lane + COL_S + g * NCOL + hb, dh[g]);
+                    tc::tmem_ld_32x4(t_lane + COL_S + g * NCOL + NH + hb, dl[g]);
+                }
+                tc::tmem_ld_32x4(t_lane + COL_S + NG * NCOL + hb, dr);
                 tc::tmem_ld_wait();
-                sc = *reinterpret_cast<const float4*>(sSC + tid * 16);
+                sc = *reinterpret_cast<const float4*>(sSC + key * 16);
                 const float scmax = fmaxf(fmaxf(fmaxf(sc.x, sc.y), fmaxf(sc.z, sc.w)), 1e-30f);
                 const float lsc = log2f(scmax);
                 inv_scmax = 1.f / scmax;
-                const bool valid = s_slots[i * TILE + tid] >= 0;
+                const bool valid = s_slots[i * TILE + key] >= 0;
                 const float scs[NG] = {sc.x, sc.y, sc.z, sc.w};
+                const float4 iq = *reinterpret_cast<const float4*>(s_invq + hb);
+                const float iqs[HPT] = {iq.x, iq.y, iq.z, iq.w};
 #pragma unroll
-                for (int h = 0; h < NH; ++h) {
+                for (int hh = 0; hh < HPT; ++hh) {
                     float lat = 0.f;
 #pragma unroll
                     for (int g = 0; g < NG; ++g)
-                        lat = fmaf(scs[g], fmaf(__uint_as_float(d[g][NH + h]), 0.0625f, __uint_as_float(d[g][h])), lat);
-                    const float s = fmaf(lat, s_invq[h], __uint_as_float(d[NG][h]));
-                    u[h] = valid ? s + lsc : -INFINITY;
+                        lat = fmaf(scs[g], fmaf(__uint_as_float(dl[g][hh]), 0.0625f, __uint_as_float(dh[g][hh])), lat);
+                    const float sv = fmaf(lat, iqs[hh], __uint_as_float(dr[hh]));
+                    u[hh] = valid ? sv + lsc : -INFINITY;
                 }
             }
             // ---- raise the reference when a value exceeds it by more than 2^RAISE ----
+            float mref[HPT];
+            {
+                const float4 m4 = *reinterpret_cast<const float4*>(s_mref + hb);
+                mref[0] = m4.x; mref[1] = m4.y; mref[2] = m4.z; mref[3] = m4.w;
+            }
             bool raise = false;
 #pragma unroll
-            for (int h = 0; h < NH; ++h) raise |= u[h] > s_mref[h] + RAISE;
+            for (int hh = 0; hh < HPT; ++hh) raise |= u[hh] > mref[hh] + RAISE;
             if (__syncthreads_or(raise)) {
 #pragma unroll
-                for (int h = 0; h < NH; ++h) {
-                    const float m = warp_max(u[h]);
-                    if (lane == 0) s_wred[warp * NH + h] = m;
+                for (int hh = 0; hh < HPT; ++hh) {
+                    const float m = warp_max(u[hh]);
+                    if (lane == 0) s_wred[wq * NH + hb + hh] = m;
                 }
                 __syncthreads();
-                float f[NH], newm[NH];
+                float f[HPT];
 #pragma unroll
-                for (int h = 0; h < NH; ++h) {
-                    const float mo = s_mref[h];
-                    const float mn = fmaxf(fmaxf(mo, fmaxf(s_wred[h], s_wred[NH + h])), fmaxf(s_wred[2 * NH + h], s_wred[3 * NH + h]));
-                    newm[h] = mn;
-                    f[h] = mn == -INFINITY ? 1.f : exp2f(mo - mn);
+                for (int hh = 0; hh < HPT; ++hh) {
+                    const int h = hb + hh;
+                    const float mn = fmaxf(fmaxf(mref[hh], fmaxf(s_wred[h], s_wred[NH + h])), fmaxf(s_wred[2 * NH + h], s_wred[3 * NH + h]));
+                    f[hh] = mn == -INFINITY ? 1.f : exp2f(mref[hh] - mn);
+                    mref[hh] = mn;
                 }
-                if (have_acc) {                                    // fold the accumulators (dims `tid` of each group) into registers
-                    uint32_t acc[2][32];
-                    tc::tmem_ld_32x32(t_lane + COL_O, acc[0]);
-                    tc::tmem_ld_32x32(t_lane + COL_O + 32, acc[1]);
-                    tc::tmem_ld_wait();
-#pragma unroll
-                    for (int c = 0; c < NG * NCOL; ++c) o_reg[c] += __uint_as_float(acc[c >> 5][c & 31]);
+                if (have_acc) {
+                    fold_acc();
                     have_acc = false;
                 }
 #pragma unroll
-                for (int c = 0; c < NG * NCOL; ++c) o_reg[c] *= f[c & (NH - 1)];
+                for (int g = 0; g < NG; ++g)
 #pragma unroll
-                for (int h = 0; h < NH; ++h) lsum[h] *= f[h];
-                __syncthreads();                                   // everybody has read the old reference
-                if (tid < NH) {
-                    float mine = newm[0];
+                    for (int hh = 0; hh < HPT; ++hh) { o_reg[g][0][hh] *= f[hh]; o_reg[g][1][hh] *= f[hh]; }
 #pragma unroll
-                    for (int h = 1; h < NH; ++h) mine = tid == h ? newm[h] : mine;
-                    s_mref[tid] = mine;
-                }
-                __syncthreads();
+                for (int hh = 0; hh < HPT; ++hh) lsum[hh] *= f[hh];
+                if (key == 0) *reinterpret_cast<float4*>(s_mref + hb) = make_float4(mref[0], mref[1], mref[2], mref[3]);
+                // (the old reference lives in registers; the next read of s_mref is after the barrier that follows P)
             }
-            // ---- P_g = exp2(u - ref) * scale[g] / scmax in two e4m3 terms: byte `tid` of rows h and 8 + h of the B operand ----
+            // ---- P_g = exp2(u - ref) * scale[g] / scmax in two e4m3 terms: byte `key` of rows h and 8 + h of the B operand ----
             {
                 const float r0 = sc.x * inv_scmax, r1 = sc.y * inv_scmax, r2 = sc.z * inv_scmax, r3 = sc.w * inv_scmax;
-                uint8_t* pb = sP + (tid & 15);
-                const int chunk = tid >> 4;
+                uint8_t* pb = sP + (key & 15);
+                const int chunk = key >> 4;
 #pragma unroll
-                for (int h = 0; h < NH; ++h) {
-                    const float e = u[h] == -INFINITY ? 0.f : exp2f(u[h] - s_mref[h]);      // masked key: 0
-                    lsum[h] = fmaf(e, inv_scmax, lsum[h]);
+                for (int hh = 0; hh < HPT; ++hh) {
+                    const int h = hb + hh;
+                    const float e = u[hh] == -INFINITY ? 0.f : exp2f(u[hh] - mref[hh]);      // masked key: 0
+                    lsum[hh] = fmaf(e, inv_scmax, lsum[hh]);
                     const float p0 = e * r0, p1 = e * r1, p2 = e * r2, p3 = e * r3;
                     const uint32_t h01 = to_e4m3x2(p0, p1), h23 = to_e4m3x2(p2, p3);
                     const float2 b01 = from_e4m3x2(h01), b23 = from_e4m3x2(h23);
                     const uint32_t l01 = to_e4m3x2((p0 - b01.x) * 16.f, (p1 - b01.y) * 16.f);
                     const uint32_t l23 = to_e4m3x2((p2 - b23.x) * 16.f, (p3 - b23.y) * 16.f);
-                    const int offh = h * 128 + ((chunk ^ (h & 7)) << 4), offl = (NH + h) * 128 + ((chunk ^ ((NH + h) & 7)) << 4);
-                    pb[0 * B_TILE + offh] = (uint8_t)(h01 & 0xffu);
-                    pb[1 * B_TILE + offh] = (uint8_t)(h01 >> 8);
-                    pb[2 * B_TILE + offh] = (uint8_t)(h23 & 0xffu);
-                    pb[3 * B_TILE + offh] = (uint8_t)(h23 >> 8);
-                    pb[0 * B_TILE + offl] = (uint8_t)(l01 & 0xffu);
-                    pb[1 * B_TILE + offl] = (uint8_t)(l01 >> 8);
-                    pb[2 * B_TILE + offl] = (uint8_t)(l23 & 0xffu);
-                    pb[3 * B_TILE + offl] = (uint8_t)(l23 >> 8);
+                    // rows h and 8 + h have the same swizzle phase (h & 7)
+                    uint8_t* ph = pb + h * 128 + ((chunk ^ (h & 7)) << 4);
+                    ph[0 * B_TILE] = (uint8_t)(h01 & 0xffu);
+                    ph[1 * B_TILE] = (uint8_t)(h01 >> 8);
+                    ph[2 * B_TILE] = (uint8_t)(h23 & 0xffu);
+                    ph[3 * B_TILE] = (uint8_t)(h23 >> 8);
+                    ph[0 * B_TILE + NH * 128] = (uint8_t)(l01 & 0xffu);
+                    ph[1 * B_TILE + NH * 128] = (uint8_t)(l01 >> 8);
+                    ph[2 * B_TILE + NH * 128] = (uint8_t)(l23 & 0xffu);
+                    ph[3 * B_TILE + NH * 128] = (uint8_t)(l23 >> 8);
                 }
             }
             tc::fence_proxy_async_smem();
@@ -373,30 +398,25 @@ __global__ void __launch_bounds__(THREADS, 2) sparse_mla_tc_kernel(SparseMlaPara
         }
         if (!ok) break;
         if (have_acc) {
-            uint32_t acc[2][32];
-            tc::tmem_ld_32x32(t_lane + COL_O, acc[0]);
-            tc::tmem_ld_32x32(t_lane + COL_O + 32, acc[1]);
-            tc::tmem_ld_wait();
-#pragma unroll
-            for (int c = 0; c < NG * NCOL; ++c) o_reg[c] += __uint_as_float(acc[c >> 5][c & 31]);
+            fold_acc();
             tc::fence_before_sync();
         }
         // ---- softmax denominators, output ----
 #pragma unroll
-        for (int h = 0; h < NH; ++h) {
-            const float x = warp_sum(lsum[h]);
-            if (lane == 0) s_wred[warp * NH + h] = x;
+        for (int hh = 0; hh < HPT; ++hh) {
+            const float x = warp_sum(lsum[hh]);
+            if (lane == 0) s_wred[wq * NH + hb + hh] = x;
         }
         __syncthreads();
 #pragma unroll
-        for (int h = 0; h < NH; ++h) {
+        for (int hh = 0; hh < HPT; ++hh) {
+            const int h = hb + hh;
             if (h < nh) {
                 const float l = s_wred[h] + s_wred[NH + h] + s_wred[2 * NH + h] + s_wred[3 * NH + h];
                 const float inv = l > 0.f ? 1.f / l : 0.f;
-                bf16* o = p.o_final + ((size_t)t * p.h + h0 + h) * R + tid;
+                bf16* o = p.o_final + ((size_t)t * p.h + h0 + h) * R + key;
 #pragma unroll
-                for (int g = 0; g < NG; ++g)
-                    o[g * GS] = __float2bfloat16(fmaf(o_reg[g * NCOL + NH + h], 0.0625f, o_reg[g * NCOL + h]) * inv);
+                for (int g = 0; g < NG; ++g) o[g * GS] = __float2bfloat16(fmaf(o_reg[g][1][hh], 0.0625f, o_reg[g][0][hh]) * inv);
             }
         }
         if (tid < nh && p.lse_final != nullptr) {
@@ -428,7 +448,8 @@ int sparse_mla_tcgen05(const SparseMlaParams* p, int T, cudaStream_t s) {
     }
     const int head_groups = (p->h + NH - 1) / NH;
     const int items = T * head_groups;
-    sl_launch(sparse_mla_tc_kernel, dim3(items < 2 * 148 ? items : 2 * 148), THREADS, SMEM_BYTES, s, *p, T, head_groups);
+    const int max_ctas = 2 * 148;
+    sl_launch(sparse_mla_tc_kernel, dim3(items < max_ctas ? items : max_ctas), THREADS, SMEM_BYTES, s, *p, T, head_groups);
     return SL_LAUNCH_CHECK();
 }
 
