@@ -73,6 +73,17 @@ __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wai
 __device__ __forceinline__ uint32_t to_e4m3x2(float a, float b) {
     return (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
 }
+// hardware approximations (2 ulp class): inputs here are finite and in range
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float lg2_approx(float x) {
+    float y;
+    asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ float2 from_e4m3x2(uint32_t v) { return e4m3x2_to_float2((uint16_t)v); }
 
 // One thread waits (bounded); everybody learns the outcome.
@@ -297,8 +308,8 @@ __global__ void __launch_bounds__(THREADS, 2) sparse_mla_tc_kernel(SparseMlaPara
                 tc::tmem_ld_wait();
                 sc = *reinterpret_cast<const float4*>(sSC + key * 16);
                 const float scmax = fmaxf(fmaxf(fmaxf(sc.x, sc.y), fmaxf(sc.z, sc.w)), 1e-30f);
-                const float lsc = log2f(scmax);
-                inv_scmax = 1.f / scmax;
+                const float lsc = lg2_approx(scmax);
+                inv_scmax = __frcp_rn(scmax);
                 const bool valid = s_slots[i * TILE + key] >= 0;
                 const float scs[NG] = {sc.x, sc.y, sc.z, sc.w};
                 const float4 iq = *reinterpret_cast<const float4*>(s_invq + hb);
@@ -358,7 +369,7 @@ __global__ void __launch_bounds__(THREADS, 2) sparse_mla_tc_kernel(SparseMlaPara
 #pragma unroll
                 for (int hh = 0; hh < HPT; ++hh) {
                     const int h = hb + hh;
-                    const float e = u[hh] == -INFINITY ? 0.f : exp2f(u[hh] - mref[hh]);      // masked key: 0
+                    const float e = u[hh] == -INFINITY ? 0.f : ex2_approx(u[hh] - mref[hh]);      // masked key: 0
                     lsum[hh] = fmaf(e, inv_scmax, lsum[hh]);
                     const float p0 = e * r0, p1 = e * r1, p2 = e * r2, p3 = e * r3;
                     const uint32_t h01 = to_e4m3x2(p0, p1), h23 = to_e4m3x2(p2, p3);
