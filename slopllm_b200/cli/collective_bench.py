@@ -180,7 +180,7 @@ def main(argv=None) -> int:
         us_l = _time_graph(run_lib, args.iters)
         weight_bytes = H * K // 2 + H * K // 16
         if T <= 32:
-            push_bytes = T * H * 4 * (W - 1)                       # fp32 rows to every peer
+            push_bytes = T * H * 4 * (W - 1)                       # 4-byte {bf16, tag} words to every peer
             roof_us = max(weight_bytes / (args.hbm_gbs * 1e3), push_bytes / (args.nvlink_gbs * 1e3))
         else:
             push_bytes = 2 * (W - 1) * (T // W) * H * 2            # bf16: partial rows to their owners, sums to every peer

@@ -20,7 +20,7 @@
 #include <cstring>
 
 struct RecvCtx {
-    const uint2* buf;          // this rank's receive buffer [world][slot_rows][row_len] of {value bits, tag}
+    uint32_t* buf;             // this rank's receive buffer [world][slot_rows][row_len] of {bf16 value, 16-bit tag} words
     const uint32_t* flags;     // unused by the tagged protocol
     uint32_t* epoch;           // completed collectives on this buffer (incremented here)
     uint32_t* done_counter;    // consumer blocks that have finished
@@ -35,37 +35,33 @@ __device__ __forceinline__ uint4 ld_volatile_16(const void* p) {
     return v;
 }
 
-// Four consecutive tagged words of every rank's slot (element columns 4i .. 4i+3 of row t): all loads of a poll
-// round are issued before any tag is tested, so a round costs one memory latency, not one per rank.  Rounds repeat
-// until every tag equals `target`; after max_spins rounds the timeout is recorded in `status` and the last values
-// seen are used (the host reads the status word after the step).  The sum runs in rank order (deterministic).
-__device__ __forceinline__ float4 ll_gather_sum(const RecvCtx& c, int t, int i, uint32_t target) {
-    uint4 lo[SL_MAX_RANKS], hi[SL_MAX_RANKS];
+// Four consecutive tagged words of every rank's slot (element columns 4i .. 4i+3 of row t, one 16-byte load per
+// rank): all loads of a poll round are issued before any tag is tested, so a round costs one memory latency, not one
+// per rank.  Rounds repeat until every tag equals `tag`; after max_spins rounds the timeout is recorded in `status` and
+// the last values seen are used (the host reads the status word after the step).  The sum runs in rank order
+// (deterministic).  The words are zeroed once used (see csrc/push.cuh).
+__device__ __forceinline__ float4 ll_gather_sum(const RecvCtx& c, int t, int i, uint32_t tag) {
+    uint4 w[SL_MAX_RANKS];
     for (uint32_t spin = 0;; ++spin) {
 #pragma unroll
-        for (int r = 0; r < SL_MAX_RANKS; ++r) {
-            if (r < c.world) {
-                const uint2* src = c.buf + ((size_t)r * c.slot_rows + t) * c.row_len + 4 * i;
-                lo[r] = ld_volatile_16(src);
-                hi[r] = ld_volatile_16(src + 2);
-            }
-        }
+        for (int r = 0; r < SL_MAX_RANKS; ++r)
+            if (r < c.world) w[r] = ld_volatile_16(c.buf + ((size_t)r * c.slot_rows + t) * c.row_len + 4 * i);
         bool ok = true;
-        uint32_t seen = target;
+        uint32_t seen = tag;
 #pragma unroll
         for (int r = 0; r < SL_MAX_RANKS; ++r) {
             if (r < c.world) {
-                if (lo[r].y != target) { ok = false; seen = lo[r].y; }
-                if (lo[r].w != target) { ok = false; seen = lo[r].w; }
-                if (hi[r].y != target) { ok = false; seen = hi[r].y; }
-                if (hi[r].w != target) { ok = false; seen = hi[r].w; }
+                if ((w[r].x & 0xffffu) != tag) { ok = false; seen = w[r].x & 0xffffu; }
+                if ((w[r].y & 0xffffu) != tag) { ok = false; seen = w[r].y & 0xffffu; }
+                if ((w[r].z & 0xffffu) != tag) { ok = false; seen = w[r].z & 0xffffu; }
+                if ((w[r].w & 0xffffu) != tag) { ok = false; seen = w[r].w & 0xffffu; }
             }
         }
         if (ok) break;
         if (spin >= c.max_spins) {
             if (c.status != nullptr && atomicCAS(c.status, 0, 1) == 0) {
                 c.status[1] = 1;
-                c.status[2] = (int)target;
+                c.status[2] = (int)tag;
                 c.status[3] = (int)seen;
             }
             break;
@@ -76,8 +72,9 @@ __device__ __forceinline__ float4 ll_gather_sum(const RecvCtx& c, int t, int i, 
 #pragma unroll
     for (int r = 0; r < SL_MAX_RANKS; ++r) {
         if (r < c.world) {
-            a.x += __uint_as_float(lo[r].x); a.y += __uint_as_float(lo[r].z);
-            a.z += __uint_as_float(hi[r].x); a.w += __uint_as_float(hi[r].z);
+            a.x += __uint_as_float(w[r].x & 0xffff0000u); a.y += __uint_as_float(w[r].y & 0xffff0000u);
+            a.z += __uint_as_float(w[r].z & 0xffff0000u); a.w += __uint_as_float(w[r].w & 0xffff0000u);
+            *reinterpret_cast<uint4*>(c.buf + ((size_t)r * c.slot_rows + t) * c.row_len + 4 * i) = make_uint4(0u, 0u, 0u, 0u);
         }
     }
     return a;
@@ -90,14 +87,14 @@ __global__ void __launch_bounds__(512) ar_add_rmsnorm_kernel(RecvCtx c, bf16* __
     pdl_grid_sync();
     __shared__ float scratch[33];
     const int t = blockIdx.x, nt = blockDim.x, n4 = H / 4;
-    const uint32_t target = *c.epoch + 1u;
+    const uint32_t target = *c.epoch + 1u, tag = push_tag_of(*c.epoch);
     float4 v[8];
     float ss = 0.f;
 #pragma unroll
     for (int q = 0; q < 8; ++q) {
         const int i = threadIdx.x + q * nt;
         if (i < n4) {
-            float4 a = ll_gather_sum(c, t, i, target);
+            float4 a = ll_gather_sum(c, t, i, tag);
             if (res_in != nullptr) {
                 const float4 r = reinterpret_cast<const float4*>(res_in + (size_t)t * H)[i];
                 a.x += r.x; a.y += r.y; a.z += r.z; a.w += r.w;

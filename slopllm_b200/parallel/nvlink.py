@@ -264,7 +264,7 @@ class SymmetricRegion:
             return o
         lay = {"flags": [take(4 * MAX_RANKS * 2) for _ in range(8)], "data": [], "guards": guards}
         for _ in range(cls.NUM_BUFS):
-            lay["data"].append(take(world * slot_rows * row_len * 8))      # {fp32 value, tag} per element
+            lay["data"].append(take(world * slot_rows * row_len * 4))      # {bf16 value, 16-bit tag} per element
         lay["gather"] = take(2 * world * gather_bytes) if gather_bytes else 0          # two halves (epoch parity)
         if cp_shape is not None:
             Tmax, h, R = cp_shape

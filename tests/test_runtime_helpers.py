@@ -187,7 +187,7 @@ def test_symmetric_region_guard_zones_detect_overruns():
     rg = SymmetricRegion(0, W, 32, H, buf, [buf.data_ptr()] * W, gather_bytes=1024, cp_shape=(32, 8, 64), bulk_rows=64)
     rg.check_canaries()
     # every area ends where its guard zone begins: a store one byte past the last receive slot lands in a guard
-    end_of_data2 = lay["data"][2] + W * 32 * H * 8
+    end_of_data2 = lay["data"][2] + W * 32 * H * 4
     assert end_of_data2 in lay["guards"]
     buf[end_of_data2] = 1
     with pytest.raises(RuntimeError, match="guard zone"):
