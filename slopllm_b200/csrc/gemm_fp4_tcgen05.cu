@@ -439,6 +439,15 @@ __global__ void __launch_bounds__(256) nvfp4_quantize_rows_kernel(const QuantPar
     const int m = blockIdx.x, ks = threadIdx.x;
     if (p.num_rows != nullptr && m >= __ldg(p.num_rows)) return;
     const int KT = p.K / 64;
+    if (m >= p.rows) {                             // padding rows of the last scale tile (ungrouped, one term): zero scales
+        if (ks < KT) {
+            const int tile = m / p.bn, r = m % p.bn;
+            uint8_t* dst = p.sf + ((size_t)tile * KT + ks) * 512 + (r % 32) * 16;
+            if (p.bn == 32) *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
+            else *reinterpret_cast<uint32_t*>(dst + (r / 32) * 4) = 0u;
+        }
+        return;
+    }
     const int sr = p.src ? p.src[m] : m;
     const bool valid = sr >= 0 && sr < p.x_rows && ks < KT;
     float v[64];
@@ -507,7 +516,11 @@ __global__ void __launch_bounds__(256) nvfp4_quantize_rows_kernel(const QuantPar
             qd[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
             qd[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
             const int tile = prow / p.bn, r = prow % p.bn;
-            *reinterpret_cast<uint32_t*>(p.sf + ((size_t)tile * KT + ks) * 512 + (r % 32) * 16 + (r / 32) * 4) = sc_word;
+            uint8_t* dst = p.sf + ((size_t)tile * KT + ks) * 512 + (r % 32) * 16;
+            // 32-row tiles use the first of the four words of a 16-byte piece; the other three are written too (zero), so
+            // the whole piece is defined without a separate clear
+            if (p.bn == 32) *reinterpret_cast<uint4*>(dst) = make_uint4(sc_word, 0u, 0u, 0u);
+            else *reinterpret_cast<uint32_t*>(dst + (r / 32) * 4) = sc_word;
         }
     }
 }
@@ -813,7 +826,8 @@ SL_API int sl_nvfp4_gather_rows(void* q, void* sf, void* g, const void* q_src, c
 // bf16 rows -> NVFP4 rows (+ residual terms).  q [rows * terms, K/2], g [rows * terms], sf = scale tiles
 // [padded rows / bn][K/64][512]; `src` (int32 [rows], may be null) gathers: output row m quantises x[src[m]].
 // `offsets` / `pad` (may be null: one group, no padding) place the scales of grouped rows, see sl_fp4_group_pad;
-// `num_rows` (device int, may be null) limits the rows that are really quantised.
+// `num_rows` (device int, may be null) limits the rows that are really quantised.  Without groups and with one term the
+// scale tiles need no clearing by the caller (padding rows of the last tile are zeroed here); otherwise pass them zeroed.
 // K % 64 == 0, K <= 16384, ldx % 8 == 0, x 16-byte aligned.
 SL_API int sl_nvfp4_quantize_rows(void* q, void* sf, void* g, const void* x, const void* src, int rows, int x_rows, int K, int ldx,
                                   int terms, const void* offsets, const void* pad, int groups, int bn, const void* num_rows,
@@ -825,6 +839,9 @@ SL_API int sl_nvfp4_quantize_rows(void* q, void* sf, void* g, const void* x, con
     QuantParams p{(uint8_t*)q, (uint8_t*)sf, (float*)g, (const bf16*)x, (const int*)src, rows, x_rows, K, ldx, terms,
                   (const int*)offsets, (const int*)pad, groups, bn, (const int*)num_rows};
     const int threads = (K / 64 + 31) / 32 * 32;
-    sl_launch(nvfp4_quantize_rows_kernel, rows, threads, 0, s, p);
+    // ungrouped rows of one term: the blocks past `rows` zero the scales of the last tile's padding rows, so the caller
+    // need not clear the scale tiles first
+    const int blocks = (offsets == nullptr && terms == 1) ? (rows + bn - 1) / bn * bn : rows;
+    sl_launch(nvfp4_quantize_rows_kernel, blocks, threads, 0, s, p);
     return (int)cudaGetLastError();
 }

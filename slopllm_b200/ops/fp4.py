@@ -109,7 +109,9 @@ def quantize_rows(x: torch.Tensor, src: Optional[torch.Tensor] = None, rows: Opt
     else:
         row_tiles = (M * terms + bn - 1) // bn
     q = torch.empty(M * terms, K // 2, dtype=torch.uint8, device=dev)
-    sf = torch.zeros(row_tiles * (K // 64) * 512, dtype=torch.uint8, device=dev)
+    # grouped rows leave padding rows between groups and residual terms share tiles: those scale tiles start zeroed; plain
+    # rows need no clearing (the kernel zeroes the last tile's padding rows; tiles past `num_rows` are never read)
+    sf = (torch.zeros if plan is not None or terms > 1 or bn == 64 else torch.empty)(row_tiles * (K // 64) * 512, dtype=torch.uint8, device=dev)
     g = torch.empty(M * terms, dtype=torch.float32, device=dev)
     N.call("sl_nvfp4_quantize_rows", q.data_ptr(), sf.data_ptr(), g.data_ptr(), x.data_ptr(), N.ptr(src), M, x.shape[0], K,
            x.stride(0), terms, N.ptr(plan.offsets) if plan else 0, N.ptr(plan.pad) if plan else 0, plan.groups if plan else 1, bn,
