@@ -17,8 +17,9 @@
 //            scale.  One accumulator per code group (the key's group scale is applied to the group sums by the thread
 //            that owns the key's TMEM lane) and one `kind::f16` accumulator for the rope part: 5 x 16 columns.
 //   softmax  two threads own key j (four heads each): s = sum_g scale[g] (hi_g + lo_g / 16) / 2^e + rope, in log2 units.  The running
-//            maximum is a reference that is only raised when a value exceeds it by more than 2^8; exponentials are
-//            taken relative to it.  The value scale is folded into P (P_g = p * scale[g]); to keep P_g inside the
+//            maximum is a reference that is only raised when a value exceeds it by more than 2^8, and then to 2^6 below
+//            the largest value seen; exponentials are taken relative to it (at most 2^8, and resolved down to 2^-19 of the
+//            row maximum by the two e4m3 terms).  The value scale is folded into P (P_g = p * scale[g]); to keep P_g inside the
 //            e4m3 range whatever the scales are, the reference tracks s + log2(max_g scale[g]).  P_g is again two
 //            e4m3 terms and is written as the K-major B operand [16 columns x 128 keys] of the second product.
 //   O^T      the same code tiles read MN-major (128 latent dims of a group on the MMA rows, keys on K): four
@@ -43,6 +44,8 @@ constexpr int STAGE_K8 = NG * K8_TILE;           // 65536
 constexpr int KR_TILE = TILE * 2 * DR;           // 16384
 constexpr int B_TILE = NCOL * 128;               // 2048: a 16-row B operand with 128-byte rows
 constexpr float RAISE = 8.f;                     // log2 units: exponentials stay below 2^8
+constexpr float HEADROOM = 6.f;                  // a raised reference sits this far below the largest value seen: the two-term
+                                                 // e4m3 form of P resolves 2^-13, i.e. 2^-19 of the row maximum
 constexpr uint32_t TMEM_COLS = 256, COL_S = 0, COL_O = 96;
 
 constexpr int MAX_TOPK = 2048;
@@ -344,7 +347,8 @@ __global__ void __launch_bounds__(THREADS, 2) sparse_mla_tc_kernel(SparseMlaPara
 #pragma unroll
                 for (int hh = 0; hh < HPT; ++hh) {
                     const int h = hb + hh;
-                    const float mn = fmaxf(fmaxf(mref[hh], fmaxf(s_wred[h], s_wred[NH + h])), fmaxf(s_wred[2 * NH + h], s_wred[3 * NH + h]));
+                    const float tmax = fmaxf(fmaxf(s_wred[h], s_wred[NH + h]), fmaxf(s_wred[2 * NH + h], s_wred[3 * NH + h]));
+                    const float mn = fmaxf(mref[hh], tmax - HEADROOM);
                     f[hh] = mn == -INFINITY ? 1.f : exp2f(mref[hh] - mn);
                     mref[hh] = mn;
                 }

@@ -386,7 +386,8 @@ def test_sparse_mla_keys_on_m(h, T, q_scale):
     close(lse[live], lse2[live], tol=1e-3, what="lse, keys-on-M vs heads-on-M")
 
 
-@pytest.mark.parametrize("h,T,q_scale,kv_scale", [(8, 160, 1.0, 2.0), (8, 300, 4.0, 2.0), (16, 150, 1.0, 0.05), (4, 310, 0.3, 30.0)])
+@pytest.mark.parametrize("h,T,q_scale,kv_scale", [(8, 160, 1.0, 2.0), (8, 300, 4.0, 2.0), (16, 150, 1.0, 0.05), (4, 310, 0.3, 30.0),
+                                                  (8, 200, 2.0, 1.0)])
 def test_sparse_mla_prefill_on_tcgen05(h, T, q_scale, kv_scale):
     """Prefill-sized sparse MLA (no key split) runs on tcgen05 straight from the e4m3 cache rows: query and
     probabilities as two e4m3 terms, code tiles read K-major for the scores and MN-major for the values.  Full, ragged,
@@ -429,6 +430,45 @@ def test_sparse_mla_prefill_on_tcgen05(h, T, q_scale, kv_scale):
         N.kernels().sl_sparse_mla_set_tcgen05(1)
     close(o, o2, what="tcgen05 vs mma.sync")
     close(lse[live], lse2[live], tol=2e-3, what="lse, tcgen05 vs mma.sync")
+
+
+def test_sparse_mla_on_tcgen05_keeps_a_long_tail_of_small_weights():
+    """One key takes about 90 % of the softmax mass and two thousand keys share the rest at about 5e-5 each: the
+    two-term e4m3 probabilities must still carry that tail (their common value component is visible in the output)."""
+    from slopllm_b200.ops import tcgen05
+    h, T = 8, 160
+    cfg = mini_cfg(num_attention_heads=h, index_topk=2048)
+    ops, ref = cuda_ops(cfg), RefOps(cfg)
+    g = torch.Generator(device=DEV).manual_seed(4242)
+    Rr, Dr, k = cfg.kv_lora_rank, cfg.qk_rope_head_dim, cfg.index_topk
+    nslots = 4096
+    lat = torch.zeros(nslots, Rr, device=DEV)
+    lat[:, :Rr // 2] = torch.randn(nslots, Rr // 2, device=DEV, generator=g)
+    lat[:, Rr // 2:] = 1.0                                   # the tail's common value component
+    heavy = torch.arange(T, device=DEV)                     # token t's dominant key is slot t
+    lat[heavy, Rr // 2:] = 0.0
+    cache = type("C", (), {})()
+    cache.kv = quant.pack_kv_rows(lat, torch.zeros(nslots, Dr, device=DEV), cfg.kv_quant_group)
+    deq, _ = quant.unpack_kv_rows(cache.kv, Rr, Dr, cfg.kv_quant_group)
+    k0 = deq[heavy]                                          # [T, R]
+    alpha = 10.0 / ((k0 * k0).sum(-1, keepdim=True) * cfg.softmax_scale)
+    q_abs = (alpha * k0)[:, None, :].expand(T, h, Rr).contiguous().to(torch.bfloat16)
+    q_pe = torch.zeros(T, h, Dr, device=DEV, dtype=torch.bfloat16)
+    slots = torch.empty(T, k, dtype=torch.int32, device=DEV)
+    for t in range(T):
+        others = torch.randperm(nslots - T, device=DEV, generator=g)[:k - 1] + T
+        slots[t] = torch.cat([others[:1000], heavy[t:t + 1], others[1000:]]).to(torch.int32)    # the dominant key sits in a middle tile
+    lengths = torch.full((T,), k, dtype=torch.int32, device=DEV)
+    assert ops._mla_splits(T, h) == 1
+    o, lse = ops.sparse_mla(q_abs, q_pe, cache, slots, lengths)
+    tcgen05.check_errors(torch.device(DEV))
+    eo, elo = ref.sparse_mla(q_abs, q_pe, cache, slots, lengths)
+    tail = eo[:, :, Rr // 2:].float().mean().item()
+    assert 0.02 < tail < 0.3, tail                           # the scenario is what the docstring says
+    close(o, eo, what="sparse mla o with a long tail")
+    rel = ((o[:, :, Rr // 2:].float().mean() - tail).abs() / tail).item()
+    assert rel < 0.02, rel
+    close(lse, elo, tol=2e-3, what="lse with a long tail")
 
 
 @pytest.mark.parametrize("T,h", [(1, 8), (3, 8), (8, 8), (13, 4), (32, 8)])
