@@ -672,8 +672,8 @@ SL_API int sl_sparse_mla_split_mma(const void* params, int T, cudaStream_t s) {
     if (p->R % 64 != 0 || p->R > 512 || (p->R + p->Dr) % 16 != 0 || p->Dr % 2 != 0 || p->group % 4 != 0) return -1;
     if (g_transposed_enabled && transposed_ok(*p)) {
         if (p->o_final != nullptr && p->splits != 1) return -1;
-        if (p->o_final != nullptr) {
-            const int r = sparse_mla_tcgen05(p, T, s);
+        {
+            const int r = sparse_mla_tcgen05(p, T, s);           // -2: not a launch it covers
             if (r != -2) return r;
         }
         return p->h <= 8 ? launch_transposed<1>(*p, T, s) : launch_transposed<2>(*p, T, s);

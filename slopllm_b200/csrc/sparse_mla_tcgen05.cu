@@ -163,11 +163,17 @@ __global__ void __launch_bounds__(THREADS, 2) sparse_mla_tc_kernel(SparseMlaPara
         cp_async_commit();
     };
 
-    const int items = T * head_groups;
+    // work item = (query token, head group, key split); with one split the item writes the final bf16 output, with
+    // several (decode) its normalised fp32 partial and log-sum-exp, which the merge kernel combines
+    const int items = T * head_groups * p.splits;
     for (int item = blockIdx.x; item < items && ok; item += gridDim.x) {
-        const int t = item / head_groups, h0 = (item % head_groups) * NH, nh = min(NH, p.h - h0);
-        const int L = min(p.lengths[t], p.topk);
-        const int* slots = p.slots + (size_t)t * p.topk;
+        const int split = item % p.splits, th = item / p.splits;
+        const int t = th / head_groups, h0 = (th % head_groups) * NH, nh = min(NH, p.h - h0);
+        const int Lt = min(p.lengths[t], p.topk);
+        const int per = (Lt + p.splits - 1) / p.splits;
+        const int j_begin = min(Lt, split * per);
+        const int L = min(Lt, j_begin + per) - j_begin;            // keys of this item
+        const int* slots = p.slots + (size_t)t * p.topk + j_begin;
         const int ntiles = (L + TILE - 1) / TILE;
         __syncthreads();                                           // the previous item is done with Q, the reference and the sums
 
@@ -429,14 +435,22 @@ __global__ void __launch_bounds__(THREADS, 2) sparse_mla_tc_kernel(SparseMlaPara
             if (h < nh) {
                 const float l = s_wred[h] + s_wred[NH + h] + s_wred[2 * NH + h] + s_wred[3 * NH + h];
                 const float inv = l > 0.f ? 1.f / l : 0.f;
-                bf16* o = p.o_final + ((size_t)t * p.h + h0 + h) * R + key;
+                if (p.o_final != nullptr) {
+                    bf16* o = p.o_final + ((size_t)t * p.h + h0 + h) * R + key;
 #pragma unroll
-                for (int g = 0; g < NG; ++g) o[g * GS] = __float2bfloat16(fmaf(o_reg[g][1][hh], 0.0625f, o_reg[g][0][hh]) * inv);
+                    for (int g = 0; g < NG; ++g) o[g * GS] = __float2bfloat16(fmaf(o_reg[g][1][hh], 0.0625f, o_reg[g][0][hh]) * inv);
+                } else {
+                    float* o = p.o_part + (((size_t)t * p.h + h0 + h) * p.splits + split) * R + key;
+#pragma unroll
+                    for (int g = 0; g < NG; ++g) o[g * GS] = fmaf(o_reg[g][1][hh], 0.0625f, o_reg[g][0][hh]) * inv;
+                }
             }
         }
-        if (tid < nh && p.lse_final != nullptr) {
+        if (tid < nh) {
             const float l = s_wred[tid] + s_wred[NH + tid] + s_wred[2 * NH + tid] + s_wred[3 * NH + tid];
-            p.lse_final[(size_t)t * p.h + h0 + tid] = l > 0.f ? (s_mref[tid] + log2f(l)) * 0.6931471805599453f : -INFINITY;
+            const float lse = l > 0.f ? (s_mref[tid] + log2f(l)) * 0.6931471805599453f : -INFINITY;
+            if (p.o_final == nullptr) p.lse_part[((size_t)t * p.h + h0 + tid) * p.splits + split] = lse;
+            else if (p.lse_final != nullptr) p.lse_final[(size_t)t * p.h + h0 + tid] = lse;
         }
     }
     cp_async_wait_all();
@@ -448,12 +462,14 @@ __global__ void __launch_bounds__(THREADS, 2) sparse_mla_tc_kernel(SparseMlaPara
     }
 }
 
-bool g_mla_tcgen05 = true;
+int g_mla_tcgen05 = 3;            // bit 0: launches that write the final output (prefill); bit 1: key-split launches (decode)
 
 }  // namespace
 
 int sparse_mla_tcgen05(const SparseMlaParams* p, int T, cudaStream_t s) {
-    if (!g_mla_tcgen05 || p->o_final == nullptr || p->splits != 1 || p->err == nullptr) return -2;
+    const bool direct = p->o_final != nullptr;
+    if (p->err == nullptr || !(g_mla_tcgen05 & (direct ? 1 : 2))) return -2;
+    if (direct ? p->splits != 1 : (p->splits < 1 || p->o_part == nullptr || p->lse_part == nullptr)) return -2;
     if (p->R != R || p->group != GS || p->Dr != DR || p->h > 2 * NH || p->topk <= 0 || p->topk > MAX_TOPK) return -2;
     if (((uintptr_t)p->q_abs & 15) != 0 || ((uintptr_t)p->q_pe & 15) != 0 || ((uintptr_t)p->kv_cache & 15) != 0) return -2;
     static bool attr_done = false;
@@ -462,11 +478,17 @@ int sparse_mla_tcgen05(const SparseMlaParams* p, int T, cudaStream_t s) {
         attr_done = true;
     }
     const int head_groups = (p->h + NH - 1) / NH;
-    const int items = T * head_groups;
+    const long long items = (long long)T * head_groups * p->splits;
     const int max_ctas = 2 * 148;
-    sl_launch(sparse_mla_tc_kernel, dim3(items < max_ctas ? items : max_ctas), THREADS, SMEM_BYTES, s, *p, T, head_groups);
+    sl_launch(sparse_mla_tc_kernel, dim3((unsigned)(items < max_ctas ? items : max_ctas)), THREADS, SMEM_BYTES, s, *p, T, head_groups);
     return SL_LAUNCH_CHECK();
 }
 
-// 0 keeps the mma.sync kernels at prefill too (comparison runs); default 1.
-SL_API void sl_sparse_mla_set_tcgen05(int on) { g_mla_tcgen05 = on != 0; }
+// Which launches take the tcgen05 kernel: 0 none (the mma.sync kernels everywhere, comparison runs), 1 those that write the
+// final output (prefill), 3 (default) also the key-split launches of decode.
+SL_API void sl_sparse_mla_set_tcgen05(int mode) { g_mla_tcgen05 = mode; }
+
+// 1 when a key-split launch with these row parameters takes the tcgen05 kernel (one 128-key tile per split is its unit of work).
+SL_API int sl_sparse_mla_tcgen05_decode_ok(int R_, int group, int Dr, int h, int topk) {
+    return ((g_mla_tcgen05 & 2) && R_ == R && group == GS && Dr == DR && h <= 2 * NH && topk > 0 && topk <= MAX_TOPK) ? 1 : 0;
+}

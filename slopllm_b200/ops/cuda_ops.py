@@ -338,7 +338,12 @@ class CudaOps:
         """Split the selected keys so that the grid fills the 148 SMs a few times over
         (the reference's `sparseMlaChunksPerBlock`, `src/sparse-mla-planner.ts:1-21`)."""
         from ..runtime.planner import sparse_mla_splits
-        return sparse_mla_splits(T, h, self.cfg.index_topk)
+        c = self.cfg
+        splits = sparse_mla_splits(T, h, c.index_topk)
+        if splits > 1 and N.kernels().sl_sparse_mla_tcgen05_decode_ok(c.kv_lora_rank, c.kv_quant_group, c.qk_rope_head_dim, h,
+                                                                      c.index_topk):
+            splits = max(2, min(splits, (c.index_topk + 127) // 128))      # the tcgen05 kernel's unit of work is a 128-key tile
+        return splits
 
     def sparse_mla_partials(self, q_abs, q_pe, layer_cache, slots, lengths):
         c = self.cfg
@@ -351,7 +356,7 @@ class CudaOps:
                               slots=slots.data_ptr(), lengths=lengths.data_ptr(), h=h, R=Rr, Dr=c.qk_rope_head_dim,
                               group=c.kv_quant_group, topk=slots.shape[1], splits=splits, sm_scale=c.softmax_scale,
                               o_part=o_part.data_ptr(), lse_part=lse_part.data_ptr(), num_slots=layer_cache.kv.shape[0],
-                              guard=self._guard(dev))
+                              guard=self._guard(dev), err=self._guard(dev) - 16)
         c_ok = Rr % 64 == 0 and Rr <= 512 and (Rr + c.qk_rope_head_dim) % 16 == 0
         N.call("sl_sparse_mla_split_mma" if c_ok else "sl_sparse_mla_split", C.byref(p), T, N.stream())
         return o_part, lse_part

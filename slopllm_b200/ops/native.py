@@ -52,7 +52,11 @@ def kernels() -> C.CDLL:
     lib.sl_sparse_mla_set_transposed(0 if os.environ.get("SLOPLLM_B200_MLA_TRANSPOSED", "1") == "0" else 1)
     lib.sl_sparse_mla_set_tcgen05.argtypes = [i32]
     lib.sl_sparse_mla_set_tcgen05.restype = None
-    lib.sl_sparse_mla_set_tcgen05(0 if os.environ.get("SLOPLLM_B200_MLA_TCGEN05", "1") == "0" else 1)
+    # SLOPLLM_B200_MLA_TCGEN05: 0 = mma.sync everywhere, prefill = tcgen05 only where the kernel writes the final output,
+    # anything else (default) = also the key-split launches of decode
+    lib.sl_sparse_mla_set_tcgen05({"0": 0, "prefill": 1}.get(os.environ.get("SLOPLLM_B200_MLA_TCGEN05", "1"), 3))
+    lib.sl_sparse_mla_tcgen05_decode_ok.argtypes = [i32, i32, i32, i32, i32]
+    lib.sl_sparse_mla_tcgen05_decode_ok.restype = i32
     return lib
 
 

@@ -382,7 +382,7 @@ def test_sparse_mla_keys_on_m(h, T, q_scale):
         o2, lse2 = ops.sparse_mla(q_abs, q_pe, cache, slots, lengths)
     finally:
         N.kernels().sl_sparse_mla_set_transposed(1)
-    close(o, o2, what="keys-on-M vs heads-on-M")
+    close(o, o2, tol=2e-2, what="keys-on-M vs heads-on-M")        # two approximations, each within 1e-2 of the fp32 definition
     close(lse[live], lse2[live], tol=1e-3, what="lse, keys-on-M vs heads-on-M")
 
 
@@ -427,7 +427,7 @@ def test_sparse_mla_prefill_on_tcgen05(h, T, q_scale, kv_scale):
     try:
         o2, lse2 = ops.sparse_mla(q_abs, q_pe, cache, slots, lengths)
     finally:
-        N.kernels().sl_sparse_mla_set_tcgen05(1)
+        N.kernels().sl_sparse_mla_set_tcgen05(3)
     close(o, o2, what="tcgen05 vs mma.sync")
     close(lse[live], lse2[live], tol=2e-3, what="lse, tcgen05 vs mma.sync")
 
