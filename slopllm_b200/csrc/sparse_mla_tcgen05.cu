@@ -177,6 +177,13 @@ __global__ void __launch_bounds__(THREADS, 2) sparse_mla_tc_kernel(SparseMlaPara
         const int ntiles = (L + TILE - 1) / TILE;
         __syncthreads();                                           // the previous item is done with Q, the reference and the sums
 
+        // this warp's query head: its loads are in flight while the slots arrive
+        uint4 qa = make_uint4(0u, 0u, 0u, 0u), qb = qa, qr4 = qa;
+        if (warp < nh) {
+            const uint4* src = reinterpret_cast<const uint4*>(p.q_abs + ((size_t)t * p.h + h0 + warp) * R + lane * 16);
+            qa = __ldg(src); qb = __ldg(src + 1);
+            if (lane < 8) qr4 = __ldg(reinterpret_cast<const uint4*>(p.q_pe + ((size_t)t * p.h + h0 + warp) * DR + lane * 8));
+        }
         // the token's slots, padded with -1 to whole tiles
         for (int j = tid; j < ntiles * TILE; j += THREADS) {
             int sl = j < L ? slots[j] : -1;
@@ -191,9 +198,7 @@ __global__ void __launch_bounds__(THREADS, 2) sparse_mla_tc_kernel(SparseMlaPara
             uint4 hi = make_uint4(0u, 0u, 0u, 0u), lo = hi;
             float inv = 1.f;
             if (hh < nh) {
-                const uint4* src = reinterpret_cast<const uint4*>(p.q_abs + ((size_t)t * p.h + h0 + hh) * R + lane * 16);
-                const uint4 a = src[0], b = src[1];
-                const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+                const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
                 float v[16];
                 float amax = 0.f;
 #pragma unroll
@@ -235,8 +240,7 @@ __global__ void __launch_bounds__(THREADS, 2) sparse_mla_tc_kernel(SparseMlaPara
             if (lane < 8) {
                 uint4 rv = make_uint4(0u, 0u, 0u, 0u);
                 if (hh < nh) {
-                    const uint4 a = *reinterpret_cast<const uint4*>(p.q_pe + ((size_t)t * p.h + h0 + hh) * DR + lane * 8);
-                    const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+                    const uint32_t w[4] = {qr4.x, qr4.y, qr4.z, qr4.w};
                     uint32_t o[4];
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
