@@ -49,6 +49,7 @@ constexpr float HEADROOM = 6.f;                  // a raised reference sits this
 constexpr uint32_t TMEM_COLS = 256, COL_S = 0, COL_O = 96;
 
 constexpr int MAX_TOPK = 2048;
+constexpr int MAX_HEADS = 128;               // any head count in groups of 8 (each group gathers the rows again)
 
 struct Smem {
     static constexpr int K8 = 0;
@@ -474,7 +475,7 @@ int sparse_mla_tcgen05(const SparseMlaParams* p, int T, cudaStream_t s) {
     const bool direct = p->o_final != nullptr;
     if (p->err == nullptr || !(g_mla_tcgen05 & (direct ? 1 : 2))) return -2;
     if (direct ? p->splits != 1 : (p->splits < 1 || p->o_part == nullptr || p->lse_part == nullptr)) return -2;
-    if (p->R != R || p->group != GS || p->Dr != DR || p->h > 2 * NH || p->topk <= 0 || p->topk > MAX_TOPK) return -2;
+    if (p->R != R || p->group != GS || p->Dr != DR || p->h > MAX_HEADS || p->topk <= 0 || p->topk > MAX_TOPK) return -2;
     if (((uintptr_t)p->q_abs & 15) != 0 || ((uintptr_t)p->q_pe & 15) != 0 || ((uintptr_t)p->kv_cache & 15) != 0) return -2;
     static bool attr_done = false;
     if (!attr_done) {
@@ -494,5 +495,5 @@ SL_API void sl_sparse_mla_set_tcgen05(int mode) { g_mla_tcgen05 = mode; }
 
 // 1 when a key-split launch with these row parameters takes the tcgen05 kernel (one 128-key tile per split is its unit of work).
 SL_API int sl_sparse_mla_tcgen05_decode_ok(int R_, int group, int Dr, int h, int topk) {
-    return ((g_mla_tcgen05 & 2) && R_ == R && group == GS && Dr == DR && h <= 2 * NH && topk > 0 && topk <= MAX_TOPK) ? 1 : 0;
+    return ((g_mla_tcgen05 & 2) && R_ == R && group == GS && Dr == DR && h <= MAX_HEADS && topk > 0 && topk <= MAX_TOPK) ? 1 : 0;
 }
