@@ -436,10 +436,14 @@ __device__ __forceinline__ float e2m1_value(uint32_t code) {
     return (code & 8u) ? -mag : mag;
 }
 
-__global__ void __launch_bounds__(256) nvfp4_quantize_rows_kernel(const QuantParams p) {
+// `lpr` = 0: one block per row (one thread per 64 values).  Short rows (at most 2048 values) take `lpr` in {4, 8, 16, 32}
+// lanes per row and 256 / lpr rows per block instead: a block per 256-value row would run four threads of a warp.
+__global__ void __launch_bounds__(256) nvfp4_quantize_rows_kernel(const QuantParams p, int lpr, int launch_rows) {
     pdl_grid_sync();
     __shared__ float scratch[33];
-    const int m = blockIdx.x, ks = threadIdx.x;
+    const int m = lpr ? blockIdx.x * (256 / lpr) + (int)threadIdx.x / lpr : (int)blockIdx.x;
+    const int ks = lpr ? (int)threadIdx.x % lpr : (int)threadIdx.x;
+    if (m >= launch_rows) return;
     if (p.num_rows != nullptr && m >= __ldg(p.num_rows)) return;
     const int KT = p.K / 64;
     if (m >= p.rows) {                             // padding rows of the last scale tile (ungrouped, one term): zero scales
@@ -488,9 +492,16 @@ __global__ void __launch_bounds__(256) nvfp4_quantize_rows_kernel(const QuantPar
             for (int i = 0; i < 16; ++i) a = fmaxf(a, fabsf(v[16 * b + i]));
             bm[b] = a;
         }
-        const float amax = block_max(fmaxf(fmaxf(bm[0], bm[1]), fmaxf(bm[2], bm[3])), scratch);
+        float amax = fmaxf(fmaxf(bm[0], bm[1]), fmaxf(bm[2], bm[3]));
+        if (lpr) {                                 // the row's lanes are an aligned group of one warp
+            const unsigned lane = threadIdx.x & 31u;
+            const unsigned gmask = (lpr == 32 ? 0xffffffffu : ((1u << lpr) - 1u)) << (lane & ~(unsigned)(lpr - 1));
+            for (int o = lpr >> 1; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(gmask, amax, o));
+        } else {
+            amax = block_max(amax, scratch);
+        }
         const float gs = amax > 0.f ? amax / (6.f * 448.f) : 1.f;
-        if (threadIdx.x == 0) p.g[orow] = gs;
+        if (ks == 0) p.g[orow] = gs;
         if (ks < KT) {
             const float inv_g = 1.f / gs;
             uint32_t sc_word = 0, packed[8];
@@ -844,7 +855,14 @@ SL_API int sl_nvfp4_quantize_rows(void* q, void* sf, void* g, const void* x, con
     const int threads = (K / 64 + 31) / 32 * 32;
     // ungrouped rows of one term: the blocks past `rows` zero the scales of the last tile's padding rows, so the caller
     // need not clear the scale tiles first
-    const int blocks = (offsets == nullptr && terms == 1) ? (rows + bn - 1) / bn * bn : rows;
-    sl_launch(nvfp4_quantize_rows_kernel, blocks, threads, 0, s, p);
+    const int launch_rows = (offsets == nullptr && terms == 1) ? (rows + bn - 1) / bn * bn : rows;
+    if (K <= 2048) {
+        int lpr = 4;
+        while (lpr * 64 < K) lpr <<= 1;
+        const int rpb = 256 / lpr;
+        sl_launch(nvfp4_quantize_rows_kernel, (launch_rows + rpb - 1) / rpb, 256, 0, s, p, lpr, launch_rows);
+    } else {
+        sl_launch(nvfp4_quantize_rows_kernel, launch_rows, threads, 0, s, p, 0, launch_rows);
+    }
     return (int)cudaGetLastError();
 }
