@@ -58,6 +58,9 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out_f32: bool = False, bn: int =
     Nn = w.shape[0]
     if bn == 0:
         bn = 256 if Nn >= 512 else 128
+        row_tiles = (M + 127) // 128
+        while bn > 64 and row_tiles * ((Nn + bn - 1) // bn) < 148:       # fewer tiles than SMs: narrower tiles (router: 256 columns)
+            bn //= 2
     pad = 4 if out_f32 else 8                        # 16-byte aligned rows for the vector stores
     ld = (Nn + pad - 1) // pad * pad
     y = torch.empty(M, ld, dtype=torch.float32 if out_f32 else torch.bfloat16, device=x.device)[:, :Nn]
