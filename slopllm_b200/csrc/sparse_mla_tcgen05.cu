@@ -1,23 +1,24 @@
-// Sparse MLA attention at prefill on the 5th-generation tensor cores, straight from the FP8 cache rows.
+// Sparse MLA attention (prefill and decode) on the 5th-generation tensor cores, straight from the FP8 cache rows.
 //
 //   o[t, h, :] = sum_j softmax_j(q[t, h] . k[j]) v[j]     j over the token's selected rows (top-k), 8 heads per CTA
 //
 // A cache row is 656 bytes: 512 e4m3 latent codes, four fp32 scales (one per 128 codes), 64 bf16 rope values.  The
 // mma.sync kernels spend their issue slots expanding those codes to f16 in shared memory; here the codes are never
-// expanded.  One CTA works on one (query token, group of 8 heads) at a time and walks the token's rows in tiles of
-// 128 keys:
+// expanded.  One CTA works on one (query token, group of 8 heads, key split) at a time and walks that split's rows in
+// tiles of 128 keys.  With one split (prefill) the item writes the final bf16 rows; with several (decode: one tile per
+// split) its normalised fp32 partial and log-sum-exp, which the merge kernel combines (`csrc/sparse_mla.cu`).
 //
 //   gather   `cp.async` (16 bytes, zero fill for rows past the token's length) copies each row's four 128-byte code
 //            groups into four K-major 128-byte-swizzled tiles [128 keys x 128 bytes], the rope part into a fifth
 //            tile and the scales aside.  A warp copies whole rows (lane = 16-byte piece).  A CTA holds one key tile
 //            and runs its phases one after the other; two CTAs share an SM (2 x 110 KB of shared memory, 2 x 256
-//            TMEM columns, 2 x 128 threads with the whole register file), so one gathers while the other computes.
+//            TMEM columns, 2 x 256 threads with the whole register file), so one gathers while the other computes.
 //   S^T      keys on the 128 MMA rows, N = 16 columns: `kind::f8f6f4` needs both operands in 8 bits, so the query is
 //            split into two e4m3 terms (q * 2^e = hi + lo / 16; columns h and 8 + h) with a per-head power-of-two
 //            scale.  One accumulator per code group (the key's group scale is applied to the group sums by the thread
 //            that owns the key's TMEM lane) and one `kind::f16` accumulator for the rope part: 5 x 16 columns.
-//   softmax  two threads own key j (four heads each): s = sum_g scale[g] (hi_g + lo_g / 16) / 2^e + rope, in log2 units.  The running
-//            maximum is a reference that is only raised when a value exceeds it by more than 2^8, and then to 2^6 below
+//   softmax  two threads own key j (four heads each): s = sum_g scale[g] (hi_g + lo_g / 16) / 2^e + rope, in log2
+//            units.  The running maximum is a reference that is only raised when a value exceeds it by more than 2^8, and then to 2^6 below
 //            the largest value seen; exponentials are taken relative to it (at most 2^8, and resolved down to 2^-19 of the
 //            row maximum by the two e4m3 terms).  The value scale is folded into P (P_g = p * scale[g]); to keep P_g inside the
 //            e4m3 range whatever the scales are, the reference tracks s + log2(max_g scale[g]).  P_g is again two
@@ -29,7 +30,8 @@
 // Every mbarrier wait is made by one thread with a time limit and its outcome is shared through a block barrier, so
 // a wait that runs out sets the error word and unwinds the whole CTA (copies drained, TMEM freed).
 //
-// Reference: the vendored prefill kernel behind `csrc/glm_sparse_mla.cu:34-126` (bf16 `mma.sync` on expanded rows).
+// Reference: the vendored decode / prefill kernels behind `csrc/glm_sparse_mla.cu:34-126` (bf16 `mma.sync` on expanded
+// rows, split-K over the selected rows + combine).
 #include "sparse_mla.cuh"
 #include "tcgen05.cuh"
 
