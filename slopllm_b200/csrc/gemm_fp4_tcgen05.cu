@@ -20,10 +20,10 @@
 //        where pad[] rounds every group up to a multiple of BN rows: tile p / BN, row p % BN.  Scale columns in TMEM
 //        then always start at a multiple of four, which the instruction requires.
 //
-// Warp roles (320 threads): warp 0 issues TMA / bulk copies into a multi-stage ring, warp 1 copies scales into TMEM and
-// issues the MMAs, warps 2-9 read the accumulators out of TMEM (one lane = one weight row; two warps per TMEM lane quarter,
-// alternate 32-column chunks each: one epilogue warp per scheduler issued at 0.3 instructions per cycle and bound tiles
-// with a short reduction) and store the transposed tile.  Two accumulator buffers when TMEM allows, so a tile's epilogue overlaps the next tile's MMAs.  No cluster
+// Warp roles: warp 0 issues TMA / bulk copies into a multi-stage ring, warp 1 copies scales into TMEM and issues the MMAs,
+// the other 4 x BN / 32 warps read the accumulators out of TMEM (one lane = one weight row; one warp per TMEM lane quarter
+// and 32-column chunk: with four epilogue warps in all, one per scheduler issued at 0.3 instructions per cycle and bound
+// tiles with a short reduction) and store the transposed tile.  Two accumulator buffers when TMEM allows, so a tile's epilogue overlaps the next tile's MMAs.  No cluster
 // multicast.  Every wait is bounded (error code, TMEM freed, normal return).
 //
 // Reference counterpart: `coop_moe_kernel` (`csrc/glm_mma_moe_coop.cu:351`), which uses the warp-level block-scaled FP4
@@ -37,7 +37,6 @@ namespace {
 constexpr int BM = 128;            // weight rows per tile
 constexpr int BKB = 128;           // bytes of packed codes per row and stage = 256 reduction indices = 4 instructions
 constexpr int KSTEPS = 4;
-constexpr int FP4_EPI_WARPS = 8, FP4_THREADS = (2 + FP4_EPI_WARPS) * 32;
 
 struct Fp4Tile {
     int a_row0;                    // first weight row of the tile (the paired "up" tile starts pair_rows further)
@@ -51,6 +50,8 @@ struct Fp4Tile {
 template <int BN, int PAIR>
 struct Fp4Cfg {
     static constexpr int NA = PAIR ? 2 : 1;
+    static constexpr int EPI_PER_Q = BN / 32;                 // epilogue warps per TMEM lane quarter: one per 32-column chunk
+    static constexpr int EPI_WARPS = 4 * EPI_PER_Q, THREADS = (2 + EPI_WARPS) * 32;
     static constexpr int A_BYTES = BM * BKB, SF_BYTES = KSTEPS * 512, B_BYTES = BN * BKB;
     static constexpr int TX = NA * (A_BYTES + SF_BYTES) + B_BYTES + SF_BYTES;        // bytes that land per stage
     static constexpr int STAGE = (TX + 1023) / 1024 * 1024;
@@ -88,7 +89,7 @@ struct Fp4Params {
 };
 
 template <int BN, int PAIR>
-__global__ void __launch_bounds__(FP4_THREADS) gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+__global__ void __launch_bounds__(Fp4Cfg<BN, PAIR>::THREADS) gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                                                        const __grid_constant__ CUtensorMap tmA2, const Fp4Params p) {
     using Cfg = Fp4Cfg<BN, PAIR>;
     constexpr int STAGES = Cfg::STAGES, NA = Cfg::NA, NBUF = Cfg::NBUF;
@@ -112,7 +113,7 @@ __global__ void __launch_bounds__(FP4_THREADS) gemm_fp4_kernel(const __grid_cons
         tc::tma_prefetch_desc(&tmB);
         tc::tma_prefetch_desc(&tmA2);
         for (int s = 0; s < STAGES; ++s) { tc::mbar_init(&full[s], 1); tc::mbar_init(&empty[s], 1); }
-        for (int b = 0; b < 2; ++b) { tc::mbar_init(&tmem_full[b], 1); tc::mbar_init(&tmem_empty[b], FP4_EPI_WARPS); }
+        for (int b = 0; b < 2; ++b) { tc::mbar_init(&tmem_full[b], 1); tc::mbar_init(&tmem_empty[b], Cfg::EPI_WARPS); }
         tc::mbar_fence_init();
     }
     if (warp == 1) {
@@ -197,7 +198,7 @@ __global__ void __launch_bounds__(FP4_THREADS) gemm_fp4_kernel(const __grid_cons
         }
     } else {
         const int q = warp & 3;               // TMEM lane quarter of this warp
-        const int chunk_half = (warp - 2) >> 2; // which of the two warps of the quarter: it takes the 32-column chunks c with c % 2 == chunk_half
+        const int chunk_half = (warp - 2) >> 2; // which of the quarter's warps: it takes the 32-column chunk of that index
         // Everything the epilogue of a tile reads from global memory (its table entry, the weights' global scales, the
         // token rows' global scales) is fetched one tile ahead, while the previous tile is being stored: with a short
         // reduction (one or two stages per tile) those dependent loads would otherwise be the tile's critical path.
@@ -241,7 +242,7 @@ __global__ void __launch_bounds__(FP4_THREADS) gemm_fp4_kernel(const __grid_cons
 #pragma unroll
             for (int c = 0; c < BN / 32; ++c) {
                 const int c0 = c * 32;
-                if ((c & 1) == chunk_half && c0 < t.b_valid) {           // (uniform over the warp)
+                if (c == chunk_half && c0 < t.b_valid) {                 // (uniform over the warp)
                     const float my_gb = cur.gb[c];                       // lane i holds token c0 + i's global scale
                     uint32_t r0[32], r1[32];
                     tc::tmem_ld_32x32(t_acc + c0, r0);
@@ -348,7 +349,7 @@ int launch_fp4(const void* W, int w_rows, const void* X, int x_rows, const Fp4Pa
         attr_set = true;
     }
     const int grid = std::min(max_tiles, fp4_sm_count());
-    sl_launch(kern, grid, FP4_THREADS, Cfg::SMEM, s, tmA, tmB, tmA2, p);
+    sl_launch(kern, grid, Cfg::THREADS, Cfg::SMEM, s, tmA, tmB, tmA2, p);
     return (int)cudaGetLastError();
 }
 
