@@ -14,6 +14,8 @@ from typing import List, Optional
 import torch
 import torch.distributed as dist
 
+_PREFILL_AR_FP32 = os.environ.get("SLOPLLM_B200_PREFILL_AR_FP32", "0") == "1"
+
 
 @dataclass
 class ParallelContext:
@@ -198,8 +200,21 @@ class Comm:
         """sum over ranks of `partial`, add to `residual`, RMSNorm.  Returns (normed, residual').
         `want_perm`: the consumer is an NVFP4 tensor-core kernel; a CUDA backend then also emits its permuted operand."""
         if want_perm and getattr(ops, "name", "") == "cuda":
-            return ops.add_rmsnorm(self.all_reduce(partial), residual, weight, eps, want_perm=True)
-        return ops.add_rmsnorm(self.all_reduce(partial), residual, weight, eps)
+            return ops.add_rmsnorm(self._reduce_partial(partial), residual, weight, eps, want_perm=True)
+        return ops.add_rmsnorm(self._reduce_partial(partial), residual, weight, eps)
+
+    PREFILL_AR_BF16_MIN_ROWS = 33
+
+    def _reduce_partial(self, partial: torch.Tensor) -> torch.Tensor:
+        """Sum of the ranks' partial rows.  Prefill-sized fp32 partials on GPUs cross the links as bf16 (half the bytes of
+        the fp32 library all-reduce; the reference's reduce kernels move bf16 too, `csrc/glm_p2p.cu:627-680`); the sum is added
+        to the fp32 residual by the norm kernel.  `SLOPLLM_B200_PREFILL_AR_FP32=1` keeps fp32 on the wire."""
+        if (self.ctx.world > 1 and partial.is_cuda and partial.dtype == torch.float32
+                and partial.shape[0] >= self.PREFILL_AR_BF16_MIN_ROWS and not _PREFILL_AR_FP32):
+            y = partial.to(torch.bfloat16)
+            dist.all_reduce(y, group=self.ctx.group)
+            return y
+        return self.all_reduce(partial)
 
     def cp_merge_heads(self, ops, o: torch.Tensor, lse: torch.Tensor):
         """Merge per-rank attention partials over all heads and return this rank's head
