@@ -348,7 +348,7 @@ def test_sparse_mla_and_v_expand(which):
     close(ops.v_expand(o, w_v), ref.v_expand(o, w_v), what="v_expand")
 
 
-@pytest.mark.parametrize("h,T,q_scale", [(8, 3, 0.3), (8, 40, 4.0), (16, 3, 4.0), (12, 5, 0.3), (8, 320, 1.0)])
+@pytest.mark.parametrize("h,T,q_scale", [(8, 3, 0.3), (8, 40, 4.0), (16, 3, 4.0), (12, 5, 0.3), (8, 320, 1.0), (40, 2, 1.0)])
 def test_sparse_mla_keys_on_m(h, T, q_scale):
     """The keys-on-M sparse MLA kernel (kv_lora_rank a multiple of 128) at the production top-k: full, ragged and
     empty key lists, one or several key splits, 8 / 12 / 16 heads per CTA; `q_scale` 4 makes later chunks exceed the
@@ -387,12 +387,12 @@ def test_sparse_mla_keys_on_m(h, T, q_scale):
 
 
 @pytest.mark.parametrize("h,T,q_scale,kv_scale", [(8, 160, 1.0, 2.0), (8, 300, 4.0, 2.0), (16, 150, 1.0, 0.05), (4, 310, 0.3, 30.0),
-                                                  (8, 200, 2.0, 1.0)])
+                                                  (8, 200, 2.0, 1.0), (32, 80, 1.0, 1.0)])
 def test_sparse_mla_prefill_on_tcgen05(h, T, q_scale, kv_scale):
     """Prefill-sized sparse MLA (no key split) runs on tcgen05 straight from the e4m3 cache rows: query and
     probabilities as two e4m3 terms, code tiles read K-major for the scores and MN-major for the values.  Full, ragged,
     one-key and empty key lists; `q_scale` 4 raises the softmax reference in later tiles (accumulators folded into
-    registers); small and large cache scales; 4, 8 and 16 heads (one or two head groups).  Against the fp32 definition and
+    registers); small and large cache scales; 4, 8 and 16 heads (one, two or four head groups).  Against the fp32 definition and
     against the mma.sync kernel through the switch."""
     from slopllm_b200.ops import native as N
     from slopllm_b200.ops import tcgen05
